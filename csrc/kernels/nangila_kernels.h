@@ -1,0 +1,72 @@
+// C interface of libnangila_kernels.so: every sm_100a kernel of the framework behind a plain C
+// launcher that takes raw device pointers and a stream, so it can be driven from the torch glue,
+// from ctypes, or from another runtime. All launchers return a cudaError_t value (0 = success);
+// none of them allocates, frees or synchronizes.
+#pragma once
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NANGILA_MAX_RANKS 16   /* ranks in one exchange group */
+#define NANGILA_MAX_VRANKS 8   /* ranks emulated inside ONE launch (single-GPU loopback world) */
+
+enum NangilaDType { NANGILA_F32 = 0, NANGILA_F16 = 1, NANGILA_BF16 = 2 };
+
+/* ---- fused prediction-residual bucket exchange -------------------------------------------------
+ * One launch per gradient bucket does, for every rank r of the group:
+ *   phase 1  e = g + ef - kappa g_hat,  g_hat = curr + mu (curr - prev); block-INT4 quantize e; store the
+ *            packed chunk into the chunk owner's receive slot over NVLink; ef <- e - deq(q)
+ *   phase 2  (owner of a chunk) wait for all ranks' slots, dequantize-accumulate, average, add the
+ *            owner's second error memory, re-quantize, store the result into every rank's slot
+ *   phase 3  wait for the reduced chunk, out = mean(kappa) g_hat + deq; write the bucket and the new history.
+ * mode 1 (uncompressed) moves the raw values instead and produces the exact mean; it is used for
+ * warm-up, Safe-Mode fallback and forced re-synchronisation, and also maintains the history.
+ *
+ * Multi-GPU: nvr = 1, rank0 = this rank, `region[r]` = rank r's mapping of the bucket's symmetric
+ * region. Single-GPU loopback: nvr = world, rank0 = 0, grid.y = nvr, launched cooperatively.
+ */
+typedef struct NangilaPredResParams {
+  void* grad[NANGILA_MAX_VRANKS];      /* in/out: bucket, n elements of grad_dtype */
+  void* prev[NANGILA_MAX_VRANKS];      /* in: g(t-1); out: new g(t) (caller swaps prev/curr after) */
+  void* curr[NANGILA_MAX_VRANKS];      /* in: g(t) */
+  void* ef[NANGILA_MAX_VRANKS];        /* in/out: error feedback, n elements of state_dtype (may be NULL) */
+  void* ef2[NANGILA_MAX_VRANKS];       /* in/out: owner-side error memory, owned_chunks*chunk elems (may be NULL) */
+  float* stats[NANGILA_MAX_VRANKS];    /* += {sum e^2, sum g^2, sum (g - g_hat)^2, sum ef_new^2}; may be NULL */
+  uint32_t* status[NANGILA_MAX_VRANKS];/* 8 words, see comm/signal.cuh; must be zero before launch */
+  uint8_t* region[NANGILA_MAX_RANKS];  /* symmetric region of every rank of the group */
+  uint64_t recv1_off, recv2_off, flag1_off, flag2_off; /* byte offsets inside a region */
+  int64_t n;                           /* elements in the bucket */
+  int32_t world, rank0, nvr;
+  int32_t chunk_elems;                 /* multiple of 4096 */
+  int32_t nchunks;                     /* ceil(n / chunk_elems) */
+  int32_t grad_dtype, state_dtype;     /* NangilaDType; state is F32 or BF16 */
+  int32_t mode;                        /* 0 compressed, 1 uncompressed */
+  int32_t stochastic;                  /* 0: round to nearest (tests), 1: stochastic rounding */
+  uint32_t epoch;                      /* strictly increasing per launch on this bucket, never 0 */
+  uint32_t seed, step, bucket_id;
+  float mu;
+  float pred_gain[NANGILA_MAX_VRANKS]; /* kappa in [0,1]: e = g + ef - kappa * g_hat; ranks may differ, the
+                                          reconstruction uses the mean of all ranks' values */
+  uint64_t timeout_ns;
+  int32_t grid_x;                      /* CTAs per rank */
+} NangilaPredResParams;
+
+/* Bytes one rank's symmetric region must have for a bucket. */
+uint64_t nangila_predres_region_bytes(int64_t n, int32_t world, int32_t chunk_elems, int32_t grad_dtype,
+                                      uint64_t* recv1_off, uint64_t* recv2_off, uint64_t* flag1_off,
+                                      uint64_t* flag2_off);
+int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_t stream);
+
+/* ---- single-scale compatibility kernels (reference signature: predict.cu / reconstruct.cu) ------- */
+int nangila_predict_quantize_gamma(const float* grad, const float* g_curr, const float* g_prev, float mu,
+                                   float gamma, uint8_t* out, int64_t n, uint32_t step, uint32_t layer_id,
+                                   cudaStream_t stream);
+int nangila_dequant_reconstruct_gamma(const uint8_t* packed, const float* g_curr, const float* g_prev, float mu,
+                                      float gamma, float* out, int64_t n, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,209 @@
+// Device helpers shared by the fused kernels: 16-element vector loads/stores for fp32 / bf16 / fp16
+// tensors, the counter-based random generator, and the block-scaled INT4 quantizer (64 elements per
+// scale, scale stored as bf16 rounded up so that |x / scale| <= 7 always holds).
+//
+// The rounding replaces the reference's host quantizer (nangila-core/src/quantizer.rs:106-214, one
+// scale per tensor, biased rounding of negative values) and its device twin
+// (nangila-cuda/src/kernels/predict.cu:30-112): here q = floor(x / scale + u) with u uniform in
+// [0, 1), which is unbiased for either sign, and u = 0.5 gives round-to-nearest for tests.
+// Nibble order is the reference's: byte k holds element 2k in its low and 2k+1 in its high nibble,
+// two's complement.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+
+namespace nangila {
+namespace dev {
+
+constexpr int kQuantBlock = 64;      // elements per scale
+constexpr int kElemsPerThread = 16;  // one thread quantizes 16 consecutive elements
+constexpr int kLanesPerBlock = kQuantBlock / kElemsPerThread;  // 4 lanes share one scale
+
+__host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+// One key per (seed, step, bucket, rank, phase); elements are then addressed by their pair index.
+__host__ __device__ __forceinline__ uint32_t make_key(uint32_t seed, uint32_t step, uint32_t bucket, uint32_t rank,
+                                             uint32_t phase) {
+  uint32_t k = mix32(seed ^ 0x9E3779B9u);
+  k = mix32(k + step * 0x85ebca6bu);
+  k = mix32(k + bucket * 0xc2b2ae35u);
+  k = mix32(k + rank * 0x27d4eb2fu + phase * 0x165667b1u);
+  return k;
+}
+
+// ---- 16-element loads / stores --------------------------------------------------------------------
+template <typename T>
+struct Vec16;
+
+template <>
+struct Vec16<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[16]) {
+    const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 a = q[i];
+      v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
+    }
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[16]) {
+    float4* q = reinterpret_cast<float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  }
+  static __device__ __forceinline__ float to_float(float x) { return x; }
+  static __device__ __forceinline__ float from_float(float x) { return x; }
+};
+
+template <>
+struct Vec16<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[16]) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 a = q[i];
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+        v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[16]) {
+    uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      q[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+};
+
+template <>
+struct Vec16<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[16]) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 a = q[i];
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        v[8 * i + 2 * j] = f.x;
+        v[8 * i + 2 * j + 1] = f.y;
+      }
+    }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&v)[16]) {
+    uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __half2 h = __floats2half2_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      q[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
+};
+
+// Load 16 elements starting at element `base` of a tensor of `n` elements; elements at or beyond n
+// read as 0. `p` must be 16-byte aligned and `base` a multiple of 16.
+template <typename T>
+__device__ __forceinline__ void load16_guarded(const T* p, int64_t base, int64_t n, float (&v)[16]) {
+  if (base + 16 <= n) {
+    Vec16<T>::load(p + base, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = (base + i < n) ? Vec16<T>::to_float(p[base + i]) : 0.0f;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store16_guarded(T* p, int64_t base, int64_t n, const float (&v)[16]) {
+  if (base + 16 <= n) {
+    Vec16<T>::store(p + base, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (base + i < n) p[base + i] = Vec16<T>::from_float(v[i]);
+  }
+}
+
+__device__ __forceinline__ float sanitize(float x) { return (fabsf(x) <= 3.0e38f) ? x : 0.0f; }  // NaN/Inf -> 0
+
+// bf16 bit pattern of the smallest bf16 >= s (s >= 0, finite).
+__device__ __forceinline__ uint32_t bf16_ceil_bits(float s) {
+  uint32_t b = __float_as_uint(s);
+  b = (b + 0xffffu) >> 16;
+  return b >= 0x7f80u ? 0x7f7fu : b;
+}
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
+
+// Quantize the 16 values of this lane. The four lanes (lane & ~3 .. lane | 3) that hold one
+// 64-element block must call this together (it shuffles). On return `e` holds the quantization error
+// e - q * scale, `packed` the 16 nibbles and `scale_bits` the block's bf16 scale.
+// `pair0` = (global element index of e[0]) / 2, the counter for the random numbers.
+__device__ __forceinline__ void quantize16(float (&e)[16], uint32_t key, uint32_t pair0, bool stochastic,
+                                           uint2& packed, uint32_t& scale_bits, float (&deq)[16]) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(e[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  scale_bits = bf16_ceil_bits(__fdiv_rn(amax, 7.0f));
+  const float s = bf16_bits_to_float(scale_bits);
+  const bool live = s > 1e-30f;
+  const float inv = live ? __frcp_rn(s) : 0.0f;
+  if (!live) scale_bits = 0;
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    float u0 = 0.5f, u1 = 0.5f;
+    if (stochastic) {
+      uint32_t h = mix32(key + (pair0 + uint32_t(i >> 1)) * 0x9E3779B9u);
+      u0 = float(h & 0xffffu) * (1.0f / 65536.0f);
+      u1 = float(h >> 16) * (1.0f / 65536.0f);
+    }
+    float q0 = fminf(fmaxf(floorf(__fmaf_rn(e[i], inv, u0)), -8.0f), 7.0f);
+    float q1 = fminf(fmaxf(floorf(__fmaf_rn(e[i + 1], inv, u1)), -8.0f), 7.0f);
+    deq[i] = live ? q0 * s : 0.0f;
+    deq[i + 1] = live ? q1 * s : 0.0f;
+    e[i] -= deq[i];
+    e[i + 1] -= deq[i + 1];
+    uint32_t n0 = uint32_t(int(q0)) & 0xfu, n1 = uint32_t(int(q1)) & 0xfu;
+    w[i >> 3] |= (n0 << (4 * (i & 7))) | (n1 << (4 * ((i + 1) & 7)));
+  }
+  packed = make_uint2(w[0], w[1]);
+}
+
+// 16 nibbles (in `packed`) times `scale`, added to acc.
+__device__ __forceinline__ void dequant16_add(const uint2 packed, float scale, float (&acc)[16]) {
+  const uint32_t w[2] = {packed.x, packed.y};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    int q = int(w[i >> 3] << (28 - 4 * (i & 7))) >> 28;
+    acc[i] = __fmaf_rn(float(q), scale, acc[i]);
+  }
+}
+
+}  // namespace dev
+}  // namespace nangila

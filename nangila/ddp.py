@@ -1,0 +1,477 @@
+"""Nangila DDP communication hook.
+
+Usage (same as the reference, python/nangila/ddp.py:15-33)::
+
+    from nangila.ddp import register_nangila_hook
+    model = DDP(model, device_ids=[local_rank])
+    hook = register_nangila_hook(model, threshold=0.95, warmup_steps=100)
+    for batch in loader:
+        loss = model(batch); loss.backward(); optimizer.step()
+        hook.step()
+
+What happens per gradient bucket:
+
+* CUDA buckets: one fused sm_100a kernel launch on a side stream does predict-subtract, error
+  feedback, block-INT4 quantization, the exchange over NVLink peer memory, dequantize-accumulate and
+  the history update (``nangila.parallel.predres_engine``). During the first ``warmup_steps`` steps
+  the same kernel runs in its uncompressed mode (exact mean). DGC and PowerSGD buckets take their own
+  fused kernels (``nangila.parallel.dgc_engine`` / ``powersgd_engine``).
+* CPU buckets (gloo): the C++ core compresses to packets, packets are all-gathered, every rank
+  reconstructs and averages (the reference's transport, ddp.py:286-347), with the warm-up
+  all-reduce done as SUM + divide because gloo has no AVG.
+
+Differences from the reference that a user can observe: the keyword arguments really reach the
+core (the reference built a config and then dropped it, ddp.py:142-151); compression starts at
+``warmup_steps`` (the reference's core kept its own 1000+100-step warm-up); bucket state is keyed by
+``bucket.index()`` instead of a call counter (ddp.py:180-181); the predictor-hash exchange carries
+the 64-bit hash as two 32-bit halves (ddp.py:392 overflowed a signed 64-bit tensor).
+"""
+
+
+import os
+import warnings
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+from torch.nn.parallel import DistributedDataParallel as DDP
+
+from ._C import CompressorType, NangilaConfig, NangilaHook, SyncMode
+
+NANGILA_AVAILABLE = True
+
+try:  # the C++ comm-hook callable lives in the torch glue
+    from ._cuda import NangilaDDPHook as NangilaCppHook  # type: ignore
+    CPP_HOOK_AVAILABLE = True
+except Exception:  # pragma: no cover - glue not built or built without the hook
+    NangilaCppHook = None
+    CPP_HOOK_AVAILABLE = False
+
+try:
+    from torch.distributed import GradBucket
+except ImportError:  # pragma: no cover
+    GradBucket = Any
+
+_LOG = os.environ.get("NANGILA_LOG", "warn").lower()
+
+
+def _log(msg: str) -> None:
+    if _LOG in ("info", "debug") and (not dist.is_initialized() or dist.get_rank() == 0):
+        print(f"[nangila] {msg}", flush=True)
+
+
+def _warn_if_advanced_ddp_options(compressor_type: int, dgc_sparsity: float, power_sgd_rank: int) -> None:
+    if int(compressor_type) != 0 or dgc_sparsity != 0.999 or power_sgd_rank != 1:
+        warnings.warn(
+            "Non-default DDP compressor tuning options are available for compatibility but are "
+            "excluded from the Nangila v0.1 stable support contract.",
+            stacklevel=3,
+        )
+
+
+def _validate_sync_mode(sync_mode: Any) -> int:
+    try:
+        m = int(sync_mode)
+    except Exception:
+        raise ValueError(f"Invalid sync_mode {sync_mode!r}. Use SyncMode.ASYNC (0), ALWAYS (1), or PERIODIC (2)")
+    if m not in (0, 1, 2):
+        raise ValueError(f"Invalid sync_mode {sync_mode!r}. Use SyncMode.ASYNC (0), ALWAYS (1), or PERIODIC (2)")
+    return m
+
+
+class NangilaDDPHook:
+    """DDP communication hook (``ddp_model.register_comm_hook(None, hook)``).
+
+    Args mirror the reference (ddp.py:100-112). ``num_layers`` is only the size of the all-Driver
+    mask of the host-side state machine; device state is created per bucket on first use.
+    Extra keyword-only knobs: ``momentum``, ``error_feedback``, ``stochastic`` (False = round to
+    nearest, for reproducible tests), ``dgc_momentum`` (momentum correction factor of the DGC path).
+    """
+
+    def __init__(
+        self,
+        process_group: Optional[Any] = None,
+        threshold: float = 0.95,
+        warmup_steps: int = 100,
+        num_layers: int = 1000,
+        sync_mode: int = 2,
+        enable_gpu_native: bool = False,
+        *,
+        compressor_type: int = 0,
+        dgc_sparsity: float = 0.999,
+        power_sgd_rank: int = 1,
+        momentum: float = 0.9,
+        error_feedback: bool = True,
+        stochastic: bool = True,
+        dgc_momentum: float = 0.9,
+        total_numel: Optional[int] = None,
+    ):
+        _warn_if_advanced_ddp_options(compressor_type, dgc_sparsity, power_sgd_rank)
+        self.process_group = process_group or dist.distributed_c10d._get_default_group()
+        self.threshold = threshold
+        self.warmup_steps = int(warmup_steps)
+        self.step_count = 0
+        self.sync_mode = _validate_sync_mode(sync_mode)
+        self.enable_gpu_native = enable_gpu_native
+        self.compressor_type = int(compressor_type)
+        self.dgc_sparsity = float(dgc_sparsity)
+        self.power_sgd_rank = int(power_sgd_rank)
+        self.momentum = float(momentum)
+        self.error_feedback = error_feedback
+        self.stochastic = stochastic
+        self.dgc_momentum = float(dgc_momentum)
+        self.config = NangilaConfig(
+            momentum=momentum, threshold=threshold, warmup_steps=self.warmup_steps, shadow_run_steps=0,
+            compressor_type=self.compressor_type, dgc_sparsity=dgc_sparsity, power_sgd_rank=power_sgd_rank,
+        )
+        self.__name__ = "nangila_hook"
+        self.__qualname__ = "nangila_hook"
+        self.hook = NangilaHook.all_drivers(max(int(num_layers), 1), self.config)
+        self.layer_counter = 0
+        self.total_original_bytes = 0
+        self.total_compressed_bytes = 0
+        self.world_size = dist.get_world_size(self.process_group)
+        self.rank = dist.get_rank(self.process_group)
+        self._total_numel = total_numel
+        self._engine = None          # PredResEngine, created on the first CUDA bucket
+        self._dgc_engine = None
+        self._psgd_engine = None
+        self._bucket_calls = 0
+        self._force_uncompressed = False
+        self._param_ids: Dict[int, int] = {}
+        _log(f"DDP hook: sync_mode={SyncMode(self.sync_mode)!r} compressor={self.compressor_type} "
+             f"warmup={self.warmup_steps} world={self.world_size}")
+
+    # ------------------------------------------------------------------------------------------
+    def __call__(self, state: Any, bucket: GradBucket) -> torch.futures.Future[torch.Tensor]:
+        self.layer_counter += 1
+        tensor = bucket.buffer()
+        try:
+            index = int(bucket.index())
+        except Exception:
+            index = self.layer_counter - 1
+        if tensor.is_cuda:
+            return self._run_cuda(bucket, tensor, index)
+        return self._run_cpu(bucket, tensor, index)
+
+    @property
+    def compressing(self) -> bool:
+        return (self.step_count >= self.warmup_steps and not self._force_uncompressed
+                and not self.hook.is_paused())
+
+    # ---- CUDA path -----------------------------------------------------------------------------
+    def _ensure_engine(self, device: torch.device):
+        if self._engine is None:
+            from .parallel.predres_engine import PredResEngine
+            from .parallel.symm import SymmArena
+
+            arena = SymmArena(self.process_group, device)
+            if self._total_numel:
+                # room for every bucket's exchange region plus flags and alignment slack
+                arena.reserve(int(self._total_numel * 1.02) + (8 << 20))
+            self._engine = PredResEngine(arena, device, momentum=self.momentum, error_feedback=self.error_feedback,
+                                         stochastic=self.stochastic)
+            self.hook.set_gpu_mode(True)
+        return self._engine
+
+    def _run_cuda(self, bucket: GradBucket, tensor: torch.Tensor, index: int) -> torch.futures.Future:
+        engine = self._ensure_engine(tensor.device)
+        compressing = self.compressing
+        ctype = self.compressor_type
+        if compressing and ctype == 1:
+            fut = self._run_cuda_dgc(bucket, tensor, index)
+        elif compressing and ctype == 2:
+            fut = self._run_cuda_powersgd(bucket, tensor, index)
+        else:
+            st = engine.reduce(index, [tensor], compressed=compressing and ctype == 0, step=self.step_count)
+            nbytes = tensor.numel() * tensor.element_size()
+            self.total_original_bytes += nbytes
+            self.total_compressed_bytes += (int(tensor.numel() * (0.5 + 2.0 / 64.0)) if compressing else nbytes)
+            fut = self._stream_future(engine.stream, tensor)
+        self._bucket_calls += 1
+        if self.sync_mode == 1 or (self.sync_mode == 2 and self._bucket_calls % 100 == 0):
+            self._check_device_status()
+        return fut
+
+    @staticmethod
+    def _stream_future(stream: Optional[torch.cuda.Stream], tensor: torch.Tensor) -> torch.futures.Future:
+        # Completing the future while the exchange stream is current records the dependency, so
+        # whoever waits on it (DDP's finalize) orders its stream after the kernel without a host sync.
+        fut: torch.futures.Future = torch.futures.Future(devices=[tensor.device])
+        if stream is not None:
+            with torch.cuda.stream(stream):
+                fut.set_result(tensor)
+        else:
+            fut.set_result(tensor)
+        return fut
+
+    def _run_cuda_dgc(self, bucket, tensor, index):
+        if self._dgc_engine is None:
+            from .parallel.dgc_engine import DGCEngine
+
+            self._dgc_engine = DGCEngine(self._engine.arena, tensor.device, sparsity=self.dgc_sparsity,
+                                         momentum=self.dgc_momentum, stream=self._engine.stream)
+        k = self._dgc_engine.reduce(index, tensor)
+        self.total_original_bytes += tensor.numel() * tensor.element_size()
+        self.total_compressed_bytes += k * 8
+        return self._stream_future(self._engine.stream, tensor)
+
+    def _run_cuda_powersgd(self, bucket, tensor, index):
+        if self._psgd_engine is None:
+            from .parallel.powersgd_engine import PowerSGDEngine
+
+            self._psgd_engine = PowerSGDEngine(self._engine.arena, tensor.device, rank=self.power_sgd_rank,
+                                               stream=self._engine.stream, group=self.process_group)
+        sent = self._psgd_engine.reduce(index, bucket, tensor)
+        self.total_original_bytes += tensor.numel() * tensor.element_size()
+        self.total_compressed_bytes += sent
+        return self._stream_future(self._engine.stream, tensor)
+
+    def _check_device_status(self) -> None:
+        if self._engine is None:
+            return
+        try:
+            self._engine.check_status()
+        except RuntimeError:
+            # leave the hook usable: the next buckets go through the uncompressed mode and re-seed
+            # the history on every rank (FORCE_SYNC semantics of the packet protocol)
+            self._force_uncompressed = True
+            for lid in range(min(10, self.hook.get_stats()["num_drivers"])):
+                self.hook.trigger_recovery(lid)
+            raise
+
+    # ---- CPU path (gloo) -------------------------------------------------------------------------
+    def _run_cpu(self, bucket: GradBucket, tensor: torch.Tensor, index: int) -> torch.futures.Future:
+        world = self.world_size
+        layer_id = index
+        if self.step_count < self.warmup_steps or self.hook.is_paused():
+            work = dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.process_group, async_op=True)
+            result: torch.futures.Future = torch.futures.Future()
+            seed_history = self.step_count + 2 >= self.warmup_steps
+
+            def _done(_):
+                tensor.div_(world)
+                if seed_history:
+                    self.hook.update(layer_id, tensor.detach().float().contiguous().numpy().reshape(-1))
+                result.set_result(tensor)
+
+            work.get_future().then(_done)
+            nbytes = tensor.numel() * tensor.element_size()
+            self.total_original_bytes += nbytes
+            self.total_compressed_bytes += nbytes
+            return result
+
+        if self.compressor_type == 2:
+            return self._run_cpu_per_parameter(bucket, tensor, index)
+        flat = tensor.detach().float().contiguous().numpy().reshape(-1)
+        averaged = self._exchange_cpu(layer_id % max(self.hook.get_stats()["num_drivers"], 1), flat, tensor.device)
+        tensor.copy_(torch.from_numpy(averaged).to(tensor.dtype).view_as(tensor))
+        fut: torch.futures.Future = torch.futures.Future()
+        fut.set_result(tensor)
+        return fut
+
+    def _exchange_cpu(self, layer_id: int, flat: np.ndarray, device: torch.device) -> np.ndarray:
+        """Compress -> all-gather packets -> reconstruct every rank's gradient -> mean -> feed the
+        mean back to the predictor. ``flat`` may carry a matrix shape; the result is 1-D."""
+        world = self.world_size
+        self.total_original_bytes += flat.nbytes
+        packet = bytes(self.hook.compress(layer_id, flat))
+        self.total_compressed_bytes += len(packet)
+        local_size = torch.tensor([len(packet)], dtype=torch.long, device=device)
+        sizes = [torch.empty_like(local_size) for _ in range(world)]
+        dist.all_gather(sizes, local_size, group=self.process_group)
+        sizes_i = [int(s.item()) for s in sizes]
+        max_size = max(sizes_i)
+        padded = torch.zeros(max_size, dtype=torch.uint8, device=device)
+        padded[:len(packet)] = torch.frombuffer(bytearray(packet), dtype=torch.uint8)
+        gathered = [torch.empty(max_size, dtype=torch.uint8, device=device) for _ in range(world)]
+        dist.all_gather(gathered, padded, group=self.process_group)
+        acc = np.zeros(flat.size, dtype=np.float64)
+        for r in range(world):
+            data = bytes(gathered[r][:sizes_i[r]].cpu().numpy())
+            rec = self.hook.decompress_gathered(layer_id, data)
+            if rec.shape[0] != flat.size:
+                raise RuntimeError(f"nangila: rank {r} sent {rec.shape[0]} elements for layer {layer_id}, "
+                                   f"expected {flat.size}")
+            acc += rec
+        averaged = (acc / world).astype(np.float32)
+        self.hook.update(layer_id, averaged)
+        return averaged
+
+    def _run_cpu_per_parameter(self, bucket: GradBucket, tensor: torch.Tensor, index: int) -> torch.futures.Future:
+        """PowerSGD needs matrix-shaped gradients: every parameter of the bucket with two or more
+        dimensions goes through the compressor with its own shape (layer id = position of the
+        parameter in the model); the remaining small / 1-D gradients are averaged uncompressed."""
+        grads = bucket.gradients()
+        try:
+            params = bucket.parameters()
+        except Exception:
+            params = [None] * len(grads)
+        nlayers = max(self.hook.get_stats()["num_drivers"], 1)
+        raw: List[torch.Tensor] = []
+        for pos, g in enumerate(grads):
+            if g.dim() >= 2 and g.numel() >= 256:
+                prm = params[pos]
+                lid = self._param_ids.get(id(prm), (index * 4096 + pos)) % nlayers
+                arr = g.detach().float().contiguous().numpy()
+                averaged = self._exchange_cpu(lid, arr, g.device)
+                g.copy_(torch.from_numpy(averaged).view_as(g).to(g.dtype))
+            else:
+                raw.append(g)
+        if raw:
+            flat = torch.cat([g.reshape(-1) for g in raw])
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.process_group)
+            flat.div_(self.world_size)
+            off = 0
+            for g in raw:
+                g.copy_(flat[off:off + g.numel()].view_as(g))
+                off += g.numel()
+            self.total_original_bytes += flat.numel() * flat.element_size()
+            self.total_compressed_bytes += flat.numel() * flat.element_size()
+        fut: torch.futures.Future = torch.futures.Future()
+        fut.set_result(tensor)
+        return fut
+
+    # ------------------------------------------------------------------------------------------
+    def step(self) -> None:
+        """Call after each optimizer step."""
+        self.step_count += 1
+        self.layer_counter = 0
+        self.hook.step()
+        if self._engine is not None:
+            self._engine.end_step()
+        if self._force_uncompressed:
+            self._force_uncompressed = False  # one uncompressed step re-seeded the history everywhere
+        if self.step_count % 10 == 0 and self.step_count > self.warmup_steps and _LOG in ("info", "debug"):
+            ratio = self.compression_ratio
+            if ratio > 1.0:
+                _log(f"[Step {self.step_count}] Compression: {self.total_original_bytes / 1e6:.1f} MB -> "
+                     f"{self.total_compressed_bytes / 1e6:.1f} MB ({ratio:.1f}x)")
+        if self.step_count % 100 == 0 and self.step_count > 0:
+            self._verify_predictor_hash()
+
+    def get_stats(self) -> dict:
+        stats = dict(self.hook.get_stats())
+        stats["step"] = self.step_count
+        stats["compression_enabled"] = self.compressing
+        stats["total_original_bytes"] = self.total_original_bytes
+        stats["total_compressed_bytes"] = self.total_compressed_bytes
+        if self.total_original_bytes > 0:
+            stats["overall_compression_ratio"] = self.total_original_bytes / max(self.total_compressed_bytes, 1)
+        if self._engine is not None:
+            stats["kernel_launches"] = self._engine.launches
+            errs = {}
+            for idx, st in self._engine.buckets.items():
+                if st.compressed_calls:
+                    errs[idx] = self._engine.prediction_error(idx)
+            stats["prediction_error_per_bucket"] = errs
+        return stats
+
+    @property
+    def compression_ratio(self) -> float:
+        if self.total_compressed_bytes == 0:
+            return 1.0
+        return self.total_original_bytes / self.total_compressed_bytes
+
+    def state_hash(self) -> int:
+        """64-bit hash of the predictor state on this rank (host core, or a device reduction of the
+        bucket histories when the CUDA path is active)."""
+        if self._engine is not None and self._engine.buckets:
+            h = 0
+            for idx in sorted(self._engine.buckets):
+                st = self._engine.buckets[idx]
+                c = st.curr[0]
+                v = c.view(torch.int16 if c.element_size() == 2 else torch.int32).to(torch.int64)
+                w = torch.arange(1, v.numel() + 1, device=v.device, dtype=torch.int64)
+                h = (h * 1000003 + int(((v * w) & 0x7FFFFFFF).sum().item()) + idx) & 0xFFFFFFFFFFFFFFFF
+            return h
+        return int(self.hook.predictor_hash())
+
+    def _verify_predictor_hash(self) -> bool:
+        """All ranks must hold the same predictor state; on a mismatch the next step runs
+        uncompressed, which re-seeds the history everywhere."""
+        try:
+            h = self.state_hash()
+            dev = "cpu"
+            if self._engine is not None:
+                dev = self._engine.device
+            t = torch.tensor([h & 0xFFFFFFFF, (h >> 32) & 0xFFFFFFFF], dtype=torch.int64, device=dev)
+            gathered = [torch.zeros_like(t) for _ in range(self.world_size)]
+            dist.all_gather(gathered, t, group=self.process_group)
+            vals = [(int(g[0].item()) | (int(g[1].item()) << 32)) for g in gathered]
+            if all(v == vals[0] for v in vals):
+                return True
+            warnings.warn(f"nangila: predictor state hash mismatch at step {self.step_count}: {vals}")
+            self._force_uncompressed = True
+            self.hook.verify_hash(vals[0] ^ 1 if vals[0] == h else vals[0])
+            return False
+        except Exception as exc:  # pragma: no cover
+            warnings.warn(f"nangila: hash verification failed: {exc!r}")
+            return True
+
+    # ---- checkpoint ------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        sd = {"step_count": self.step_count, "total_original_bytes": self.total_original_bytes,
+              "total_compressed_bytes": self.total_compressed_bytes,
+              "core": bytes(self.hook.make_checkpoint().to_bytes())}
+        if self._engine is not None:
+            sd["predres"] = self._engine.state_dict()
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        from ._C import NangilaCheckpoint
+
+        self.step_count = int(sd["step_count"])
+        self.total_original_bytes = int(sd.get("total_original_bytes", 0))
+        self.total_compressed_bytes = int(sd.get("total_compressed_bytes", 0))
+        self.hook.restore_checkpoint(NangilaCheckpoint.from_bytes(sd["core"]))
+        if self._engine is not None and "predres" in sd:
+            self._engine.load_state_dict(sd["predres"])
+
+    def enable_safe_mode(self, config=None) -> None:
+        from ._C import SafeModeConfig
+
+        self.hook.enable_safe_mode(config or SafeModeConfig())
+
+    def report_validation_loss(self, loss: float):
+        return self.hook.report_validation_loss(float(loss))
+
+
+def register_nangila_hook(
+    ddp_model: DDP,
+    threshold: float = 0.95,
+    warmup_steps: int = 100,
+    prefer_cpp: bool = True,
+    sync_mode: int = 2,
+    enable_gpu_native: bool = False,
+    *,
+    compressor_type: int = 0,
+    dgc_sparsity: float = 0.999,
+    power_sgd_rank: int = 1,
+    **extra: Any,
+) -> "NangilaDDPHook":
+    """Register the Nangila compression hook on a DDP model and return it (call ``.step()`` after
+    every optimizer step). Signature and defaults as the reference (ddp.py:415-426)."""
+    if not isinstance(ddp_model, DDP):
+        raise TypeError(f"Expected DistributedDataParallel, got {type(ddp_model)}")
+    _warn_if_advanced_ddp_options(compressor_type, dgc_sparsity, power_sgd_rank)
+    sync_mode = _validate_sync_mode(sync_mode)
+    params = [p for p in ddp_model.parameters() if p.requires_grad]
+    num_layers = len(list(ddp_model.parameters()))
+    # bytes of symmetric memory the bucket regions will need: two areas per bucket, each holding the
+    # larger of the raw and the packed form of every element
+    total = sum(p.numel() * (8 if p.element_size() >= 4 else 4) for p in params)
+    hook = NangilaDDPHook(
+        process_group=ddp_model.process_group, threshold=threshold, warmup_steps=warmup_steps,
+        num_layers=num_layers, sync_mode=sync_mode, enable_gpu_native=enable_gpu_native,
+        compressor_type=compressor_type, dgc_sparsity=dgc_sparsity, power_sgd_rank=power_sgd_rank,
+        total_numel=total, **extra,
+    )
+    hook.prefer_cpp = bool(prefer_cpp)
+    hook._param_ids = {id(p): i for i, p in enumerate(ddp_model.parameters())}
+    ddp_model.register_comm_hook(state=None, hook=hook)
+    return hook
+
+
+__all__ = ["NangilaDDPHook", "register_nangila_hook", "CPP_HOOK_AVAILABLE", "NangilaCppHook"]

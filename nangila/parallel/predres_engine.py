@@ -1,0 +1,288 @@
+"""Host driver of the fused prediction-residual bucket kernel.
+
+One :class:`PredResEngine` per process group keeps, for every gradient bucket it has seen, the
+device state the kernel needs (two-step history, error-feedback memories, the bucket's symmetric
+exchange region, its epoch counter) and queues exactly one kernel launch per bucket call on a
+dedicated high-priority stream, so the exchange overlaps with the rest of backward.
+
+Replaces the per-bucket sequence of the reference hook — compress kernel, two all-gathers with host
+synchronisation, one reconstruct kernel per rank, mean, history copies (python/nangila/ddp.py:236-284,
+nangila_ddp/src/ddp_hook.cpp:104-335) — and its per-layer GPU history buffers with pointer-swap
+rotation (nangila-cuda/src/state.rs:99-184).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .symm import LoopbackArena, Region, SymmArena
+
+_DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+STATUS_MESSAGES = {
+    2: "timeout in phase 2: a chunk owner did not receive every rank's contribution",
+    3: "timeout in phase 3: a reduced chunk did not arrive from its owner",
+    4: "timeout in an intra-GPU grid barrier",
+    5: "bad argument",
+}
+
+
+def _glue():
+    """The compiled torch glue. Raises with a clear message when it has not been built."""
+    try:
+        from .. import _cuda  # type: ignore
+    except ImportError as exc:  # pragma: no cover
+        raise RuntimeError(
+            "nangila: the CUDA extension (nangila/_cuda*.so) is not built; run `python -m nangila._build`"
+        ) from exc
+    return _cuda
+
+
+def default_chunk_elems(n: int, world: int) -> int:
+    """Chunk size (elements): 16384 for large buckets, smaller when the bucket would otherwise give
+    fewer chunks than 4 per rank, never below 4096."""
+    env = os.environ.get("NANGILA_CHUNK")
+    if env:
+        return int(env)
+    c = 16384
+    while c > 4096 and (n + c - 1) // c < 4 * world:
+        c //= 2
+    return c
+
+
+@dataclass
+class BucketState:
+    n: int
+    grad_dtype: torch.dtype
+    state_dtype: torch.dtype
+    chunk: int
+    region: Region
+    layout: Tuple[int, int, int, int]
+    prev: List[torch.Tensor]
+    curr: List[torch.Tensor]
+    ef: List[Optional[torch.Tensor]]
+    ef2: List[Optional[torch.Tensor]]
+    stats: List[torch.Tensor]
+    slot: int = 0                       # row of this bucket in the engine's statistics table
+    pred_gain: float = 1.0              # kappa: 1 = full momentum prediction, 0 = none
+    miss_ema: Optional[float] = None    # running ||g - g_hat||^2 / ||g||^2
+    cooldown: int = 0
+    totals: List[float] = field(default_factory=lambda: [0.0, 0.0, 0.0, 0.0])
+    epoch: int = 0
+    calls: int = 0
+    compressed_calls: int = 0
+    extra: dict = field(default_factory=dict)
+
+    def swap(self) -> None:
+        self.prev, self.curr = self.curr, self.prev
+
+
+class PredResEngine:
+    """Drives ``nangila_predres_launch``.
+
+    ``arena`` is a :class:`SymmArena` (real group; one rank per process) or a :class:`LoopbackArena`
+    (all ``world`` ranks emulated in one launch on this device).
+    """
+
+    def __init__(self, arena, device: torch.device, momentum: float = 0.9, error_feedback: bool = True,
+                 state_dtype: Optional[torch.dtype] = None, stochastic: bool = True, seed: int = 42,
+                 timeout_s: Optional[float] = None, ctas: Optional[int] = None, use_side_stream: bool = True,
+                 owner_error_feedback: bool = False, adaptive_gain: bool = True, max_buckets: int = 512):
+        self.arena = arena
+        self.device = torch.device(device)
+        self.world = arena.world
+        self.rank = arena.rank
+        self.loopback = isinstance(arena, LoopbackArena)
+        self.nvr = self.world if self.loopback else 1
+        self.momentum = float(momentum)
+        self.error_feedback = error_feedback
+        self.state_dtype = state_dtype
+        self.stochastic = stochastic
+        self.seed = seed
+        self.timeout_s = float(os.environ.get("NANGILA_WAIT_TIMEOUT_MS", "2000")) / 1e3 if timeout_s is None else timeout_s
+        self.ctas = int(os.environ.get("NANGILA_COMM_CTAS", "0")) if ctas is None else ctas
+        self.owner_error_feedback = owner_error_feedback
+        self.adaptive_gain = adaptive_gain and os.environ.get("NANGILA_PRED_GAIN") is None
+        self.fixed_gain = float(os.environ.get("NANGILA_PRED_GAIN", "1"))
+        self.buckets: Dict[int, BucketState] = {}
+        # one row of 8 floats per (bucket, emulated rank): {sum e^2, sum g^2, sum miss^2, sum ef^2, ...}
+        self.max_buckets = max_buckets
+        self.stats_table = torch.zeros(max_buckets * self.nvr, 8, dtype=torch.float32, device=self.device)
+        self._stats_host = torch.zeros(max_buckets * self.nvr, 8, dtype=torch.float32).pin_memory() \
+            if torch.cuda.is_available() else torch.zeros(max_buckets * self.nvr, 8)
+        self._stats_event: Optional[torch.cuda.Event] = None
+        self.status = [torch.zeros(8, dtype=torch.int32, device=self.device) for _ in range(self.nvr)]
+        self.launches = 0
+        self.stream: Optional[torch.cuda.Stream] = None
+        if use_side_stream:
+            self.stream = torch.cuda.Stream(device=self.device, priority=-1)
+        self._glue = _glue()
+
+    # ------------------------------------------------------------------------------------------
+    def _grid(self, st: BucketState) -> int:
+        nchunks = (st.n + st.chunk - 1) // st.chunk
+        owned = (nchunks + self.world - 1) // self.world
+        want = owned * self.world
+        if self.ctas > 0:
+            cap = self.ctas
+        elif self.loopback:
+            cap = max(1, (148 * 2) // self.nvr)  # the cooperative launch must be co-resident
+        else:
+            cap = 148 * 2
+        return max(1, min(want, cap))
+
+    def _state_dtype_for(self, grad_dtype: torch.dtype) -> torch.dtype:
+        if self.state_dtype is not None:
+            return self.state_dtype
+        return torch.float32 if grad_dtype == torch.float32 else torch.bfloat16
+
+    def bucket_state(self, index: int, grads: List[torch.Tensor]) -> BucketState:
+        g0 = grads[0]
+        n = g0.numel()
+        st = self.buckets.get(index)
+        if st is not None and st.n == n and st.grad_dtype == g0.dtype:
+            return st
+        if g0.dtype not in _DTYPE_CODE:
+            raise TypeError(f"nangila: unsupported gradient dtype {g0.dtype}")
+        chunk = default_chunk_elems(n, self.world)
+        total, r1, r2, f1, f2 = self._glue.predres_region_layout(n, self.world, chunk, _DTYPE_CODE[g0.dtype])
+        region = self.arena.allocate(int(total))
+        sdt = self._state_dtype_for(g0.dtype)
+        nchunks = (n + chunk - 1) // chunk
+        owned = (nchunks + self.world - 1) // self.world
+        mk = lambda m, dt=sdt: torch.zeros(m, dtype=dt, device=self.device)  # noqa: E731
+        st = BucketState(
+            n=n, grad_dtype=g0.dtype, state_dtype=sdt, chunk=chunk, region=region, layout=(r1, r2, f1, f2),
+            prev=[mk(n) for _ in range(self.nvr)], curr=[mk(n) for _ in range(self.nvr)],
+            ef=[mk(n) if self.error_feedback else None for _ in range(self.nvr)],
+            ef2=[mk(owned * chunk) if (self.error_feedback and self.owner_error_feedback) else None
+                 for _ in range(self.nvr)],
+            stats=[], slot=len(self.buckets) % self.max_buckets, pred_gain=self.fixed_gain,
+        )
+        st.stats = [self.stats_table[st.slot * self.nvr + v] for v in range(self.nvr)]
+        for t in st.stats:
+            t.zero_()
+        self.buckets[index] = st
+        return st
+
+    def reduce(self, index: int, grads: List[torch.Tensor], compressed: bool, step: int = 0) -> BucketState:
+        """Queue the fused exchange for one bucket. ``grads`` has one tensor per emulated rank (one
+        in a real group). The result overwrites ``grads`` in place; the history advances."""
+        st = self.bucket_state(index, grads)
+        st.epoch += 1
+        st.calls += 1
+        st.compressed_calls += int(compressed)
+        self.launches += 1
+        r1, r2, f1, f2 = st.layout
+        args = dict(
+            grad=grads, prev=st.prev, curr=st.curr, ef=st.ef, ef2=st.ef2, stats=st.stats, status=self.status,
+            region_ptrs=st.region.ptrs, recv1_off=r1, recv2_off=r2, flag1_off=f1, flag2_off=f2,
+            rank0=0 if self.loopback else self.rank, chunk_elems=st.chunk, mode=0 if compressed else 1,
+            stochastic=self.stochastic, epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
+            mu=self.momentum, pred_gain=self._gains(st), timeout_s=self.timeout_s, grid_x=self._grid(st),
+        )
+        if self.stream is not None:
+            self.stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.stream):
+                self._glue.predres_launch(**args)
+        else:
+            self._glue.predres_launch(**args)
+        st.swap()
+        return st
+
+    def _gains(self, st: BucketState) -> List[float]:
+        g = st.extra.get("pred_gain_per_rank")
+        return list(g) if g is not None else [st.pred_gain] * self.nvr
+
+    # ------------------------------------------------------------------------------------------
+    def end_step(self) -> None:
+        """Call once per training step after the last bucket was queued. Reads the statistics of the
+        PREVIOUS step (already on the host, so nothing blocks), adapts every bucket's prediction gain,
+        then queues the copy of this step's statistics.
+
+        Gain control: the momentum predictor helps only while ||g - g_hat||^2 < ||g||^2. Beyond that
+        point it makes the residual larger than the gradient, and together with error feedback the
+        loop can amplify its own quantization noise, so the bucket is switched to kappa = 0 (plain
+        error-feedback quantization) and back once the predictor would pay again. The decision is
+        local: ranks may disagree and the kernel applies the mean of their gains.
+        """
+        if self._stats_event is not None:
+            self._stats_event.synchronize()
+            host = self._stats_host
+            for st in self.buckets.values():
+                row = host[st.slot * self.nvr].tolist()
+                e2, g2, m2, f2 = row[0], row[1], row[2], row[3]
+                if g2 <= 0.0:
+                    continue
+                for k, v in enumerate((e2, g2, m2, f2)):
+                    st.totals[k] += v
+                miss = m2 / g2
+                st.miss_ema = miss if st.miss_ema is None else 0.7 * st.miss_ema + 0.3 * miss
+                if not self.adaptive_gain:
+                    continue
+                if st.cooldown > 0:
+                    st.cooldown -= 1
+                if st.pred_gain > 0.0 and (st.miss_ema > 1.0 or f2 > 2.0 * g2):
+                    st.pred_gain, st.cooldown = 0.0, 20
+                elif st.pred_gain == 0.0 and st.cooldown == 0 and st.miss_ema < 0.7:
+                    st.pred_gain = 1.0
+        stream = self.stream if self.stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(stream):
+            self._stats_host.copy_(self.stats_table, non_blocking=True)
+            self.stats_table.zero_()
+            ev = torch.cuda.Event()
+            ev.record(stream)
+        self._stats_event = ev
+
+    def check_status(self) -> None:
+        """Synchronise the exchange stream and raise if a kernel gave up waiting."""
+        if self.stream is not None:
+            self.stream.synchronize()
+        else:
+            torch.cuda.synchronize(self.device)
+        for vr, s in enumerate(self.status):
+            w = s.cpu().tolist()
+            if w[0] != 0:
+                s.zero_()
+                raise RuntimeError(
+                    f"nangila: fused exchange failed on rank {w[1]} ({STATUS_MESSAGES.get(w[0], 'code %d' % w[0])}); "
+                    f"waiting for rank {w[2]}, epoch {w[3]} (last seen {w[4]}), phase {w[5]}, chunk {w[6]}")
+
+    def prediction_error(self, index: int) -> float:
+        """sqrt(sum e^2 / sum g^2) accumulated over the compressed calls of a bucket (rank 0's view)."""
+        st = self.buckets[index]
+        a, b = st.stats[0][:2].tolist()
+        a += st.totals[0]
+        b += st.totals[1]
+        return (a / b) ** 0.5 if b > 0 else 0.0
+
+    def wire_bytes(self, st: BucketState, compressed: bool) -> int:
+        """Bytes this rank stores into *other* ranks' memory for one call on this bucket."""
+        w = self.world
+        per_elem = (0.5 + 2.0 / 64.0) if compressed else st.grad_dtype.itemsize
+        return int(2 * st.n * per_elem * (w - 1) / w)
+
+    def state_dict(self) -> dict:
+        out = {}
+        for idx, st in self.buckets.items():
+            out[idx] = {
+                "n": st.n, "epoch": st.epoch, "prev": st.prev[0].clone(), "curr": st.curr[0].clone(),
+                "ef": None if st.ef[0] is None else st.ef[0].clone(),
+                "ef2": None if st.ef2[0] is None else st.ef2[0].clone(),
+            }
+        return out
+
+    def load_state_dict(self, sd: dict) -> None:
+        for idx, d in sd.items():
+            st = self.buckets.get(idx)
+            if st is None or st.n != d["n"]:
+                continue
+            st.prev[0].copy_(d["prev"])
+            st.curr[0].copy_(d["curr"])
+            if st.ef[0] is not None and d.get("ef") is not None:
+                st.ef[0].copy_(d["ef"])
+            if st.ef2[0] is not None and d.get("ef2") is not None:
+                st.ef2[0].copy_(d["ef2"])

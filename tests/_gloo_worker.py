@@ -1,0 +1,67 @@
+"""Worker for the CPU/gloo DDP tests: fp32 MLP 784->256->ReLU->10, batch 32 per rank from N(0,1),
+uniform labels, cross-entropy, SGD lr 0.01, seed 0."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.nn.parallel import DistributedDataParallel as DDP
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def run(rank, world, port, steps, use_hook, out_path, hook_kwargs, calib_steps=0, fixed_batch=False):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(784, 256), nn.ReLU(), nn.Linear(256, 10))
+    ddp = DDP(model)
+    hook = None
+    sculptor = None
+    if use_hook:
+        import nangila
+        from nangila.ddp import register_nangila_hook
+
+        hook = register_nangila_hook(ddp, **hook_kwargs)
+        if calib_steps:
+            sculptor = nangila.Sculptor(hook_kwargs.get("threshold", 0.95))
+    opt = torch.optim.SGD(ddp.parameters(), lr=0.01)
+    g = torch.Generator().manual_seed(1000 + rank)
+    losses = []
+    mask_info = None
+    xb = torch.randn(32, 784, generator=g)
+    yb = torch.randint(0, 10, (32,), generator=g)
+    for step in range(steps):
+        if fixed_batch:
+            x, y = xb, yb
+        else:
+            x = torch.randn(32, 784, generator=g)
+            y = torch.randint(0, 10, (32,), generator=g)
+        opt.zero_grad()
+        loss = nn.functional.cross_entropy(ddp(x), y)
+        loss.backward()
+        if sculptor is not None and step < calib_steps:
+            for lid, p in enumerate(model.parameters()):
+                sculptor.record(lid, p.grad.detach().reshape(-1).numpy())
+            sculptor.end_step()
+            if step == calib_steps - 1:
+                mask = sculptor.generate_mask()
+                h = nangila.NangilaHook(mask)
+                st = h.get_stats()
+                mask_info = (len(mask), st["num_drivers"], st["num_passengers"], sculptor.num_samples())
+        opt.step()
+        if hook is not None:
+            hook.step()
+        losses.append(float(loss))
+    result = {"losses": losses, "mask_info": mask_info,
+              "params": [p.detach().clone() for p in model.parameters()]}
+    if hook is not None:
+        result["stats"] = hook.get_stats()
+    if rank == 0:
+        torch.save(result, out_path)
+    # every rank also saves its first parameter to check replicas stay identical
+    torch.save(result["params"][0], out_path + f".rank{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
