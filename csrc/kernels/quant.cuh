@@ -169,7 +169,7 @@ __device__ __forceinline__ void quantize16(float (&e)[16], uint32_t key, uint32_
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(e[i]));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  scale_bits = bf16_ceil_bits(__fdiv_rn(amax, 7.0f));
+  scale_bits = bf16_ceil_bits(__fmul_rn(amax, 0.14285715f));  // amax * fl(1/7), rounded up to bf16
   const float s = bf16_bits_to_float(scale_bits);
   const bool live = s > 1e-30f;
   const float inv = live ? __frcp_rn(s) : 0.0f;

@@ -366,7 +366,25 @@ class NangilaDDPHook:
                 if st.compressed_calls:
                     errs[idx] = self._engine.prediction_error(idx)
             stats["prediction_error_per_bucket"] = errs
+            stats["pred_gain_per_bucket"] = {idx: st.pred_gain for idx, st in self._engine.buckets.items()}
         return stats
+
+    def fast_forward(self, to_step: int) -> None:
+        """Advance the step counters to ``to_step`` without exchanging anything (all ranks must call
+        it at the same point). Used to leave the warm-up early once the history is seeded; the
+        reference's examples do the same by stepping the hook in a loop (examples/train_llm.py:29-34,
+        nangila_ddp/src/ddp_hook.cpp:60-63)."""
+        while self.hook.current_step() < to_step:
+            self.hook.step()
+        self.step_count = max(self.step_count, int(to_step))
+
+    def get_kernel_launches(self) -> int:
+        """Number of fused-kernel launches queued by this hook so far on this rank."""
+        n = 0
+        for eng in (self._engine, self._dgc_engine, self._psgd_engine):
+            if eng is not None:
+                n += eng.launches
+        return n
 
     @property
     def compression_ratio(self) -> float:

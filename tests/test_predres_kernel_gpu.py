@@ -1,0 +1,201 @@
+"""GPU tests of the fused prediction-residual bucket kernel in the single-GPU loopback world
+(W emulated ranks inside one cooperative launch), against a plain PyTorch FP32 restatement."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(world, **kw):
+    from nangila.parallel.predres_engine import PredResEngine
+    from nangila.parallel.symm import LoopbackArena
+
+    dev = torch.device("cuda", 0)
+    kw.setdefault("use_side_stream", False)
+    kw.setdefault("adaptive_gain", False)
+    return PredResEngine(LoopbackArena(world, dev), dev, **kw)
+
+
+def _bf16_ceil(x):
+    """Smallest bf16 >= x for x >= 0 (as float32)."""
+    b = x.float().view(torch.int32)
+    b = ((b + 0xFFFF) >> 16) << 16
+    return b.view(torch.float32)
+
+
+def ref_quantize(e, nearest=True):
+    """Block-64 INT4: scale = bf16_ceil(amax * fl32(1/7)), q = floor(e/scale + 0.5) clamped to [-8, 7]."""
+    n = e.numel()
+    pad = (-n) % 64
+    x = torch.cat([e.float(), e.new_zeros(pad, dtype=torch.float32)]).view(-1, 64)
+    amax = x.abs().amax(dim=1, keepdim=True)
+    s = _bf16_ceil(amax * 0.14285715)
+    live = s > 1e-30
+    inv = torch.where(live, 1.0 / s, torch.zeros_like(s))
+    q = torch.floor(x * inv + 0.5).clamp_(-8, 7)
+    deq = torch.where(live, q * s, torch.zeros_like(q))
+    return deq.view(-1)[:n], s.view(-1)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [4096 * 3 + 17, 100_000, 1 << 20])
+def test_uncompressed_is_exact_mean(world, dtype, n):
+    eng = _engine(world)
+    torch.manual_seed(n + world)
+    grads = [torch.randn(n, device="cuda").mul_(0.01).to(dtype) for _ in range(world)]
+    want = torch.stack([g.float() for g in grads]).mean(0)
+    eng.reduce(0, grads, compressed=False)
+    eng.check_status()
+    tol = 0 if dtype == torch.float32 and world <= 2 else (1e-7 if dtype == torch.float32 else 2e-4)
+    for g in grads:
+        assert torch.allclose(g.float(), want, atol=max(tol, 1e-9), rtol=1e-2 if dtype == torch.bfloat16 else 1e-6)
+    for g in grads[1:]:
+        assert torch.equal(g, grads[0])
+    st = eng.buckets[0]
+    # history: the newest entry (curr after the swap) is the reduced gradient
+    for v in range(world):
+        assert torch.equal(st.curr[v].float(), grads[0].to(st.state_dtype).float())
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_compressed_matches_reference_math(world, dtype):
+    """Round-to-nearest mode, no error feedback: out = g_hat + Q(mean_r Q(g_r - g_hat))."""
+    n = 4096 * 8 + 4096 * 3 + 100
+    eng = _engine(world, stochastic=False, error_feedback=False, state_dtype=torch.float32)
+    torch.manual_seed(7)
+    mu = eng.momentum
+    hist = []
+    for step in range(2):  # two uncompressed steps build the history
+        grads = [(torch.randn(n, device="cuda") * 0.02 + 0.01 * step).to(dtype) for _ in range(world)]
+        eng.reduce(0, grads, compressed=False, step=step)
+        hist.append(grads[0].float().clone())
+    prev, curr = hist
+    pred = curr + mu * (curr - prev)
+    grads = [(pred + torch.randn(n, device="cuda") * 0.005).to(dtype) for _ in range(world)]
+    orig = [g.float().clone() for g in grads]
+    eng.reduce(0, grads, compressed=True, step=2)
+    eng.check_status()
+    acc = torch.zeros(n, device="cuda")
+    for g in orig:
+        deq, _ = ref_quantize(g - pred)
+        acc += deq
+    deq2, scale2 = ref_quantize(acc / world)
+    want = pred + deq2
+    got = grads[0].float()
+    step_size = scale2.repeat_interleave(64)[:n]
+    err = (got - want).abs()
+    tol = step_size * 1.01 + (1e-6 if dtype == torch.float32 else 4e-3 * want.abs() + 1e-5)
+    assert bool((err <= tol).all()), f"max err {err.max().item()}"
+    # at most a small fraction of elements may land one level away (ties under fused multiply-add)
+    exact_tol = 1e-6 if dtype == torch.float32 else 4e-3 * want.abs() + 1e-5
+    assert (err > exact_tol).float().mean().item() < 5e-3
+    for g in grads[1:]:
+        assert torch.equal(g, grads[0])  # every rank reconstructs the same bytes
+    # quality: the reconstruction is close to the true mean
+    true_mean = torch.stack(orig).mean(0)
+    rel = (got - true_mean).norm() / true_mean.norm()
+    assert rel < 0.05
+
+
+def test_error_feedback_identity_and_state():
+    world, n = 2, 4096 * 5
+    eng = _engine(world, stochastic=True, error_feedback=True, state_dtype=torch.float32)
+    torch.manual_seed(3)
+    grads = [torch.randn(n, device="cuda") * 0.01 for _ in range(world)]
+    orig = [g.clone() for g in grads]
+    eng.reduce(0, grads, compressed=True, step=0)  # zero history: g_hat = 0
+    eng.check_status()
+    st = eng.buckets[0]
+    # ef = e - deq(q) with e = g (first step): |ef| <= one quantization step of its block
+    for v in range(world):
+        ef = st.ef[v]
+        amax = orig[v].view(-1, 64).abs().amax(1)
+        assert bool((ef.view(-1, 64).abs().amax(1) <= _bf16_ceil(amax * 0.14285715) * 1.001).all())
+    # new history entry equals the output
+    assert torch.equal(st.curr[0], grads[0])
+    # unbiasedness of stochastic rounding: mean error far below a quantization step
+    bias = (grads[0] - torch.stack(orig).mean(0)).mean().abs().item()
+    assert bias < 2e-5
+
+
+def test_stochastic_rounding_is_unbiased():
+    world, n = 1, 1 << 20
+    eng = _engine(world, stochastic=True, error_feedback=False, state_dtype=torch.float32)
+    base = torch.full((n,), 0.0123, device="cuda")
+    base[::64] = 0.07  # sets every block's scale to 0.01
+    acc = torch.zeros(n, device="cuda")
+    reps = 16
+    for step in range(reps):
+        g = [base.clone()]
+        eng.buckets.clear()  # fresh zero history each time
+        eng.reduce(0, g, compressed=True, step=step)
+        acc += g[0]
+    eng.check_status()
+    mean = acc / reps
+    assert abs(mean[1::64].mean().item() - 0.0123) < 2e-4
+
+
+def test_prediction_gain_mean_and_stats():
+    world, n = 2, 4096 * 4
+    eng = _engine(world, stochastic=False, error_feedback=False, state_dtype=torch.float32)
+    torch.manual_seed(11)
+    for step in range(2):
+        grads = [torch.randn(n, device="cuda") * 0.02 for _ in range(world)]
+        eng.reduce(0, grads, compressed=False, step=step)
+    st = eng.buckets[0]
+    prev, curr = st.prev[0].clone(), st.curr[0].clone()
+    pred = curr + eng.momentum * (curr - prev)
+    st.extra["pred_gain_per_rank"] = [1.0, 0.0]
+    grads = [torch.randn(n, device="cuda") * 0.02 for _ in range(world)]
+    orig = [g.clone() for g in grads]
+    eng.reduce(0, grads, compressed=True, step=2)
+    eng.check_status()
+    d0, _ = ref_quantize(orig[0] - pred)
+    d1, _ = ref_quantize(orig[1])
+    deq2, s2 = ref_quantize((d0 + d1) / 2)
+    want = 0.5 * pred + deq2
+    err = (grads[0] - want).abs()
+    assert bool((err <= s2.repeat_interleave(64)[:n] * 1.01 + 1e-6).all())
+    assert (err > 1e-6).float().mean().item() < 5e-3
+    stats = eng.stats_table[st.slot * world].tolist()
+    assert stats[1] == pytest.approx(orig[0].pow(2).sum().item(), rel=1e-3)
+    assert stats[2] == pytest.approx((orig[0] - pred).pow(2).sum().item(), rel=1e-3)
+
+
+class _OneOfTwo:
+    """Arena of a two-rank group in which only rank 0 exists: rank 1's buffer is mapped but nobody
+    ever launches rank 1's kernel, so the flags rank 0 waits for are never set."""
+
+    world, rank, provider = 2, 0, "test"
+
+    def __init__(self, dev):
+        from nangila.parallel.symm import LoopbackArena
+
+        self._inner = LoopbackArena(2, dev)
+
+    def reserve(self, nbytes):
+        return None
+
+    def allocate(self, nbytes):
+        return self._inner.allocate(nbytes)
+
+
+def test_wait_times_out_and_reports_status():
+    """The host withholds rank 1: rank 0's bounded wait expires, the kernel records what it was
+    waiting for and returns, and the context stays usable."""
+    from nangila.parallel.predres_engine import PredResEngine
+
+    dev = torch.device("cuda", 0)
+    eng = PredResEngine(_OneOfTwo(dev), dev, use_side_stream=False, timeout_s=0.2, adaptive_gain=False)
+    n = 4096 * 4
+    grads = [torch.randn(n, device="cuda")]
+    before = grads[0].clone()
+    eng.reduce(0, grads, compressed=False)
+    with pytest.raises(RuntimeError, match="timeout in phase 2"):
+        eng.check_status()
+    assert torch.equal(grads[0], before)  # nothing was reconstructed, the bucket is untouched
+    assert torch.ones(4, device="cuda").sum().item() == 4.0  # the device is still healthy
+    # the status block was cleared by the check: a later launch can be diagnosed again
+    assert int(eng.status[0][0].item()) == 0
