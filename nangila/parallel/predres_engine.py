@@ -110,6 +110,7 @@ class PredResEngine:
         self.buckets: Dict[int, BucketState] = {}
         # one row of 8 floats per (bucket, emulated rank): {sum e^2, sum g^2, sum miss^2, sum ef^2, ...}
         self.max_buckets = max_buckets
+        self._next_slot = 0
         self.stats_table = torch.zeros(max_buckets * self.nvr, 8, dtype=torch.float32, device=self.device)
         self._stats_host = torch.zeros(max_buckets * self.nvr, 8, dtype=torch.float32).pin_memory() \
             if torch.cuda.is_available() else torch.zeros(max_buckets * self.nvr, 8)
@@ -133,6 +134,15 @@ class PredResEngine:
         else:
             cap = 148 * 2
         return max(1, min(want, cap))
+
+    def _take_slot(self, index: int) -> int:
+        """Row of the statistics table for a bucket; a rebuilt bucket keeps the row of its index."""
+        old = self.buckets.get(index)
+        if old is not None:
+            return old.slot
+        slot = self._next_slot % self.max_buckets
+        self._next_slot += 1
+        return slot
 
     def _state_dtype_for(self, grad_dtype: torch.dtype) -> torch.dtype:
         if self.state_dtype is not None:
@@ -160,7 +170,7 @@ class PredResEngine:
             ef=[mk(n) if self.error_feedback else None for _ in range(self.nvr)],
             ef2=[mk(owned * chunk) if (self.error_feedback and self.owner_error_feedback) else None
                  for _ in range(self.nvr)],
-            stats=[], slot=len(self.buckets) % self.max_buckets, pred_gain=self.fixed_gain,
+            stats=[], slot=self._take_slot(index), pred_gain=self.fixed_gain,
         )
         st.stats = [self.stats_table[st.slot * self.nvr + v] for v in range(self.nvr)]
         for t in st.stats:

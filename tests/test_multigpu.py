@@ -1,0 +1,35 @@
+"""Launches the multi-GPU worker on 2 (and 4) GPUs of this node. NVLS is switched off in NCCL and the
+framework's own kernels use plain peer stores, so a failing rank cannot fault its peers' links."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, what, tmp_path, port):
+    out = tmp_path / f"res_{nproc}_{what}.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_mgpu_worker.py"), what, str(out)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    return json.loads(out.read_text())
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_exchange_matches_nccl(nproc, tmp_path):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    res = _run(nproc, "exchange", tmp_path, 29731 + nproc)
+    assert res["world"] == nproc
+
+
+def test_ddp_loss_parity_two_gpus(tmp_path):
+    res = _run(2, "train", tmp_path, 29741)
+    assert res["compression_ratio"] > 1.5 and res["launches"] > 0
