@@ -57,14 +57,18 @@ struct Reader {
 };
 
 // Driver payload: f32 gamma, u32 numel, u32 ndim, u32 dims[ndim], u8 packed[...]
-// (nangila-hook/src/hook.rs:697-742).
+// (nangila-hook/src/hook.rs:697-742). Block-scaled extension: the gamma field holds -block_size
+// (a negative number no real scale can be) and, after the dims, f32 prediction_gain and
+// f32 scales[ceil(numel / block_size)] precede the packed bytes.
 inline std::vector<uint8_t> serialize_compressed(const CompressedTensor& c) {
   std::vector<uint8_t> o;
-  o.reserve(12 + 4 * c.shape.size() + c.data.size());
-  put_f32(o, c.gamma);
+  o.reserve(12 + 4 * c.shape.size() + 4 * c.scales.size() + c.data.size());
+  put_f32(o, c.block ? -float(c.block) : c.gamma);
   put_u32(o, uint32_t(c.numel));
   put_u32(o, uint32_t(c.shape.size()));
   for (size_t d : c.shape) put_u32(o, uint32_t(d));
+  if (c.block) put_f32(o, c.pred_gain);
+  for (float sc : c.scales) put_f32(o, sc);
   o.insert(o.end(), c.data.begin(), c.data.end());
   return o;
 }
@@ -76,6 +80,16 @@ inline CompressedTensor deserialize_compressed(const uint8_t* p, size_t len) {
   c.numel = r.u32();
   uint32_t nd = r.u32();
   for (uint32_t i = 0; i < nd && r.off + 4 <= len; ++i) c.shape.push_back(r.u32());
+  if (c.gamma < 0.0f) {
+    c.block = size_t(-c.gamma);
+    size_t nb = c.block ? (c.numel + c.block - 1) / c.block : 0;
+    if (c.block == 0 || r.off + 4 + nb * 4 > len) return CompressedTensor{};
+    c.pred_gain = r.f32();
+    c.scales.resize(nb);
+    double mean = 0;
+    for (size_t b = 0; b < nb; ++b) mean += (c.scales[b] = r.f32());
+    c.gamma = nb ? float(mean / double(nb)) : 0.0f;
+  }
   c.data.assign(p + r.off, p + len);
   return c;
 }
@@ -130,7 +144,7 @@ class PredictionResidualCompressor : public Compressor {
       : predictor_(cfg.momentum, cfg.warmup_steps),
         quantizer_(cfg.quantize_bits, cfg.dynamic_gamma, reference_exact),
         error_feedback_(error_feedback && !reference_exact),
-        adaptive_gate_(!reference_exact) {}
+        adaptive_gain_(!reference_exact) {}
 
   Tensor prediction_or_zero(LayerId layer, size_t n) const {
     if (predictor_.can_predict(layer)) {
@@ -140,55 +154,41 @@ class PredictionResidualCompressor : public Compressor {
     return Tensor::zeros({n});
   }
 
-  // Per-layer prediction gate. The momentum predictor only pays while ||g - g_hat||^2 < ||g||^2;
-  // past that it enlarges the residual and, through error feedback, can amplify its own
-  // quantization noise. The gate switches a layer to plain error-feedback quantization (packet flag
-  // NO_PREDICTION) and back once the predictor would pay again. Each sender decides for itself;
-  // receivers follow the flag of each packet.
-  struct Gate {
-    bool predict = true;
-    float miss_ema = -1.0f;
-    int cooldown = 0;
-  };
-  bool gate_decide(LayerId layer, float miss, float ef_ratio) {
-    Gate& g = gates_[layer];
-    if (!adaptive_gate_) return g.predict;
-    g.miss_ema = g.miss_ema < 0.0f ? miss : 0.7f * g.miss_ema + 0.3f * miss;
-    if (g.cooldown > 0) --g.cooldown;
-    if (g.predict && (g.miss_ema > 1.0f || ef_ratio > 2.0f)) {
-      g.predict = false;
-      g.cooldown = 20;
-    } else if (!g.predict && g.cooldown == 0 && g.miss_ema < 0.7f) {
-      g.predict = true;
-    }
-    return g.predict;
-  }
-  void set_adaptive_gate(bool on) { adaptive_gate_ = on; }
-  bool layer_predicts(LayerId layer) const {
-    auto it = gates_.find(layer);
-    return it == gates_.end() ? true : it->second.predict;
-  }
+  // Prediction gain. The compressor subtracts kappa * g_hat, with kappa the least-squares shrinkage
+  // <g + ef, g_hat> / <g_hat, g_hat> clipped to [0, 1]: 1 when the momentum predictor tracks the
+  // gradient, near 0 when consecutive gradients are dominated by mini-batch noise (a full-size
+  // prediction would then make the residual larger than the gradient and, through error feedback,
+  // amplify the predictor's own quantization noise). kappa travels in the block-scaled payload;
+  // single-scale payloads carry it as the NO_PREDICTION flag (kappa = 0) or its absence (kappa = 1).
+  void set_adaptive_gain(bool on) { adaptive_gain_ = on; }
+  float last_gain() const { return last_gain_; }
 
   Packet compress(const Tensor& g, LayerId layer) override {
+    const bool can = predictor_.can_predict(layer);
     Tensor pred = prediction_or_zero(layer, g.numel());
-    Tensor resid = g.sub(pred);
-    const float gn = g.norm();
-    const float miss = gn > 0 ? (resid.norm() / gn) * (resid.norm() / gn) : 0.0f;
-    float ef_ratio = 0.0f;
+    Tensor x = g;  // g + ef
     auto ef_it = ef_.find(layer);
-    const bool have_ef = error_feedback_ && ef_it != ef_.end() && ef_it->second.size() == resid.data.size();
-    if (have_ef && gn > 0) {
-      double s = 0;
-      for (float v : ef_it->second) s += double(v) * double(v);
-      ef_ratio = float(s) / (gn * gn);
+    if (error_feedback_ && ef_it != ef_.end() && ef_it->second.size() == x.data.size())
+      for (size_t i = 0; i < x.data.size(); ++i) x.data[i] += ef_it->second[i];
+    float kappa = can ? 1.0f : 0.0f;
+    if (can && adaptive_gain_) {
+      double xp = 0, pp = 0;
+      for (size_t i = 0; i < x.data.size(); ++i) {
+        xp += double(x.data[i]) * double(pred.data[i]);
+        pp += double(pred.data[i]) * double(pred.data[i]);
+      }
+      kappa = pp > 0 ? float(std::min(std::max(xp / pp, 0.0), 1.0)) : 0.0f;
+      if (quantizer_.block_size() == 0) kappa = kappa >= 0.5f ? 1.0f : 0.0f;  // only the flag can travel
     }
-    const bool predict = predictor_.can_predict(layer) ? gate_decide(layer, miss, ef_ratio) : true;
-    if (!predict) resid = g;
-    if (have_ef)
-      for (size_t i = 0; i < resid.data.size(); ++i) resid.data[i] += ef_it->second[i];
+    last_gain_ = kappa;
+    Tensor resid = x;
+    if (kappa != 0.0f)
+      for (size_t i = 0; i < resid.data.size(); ++i) resid.data[i] -= kappa * pred.data[i];
+    const float gn = g.norm();
     last_pred_error_ = gn > 0 ? resid.norm() / gn : 0.0f;
     CompressedTensor c = quantizer_.quantize(resid, layer, step_);
     c.shape = g.shape;
+    c.pred_gain = kappa;
     if (error_feedback_) {
       Tensor deq = quantizer_.dequantize(c);
       std::vector<float>& ef = ef_[layer];
@@ -198,22 +198,32 @@ class PredictionResidualCompressor : public Compressor {
     std::vector<uint8_t> payload = wire::serialize_compressed(c);
     last_ratio_ = float(g.numel() * 4) / float(std::max<size_t>(payload.size(), 1));
     PacketHeader h = PacketHeader::new_driver(uint32_t(step_), layer);
-    if (!predict) h.flags |= flags::NO_PREDICTION;
+    if (kappa == 0.0f && can) h.flags |= flags::NO_PREDICTION;
     return Packet(h, std::move(payload));
+  }
+  static float packet_gain(const Packet& p, const CompressedTensor& c) {
+    if (p.header.flags & flags::NO_PREDICTION) return 0.0f;
+    return c.block ? c.pred_gain : 1.0f;
   }
   Tensor decompress(const Packet& p, LayerId layer) override {
     CompressedTensor c = wire::deserialize_compressed(p.payload.data(), p.payload.size());
     Tensor out = quantizer_.dequantize(c);
-    if (!(p.header.flags & flags::NO_PREDICTION)) out = prediction_or_zero(layer, out.numel()).add(out);
+    const float kappa = packet_gain(p, c);
+    if (kappa != 0.0f && predictor_.can_predict(layer)) {
+      Tensor pred = predictor_.predict(layer);
+      if (pred.numel() == out.numel())
+        for (size_t i = 0; i < out.data.size(); ++i) out.data[i] += kappa * pred.data[i];
+    }
     out.shape = c.shape.empty() ? std::vector<size_t>{out.numel()} : c.shape;
     return out;
   }
   Tensor decompress_partial(const Packet& p, LayerId layer, size_t start, size_t end) {
     CompressedTensor c = wire::deserialize_compressed(p.payload.data(), p.payload.size());
     Tensor resid = quantizer_.dequantize_partial(c, start, end);
-    if (!(p.header.flags & flags::NO_PREDICTION) && predictor_.can_predict(layer)) {
+    const float kappa = packet_gain(p, c);
+    if (kappa != 0.0f && predictor_.can_predict(layer)) {
       Tensor pred = predictor_.predict_partial(layer, start, end);
-      if (pred.numel() == resid.numel()) return pred.add(resid);
+      if (pred.numel() == resid.numel()) return pred.scale(kappa).add(resid);
     }
     return resid;
   }
@@ -244,8 +254,8 @@ class PredictionResidualCompressor : public Compressor {
   Quantizer quantizer_;
   bool error_feedback_;
   std::map<LayerId, std::vector<float>> ef_;
-  std::map<LayerId, Gate> gates_;
-  bool adaptive_gate_ = true;
+  bool adaptive_gain_ = true;
+  float last_gain_ = 1.0f;
   uint64_t step_ = 0;
   float last_ratio_ = 1.0f;
   float last_pred_error_ = 0.0f;

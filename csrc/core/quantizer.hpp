@@ -1,11 +1,11 @@
-// Host-side INT4 (or narrower/wider, up to 8 bit) stochastic quantizer with one scale per tensor.
-// This is the quantizer of the CPU/gloo transport and the oracle for the device kernels' single
-// scale compatibility entry points. The fused device kernels use per-block scales instead.
+// Host-side INT4 (or narrower/wider, up to 8 bit) stochastic quantizer. This is the quantizer of
+// the CPU/gloo transport and the oracle for the device kernels.
 //
 // Two behaviours:
-//  * default: gamma = p99(|x|) / qmax of the tensor being quantized (no lag), unbiased stochastic
-//    rounding q = floor(x/gamma + u), u in [0,1) from a counter-based generator keyed by
-//    (seed, layer, step, global element index);
+//  * default: one scale per block of 64 elements (scale = absmax / qmax, nothing is clipped), like
+//    the fused device kernels; unbiased stochastic rounding q = floor(x/scale + u), u in [0,1) from
+//    a counter-based generator keyed by (seed, layer, step, global element index). With
+//    block_size = 0 it falls back to one scale per tensor, gamma = p99(|x|) / qmax (no lag);
 //  * reference_exact: reproduces nangila-core/src/quantizer.rs as written — gamma is an EMA
 //    (0.99) shared by all layers starting at 1.0 (:64-73, :123-131), and negative values are
 //    rounded away from zero with probability frac (:178-190).
@@ -24,11 +24,15 @@ namespace nangila {
 
 struct CompressedTensor {
   std::vector<uint8_t> data;
-  float gamma = 0.0f;
+  float gamma = 0.0f;          // per-tensor scale; with block scales: their mean (informational)
   std::vector<size_t> shape;
   size_t numel = 0;
+  size_t block = 0;            // 0 = one scale (gamma); else elements per entry of `scales`
+  std::vector<float> scales;
+  float pred_gain = 1.0f;      // kappa the sender applied to its prediction (block format only)
 
-  size_t size_bytes() const { return data.size() + 4 + shape.size() * 8 + 8; }
+  float scale_at(size_t i) const { return block ? scales[i / block] : gamma; }
+  size_t size_bytes() const { return data.size() + scales.size() * 4 + 4 + shape.size() * 8 + 8; }
   float compression_ratio(size_t original_numel) const {
     size_t b = size_bytes();
     return b == 0 ? 1.0f : float(original_numel * 4) / float(b);
@@ -66,7 +70,8 @@ inline std::vector<int8_t> unpack_int4(const std::vector<uint8_t>& p, size_t num
 class Quantizer {
  public:
   Quantizer(uint8_t bits = 4, bool dynamic_gamma = true, bool reference_exact = false)
-      : bits_(bits), dynamic_gamma_(dynamic_gamma), reference_exact_(reference_exact) {
+      : bits_(bits), dynamic_gamma_(dynamic_gamma), reference_exact_(reference_exact),
+        block_(reference_exact ? 0 : 64) {
     if (bits == 0 || bits > 8) throw NangilaError(ErrorKind::Config, "Maximum 8 bits supported");
   }
   static Quantizer int4() { return Quantizer(4, true); }
@@ -98,8 +103,27 @@ class Quantizer {
   CompressedTensor quantize_with_offset(const Tensor& t, uint32_t layer_id, uint64_t step, size_t global_offset) {
     CompressedTensor out;
     if (t.numel() == 0) return out;
+    const bool blocked = block_ > 0 && dynamic_gamma_;
+    if (blocked) {
+      const size_t nb = (t.numel() + block_ - 1) / block_;
+      out.block = block_;
+      out.scales.resize(nb);
+      double mean = 0;
+      for (size_t b = 0; b < nb; ++b) {
+        float amax = 0.0f;
+        for (size_t i = b * block_, e = std::min(t.numel(), (b + 1) * block_); i < e; ++i) {
+          float v = std::fabs(t.data[i]);
+          if (std::isfinite(v)) amax = std::max(amax, v);
+        }
+        out.scales[b] = amax / float(qmax());
+        mean += out.scales[b];
+      }
+      gamma_ema_ = float(mean / double(nb));
+    }
     float gamma;
-    if (dynamic_gamma_) {
+    if (blocked) {
+      gamma = gamma_ema_;
+    } else if (dynamic_gamma_) {
       float g = compute_gamma(t);
       gamma_ema_ = reference_exact_ ? gamma_momentum_ * gamma_ema_ + (1.0f - gamma_momentum_) * g : g;
       gamma = std::max(gamma_ema_, 1e-8f);
@@ -113,7 +137,8 @@ class Quantizer {
     for (size_t i = 0; i < t.numel(); ++i) {
       float x = t.data[i];
       if (!std::isfinite(x)) x = 0.0f;
-      float scaled = x / gamma;
+      const float sc = blocked ? out.scales[i / block_] : gamma;
+      float scaled = sc > 0.0f ? x / sc : 0.0f;
       float fl = std::floor(scaled);
       float frac = scaled - fl;
       float r;
@@ -155,7 +180,7 @@ class Quantizer {
     if (c.numel == 0) return Tensor::zeros(c.shape);
     std::vector<int8_t> q = unpack(c);
     std::vector<float> d(c.numel, 0.0f);
-    for (size_t i = 0; i < q.size() && i < d.size(); ++i) d[i] = float(q[i]) * c.gamma;
+    for (size_t i = 0; i < q.size() && i < d.size(); ++i) d[i] = float(q[i]) * c.scale_at(i);
     return Tensor(std::move(d), c.shape.empty() ? std::vector<size_t>{c.numel} : c.shape);
   }
   Tensor dequantize_partial(const CompressedTensor& c, size_t start, size_t end) const {
@@ -175,7 +200,7 @@ class Quantizer {
         if (i >= c.data.size()) break;
         q = int8_t(c.data[i]);
       }
-      d.push_back(float(q) * c.gamma);
+      d.push_back(float(q) * c.scale_at(i));
     }
     size_t n = d.size();
     return Tensor(std::move(d), {n});
@@ -186,6 +211,8 @@ class Quantizer {
   void set_dynamic_gamma(bool d) { dynamic_gamma_ = d; }
   void set_stochastic(bool s) { stochastic_ = s; }
   void set_seed(uint64_t s) { seed_ = s; }
+  void set_block_size(size_t b) { block_ = b; }
+  size_t block_size() const { return block_; }
   uint8_t bits() const { return bits_; }
   bool reference_exact() const { return reference_exact_; }
 
@@ -193,6 +220,7 @@ class Quantizer {
   uint8_t bits_;
   bool dynamic_gamma_;
   bool reference_exact_;
+  size_t block_;
   bool stochastic_ = true;
   float gamma_ema_ = 1.0f;
   float gamma_momentum_ = 0.99f;

@@ -101,7 +101,7 @@ void predres_launch(const std::vector<at::Tensor>& grad, const std::vector<at::T
       p.ef2[v] = ef2[v]->data_ptr();
     }
     if (stats[v].has_value()) {
-      TORCH_CHECK(stats[v]->is_cuda() && stats[v]->scalar_type() == at::kFloat && stats[v]->numel() >= 4, "nangila: stats");
+      TORCH_CHECK(stats[v]->is_cuda() && stats[v]->scalar_type() == at::kFloat && stats[v]->numel() >= 8, "nangila: stats");
       p.stats[v] = stats[v]->data_ptr<float>();
     }
     TORCH_CHECK(status[v].is_cuda() && status[v].scalar_type() == at::kInt && status[v].numel() >= 8, "nangila: status");

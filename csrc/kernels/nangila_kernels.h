@@ -34,7 +34,7 @@ typedef struct NangilaPredResParams {
   void* curr[NANGILA_MAX_VRANKS];      /* in: g(t) */
   void* ef[NANGILA_MAX_VRANKS];        /* in/out: error feedback, n elements of state_dtype (may be NULL) */
   void* ef2[NANGILA_MAX_VRANKS];       /* in/out: owner-side error memory, owned_chunks*chunk elems (may be NULL) */
-  float* stats[NANGILA_MAX_VRANKS];    /* += {sum e^2, sum g^2, sum (g - g_hat)^2, sum ef_new^2}; may be NULL */
+  float* stats[NANGILA_MAX_VRANKS];    /* += {sum e^2, sum g^2, <g+ef, g_hat>, <g_hat, g_hat>, sum ef_new^2}; >= 8 floats; may be NULL */
   uint32_t* status[NANGILA_MAX_VRANKS];/* 8 words, see comm/signal.cuh; must be zero before launch */
   uint8_t* region[NANGILA_MAX_RANKS];  /* symmetric region of every rank of the group */
   uint64_t recv1_off, recv2_off, flag1_off, flag2_off; /* byte offsets inside a region */

@@ -76,7 +76,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   const uint32_t key2 = make_key(p.seed, p.step, p.bucket_id, 0u, 2u);
   const bool stochastic = p.stochastic != 0;
 
-  float sum_e2 = 0.0f, sum_g2 = 0.0f, sum_p2 = 0.0f, sum_f2 = 0.0f;
+  float sum_e2 = 0.0f, sum_g2 = 0.0f, sum_xp = 0.0f, sum_pp = 0.0f, sum_f2 = 0.0f;
 
   const int T1 = owned_max * W;
   const int ntasks = T1 + my_owned + NC;
@@ -102,22 +102,23 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           load16_guarded<S>(prev, base, n, pv);
           load16_guarded<S>(curr, base, n, cu);
           float e[16];
+          if (ef != nullptr) {
+            load16_guarded<S>(ef, base, n, e);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) e[i] += g[i];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) e[i] = g[i];
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float pred = __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
-            const float miss = g[i] - pred;  // what full prediction would leave
             sum_g2 = __fmaf_rn(g[i], g[i], sum_g2);
-            sum_p2 = __fmaf_rn(miss, miss, sum_p2);
-            e[i] = __fmaf_rn(-kappa, pred, g[i]);
+            sum_xp = __fmaf_rn(e[i], pred, sum_xp);  // <g + ef, g_hat>
+            sum_pp = __fmaf_rn(pred, pred, sum_pp);  // <g_hat, g_hat>
+            e[i] = __fmaf_rn(-kappa, pred, e[i]);
+            sum_e2 = __fmaf_rn(e[i], e[i], sum_e2);
           }
-          if (ef != nullptr) {
-            float f[16];
-            load16_guarded<S>(ef, base, n, f);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) e[i] += f[i];
-          }
-#pragma unroll
-          for (int i = 0; i < 16; ++i) sum_e2 = __fmaf_rn(e[i], e[i], sum_e2);
           uint2 packed;
           uint32_t sb;
           float deq[16];
@@ -250,18 +251,18 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
     }
   }
 
-  // per-rank telemetry: four atomics per CTA
+  // per-rank telemetry: five atomics per CTA
   if (p.stats[vr] != nullptr && COMPRESSED) {
-    __shared__ float red[4][kThreads / 32];
-    float v[4] = {sum_e2, sum_g2, sum_p2, sum_f2};
+    __shared__ float red[5][kThreads / 32];
+    float v[5] = {sum_e2, sum_g2, sum_xp, sum_pp, sum_f2};
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < 5; ++k) {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) v[k] += __shfl_xor_sync(0xffffffffu, v[k], off);
       if ((tid & 31) == 0) red[k][tid >> 5] = v[k];
     }
     __syncthreads();
-    if (tid < 4) {
+    if (tid < 5) {
       float a = 0.0f;
 #pragma unroll
       for (int i = 0; i < kThreads / 32; ++i) a += red[tid][i];

@@ -213,32 +213,36 @@ class PredResEngine:
         PREVIOUS step (already on the host, so nothing blocks), adapts every bucket's prediction gain,
         then queues the copy of this step's statistics.
 
-        Gain control: the momentum predictor helps only while ||g - g_hat||^2 < ||g||^2. Beyond that
-        point it makes the residual larger than the gradient, and together with error feedback the
-        loop can amplify its own quantization noise, so the bucket is switched to kappa = 0 (plain
-        error-feedback quantization) and back once the predictor would pay again. The decision is
-        local: ranks may disagree and the kernel applies the mean of their gains.
+        Gain control: the kernel subtracts kappa * g_hat. The best kappa for a step is the
+        least-squares shrinkage <g + ef, g_hat> / <g_hat, g_hat> clipped to [0, 1]: 1 when the
+        momentum predictor tracks the gradient, near 0 when consecutive gradients are dominated by
+        mini-batch noise (subtracting a full-size prediction there would make the residual larger
+        than the gradient and, through error feedback, amplify the predictor's own quantization
+        noise). Both inner products come from the kernel; the value of the previous step is used
+        (smoothed). The decision is local: ranks may differ, the kernel applies the mean of all
+        ranks' gains. A run-away error-feedback memory switches prediction off for a while.
         """
         if self._stats_event is not None:
             self._stats_event.synchronize()
             host = self._stats_host
             for st in self.buckets.values():
                 row = host[st.slot * self.nvr].tolist()
-                e2, g2, m2, f2 = row[0], row[1], row[2], row[3]
+                e2, g2, xp, pp, f2 = row[0], row[1], row[2], row[3], row[4]
                 if g2 <= 0.0:
                     continue
-                for k, v in enumerate((e2, g2, m2, f2)):
+                for k, v in enumerate((e2, g2, xp, pp)):
                     st.totals[k] += v
-                miss = m2 / g2
-                st.miss_ema = miss if st.miss_ema is None else 0.7 * st.miss_ema + 0.3 * miss
+                st.miss_ema = e2 / g2 if st.miss_ema is None else 0.7 * st.miss_ema + 0.3 * e2 / g2
                 if not self.adaptive_gain:
                     continue
                 if st.cooldown > 0:
                     st.cooldown -= 1
-                if st.pred_gain > 0.0 and (st.miss_ema > 1.0 or f2 > 2.0 * g2):
+                    continue
+                if f2 > 2.0 * g2:
                     st.pred_gain, st.cooldown = 0.0, 20
-                elif st.pred_gain == 0.0 and st.cooldown == 0 and st.miss_ema < 0.7:
-                    st.pred_gain = 1.0
+                    continue
+                best = min(max(xp / pp, 0.0), 1.0) if pp > 0.0 else 0.0
+                st.pred_gain = 0.5 * st.pred_gain + 0.5 * best
         stream = self.stream if self.stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(stream):
             self._stats_host.copy_(self.stats_table, non_blocking=True)

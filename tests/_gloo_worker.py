@@ -54,7 +54,7 @@ def run(rank, world, port, steps, use_hook, out_path, hook_kwargs, calib_steps=0
         opt.step()
         if hook is not None:
             hook.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     result = {"losses": losses, "mask_info": mask_info,
               "params": [p.detach().clone() for p in model.parameters()]}
     if hook is not None:

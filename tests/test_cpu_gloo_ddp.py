@@ -1,0 +1,80 @@
+"""CPU / gloo, world_size 2: the DDP plumbing check. fp32 MLP 784 -> 256 -> ReLU -> 10, batch 32 per
+rank from N(0,1), uniform labels, cross-entropy, SGD lr 0.01, 200 steps,
+register_nangila_hook(threshold=0.95, warmup_steps=100), Sculptor calibration over the first 50
+steps, seed 0. Compared against plain DDP on the same data."""
+import os
+import socket
+import sys
+import warnings
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _gloo_worker import run  # noqa: E402
+
+
+def _port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _spawn(tmp_path, name, steps, use_hook, kwargs, calib=0, fixed=False):
+    out = str(tmp_path / name)
+    mp.spawn(run, args=(2, _port(), steps, use_hook, out, kwargs, calib, fixed), nprocs=2, join=True)
+    return torch.load(out, weights_only=False), torch.load(out + ".rank0"), torch.load(out + ".rank1")
+
+
+@pytest.mark.timeout(600)
+def test_mlp_200_steps_with_calibration(tmp_path):
+    ours, p0, p1 = _spawn(tmp_path, "ours.pt", 200, True, dict(threshold=0.95, warmup_steps=100), calib=50)
+    base, _, _ = _spawn(tmp_path, "base.pt", 200, False, {})
+    # warm-up is an exact average: identical losses for the first 100 steps
+    assert ours["losses"][:100] == pytest.approx(base["losses"][:100], abs=1e-6)
+    st = ours["stats"]
+    assert st["step"] == 200 and st["compression_enabled"]
+    assert st["overall_compression_ratio"] > 1.5  # 100 exact + 100 compressed (INT4) steps
+    # replicas stay bit-identical under compression
+    assert torch.equal(p0, p1)
+    # final-loss parity with uncompressed DDP (random labels: loss stays near ln 10)
+    a = sum(ours["losses"][-20:]) / 20
+    b = sum(base["losses"][-20:]) / 20
+    assert abs(a - b) < 0.05 * b
+    # Sculptor calibration ran over 50 steps; the four parameters differ in size, so all are Drivers
+    nbytes, drivers, passengers, samples = ours["mask_info"]
+    assert (drivers, passengers, samples) == (4, 0, 50) and nbytes == 4 + 4 * 5
+
+
+@pytest.mark.timeout(600)
+def test_compressed_training_learns_fixed_batch(tmp_path):
+    ours, p0, p1 = _spawn(tmp_path, "o.pt", 120, True, dict(warmup_steps=10), fixed=True)
+    base, _, _ = _spawn(tmp_path, "b.pt", 120, False, {}, fixed=True)
+    assert torch.equal(p0, p1)
+    assert base["losses"][-1] < base["losses"][0] - 0.05
+    assert abs(ours["losses"][-1] - base["losses"][-1]) < 0.05
+    assert ours["stats"]["overall_compression_ratio"] > 4.0
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("ctype,extra", [(1, dict(dgc_sparsity=0.9)), (2, dict(power_sgd_rank=4))])
+def test_dgc_and_powersgd_knobs_are_real(tmp_path, ctype, extra):
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        ours, p0, p1 = _spawn(tmp_path, f"c{ctype}.pt", 80, True, dict(warmup_steps=5, compressor_type=ctype, **extra),
+                              fixed=True)
+    base, _, _ = _spawn(tmp_path, f"b{ctype}.pt", 80, False, {}, fixed=True)
+    assert torch.equal(p0, p1)
+    assert ours["stats"]["overall_compression_ratio"] > 2.0
+    assert ours["losses"][-1] < ours["losses"][0]  # still trains
+    assert abs(ours["losses"][-1] - base["losses"][-1]) < 0.15
+
+
+def test_register_rejects_non_ddp_and_warns():
+    import nangila
+
+    with pytest.raises(TypeError):
+        nangila.register_nangila_hook(torch.nn.Linear(2, 2))

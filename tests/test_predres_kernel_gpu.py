@@ -159,9 +159,11 @@ def test_prediction_gain_mean_and_stats():
     err = (grads[0] - want).abs()
     assert bool((err <= s2.repeat_interleave(64)[:n] * 1.01 + 1e-6).all())
     assert (err > 1e-6).float().mean().item() < 5e-3
-    stats = eng.stats_table[st.slot * world].tolist()
+    stats = eng.stats_table[st.slot * world].tolist()  # rank 0: kappa = 1, no error feedback
+    assert stats[0] == pytest.approx((orig[0] - pred).pow(2).sum().item(), rel=1e-3)
     assert stats[1] == pytest.approx(orig[0].pow(2).sum().item(), rel=1e-3)
-    assert stats[2] == pytest.approx((orig[0] - pred).pow(2).sum().item(), rel=1e-3)
+    assert stats[2] == pytest.approx((orig[0] * pred).sum().item(), rel=1e-2, abs=1e-3)
+    assert stats[3] == pytest.approx(pred.pow(2).sum().item(), rel=1e-3)
 
 
 class _OneOfTwo:
