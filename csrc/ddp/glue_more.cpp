@@ -1,6 +1,204 @@
-// Bindings of the remaining kernels; kept in its own translation unit so the two compile in parallel.
+// Bindings of the kernels other than the prediction-residual bucket exchange; kept in its own
+// translation unit so the glue compiles in parallel.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "nangila_kernels.h"
 
 namespace py = pybind11;
 
-void register_more(py::module_& m) { (void)m; }
+namespace {
+
+int dtype_code(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return NANGILA_F32;
+    case at::kHalf: return NANGILA_F16;
+    case at::kBFloat16: return NANGILA_BF16;
+    default: TORCH_CHECK(false, "nangila: unsupported dtype ", t.scalar_type());
+  }
+}
+void check_launch(int err, const char* what) {
+  TORCH_CHECK(err == 0, "nangila: ", what, " failed: ", cudaGetErrorString(static_cast<cudaError_t>(err)));
+}
+uint8_t* as_ptr(int64_t v) { return reinterpret_cast<uint8_t*>(static_cast<uintptr_t>(v)); }
+
+py::tuple dgc_region_layout(int64_t capacity, int64_t world) {
+  uint64_t r, f;
+  uint64_t total = nangila_dgc_region_bytes(uint32_t(capacity), int32_t(world), &r, &f);
+  return py::make_tuple(total, r, f, nangila_dgc_scratch_words());
+}
+
+void dgc_launch(const std::vector<at::Tensor>& grad, const std::vector<at::Tensor>& u, const std::vector<at::Tensor>& v,
+                const std::vector<at::Tensor>& scratch, const std::vector<at::Tensor>& status,
+                const std::vector<at::Tensor>& out_count, const std::vector<int64_t>& region_ptrs, int64_t recv_off,
+                int64_t flag_off, int64_t rank0, int64_t k, int64_t capacity, int64_t epoch, double momentum,
+                double timeout_s, int64_t grid_x) {
+  const size_t nvr = grad.size();
+  TORCH_CHECK(nvr >= 1 && nvr <= NANGILA_MAX_VRANKS && u.size() == nvr && v.size() == nvr && scratch.size() == nvr &&
+                  status.size() == nvr && out_count.size() == nvr, "nangila: per-rank list length mismatch");
+  const size_t world = region_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= NANGILA_MAX_RANKS, "nangila: bad world size");
+  NangilaDgcParams p;
+  std::memset(&p, 0, sizeof p);
+  p.n = grad[0].numel();
+  p.world = int32_t(world);
+  p.rank0 = int32_t(rank0);
+  p.nvr = int32_t(nvr);
+  p.grad_dtype = dtype_code(grad[0]);
+  p.k = uint32_t(k);
+  p.capacity = uint32_t(capacity);
+  p.epoch = uint32_t(epoch);
+  p.momentum = float(momentum);
+  p.timeout_ns = uint64_t(timeout_s * 1e9);
+  p.grid_x = int32_t(grid_x);
+  p.recv_off = uint64_t(recv_off);
+  p.flag_off = uint64_t(flag_off);
+  for (size_t i = 0; i < nvr; ++i) {
+    TORCH_CHECK(grad[i].is_cuda() && grad[i].is_contiguous() && grad[i].numel() == p.n, "nangila: grad");
+    TORCH_CHECK(u[i].scalar_type() == at::kFloat && v[i].scalar_type() == at::kFloat && u[i].numel() == p.n &&
+                    v[i].numel() == p.n && u[i].is_contiguous() && v[i].is_contiguous(), "nangila: u/v must be fp32[n]");
+    TORCH_CHECK(scratch[i].scalar_type() == at::kInt && scratch[i].numel() >= int64_t(nangila_dgc_scratch_words()), "scratch");
+    TORCH_CHECK(status[i].scalar_type() == at::kInt && status[i].numel() >= 8, "status");
+    TORCH_CHECK(out_count[i].scalar_type() == at::kInt && out_count[i].numel() >= 2, "out_count");
+    p.grad[i] = grad[i].data_ptr();
+    p.u[i] = u[i].data_ptr<float>();
+    p.v[i] = v[i].data_ptr<float>();
+    p.scratch[i] = reinterpret_cast<uint32_t*>(scratch[i].data_ptr<int32_t>());
+    p.status[i] = reinterpret_cast<uint32_t*>(status[i].data_ptr<int32_t>());
+    p.out_count[i] = reinterpret_cast<uint32_t*>(out_count[i].data_ptr<int32_t>());
+  }
+  for (size_t r = 0; r < world; ++r) p.region[r] = as_ptr(region_ptrs[r]);
+  c10::cuda::CUDAGuard guard(grad[0].device());
+  check_launch(nangila_dgc_launch(&p, at::cuda::getCurrentCUDAStream()), "dgc_launch");
+}
+
+// ---- small reductions ---------------------------------------------------------------------------------
+at::Tensor state_hash(const std::vector<at::Tensor>& tensors, int64_t seed) {
+  TORCH_CHECK(!tensors.empty(), "nangila: state_hash needs at least one tensor");
+  auto out = at::zeros({1}, tensors[0].options().dtype(at::kLong));
+  c10::cuda::CUDAGuard guard(tensors[0].device());
+  uint64_t s = uint64_t(seed);
+  for (const at::Tensor& t : tensors) {
+    TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "nangila: state_hash wants contiguous CUDA tensors");
+    check_launch(nangila_state_hash(t.data_ptr(), t.numel() * t.element_size(), s,
+                                    reinterpret_cast<uint64_t*>(out.data_ptr<int64_t>()),
+                                    at::cuda::getCurrentCUDAStream()), "state_hash");
+    s = s * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull;  // a different stream of hashes per tensor
+  }
+  return out;
+}
+at::Tensor crc32_device(const at::Tensor& t) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "nangila: crc32 wants a contiguous CUDA tensor");
+  const int64_t nbytes = t.numel() * t.element_size();
+  auto scratch = at::empty({nangila_crc32_scratch_words(nbytes)}, t.options().dtype(at::kInt));
+  auto out = at::zeros({1}, t.options().dtype(at::kInt));
+  c10::cuda::CUDAGuard guard(t.device());
+  check_launch(nangila_crc32(t.data_ptr(), nbytes, reinterpret_cast<uint32_t*>(scratch.data_ptr<int32_t>()),
+                             reinterpret_cast<uint32_t*>(out.data_ptr<int32_t>()), at::cuda::getCurrentCUDAStream()),
+               "crc32");
+  return out;
+}
+// returns (float[4] = {max|x|, k-th largest |x|, gamma, non-finite count}, int32[256] histogram of |x|/max)
+py::tuple absmax_hist(const at::Tensor& x, int64_t k, double qmax) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "nangila: absmax_hist wants a contiguous CUDA tensor");
+  auto scratch = at::empty({int64_t(nangila_absmax_scratch_words())}, x.options().dtype(at::kInt));
+  auto out = at::zeros({4}, x.options().dtype(at::kFloat));
+  auto hist = at::zeros({256}, x.options().dtype(at::kInt));
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(nangila_absmax_hist(x.data_ptr(), dtype_code(x), x.numel(), uint32_t(k), float(qmax),
+                                   reinterpret_cast<uint32_t*>(scratch.data_ptr<int32_t>()), out.data_ptr<float>(),
+                                   reinterpret_cast<uint32_t*>(hist.data_ptr<int32_t>()),
+                                   at::cuda::getCurrentCUDAStream()), "absmax_hist");
+  return py::make_tuple(out, hist);
+}
+
+// ---- Sculptor statistics ---------------------------------------------------------------------------------
+template <class Desc>
+at::Tensor to_device_descs(const std::vector<Desc>& v, const at::Device& dev) {
+  auto host = at::empty({int64_t(v.size() * sizeof(Desc))}, at::TensorOptions().dtype(at::kByte));
+  std::memcpy(host.data_ptr(), v.data(), v.size() * sizeof(Desc));
+  return host.to(dev);
+}
+at::Tensor sculptor_layer_sumsq(const std::vector<at::Tensor>& layers) {
+  TORCH_CHECK(!layers.empty(), "nangila: no layers");
+  std::vector<NangilaLayerDesc> d(layers.size());
+  int64_t mx = 1;
+  for (size_t i = 0; i < layers.size(); ++i) {
+    TORCH_CHECK(layers[i].is_cuda() && layers[i].is_contiguous(), "nangila: layers must be contiguous CUDA tensors");
+    d[i] = NangilaLayerDesc{layers[i].data_ptr(), layers[i].numel(), dtype_code(layers[i]), 0};
+    mx = std::max<int64_t>(mx, layers[i].numel());
+  }
+  c10::cuda::CUDAGuard guard(layers[0].device());
+  at::Tensor descs = to_device_descs(d, layers[0].device());
+  auto out = at::zeros({int64_t(layers.size())}, layers[0].options().dtype(at::kDouble));
+  check_launch(nangila_sculptor_layer_sumsq(reinterpret_cast<const NangilaLayerDesc*>(descs.data_ptr()),
+                                            int32_t(layers.size()), mx, out.data_ptr<double>(),
+                                            at::cuda::getCurrentCUDAStream()), "sculptor_layer_sumsq");
+  return out;
+}
+std::vector<NangilaPairDesc> pair_descs(const std::vector<at::Tensor>& xi, const std::vector<at::Tensor>& xj,
+                                        const std::vector<at::Tensor>& state, const std::vector<int64_t>& count_after,
+                                        int64_t* mx) {
+  TORCH_CHECK(xi.size() == xj.size() && xi.size() == state.size() && xi.size() == count_after.size() && !xi.empty(),
+              "nangila: pair list length mismatch");
+  std::vector<NangilaPairDesc> d(xi.size());
+  *mx = 1;
+  for (size_t i = 0; i < xi.size(); ++i) {
+    TORCH_CHECK(xi[i].numel() == xj[i].numel() && xi[i].scalar_type() == xj[i].scalar_type() && xi[i].is_contiguous() &&
+                    xj[i].is_contiguous(), "nangila: pair members must match in size and dtype");
+    TORCH_CHECK(state[i].scalar_type() == at::kFloat && state[i].numel() == 5 * xi[i].numel() && state[i].is_contiguous(),
+                "nangila: pair state must be float[5 * numel]");
+    d[i] = NangilaPairDesc{xi[i].data_ptr(), xj[i].data_ptr(), state[i].data_ptr<float>(), xi[i].numel(),
+                           dtype_code(xi[i]), int32_t(count_after[i])};
+    *mx = std::max<int64_t>(*mx, xi[i].numel());
+  }
+  return d;
+}
+void sculptor_pair_update(const std::vector<at::Tensor>& xi, const std::vector<at::Tensor>& xj,
+                          const std::vector<at::Tensor>& state, const std::vector<int64_t>& count_after) {
+  int64_t mx;
+  auto d = pair_descs(xi, xj, state, count_after, &mx);
+  c10::cuda::CUDAGuard guard(xi[0].device());
+  at::Tensor descs = to_device_descs(d, xi[0].device());
+  check_launch(nangila_sculptor_pair_update(reinterpret_cast<const NangilaPairDesc*>(descs.data_ptr()), int32_t(d.size()),
+                                            mx, at::cuda::getCurrentCUDAStream()), "sculptor_pair_update");
+}
+at::Tensor sculptor_pair_finalize(const std::vector<at::Tensor>& state, const std::vector<int64_t>& count) {
+  std::vector<at::Tensor> dummy;
+  TORCH_CHECK(!state.empty() && state.size() == count.size(), "nangila: pair list length mismatch");
+  std::vector<NangilaPairDesc> d(state.size());
+  int64_t mx = 1;
+  for (size_t i = 0; i < state.size(); ++i) {
+    const int64_t n = state[i].numel() / 5;
+    d[i] = NangilaPairDesc{nullptr, nullptr, state[i].data_ptr<float>(), n, NANGILA_F32, int32_t(count[i])};
+    mx = std::max<int64_t>(mx, n);
+  }
+  c10::cuda::CUDAGuard guard(state[0].device());
+  at::Tensor descs = to_device_descs(d, state[0].device());
+  auto out = at::zeros({int64_t(state.size()), 8}, state[0].options().dtype(at::kDouble));
+  check_launch(nangila_sculptor_pair_finalize(reinterpret_cast<const NangilaPairDesc*>(descs.data_ptr()),
+                                              int32_t(d.size()), mx, out.data_ptr<double>(),
+                                              at::cuda::getCurrentCUDAStream()), "sculptor_pair_finalize");
+  return out;
+}
+
+}  // namespace
+
+void register_more(py::module_& m) {
+  m.def("dgc_region_layout", &dgc_region_layout);
+  m.def("dgc_launch", &dgc_launch, py::arg("grad"), py::arg("u"), py::arg("v"), py::arg("scratch"), py::arg("status"),
+        py::arg("out_count"), py::arg("region_ptrs"), py::arg("recv_off"), py::arg("flag_off"), py::arg("rank0"),
+        py::arg("k"), py::arg("capacity"), py::arg("epoch"), py::arg("momentum"), py::arg("timeout_s"),
+        py::arg("grid_x"));
+  m.def("state_hash", &state_hash, py::arg("tensors"), py::arg("seed") = 0);
+  m.def("crc32", &crc32_device);
+  m.def("absmax_hist", &absmax_hist, py::arg("x"), py::arg("k"), py::arg("qmax") = 7.0);
+  m.def("sculptor_layer_sumsq", &sculptor_layer_sumsq);
+  m.def("sculptor_pair_update", &sculptor_pair_update);
+  m.def("sculptor_pair_finalize", &sculptor_pair_finalize);
+}

@@ -40,7 +40,7 @@ typedef struct NangilaPredResParams {
   uint64_t recv1_off, recv2_off, flag1_off, flag2_off; /* byte offsets inside a region */
   int64_t n;                           /* elements in the bucket */
   int32_t world, rank0, nvr;
-  int32_t chunk_elems;                 /* multiple of 4096 */
+  int32_t chunk_elems;                 /* multiple of 2048 */
   int32_t nchunks;                     /* ceil(n / chunk_elems) */
   int32_t grad_dtype, state_dtype;     /* NangilaDType; state is F32 or BF16 */
   int32_t mode;                        /* 0 compressed, 1 uncompressed */
@@ -59,6 +59,62 @@ uint64_t nangila_predres_region_bytes(int64_t n, int32_t world, int32_t chunk_el
                                       uint64_t* recv1_off, uint64_t* recv2_off, uint64_t* flag1_off,
                                       uint64_t* flag2_off);
 int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_t stream);
+
+/* ---- fused DGC exchange (see dgc_fused.cu) ------------------------------------------------------------
+ * u = m u + g; v += u; exact k-th largest |v| by radix select; (index, value) compaction with masking
+ * of u and v; sparse all-gather into every rank's receive slots; scatter-add value / W into the
+ * bucket. Cooperative launch; grid_x * nvr CTAs must be co-resident. */
+typedef struct NangilaDgcParams {
+  void* grad[NANGILA_MAX_VRANKS];       /* in: gradient; out: dense mean of the selected entries */
+  float* u[NANGILA_MAX_VRANKS];         /* momentum-corrected velocity, n floats */
+  float* v[NANGILA_MAX_VRANKS];         /* accumulated (unsent) gradient, n floats */
+  uint32_t* scratch[NANGILA_MAX_VRANKS];/* nangila_dgc_scratch_words() words, any content */
+  uint32_t* status[NANGILA_MAX_VRANKS]; /* 8 words, zero before launch */
+  uint32_t* out_count[NANGILA_MAX_VRANKS]; /* [0] entries sent by this rank, [1] threshold bit pattern */
+  uint8_t* region[NANGILA_MAX_RANKS];
+  uint64_t recv_off, flag_off;
+  int64_t n;
+  int32_t world, rank0, nvr, grad_dtype;
+  uint32_t k;                           /* entries to keep: ceil(n (1 - sparsity)) */
+  uint32_t capacity;                    /* list capacity per rank, multiple of 4, >= k */
+  uint32_t epoch;
+  float momentum;                       /* momentum-correction factor m in [0, 1) */
+  uint64_t timeout_ns;
+  int32_t grid_x;
+} NangilaDgcParams;
+uint64_t nangila_dgc_region_bytes(uint32_t capacity, int32_t world, uint64_t* recv_off, uint64_t* flag_off);
+uint32_t nangila_dgc_scratch_words(void);
+int nangila_dgc_launch(const NangilaDgcParams* p, cudaStream_t stream);
+
+/* ---- Sculptor calibration statistics (sculptor_stats.cu) -----------------------------------------------
+ * Descriptor arrays live in DEVICE memory. */
+typedef struct NangilaLayerDesc {
+  const void* data;
+  int64_t numel;
+  int32_t dtype;
+  int32_t pad_;
+} NangilaLayerDesc;
+typedef struct NangilaPairDesc {
+  const void* data_i;
+  const void* data_j;
+  float* state;          /* 5 * numel floats: mean_i, mean_j, m2_i, m2_j, co-moment */
+  int64_t numel;
+  int32_t dtype;
+  int32_t count_after;   /* number of samples including the one being added */
+} NangilaPairDesc;
+int nangila_sculptor_layer_sumsq(const NangilaLayerDesc* layers, int32_t nlayers, int64_t max_numel, double* out,
+                                 cudaStream_t stream);
+int nangila_sculptor_pair_update(const NangilaPairDesc* pairs, int32_t npairs, int64_t max_numel, cudaStream_t stream);
+int nangila_sculptor_pair_finalize(const NangilaPairDesc* pairs, int32_t npairs, int64_t max_numel, double* out,
+                                   cudaStream_t stream);
+
+/* ---- state hash, parallel CRC32, absmax / percentile ------------------------------------------------------ */
+int nangila_state_hash(const void* data, int64_t nbytes, uint64_t seed, uint64_t* out, cudaStream_t stream);
+int64_t nangila_crc32_scratch_words(int64_t nbytes);
+int nangila_crc32(const void* data, int64_t nbytes, uint32_t* scratch, uint32_t* out, cudaStream_t stream);
+uint32_t nangila_absmax_scratch_words(void);
+int nangila_absmax_hist(const void* x, int32_t dtype, int64_t n, uint32_t k, float qmax, uint32_t* scratch, float* out,
+                        uint32_t* hist256, cudaStream_t stream);
 
 /* ---- single-scale compatibility kernels (reference signature: predict.cu / reconstruct.cu) ------- */
 int nangila_predict_quantize_gamma(const float* grad, const float* g_curr, const float* g_prev, float mu,

@@ -37,7 +37,10 @@ using namespace dev;
 using namespace comm;
 
 constexpr int kThreads = 256;
-constexpr int kElemsPerIter = kThreads * kElemsPerThread;  // 4096
+constexpr int kE = kElems8;                       // elements per thread per iteration
+constexpr int kElemsPerIter = kThreads * kE;      // 2048
+constexpr int kPackedPerIter = kElemsPerIter / 2; // bytes of nibbles per iteration
+constexpr int kScalesPerIter = kElemsPerIter / kQuantBlock;
 
 // packed nibbles, then one bf16 scale per 64 elements, then a 16-byte trailer whose first word is the
 // sender's prediction gain (phase 1) or the mean gain of all senders (phase 2)
@@ -46,8 +49,52 @@ __host__ __device__ inline uint64_t compressed_trailer_off(int chunk) {
 }
 __host__ __device__ inline uint64_t compressed_slot_bytes(int chunk) { return compressed_trailer_off(chunk) + 16; }
 
+__device__ __forceinline__ uint32_t* packed_ptr(uint8_t* slot, int it, int tid) {
+  return reinterpret_cast<uint32_t*>(slot + uint64_t(it) * kPackedPerIter) + tid;
+}
+__device__ __forceinline__ uint16_t* scale_ptr(uint8_t* slot, int C, int it, int tid) {
+  return reinterpret_cast<uint16_t*>(slot + uint64_t(C) / 2) + (it * kScalesPerIter + tid / kLanes8);
+}
+
+struct TaskInfo {
+  int phase;  // 1, 2, 3 or 0 (padding task: nothing to do)
+  int c;      // chunk
+  int j;      // index of the chunk among its owner's chunks
+  int o;      // owner rank
+};
+__device__ __forceinline__ TaskInfo decode_task(int task, int me, int W, int NC, int T1, int my_owned) {
+  TaskInfo t;
+  if (task < T1) {
+    const int k = task / W, d = task % W;
+    t.o = (me + 1 + d) % W;  // remote owners first, own chunk last in each round
+    t.c = k * W + t.o;
+    t.j = k;
+    t.phase = t.c < NC ? 1 : 0;
+  } else if (task < T1 + my_owned) {
+    t.j = task - T1;
+    t.c = t.j * W + me;
+    t.o = me;
+    t.phase = 2;
+  } else {
+    t.c = task - T1 - my_owned;
+    t.j = t.c / W;
+    t.o = t.c % W;
+    t.phase = 3;
+  }
+  return t;
+}
+
+constexpr int kWarps = kThreads / 32;
+constexpr int kSlots = 4;  // completion counters in flight per CTA
+
+// The eight warps of a CTA work on the same task but never meet at a block barrier: each warp waits
+// for the task's input flag itself, processes its own 256-element slices of every iteration, and then
+// bumps the task's completion counter in shared memory. Whichever warp arrives last publishes the
+// task's flag (system-scope fence + release store). A block barrier here would leave every warp idle,
+// with no loads in flight, until the slowest one and the fence were done. A warp may run at most
+// kSlots - 1 tasks ahead of the slowest warp of its CTA (the counters are reused round-robin).
 template <typename T, typename S, bool COMPRESSED>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 4)
 predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   const int vr = blockIdx.y;
   const int me = p.rank0 + vr;
@@ -59,59 +106,87 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   const int my_owned = NC > me ? (NC - me + W - 1) / W : 0;
   const int64_t n = p.n;
   const int tid = threadIdx.x;
+  const int lane = tid & 31;
   const uint64_t slot = COMPRESSED ? compressed_slot_bytes(C) : uint64_t(C) * sizeof(T);
   const uint32_t epoch = p.epoch;
+  uint32_t* status = p.status[vr];
+  uint8_t* myreg = p.region[me];
+  const int T1 = owned_max * W;
+  const int ntasks = T1 + my_owned + NC;
+
+  __shared__ int s_count[kSlots];   // warps that have finished the task in this slot
+  __shared__ int s_done;            // tasks of this CTA whose flag has been published
+  __shared__ float red[5][kWarps];
+  if (tid < kSlots) s_count[tid] = 0;
+  if (tid == 0) s_done = 0;
+  __syncthreads();
+
   const float mu = p.mu;
   const float kappa = p.pred_gain[vr];  // this rank's prediction gain for the bucket, in [0, 1]
-
   T* __restrict__ grad = static_cast<T*>(p.grad[vr]);
   S* __restrict__ prev = static_cast<S*>(p.prev[vr]);
   const S* __restrict__ curr = static_cast<const S*>(p.curr[vr]);
   S* __restrict__ ef = static_cast<S*>(p.ef[vr]);
   S* __restrict__ ef2 = static_cast<S*>(p.ef2[vr]);
-  uint32_t* status = p.status[vr];
-  uint8_t* myreg = p.region[me];
-
   const uint32_t key1 = make_key(p.seed, p.step, p.bucket_id, uint32_t(me), 1u);
   const uint32_t key2 = make_key(p.seed, p.step, p.bucket_id, 0u, 2u);
   const bool stochastic = p.stochastic != 0;
-
   float sum_e2 = 0.0f, sum_g2 = 0.0f, sum_xp = 0.0f, sum_pp = 0.0f, sum_f2 = 0.0f;
 
-  const int T1 = owned_max * W;
-  const int ntasks = T1 + my_owned + NC;
-  for (int task = blockIdx.x; task < ntasks; task += gridDim.x) {
-    if (*reinterpret_cast<volatile uint32_t*>(&status[kStatusCode]) != 0u) break;
+  int local = 0;  // number of the task within this CTA
+  for (int task = blockIdx.x; task < ntasks; task += gridDim.x, ++local) {
+    const TaskInfo t = decode_task(task, me, W, NC, T1, my_owned);
+    const int c = t.c, j = t.j;
+    // ---- entry (per warp): stop if this rank has failed; do not run too far ahead; wait for inputs ----
+    int ok = 1;
+    if (lane == 0) {
+      if (*reinterpret_cast<volatile uint32_t*>(&status[kStatusCode]) != 0u) ok = 0;
+      const uint64_t t0 = globaltimer_ns();
+      while (ok && local - *reinterpret_cast<volatile int*>(&s_done) >= kSlots) {
+        __nanosleep(64);
+        if (*reinterpret_cast<volatile uint32_t*>(&status[kStatusCode]) != 0u) ok = 0;
+        else if (globaltimer_ns() - t0 > p.timeout_ns) {
+          report_failure(status, kTimeoutGrid, uint32_t(me), 0xffffffffu, epoch, 0u, uint32_t(t.phase), uint32_t(c));
+          ok = 0;
+        }
+      }
+      if (ok && t.phase == 2) {
+        for (int r = 0; r < W && ok; ++r)
+          ok = wait_flag(reinterpret_cast<const uint32_t*>(myreg + p.flag1_off) + (uint64_t(j) * W + r), epoch,
+                         p.timeout_ns, status, kTimeoutPhase2, uint32_t(me), uint32_t(r), 2u, uint32_t(c));
+      } else if (ok && t.phase == 3) {
+        ok = wait_flag(reinterpret_cast<const uint32_t*>(myreg + p.flag2_off) + c, epoch, p.timeout_ns, status,
+                       kTimeoutPhase3, uint32_t(me), uint32_t(t.o), 3u, uint32_t(c));
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) break;
 
-    if (task < T1) {
-      // ---------------- phase 1: quantize own residual, push to the chunk's owner -----------------
-      const int k = task / W, d = task % W;
-      const int o = (me + 1 + d) % W;  // remote owners first, own chunk last in each round
-      const int c = k * W + o;
-      if (c >= NC) continue;
-      const int j = c / W;
-      uint8_t* dst = p.region[o] + p.recv1_off + (uint64_t(j) * W + me) * slot;
+    if (t.phase == 1) {
+      // ---------------- phase 1: quantize own residual, push to the chunk's owner -------------------
+      uint8_t* dst = p.region[t.o] + p.recv1_off + (uint64_t(j) * W + me) * slot;
+#pragma unroll 2
       for (int it = 0; it < iters; ++it) {
-        const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kElemsPerThread;
-        float g[16];
-        load16_guarded<T>(grad, base, n, g);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) g[i] = sanitize(g[i]);
+        const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kE;
+        float g[kE];
+        load8_guarded<T>(grad, base, n, g);
         if constexpr (COMPRESSED) {
-          float pv[16], cu[16];
-          load16_guarded<S>(prev, base, n, pv);
-          load16_guarded<S>(curr, base, n, cu);
-          float e[16];
+          float pv[kE], cu[kE], e[kE];
+          load8_guarded<S>(prev, base, n, pv);
+          load8_guarded<S>(curr, base, n, cu);
           if (ef != nullptr) {
-            load16_guarded<S>(ef, base, n, e);
+            load8_guarded<S>(ef, base, n, e);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) e[i] += g[i];
+            for (int i = 0; i < kE; ++i) {
+              g[i] = sanitize(g[i]);
+              e[i] += g[i];
+            }
           } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) e[i] = g[i];
+            for (int i = 0; i < kE; ++i) e[i] = g[i] = sanitize(g[i]);
           }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < kE; ++i) {
             const float pred = __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
             sum_g2 = __fmaf_rn(g[i], g[i], sum_g2);
             sum_xp = __fmaf_rn(e[i], pred, sum_xp);  // <g + ef, g_hat>
@@ -119,153 +194,141 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
             e[i] = __fmaf_rn(-kappa, pred, e[i]);
             sum_e2 = __fmaf_rn(e[i], e[i], sum_e2);
           }
-          uint2 packed;
-          uint32_t sb;
-          float deq[16];
-          quantize16(e, key1, uint32_t(base >> 1), stochastic, packed, sb, deq);
+          uint32_t packed, sb;
+          quantize8(e, key1, uint32_t(base >> 1), stochastic, packed, sb);
           if (ef != nullptr) {
-            store16_guarded<S>(ef, base, n, e);
+            store8_guarded<S>(ef, base, n, e);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) sum_f2 = __fmaf_rn(e[i], e[i], sum_f2);
+            for (int i = 0; i < kE; ++i) sum_f2 = __fmaf_rn(e[i], e[i], sum_f2);
           }
-          *reinterpret_cast<uint2*>(dst + uint64_t(it) * (kElemsPerIter / 2) + tid * 8) = packed;
-          if ((tid & (kLanesPerBlock - 1)) == 0)
-            *reinterpret_cast<uint16_t*>(dst + uint64_t(C) / 2 +
-                                         (uint64_t(it) * (kElemsPerIter / kQuantBlock) + tid / kLanesPerBlock) * 2) =
-                uint16_t(sb);
+          *packed_ptr(dst, it, tid) = packed;
+          if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
         } else {
-          Vec16<T>::store(reinterpret_cast<T*>(dst) + int64_t(it) * kElemsPerIter + tid * kElemsPerThread, g);
+#pragma unroll
+          for (int i = 0; i < kE; ++i) g[i] = sanitize(g[i]);
+          Vec8<T>::store(reinterpret_cast<T*>(dst) + int64_t(it) * kElemsPerIter + tid * kE, g);
         }
       }
       if (COMPRESSED && tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
-      __syncthreads();
-      if (tid == 0) {
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t*>(p.region[o] + p.flag1_off) + (uint64_t(j) * W + me), epoch);
-      }
-    } else if (task < T1 + my_owned) {
-      // ---------------- phase 2: owner reduces the W contributions and broadcasts ------------------
-      const int j = task - T1;
-      const int c = j * W + me;
-      bool ok = true;
-      if (tid < W)
-        ok = wait_flag(reinterpret_cast<const uint32_t*>(myreg + p.flag1_off) + (uint64_t(j) * W + tid), epoch,
-                       p.timeout_ns, status, kTimeoutPhase2, uint32_t(me), uint32_t(tid), 2u, uint32_t(c));
-      if (!__syncthreads_and(ok ? 1 : 0)) break;
+    } else if (t.phase == 2) {
+      // ---------------- phase 2: owner reduces the W contributions and broadcasts --------------------
       const float inv_w = 1.0f / float(W);
+      uint8_t* src0 = myreg + p.recv1_off + uint64_t(j) * W * slot;
       if (COMPRESSED && tid < W) {
         // mean prediction gain of the senders: every rank applies the same value in phase 3
         float kbar = 0.0f;
         for (int r = 0; r < W; ++r)
-          kbar += *reinterpret_cast<const float*>(myreg + p.recv1_off + (uint64_t(j) * W + r) * slot +
-                                                  compressed_trailer_off(C));
+          kbar += *reinterpret_cast<const float*>(src0 + uint64_t(r) * slot + compressed_trailer_off(C));
         *reinterpret_cast<float*>(p.region[tid] + p.recv2_off + uint64_t(c) * slot + compressed_trailer_off(C)) =
             kbar * inv_w;
       }
+#pragma unroll 2
       for (int it = 0; it < iters; ++it) {
-        float acc[16];
+        float acc[kE];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-        for (int r = 0; r < W; ++r) {
-          const uint8_t* src = myreg + p.recv1_off + (uint64_t(j) * W + r) * slot;
-          if constexpr (COMPRESSED) {
-            const uint2 pk = *reinterpret_cast<const uint2*>(src + uint64_t(it) * (kElemsPerIter / 2) + tid * 8);
-            const uint32_t sb = *reinterpret_cast<const uint16_t*>(
-                src + uint64_t(C) / 2 + (uint64_t(it) * (kElemsPerIter / kQuantBlock) + tid / kLanesPerBlock) * 2);
-            dequant16_add(pk, bf16_bits_to_float(sb), acc);
-          } else {
-            float v[16];
-            Vec16<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kElemsPerThread, v);
+        for (int i = 0; i < kE; ++i) acc[i] = 0.0f;
+        if constexpr (COMPRESSED) {
+#pragma unroll 4
+          for (int r = 0; r < W; ++r) {
+            uint8_t* src = src0 + uint64_t(r) * slot;
+            dequant8_add(*packed_ptr(src, it, tid), bf16_bits_to_float(*scale_ptr(src, C, it, tid)), acc);
+          }
+        } else {
+#pragma unroll 4
+          for (int r = 0; r < W; ++r) {
+            float v[kE];
+            Vec8<T>::load(reinterpret_cast<const T*>(src0 + uint64_t(r) * slot) + int64_t(it) * kElemsPerIter + tid * kE, v);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] += v[i];
+            for (int i = 0; i < kE; ++i) acc[i] += v[i];
           }
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] *= inv_w;
+        for (int i = 0; i < kE; ++i) acc[i] *= inv_w;
         if constexpr (COMPRESSED) {
-          const int64_t obase = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kElemsPerThread;
+          const int64_t obase = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
           if (ef2 != nullptr) {
-            float f[16];
-            Vec16<S>::load(ef2 + obase, f);
+            float f[kE];
+            Vec8<S>::load(ef2 + obase, f);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] += f[i];
+            for (int i = 0; i < kE; ++i) acc[i] += f[i];
           }
-          const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kElemsPerThread;
-          uint2 packed;
-          uint32_t sb;
-          float deq[16];
-          quantize16(acc, key2, uint32_t(base >> 1), stochastic, packed, sb, deq);
-          if (ef2 != nullptr) Vec16<S>::store(ef2 + obase, acc);
+          const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kE;
+          uint32_t packed, sb;
+          quantize8(acc, key2, uint32_t(base >> 1), stochastic, packed, sb);
+          if (ef2 != nullptr) Vec8<S>::store(ef2 + obase, acc);
           for (int r = 0; r < W; ++r) {
-            const int rr = (me + 1 + r) % W;
-            uint8_t* dst = p.region[rr] + p.recv2_off + uint64_t(c) * slot;
-            *reinterpret_cast<uint2*>(dst + uint64_t(it) * (kElemsPerIter / 2) + tid * 8) = packed;
-            if ((tid & (kLanesPerBlock - 1)) == 0)
-              *reinterpret_cast<uint16_t*>(dst + uint64_t(C) / 2 +
-                                           (uint64_t(it) * (kElemsPerIter / kQuantBlock) + tid / kLanesPerBlock) * 2) =
-                  uint16_t(sb);
+            uint8_t* dst = p.region[(me + 1 + r) % W] + p.recv2_off + uint64_t(c) * slot;
+            *packed_ptr(dst, it, tid) = packed;
+            if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
           }
         } else {
           for (int r = 0; r < W; ++r) {
-            const int rr = (me + 1 + r) % W;
-            uint8_t* dst = p.region[rr] + p.recv2_off + uint64_t(c) * slot;
-            Vec16<T>::store(reinterpret_cast<T*>(dst) + int64_t(it) * kElemsPerIter + tid * kElemsPerThread, acc);
+            uint8_t* dst = p.region[(me + 1 + r) % W] + p.recv2_off + uint64_t(c) * slot;
+            Vec8<T>::store(reinterpret_cast<T*>(dst) + int64_t(it) * kElemsPerIter + tid * kE, acc);
           }
         }
       }
-      __syncthreads();
-      if (tid < W) {
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t*>(p.region[tid] + p.flag2_off) + c, epoch);
-      }
-    } else {
-      // ---------------- phase 3: reconstruct, write bucket and history ------------------------------
-      const int c = task - T1 - my_owned;
-      bool ok = true;
-      if (tid == 0)
-        ok = wait_flag(reinterpret_cast<const uint32_t*>(myreg + p.flag2_off) + c, epoch, p.timeout_ns, status,
-                       kTimeoutPhase3, uint32_t(me), uint32_t(c % W), 3u, uint32_t(c));
-      if (!__syncthreads_and(ok ? 1 : 0)) break;
-      const uint8_t* src = myreg + p.recv2_off + uint64_t(c) * slot;
+    } else if (t.phase == 3) {
+      // ---------------- phase 3: reconstruct, write bucket and history -------------------------------
+      uint8_t* src = myreg + p.recv2_off + uint64_t(c) * slot;
       const float kbar = COMPRESSED ? *reinterpret_cast<const float*>(src + compressed_trailer_off(C)) : 0.0f;
+#pragma unroll 2
       for (int it = 0; it < iters; ++it) {
-        const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kElemsPerThread;
+        const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kE;
         if (base >= n) continue;
-        float out[16];
+        float out[kE];
         if constexpr (COMPRESSED) {
-          float pv[16], cu[16];
-          load16_guarded<S>(prev, base, n, pv);
-          load16_guarded<S>(curr, base, n, cu);
+          float pv[kE], cu[kE];
+          load8_guarded<S>(prev, base, n, pv);
+          load8_guarded<S>(curr, base, n, cu);
+          const uint32_t pk = *packed_ptr(src, it, tid);
+          const float sc = bf16_bits_to_float(*scale_ptr(src, C, it, tid));
 #pragma unroll
-          for (int i = 0; i < 16; ++i) out[i] = kbar * __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
-          const uint2 pk = *reinterpret_cast<const uint2*>(src + uint64_t(it) * (kElemsPerIter / 2) + tid * 8);
-          const uint32_t sb = *reinterpret_cast<const uint16_t*>(
-              src + uint64_t(C) / 2 + (uint64_t(it) * (kElemsPerIter / kQuantBlock) + tid / kLanesPerBlock) * 2);
-          dequant16_add(pk, bf16_bits_to_float(sb), out);
+          for (int i = 0; i < kE; ++i) out[i] = kbar * __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+          dequant8_add(pk, sc, out);
         } else {
-          Vec16<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kElemsPerThread, out);
+          Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
         }
-        store16_guarded<T>(grad, base, n, out);
-        store16_guarded<S>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
+        store8_guarded<T>(grad, base, n, out);
+        store8_guarded<S>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
+      }
+    }
+
+    // ---- exit (per warp): count this warp in; the last warp of the CTA publishes the task ----
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      const int sl = local % kSlots;
+      if (atomicAdd(&s_count[sl], 1) == kWarps - 1) {
+        s_count[sl] = 0;
+        if (t.phase == 1) {
+          __threadfence_system();
+          st_release_sys(reinterpret_cast<uint32_t*>(p.region[t.o] + p.flag1_off) + (uint64_t(j) * W + me), epoch);
+        } else if (t.phase == 2) {
+          __threadfence_system();
+          for (int r = 0; r < W; ++r)
+            st_release_sys(reinterpret_cast<uint32_t*>(p.region[(me + 1 + r) % W] + p.flag2_off) + c, epoch);
+        }
+        __threadfence_block();
+        atomicAdd(&s_done, 1);
       }
     }
   }
 
   // per-rank telemetry: five atomics per CTA
   if (p.stats[vr] != nullptr && COMPRESSED) {
-    __shared__ float red[5][kThreads / 32];
     float v[5] = {sum_e2, sum_g2, sum_xp, sum_pp, sum_f2};
 #pragma unroll
     for (int k = 0; k < 5; ++k) {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) v[k] += __shfl_xor_sync(0xffffffffu, v[k], off);
-      if ((tid & 31) == 0) red[k][tid >> 5] = v[k];
+      if (lane == 0) red[k][tid >> 5] = v[k];
     }
     __syncthreads();
     if (tid < 5) {
       float a = 0.0f;
 #pragma unroll
-      for (int i = 0; i < kThreads / 32; ++i) a += red[tid][i];
+      for (int i = 0; i < kWarps; ++i) a += red[tid][i];
       atomicAdd(&p.stats[vr][tid], a);
     }
   }

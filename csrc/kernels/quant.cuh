@@ -205,5 +205,125 @@ __device__ __forceinline__ void dequant16_add(const uint2 packed, float scale, f
   }
 }
 
+// ---- 8-element variants: one 16-byte load per 16-bit tensor, eight lanes share a 64-element block ----
+constexpr int kElems8 = 8;
+constexpr int kLanes8 = kQuantBlock / kElems8;  // 8
+
+template <typename T>
+struct Vec8;
+template <>
+struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <>
+struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(w[j] << 16);
+      v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <>
+struct Vec8<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <typename T>
+__device__ __forceinline__ void load8_guarded(const T* p, int64_t base, int64_t n, float (&v)[8]) {
+  if (base + 8 <= n) {
+    Vec8<T>::load(p + base, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (base + i < n) ? Vec16<T>::to_float(p[base + i]) : 0.0f;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8_guarded(T* p, int64_t base, int64_t n, const float (&v)[8]) {
+  if (base + 8 <= n) {
+    Vec8<T>::store(p + base, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (base + i < n) p[base + i] = Vec16<T>::from_float(v[i]);
+  }
+}
+
+// Quantize the 8 values of this lane; the eight lanes (lane & ~7 .. lane | 7) holding one 64-element
+// block call it together. On return `e` holds the error e - q * scale. `pair0` = index of e[0] / 2.
+__device__ __forceinline__ void quantize8(float (&e)[8], uint32_t key, uint32_t pair0, bool stochastic,
+                                          uint32_t& packed, uint32_t& scale_bits) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(e[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  scale_bits = bf16_ceil_bits(__fmul_rn(amax, 0.14285715f));  // amax * fl(1/7), rounded up to bf16
+  const float s = bf16_bits_to_float(scale_bits);
+  const bool live = s > 1e-30f;
+  const float inv = live ? __frcp_rn(s) : 0.0f;
+  if (!live) scale_bits = 0;
+  uint32_t w = 0u;
+#pragma unroll
+  for (int i = 0; i < 8; i += 2) {
+    float u0 = 0.5f, u1 = 0.5f;
+    if (stochastic) {
+      uint32_t h = mix32(key + (pair0 + uint32_t(i >> 1)) * 0x9E3779B9u);
+      u0 = float(h & 0xffffu) * (1.0f / 65536.0f);
+      u1 = float(h >> 16) * (1.0f / 65536.0f);
+    }
+    const float q0 = fminf(fmaxf(floorf(__fmaf_rn(e[i], inv, u0)), -8.0f), 7.0f);
+    const float q1 = fminf(fmaxf(floorf(__fmaf_rn(e[i + 1], inv, u1)), -8.0f), 7.0f);
+    e[i] = live ? __fmaf_rn(-q0, s, e[i]) : e[i];
+    e[i + 1] = live ? __fmaf_rn(-q1, s, e[i + 1]) : e[i + 1];
+    w |= ((uint32_t(int(q0)) & 0xfu) << (4 * i)) | ((uint32_t(int(q1)) & 0xfu) << (4 * (i + 1)));
+  }
+  packed = w;
+}
+__device__ __forceinline__ void dequant8_add(uint32_t packed, float scale, float (&acc)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int q = int(packed << (28 - 4 * i)) >> 28;
+    acc[i] = __fmaf_rn(float(q), scale, acc[i]);
+  }
+}
+
 }  // namespace dev
 }  // namespace nangila

@@ -130,9 +130,9 @@ class PredResEngine:
         if self.ctas > 0:
             cap = self.ctas
         elif self.loopback:
-            cap = max(1, (148 * 2) // self.nvr)  # the cooperative launch must be co-resident
+            cap = max(1, (148 * 4) // self.nvr)  # the cooperative launch must be co-resident
         else:
-            cap = 148 * 2
+            cap = 148 * 4
         return max(1, min(want, cap))
 
     def _take_slot(self, index: int) -> int:

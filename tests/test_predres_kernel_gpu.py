@@ -195,7 +195,7 @@ def test_wait_times_out_and_reports_status():
     grads = [torch.randn(n, device="cuda")]
     before = grads[0].clone()
     eng.reduce(0, grads, compressed=False)
-    with pytest.raises(RuntimeError, match="timeout in phase 2"):
+    with pytest.raises(RuntimeError, match="timeout in phase"):
         eng.check_status()
     assert torch.equal(grads[0], before)  # nothing was reconstructed, the bucket is untouched
     assert torch.ones(4, device="cuda").sum().item() == 4.0  # the device is still healthy
