@@ -187,6 +187,106 @@ at::Tensor sculptor_pair_finalize(const std::vector<at::Tensor>& state, const st
   return out;
 }
 
+// ---- fully-sharded collectives -------------------------------------------------------------------------
+py::tuple rs_region_layout(int64_t n, int64_t world, int64_t chunk_elems) {
+  uint64_t r1, f1;
+  int32_t nchunks;
+  uint64_t total = nangila_rs_region_bytes(n, int32_t(world), int32_t(chunk_elems), &r1, &f1, &nchunks);
+  return py::make_tuple(total, r1, f1, nchunks);
+}
+// Compressed reduce-scatter: `input[v]` holds world equal shards; `output[v]` receives the reduced shard.
+void rs_launch(const std::vector<at::Tensor>& input, const std::vector<at::Tensor>& output,
+               const std::vector<c10::optional<at::Tensor>>& ef, const std::vector<at::Tensor>& status,
+               const std::vector<int64_t>& region_ptrs, int64_t recv1_off, int64_t flag1_off, int64_t nchunks,
+               int64_t rank0, int64_t chunk_elems, bool stochastic, int64_t epoch, int64_t seed, int64_t step,
+               int64_t bucket_id, double out_scale, double timeout_s, int64_t grid_x) {
+  const size_t nvr = input.size();
+  const size_t world = region_ptrs.size();
+  TORCH_CHECK(nvr >= 1 && nvr <= NANGILA_MAX_VRANKS && output.size() == nvr && ef.size() == nvr && status.size() == nvr,
+              "nangila: per-rank list length mismatch");
+  TORCH_CHECK(world >= 1 && world <= NANGILA_MAX_RANKS, "nangila: bad world size");
+  NangilaPredResParams p;
+  std::memset(&p, 0, sizeof p);
+  p.n = input[0].numel();
+  p.world = int32_t(world);
+  p.rank0 = int32_t(rank0);
+  p.nvr = int32_t(nvr);
+  p.chunk_elems = int32_t(chunk_elems);
+  p.nchunks = int32_t(nchunks);
+  p.grad_dtype = dtype_code(input[0]);
+  p.state_dtype = NANGILA_BF16;
+  p.mode = 2;
+  p.stochastic = stochastic ? 1 : 0;
+  p.epoch = uint32_t(epoch);
+  p.seed = uint32_t(seed);
+  p.step = uint32_t(step);
+  p.bucket_id = uint32_t(bucket_id);
+  p.mu = 0.0f;
+  p.out_scale = float(out_scale);
+  p.timeout_ns = uint64_t(timeout_s * 1e9);
+  p.grid_x = int32_t(grid_x);
+  p.recv1_off = uint64_t(recv1_off);
+  p.flag1_off = uint64_t(flag1_off);
+  for (size_t v = 0; v < nvr; ++v) {
+    TORCH_CHECK(input[v].is_cuda() && input[v].is_contiguous() && input[v].numel() == p.n, "nangila: rs input");
+    TORCH_CHECK(output[v].is_cuda() && output[v].is_contiguous() && output[v].numel() * int64_t(world) == p.n &&
+                    output[v].scalar_type() == input[v].scalar_type(), "nangila: rs output must be one shard of the input dtype");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(input[v].data_ptr()) & 15u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(output[v].data_ptr()) & 15u) == 0, "nangila: rs buffers must be 16-byte aligned");
+    p.grad[v] = input[v].data_ptr();
+    p.out_shard[v] = output[v].data_ptr();
+    if (ef[v].has_value()) {
+      TORCH_CHECK(ef[v]->scalar_type() == at::kBFloat16 && ef[v]->numel() == p.n && ef[v]->is_contiguous(), "nangila: rs ef must be bf16[n]");
+      p.ef[v] = ef[v]->data_ptr();
+    }
+    p.status[v] = reinterpret_cast<uint32_t*>(status[v].data_ptr<int32_t>());
+  }
+  for (size_t r = 0; r < world; ++r) p.region[r] = as_ptr(region_ptrs[r]);
+  c10::cuda::CUDAGuard guard(input[0].device());
+  check_launch(nangila_predres_launch(&p, at::cuda::getCurrentCUDAStream()), "rs_launch");
+}
+
+py::tuple ag_region_layout(int64_t shard_elems, int64_t world, int64_t chunk_elems, int64_t bits) {
+  uint64_t r, f;
+  uint64_t total = nangila_ag_region_bytes(shard_elems, int32_t(world), int32_t(chunk_elems), int32_t(bits), &r, &f);
+  return py::make_tuple(total, r, f);
+}
+void ag_launch(const std::vector<at::Tensor>& input, const std::vector<at::Tensor>& output,
+               const std::vector<at::Tensor>& status, const std::vector<int64_t>& region_ptrs, int64_t recv_off,
+               int64_t flag_off, int64_t rank0, int64_t chunk_elems, int64_t bits, int64_t epoch, double timeout_s,
+               int64_t grid_x) {
+  const size_t nvr = input.size();
+  const size_t world = region_ptrs.size();
+  TORCH_CHECK(nvr >= 1 && nvr <= NANGILA_MAX_VRANKS && output.size() == nvr && status.size() == nvr, "nangila: list length mismatch");
+  NangilaAgParams p;
+  std::memset(&p, 0, sizeof p);
+  p.shard_elems = input[0].numel();
+  p.world = int32_t(world);
+  p.rank0 = int32_t(rank0);
+  p.nvr = int32_t(nvr);
+  p.dtype = dtype_code(input[0]);
+  p.chunk_elems = int32_t(chunk_elems);
+  p.bits = int32_t(bits);
+  p.epoch = uint32_t(epoch);
+  p.timeout_ns = uint64_t(timeout_s * 1e9);
+  p.grid_x = int32_t(grid_x);
+  p.recv_off = uint64_t(recv_off);
+  p.flag_off = uint64_t(flag_off);
+  for (size_t v = 0; v < nvr; ++v) {
+    TORCH_CHECK(input[v].is_cuda() && input[v].is_contiguous() && input[v].numel() == p.shard_elems, "nangila: ag input");
+    TORCH_CHECK(output[v].is_cuda() && output[v].is_contiguous() && output[v].numel() == p.shard_elems * int64_t(world) &&
+                    output[v].scalar_type() == input[v].scalar_type(), "nangila: ag output must hold world shards of the input dtype");
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(input[v].data_ptr()) & 15u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(output[v].data_ptr()) & 15u) == 0, "nangila: ag buffers must be 16-byte aligned");
+    p.in_shard[v] = input[v].data_ptr();
+    p.out_full[v] = output[v].data_ptr();
+    p.status[v] = reinterpret_cast<uint32_t*>(status[v].data_ptr<int32_t>());
+  }
+  for (size_t r = 0; r < world; ++r) p.region[r] = as_ptr(region_ptrs[r]);
+  c10::cuda::CUDAGuard guard(input[0].device());
+  check_launch(nangila_ag_launch(&p, at::cuda::getCurrentCUDAStream()), "ag_launch");
+}
+
 }  // namespace
 
 void register_more(py::module_& m) {
@@ -195,6 +295,10 @@ void register_more(py::module_& m) {
         py::arg("out_count"), py::arg("region_ptrs"), py::arg("recv_off"), py::arg("flag_off"), py::arg("rank0"),
         py::arg("k"), py::arg("capacity"), py::arg("epoch"), py::arg("momentum"), py::arg("timeout_s"),
         py::arg("grid_x"));
+  m.def("rs_region_layout", &rs_region_layout);
+  m.def("rs_launch", &rs_launch);
+  m.def("ag_region_layout", &ag_region_layout);
+  m.def("ag_launch", &ag_launch);
   m.def("state_hash", &state_hash, py::arg("tensors"), py::arg("seed") = 0);
   m.def("crc32", &crc32_device);
   m.def("absmax_hist", &absmax_hist, py::arg("x"), py::arg("k"), py::arg("qmax") = 7.0);

@@ -43,8 +43,9 @@ typedef struct NangilaPredResParams {
   int32_t chunk_elems;                 /* multiple of 2048 */
   int32_t nchunks;                     /* ceil(n / chunk_elems) */
   int32_t grad_dtype, state_dtype;     /* NangilaDType; state is F32 or BF16 */
-  int32_t mode;                        /* 0 compressed, 1 uncompressed */
+  int32_t mode;                        /* 0 compressed all-reduce, 1 exact all-reduce, 2 compressed reduce-scatter */
   int32_t stochastic;                  /* 0: round to nearest (tests), 1: stochastic rounding */
+  int32_t measure;                     /* 1: accumulate <g+ef,g_hat>, <g_hat,g_hat> even when the gain is 0 */
   uint32_t epoch;                      /* strictly increasing per launch on this bucket, never 0 */
   uint32_t seed, step, bucket_id;
   float mu;
@@ -52,13 +53,36 @@ typedef struct NangilaPredResParams {
                                           reconstruction uses the mean of all ranks' values */
   uint64_t timeout_ns;
   int32_t grid_x;                      /* CTAs per rank */
+  void* out_shard[NANGILA_MAX_VRANKS]; /* mode 2: n / world elements of grad_dtype, this rank's reduced shard */
+  float out_scale;                     /* mode 2: result = sum of all ranks' values * out_scale (1/W for a mean) */
 } NangilaPredResParams;
 
 /* Bytes one rank's symmetric region must have for a bucket. */
 uint64_t nangila_predres_region_bytes(int64_t n, int32_t world, int32_t chunk_elems, int32_t grad_dtype,
                                       uint64_t* recv1_off, uint64_t* recv2_off, uint64_t* flag1_off,
                                       uint64_t* flag2_off);
+uint64_t nangila_rs_region_bytes(int64_t n, int32_t world, int32_t chunk_elems, uint64_t* recv1_off,
+                                 uint64_t* flag1_off, int32_t* nchunks);
 int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_t stream);
+
+/* ---- quantizing parameter all-gather (fsdp_ag_dequant.cu) ------------------------------------------------ */
+typedef struct NangilaAgParams {
+  const void* in_shard[NANGILA_MAX_VRANKS]; /* this rank's shard, shard_elems of dtype */
+  void* out_full[NANGILA_MAX_VRANKS];       /* world * shard_elems of dtype */
+  uint32_t* status[NANGILA_MAX_VRANKS];
+  uint8_t* region[NANGILA_MAX_RANKS];
+  uint64_t recv_off, flag_off;
+  int64_t shard_elems;                      /* multiple of 8 */
+  int32_t world, rank0, nvr, dtype;
+  int32_t chunk_elems;                      /* multiple of 2048 */
+  int32_t bits;                             /* 8 or 4 */
+  uint32_t epoch;
+  uint64_t timeout_ns;
+  int32_t grid_x;
+} NangilaAgParams;
+uint64_t nangila_ag_region_bytes(int64_t shard_elems, int32_t world, int32_t chunk_elems, int32_t bits,
+                                 uint64_t* recv_off, uint64_t* flag_off);
+int nangila_ag_launch(const NangilaAgParams* p, cudaStream_t stream);
 
 /* ---- fused DGC exchange (see dgc_fused.cu) ------------------------------------------------------------
  * u = m u + g; v += u; exact k-th largest |v| by radix select; (index, value) compaction with masking

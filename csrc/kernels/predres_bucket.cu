@@ -57,29 +57,42 @@ __device__ __forceinline__ uint16_t* scale_ptr(uint8_t* slot, int C, int it, int
 }
 
 struct TaskInfo {
-  int phase;  // 1, 2, 3 or 0 (padding task: nothing to do)
-  int c;      // chunk
-  int j;      // index of the chunk among its owner's chunks
-  int o;      // owner rank
+  int phase;      // 1, 2, 3 or 0 (padding task: nothing to do)
+  int c;          // chunk id (flag index)
+  int j;          // index of the chunk among its owner's chunks
+  int o;          // owner rank
+  int64_t base;   // first element of the chunk in the bucket
+  int64_t limit;  // elements at or beyond this index do not belong to the chunk's range
 };
-__device__ __forceinline__ TaskInfo decode_task(int task, int me, int W, int NC, int T1, int my_owned) {
+// All-reduce modes: chunk c covers [c C, (c+1) C) and belongs to rank c % W.
+// Reduce-scatter mode: the bucket is W equal shards; rank o owns shard o, cut into `cps` chunks.
+template <bool RS>
+__device__ __forceinline__ TaskInfo decode_task(int task, int me, int W, int NC, int T1, int my_owned, int C,
+                                                int64_t n, int cps, int64_t shard) {
   TaskInfo t;
   if (task < T1) {
     const int k = task / W, d = task % W;
     t.o = (me + 1 + d) % W;  // remote owners first, own chunk last in each round
-    t.c = k * W + t.o;
     t.j = k;
+    t.c = RS ? t.o * cps + k : k * W + t.o;
     t.phase = t.c < NC ? 1 : 0;
   } else if (task < T1 + my_owned) {
     t.j = task - T1;
-    t.c = t.j * W + me;
     t.o = me;
+    t.c = RS ? me * cps + t.j : t.j * W + me;
     t.phase = 2;
   } else {
     t.c = task - T1 - my_owned;
     t.j = t.c / W;
     t.o = t.c % W;
     t.phase = 3;
+  }
+  if (RS) {
+    t.base = int64_t(t.o) * shard + int64_t(t.j) * C;
+    t.limit = int64_t(t.o + 1) * shard;
+  } else {
+    t.base = int64_t(t.c) * C;
+    t.limit = n;
   }
   return t;
 }
@@ -93,18 +106,24 @@ constexpr int kSlots = 4;  // completion counters in flight per CTA
 // task's flag (system-scope fence + release store). A block barrier here would leave every warp idle,
 // with no loads in flight, until the slowest one and the fence were done. A warp may run at most
 // kSlots - 1 tasks ahead of the slowest warp of its CTA (the counters are reused round-robin).
-template <typename T, typename S, bool COMPRESSED>
+// MODE 0: exact all-reduce; 1: compressed all-reduce; 2: compressed reduce-scatter (phases 1 and 2
+// only: the owner writes the mean of its shard to out_shard, nothing is broadcast, no history).
+template <typename T, typename S, int MODE>
 __global__ void __launch_bounds__(kThreads, 4)
 predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
+  constexpr bool COMPRESSED = MODE != 0;
+  constexpr bool RS = MODE == 2;
   const int vr = blockIdx.y;
   const int me = p.rank0 + vr;
   const int W = p.world;
   const int C = p.chunk_elems;
   const int iters = C / kElemsPerIter;
   const int NC = p.nchunks;
-  const int owned_max = (NC + W - 1) / W;
-  const int my_owned = NC > me ? (NC - me + W - 1) / W : 0;
   const int64_t n = p.n;
+  const int64_t shard = RS ? n / W : 0;
+  const int cps = RS ? NC / W : 0;
+  const int owned_max = RS ? cps : (NC + W - 1) / W;
+  const int my_owned = RS ? cps : (NC > me ? (NC - me + W - 1) / W : 0);
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const uint64_t slot = COMPRESSED ? compressed_slot_bytes(C) : uint64_t(C) * sizeof(T);
@@ -112,7 +131,11 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   uint32_t* status = p.status[vr];
   uint8_t* myreg = p.region[me];
   const int T1 = owned_max * W;
-  const int ntasks = T1 + my_owned + NC;
+  const int ntasks = T1 + my_owned + (RS ? 0 : NC);
+  // Reduce-scatter has no phase 3 to prove that the owner is done reading, so its slots alternate
+  // between two sets by launch parity (a rank cannot get two launches ahead of a peer: its phase 2 of
+  // the launch in between needs that peer's flags).
+  const uint64_t recv1 = p.recv1_off + (RS ? uint64_t(epoch & 1u) * uint64_t(cps) * W * slot : 0);
 
   __shared__ int s_count[kSlots];   // warps that have finished the task in this slot
   __shared__ int s_done;            // tasks of this CTA whose flag has been published
@@ -122,7 +145,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   __syncthreads();
 
   const float mu = p.mu;
-  const float kappa = p.pred_gain[vr];  // this rank's prediction gain for the bucket, in [0, 1]
+  const float kappa = RS ? 0.0f : p.pred_gain[vr];  // this rank's prediction gain for the bucket, in [0, 1]
   T* __restrict__ grad = static_cast<T*>(p.grad[vr]);
   S* __restrict__ prev = static_cast<S*>(p.prev[vr]);
   const S* __restrict__ curr = static_cast<const S*>(p.curr[vr]);
@@ -131,12 +154,16 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   const uint32_t key1 = make_key(p.seed, p.step, p.bucket_id, uint32_t(me), 1u);
   const uint32_t key2 = make_key(p.seed, p.step, p.bucket_id, 0u, 2u);
   const bool stochastic = p.stochastic != 0;
+  // With a zero gain the history only matters for the statistics that steer the gain; the host asks
+  // for them on probe steps (p.measure) and the loads are skipped otherwise.
+  const bool use_history = !RS && (kappa != 0.0f || p.measure != 0);
   float sum_e2 = 0.0f, sum_g2 = 0.0f, sum_xp = 0.0f, sum_pp = 0.0f, sum_f2 = 0.0f;
 
   int local = 0;  // number of the task within this CTA
   for (int task = blockIdx.x; task < ntasks; task += gridDim.x, ++local) {
-    const TaskInfo t = decode_task(task, me, W, NC, T1, my_owned);
+    const TaskInfo t = decode_task<RS>(task, me, W, NC, T1, my_owned, C, n, cps, shard);
     const int c = t.c, j = t.j;
+    const int64_t lim = t.limit;
     // ---- entry (per warp): stop if this rank has failed; do not run too far ahead; wait for inputs ----
     int ok = 1;
     if (lane == 0) {
@@ -164,18 +191,23 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
 
     if (t.phase == 1) {
       // ---------------- phase 1: quantize own residual, push to the chunk's owner -------------------
-      uint8_t* dst = p.region[t.o] + p.recv1_off + (uint64_t(j) * W + me) * slot;
+      uint8_t* dst = p.region[t.o] + recv1 + (uint64_t(j) * W + me) * slot;
 #pragma unroll 2
       for (int it = 0; it < iters; ++it) {
-        const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kE;
+        const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
         float g[kE];
-        load8_guarded<T>(grad, base, n, g);
+        load8_guarded<T>(grad, base, lim, g);
         if constexpr (COMPRESSED) {
           float pv[kE], cu[kE], e[kE];
-          load8_guarded<S>(prev, base, n, pv);
-          load8_guarded<S>(curr, base, n, cu);
+          if (use_history) {
+            load8_guarded<S>(prev, base, lim, pv);
+            load8_guarded<S>(curr, base, lim, cu);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kE; ++i) pv[i] = cu[i] = 0.0f;
+          }
           if (ef != nullptr) {
-            load8_guarded<S>(ef, base, n, e);
+            load8_guarded<S>(ef, base, lim, e);
 #pragma unroll
             for (int i = 0; i < kE; ++i) {
               g[i] = sanitize(g[i]);
@@ -197,7 +229,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           uint32_t packed, sb;
           quantize8(e, key1, uint32_t(base >> 1), stochastic, packed, sb);
           if (ef != nullptr) {
-            store8_guarded<S>(ef, base, n, e);
+            store8_guarded<S>(ef, base, lim, e);
 #pragma unroll
             for (int i = 0; i < kE; ++i) sum_f2 = __fmaf_rn(e[i], e[i], sum_f2);
           }
@@ -213,8 +245,8 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
     } else if (t.phase == 2) {
       // ---------------- phase 2: owner reduces the W contributions and broadcasts --------------------
       const float inv_w = 1.0f / float(W);
-      uint8_t* src0 = myreg + p.recv1_off + uint64_t(j) * W * slot;
-      if (COMPRESSED && tid < W) {
+      uint8_t* src0 = myreg + recv1 + uint64_t(j) * W * slot;
+      if (COMPRESSED && !RS && tid < W) {
         // mean prediction gain of the senders: every rank applies the same value in phase 3
         float kbar = 0.0f;
         for (int r = 0; r < W; ++r)
@@ -243,8 +275,12 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           }
         }
 #pragma unroll
-        for (int i = 0; i < kE; ++i) acc[i] *= inv_w;
-        if constexpr (COMPRESSED) {
+        for (int i = 0; i < kE; ++i) acc[i] *= RS ? p.out_scale : inv_w;
+        if constexpr (RS) {
+          // reduce-scatter: the mean of this rank's shard is the result; nothing is broadcast
+          const int64_t local = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
+          store8_guarded<T>(static_cast<T*>(p.out_shard[vr]), local, shard, acc);
+        } else if constexpr (COMPRESSED) {
           const int64_t obase = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
           if (ef2 != nullptr) {
             float f[kE];
@@ -252,7 +288,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
 #pragma unroll
             for (int i = 0; i < kE; ++i) acc[i] += f[i];
           }
-          const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kE;
+          const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
           uint32_t packed, sb;
           quantize8(acc, key2, uint32_t(base >> 1), stochastic, packed, sb);
           if (ef2 != nullptr) Vec8<S>::store(ef2 + obase, acc);
@@ -274,17 +310,22 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
       const float kbar = COMPRESSED ? *reinterpret_cast<const float*>(src + compressed_trailer_off(C)) : 0.0f;
 #pragma unroll 2
       for (int it = 0; it < iters; ++it) {
-        const int64_t base = int64_t(c) * C + int64_t(it) * kElemsPerIter + tid * kE;
+        const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
         if (base >= n) continue;
         float out[kE];
         if constexpr (COMPRESSED) {
-          float pv[kE], cu[kE];
-          load8_guarded<S>(prev, base, n, pv);
-          load8_guarded<S>(curr, base, n, cu);
           const uint32_t pk = *packed_ptr(src, it, tid);
           const float sc = bf16_bits_to_float(*scale_ptr(src, C, it, tid));
+          if (kbar != 0.0f) {
+            float pv[kE], cu[kE];
+            load8_guarded<S>(prev, base, n, pv);
+            load8_guarded<S>(curr, base, n, cu);
 #pragma unroll
-          for (int i = 0; i < kE; ++i) out[i] = kbar * __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+            for (int i = 0; i < kE; ++i) out[i] = kbar * __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kE; ++i) out[i] = 0.0f;
+          }
           dequant8_add(pk, sc, out);
         } else {
           Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
@@ -304,7 +345,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
         if (t.phase == 1) {
           __threadfence_system();
           st_release_sys(reinterpret_cast<uint32_t*>(p.region[t.o] + p.flag1_off) + (uint64_t(j) * W + me), epoch);
-        } else if (t.phase == 2) {
+        } else if (t.phase == 2 && !RS) {
           __threadfence_system();
           for (int r = 0; r < W; ++r)
             st_release_sys(reinterpret_cast<uint32_t*>(p.region[(me + 1 + r) % W] + p.flag2_off) + c, epoch);
@@ -339,8 +380,9 @@ cudaError_t launch_ts(const NangilaPredResParams& p, cudaStream_t stream) {
   dim3 grid(unsigned(p.grid_x), unsigned(p.nvr));
   dim3 block(kThreads);
   void* args[] = {const_cast<NangilaPredResParams*>(&p)};
-  const void* fn = p.mode == 0 ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, true>)
-                               : reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, false>);
+  const void* fn = p.mode == 0   ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 1>)
+                   : p.mode == 1 ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 0>)
+                                 : reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 2>);
   if (p.nvr > 1) return cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream);
   return cudaLaunchKernel(fn, grid, block, args, 0, stream);
 }
@@ -368,14 +410,39 @@ extern "C" uint64_t nangila_predres_region_bytes(int64_t n, int32_t world, int32
   return off;
 }
 
+// Reduce-scatter mode (mode 2): only the phase-1 slots and flags are needed.
+extern "C" uint64_t nangila_rs_region_bytes(int64_t n, int32_t world, int32_t chunk_elems, uint64_t* recv1_off,
+                                            uint64_t* flag1_off, int32_t* nchunks) {
+  auto align = [](uint64_t x) { return (x + 255) & ~uint64_t(255); };
+  const int64_t shard = n / world;
+  const uint64_t cps = uint64_t((shard + chunk_elems - 1) / chunk_elems);
+  if (nchunks) *nchunks = int32_t(cps * world);
+  uint64_t off = 0;
+  if (recv1_off) *recv1_off = off;
+  off = align(off + 2 * cps * world * nangila::compressed_slot_bytes(chunk_elems));
+  if (flag1_off) *flag1_off = off;
+  off = align(off + cps * world * 4);
+  return off;
+}
+
 extern "C" int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_t stream) {
   using namespace nangila;
   if (p == nullptr || p->n <= 0 || p->world < 1 || p->world > NANGILA_MAX_RANKS || p->nvr < 1 ||
       p->nvr > NANGILA_MAX_VRANKS || p->rank0 < 0 || p->rank0 + p->nvr > p->world || p->chunk_elems <= 0 ||
-      p->chunk_elems % kElemsPerIter != 0 || p->epoch == 0 || p->grid_x < 1 ||
-      p->nchunks != int32_t((p->n + p->chunk_elems - 1) / p->chunk_elems) || !(p->mu >= 0.0f && p->mu <= 1.0f) ||
-      false)
+      p->chunk_elems % kElemsPerIter != 0 || p->epoch == 0 || p->grid_x < 1 || p->mode < 0 || p->mode > 2 ||
+      !(p->mu >= 0.0f && p->mu <= 1.0f))
     return int(cudaErrorInvalidValue);
+  if (p->mode == 2) {
+    // reduce-scatter: W equal shards whose length keeps 16-byte vector accesses aligned
+    if (p->n % p->world != 0 || (p->n / p->world) % 8 != 0) return int(cudaErrorInvalidValue);
+    const int64_t shard = p->n / p->world;
+    if (p->nchunks != int32_t(p->world * ((shard + p->chunk_elems - 1) / p->chunk_elems)))
+      return int(cudaErrorInvalidValue);
+    for (int v = 0; v < p->nvr; ++v)
+      if (p->out_shard[v] == nullptr) return int(cudaErrorInvalidValue);
+  } else if (p->nchunks != int32_t((p->n + p->chunk_elems - 1) / p->chunk_elems)) {
+    return int(cudaErrorInvalidValue);
+  }
   if (p->nvr > 1 && p->nvr != p->world) return int(cudaErrorInvalidValue);
   for (int v = 0; v < p->nvr; ++v)
     if (!(p->pred_gain[v] >= 0.0f && p->pred_gain[v] <= 1.0f)) return int(cudaErrorInvalidValue);

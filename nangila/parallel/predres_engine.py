@@ -107,6 +107,8 @@ class PredResEngine:
         self.owner_error_feedback = owner_error_feedback
         self.adaptive_gain = adaptive_gain and os.environ.get("NANGILA_PRED_GAIN") is None
         self.fixed_gain = float(os.environ.get("NANGILA_PRED_GAIN", "1"))
+        # with a zero gain the kernel skips the history loads except on every probe_every-th call
+        self.probe_every = max(1, int(os.environ.get("NANGILA_PROBE_EVERY", "8")))
         self.buckets: Dict[int, BucketState] = {}
         # one row of 8 floats per (bucket, emulated rank): {sum e^2, sum g^2, sum miss^2, sum ef^2, ...}
         self.max_buckets = max_buckets
@@ -191,7 +193,7 @@ class PredResEngine:
             grad=grads, prev=st.prev, curr=st.curr, ef=st.ef, ef2=st.ef2, stats=st.stats, status=self.status,
             region_ptrs=st.region.ptrs, recv1_off=r1, recv2_off=r2, flag1_off=f1, flag2_off=f2,
             rank0=0 if self.loopback else self.rank, chunk_elems=st.chunk, mode=0 if compressed else 1,
-            stochastic=self.stochastic, epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
+            stochastic=self.stochastic, measure=(st.calls % self.probe_every == 0), epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
             mu=self.momentum, pred_gain=self._gains(st), timeout_s=self.timeout_s, grid_x=self._grid(st),
         )
         if self.stream is not None:
@@ -241,8 +243,11 @@ class PredResEngine:
                 if f2 > 2.0 * g2:
                     st.pred_gain, st.cooldown = 0.0, 20
                     continue
-                best = min(max(xp / pp, 0.0), 1.0) if pp > 0.0 else 0.0
-                st.pred_gain = 0.5 * st.pred_gain + 0.5 * best
+                if pp <= 0.0:
+                    continue  # not a probe step: the kernel did not look at the history
+                best = min(max(xp / pp, 0.0), 1.0)
+                gain = 0.5 * st.pred_gain + 0.5 * best
+                st.pred_gain = gain if gain >= 0.05 else 0.0  # below 5 % the history loads cost more than they save
         stream = self.stream if self.stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(stream):
             self._stats_host.copy_(self.stats_table, non_blocking=True)
