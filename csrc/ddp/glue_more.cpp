@@ -287,6 +287,77 @@ void ag_launch(const std::vector<at::Tensor>& input, const std::vector<at::Tenso
   check_launch(nangila_ag_launch(&p, at::cuda::getCurrentCUDAStream()), "ag_launch");
 }
 
+// ---- PowerSGD (tcgen05) ----------------------------------------------------------------------------------
+// out (rows x 16 fp32) = M * Bt^T or M^T * Bt^T; zero-fills `out` first (the kernel may split K).
+void psgd_gemm(const at::Tensor& M, const at::Tensor& Bt, bool transposed, at::Tensor out, at::Tensor status,
+               double timeout_s) {
+  TORCH_CHECK(M.is_cuda() && M.dim() == 2 && M.scalar_type() == at::kBFloat16 && M.is_contiguous(), "nangila: M must be a contiguous bf16 matrix");
+  const int64_t m = M.size(0), n = M.size(1);
+  const int64_t k = transposed ? m : n, rows = transposed ? n : m;
+  TORCH_CHECK(Bt.scalar_type() == at::kBFloat16 && Bt.is_contiguous() && Bt.numel() == 16 * k, "nangila: Bt must be bf16[16, K]");
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == rows * 16, "nangila: out must be fp32[rows, 16]");
+  c10::cuda::CUDAGuard guard(M.device());
+  out.zero_();
+  check_launch(nangila_psgd_gemm(M.data_ptr(), int32_t(m), int32_t(n), Bt.data_ptr(), transposed ? 1 : 0, out.data_ptr<float>(),
+                                 reinterpret_cast<uint32_t*>(status.data_ptr<int32_t>()), uint64_t(timeout_s * 1e9),
+                                 at::cuda::getCurrentCUDAStream()), "psgd_gemm");
+}
+void psgd_prep(const at::Tensor& grad, const at::Tensor& ef, at::Tensor mef) {
+  TORCH_CHECK(grad.is_cuda() && grad.is_contiguous() && ef.scalar_type() == at::kBFloat16 && mef.scalar_type() == at::kBFloat16 &&
+                  ef.numel() == grad.numel() && mef.numel() == grad.numel(), "nangila: psgd_prep shapes");
+  c10::cuda::CUDAGuard guard(grad.device());
+  check_launch(nangila_psgd_prep(grad.data_ptr(), dtype_code(grad), ef.data_ptr(), mef.data_ptr(), grad.numel(),
+                                 at::cuda::getCurrentCUDAStream()), "psgd_prep");
+}
+void psgd_reconstruct(at::Tensor grad, at::Tensor ef, const at::Tensor& mef, const at::Tensor& P, const at::Tensor& Q,
+                      int64_t m, int64_t n, int64_t r) {
+  TORCH_CHECK(grad.is_cuda() && grad.is_contiguous() && grad.numel() == m * n && P.numel() == m * 16 && Q.numel() == n * 16 &&
+                  P.scalar_type() == at::kFloat && Q.scalar_type() == at::kFloat, "nangila: psgd_reconstruct shapes");
+  c10::cuda::CUDAGuard guard(grad.device());
+  check_launch(nangila_psgd_reconstruct(grad.data_ptr(), dtype_code(grad), ef.data_ptr(), mef.data_ptr(), P.data_ptr<float>(),
+                                        Q.data_ptr<float>(), int32_t(m), int32_t(n), int32_t(r),
+                                        at::cuda::getCurrentCUDAStream()), "psgd_reconstruct");
+}
+py::tuple psgd_exchange_layout(int64_t rows, int64_t rank, int64_t world) {
+  uint64_t r, f;
+  uint64_t total = nangila_psgd_exchange_region_bytes(int32_t(rows), int32_t(rank), int32_t(world), &r, &f);
+  return py::make_tuple(total, r, f);
+}
+void psgd_exchange(const std::vector<at::Tensor>& local, const std::vector<at::Tensor>& mean_out,
+                   const std::vector<at::Tensor>& scratch, const std::vector<at::Tensor>& t_out,
+                   const std::vector<at::Tensor>& status, const std::vector<int64_t>& region_ptrs, int64_t recv_off,
+                   int64_t flag_off, int64_t rows, int64_t rank, int64_t rank0, bool orth_mean, int64_t epoch,
+                   double timeout_s) {
+  const size_t nvr = local.size();
+  TORCH_CHECK(nvr >= 1 && nvr <= NANGILA_MAX_VRANKS && mean_out.size() == nvr && scratch.size() == nvr && t_out.size() == nvr &&
+                  status.size() == nvr, "nangila: list length mismatch");
+  NangilaPsgdExchangeParams p;
+  std::memset(&p, 0, sizeof p);
+  p.rows = int32_t(rows);
+  p.rank = int32_t(rank);
+  p.world = int32_t(region_ptrs.size());
+  p.rank0 = int32_t(rank0);
+  p.nvr = int32_t(nvr);
+  p.orth_mean = orth_mean ? 1 : 0;
+  p.epoch = uint32_t(epoch);
+  p.timeout_ns = uint64_t(timeout_s * 1e9);
+  p.recv_off = uint64_t(recv_off);
+  p.flag_off = uint64_t(flag_off);
+  for (size_t v = 0; v < nvr; ++v) {
+    TORCH_CHECK(local[v].scalar_type() == at::kFloat && local[v].numel() == rows * 16 && mean_out[v].numel() == rows * 16 &&
+                    scratch[v].numel() == rows * 16 && t_out[v].scalar_type() == at::kBFloat16 && t_out[v].numel() == rows * 16,
+                "nangila: psgd_exchange buffers must be [rows, 16]");
+    p.local[v] = local[v].data_ptr<float>();
+    p.mean_out[v] = mean_out[v].data_ptr<float>();
+    p.scratch[v] = scratch[v].data_ptr<float>();
+    p.t_out[v] = t_out[v].data_ptr();
+    p.status[v] = reinterpret_cast<uint32_t*>(status[v].data_ptr<int32_t>());
+  }
+  for (size_t r = 0; r < region_ptrs.size(); ++r) p.region[r] = as_ptr(region_ptrs[r]);
+  c10::cuda::CUDAGuard guard(local[0].device());
+  check_launch(nangila_psgd_exchange(&p, at::cuda::getCurrentCUDAStream()), "psgd_exchange");
+}
+
 }  // namespace
 
 void register_more(py::module_& m) {
@@ -295,6 +366,11 @@ void register_more(py::module_& m) {
         py::arg("out_count"), py::arg("region_ptrs"), py::arg("recv_off"), py::arg("flag_off"), py::arg("rank0"),
         py::arg("k"), py::arg("capacity"), py::arg("epoch"), py::arg("momentum"), py::arg("timeout_s"),
         py::arg("grid_x"));
+  m.def("psgd_gemm", &psgd_gemm);
+  m.def("psgd_prep", &psgd_prep);
+  m.def("psgd_reconstruct", &psgd_reconstruct);
+  m.def("psgd_exchange_layout", &psgd_exchange_layout);
+  m.def("psgd_exchange", &psgd_exchange);
   m.def("rs_region_layout", &rs_region_layout);
   m.def("rs_launch", &rs_launch);
   m.def("ag_region_layout", &ag_region_layout);

@@ -84,6 +84,30 @@ uint64_t nangila_ag_region_bytes(int64_t shard_elems, int32_t world, int32_t chu
                                  uint64_t* recv_off, uint64_t* flag_off);
 int nangila_ag_launch(const NangilaAgParams* p, cudaStream_t stream);
 
+/* ---- PowerSGD on tcgen05 tensor cores (powersgd_tcgen05.cu) ------------------------------------------------ */
+/* out (rows x 16 fp32, zero-filled by the caller) += M * Bt^T (transposed = 0, rows = m) or M^T * Bt^T
+ * (transposed = 1, rows = n). M: m x n bf16 row-major, m and n multiples of 8. Bt: 16 x K bf16. */
+int nangila_psgd_gemm(const void* M, int32_t m, int32_t n, const void* Bt, int32_t transposed, float* out,
+                      uint32_t* status, uint64_t timeout_ns, cudaStream_t stream);
+int nangila_psgd_prep(const void* grad, int32_t dtype, const void* ef, void* mef, int64_t numel, cudaStream_t stream);
+int nangila_psgd_reconstruct(void* grad, int32_t dtype, void* ef, const void* mef, const float* P, const float* Q,
+                             int32_t m, int32_t n, int32_t r, cudaStream_t stream);
+typedef struct NangilaPsgdExchangeParams {
+  const float* local[NANGILA_MAX_VRANKS];   /* rows x 16 fp32: this rank's factor */
+  float* mean_out[NANGILA_MAX_VRANKS];      /* rows x 16 fp32: mean over ranks (orthonormalised if orth_mean) */
+  float* scratch[NANGILA_MAX_VRANKS];       /* rows x 16 fp32, needed when orth_mean == 0 */
+  void* t_out[NANGILA_MAX_VRANKS];          /* 16 x rows bf16: orthonormalised mean, transposed */
+  uint32_t* status[NANGILA_MAX_VRANKS];
+  uint8_t* region[NANGILA_MAX_RANKS];
+  uint64_t recv_off, flag_off;
+  int32_t rows, rank, world, rank0, nvr, orth_mean;
+  uint32_t epoch;
+  uint64_t timeout_ns;
+} NangilaPsgdExchangeParams;
+uint64_t nangila_psgd_exchange_region_bytes(int32_t rows, int32_t rank, int32_t world, uint64_t* recv_off,
+                                            uint64_t* flag_off);
+int nangila_psgd_exchange(const NangilaPsgdExchangeParams* p, cudaStream_t stream);
+
 /* ---- fused DGC exchange (see dgc_fused.cu) ------------------------------------------------------------
  * u = m u + g; v += u; exact k-th largest |v| by radix select; (index, value) compaction with masking
  * of u and v; sparse all-gather into every rank's receive slots; scatter-add value / W into the
