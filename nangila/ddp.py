@@ -222,7 +222,8 @@ class NangilaDDPHook:
             from .parallel.powersgd_engine import PowerSGDEngine
 
             self._psgd_engine = PowerSGDEngine(self._engine.arena, tensor.device, rank=self.power_sgd_rank,
-                                               stream=self._engine.stream, group=self.process_group)
+                                               stream=self._engine.stream, group=self.process_group,
+                                               exact_engine=self._engine)
         sent = self._psgd_engine.reduce(index, bucket, tensor)
         self.total_original_bytes += tensor.numel() * tensor.element_size()
         self.total_compressed_bytes += sent

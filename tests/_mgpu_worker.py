@@ -118,6 +118,14 @@ def main():
         results["launches"] = stats["kernel_launches"]
         assert results["loss_base"] < 0.8 * base[0], "baseline did not learn"
         assert abs(results["loss_ours"] - results["loss_base"]) < 0.15 * results["loss_base"] + 0.05, results
+    if what in ("all", "compressors"):
+        base, _ = train(dev, rank, world, False, 60)
+        for ctype, name in ((1, "dgc"), (2, "powersgd")):
+            ours, stats = train(dev, rank, world, True, 60, compressor_type=ctype)
+            results[f"loss_{name}"] = sum(ours[-10:]) / 10
+            results[f"ratio_{name}"] = stats["overall_compression_ratio"]
+            assert results[f"loss_{name}"] < 0.9 * base[0], (name, results)
+        results["loss_base"] = sum(base[-10:]) / 10
     if rank == 0:
         print("MGPU_RESULT " + json.dumps(results), flush=True)
         if out_path:
