@@ -397,14 +397,13 @@ class NangilaDDPHook:
         """64-bit hash of the predictor state on this rank (host core, or a device reduction of the
         bucket histories when the CUDA path is active)."""
         if self._engine is not None and self._engine.buckets:
-            h = 0
+            from .ops.reductions import state_hash as device_hash
+
+            tensors = []
             for idx in sorted(self._engine.buckets):
                 st = self._engine.buckets[idx]
-                c = st.curr[0]
-                v = c.view(torch.int16 if c.element_size() == 2 else torch.int32).to(torch.int64)
-                w = torch.arange(1, v.numel() + 1, device=v.device, dtype=torch.int64)
-                h = (h * 1000003 + int(((v * w) & 0x7FFFFFFF).sum().item()) + idx) & 0xFFFFFFFFFFFFFFFF
-            return h
+                tensors += [st.curr[0], st.prev[0]]
+            return device_hash(tensors, seed=self.step_count)
         return int(self.hook.predictor_hash())
 
     def _verify_predictor_hash(self) -> bool:
