@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include "nangila_kernels.h"
+#include "nangila_noalloc.h"
 
 namespace nangila {
 namespace {
@@ -97,6 +98,58 @@ extern "C" int nangila_crc32(const void* data, int64_t nbytes, uint32_t* scratch
     return int(cudaErrorInvalidValue);
   if (nbytes == 0) return int(cudaMemsetAsync(out, 0, 4, stream));
   const int64_t nchunks = (nbytes + kChunk - 1) / kChunk;
+  crc_chunks_kernel<<<unsigned((nchunks + 127) / 128), 128, 0, stream>>>(static_cast<const uint8_t*>(data), nbytes,
+                                                                       scratch, nchunks);
+  crc_combine_kernel<<<1, 1024, 0, stream>>>(scratch, nchunks, nbytes, out);
+  return int(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in nangila_noalloc.h; the reference has nothing like it).
+//
+// The chunk table that nangila_crc32() takes from its caller lives here in a fixed array inside the
+// library image, so a caller that has no way to obtain device memory can still checksum a buffer: it
+// hands over only the data pointer and the 4-byte result location.
+namespace nangila {
+namespace {
+
+constexpr int64_t kNoAllocMaxBytes = int64_t(64) << 20;                    // largest buffer accepted
+constexpr int64_t kNoAllocWords = kNoAllocMaxBytes / kChunk + 1;           // 131073 words = 512 KiB + 4
+static __device__ __align__(256) uint32_t g_crc_scratch[kNoAllocWords];
+
+constexpr int kMaxDevices = 64;
+uint32_t* g_scratch_addr[kMaxDevices] = {};  // device address of g_crc_scratch, per device ordinal
+
+}  // namespace
+}  // namespace nangila
+
+extern "C" int64_t nangila_crc32_noalloc_max_bytes(void) { return nangila::kNoAllocMaxBytes; }
+
+extern "C" int nangila_crc32_noalloc(const void* data, int64_t nbytes, uint32_t* out, cudaStream_t stream) {
+  using namespace nangila;
+  if (out == nullptr || nbytes < 0 || (nbytes > 0 && data == nullptr)) return int(cudaErrorInvalidValue);
+  if (nbytes > kNoAllocMaxBytes) return int(cudaErrorInvalidValue);  // beyond the built-in table: refuse
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return int(e);
+  if (dev < 0 || dev >= kMaxDevices) return int(cudaErrorInvalidDevice);
+  if (g_scratch_addr[dev] == nullptr) {
+    // In host code `g_crc_scratch` is only a handle for the symbol, not an address a kernel could
+    // use; the address inside the current device's copy of the image has to be asked for.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_crc_scratch);
+    if (e != cudaSuccess) return int(e);
+    g_scratch_addr[dev] = static_cast<uint32_t*>(p);
+  }
+  uint32_t* scratch = g_scratch_addr[dev];
+  if (nbytes == 0) {
+    // nothing to hash: the result is 0; written by a kernel so that no memset node is needed either
+    crc_combine_kernel<<<1, 32, 0, stream>>>(scratch, 0, 0, out);
+    return int(cudaGetLastError());
+  }
+  const int64_t nchunks = (nbytes + kChunk - 1) / kChunk;
+  // Every table entry the second kernel reads is written by the first one in this same call, so
+  // nothing left over from an earlier call can leak into the result and nothing needs clearing.
   crc_chunks_kernel<<<unsigned((nchunks + 127) / 128), 128, 0, stream>>>(static_cast<const uint8_t*>(data), nbytes,
                                                                        scratch, nchunks);
   crc_combine_kernel<<<1, 1024, 0, stream>>>(scratch, nchunks, nbytes, out);
