@@ -120,6 +120,7 @@ def main() -> int:
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--model", default="small", choices=["small", "tiny"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--python-hook", action="store_true", help="per-bucket path in Python instead of the C++ hook")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -152,7 +153,7 @@ def main() -> int:
     ddp = DDP(model, device_ids=[local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
     hook = None
     if args.impl == "ours":
-        hook = register_nangila_hook(ddp, threshold=0.95, warmup_steps=100)
+        hook = register_nangila_hook(ddp, threshold=0.95, warmup_steps=100, prefer_cpp=not args.python_hook)
     opt = torch.optim.AdamW(ddp.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
 
     mb = args.micro_batch
@@ -245,7 +246,8 @@ def main() -> int:
         if hook is not None:
             st = hook.get_stats()
             out["compression"] = {"ratio": st.get("overall_compression_ratio"), "compressing": st["compression_enabled"],
-                                  "pred_gain": st.get("pred_gain_per_bucket")}
+                                  "pred_gain": st.get("pred_gain_per_bucket"),
+                                  "hook_impl": "c++" if st.get("cpp_hook") else "python"}
         print(json.dumps(out))
     dist.barrier()
     dist.destroy_process_group()

@@ -64,6 +64,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--iters", type=int, default=0)
     ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--gain", type=float, default=1.0,
+                    help="prediction gain of the compressed mode (0 = the history is neither read nor probed)")
     ap.add_argument("--out", default="")
     ap.add_argument("--only", default="", help="comma list of: nccl,exact,compressed")
     args = ap.parse_args()
@@ -88,6 +90,9 @@ def main() -> int:
     esize = 2 if dtype == torch.bfloat16 else 4
     arena = SymmArena(None, dev, segment_bytes=256 << 20)
     eng = PredResEngine(arena, dev, use_side_stream=False, adaptive_gain=False, ctas=args.ctas or None)
+    eng.fixed_gain = args.gain
+    if args.gain == 0.0:
+        eng.probe_every = 1 << 30
     hbm = measured_hbm_gbs()
     which = set(args.only.split(",")) if args.only else {"nccl", "exact", "compressed"}
     rows = []
@@ -98,7 +103,7 @@ def main() -> int:
         pool = max(2, min(8, int((300 << 20) // max(nbytes, 1)) + 1))  # rotate through > 2x L2
         iters = args.iters or (50 if nbytes <= (16 << 20) else 20 if nbytes <= (256 << 20) else 8)
         bufs = [(torch.randn(n, device=dev) * 1e-3).to(dtype) for _ in range(pool)]
-        row = {"mb": mb, "bytes": nbytes, "world": world, "dtype": args.dtype, "pool": pool, "iters": iters}
+        row = {"mb": mb, "bytes": nbytes, "world": world, "dtype": args.dtype, "pool": pool, "iters": iters, "gain": args.gain}
         scale = 2.0 * (world - 1) / world if world > 1 else 1.0
         if "nccl" in which and world > 1:
             t = time_ms(lambda i: dist.all_reduce(bufs[i % pool]), iters)
@@ -121,7 +126,8 @@ def main() -> int:
             ssize = st.state_dtype.itemsize
             if comp:
                 q = 0.5 + 2.0 / 64
-                hbm_bytes = n * (esize + 3 * ssize + ssize + q) + n * q * 2 + n * (q + 2 * ssize + esize + ssize)
+                hist = 2 * ssize if args.gain != 0.0 else 0  # history reads in phase 1 and again in phase 3
+                hbm_bytes = n * (esize + hist + 2 * ssize + q) + n * q * 2 + n * (q + hist + esize + ssize)
             else:
                 hbm_bytes = n * (esize * 2) + n * esize * 2 + n * (esize + esize + ssize)
             bound_ms = max(wire / (NVLINK_GBS * 1e6), hbm_bytes / (hbm * 1e6))

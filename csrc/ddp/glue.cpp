@@ -158,7 +158,8 @@ std::string error_string(int code) { return cudaGetErrorString(static_cast<cudaE
 
 }  // namespace
 
-void register_more(py::module_& m);  // other glue translation units append their bindings here
+void register_more(py::module_& m);
+void register_ddp_hook(py::module_& m);  // ddp_hook.cpp  // other glue translation units append their bindings here
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "nangila torch glue over the sm_100a kernels";
@@ -175,4 +176,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("stream_synchronize", &stream_synchronize);
   m.def("error_string", &error_string);
   register_more(m);
+  register_ddp_hook(m);
 }

@@ -22,6 +22,7 @@
 // chunk's reduction needs all ranks, a rank that has finished launch k of a bucket knows that all
 // ranks have finished reading what it wrote in launch k-1, so the slots need no double buffering.
 #include <algorithm>
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -97,6 +98,69 @@ __device__ __forceinline__ TaskInfo decode_task(int task, int me, int W, int NC,
   return t;
 }
 
+struct Stats {
+  float e2 = 0.0f, g2 = 0.0f, xp = 0.0f, pp = 0.0f, f2 = 0.0f;
+};
+
+// Phase 1 of the compressed modes for one chunk: x = g + ef - kappa * g_hat, block-INT4 quantize, new
+// error memory, packed nibbles and scales stored into the owner's slot `dst`.
+// LEAN: the rank's gain is zero and no statistics were asked for, so neither the history nor the
+// five running sums are touched. GUARD: the chunk straddles the end of the range.
+template <typename T, typename S, bool LEAN, bool GUARD>
+__device__ __forceinline__ void phase1_compressed(const T* __restrict__ grad, const S* __restrict__ prev,
+                                                  const S* __restrict__ curr, S* __restrict__ ef, uint8_t* dst,
+                                                  int64_t tbase, int64_t lim, int iters, int C, int tid, float mu,
+                                                  float kappa, bool use_history, uint32_t key1, bool stochastic,
+                                                  Stats& st) {
+#pragma unroll 2
+  for (int it = 0; it < iters; ++it) {
+    const int64_t base = tbase + int64_t(it) * kElemsPerIter + tid * kE;
+    float g[kE], e[kE];
+    load8<T, GUARD>(grad, base, lim, g);
+    if (ef != nullptr) {
+      load8<S, GUARD>(ef, base, lim, e);
+#pragma unroll
+      for (int i = 0; i < kE; ++i) {
+        g[i] = sanitize(g[i]);
+        e[i] += g[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) e[i] = g[i] = sanitize(g[i]);
+    }
+    if constexpr (!LEAN) {
+      float pv[kE], cu[kE];
+      if (use_history) {
+        load8<S, GUARD>(prev, base, lim, pv);
+        load8<S, GUARD>(curr, base, lim, cu);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kE; ++i) pv[i] = cu[i] = 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < kE; ++i) {
+        const float pred = __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+        st.g2 = __fmaf_rn(g[i], g[i], st.g2);
+        st.xp = __fmaf_rn(e[i], pred, st.xp);  // <g + ef, g_hat>
+        st.pp = __fmaf_rn(pred, pred, st.pp);  // <g_hat, g_hat>
+        e[i] = __fmaf_rn(-kappa, pred, e[i]);
+        st.e2 = __fmaf_rn(e[i], e[i], st.e2);
+      }
+    }
+    uint32_t packed, sb;
+    quantize8(e, key1, uint32_t(base >> 1), stochastic, packed, sb);
+    if (ef != nullptr) {
+      store8<S, GUARD>(ef, base, lim, e);
+      if constexpr (!LEAN) {
+#pragma unroll
+        for (int i = 0; i < kE; ++i) st.f2 = __fmaf_rn(e[i], e[i], st.f2);
+      }
+    }
+    *packed_ptr(dst, it, tid) = packed;
+    if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+  }
+}
+
 constexpr int kWarps = kThreads / 32;
 constexpr int kSlots = 4;  // completion counters in flight per CTA
 
@@ -107,12 +171,14 @@ constexpr int kSlots = 4;  // completion counters in flight per CTA
 // with no loads in flight, until the slowest one and the fence were done. A warp may run at most
 // kSlots - 1 tasks ahead of the slowest warp of its CTA (the counters are reused round-robin).
 // MODE 0: exact all-reduce; 1: compressed all-reduce; 2: compressed reduce-scatter (phases 1 and 2
-// only: the owner writes the mean of its shard to out_shard, nothing is broadcast, no history).
+// only: the owner writes the mean of its shard to out_shard, nothing is broadcast, no history);
+// 3: compressed all-reduce, lean phase 1 (this rank's gain is zero and no statistics are wanted).
 template <typename T, typename S, int MODE>
 __global__ void __launch_bounds__(kThreads, 4)
 predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   constexpr bool COMPRESSED = MODE != 0;
   constexpr bool RS = MODE == 2;
+  constexpr bool LEAN = MODE == 2 || MODE == 3;
   const int vr = blockIdx.y;
   const int me = p.rank0 + vr;
   const int W = p.world;
@@ -157,7 +223,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   // With a zero gain the history only matters for the statistics that steer the gain; the host asks
   // for them on probe steps (p.measure) and the loads are skipped otherwise.
   const bool use_history = !RS && (kappa != 0.0f || p.measure != 0);
-  float sum_e2 = 0.0f, sum_g2 = 0.0f, sum_xp = 0.0f, sum_pp = 0.0f, sum_f2 = 0.0f;
+  Stats acc_stats;
 
   int local = 0;  // number of the task within this CTA
   for (int task = blockIdx.x; task < ntasks; task += gridDim.x, ++local) {
@@ -192,56 +258,27 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
     if (t.phase == 1) {
       // ---------------- phase 1: quantize own residual, push to the chunk's owner -------------------
       uint8_t* dst = p.region[t.o] + recv1 + (uint64_t(j) * W + me) * slot;
+      const bool full = t.base + C <= lim;  // whole chunk inside the range: no per-access bounds checks
+      if constexpr (COMPRESSED) {
+        if (full)
+          phase1_compressed<T, S, LEAN, false>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
+                                               use_history, key1, stochastic, acc_stats);
+        else
+          phase1_compressed<T, S, LEAN, true>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
+                                              use_history, key1, stochastic, acc_stats);
+        if (tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
+      } else {
 #pragma unroll 2
-      for (int it = 0; it < iters; ++it) {
-        const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
-        float g[kE];
-        load8_guarded<T>(grad, base, lim, g);
-        if constexpr (COMPRESSED) {
-          float pv[kE], cu[kE], e[kE];
-          if (use_history) {
-            load8_guarded<S>(prev, base, lim, pv);
-            load8_guarded<S>(curr, base, lim, cu);
-          } else {
-#pragma unroll
-            for (int i = 0; i < kE; ++i) pv[i] = cu[i] = 0.0f;
-          }
-          if (ef != nullptr) {
-            load8_guarded<S>(ef, base, lim, e);
-#pragma unroll
-            for (int i = 0; i < kE; ++i) {
-              g[i] = sanitize(g[i]);
-              e[i] += g[i];
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < kE; ++i) e[i] = g[i] = sanitize(g[i]);
-          }
-#pragma unroll
-          for (int i = 0; i < kE; ++i) {
-            const float pred = __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
-            sum_g2 = __fmaf_rn(g[i], g[i], sum_g2);
-            sum_xp = __fmaf_rn(e[i], pred, sum_xp);  // <g + ef, g_hat>
-            sum_pp = __fmaf_rn(pred, pred, sum_pp);  // <g_hat, g_hat>
-            e[i] = __fmaf_rn(-kappa, pred, e[i]);
-            sum_e2 = __fmaf_rn(e[i], e[i], sum_e2);
-          }
-          uint32_t packed, sb;
-          quantize8(e, key1, uint32_t(base >> 1), stochastic, packed, sb);
-          if (ef != nullptr) {
-            store8_guarded<S>(ef, base, lim, e);
-#pragma unroll
-            for (int i = 0; i < kE; ++i) sum_f2 = __fmaf_rn(e[i], e[i], sum_f2);
-          }
-          *packed_ptr(dst, it, tid) = packed;
-          if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
-        } else {
+        for (int it = 0; it < iters; ++it) {
+          const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
+          float g[kE];
+          if (full) Vec8<T>::load(grad + base, g);
+          else load8_guarded<T>(grad, base, lim, g);
 #pragma unroll
           for (int i = 0; i < kE; ++i) g[i] = sanitize(g[i]);
           Vec8<T>::store(reinterpret_cast<T*>(dst) + int64_t(it) * kElemsPerIter + tid * kE, g);
         }
       }
-      if (COMPRESSED && tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
     } else if (t.phase == 2) {
       // ---------------- phase 2: owner reduces the W contributions and broadcasts --------------------
       const float inv_w = 1.0f / float(W);
@@ -308,31 +345,36 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
       // ---------------- phase 3: reconstruct, write bucket and history -------------------------------
       uint8_t* src = myreg + p.recv2_off + uint64_t(c) * slot;
       const float kbar = COMPRESSED ? *reinterpret_cast<const float*>(src + compressed_trailer_off(C)) : 0.0f;
+      auto body = [&](auto guard_tag) {
+        constexpr bool GUARD = decltype(guard_tag)::value;
 #pragma unroll 2
-      for (int it = 0; it < iters; ++it) {
-        const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
-        if (base >= n) continue;
-        float out[kE];
-        if constexpr (COMPRESSED) {
-          const uint32_t pk = *packed_ptr(src, it, tid);
-          const float sc = bf16_bits_to_float(*scale_ptr(src, C, it, tid));
-          if (kbar != 0.0f) {
-            float pv[kE], cu[kE];
-            load8_guarded<S>(prev, base, n, pv);
-            load8_guarded<S>(curr, base, n, cu);
+        for (int it = 0; it < iters; ++it) {
+          const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
+          if (GUARD && base >= n) continue;
+          float out[kE];
+          if constexpr (COMPRESSED) {
+            const uint32_t pk = *packed_ptr(src, it, tid);
+            const float sc = bf16_bits_to_float(*scale_ptr(src, C, it, tid));
+            if (kbar != 0.0f) {
+              float pv[kE], cu[kE];
+              load8<S, GUARD>(prev, base, n, pv);
+              load8<S, GUARD>(curr, base, n, cu);
 #pragma unroll
-            for (int i = 0; i < kE; ++i) out[i] = kbar * __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+              for (int i = 0; i < kE; ++i) out[i] = kbar * __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < kE; ++i) out[i] = 0.0f;
+            }
+            dequant8_add(pk, sc, out);
           } else {
-#pragma unroll
-            for (int i = 0; i < kE; ++i) out[i] = 0.0f;
+            Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
           }
-          dequant8_add(pk, sc, out);
-        } else {
-          Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
+          store8<T, GUARD>(grad, base, n, out);
+          store8<S, GUARD>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
         }
-        store8_guarded<T>(grad, base, n, out);
-        store8_guarded<S>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
-      }
+      };
+      if (t.base + C <= n) body(std::false_type{});
+      else body(std::true_type{});
     }
 
     // ---- exit (per warp): count this warp in; the last warp of the CTA publishes the task ----
@@ -357,8 +399,8 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   }
 
   // per-rank telemetry: five atomics per CTA
-  if (p.stats[vr] != nullptr && COMPRESSED) {
-    float v[5] = {sum_e2, sum_g2, sum_xp, sum_pp, sum_f2};
+  if (p.stats[vr] != nullptr && COMPRESSED && !LEAN) {
+    float v[5] = {acc_stats.e2, acc_stats.g2, acc_stats.xp, acc_stats.pp, acc_stats.f2};
 #pragma unroll
     for (int k = 0; k < 5; ++k) {
 #pragma unroll
@@ -380,7 +422,10 @@ cudaError_t launch_ts(const NangilaPredResParams& p, cudaStream_t stream) {
   dim3 grid(unsigned(p.grid_x), unsigned(p.nvr));
   dim3 block(kThreads);
   void* args[] = {const_cast<NangilaPredResParams*>(&p)};
-  const void* fn = p.mode == 0   ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 1>)
+  bool lean = p.mode == 0 && p.measure == 0;
+  for (int v = 0; v < p.nvr; ++v) lean = lean && p.pred_gain[v] == 0.0f;
+  const void* fn = p.mode == 0   ? (lean ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 3>)
+                                         : reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 1>))
                    : p.mode == 1 ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 0>)
                                  : reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 2>);
   if (p.nvr > 1) return cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream);

@@ -274,6 +274,11 @@ __device__ __forceinline__ void load8_guarded(const T* p, int64_t base, int64_t 
     for (int i = 0; i < 8; ++i) v[i] = (base + i < n) ? Vec16<T>::to_float(p[base + i]) : 0.0f;
   }
 }
+template <typename T, bool GUARD>
+__device__ __forceinline__ void load8(const T* p, int64_t base, int64_t n, float (&v)[8]) {
+  if constexpr (GUARD) load8_guarded<T>(p, base, n, v);
+  else Vec8<T>::load(p + base, v);
+}
 template <typename T>
 __device__ __forceinline__ void store8_guarded(T* p, int64_t base, int64_t n, const float (&v)[8]) {
   if (base + 8 <= n) {
@@ -287,6 +292,15 @@ __device__ __forceinline__ void store8_guarded(T* p, int64_t base, int64_t n, co
 
 // Quantize the 8 values of this lane; the eight lanes (lane & ~7 .. lane | 7) holding one 64-element
 // block call it together. On return `e` holds the error e - q * scale. `pair0` = index of e[0] / 2.
+//
+// Instruction diet (this routine bounds the kernel's issue rate):
+//  * uniforms: one hash per FOUR elements; byte k becomes the float 2^23 + byte with one byte-permute,
+//    and one FMA maps it to u = (byte + 0.5) / 256 (centred, so E[u] = 0.5 exactly);
+//  * q = min(floor(e / s + u), 7): no lower clamp is needed because |e| <= 7 s by construction, and a
+//    dead block (s == 0) has inv = 0, hence q = 0 and the error stays e;
+//  * packing: q + 8 of four elements is accumulated in ONE float by Horner steps of 16 (exact below
+//    2^16), converted once, and the two halves are merged; xor 0x88888888 turns the offset nibbles into
+//    two's complement.
 __device__ __forceinline__ void quantize8(float (&e)[8], uint32_t key, uint32_t pair0, bool stochastic,
                                           uint32_t& packed, uint32_t& scale_bits) {
   float amax = 0.0f;
@@ -296,26 +310,36 @@ __device__ __forceinline__ void quantize8(float (&e)[8], uint32_t key, uint32_t 
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
   scale_bits = bf16_ceil_bits(__fmul_rn(amax, 0.14285715f));  // amax * fl(1/7), rounded up to bf16
-  const float s = bf16_bits_to_float(scale_bits);
+  float s = bf16_bits_to_float(scale_bits);
   const bool live = s > 1e-30f;
   const float inv = live ? __frcp_rn(s) : 0.0f;
-  if (!live) scale_bits = 0;
-  uint32_t w = 0u;
-#pragma unroll
-  for (int i = 0; i < 8; i += 2) {
-    float u0 = 0.5f, u1 = 0.5f;
-    if (stochastic) {
-      uint32_t h = mix32(key + (pair0 + uint32_t(i >> 1)) * 0x9E3779B9u);
-      u0 = float(h & 0xffffu) * (1.0f / 65536.0f);
-      u1 = float(h >> 16) * (1.0f / 65536.0f);
-    }
-    const float q0 = fminf(fmaxf(floorf(__fmaf_rn(e[i], inv, u0)), -8.0f), 7.0f);
-    const float q1 = fminf(fmaxf(floorf(__fmaf_rn(e[i + 1], inv, u1)), -8.0f), 7.0f);
-    e[i] = live ? __fmaf_rn(-q0, s, e[i]) : e[i];
-    e[i + 1] = live ? __fmaf_rn(-q1, s, e[i + 1]) : e[i + 1];
-    w |= ((uint32_t(int(q0)) & 0xfu) << (4 * i)) | ((uint32_t(int(q1)) & 0xfu) << (4 * (i + 1)));
+  if (!live) {
+    scale_bits = 0;
+    s = 0.0f;
   }
-  packed = w;
+  float half[2];
+#pragma unroll
+  for (int hlf = 0; hlf < 2; ++hlf) {
+    float u[4] = {0.5f, 0.5f, 0.5f, 0.5f};
+    if (stochastic) {
+      const uint32_t h = mix32(key + (pair0 + uint32_t(hlf)) * 0x9E3779B9u);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        // bytes {h.byte[k], 0x00, 0x00, 0x4B}: the float 2^23 + byte
+        const float m = __uint_as_float(__byte_perm(h, 0x4B000000u, 0x7540u + uint32_t(k)));
+        u[k] = __fmaf_rn(m, 0.00390625f, -32767.998046875f);  // (byte + 0.5) / 256
+      }
+    }
+    float q[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = 4 * hlf + k;
+      q[k] = fminf(floorf(__fmaf_rn(e[i], inv, u[k])), 7.0f);
+      e[i] = __fmaf_rn(-q[k], s, e[i]);
+    }
+    half[hlf] = __fmaf_rn(__fmaf_rn(__fmaf_rn(q[3], 16.0f, q[2]), 16.0f, q[1]), 16.0f, q[0]) + 34952.0f;  // + 0x8888
+  }
+  packed = (__float2uint_rn(half[0]) | (__float2uint_rn(half[1]) << 16)) ^ 0x88888888u;
 }
 __device__ __forceinline__ void dequant8_add(uint32_t packed, float scale, float (&acc)[8]) {
 #pragma unroll
@@ -323,6 +347,12 @@ __device__ __forceinline__ void dequant8_add(uint32_t packed, float scale, float
     const int q = int(packed << (28 - 4 * i)) >> 28;
     acc[i] = __fmaf_rn(float(q), scale, acc[i]);
   }
+}
+
+template <typename T, bool GUARD>
+__device__ __forceinline__ void store8(T* p, int64_t base, int64_t n, const float (&v)[8]) {
+  if constexpr (GUARD) store8_guarded<T>(p, base, n, v);
+  else Vec8<T>::store(p + base, v);
 }
 
 }  // namespace dev

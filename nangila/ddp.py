@@ -41,17 +41,65 @@ from ._C import CompressorType, NangilaConfig, NangilaHook, SyncMode
 
 NANGILA_AVAILABLE = True
 
-try:  # the C++ comm-hook callable lives in the torch glue
-    from ._cuda import NangilaDDPHook as NangilaCppHook  # type: ignore
-    CPP_HOOK_AVAILABLE = True
-except Exception:  # pragma: no cover - glue not built or built without the hook
-    NangilaCppHook = None
-    CPP_HOOK_AVAILABLE = False
-
 try:
     from torch.distributed import GradBucket
 except ImportError:  # pragma: no cover
     GradBucket = Any
+
+try:  # the C++ comm-hook class lives in the torch glue
+    from ._cuda import NangilaDDPHook as _CppHookBase  # type: ignore
+    CPP_HOOK_AVAILABLE = True
+except Exception:  # pragma: no cover - glue not built
+    _CppHookBase = None
+    CPP_HOOK_AVAILABLE = False
+
+
+if CPP_HOOK_AVAILABLE:
+
+    class NangilaCppHook(_CppHookBase):
+        """The C++ DDP hook as a comm-hook callable: ``ddp.register_comm_hook(None, NangilaCppHook(n, warmup))``.
+
+        All per-bucket work (state lookup, stream hand-over, the fused kernel launch, the future) is
+        C++; this subclass only supplies the annotated ``__call__`` DDP insists on and the symmetric
+        memory the first time a bucket is seen. Same constructor as the reference's
+        ``NangilaCppHook(num_layers, warmup_steps)`` (nangila_ddp/src/bindings.cpp:18-60); it handles
+        the prediction-residual compressor on CUDA buckets.
+        """
+
+        def __init__(self, num_layers: int = 1000, warmup_steps: int = 100, process_group: Optional[Any] = None, *,
+                     momentum: float = 0.9, error_feedback: bool = True, stochastic: bool = True, seed: int = 42,
+                     reserve_bytes: Optional[int] = None):
+            super().__init__(int(num_layers), int(warmup_steps))
+            self.configure(momentum=momentum, error_feedback=error_feedback, stochastic=stochastic, seed=seed)
+            self.process_group = process_group
+            self._reserve_bytes = reserve_bytes
+            self._arena = None
+            self._regions: List[Any] = []
+            self.__name__ = "nangila_cpp_hook"
+            self.__qualname__ = "nangila_cpp_hook"
+
+        def _attach(self, device: torch.device) -> None:
+            from .parallel.symm import SymmArena
+
+            group = self.process_group or dist.distributed_c10d._get_default_group()
+            self._arena = SymmArena(group, device)
+            if self._reserve_bytes:
+                self._arena.reserve(int(self._reserve_bytes))
+
+            def allocate(nbytes: int) -> List[int]:
+                region = self._arena.allocate(int(nbytes))
+                self._regions.append(region)  # keeps the mapping alive
+                return [int(p) for p in region.ptrs]
+
+            self.attach(self._arena.rank, self._arena.world, allocate)
+
+        def __call__(self, state: Any, bucket: GradBucket) -> torch.futures.Future[torch.Tensor]:
+            if self._arena is None:
+                self._attach(bucket.buffer().device)
+            return self.run(bucket)
+
+else:  # pragma: no cover
+    NangilaCppHook = None
 
 _LOG = os.environ.get("NANGILA_LOG", "warn").lower()
 
@@ -139,6 +187,8 @@ class NangilaDDPHook:
         self._psgd_engine = None
         self._bucket_calls = 0
         self._force_uncompressed = False
+        self.prefer_cpp = False      # set by register_nangila_hook(prefer_cpp=True)
+        self._cpp = None             # NangilaCppHook once the first CUDA bucket went through it
         self._param_ids: Dict[int, int] = {}
         _log(f"DDP hook: sync_mode={SyncMode(self.sync_mode)!r} compressor={self.compressor_type} "
              f"warmup={self.warmup_steps} world={self.world_size}")
@@ -152,8 +202,27 @@ class NangilaDDPHook:
         except Exception:
             index = self.layer_counter - 1
         if tensor.is_cuda:
+            if self.prefer_cpp and CPP_HOOK_AVAILABLE and self.compressor_type == 0:
+                return self._run_cpp(bucket, tensor)
             return self._run_cuda(bucket, tensor, index)
         return self._run_cpu(bucket, tensor, index)
+
+    def _run_cpp(self, bucket: GradBucket, tensor: torch.Tensor) -> torch.futures.Future:
+        """Prediction-residual compressor through the C++ hook: everything per bucket is native."""
+        cpp = self._cpp
+        if cpp is None:
+            cpp = self._cpp = NangilaCppHook(
+                1, self.warmup_steps, self.process_group, momentum=self.momentum, error_feedback=self.error_feedback,
+                stochastic=self.stochastic,
+                reserve_bytes=(int(self._total_numel * 1.02) + (8 << 20)) if self._total_numel else None)
+            cpp.fast_forward(self.step_count)
+            self.hook.set_gpu_mode(True)
+        cpp.set_paused(self._force_uncompressed or self.hook.is_paused())
+        fut = cpp(None, bucket)
+        self._bucket_calls += 1
+        if self.sync_mode == 1 or (self.sync_mode == 2 and self._bucket_calls % 100 == 0):
+            self._check_device_status()
+        return fut
 
     @property
     def compressing(self) -> bool:
@@ -230,10 +299,13 @@ class NangilaDDPHook:
         return self._stream_future(self._engine.stream, tensor)
 
     def _check_device_status(self) -> None:
-        if self._engine is None:
+        if self._engine is None and self._cpp is None:
             return
         try:
-            self._engine.check_status()
+            if self._cpp is not None:
+                self._cpp.check_status()
+            if self._engine is not None:
+                self._engine.check_status()
         except RuntimeError:
             # leave the hook usable: the next buckets go through the uncompressed mode and re-seed
             # the history on every rank (FORCE_SYNC semantics of the packet protocol)
@@ -342,6 +414,8 @@ class NangilaDDPHook:
         self.hook.step()
         if self._engine is not None:
             self._engine.end_step()
+        if self._cpp is not None:
+            self._cpp.step()
         if self._force_uncompressed:
             self._force_uncompressed = False  # one uncompressed step re-seeded the history everywhere
         if self.step_count % 10 == 0 and self.step_count > self.warmup_steps and _LOG in ("info", "debug"):
@@ -360,6 +434,14 @@ class NangilaDDPHook:
         stats["total_compressed_bytes"] = self.total_compressed_bytes
         if self.total_original_bytes > 0:
             stats["overall_compression_ratio"] = self.total_original_bytes / max(self.total_compressed_bytes, 1)
+        if self._cpp is not None:
+            native = self._cpp.get_stats()
+            stats["kernel_launches"] = native["kernel_launches"]
+            stats["total_original_bytes"] = native["total_original_bytes"]
+            stats["total_compressed_bytes"] = native["total_compressed_bytes"]
+            stats["overall_compression_ratio"] = native["compression_ratio"]
+            stats["pred_gain_per_bucket"] = dict(native["prediction_gain"])
+            stats["cpp_hook"] = True
         if self._engine is not None:
             stats["kernel_launches"] = self._engine.launches
             errs = {}
@@ -378,10 +460,12 @@ class NangilaDDPHook:
         while self.hook.current_step() < to_step:
             self.hook.step()
         self.step_count = max(self.step_count, int(to_step))
+        if self._cpp is not None:
+            self._cpp.fast_forward(int(to_step))
 
     def get_kernel_launches(self) -> int:
         """Number of fused-kernel launches queued by this hook so far on this rank."""
-        n = 0
+        n = self._cpp.get_kernel_launches() if self._cpp is not None else 0
         for eng in (self._engine, self._dgc_engine, self._psgd_engine):
             if eng is not None:
                 n += eng.launches
@@ -389,6 +473,8 @@ class NangilaDDPHook:
 
     @property
     def compression_ratio(self) -> float:
+        if self._cpp is not None:
+            return float(self._cpp.get_stats()["compression_ratio"])
         if self.total_compressed_bytes == 0:
             return 1.0
         return self.total_original_bytes / self.total_compressed_bytes
@@ -396,6 +482,14 @@ class NangilaDDPHook:
     def state_hash(self) -> int:
         """64-bit hash of the predictor state on this rank (host core, or a device reduction of the
         bucket histories when the CUDA path is active)."""
+        if self._cpp is not None and self._cpp.get_stats()["num_buckets"]:
+            from .ops.reductions import state_hash as device_hash
+
+            tensors = []
+            for idx in sorted(self._cpp.get_stats()["prediction_gain"]):
+                st = self._cpp.bucket_state(idx)
+                tensors += [st["curr"], st["prev"]]
+            return device_hash(tensors, seed=self.step_count)
         if self._engine is not None and self._engine.buckets:
             from .ops.reductions import state_hash as device_hash
 
@@ -414,6 +508,8 @@ class NangilaDDPHook:
             dev = "cpu"
             if self._engine is not None:
                 dev = self._engine.device
+            elif self._cpp is not None:
+                dev = self._cpp._arena.device
             t = torch.tensor([h & 0xFFFFFFFF, (h >> 32) & 0xFFFFFFFF], dtype=torch.int64, device=dev)
             gathered = [torch.zeros_like(t) for _ in range(self.world_size)]
             dist.all_gather(gathered, t, group=self.process_group)
@@ -435,6 +531,12 @@ class NangilaDDPHook:
               "core": bytes(self.hook.make_checkpoint().to_bytes())}
         if self._engine is not None:
             sd["predres"] = self._engine.state_dict()
+        if self._cpp is not None:
+            out = {}
+            for idx in self._cpp.get_stats()["prediction_gain"]:
+                st = self._cpp.bucket_state(idx)
+                out[idx] = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
+            sd["predres_cpp"] = out
         return sd
 
     def load_state_dict(self, sd: dict) -> None:
@@ -446,6 +548,17 @@ class NangilaDDPHook:
         self.hook.restore_checkpoint(NangilaCheckpoint.from_bytes(sd["core"]))
         if self._engine is not None and "predres" in sd:
             self._engine.load_state_dict(sd["predres"])
+        if self._cpp is not None:
+            self._cpp.fast_forward(self.step_count)
+            for idx, d in sd.get("predres_cpp", {}).items():
+                try:
+                    st = self._cpp.bucket_state(idx)
+                except RuntimeError:
+                    continue  # bucket not seen yet on this hook
+                if st["n"] == d["n"]:
+                    for k in ("prev", "curr", "ef"):
+                        if k in st and k in d:
+                            st[k].copy_(d[k])
 
     def enable_safe_mode(self, config=None) -> None:
         from ._C import SafeModeConfig
@@ -486,7 +599,8 @@ def register_nangila_hook(
         compressor_type=compressor_type, dgc_sparsity=dgc_sparsity, power_sgd_rank=power_sgd_rank,
         total_numel=total, **extra,
     )
-    hook.prefer_cpp = bool(prefer_cpp)
+    # NANGILA_PREFER_CPP=0/1 overrides the argument (to compare the two hook implementations)
+    hook.prefer_cpp = bool(int(os.environ.get("NANGILA_PREFER_CPP", int(bool(prefer_cpp)))))
     hook._param_ids = {id(p): i for i, p in enumerate(ddp_model.parameters())}
     ddp_model.register_comm_hook(state=None, hook=hook)
     return hook

@@ -247,7 +247,7 @@ class PredResEngine:
                     continue  # not a probe step: the kernel did not look at the history
                 best = min(max(xp / pp, 0.0), 1.0)
                 gain = 0.5 * st.pred_gain + 0.5 * best
-                st.pred_gain = gain if gain >= 0.05 else 0.0  # below 5 % the history loads cost more than they save
+                st.pred_gain = gain if gain >= 0.2 else 0.0  # below 0.2 (< 4 % less residual energy) the history loads cost more than they save
         stream = self.stream if self.stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(stream):
             self._stats_host.copy_(self.stats_table, non_blocking=True)

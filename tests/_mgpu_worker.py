@@ -52,7 +52,7 @@ def check_exchange(dev, rank, world, results):
             results[f"rel_err_{str(dtype)[6:]}_{n}"] = rel
 
 
-def train(dev, rank, world, use_hook, steps, compressor_type=0):
+def train(dev, rank, world, use_hook, steps, compressor_type=0, prefer_cpp=True):
     from torch.nn.parallel import DistributedDataParallel as DDP
 
     from nangila.ddp import register_nangila_hook
@@ -68,7 +68,7 @@ def train(dev, rank, world, use_hook, steps, compressor_type=0):
 
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
-            hook = register_nangila_hook(ddp, warmup_steps=10, sync_mode=1, compressor_type=compressor_type,
+            hook = register_nangila_hook(ddp, warmup_steps=10, sync_mode=1, compressor_type=compressor_type, prefer_cpp=prefer_cpp,
                                          dgc_sparsity=0.99 if compressor_type == 1 else 0.999,
                                          power_sgd_rank=4 if compressor_type == 2 else 1)
     opt = torch.optim.AdamW(ddp.parameters(), lr=3e-3)
@@ -116,6 +116,11 @@ def main():
         results["loss_first"] = base[0]
         results["compression_ratio"] = stats["overall_compression_ratio"]
         results["launches"] = stats["kernel_launches"]
+        results["cpp_hook"] = bool(stats.get("cpp_hook"))
+        py_losses, py_stats = train(dev, rank, world, True, 60, prefer_cpp=False)
+        results["loss_ours_python_hook"] = sum(py_losses[-10:]) / 10
+        assert not py_stats.get("cpp_hook") and py_stats["kernel_launches"] > 0
+        assert abs(results["loss_ours_python_hook"] - results["loss_base"]) < 0.15 * results["loss_base"] + 0.05, results
         assert results["loss_base"] < 0.8 * base[0], "baseline did not learn"
         assert abs(results["loss_ours"] - results["loss_base"]) < 0.15 * results["loss_base"] + 0.05, results
     if what in ("all", "compressors"):

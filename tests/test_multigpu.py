@@ -31,5 +31,15 @@ def test_exchange_matches_nccl(nproc, tmp_path):
 
 
 def test_ddp_loss_parity_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
     res = _run(2, "train", tmp_path, 29741)
     assert res["compression_ratio"] > 1.5 and res["launches"] > 0
+    assert res["cpp_hook"], "the C++ hook did not take the prediction-residual path"
+
+
+def test_dgc_and_powersgd_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, "compressors", tmp_path, 29751)
+    assert res["ratio_dgc"] > 5 and res["ratio_powersgd"] > 2
