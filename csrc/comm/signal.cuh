@@ -28,6 +28,7 @@ enum StatusCode : uint32_t {
   kTimeoutPhase2 = 2,   // owner did not get every rank's contribution
   kTimeoutPhase3 = 3,   // reduced chunk did not arrive from its owner
   kTimeoutGrid = 4,     // grid-wide barrier inside one GPU did not complete
+  kTimeoutBulk = 6,     // a bulk copy into shared memory did not complete
   kBadArgument = 5,
 };
 

@@ -110,6 +110,18 @@ class DdpHook {
     return run_tensor(index, tensor);
   }
 
+  // Create the device state of a bucket without launching anything (checkpoint restore fills it in).
+  void ensure_bucket(py::object bucket) {
+    at::Tensor tensor = bucket.attr("buffer")().cast<at::Tensor>();
+    const int64_t index = bucket.attr("index")().cast<int64_t>();
+    TORCH_CHECK(attached_, "nangila: attach() was not called");
+    TORCH_CHECK(tensor.is_cuda() && tensor.is_contiguous(), "nangila: the C++ hook needs a contiguous CUDA bucket");
+    c10::cuda::CUDAGuard guard(tensor.device());
+    std::lock_guard<std::mutex> lock(mutex_);
+    ensure_device(tensor);
+    bucket_for(index, tensor);
+  }
+
   py::object run_tensor(int64_t index, at::Tensor tensor) {
     TORCH_CHECK(attached_, "nangila: attach() was not called");
     TORCH_CHECK(tensor.is_cuda() && tensor.is_contiguous(), "nangila: the C++ hook needs a contiguous CUDA bucket");
@@ -388,6 +400,7 @@ void register_ddp_hook(py::module_& m) {
            py::arg("stochastic") = true, py::arg("seed") = 42, py::arg("max_buckets") = 512)
       .def("run", &DdpHook::run, py::arg("bucket"))
       .def("run_tensor", &DdpHook::run_tensor, py::arg("index"), py::arg("tensor"))
+      .def("ensure_bucket", &DdpHook::ensure_bucket, py::arg("bucket"))
       .def("step", &DdpHook::step)
       .def("current_step", &DdpHook::current_step)
       .def("is_compression_enabled", &DdpHook::is_compression_enabled)

@@ -28,6 +28,7 @@
 #include <cuda_runtime.h>
 
 #include "nangila_kernels.h"
+#include "ptx_sm100.cuh"
 #include "quant.cuh"
 #include "signal.cuh"
 
@@ -161,6 +162,124 @@ __device__ __forceinline__ void phase1_compressed(const T* __restrict__ grad, co
   }
 }
 
+constexpr int kWarpElems = 32 * kE;  // elements one warp handles per iteration (contiguous)
+constexpr int kRingBytesPerWarp = 6144;
+
+template <typename T, typename S, bool LEAN>
+struct Ring {
+  static constexpr int GB = kWarpElems * int(sizeof(T));
+  static constexpr int SB = kWarpElems * int(sizeof(S));
+  static constexpr int STAGE = GB + SB * (LEAN ? 1 : 3);  // grad, error memory, [prev, curr]
+  static constexpr int D = (kRingBytesPerWarp / STAGE) < 2 ? 2 : (kRingBytesPerWarp / STAGE);
+  static constexpr int BYTES_PER_WARP = D * STAGE;
+};
+constexpr int kMaxDepth = 6;
+
+// Phase 1 for a chunk that lies wholly inside the range, with the inputs streamed through a per-warp
+// ring in shared memory: lane 0 issues bulk copies (cp.async.bulk, completion on an mbarrier) D
+// iterations ahead, so the warp never waits on a global load once the ring is primed and far more
+// bytes are in flight than registers could hold. Each warp owns its ring and its barriers; `kuse`
+// counts the stage uses of this warp since the start of the kernel (stage = kuse % D, parity from
+// kuse / D). Returns false if a copy did not complete in time (the failure has been reported).
+template <typename T, typename S, bool LEAN>
+__device__ __forceinline__ bool phase1_bulk(const T* __restrict__ grad, const S* __restrict__ prev,
+                                            const S* __restrict__ curr, S* __restrict__ ef, uint8_t* dst,
+                                            int64_t tbase, int iters, int C, int tid, float mu, float kappa,
+                                            bool use_history, uint32_t key1, bool stochastic, Stats& st,
+                                            uint8_t* ring, uint64_t* bars, uint32_t& kuse, uint64_t timeout_ns) {
+  using R = Ring<T, S, LEAN>;
+  constexpr int D = R::D;
+  const int lane = tid & 31, warp = tid >> 5;
+  const bool has_ef = ef != nullptr;
+  const bool hist = !LEAN && use_history;
+  const uint32_t bytes = uint32_t(R::GB + (has_ef ? R::SB : 0) + (hist ? 2 * R::SB : 0));
+  auto issue = [&](int it, uint32_t k) {
+    if (lane == 0) {
+      uint8_t* sdst = ring + (k % D) * R::STAGE;
+      uint64_t* bar = bars + (k % D);
+      const int64_t e0 = tbase + int64_t(it) * kElemsPerIter + warp * kWarpElems;
+      sm100::mbar_arrive_expect_tx(bar, bytes);
+      sm100::bulk_load(sdst, grad + e0, R::GB, bar);
+      if (has_ef) sm100::bulk_load(sdst + R::GB, ef + e0, R::SB, bar);
+      if (hist) {
+        sm100::bulk_load(sdst + R::GB + R::SB, prev + e0, R::SB, bar);
+        sm100::bulk_load(sdst + R::GB + 2 * R::SB, curr + e0, R::SB, bar);
+      }
+    }
+  };
+  const uint32_t k0 = kuse;
+  const int primed = iters < D ? iters : D;
+  for (int i = 0; i < primed; ++i) issue(i, k0 + uint32_t(i));
+  int issued = primed;
+  bool ok = true;
+  for (int it = 0; it < iters; ++it) {
+    const uint32_t k = k0 + uint32_t(it);
+    if (!__all_sync(0xffffffffu, sm100::mbar_wait(bars + (k % D), (k / D) & 1u, timeout_ns))) {
+      ok = false;
+      kuse = k;
+      // drain what is still in flight (bounded) so that no copy lands after the CTA has gone
+      for (int j = it + 1; j < issued; ++j) {
+        const uint32_t kj = k0 + uint32_t(j);
+        sm100::mbar_wait(bars + (kj % D), (kj / D) & 1u, timeout_ns);
+      }
+      break;
+    }
+    const uint8_t* sp = ring + (k % D) * R::STAGE;
+    const int64_t base = tbase + int64_t(it) * kElemsPerIter + tid * kE;
+    float g[kE], e[kE], pv[kE], cu[kE];
+    Vec8<T>::load(reinterpret_cast<const T*>(sp) + lane * kE, g);
+    if (has_ef) Vec8<S>::load(reinterpret_cast<const S*>(sp + R::GB) + lane * kE, e);
+    if constexpr (!LEAN) {
+      if (hist) {
+        Vec8<S>::load(reinterpret_cast<const S*>(sp + R::GB + R::SB) + lane * kE, pv);
+        Vec8<S>::load(reinterpret_cast<const S*>(sp + R::GB + 2 * R::SB) + lane * kE, cu);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kE; ++i) pv[i] = cu[i] = 0.0f;
+      }
+    }
+    __syncwarp();  // every lane has read the stage: lane 0 may refill it
+    if (it + D < iters) {
+      issue(it + D, k + uint32_t(D));
+      issued = it + D + 1;
+    }
+    if (has_ef) {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) {
+        g[i] = sanitize(g[i]);
+        e[i] += g[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) e[i] = g[i] = sanitize(g[i]);
+    }
+    if constexpr (!LEAN) {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) {
+        const float pred = __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+        st.g2 = __fmaf_rn(g[i], g[i], st.g2);
+        st.xp = __fmaf_rn(e[i], pred, st.xp);
+        st.pp = __fmaf_rn(pred, pred, st.pp);
+        e[i] = __fmaf_rn(-kappa, pred, e[i]);
+        st.e2 = __fmaf_rn(e[i], e[i], st.e2);
+      }
+    }
+    uint32_t packed, sb;
+    quantize8(e, key1, uint32_t(base >> 1), stochastic, packed, sb);
+    if (has_ef) {
+      Vec8<S>::store(ef + base, e);
+      if constexpr (!LEAN) {
+#pragma unroll
+        for (int i = 0; i < kE; ++i) st.f2 = __fmaf_rn(e[i], e[i], st.f2);
+      }
+    }
+    *packed_ptr(dst, it, tid) = packed;
+    if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+  }
+  if (ok) kuse = k0 + uint32_t(iters);
+  return ok;
+}
+
 constexpr int kWarps = kThreads / 32;
 constexpr int kSlots = 4;  // completion counters in flight per CTA
 
@@ -206,9 +325,14 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   __shared__ int s_count[kSlots];   // warps that have finished the task in this slot
   __shared__ int s_done;            // tasks of this CTA whose flag has been published
   __shared__ float red[5][kWarps];
+  __shared__ __align__(8) uint64_t s_bars[kWarps][kMaxDepth];  // per-warp ring barriers (phase 1)
+  extern __shared__ __align__(128) uint8_t s_ring[];           // kWarps * Ring::BYTES_PER_WARP (compressed modes)
   if (tid < kSlots) s_count[tid] = 0;
   if (tid == 0) s_done = 0;
+  if (COMPRESSED && tid < kWarps * kMaxDepth) sm100::mbar_init(&s_bars[0][0] + tid, 1);
+  if (COMPRESSED) sm100::fence_barrier_init();
   __syncthreads();
+  uint32_t ring_uses = 0;  // stage uses of this warp's ring so far
 
   const float mu = p.mu;
   const float kappa = RS ? 0.0f : p.pred_gain[vr];  // this rank's prediction gain for the bucket, in [0, 1]
@@ -260,10 +384,17 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
       uint8_t* dst = p.region[t.o] + recv1 + (uint64_t(j) * W + me) * slot;
       const bool full = t.base + C <= lim;  // whole chunk inside the range: no per-access bounds checks
       if constexpr (COMPRESSED) {
-        if (full)
-          phase1_compressed<T, S, LEAN, false>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
-                                               use_history, key1, stochastic, acc_stats);
-        else
+        if (full) {
+          using R = Ring<T, S, LEAN>;
+          const int warp = tid >> 5;
+          if (!phase1_bulk<T, S, LEAN>(grad, prev, curr, ef, dst, t.base, iters, C, tid, mu, kappa, use_history, key1,
+                                       stochastic, acc_stats, s_ring + warp * R::BYTES_PER_WARP, &s_bars[warp][0],
+                                       ring_uses, p.timeout_ns)) {
+            if (lane == 0)
+              report_failure(status, kTimeoutBulk, uint32_t(me), 0xffffffffu, epoch, 0u, 1u, uint32_t(c));
+            break;
+          }
+        } else
           phase1_compressed<T, S, LEAN, true>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
                                               use_history, key1, stochastic, acc_stats);
         if (tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
@@ -347,30 +478,46 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
       const float kbar = COMPRESSED ? *reinterpret_cast<const float*>(src + compressed_trailer_off(C)) : 0.0f;
       auto body = [&](auto guard_tag) {
         constexpr bool GUARD = decltype(guard_tag)::value;
-#pragma unroll 2
-        for (int it = 0; it < iters; ++it) {
-          const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
-          if (GUARD && base >= n) continue;
-          float out[kE];
+        constexpr int B = 4;  // iterations whose (small) inputs are loaded before any of them is processed
+        for (int it0 = 0; it0 < iters; it0 += B) {
+          [[maybe_unused]] uint32_t pk[B];
+          [[maybe_unused]] uint16_t sc[B];
           if constexpr (COMPRESSED) {
-            const uint32_t pk = *packed_ptr(src, it, tid);
-            const float sc = bf16_bits_to_float(*scale_ptr(src, C, it, tid));
-            if (kbar != 0.0f) {
-              float pv[kE], cu[kE];
-              load8<S, GUARD>(prev, base, n, pv);
-              load8<S, GUARD>(curr, base, n, cu);
 #pragma unroll
-              for (int i = 0; i < kE; ++i) out[i] = kbar * __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < kE; ++i) out[i] = 0.0f;
+            for (int i = 0; i < B; ++i) {
+              pk[i] = 0u;
+              sc[i] = 0;
+              if (it0 + i < iters) {
+                pk[i] = *packed_ptr(src, it0 + i, tid);
+                sc[i] = *scale_ptr(src, C, it0 + i, tid);
+              }
             }
-            dequant8_add(pk, sc, out);
-          } else {
-            Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
           }
-          store8<T, GUARD>(grad, base, n, out);
-          store8<S, GUARD>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
+#pragma unroll
+          for (int i = 0; i < B; ++i) {
+            const int it = it0 + i;
+            if (it >= iters) break;
+            const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
+            if (GUARD && base >= n) continue;
+            float out[kE];
+            if constexpr (COMPRESSED) {
+              if (kbar != 0.0f) {
+                float pv[kE], cu[kE];
+                load8<S, GUARD>(prev, base, n, pv);
+                load8<S, GUARD>(curr, base, n, cu);
+#pragma unroll
+                for (int q = 0; q < kE; ++q) out[q] = kbar * __fmaf_rn(mu, cu[q] - pv[q], cu[q]);
+              } else {
+#pragma unroll
+                for (int q = 0; q < kE; ++q) out[q] = 0.0f;
+              }
+              dequant8_add(pk[i], bf16_bits_to_float(sc[i]), out);
+            } else {
+              Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
+            }
+            store8<T, GUARD>(grad, base, n, out);
+            store8<S, GUARD>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
+          }
         }
       };
       if (t.base + C <= n) body(std::false_type{});
@@ -417,19 +564,45 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   }
 }
 
+template <typename T, typename S, int MODE>
+cudaError_t launch_mode(const NangilaPredResParams& p, cudaStream_t stream) {
+  constexpr bool LEAN = MODE == 2 || MODE == 3;
+  constexpr int smem = MODE == 0 ? 0 : kWarps * Ring<T, S, LEAN>::BYTES_PER_WARP;
+  static_assert(Ring<T, S, LEAN>::D <= kMaxDepth, "ring depth");
+  const void* fn = reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, MODE>);
+  static bool configured[64] = {};  // per device: the opt-in for more than 48 KB of shared memory
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (smem > 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  int grid_x = p.grid_x;
+  if (p.nvr > 1) {
+    // cooperative launch: every CTA of every emulated rank must be resident at once
+    int per_sm = 0, sms = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem);
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    grid_x = std::max(1, std::min(grid_x, per_sm * sms / p.nvr));
+  }
+  dim3 grid{unsigned(grid_x), unsigned(p.nvr)};
+  dim3 block{unsigned(kThreads)};
+  void* args[] = {const_cast<NangilaPredResParams*>(&p)};
+  if (p.nvr > 1) return cudaLaunchCooperativeKernel(fn, grid, block, args, size_t(smem), stream);
+  return cudaLaunchKernel(fn, grid, block, args, size_t(smem), stream);
+}
+
 template <typename T, typename S>
 cudaError_t launch_ts(const NangilaPredResParams& p, cudaStream_t stream) {
-  dim3 grid(unsigned(p.grid_x), unsigned(p.nvr));
-  dim3 block(kThreads);
-  void* args[] = {const_cast<NangilaPredResParams*>(&p)};
   bool lean = p.mode == 0 && p.measure == 0;
   for (int v = 0; v < p.nvr; ++v) lean = lean && p.pred_gain[v] == 0.0f;
-  const void* fn = p.mode == 0   ? (lean ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 3>)
-                                         : reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 1>))
-                   : p.mode == 1 ? reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 0>)
-                                 : reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, 2>);
-  if (p.nvr > 1) return cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream);
-  return cudaLaunchKernel(fn, grid, block, args, 0, stream);
+  if (p.mode == 0) return lean ? launch_mode<T, S, 3>(p, stream) : launch_mode<T, S, 1>(p, stream);
+  if (p.mode == 1) return launch_mode<T, S, 0>(p, stream);
+  return launch_mode<T, S, 2>(p, stream);
 }
 
 }  // namespace

@@ -188,6 +188,10 @@ class NangilaDDPHook:
         self._bucket_calls = 0
         self._force_uncompressed = False
         self.prefer_cpp = False      # set by register_nangila_hook(prefer_cpp=True)
+        self.recovered_failures = 0  # buckets that fell back to an exact all-reduce after a rejected packet
+        self._exact_until_step = 0   # buckets go through a plain all-reduce before this step (after a resume)
+        self._pending_state: Dict[int, dict] = {}  # restored device state, applied when its bucket appears
+        self._packet_filter = None   # tests: callable(step, layer_id, src_rank, bytes) -> bytes
         self._cpp = None             # NangilaCppHook once the first CUDA bucket went through it
         self._param_ids: Dict[int, int] = {}
         _log(f"DDP hook: sync_mode={SyncMode(self.sync_mode)!r} compressor={self.compressor_type} "
@@ -201,11 +205,34 @@ class NangilaDDPHook:
             index = int(bucket.index())
         except Exception:
             index = self.layer_counter - 1
+        if self.step_count < self._exact_until_step:
+            return self._run_plain_allreduce(tensor)
         if tensor.is_cuda:
             if self.prefer_cpp and CPP_HOOK_AVAILABLE and self.compressor_type == 0:
                 return self._run_cpp(bucket, tensor)
             return self._run_cuda(bucket, tensor, index)
         return self._run_cpu(bucket, tensor, index)
+
+    def _run_plain_allreduce(self, tensor: torch.Tensor) -> torch.futures.Future:
+        """Exact mean through the process group, touching no compressor state. Used for the first step
+        after a resume: a new DDP instance lays its buckets out in construction order for one
+        iteration and only then switches to the gradient-ready order the saved state belongs to."""
+        world = self.world_size
+        nbytes = tensor.numel() * tensor.element_size()
+        self.total_original_bytes += nbytes
+        self.total_compressed_bytes += nbytes
+        work = dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.process_group, async_op=True)
+        return work.get_future().then(lambda f: f.value()[0].div_(world))
+
+    def _apply_pending(self, index: int, target: dict) -> None:
+        """Copy a restored bucket state (history, error memory) into freshly created device state."""
+        saved = self._pending_state.pop(index, None)
+        if saved is None or int(saved.get("n", -1)) != int(target["n"]):
+            return
+        for k in ("prev", "curr", "ef", "ef2"):
+            src, dst = saved.get(k), target.get(k)
+            if isinstance(src, torch.Tensor) and isinstance(dst, torch.Tensor) and src.numel() == dst.numel():
+                dst.copy_(src.to(dst.dtype))
 
     def _run_cpp(self, bucket: GradBucket, tensor: torch.Tensor) -> torch.futures.Future:
         """Prediction-residual compressor through the C++ hook: everything per bucket is native."""
@@ -218,6 +245,13 @@ class NangilaDDPHook:
             cpp.fast_forward(self.step_count)
             self.hook.set_gpu_mode(True)
         cpp.set_paused(self._force_uncompressed or self.hook.is_paused())
+        if self._pending_state:
+            index = int(bucket.index())
+            if index in self._pending_state:
+                if cpp._arena is None:
+                    cpp._attach(tensor.device)
+                cpp.ensure_bucket(bucket)
+                self._apply_pending(index, cpp.bucket_state(index))
         fut = cpp(None, bucket)
         self._bucket_calls += 1
         if self.sync_mode == 1 or (self.sync_mode == 2 and self._bucket_calls % 100 == 0):
@@ -253,6 +287,9 @@ class NangilaDDPHook:
         elif compressing and ctype == 2:
             fut = self._run_cuda_powersgd(bucket, tensor, index)
         else:
+            if index in self._pending_state:
+                bs = engine.bucket_state(index, [tensor])
+                self._apply_pending(index, {"n": bs.n, "prev": bs.prev[0], "curr": bs.curr[0], "ef": bs.ef[0], "ef2": bs.ef2[0]})
             st = engine.reduce(index, [tensor], compressed=compressing and ctype == 0, step=self.step_count)
             nbytes = tensor.numel() * tensor.element_size()
             self.total_original_bytes += nbytes
@@ -360,14 +397,43 @@ class NangilaDDPHook:
         padded[:len(packet)] = torch.frombuffer(bytearray(packet), dtype=torch.uint8)
         gathered = [torch.empty(max_size, dtype=torch.uint8, device=device) for _ in range(world)]
         dist.all_gather(gathered, padded, group=self.process_group)
+        filt = self._packet_filter
         acc = np.zeros(flat.size, dtype=np.float64)
+        failure: Optional[str] = None
+        crc0 = self.hook.crc_failure_count(layer_id)
         for r in range(world):
             data = bytes(gathered[r][:sizes_i[r]].cpu().numpy())
-            rec = self.hook.decompress_gathered(layer_id, data)
-            if rec.shape[0] != flat.size:
-                raise RuntimeError(f"nangila: rank {r} sent {rec.shape[0]} elements for layer {layer_id}, "
-                                   f"expected {flat.size}")
-            acc += rec
+            if filt is not None:  # host-side fault injection (tests): may corrupt, truncate or replace a packet
+                data = filt(self.step_count, layer_id, r, data)
+            try:
+                rec = self.hook.decompress_gathered(layer_id, data)
+                if rec.shape[0] != flat.size:
+                    raise RuntimeError(f"rank {r} sent {rec.shape[0]} elements, expected {flat.size}")
+                if self.hook.crc_failure_count(layer_id) > crc0:
+                    # the core substituted its prediction for the damaged payload; that is not this
+                    # rank's gradient, so the bucket is exchanged again exactly
+                    raise RuntimeError("checksum mismatch")
+                acc += rec
+            except Exception as exc:  # CRC mismatch, truncated packet, step / layer mismatch, size mismatch
+                failure = f"packet of rank {r} for layer {layer_id} rejected: {exc}"
+                break
+        # A packet may be unreadable on some ranks only (a desynchronised replica): agree on the outcome
+        # before choosing the collective that follows.
+        bad = torch.tensor([1 if failure else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX, group=self.process_group)
+        if int(bad.item()):
+            # Recovery (FORCE_SYNC semantics of the packet protocol): this bucket is averaged exactly,
+            # the averaged gradient re-seeds the predictor on every rank, and the next packet of the
+            # layer is sent uncompressed with the FORCE_SYNC flag.
+            self.recovered_failures += 1
+            warnings.warn(f"nangila: {failure or 'a peer rejected a packet'}; exact all-reduce for this bucket "
+                          f"(step {self.step_count})")
+            t = torch.from_numpy(np.ascontiguousarray(flat.reshape(-1), dtype=np.float32)).to(device)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.process_group)
+            averaged = (t / world).cpu().numpy().astype(np.float32)
+            self.hook.trigger_recovery(layer_id)
+            self.hook.update(layer_id, averaged)
+            return averaged
         averaged = (acc / world).astype(np.float32)
         self.hook.update(layer_id, averaged)
         return averaged
@@ -432,6 +498,7 @@ class NangilaDDPHook:
         stats["compression_enabled"] = self.compressing
         stats["total_original_bytes"] = self.total_original_bytes
         stats["total_compressed_bytes"] = self.total_compressed_bytes
+        stats["recovered_failures"] = self.recovered_failures
         if self.total_original_bytes > 0:
             stats["overall_compression_ratio"] = self.total_original_bytes / max(self.total_compressed_bytes, 1)
         if self._cpp is not None:
@@ -536,7 +603,7 @@ class NangilaDDPHook:
             for idx in self._cpp.get_stats()["prediction_gain"]:
                 st = self._cpp.bucket_state(idx)
                 out[idx] = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
-            sd["predres_cpp"] = out
+            sd["predres"] = out
         return sd
 
     def load_state_dict(self, sd: dict) -> None:
@@ -546,19 +613,12 @@ class NangilaDDPHook:
         self.total_original_bytes = int(sd.get("total_original_bytes", 0))
         self.total_compressed_bytes = int(sd.get("total_compressed_bytes", 0))
         self.hook.restore_checkpoint(NangilaCheckpoint.from_bytes(sd["core"]))
-        if self._engine is not None and "predres" in sd:
-            self._engine.load_state_dict(sd["predres"])
+        # Device state is applied lazily, bucket by bucket, once DDP has settled on its bucket layout;
+        # until then (one step) gradients are averaged exactly.
+        self._pending_state = {int(k): v for k, v in (sd.get("predres") or {}).items()}
+        self._exact_until_step = self.step_count + 1
         if self._cpp is not None:
             self._cpp.fast_forward(self.step_count)
-            for idx, d in sd.get("predres_cpp", {}).items():
-                try:
-                    st = self._cpp.bucket_state(idx)
-                except RuntimeError:
-                    continue  # bucket not seen yet on this hook
-                if st["n"] == d["n"]:
-                    for k in ("prev", "curr", "ef"):
-                        if k in st and k in d:
-                            st[k].copy_(d[k])
 
     def enable_safe_mode(self, config=None) -> None:
         from ._C import SafeModeConfig

@@ -27,6 +27,7 @@ STATUS_MESSAGES = {
     3: "timeout in phase 3: a reduced chunk did not arrive from its owner",
     4: "timeout in an intra-GPU grid barrier",
     5: "bad argument",
+    6: "timeout waiting for a bulk copy into shared memory",
 }
 
 

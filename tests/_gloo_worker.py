@@ -24,7 +24,26 @@ def run(rank, world, port, steps, use_hook, out_path, hook_kwargs, calib_steps=0
         import nangila
         from nangila.ddp import register_nangila_hook
 
+        hook_kwargs = dict(hook_kwargs)
+        faults = hook_kwargs.pop("_faults", [])
+        ckpt_at = hook_kwargs.pop("_ckpt_at", None)
+        resume = hook_kwargs.pop("_resume", None)
         hook = register_nangila_hook(ddp, **hook_kwargs)
+        if faults:
+            def packet_filter(step, layer_id, src, data, _faults=faults, _rank=rank):
+                for f in _faults:
+                    if f["step"] == step and f.get("layer", 0) == layer_id and f.get("src", 1) == src \
+                            and f.get("on_rank", _rank) == _rank:
+                        if f["kind"] == "corrupt":
+                            b = bytearray(data)
+                            b[len(b) // 2] ^= 0x5A
+                            return bytes(b)
+                        if f["kind"] == "truncate":
+                            return data[: len(data) // 2]
+                        if f["kind"] == "drop":
+                            return b""
+                return data
+            hook._packet_filter = packet_filter
         if calib_steps:
             sculptor = nangila.Sculptor(hook_kwargs.get("threshold", 0.95))
     opt = torch.optim.SGD(ddp.parameters(), lr=0.01)
@@ -33,7 +52,18 @@ def run(rank, world, port, steps, use_hook, out_path, hook_kwargs, calib_steps=0
     mask_info = None
     xb = torch.randn(32, 784, generator=g)
     yb = torch.randint(0, 10, (32,), generator=g)
-    for step in range(steps):
+    start = 0
+    if use_hook and resume:
+        ck = torch.load(resume + f".rank{rank}", weights_only=False)
+        model.load_state_dict(ck["model"])
+        opt.load_state_dict(ck["opt"])
+        hook.load_state_dict(ck["hook"])
+        g.set_state(ck["gen"])
+        start = ck["step"]
+    for step in range(start, steps):
+        if use_hook and ckpt_at is not None and step == ckpt_at:
+            torch.save({"model": model.state_dict(), "opt": opt.state_dict(), "hook": hook.state_dict(),
+                        "gen": g.get_state(), "step": step}, out_path + f".ckpt.rank{rank}")
         if fixed_batch:
             x, y = xb, yb
         else:

@@ -78,3 +78,36 @@ def test_register_rejects_non_ddp_and_warns():
 
     with pytest.raises(TypeError):
         nangila.register_nangila_hook(torch.nn.Linear(2, 2))
+
+
+@pytest.mark.timeout(600)
+def test_rejected_packets_fall_back_to_exact_allreduce(tmp_path):
+    """Host-side fault injection: a corrupted packet seen by every rank, a truncated packet seen by one
+    rank only, and a dropped packet. Each costs one exact all-reduce of that bucket; training goes on
+    and the replicas stay identical."""
+    faults = [dict(step=14, kind="corrupt", src=1), dict(step=18, kind="truncate", src=0, on_rank=1),
+              dict(step=22, kind="drop", src=1)]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        ours, p0, p1 = _spawn(tmp_path, "faulty.pt", 40, True, dict(warmup_steps=10, _faults=faults), fixed=True)
+    assert ours["stats"]["recovered_failures"] == 3
+    assert torch.equal(p0, p1)
+    assert all(l == l for l in ours["losses"]) and ours["losses"][-1] < ours["losses"][0]
+    assert ours["stats"]["compression_enabled"]
+
+
+@pytest.mark.timeout(600)
+def test_checkpoint_resume_continues_the_run(tmp_path):
+    """Model + optimizer + hook state saved at step 15 of 30; a fresh job resumed from it ends next to
+    the uninterrupted run. The first step after a resume is averaged exactly (a new DDP instance uses
+    its construction-order bucket layout for one iteration, which the saved per-bucket state does not
+    match), so the two trajectories differ by one step's quantization noise, not more."""
+    full, f0, f1 = _spawn(tmp_path, "full.pt", 30, True, dict(warmup_steps=5, _ckpt_at=15))
+    resumed, r0, r1 = _spawn(tmp_path, "resumed.pt", 30, True,
+                             dict(warmup_steps=5, _resume=str(tmp_path / "full.pt.ckpt")))
+    assert torch.equal(f0, f1) and torch.equal(r0, r1)
+    assert (f0 - r0).abs().max().item() < 1e-4
+    assert resumed["stats"]["step"] == 30 and resumed["stats"]["compression_enabled"]
+    assert resumed["losses"][-1] == pytest.approx(full["losses"][-1], abs=1e-3)
+    # 15 compressed steps were resumed: the byte counters keep counting from the saved values
+    assert resumed["stats"]["total_original_bytes"] == full["stats"]["total_original_bytes"]
