@@ -107,8 +107,8 @@ struct Stats {
 // error memory, packed nibbles and scales stored into the owner's slot `dst`.
 // LEAN: the rank's gain is zero and no statistics were asked for, so neither the history nor the
 // five running sums are touched. GUARD: the chunk straddles the end of the range.
-template <typename T, typename S, bool LEAN, bool GUARD>
-__device__ __forceinline__ void phase1_compressed(const T* __restrict__ grad, const S* __restrict__ prev,
+template <typename T, typename S, bool LEAN, bool GUARD, bool SINGLE>
+__device__ __forceinline__ void phase1_compressed(T* __restrict__ grad, S* __restrict__ prev,
                                                   const S* __restrict__ curr, S* __restrict__ ef, uint8_t* dst,
                                                   int64_t tbase, int64_t lim, int iters, int C, int tid, float mu,
                                                   float kappa, bool use_history, uint32_t key1, bool stochastic,
@@ -129,6 +129,7 @@ __device__ __forceinline__ void phase1_compressed(const T* __restrict__ grad, co
 #pragma unroll
       for (int i = 0; i < kE; ++i) e[i] = g[i] = sanitize(g[i]);
     }
+    [[maybe_unused]] float pred[kE];
     if constexpr (!LEAN) {
       float pv[kE], cu[kE];
       if (use_history) {
@@ -140,13 +141,18 @@ __device__ __forceinline__ void phase1_compressed(const T* __restrict__ grad, co
       }
 #pragma unroll
       for (int i = 0; i < kE; ++i) {
-        const float pred = __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
+        pred[i] = __fmaf_rn(mu, cu[i] - pv[i], cu[i]);
         st.g2 = __fmaf_rn(g[i], g[i], st.g2);
-        st.xp = __fmaf_rn(e[i], pred, st.xp);  // <g + ef, g_hat>
-        st.pp = __fmaf_rn(pred, pred, st.pp);  // <g_hat, g_hat>
-        e[i] = __fmaf_rn(-kappa, pred, e[i]);
+        st.xp = __fmaf_rn(e[i], pred[i], st.xp);  // <g + ef, g_hat>
+        st.pp = __fmaf_rn(pred[i], pred[i], st.pp);  // <g_hat, g_hat>
+        e[i] = __fmaf_rn(-kappa, pred[i], e[i]);
         st.e2 = __fmaf_rn(e[i], e[i], st.e2);
       }
+    }
+    [[maybe_unused]] float out[kE];
+    if constexpr (SINGLE) {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) out[i] = e[i];
     }
     uint32_t packed, sb;
     quantize8(e, key1, uint32_t(base >> 1), stochastic, packed, sb);
@@ -157,8 +163,19 @@ __device__ __forceinline__ void phase1_compressed(const T* __restrict__ grad, co
         for (int i = 0; i < kE; ++i) st.f2 = __fmaf_rn(e[i], e[i], st.f2);
       }
     }
-    *packed_ptr(dst, it, tid) = packed;
-    if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+    if constexpr (SINGLE) {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) out[i] -= e[i];
+      if constexpr (!LEAN) {
+#pragma unroll
+        for (int i = 0; i < kE; ++i) out[i] = __fmaf_rn(kappa, pred[i], out[i]);
+      }
+      store8<T, GUARD>(grad, base, lim, out);
+      store8<S, GUARD>(prev, base, lim, out);
+    } else {
+      *packed_ptr(dst, it, tid) = packed;
+      if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+    }
   }
 }
 
@@ -180,9 +197,11 @@ constexpr int kMaxDepth = 6;
 // iterations ahead, so the warp never waits on a global load once the ring is primed and far more
 // bytes are in flight than registers could hold. Each warp owns its ring and its barriers; `kuse`
 // counts the stage uses of this warp since the start of the kernel (stage = kuse % D, parity from
-// kuse / D). Returns false if a copy did not complete in time (the failure has been reported).
-template <typename T, typename S, bool LEAN>
-__device__ __forceinline__ bool phase1_bulk(const T* __restrict__ grad, const S* __restrict__ prev,
+// kuse / D). Returns false if a copy did not complete in time (the caller reports the failure).
+// SINGLE (a world of one rank): nothing is exchanged; the dequantized value is written straight back to
+// the bucket and the history, so the whole step is this one pass.
+template <typename T, typename S, bool LEAN, bool SINGLE>
+__device__ __forceinline__ bool phase1_bulk(T* __restrict__ grad, S* __restrict__ prev,
                                             const S* __restrict__ curr, S* __restrict__ ef, uint8_t* dst,
                                             int64_t tbase, int iters, int C, int tid, float mu, float kappa,
                                             bool use_history, uint32_t key1, bool stochastic, Stats& st,
@@ -264,6 +283,11 @@ __device__ __forceinline__ bool phase1_bulk(const T* __restrict__ grad, const S*
         st.e2 = __fmaf_rn(e[i], e[i], st.e2);
       }
     }
+    float out[kE];
+    if constexpr (SINGLE) {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) out[i] = e[i];
+    }
     uint32_t packed, sb;
     quantize8(e, key1, uint32_t(base >> 1), stochastic, packed, sb);
     if (has_ef) {
@@ -273,8 +297,19 @@ __device__ __forceinline__ bool phase1_bulk(const T* __restrict__ grad, const S*
         for (int i = 0; i < kE; ++i) st.f2 = __fmaf_rn(e[i], e[i], st.f2);
       }
     }
-    *packed_ptr(dst, it, tid) = packed;
-    if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+    if constexpr (SINGLE) {
+#pragma unroll
+      for (int i = 0; i < kE; ++i) out[i] -= e[i];  // q * scale
+      if constexpr (!LEAN) {
+#pragma unroll
+        for (int i = 0; i < kE; ++i) out[i] = __fmaf_rn(kappa, __fmaf_rn(mu, cu[i] - pv[i], cu[i]), out[i]);
+      }
+      Vec8<T>::store(grad + base, out);
+      Vec8<S>::store(prev + base, out);  // becomes g(t) after the caller swaps prev and curr
+    } else {
+      *packed_ptr(dst, it, tid) = packed;
+      if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+    }
   }
   if (ok) kuse = k0 + uint32_t(iters);
   return ok;
@@ -291,13 +326,15 @@ constexpr int kSlots = 4;  // completion counters in flight per CTA
 // kSlots - 1 tasks ahead of the slowest warp of its CTA (the counters are reused round-robin).
 // MODE 0: exact all-reduce; 1: compressed all-reduce; 2: compressed reduce-scatter (phases 1 and 2
 // only: the owner writes the mean of its shard to out_shard, nothing is broadcast, no history);
-// 3: compressed all-reduce, lean phase 1 (this rank's gain is zero and no statistics are wanted).
+// 3: compressed all-reduce, lean phase 1 (this rank's gain is zero and no statistics are wanted);
+// 4 / 5: world of one rank, full / lean: phase 1 alone quantizes, reconstructs and writes the result.
 template <typename T, typename S, int MODE>
 __global__ void __launch_bounds__(kThreads, 4)
 predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   constexpr bool COMPRESSED = MODE != 0;
   constexpr bool RS = MODE == 2;
-  constexpr bool LEAN = MODE == 2 || MODE == 3;
+  constexpr bool LEAN = MODE == 2 || MODE == 3 || MODE == 5;
+  constexpr bool SINGLE = MODE == 4 || MODE == 5;
   const int vr = blockIdx.y;
   const int me = p.rank0 + vr;
   const int W = p.world;
@@ -316,7 +353,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   uint32_t* status = p.status[vr];
   uint8_t* myreg = p.region[me];
   const int T1 = owned_max * W;
-  const int ntasks = T1 + my_owned + (RS ? 0 : NC);
+  const int ntasks = SINGLE ? T1 : T1 + my_owned + (RS ? 0 : NC);
   // Reduce-scatter has no phase 3 to prove that the owner is done reading, so its slots alternate
   // between two sets by launch parity (a rank cannot get two launches ahead of a peer: its phase 2 of
   // the launch in between needs that peer's flags).
@@ -387,7 +424,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
         if (full) {
           using R = Ring<T, S, LEAN>;
           const int warp = tid >> 5;
-          if (!phase1_bulk<T, S, LEAN>(grad, prev, curr, ef, dst, t.base, iters, C, tid, mu, kappa, use_history, key1,
+          if (!phase1_bulk<T, S, LEAN, SINGLE>(grad, prev, curr, ef, dst, t.base, iters, C, tid, mu, kappa, use_history, key1,
                                        stochastic, acc_stats, s_ring + warp * R::BYTES_PER_WARP, &s_bars[warp][0],
                                        ring_uses, p.timeout_ns)) {
             if (lane == 0)
@@ -395,9 +432,9 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
             break;
           }
         } else
-          phase1_compressed<T, S, LEAN, true>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
+          phase1_compressed<T, S, LEAN, true, SINGLE>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
                                               use_history, key1, stochastic, acc_stats);
-        if (tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
+        if (!SINGLE && tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
       } else {
 #pragma unroll 2
         for (int it = 0; it < iters; ++it) {
@@ -531,7 +568,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
       const int sl = local % kSlots;
       if (atomicAdd(&s_count[sl], 1) == kWarps - 1) {
         s_count[sl] = 0;
-        if (t.phase == 1) {
+        if (t.phase == 1 && !SINGLE) {
           __threadfence_system();
           st_release_sys(reinterpret_cast<uint32_t*>(p.region[t.o] + p.flag1_off) + (uint64_t(j) * W + me), epoch);
         } else if (t.phase == 2 && !RS) {
@@ -566,7 +603,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
 
 template <typename T, typename S, int MODE>
 cudaError_t launch_mode(const NangilaPredResParams& p, cudaStream_t stream) {
-  constexpr bool LEAN = MODE == 2 || MODE == 3;
+  constexpr bool LEAN = MODE == 2 || MODE == 3 || MODE == 5;
   constexpr int smem = MODE == 0 ? 0 : kWarps * Ring<T, S, LEAN>::BYTES_PER_WARP;
   static_assert(Ring<T, S, LEAN>::D <= kMaxDepth, "ring depth");
   const void* fn = reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, MODE>);
@@ -600,6 +637,7 @@ template <typename T, typename S>
 cudaError_t launch_ts(const NangilaPredResParams& p, cudaStream_t stream) {
   bool lean = p.mode == 0 && p.measure == 0;
   for (int v = 0; v < p.nvr; ++v) lean = lean && p.pred_gain[v] == 0.0f;
+  if (p.mode == 0 && p.world == 1) return lean ? launch_mode<T, S, 5>(p, stream) : launch_mode<T, S, 4>(p, stream);
   if (p.mode == 0) return lean ? launch_mode<T, S, 3>(p, stream) : launch_mode<T, S, 1>(p, stream);
   if (p.mode == 1) return launch_mode<T, S, 0>(p, stream);
   return launch_mode<T, S, 2>(p, stream);
