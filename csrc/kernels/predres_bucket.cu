@@ -41,8 +41,6 @@ using namespace comm;
 constexpr int kThreads = 256;
 constexpr int kE = kElems8;                       // elements per thread per iteration
 constexpr int kElemsPerIter = kThreads * kE;      // 2048
-constexpr int kPackedPerIter = kElemsPerIter / 2; // bytes of nibbles per iteration
-constexpr int kScalesPerIter = kElemsPerIter / kQuantBlock;
 
 // packed nibbles, then one bf16 scale per 64 elements, then a 16-byte trailer whose first word is the
 // sender's prediction gain (phase 1) or the mean gain of all senders (phase 2)
@@ -51,11 +49,16 @@ __host__ __device__ inline uint64_t compressed_trailer_off(int chunk) {
 }
 __host__ __device__ inline uint64_t compressed_slot_bytes(int chunk) { return compressed_trailer_off(chunk) + 16; }
 
-__device__ __forceinline__ uint32_t* packed_ptr(uint8_t* slot, int it, int tid) {
-  return reinterpret_cast<uint32_t*>(slot + uint64_t(it) * kPackedPerIter) + tid;
+// Slot layout (compressed modes), warp-major so that everything one warp needs from a chunk is
+// contiguous and can be fetched with one bulk copy: packed nibbles [warp][iteration][lane] (4 bytes per
+// lane = 8 elements), then bf16 scales [warp][iteration][4] (one per 64 elements), then the trailer.
+__device__ __forceinline__ uint32_t* packed_ptr(uint8_t* slot, int C, int it, int tid) {
+  const int iters = C / kElemsPerIter;
+  return reinterpret_cast<uint32_t*>(slot) + ((tid >> 5) * iters + it) * 32 + (tid & 31);
 }
 __device__ __forceinline__ uint16_t* scale_ptr(uint8_t* slot, int C, int it, int tid) {
-  return reinterpret_cast<uint16_t*>(slot + uint64_t(C) / 2) + (it * kScalesPerIter + tid / kLanes8);
+  const int iters = C / kElemsPerIter;
+  return reinterpret_cast<uint16_t*>(slot + uint64_t(C) / 2) + ((tid >> 5) * iters + it) * 4 + ((tid & 31) >> 3);
 }
 
 struct TaskInfo {
@@ -173,7 +176,7 @@ __device__ __forceinline__ void phase1_compressed(T* __restrict__ grad, S* __res
       store8<T, GUARD>(grad, base, lim, out);
       store8<S, GUARD>(prev, base, lim, out);
     } else {
-      *packed_ptr(dst, it, tid) = packed;
+      *packed_ptr(dst, C, it, tid) = packed;
       if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
     }
   }
@@ -307,7 +310,7 @@ __device__ __forceinline__ bool phase1_bulk(T* __restrict__ grad, S* __restrict_
       Vec8<T>::store(grad + base, out);
       Vec8<S>::store(prev + base, out);  // becomes g(t) after the caller swaps prev and curr
     } else {
-      *packed_ptr(dst, it, tid) = packed;
+      *packed_ptr(dst, C, it, tid) = packed;
       if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
     }
   }
@@ -363,13 +366,26 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   __shared__ int s_done;            // tasks of this CTA whose flag has been published
   __shared__ float red[5][kWarps];
   __shared__ __align__(8) uint64_t s_bars[kWarps][kMaxDepth];  // per-warp ring barriers (phase 1)
+  __shared__ __align__(8) uint64_t s_bat[kWarps][2];            // per-warp batch barriers (phases 2 and 3)
   extern __shared__ __align__(128) uint8_t s_ring[];           // kWarps * Ring::BYTES_PER_WARP (compressed modes)
   if (tid < kSlots) s_count[tid] = 0;
   if (tid == 0) s_done = 0;
   if (COMPRESSED && tid < kWarps * kMaxDepth) sm100::mbar_init(&s_bars[0][0] + tid, 1);
+  if (COMPRESSED && tid < kWarps * 2) sm100::mbar_init(&s_bat[0][0] + tid, 1);
   if (COMPRESSED) sm100::fence_barrier_init();
   __syncthreads();
   uint32_t ring_uses = 0;  // stage uses of this warp's ring so far
+  // Phases 2 and 3 fetch their (small, strided) inputs in batches of `ib` iterations with bulk copies
+  // into the two halves of the warp's ring: batch b+1 is in flight while batch b is processed.
+  constexpr int kRingBytes = COMPRESSED ? Ring<T, S, LEAN>::BYTES_PER_WARP : 0;
+  constexpr int kHalf = (kRingBytes / 2) & ~127;
+  constexpr int kIterBytes = 32 * 4 + 4 * 2;  // packed words + scales of one warp for one iteration
+  constexpr int kStateBytes = kWarpElems * int(sizeof(S));
+  const int warp = tid >> 5;
+  uint8_t* const wring = s_ring + warp * kRingBytes;
+  uint64_t* const wbat = &s_bat[warp][0];
+  uint32_t bat_parity = 0u;  // bit h: parity of the next phase of this warp's batch barrier h
+  bool failed = false;
 
   const float mu = p.mu;
   const float kappa = RS ? 0.0f : p.pred_gain[vr];  // this rank's prediction gain for the bucket, in [0, 1]
@@ -404,17 +420,27 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           ok = 0;
         }
       }
-      if (ok && t.phase == 2) {
-        for (int r = 0; r < W && ok; ++r)
-          ok = wait_flag(reinterpret_cast<const uint32_t*>(myreg + p.flag1_off) + (uint64_t(j) * W + r), epoch,
-                         p.timeout_ns, status, kTimeoutPhase2, uint32_t(me), uint32_t(r), 2u, uint32_t(c));
-      } else if (ok && t.phase == 3) {
+      if (ok && t.phase == 3) {
         ok = wait_flag(reinterpret_cast<const uint32_t*>(myreg + p.flag2_off) + c, epoch, p.timeout_ns, status,
                        kTimeoutPhase3, uint32_t(me), uint32_t(t.o), 3u, uint32_t(c));
       }
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok && t.phase == 2) {
+      // one lane per source rank: the W flags are polled side by side
+      int mine = 1;
+      for (int r = lane; r < W; r += 32)
+        mine = mine && wait_flag(reinterpret_cast<const uint32_t*>(myreg + p.flag1_off) + (uint64_t(j) * W + r), epoch,
+                                 p.timeout_ns, status, kTimeoutPhase2, uint32_t(me), uint32_t(r), 2u, uint32_t(c));
+      ok = __all_sync(0xffffffffu, mine);
+    }
     if (!ok) break;
+    if (COMPRESSED && t.phase != 1) {
+      // the flags were acquired through the generic proxy; the bulk copies below read through the
+      // async proxy
+      __syncwarp();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+    }
 
     if (t.phase == 1) {
       // ---------------- phase 1: quantize own residual, push to the chunk's owner -------------------
@@ -459,32 +485,14 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
         *reinterpret_cast<float*>(p.region[tid] + p.recv2_off + uint64_t(c) * slot + compressed_trailer_off(C)) =
             kbar * inv_w;
       }
-#pragma unroll 2
-      for (int it = 0; it < iters; ++it) {
-        float acc[kE];
-#pragma unroll
-        for (int i = 0; i < kE; ++i) acc[i] = 0.0f;
-        if constexpr (COMPRESSED) {
-#pragma unroll 4
-          for (int r = 0; r < W; ++r) {
-            uint8_t* src = src0 + uint64_t(r) * slot;
-            dequant8_add(*packed_ptr(src, it, tid), bf16_bits_to_float(*scale_ptr(src, C, it, tid)), acc);
-          }
-        } else {
-#pragma unroll 4
-          for (int r = 0; r < W; ++r) {
-            float v[kE];
-            Vec8<T>::load(reinterpret_cast<const T*>(src0 + uint64_t(r) * slot) + int64_t(it) * kElemsPerIter + tid * kE, v);
-#pragma unroll
-            for (int i = 0; i < kE; ++i) acc[i] += v[i];
-          }
-        }
+      // what happens to the sum of one iteration (8 elements of this lane)
+      auto finish = [&](int it, float (&acc)[kE]) {
 #pragma unroll
         for (int i = 0; i < kE; ++i) acc[i] *= RS ? p.out_scale : inv_w;
         if constexpr (RS) {
           // reduce-scatter: the mean of this rank's shard is the result; nothing is broadcast
-          const int64_t local = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
-          store8_guarded<T>(static_cast<T*>(p.out_shard[vr]), local, shard, acc);
+          const int64_t local_i = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
+          store8_guarded<T>(static_cast<T*>(p.out_shard[vr]), local_i, shard, acc);
         } else if constexpr (COMPRESSED) {
           const int64_t obase = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
           if (ef2 != nullptr) {
@@ -499,7 +507,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           if (ef2 != nullptr) Vec8<S>::store(ef2 + obase, acc);
           for (int r = 0; r < W; ++r) {
             uint8_t* dst = p.region[(me + 1 + r) % W] + p.recv2_off + uint64_t(c) * slot;
-            *packed_ptr(dst, it, tid) = packed;
+            *packed_ptr(dst, C, it, tid) = packed;
             if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
           }
         } else {
@@ -508,57 +516,176 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
             Vec8<T>::store(reinterpret_cast<T*>(dst) + int64_t(it) * kElemsPerIter + tid * kE, acc);
           }
         }
+      };
+      bool batched = false;
+      if constexpr (COMPRESSED) {
+        const int ib = min(iters, kHalf / (W * kIterBytes)) & ~1;
+        if ((iters & 1) == 0 && ib >= 2) {
+          batched = true;
+          const int nb = (iters + ib - 1) / ib;
+          auto issue = [&](int b) {
+            if (lane == 0) {
+              const int h = b & 1, it0 = b * ib, m = min(ib, iters - it0);
+              uint8_t* buf = wring + h * kHalf;
+              sm100::mbar_arrive_expect_tx(wbat + h, uint32_t(W * m * kIterBytes));
+              for (int r = 0; r < W; ++r) {
+                uint8_t* src = src0 + uint64_t(r) * slot;
+                sm100::bulk_load(buf + r * ib * 128, packed_ptr(src, C, it0, warp * 32), uint32_t(m * 128), wbat + h);
+                sm100::bulk_load(buf + W * ib * 128 + r * ib * 8, scale_ptr(src, C, it0, warp * 32), uint32_t(m * 8),
+                                 wbat + h);
+              }
+            }
+          };
+          issue(0);
+          for (int b = 0; b < nb; ++b) {
+            if (b + 1 < nb) issue(b + 1);
+            const int h = b & 1, it0 = b * ib, m = min(ib, iters - it0);
+            if (!__all_sync(0xffffffffu, sm100::mbar_wait(wbat + h, (bat_parity >> h) & 1u, p.timeout_ns))) {
+              if (b + 1 < nb) sm100::mbar_wait(wbat + (h ^ 1), (bat_parity >> (h ^ 1)) & 1u, p.timeout_ns);
+              failed = true;
+              break;
+            }
+            bat_parity ^= 1u << h;
+            const uint8_t* buf = wring + h * kHalf;
+            for (int i = 0; i < m; ++i) {
+              float acc[kE];
+#pragma unroll
+              for (int q = 0; q < kE; ++q) acc[q] = 0.0f;
+#pragma unroll 4
+              for (int r = 0; r < W; ++r) {
+                const uint32_t pk = reinterpret_cast<const uint32_t*>(buf + r * ib * 128)[i * 32 + lane];
+                const uint16_t sc = reinterpret_cast<const uint16_t*>(buf + W * ib * 128 + r * ib * 8)[i * 4 + (lane >> 3)];
+                dequant8_add(pk, bf16_bits_to_float(sc), acc);
+              }
+              finish(it0 + i, acc);
+            }
+            __syncwarp();  // the half may be refilled by the issue two batches later
+          }
+        }
+      }
+      if (!batched) {
+#pragma unroll 2
+        for (int it = 0; it < iters; ++it) {
+          float acc[kE];
+#pragma unroll
+          for (int i = 0; i < kE; ++i) acc[i] = 0.0f;
+          if constexpr (COMPRESSED) {
+#pragma unroll 4
+            for (int r = 0; r < W; ++r) {
+              uint8_t* src = src0 + uint64_t(r) * slot;
+              dequant8_add(*packed_ptr(src, C, it, tid), bf16_bits_to_float(*scale_ptr(src, C, it, tid)), acc);
+            }
+          } else {
+#pragma unroll 4
+            for (int r = 0; r < W; ++r) {
+              float v[kE];
+              Vec8<T>::load(reinterpret_cast<const T*>(src0 + uint64_t(r) * slot) + int64_t(it) * kElemsPerIter + tid * kE, v);
+#pragma unroll
+              for (int i = 0; i < kE; ++i) acc[i] += v[i];
+            }
+          }
+          finish(it, acc);
+        }
       }
     } else if (t.phase == 3) {
       // ---------------- phase 3: reconstruct, write bucket and history -------------------------------
       uint8_t* src = myreg + p.recv2_off + uint64_t(c) * slot;
       const float kbar = COMPRESSED ? *reinterpret_cast<const float*>(src + compressed_trailer_off(C)) : 0.0f;
-      auto body = [&](auto guard_tag) {
+      // one iteration of this lane once its packed word and scale are known
+      auto emit = [&](auto guard_tag, int it, uint32_t pk, uint16_t sc, const uint8_t* hist_smem) {
         constexpr bool GUARD = decltype(guard_tag)::value;
-        constexpr int B = 4;  // iterations whose (small) inputs are loaded before any of them is processed
-        for (int it0 = 0; it0 < iters; it0 += B) {
-          [[maybe_unused]] uint32_t pk[B];
-          [[maybe_unused]] uint16_t sc[B];
-          if constexpr (COMPRESSED) {
-#pragma unroll
-            for (int i = 0; i < B; ++i) {
-              pk[i] = 0u;
-              sc[i] = 0;
-              if (it0 + i < iters) {
-                pk[i] = *packed_ptr(src, it0 + i, tid);
-                sc[i] = *scale_ptr(src, C, it0 + i, tid);
-              }
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < B; ++i) {
-            const int it = it0 + i;
-            if (it >= iters) break;
-            const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
-            if (GUARD && base >= n) continue;
-            float out[kE];
-            if constexpr (COMPRESSED) {
-              if (kbar != 0.0f) {
-                float pv[kE], cu[kE];
-                load8<S, GUARD>(prev, base, n, pv);
-                load8<S, GUARD>(curr, base, n, cu);
-#pragma unroll
-                for (int q = 0; q < kE; ++q) out[q] = kbar * __fmaf_rn(mu, cu[q] - pv[q], cu[q]);
-              } else {
-#pragma unroll
-                for (int q = 0; q < kE; ++q) out[q] = 0.0f;
-              }
-              dequant8_add(pk[i], bf16_bits_to_float(sc[i]), out);
+        const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
+        if (GUARD && base >= n) return;
+        float out[kE];
+        if constexpr (COMPRESSED) {
+          if (kbar != 0.0f) {
+            float pv[kE], cu[kE];
+            if (hist_smem != nullptr) {
+              Vec8<S>::load(reinterpret_cast<const S*>(hist_smem) + lane * kE, pv);
+              Vec8<S>::load(reinterpret_cast<const S*>(hist_smem + kStateBytes) + lane * kE, cu);
             } else {
-              Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
+              load8<S, GUARD>(prev, base, n, pv);
+              load8<S, GUARD>(curr, base, n, cu);
             }
-            store8<T, GUARD>(grad, base, n, out);
-            store8<S, GUARD>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
+#pragma unroll
+            for (int q = 0; q < kE; ++q) out[q] = kbar * __fmaf_rn(mu, cu[q] - pv[q], cu[q]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < kE; ++q) out[q] = 0.0f;
+          }
+          dequant8_add(pk, bf16_bits_to_float(sc), out);
+        } else {
+          Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
+        }
+        store8<T, GUARD>(grad, base, n, out);
+        store8<S, GUARD>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
+      };
+      const bool whole = t.base + C <= n;
+      bool batched = false;
+      if constexpr (COMPRESSED) {
+        // the history rides along only for whole chunks (a bulk copy may not run past the bucket's end)
+        const bool hist = kbar != 0.0f && whole;
+        const int per_it = kIterBytes + (hist ? 2 * kStateBytes : 0);
+        const int ib = min(iters, kHalf / per_it) & ~1;
+        if ((iters & 1) == 0 && ib >= 2) {
+          batched = true;
+          const int nb = (iters + ib - 1) / ib;
+          auto issue = [&](int b) {
+            if (lane == 0) {
+              const int h = b & 1, it0 = b * ib, m = min(ib, iters - it0);
+              uint8_t* buf = wring + h * kHalf;
+              sm100::mbar_arrive_expect_tx(wbat + h, uint32_t(m * per_it));
+              sm100::bulk_load(buf, packed_ptr(src, C, it0, warp * 32), uint32_t(m * 128), wbat + h);
+              sm100::bulk_load(buf + ib * 128, scale_ptr(src, C, it0, warp * 32), uint32_t(m * 8), wbat + h);
+              if (hist) {
+                for (int i = 0; i < m; ++i) {
+                  const int64_t e0 = t.base + int64_t(it0 + i) * kElemsPerIter + warp * kWarpElems;
+                  uint8_t* hb = buf + ib * kIterBytes + i * 2 * kStateBytes;
+                  sm100::bulk_load(hb, prev + e0, uint32_t(kStateBytes), wbat + h);
+                  sm100::bulk_load(hb + kStateBytes, curr + e0, uint32_t(kStateBytes), wbat + h);
+                }
+              }
+            }
+          };
+          issue(0);
+          for (int b = 0; b < nb; ++b) {
+            if (b + 1 < nb) issue(b + 1);
+            const int h = b & 1, it0 = b * ib, m = min(ib, iters - it0);
+            if (!__all_sync(0xffffffffu, sm100::mbar_wait(wbat + h, (bat_parity >> h) & 1u, p.timeout_ns))) {
+              if (b + 1 < nb) sm100::mbar_wait(wbat + (h ^ 1), (bat_parity >> (h ^ 1)) & 1u, p.timeout_ns);
+              failed = true;
+              break;
+            }
+            bat_parity ^= 1u << h;
+            const uint8_t* buf = wring + h * kHalf;
+            for (int i = 0; i < m; ++i) {
+              const uint32_t pk = reinterpret_cast<const uint32_t*>(buf)[i * 32 + lane];
+              const uint16_t sc = reinterpret_cast<const uint16_t*>(buf + ib * 128)[i * 4 + (lane >> 3)];
+              const uint8_t* hs = hist ? buf + ib * kIterBytes + i * 2 * kStateBytes : nullptr;
+              if (whole) emit(std::false_type{}, it0 + i, pk, sc, hs);
+              else emit(std::true_type{}, it0 + i, pk, sc, hs);
+            }
+            __syncwarp();
           }
         }
-      };
-      if (t.base + C <= n) body(std::false_type{});
-      else body(std::true_type{});
+      }
+      if (!batched) {
+        for (int it = 0; it < iters; ++it) {
+          uint32_t pk = 0u;
+          uint16_t sc = 0;
+          if constexpr (COMPRESSED) {
+            pk = *packed_ptr(src, C, it, tid);
+            sc = *scale_ptr(src, C, it, tid);
+          }
+          if (whole) emit(std::false_type{}, it, pk, sc, nullptr);
+          else emit(std::true_type{}, it, pk, sc, nullptr);
+        }
+      }
+    }
+    if (failed) {
+      if (lane == 0)
+        report_failure(status, kTimeoutBulk, uint32_t(me), 0xffffffffu, epoch, 0u, uint32_t(t.phase), uint32_t(c));
+      break;
     }
 
     // ---- exit (per warp): count this warp in; the last warp of the CTA publishes the task ----
