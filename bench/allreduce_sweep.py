@@ -66,6 +66,9 @@ def main() -> int:
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--gain", type=float, default=1.0,
                     help="prediction gain of the compressed mode (0 = the history is neither read nor probed)")
+    ap.add_argument("--loopback", type=int, default=0,
+                    help="emulate this many ranks on ONE GPU (one cooperative launch); for profiling the multi-rank "
+                         "phases under a single-process profiler")
     ap.add_argument("--out", default="")
     ap.add_argument("--only", default="", help="comma list of: nccl,exact,compressed")
     args = ap.parse_args()
@@ -84,11 +87,17 @@ def main() -> int:
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
 
     from nangila.parallel.predres_engine import PredResEngine
-    from nangila.parallel.symm import SymmArena
+    from nangila.parallel.symm import LoopbackArena, SymmArena
 
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     esize = 2 if dtype == torch.bfloat16 else 4
-    arena = SymmArena(None, dev, segment_bytes=256 << 20)
+    nvr = 1
+    if args.loopback > 1:
+        assert world == 1, "--loopback runs in a single process"
+        arena = LoopbackArena(args.loopback, dev)
+        nvr = world = args.loopback
+    else:
+        arena = SymmArena(None, dev, segment_bytes=256 << 20)
     eng = PredResEngine(arena, dev, use_side_stream=False, adaptive_gain=False, ctas=args.ctas or None)
     eng.fixed_gain = args.gain
     if args.gain == 0.0:
@@ -102,11 +111,12 @@ def main() -> int:
         n = nbytes // esize
         pool = max(2, min(8, int((300 << 20) // max(nbytes, 1)) + 1))  # rotate through > 2x L2
         iters = args.iters or (50 if nbytes <= (16 << 20) else 20 if nbytes <= (256 << 20) else 8)
-        bufs = [(torch.randn(n, device=dev) * 1e-3).to(dtype) for _ in range(pool)]
-        row = {"mb": mb, "bytes": nbytes, "world": world, "dtype": args.dtype, "pool": pool, "iters": iters, "gain": args.gain}
+        bufs = [[(torch.randn(n, device=dev) * 1e-3).to(dtype) for _ in range(nvr)] for _ in range(pool)]
+        row = {"mb": mb, "bytes": nbytes, "world": world, "dtype": args.dtype, "pool": pool, "iters": iters, "gain": args.gain,
+               "loopback_ranks_on_one_gpu": nvr if nvr > 1 else None}
         scale = 2.0 * (world - 1) / world if world > 1 else 1.0
-        if "nccl" in which and world > 1:
-            t = time_ms(lambda i: dist.all_reduce(bufs[i % pool]), iters)
+        if "nccl" in which and world > 1 and nvr == 1:
+            t = time_ms(lambda i: dist.all_reduce(bufs[i % pool][0]), iters)
             row["nccl_ms"] = t
             row["nccl_algbw_gbs"] = nbytes / t / 1e6
             row["nccl_busbw_gbs"] = nbytes * scale / t / 1e6
@@ -117,9 +127,9 @@ def main() -> int:
             # one bucket state per pool entry so that state traffic is not L2-resident either
             base = 1000 * int(mb * 16) + (500 if comp else 0)
             for j in range(pool):  # build history / allocate outside the timed region
-                eng.reduce(base + j, [bufs[j]], compressed=False)
+                eng.reduce(base + j, bufs[j], compressed=False)
             eng.check_status()
-            t = time_ms(lambda i: eng.reduce(base + i % pool, [bufs[i % pool]], compressed=comp, step=i), iters)
+            t = time_ms(lambda i: eng.reduce(base + i % pool, bufs[i % pool], compressed=comp, step=i), iters)
             eng.check_status()
             st = eng.buckets[base]
             wire = eng.wire_bytes(st, comp)

@@ -81,6 +81,7 @@ class DdpHook {
     probe_every_ = std::max<int64_t>(1, int64_t(env_double("NANGILA_PROBE_EVERY", 8)));
     chunk_override_ = int32_t(env_double("NANGILA_CHUNK", 0));
     ctas_ = int32_t(env_double("NANGILA_COMM_CTAS", 0));
+    gather_max_world_ = std::min<int32_t>(NANGILA_GATHER_MAX_WORLD, int32_t(env_double("NANGILA_GATHER_MAX_WORLD", NANGILA_GATHER_MAX_WORLD)));
   }
 
   // `allocate(bytes)` returns the addresses (one per rank, as ints) of a fresh zero-initialised
@@ -153,6 +154,8 @@ class DdpHook {
     p.mode = compressed ? 0 : 1;
     p.stochastic = stochastic_ ? 1 : 0;
     p.measure = (b.calls % uint64_t(probe_every_)) == 0 ? 1 : 0;
+    p.gather = (compressed && world_ >= 2 && world_ <= gather_max_world_) ? 1 : 0;
+    p.uniform_gain = 1;  // the statistics are summed over the group before the controller reads them
     p.epoch = b.epoch;
     p.seed = seed_;
     p.step = uint32_t(step_);
@@ -273,6 +276,11 @@ class DdpHook {
     return d;
   }
   int64_t launches() const { return launches_; }
+  // The device table of per-bucket statistics and the exchange stream, so that the caller can sum the
+  // table over the process group (on that stream) before step() copies it to the host. Every rank then
+  // derives the same prediction gains.
+  py::object stats_tensor() const { return stats_dev_.defined() ? py::cast(stats_dev_) : py::none(); }
+  int64_t stream_ptr() const { return stream_ ? int64_t(reinterpret_cast<intptr_t>(stream_->stream())) : 0; }
   static std::string version() { return "0.1.0"; }
 
   // History / error-feedback tensors of a bucket, for checkpointing and tests.
@@ -307,10 +315,12 @@ class DdpHook {
     Bucket b;
     b.n = t.numel();
     b.grad_dtype = code;
-    int32_t c = 16384;
+    // the power of two at or above n / 1024 in [4096, 131072], at least 4 chunks per rank
+    int32_t c = 4096;
     if (chunk_override_ > 0) {
       c = chunk_override_;
     } else {
+      while (c < 131072 && int64_t(c) * 1024 < b.n) c *= 2;
       while (c > 4096 && (b.n + c - 1) / c < 4 * int64_t(world_)) c /= 2;
     }
     b.chunk = c;
@@ -335,7 +345,7 @@ class DdpHook {
 
   int32_t grid_for(const Bucket& b) const {
     const int64_t owned = (b.nchunks + world_ - 1) / world_;
-    const int64_t want = owned * world_;
+    const int64_t want = owned * world_;  // = chunks of the bucket, rounded up to whole rounds
     const int64_t cap = ctas_ > 0 ? ctas_ : kSmCount * 4;
     return int32_t(std::max<int64_t>(1, std::min(want, cap)));
   }
@@ -376,6 +386,7 @@ class DdpHook {
   int64_t probe_every_;
   int32_t chunk_override_;
   int32_t ctas_;
+  int32_t gather_max_world_;
   std::mutex mutex_;
   std::map<int64_t, Bucket> buckets_;
   int next_slot_ = 0;
@@ -412,6 +423,8 @@ void register_ddp_hook(py::module_& m) {
       .def("check_status", &DdpHook::check_status)
       .def("get_stats", &DdpHook::get_stats)
       .def("get_kernel_launches", &DdpHook::launches)
+      .def("stats_tensor", &DdpHook::stats_tensor)
+      .def("stream_ptr", &DdpHook::stream_ptr)
       .def("bucket_state", &DdpHook::bucket_state)
       .def_static("version", &DdpHook::version);
 }

@@ -11,6 +11,7 @@ extern "C" {
 #endif
 
 #define NANGILA_MAX_RANKS 16   /* ranks in one exchange group */
+#define NANGILA_GATHER_MAX_WORLD 4
 #define NANGILA_MAX_VRANKS 8   /* ranks emulated inside ONE launch (single-GPU loopback world) */
 
 enum NangilaDType { NANGILA_F32 = 0, NANGILA_F16 = 1, NANGILA_BF16 = 2 };
@@ -46,6 +47,12 @@ typedef struct NangilaPredResParams {
   int32_t mode;                        /* 0 compressed all-reduce, 1 exact all-reduce, 2 compressed reduce-scatter */
   int32_t stochastic;                  /* 0: round to nearest (tests), 1: stochastic rounding */
   int32_t measure;                     /* 1: accumulate <g+ef,g_hat>, <g_hat,g_hat> even when the gain is 0 */
+  int32_t gather;                      /* 1 (compressed all-reduce, 2 <= world <= NANGILA_GATHER_MAX_WORLD): every rank
+                                          receives every rank's packed chunks and sums them itself: one
+                                          quantization and two phases instead of two and three */
+  int32_t uniform_gain;                /* 1: every rank of the group passes the same pred_gain (the host
+                                          keeps the controllers in step), so phase 3 need not read the
+                                          owner's mean from the chunk trailer before fetching the history */
   uint32_t epoch;                      /* strictly increasing per launch on this bucket, never 0 */
   uint32_t seed, step, bucket_id;
   float mu;

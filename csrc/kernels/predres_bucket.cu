@@ -71,10 +71,20 @@ struct TaskInfo {
 };
 // All-reduce modes: chunk c covers [c C, (c+1) C) and belongs to rank c % W.
 // Reduce-scatter mode: the bucket is W equal shards; rank o owns shard o, cut into `cps` chunks.
-template <bool RS>
+// Gather mode: every rank pushes each of its packed chunks to all ranks and later sums all W
+// contributions of every chunk itself: tasks are NC quantize tasks followed by NC sum tasks.
+template <bool RS, bool GATHER>
 __device__ __forceinline__ TaskInfo decode_task(int task, int me, int W, int NC, int T1, int my_owned, int C,
                                                 int64_t n, int cps, int64_t shard) {
   TaskInfo t;
+  if (GATHER) {
+    t.phase = task < NC ? 1 : 2;
+    t.c = t.j = task < NC ? task : task - NC;
+    t.o = me;
+    t.base = int64_t(t.c) * C;
+    t.limit = n;
+    return t;
+  }
   if (task < T1) {
     const int k = task / W, d = task % W;
     t.o = (me + 1 + d) % W;  // remote owners first, own chunk last in each round
@@ -115,7 +125,7 @@ __device__ __forceinline__ void phase1_compressed(T* __restrict__ grad, S* __res
                                                   const S* __restrict__ curr, S* __restrict__ ef, uint8_t* dst,
                                                   int64_t tbase, int64_t lim, int iters, int C, int tid, float mu,
                                                   float kappa, bool use_history, uint32_t key1, bool stochastic,
-                                                  Stats& st) {
+                                                  Stats& st, int ndst, uint8_t* const* regions, uint64_t dst_off) {
 #pragma unroll 2
   for (int it = 0; it < iters; ++it) {
     const int64_t base = tbase + int64_t(it) * kElemsPerIter + tid * kE;
@@ -175,9 +185,16 @@ __device__ __forceinline__ void phase1_compressed(T* __restrict__ grad, S* __res
       }
       store8<T, GUARD>(grad, base, lim, out);
       store8<S, GUARD>(prev, base, lim, out);
-    } else {
+    } else if (ndst == 1) {
       *packed_ptr(dst, C, it, tid) = packed;
       if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+    } else {
+      // gather mode: the same words go to this chunk's slot [source = me] on every rank
+      for (int r = 0; r < ndst; ++r) {
+        uint8_t* d = regions[r] + dst_off;
+        *packed_ptr(d, C, it, tid) = packed;
+        if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(d, C, it, tid) = uint16_t(sb);
+      }
     }
   }
 }
@@ -208,7 +225,8 @@ __device__ __forceinline__ bool phase1_bulk(T* __restrict__ grad, S* __restrict_
                                             const S* __restrict__ curr, S* __restrict__ ef, uint8_t* dst,
                                             int64_t tbase, int iters, int C, int tid, float mu, float kappa,
                                             bool use_history, uint32_t key1, bool stochastic, Stats& st,
-                                            uint8_t* ring, uint64_t* bars, uint32_t& kuse, uint64_t timeout_ns) {
+                                            uint8_t* ring, uint64_t* bars, uint32_t& kuse, uint64_t timeout_ns,
+                                            int ndst, uint8_t* const* regions, uint64_t dst_off) {
   using R = Ring<T, S, LEAN>;
   constexpr int D = R::D;
   const int lane = tid & 31, warp = tid >> 5;
@@ -309,9 +327,16 @@ __device__ __forceinline__ bool phase1_bulk(T* __restrict__ grad, S* __restrict_
       }
       Vec8<T>::store(grad + base, out);
       Vec8<S>::store(prev + base, out);  // becomes g(t) after the caller swaps prev and curr
-    } else {
+    } else if (ndst == 1) {
       *packed_ptr(dst, C, it, tid) = packed;
       if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+    } else {
+      // gather mode: the same words go to this chunk's slot [source = me] on every rank
+      for (int r = 0; r < ndst; ++r) {
+        uint8_t* d = regions[r] + dst_off;
+        *packed_ptr(d, C, it, tid) = packed;
+        if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(d, C, it, tid) = uint16_t(sb);
+      }
     }
   }
   if (ok) kuse = k0 + uint32_t(iters);
@@ -330,14 +355,17 @@ constexpr int kSlots = 4;  // completion counters in flight per CTA
 // MODE 0: exact all-reduce; 1: compressed all-reduce; 2: compressed reduce-scatter (phases 1 and 2
 // only: the owner writes the mean of its shard to out_shard, nothing is broadcast, no history);
 // 3: compressed all-reduce, lean phase 1 (this rank's gain is zero and no statistics are wanted);
-// 4 / 5: world of one rank, full / lean: phase 1 alone quantizes, reconstructs and writes the result.
+// 4 / 5: world of one rank, full / lean: phase 1 alone quantizes, reconstructs and writes the result;
+// 6 / 7: gather mode, full / lean (small worlds): phase 1 pushes the packed chunk to every rank, and
+// every rank sums the W contributions of every chunk itself: one quantization, two phases.
 template <typename T, typename S, int MODE>
 __global__ void __launch_bounds__(kThreads, 4)
 predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   constexpr bool COMPRESSED = MODE != 0;
   constexpr bool RS = MODE == 2;
-  constexpr bool LEAN = MODE == 2 || MODE == 3 || MODE == 5;
+  constexpr bool LEAN = MODE == 2 || MODE == 3 || MODE == 5 || MODE == 7;
   constexpr bool SINGLE = MODE == 4 || MODE == 5;
+  constexpr bool GATHER = MODE == 6 || MODE == 7;
   const int vr = blockIdx.y;
   const int me = p.rank0 + vr;
   const int W = p.world;
@@ -356,11 +384,14 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   uint32_t* status = p.status[vr];
   uint8_t* myreg = p.region[me];
   const int T1 = owned_max * W;
-  const int ntasks = SINGLE ? T1 : T1 + my_owned + (RS ? 0 : NC);
+  const int ntasks = GATHER ? 2 * NC : SINGLE ? T1 : T1 + my_owned + (RS ? 0 : NC);
   // Reduce-scatter has no phase 3 to prove that the owner is done reading, so its slots alternate
   // between two sets by launch parity (a rank cannot get two launches ahead of a peer: its phase 2 of
   // the launch in between needs that peer's flags).
-  const uint64_t recv1 = p.recv1_off + (RS ? uint64_t(epoch & 1u) * uint64_t(cps) * W * slot : 0);
+  // (gather mode alternates for the same reason: a rank may start the next launch while a peer still sums)
+  const uint64_t recv1 = p.recv1_off + (RS       ? uint64_t(epoch & 1u) * uint64_t(cps) * W * slot
+                                        : GATHER ? uint64_t(epoch & 1u) * uint64_t(NC) * W * slot
+                                                 : 0);
 
   __shared__ int s_count[kSlots];   // warps that have finished the task in this slot
   __shared__ int s_done;            // tasks of this CTA whose flag has been published
@@ -404,7 +435,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
 
   int local = 0;  // number of the task within this CTA
   for (int task = blockIdx.x; task < ntasks; task += gridDim.x, ++local) {
-    const TaskInfo t = decode_task<RS>(task, me, W, NC, T1, my_owned, C, n, cps, shard);
+    const TaskInfo t = decode_task<RS, GATHER>(task, me, W, NC, T1, my_owned, C, n, cps, shard);
     const int c = t.c, j = t.j;
     const int64_t lim = t.limit;
     // ---- entry (per warp): stop if this rank has failed; do not run too far ahead; wait for inputs ----
@@ -444,7 +475,9 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
 
     if (t.phase == 1) {
       // ---------------- phase 1: quantize own residual, push to the chunk's owner -------------------
-      uint8_t* dst = p.region[t.o] + recv1 + (uint64_t(j) * W + me) * slot;
+      const uint64_t dst_off = recv1 + (uint64_t(j) * W + me) * slot;
+      uint8_t* dst = p.region[t.o] + dst_off;
+      const int ndst = GATHER ? W : 1;
       const bool full = t.base + C <= lim;  // whole chunk inside the range: no per-access bounds checks
       if constexpr (COMPRESSED) {
         if (full) {
@@ -452,15 +485,16 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           const int warp = tid >> 5;
           if (!phase1_bulk<T, S, LEAN, SINGLE>(grad, prev, curr, ef, dst, t.base, iters, C, tid, mu, kappa, use_history, key1,
                                        stochastic, acc_stats, s_ring + warp * R::BYTES_PER_WARP, &s_bars[warp][0],
-                                       ring_uses, p.timeout_ns)) {
+                                       ring_uses, p.timeout_ns, ndst, p.region, dst_off)) {
             if (lane == 0)
               report_failure(status, kTimeoutBulk, uint32_t(me), 0xffffffffu, epoch, 0u, 1u, uint32_t(c));
             break;
           }
         } else
           phase1_compressed<T, S, LEAN, true, SINGLE>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
-                                              use_history, key1, stochastic, acc_stats);
-        if (!SINGLE && tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
+                                              use_history, key1, stochastic, acc_stats, ndst, p.region, dst_off);
+        if (!SINGLE && !GATHER && tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
+        if (GATHER && tid < W) *reinterpret_cast<float*>(p.region[tid] + dst_off + compressed_trailer_off(C)) = kappa;
       } else {
 #pragma unroll 2
         for (int it = 0; it < iters; ++it) {
@@ -477,7 +511,14 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
       // ---------------- phase 2: owner reduces the W contributions and broadcasts --------------------
       const float inv_w = 1.0f / float(W);
       uint8_t* src0 = myreg + recv1 + uint64_t(j) * W * slot;
-      if (COMPRESSED && !RS && tid < W) {
+      [[maybe_unused]] float gbar = kappa;  // gather mode: the gain applied to the prediction
+      if (GATHER && p.uniform_gain == 0) {
+        gbar = 0.0f;
+        for (int r = 0; r < W; ++r)
+          gbar += *reinterpret_cast<const float*>(src0 + uint64_t(r) * slot + compressed_trailer_off(C));
+        gbar *= inv_w;
+      }
+      if (COMPRESSED && !RS && !GATHER && tid < W) {
         // mean prediction gain of the senders: every rank applies the same value in phase 3
         float kbar = 0.0f;
         for (int r = 0; r < W; ++r)
@@ -485,6 +526,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
         *reinterpret_cast<float*>(p.region[tid] + p.recv2_off + uint64_t(c) * slot + compressed_trailer_off(C)) =
             kbar * inv_w;
       }
+      const uint64_t off2 = p.recv2_off + uint64_t(c) * slot;  // this chunk's broadcast slot in every region
       // what happens to the sum of one iteration (8 elements of this lane)
       auto finish = [&](int it, float (&acc)[kE]) {
 #pragma unroll
@@ -493,6 +535,20 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           // reduce-scatter: the mean of this rank's shard is the result; nothing is broadcast
           const int64_t local_i = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
           store8_guarded<T>(static_cast<T*>(p.out_shard[vr]), local_i, shard, acc);
+        } else if constexpr (GATHER) {
+          // the mean of the W dequantized residuals plus the prediction is the result on every rank
+          const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
+          if (base < n) {
+            if (gbar != 0.0f) {
+              float pv[kE], cu[kE];
+              load8_guarded<S>(prev, base, n, pv);
+              load8_guarded<S>(curr, base, n, cu);
+#pragma unroll
+              for (int i = 0; i < kE; ++i) acc[i] = __fmaf_rn(gbar, __fmaf_rn(mu, cu[i] - pv[i], cu[i]), acc[i]);
+            }
+            store8_guarded<T>(grad, base, n, acc);
+            store8_guarded<S>(prev, base, n, acc);  // becomes g(t) after the caller swaps prev and curr
+          }
         } else if constexpr (COMPRESSED) {
           const int64_t obase = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
           if (ef2 != nullptr) {
@@ -505,15 +561,19 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           uint32_t packed, sb;
           quantize8(acc, key2, uint32_t(base >> 1), stochastic, packed, sb);
           if (ef2 != nullptr) Vec8<S>::store(ef2 + obase, acc);
+          // peers first, this rank last; no division in the loop
+          int rr = me + 1 == W ? 0 : me + 1;
           for (int r = 0; r < W; ++r) {
-            uint8_t* dst = p.region[(me + 1 + r) % W] + p.recv2_off + uint64_t(c) * slot;
+            uint8_t* dst = p.region[rr] + off2;
             *packed_ptr(dst, C, it, tid) = packed;
             if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+            rr = rr + 1 == W ? 0 : rr + 1;
           }
         } else {
+          int rr = me + 1 == W ? 0 : me + 1;
           for (int r = 0; r < W; ++r) {
-            uint8_t* dst = p.region[(me + 1 + r) % W] + p.recv2_off + uint64_t(c) * slot;
-            Vec8<T>::store(reinterpret_cast<T*>(dst) + int64_t(it) * kElemsPerIter + tid * kE, acc);
+            Vec8<T>::store(reinterpret_cast<T*>(p.region[rr] + off2) + int64_t(it) * kElemsPerIter + tid * kE, acc);
+            rr = rr + 1 == W ? 0 : rr + 1;
           }
         }
       };
@@ -590,7 +650,10 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
     } else if (t.phase == 3) {
       // ---------------- phase 3: reconstruct, write bucket and history -------------------------------
       uint8_t* src = myreg + p.recv2_off + uint64_t(c) * slot;
-      const float kbar = COMPRESSED ? *reinterpret_cast<const float*>(src + compressed_trailer_off(C)) : 0.0f;
+      // with uniform gains the owner's mean equals this rank's own gain: no dependent load before the copies
+      const float kbar = !COMPRESSED        ? 0.0f
+                         : p.uniform_gain != 0 ? kappa
+                                               : *reinterpret_cast<const float*>(src + compressed_trailer_off(C));
       // one iteration of this lane once its packed word and scale are known
       auto emit = [&](auto guard_tag, int it, uint32_t pk, uint16_t sc, const uint8_t* hist_smem) {
         constexpr bool GUARD = decltype(guard_tag)::value;
@@ -695,10 +758,14 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
       const int sl = local % kSlots;
       if (atomicAdd(&s_count[sl], 1) == kWarps - 1) {
         s_count[sl] = 0;
-        if (t.phase == 1 && !SINGLE) {
+        if (t.phase == 1 && GATHER) {
+          __threadfence_system();
+          for (int r = 0; r < W; ++r)
+            st_release_sys(reinterpret_cast<uint32_t*>(p.region[r] + p.flag1_off) + (uint64_t(j) * W + me), epoch);
+        } else if (t.phase == 1 && !SINGLE) {
           __threadfence_system();
           st_release_sys(reinterpret_cast<uint32_t*>(p.region[t.o] + p.flag1_off) + (uint64_t(j) * W + me), epoch);
-        } else if (t.phase == 2 && !RS) {
+        } else if (t.phase == 2 && !RS && !GATHER) {
           __threadfence_system();
           for (int r = 0; r < W; ++r)
             st_release_sys(reinterpret_cast<uint32_t*>(p.region[(me + 1 + r) % W] + p.flag2_off) + c, epoch);
@@ -730,7 +797,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
 
 template <typename T, typename S, int MODE>
 cudaError_t launch_mode(const NangilaPredResParams& p, cudaStream_t stream) {
-  constexpr bool LEAN = MODE == 2 || MODE == 3 || MODE == 5;
+  constexpr bool LEAN = MODE == 2 || MODE == 3 || MODE == 5 || MODE == 7;
   constexpr int smem = MODE == 0 ? 0 : kWarps * Ring<T, S, LEAN>::BYTES_PER_WARP;
   static_assert(Ring<T, S, LEAN>::D <= kMaxDepth, "ring depth");
   const void* fn = reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, MODE>);
@@ -765,6 +832,7 @@ cudaError_t launch_ts(const NangilaPredResParams& p, cudaStream_t stream) {
   bool lean = p.mode == 0 && p.measure == 0;
   for (int v = 0; v < p.nvr; ++v) lean = lean && p.pred_gain[v] == 0.0f;
   if (p.mode == 0 && p.world == 1) return lean ? launch_mode<T, S, 5>(p, stream) : launch_mode<T, S, 4>(p, stream);
+  if (p.mode == 0 && p.gather != 0) return lean ? launch_mode<T, S, 7>(p, stream) : launch_mode<T, S, 6>(p, stream);
   if (p.mode == 0) return lean ? launch_mode<T, S, 3>(p, stream) : launch_mode<T, S, 1>(p, stream);
   if (p.mode == 1) return launch_mode<T, S, 0>(p, stream);
   return launch_mode<T, S, 2>(p, stream);
@@ -781,13 +849,16 @@ extern "C" uint64_t nangila_predres_region_bytes(int64_t n, int32_t world, int32
   const uint64_t nchunks = uint64_t((n + chunk_elems - 1) / chunk_elems);
   const uint64_t owned_max = (nchunks + world - 1) / world;
   const uint64_t slot = std::max<uint64_t>(nangila::compressed_slot_bytes(chunk_elems), uint64_t(chunk_elems) * esize);
+  // gather mode (small worlds): every rank holds all W slots of every chunk, twice (launch parity)
+  const bool gather_ok = world >= 2 && world <= NANGILA_GATHER_MAX_WORLD;
+  const uint64_t cslot = nangila::compressed_slot_bytes(chunk_elems);
   uint64_t off = 0;
   if (recv1_off) *recv1_off = off;
-  off = align(off + owned_max * world * slot);
+  off = align(off + std::max<uint64_t>(owned_max * world * slot, gather_ok ? 2 * nchunks * world * cslot : 0));
   if (recv2_off) *recv2_off = off;
   off = align(off + nchunks * slot);
   if (flag1_off) *flag1_off = off;
-  off = align(off + owned_max * world * 4);
+  off = align(off + std::max<uint64_t>(owned_max, gather_ok ? nchunks : 0) * world * 4);
   if (flag2_off) *flag2_off = off;
   off = align(off + nchunks * 4);
   return off;
@@ -827,6 +898,7 @@ extern "C" int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_
     return int(cudaErrorInvalidValue);
   }
   if (p->nvr > 1 && p->nvr != p->world) return int(cudaErrorInvalidValue);
+  if (p->gather != 0 && (p->world < 2 || p->world > NANGILA_GATHER_MAX_WORLD)) return int(cudaErrorInvalidValue);
   for (int v = 0; v < p->nvr; ++v)
     if (!(p->pred_gain[v] >= 0.0f && p->pred_gain[v] <= 1.0f)) return int(cudaErrorInvalidValue);
   cudaError_t e;

@@ -481,6 +481,11 @@ class NangilaDDPHook:
         if self._engine is not None:
             self._engine.end_step()
         if self._cpp is not None:
+            stats = self._cpp.stats_tensor()
+            if stats is not None and self.world_size > 1:
+                # sum the kernels' statistics over the group so that every rank derives the same gains
+                with torch.cuda.stream(torch.cuda.ExternalStream(self._cpp.stream_ptr(), device=stats.device)):
+                    dist.all_reduce(stats, group=self.process_group)
             self._cpp.step()
         if self._force_uncompressed:
             self._force_uncompressed = False  # one uncompressed step re-seeded the history everywhere

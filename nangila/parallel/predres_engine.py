@@ -17,6 +17,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import torch
+import torch.distributed as dist
 
 from .symm import LoopbackArena, Region, SymmArena
 
@@ -43,12 +44,15 @@ def _glue():
 
 
 def default_chunk_elems(n: int, world: int) -> int:
-    """Chunk size (elements): 16384 for large buckets, smaller when the bucket would otherwise give
-    fewer chunks than 4 per rank, never below 4096."""
+    """Chunk size (elements): the power of two at or above n / 1024, between 4096 and 131072, halved
+    while the bucket would give fewer than 4 chunks per rank. Every chunk costs one flag round trip per
+    phase, so large buckets want large chunks; small ones want enough chunks to fill the GPU."""
     env = os.environ.get("NANGILA_CHUNK")
     if env:
         return int(env)
-    c = 16384
+    c = 4096
+    while c < 131072 and c * 1024 < n:
+        c *= 2
     while c > 4096 and (n + c - 1) // c < 4 * world:
         c //= 2
     return c
@@ -110,6 +114,8 @@ class PredResEngine:
         self.fixed_gain = float(os.environ.get("NANGILA_PRED_GAIN", "1"))
         # with a zero gain the kernel skips the history loads except on every probe_every-th call
         self.probe_every = max(1, int(os.environ.get("NANGILA_PROBE_EVERY", "8")))
+        # small worlds use the kernel's gather mode (one quantization, two phases)
+        self.gather_max_world = min(4, int(os.environ.get("NANGILA_GATHER_MAX_WORLD", "4")))
         self.buckets: Dict[int, BucketState] = {}
         # one row of 8 floats per (bucket, emulated rank): {sum e^2, sum g^2, sum miss^2, sum ef^2, ...}
         self.max_buckets = max_buckets
@@ -196,6 +202,8 @@ class PredResEngine:
             rank0=0 if self.loopback else self.rank, chunk_elems=st.chunk, mode=0 if compressed else 1,
             stochastic=self.stochastic, measure=(st.calls % self.probe_every == 0), epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
             mu=self.momentum, pred_gain=self._gains(st), timeout_s=self.timeout_s, grid_x=self._grid(st),
+            uniform_gain=st.extra.get("pred_gain_per_rank") is None,
+            gather=compressed and 2 <= self.world <= self.gather_max_world,
         )
         if self.stream is not None:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -222,14 +230,17 @@ class PredResEngine:
         mini-batch noise (subtracting a full-size prediction there would make the residual larger
         than the gradient and, through error feedback, amplify the predictor's own quantization
         noise). Both inner products come from the kernel; the value of the previous step is used
-        (smoothed). The decision is local: ranks may differ, the kernel applies the mean of all
-        ranks' gains. A run-away error-feedback memory switches prediction off for a while.
+        (smoothed). The statistics are summed over the process group before they are read, so every
+        rank derives the same gain and the kernel is told so (``uniform_gain``); when a caller sets
+        different gains per rank the kernel applies their mean, carried in the chunk trailers. A
+        run-away error-feedback memory switches prediction off for a while.
         """
         if self._stats_event is not None:
             self._stats_event.synchronize()
             host = self._stats_host
             for st in self.buckets.values():
-                row = host[st.slot * self.nvr].tolist()
+                # emulated ranks: one controller for all of them, fed with the sum of their rows
+                row = host[st.slot * self.nvr:(st.slot + 1) * self.nvr].sum(0).tolist()
                 e2, g2, xp, pp, f2 = row[0], row[1], row[2], row[3], row[4]
                 if g2 <= 0.0:
                     continue
@@ -251,6 +262,9 @@ class PredResEngine:
                 st.pred_gain = gain if gain >= 0.2 else 0.0  # below 0.2 (< 4 % less residual energy) the history loads cost more than they save
         stream = self.stream if self.stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(stream):
+            if self.world > 1 and not self.loopback and self.adaptive_gain:
+                # every rank must derive the same gains: sum the statistics over the group first
+                dist.all_reduce(self.stats_table, group=getattr(self.arena, "group", None))
             self._stats_host.copy_(self.stats_table, non_blocking=True)
             self.stats_table.zero_()
             ev = torch.cuda.Event()

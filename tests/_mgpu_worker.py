@@ -96,6 +96,47 @@ def train(dev, rank, world, use_hook, steps, compressor_type=0, prefer_cpp=True)
     return out.tolist(), stats
 
 
+def train_fsdp(dev, rank, world, compress, steps):
+    """FSDP2 on a tiny Llama: per-block fully_shard, bf16 mixed precision, optional fused collectives."""
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    from nangila.fsdp import apply_nangila_fsdp
+    from nangila.models.llama import Llama, LlamaConfig
+
+    torch.manual_seed(0)
+    model = Llama(LlamaConfig.tiny()).to(dev)
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16)
+    for blk in model.blocks:
+        fully_shard(blk, mp_policy=mp)
+    fully_shard(model, mp_policy=mp)
+    rs = ag = None
+    if compress:
+        rs, ag = apply_nangila_fsdp(model, parameter_bits=8)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    gen = torch.Generator().manual_seed(7)
+    data = torch.randint(0, 64, (64, 33), generator=gen)
+    losses = []
+    for step in range(steps):
+        rows = torch.randint(0, 64, (4 * world,), generator=gen)[rank * 4:(rank + 1) * 4]
+        tok = data[rows].to(dev)
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        if rs is not None:
+            rs.step += 1
+        losses.append(loss.detach())
+    out = torch.stack(losses).float()
+    dist.all_reduce(out)
+    out /= world
+    info = None
+    if compress:
+        rs.check_status()
+        ag.check_status()
+        info = {"rs_launches": rs.launches, "ag_launches": ag.launches, "fallbacks": rs.fallbacks + ag.fallbacks}
+    return out.tolist(), info
+
+
 def main():
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -131,6 +172,15 @@ def main():
             results[f"ratio_{name}"] = stats["overall_compression_ratio"]
             assert results[f"loss_{name}"] < 0.9 * base[0], (name, results)
         results["loss_base"] = sum(base[-10:]) / 10
+    if what in ("all", "fsdp"):
+        base, _ = train_fsdp(dev, rank, world, False, 60)
+        ours, info = train_fsdp(dev, rank, world, True, 60)
+        results["fsdp_loss_base"] = sum(base[-10:]) / 10
+        results["fsdp_loss_ours"] = sum(ours[-10:]) / 10
+        results["fsdp"] = info
+        assert results["fsdp_loss_base"] < 0.8 * base[0], "FSDP baseline did not learn"
+        assert abs(results["fsdp_loss_ours"] - results["fsdp_loss_base"]) < 0.2 * results["fsdp_loss_base"] + 0.05, results
+        assert info["rs_launches"] > 0 and info["ag_launches"] > 0
     if rank == 0:
         print("MGPU_RESULT " + json.dumps(results), flush=True)
         if out_path:

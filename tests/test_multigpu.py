@@ -43,3 +43,10 @@ def test_dgc_and_powersgd_two_gpus(tmp_path):
         pytest.skip("needs 2 GPUs")
     res = _run(2, "compressors", tmp_path, 29751)
     assert res["ratio_dgc"] > 5 and res["ratio_powersgd"] > 2
+
+
+def test_fsdp2_fused_collectives_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, "fsdp", tmp_path, 29761)
+    assert res["fsdp"]["rs_launches"] > 0 and res["fsdp"]["ag_launches"] > 0
