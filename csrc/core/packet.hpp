@@ -30,18 +30,23 @@ constexpr uint8_t NO_PREDICTION = 0x80;
 }  // namespace flags
 
 namespace detail {
-inline const std::array<uint32_t, 256>& crc32_table() {
-  static const std::array<uint32_t, 256> table = [] {
-    std::array<uint32_t, 256> t{};
+// Slicing-by-8 tables: row 0 is the classic byte table; row k advances a byte that lies k positions
+// further from the end of an 8-byte group, so eight bytes are folded per step.
+inline const std::array<std::array<uint32_t, 256>, 8>& crc32_tables() {
+  static const std::array<std::array<uint32_t, 256>, 8> tables = [] {
+    std::array<std::array<uint32_t, 256>, 8> t{};
     for (uint32_t i = 0; i < 256; ++i) {
       uint32_t c = i;
       for (int k = 0; k < 8; ++k) c = (c & 1u) ? (0xEDB88320u ^ (c >> 1)) : (c >> 1);
-      t[i] = c;
+      t[0][i] = c;
     }
+    for (uint32_t i = 0; i < 256; ++i)
+      for (int k = 1; k < 8; ++k) t[k][i] = t[0][t[k - 1][i] & 0xff] ^ (t[k - 1][i] >> 8);
     return t;
   }();
-  return table;
+  return tables;
 }
+inline const std::array<uint32_t, 256>& crc32_table() { return crc32_tables()[0]; }
 template <class T>
 inline void put_le(uint8_t* p, T v) {
   for (size_t i = 0; i < sizeof(T); ++i) p[i] = uint8_t((uint64_t(v) >> (8 * i)) & 0xff);
@@ -56,9 +61,17 @@ inline T get_le(const uint8_t* p) {
 
 // Incremental form: pass the previous return value as `crc` to continue over a second buffer.
 inline uint32_t crc32_update(uint32_t crc, const uint8_t* data, size_t len) {
-  const auto& t = detail::crc32_table();
+  const auto& T = detail::crc32_tables();
+  const auto& t = T[0];
   uint32_t c = crc ^ 0xFFFFFFFFu;
-  for (size_t i = 0; i < len; ++i) c = t[(c ^ data[i]) & 0xff] ^ (c >> 8);
+  size_t i = 0;
+  for (; i + 8 <= len; i += 8) {
+    const uint32_t lo = c ^ (uint32_t(data[i]) | uint32_t(data[i + 1]) << 8 | uint32_t(data[i + 2]) << 16 |
+                             uint32_t(data[i + 3]) << 24);
+    c = T[7][lo & 0xff] ^ T[6][(lo >> 8) & 0xff] ^ T[5][(lo >> 16) & 0xff] ^ T[4][lo >> 24] ^ T[3][data[i + 4]] ^
+        T[2][data[i + 5]] ^ T[1][data[i + 6]] ^ T[0][data[i + 7]];
+  }
+  for (; i < len; ++i) c = t[(c ^ data[i]) & 0xff] ^ (c >> 8);
   return c ^ 0xFFFFFFFFu;
 }
 inline uint32_t compute_crc32(const uint8_t* data, size_t len) { return crc32_update(0, data, len); }

@@ -17,6 +17,8 @@
 #include <torch/csrc/jit/python/pybind_utils.h>
 #include <torch/extension.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -67,6 +69,8 @@ struct Bucket {
   uint64_t calls = 0;
   uint64_t compressed_calls = 0;
   double totals[4] = {0, 0, 0, 0};
+  // NANGILA_TIMING=1: events around the most recent launch of this bucket
+  std::shared_ptr<at::cuda::CUDAEvent> t0, t1;
 };
 
 class DdpHook {
@@ -81,6 +85,8 @@ class DdpHook {
     probe_every_ = std::max<int64_t>(1, int64_t(env_double("NANGILA_PROBE_EVERY", 8)));
     chunk_override_ = int32_t(env_double("NANGILA_CHUNK", 0));
     ctas_ = int32_t(env_double("NANGILA_COMM_CTAS", 0));
+    timing_ = env_double("NANGILA_TIMING", 0) != 0;
+    nvtx_ = env_double("NANGILA_NVTX", 0) != 0;
     gather_max_world_ = std::min<int32_t>(NANGILA_GATHER_MAX_WORLD, int32_t(env_double("NANGILA_GATHER_MAX_WORLD", NANGILA_GATHER_MAX_WORLD)));
   }
 
@@ -181,7 +187,17 @@ class DdpHook {
     c10::cuda::CUDAStream producer = c10::cuda::getCurrentCUDAStream(tensor.device().index());
     ready_.record(producer);
     ready_.block(*stream_);
+    if (nvtx_) nvtxRangePushA(compressed ? "nangila.bucket.int4" : "nangila.bucket.exact");
+    if (timing_) {
+      if (!b.t0) {
+        b.t0 = std::make_shared<at::cuda::CUDAEvent>(cudaEventDefault);
+        b.t1 = std::make_shared<at::cuda::CUDAEvent>(cudaEventDefault);
+      }
+      b.t0->record(*stream_);
+    }
     const int err = nangila_predres_launch(&p, stream_->stream());
+    if (timing_) b.t1->record(*stream_);
+    if (nvtx_) nvtxRangePop();
     TORCH_CHECK(err == 0, "nangila: predres_launch failed: ", cudaGetErrorString(static_cast<cudaError_t>(err)));
     std::swap(b.prev, b.curr);
     }  // state lock released: completing the future below drops and re-takes the GIL
@@ -273,6 +289,13 @@ class DdpHook {
     py::dict gains;
     for (auto& kv : buckets_) gains[py::int_(kv.first)] = kv.second.pred_gain;
     d["prediction_gain"] = gains;
+    if (timing_) {
+      // device time of each bucket's most recent launch, where it has completed (nothing is synchronised)
+      py::dict ms;
+      for (auto& kv : buckets_)
+        if (kv.second.t1 && kv.second.t1->query()) ms[py::int_(kv.first)] = kv.second.t0->elapsed_time(*kv.second.t1);
+      d["bucket_kernel_ms"] = ms;
+    }
     return d;
   }
   int64_t launches() const { return launches_; }
@@ -301,7 +324,8 @@ class DdpHook {
   void ensure_device(const at::Tensor& t) {
     if (stream_) return;
     device_ = t.device();
-    stream_.emplace(c10::cuda::getStreamFromPool(/*isHighPriority=*/true, device_.index()));
+    // NANGILA_STREAM_PRIORITY=0 puts the exchange on a normal-priority stream (default: high priority)
+    stream_.emplace(c10::cuda::getStreamFromPool(/*isHighPriority=*/env_double("NANGILA_STREAM_PRIORITY", -1) < 0, device_.index()));
     auto f32 = at::TensorOptions().dtype(at::kFloat).device(device_);
     stats_dev_ = at::zeros({max_buckets_, kStatsWidth}, f32);
     stats_host_ = at::zeros({max_buckets_, kStatsWidth}, at::TensorOptions().dtype(at::kFloat).pinned_memory(true));
@@ -387,6 +411,8 @@ class DdpHook {
   int32_t chunk_override_;
   int32_t ctas_;
   int32_t gather_max_world_;
+  bool timing_ = false;
+  bool nvtx_ = false;
   std::mutex mutex_;
   std::map<int64_t, Bucket> buckets_;
   int next_slot_ = 0;

@@ -514,8 +514,12 @@ class NangilaDDPHook:
             stats["overall_compression_ratio"] = native["compression_ratio"]
             stats["pred_gain_per_bucket"] = dict(native["prediction_gain"])
             stats["cpp_hook"] = True
+            if "bucket_kernel_ms" in native:
+                stats["bucket_kernel_ms"] = dict(native["bucket_kernel_ms"])
         if self._engine is not None:
             stats["kernel_launches"] = self._engine.launches
+            if self._engine.timing:
+                stats["bucket_kernel_ms"] = self._engine.kernel_times_ms()
             errs = {}
             for idx, st in self._engine.buckets.items():
                 if st.compressed_calls:

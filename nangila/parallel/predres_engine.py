@@ -126,6 +126,9 @@ class PredResEngine:
         self._stats_event: Optional[torch.cuda.Event] = None
         self.status = [torch.zeros(8, dtype=torch.int32, device=self.device) for _ in range(self.nvr)]
         self.launches = 0
+        self.nvtx = os.environ.get("NANGILA_NVTX", "0") == "1"      # one NVTX range per bucket launch
+        self.timing = os.environ.get("NANGILA_TIMING", "0") == "1"  # CUDA events around every launch
+        self._events: Dict[int, tuple] = {}
         self.stream: Optional[torch.cuda.Stream] = None
         if use_side_stream:
             self.stream = torch.cuda.Stream(device=self.device, priority=-1)
@@ -205,14 +208,38 @@ class PredResEngine:
             uniform_gain=st.extra.get("pred_gain_per_rank") is None,
             gather=compressed and 2 <= self.world <= self.gather_max_world,
         )
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(f"nangila.bucket{index}.{'int4' if compressed else 'exact'}")
         if self.stream is not None:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.stream):
-                self._glue.predres_launch(**args)
+                self._timed_launch(index, args)
         else:
-            self._glue.predres_launch(**args)
+            self._timed_launch(index, args)
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
         st.swap()
         return st
+
+    def _timed_launch(self, index: int, args: dict) -> None:
+        if not self.timing:
+            self._glue.predres_launch(**args)
+            return
+        ev = self._events.get(index)
+        if ev is None:
+            ev = self._events[index] = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        ev[0].record()
+        self._glue.predres_launch(**args)
+        ev[1].record()
+
+    def kernel_times_ms(self) -> Dict[int, float]:
+        """Device time of the most recent launch of every bucket (``NANGILA_TIMING=1``); buckets whose
+        last launch has not finished yet are left out. Nothing is synchronised."""
+        out = {}
+        for idx, (e0, e1) in self._events.items():
+            if e1.query():
+                out[idx] = e0.elapsed_time(e1)
+        return out
 
     def _gains(self, st: BucketState) -> List[float]:
         g = st.extra.get("pred_gain_per_rank")
@@ -277,6 +304,8 @@ class PredResEngine:
             self.stream.synchronize()
         else:
             torch.cuda.synchronize(self.device)
+        if os.environ.get("NANGILA_CHECKED", "0") == "1" and hasattr(self.arena, "check_canaries"):
+            self.arena.check_canaries()
         for vr, s in enumerate(self.status):
             w = s.cpu().tolist()
             if w[0] != 0:

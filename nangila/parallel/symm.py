@@ -26,6 +26,8 @@ import torch
 import torch.distributed as dist
 
 _ALIGN = 256
+_CANARY = 0xA5          # NANGILA_CHECKED=1: every region is followed by a guard block of this byte
+_CANARY_BYTES = 256
 
 
 def _round_up(x: int, a: int = _ALIGN) -> int:
@@ -80,6 +82,7 @@ class SymmArena:
         self.world = dist.get_world_size(self.group)
         self.segment_bytes = segment_bytes
         self.segments: List[_Segment] = []
+        self._guards: List[torch.Tensor] = []
         self.provider = _provider_for(self.world)
 
     # -- providers ---------------------------------------------------------------------------
@@ -157,14 +160,35 @@ class SymmArena:
             self._new_segment(nbytes)
 
     def allocate(self, nbytes: int) -> Region:
+        checked = os.environ.get("NANGILA_CHECKED", "0") == "1"
+        want = _round_up(nbytes) + (_CANARY_BYTES if checked else 0)
+        off = None
         for seg in self.segments:
-            off = seg.take(nbytes)
+            off = seg.take(want)
             if off is not None:
-                return Region(seg, off, nbytes)
-        seg = self._new_segment(nbytes)
-        off = seg.take(nbytes)
-        assert off is not None
-        return Region(seg, off, nbytes)
+                break
+        if off is None:
+            seg = self._new_segment(want)
+            off = seg.take(want)
+            assert off is not None
+        region = Region(seg, off, nbytes)
+        if checked:
+            guard = seg.local[off + _round_up(nbytes):off + _round_up(nbytes) + _CANARY_BYTES]
+            guard.fill_(_CANARY)
+            self._guards.append(guard)
+            torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+        return region
+
+    def check_canaries(self) -> None:
+        """Checked mode: raise if any kernel (local or a peer's) wrote past the end of a region of this
+        rank. The guards are filled at allocation and never written afterwards."""
+        for i, g in enumerate(self._guards):
+            if not bool((g == _CANARY).all()):
+                bad = int((g != _CANARY).nonzero()[0])
+                raise RuntimeError(f"nangila: guard block after symmetric region {i} was overwritten at byte {bad} "
+                                   f"(rank {self.rank})")
 
 
 class LoopbackArena:
@@ -175,12 +199,24 @@ class LoopbackArena:
         self.rank = 0
         self.device = torch.device(device)
         self.provider = "loopback"
+        self._guards: List[torch.Tensor] = []
 
     def reserve(self, nbytes: int) -> None:
         return None
 
     def allocate(self, nbytes: int) -> Region:
         nbytes = _round_up(nbytes)
-        bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=self.device) for _ in range(self.world)]
+        checked = os.environ.get("NANGILA_CHECKED", "0") == "1"
+        total = nbytes + (_CANARY_BYTES if checked else 0)
+        bufs = [torch.zeros(total, dtype=torch.uint8, device=self.device) for _ in range(self.world)]
+        if checked:
+            for b in bufs:
+                b[nbytes:].fill_(_CANARY)
+                self._guards.append(b[nbytes:])
         seg = _Segment(bufs[0], [b.data_ptr() for b in bufs], keepalive=bufs)
         return Region(seg, 0, nbytes)
+
+    def check_canaries(self) -> None:
+        for i, g in enumerate(self._guards):
+            if not bool((g == _CANARY).all()):
+                raise RuntimeError(f"nangila: guard block {i} of the loopback arena was overwritten")

@@ -209,3 +209,68 @@ def test_wait_times_out_and_reports_status():
     assert torch.ones(4, device="cuda").sum().item() == 4.0  # the device is still healthy
     # the status block was cleared by the check: a later launch can be diagnosed again
     assert int(eng.status[0][0].item()) == 0
+
+
+def test_replay_is_deterministic_and_guards_hold(monkeypatch):
+    """Two engines fed the same inputs produce the same bytes (outputs, history, error memory), with
+    stochastic rounding on; in checked mode the guard blocks behind every symmetric region stay intact."""
+    monkeypatch.setenv("NANGILA_CHECKED", "1")
+    world, n = 4, 4096 * 9 + 333
+    outs = []
+    for _ in range(2):
+        eng = _engine(world, stochastic=True, error_feedback=True)
+        gen = torch.Generator(device="cuda").manual_seed(5)
+        for step in range(4):
+            grads = [(torch.randn(n, device="cuda", generator=gen) * 0.01).to(torch.bfloat16) for _ in range(world)]
+            eng.reduce(0, grads, compressed=step >= 2, step=step)
+        eng.check_status()  # includes the guard check
+        st = eng.buckets[0]
+        outs.append([grads[0].clone(), st.curr[0].clone(), st.prev[0].clone(), st.ef[0].clone()])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+def test_cpp_hook_matches_python_engine_on_one_gpu(monkeypatch):
+    """The C++ hook and the Python engine drive the same kernel: identical results for identical inputs
+    (single-rank group, round-to-nearest, fixed prediction gain, so nothing is random or adaptive)."""
+    import os
+
+    monkeypatch.setenv("NANGILA_PRED_GAIN", "1")
+    import socket
+
+    import torch.distributed as dist
+
+    import nangila
+    from nangila.parallel.predres_engine import PredResEngine
+    from nangila.parallel.symm import SymmArena
+
+    created = False
+    if not dist.is_initialized():
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(s.getsockname()[1])
+        s.close()
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        created = True
+    try:
+        dev = torch.device("cuda", 0)
+        n = 4096 * 7 + 40
+        cpp = nangila.NangilaCppHook(1, 2, None, stochastic=False)
+        cpp._attach(dev)
+        eng = PredResEngine(SymmArena(None, dev), dev, stochastic=False, use_side_stream=False, adaptive_gain=False)
+        eng.fixed_gain = 1.0
+        gen = torch.Generator(device="cuda").manual_seed(9)
+        for step in range(5):
+            g = (torch.randn(n, device="cuda", generator=gen) * 0.01).to(torch.bfloat16)
+            a, b = g.clone(), g.clone()
+            cpp.run_tensor(0, a).wait()
+            eng.reduce(0, [b], compressed=step >= 2, step=step)
+            torch.cuda.synchronize()
+            cpp.step()
+            eng.end_step()
+            assert torch.equal(a, b), f"step {step}"
+        cpp.check_status()
+        assert cpp.get_stats()["compression_enabled"] and cpp.get_kernel_launches() == 5
+    finally:
+        if created:
+            dist.destroy_process_group()
