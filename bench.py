@@ -115,7 +115,7 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ddp"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ddp", "refkernels"])
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--model", default="small", choices=["small", "tiny"])
@@ -152,6 +152,12 @@ def main() -> int:
     model = GPT2(cfg).to(dev).to(torch.bfloat16)
     ddp = DDP(model, device_ids=[local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
     hook = None
+    if args.impl == "refkernels":
+        # the reference's own CUDA kernels (compiled unmodified) behind NCCL all-gathers: "compress, then call NCCL"
+        from baseline.ref_kernel_hook import RefKernelHook
+
+        hook = RefKernelHook(ddp.process_group, warmup_steps=100)
+        ddp.register_comm_hook(None, hook)
     if args.impl == "ours":
         hook = register_nangila_hook(ddp, threshold=0.95, warmup_steps=100, prefer_cpp=not args.python_hook)
     opt = torch.optim.AdamW(ddp.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
@@ -238,7 +244,9 @@ def main() -> int:
             "config": {"model": f"gpt2-{args.model} 12L d768 h12 mlp3072 vocab50257 ctx1024" if args.model == "small" else "gpt2-tiny",
                        "global_batch": mb * world, "micro_batch_per_gpu": mb, "seq_len": seq,
                        "parallelism": f"dp{world}", "bucket_mb": 25, "optimizer": "AdamW(fused)",
-                       "hook": ("nangila prediction-residual INT4, warmup_steps=100 (fast-forwarded after 2 exact steps)"
+                       "hook": ("reference CUDA kernels (unmodified) + NCCL all-gathers, single gamma per bucket"
+                                if args.impl == "refkernels" else
+                                "nangila prediction-residual INT4, warmup_steps=100 (fast-forwarded after 2 exact steps)"
                                 if hook is not None else "stock DDP all-reduce"),
                        "l2": "per-step working set (weights, grads, optimizer state, activations: several GB) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,
