@@ -50,9 +50,37 @@ constexpr int kScratchWords = kCursor + 8;
 template <typename T>
 __device__ __forceinline__ float ldf(const T* p, int64_t i) { return dev::Vec16<T>::to_float(p[i]); }
 
+// Four consecutive elements (the bucket and the fp32 state are at least 16-byte aligned and the
+// vector index is a multiple of 4, so 8- and 16-byte accesses are aligned).
+template <typename T>
+__device__ __forceinline__ void ld4(const T* p, int64_t i, float (&x)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p + i);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+  } else {
+    const uint2 a = *reinterpret_cast<const uint2*>(p + i);
+    const T* h = reinterpret_cast<const T*>(&a);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) x[k] = dev::Vec16<T>::to_float(h[k]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void st4_zero(T* p, int64_t i) {
+  if constexpr (sizeof(T) == 4) *reinterpret_cast<float4*>(p + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+  else *reinterpret_cast<uint2*>(p + i) = make_uint2(0u, 0u);
+}
+
+// One vote per distinct bin of the warp: gradients cluster in a handful of exponent bins, and 32 lanes
+// adding to the same shared-memory word would be serialised. `active` lanes hold a valid `bin`.
+__device__ __forceinline__ void hist_add(uint32_t* hist, uint32_t bin, bool active) {
+  const uint32_t live = __ballot_sync(0xffffffffu, active);
+  if (!active) return;
+  const uint32_t peers = __match_any_sync(live, bin);
+  if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], uint32_t(__popc(peers)));
+}
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 2) dgc_fused_kernel(const __grid_constant__ NangilaDgcParams p) {
+__global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_constant__ NangilaDgcParams p) {
   cg::grid_group grid = cg::this_grid();
   const int vr = blockIdx.y;
   const int me = p.rank0 + vr;
@@ -79,6 +107,11 @@ __global__ void __launch_bounds__(kThreads, 2) dgc_fused_kernel(const __grid_con
   __shared__ uint32_t sh_sel[2];
   const int64_t tid0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * kThreads;
+  // The dense passes walk the bucket in groups of 4 elements; every warp keeps all 32 lanes in the loop
+  // (the loop bound is rounded up per warp) so that the warp-wide votes below are well defined.
+  const int64_t n4 = n / 4;                          // whole groups
+  const int64_t groups = (n + 3) / 4;                // including the ragged last one
+  const int64_t groups_rounded = (groups + 31) / 32 * 32;
 
   // ---- phase 0 ----
   for (int i = int(tid0); i < kScratchWords; i += int(stride)) scratch[i] = 0u;
@@ -87,13 +120,38 @@ __global__ void __launch_bounds__(kThreads, 2) dgc_fused_kernel(const __grid_con
   // ---- phase 1: momentum correction + histogram of bits [30:20] ----
   for (int i = threadIdx.x; i < kBins0; i += kThreads) sh_hist[i] = 0u;
   __syncthreads();
-  for (int64_t i = tid0; i < n; i += stride) {
-    float g = dev::sanitize(ldf(grad, i));
-    float un = __fmaf_rn(p.momentum, u[i], g);
-    float vn = v[i] + un;
-    u[i] = un;
-    v[i] = vn;
-    atomicAdd(&sh_hist[(__float_as_uint(vn) & 0x7fffffffu) >> 20], 1u);
+  for (int64_t q = tid0; q < groups_rounded; q += stride) {
+    float vn[4];
+    int valid = 0;
+    if (q < n4) {
+      float g[4];
+      ld4<T>(grad, q * 4, g);
+      float4 uu = *reinterpret_cast<const float4*>(u + q * 4);
+      float4 vv = *reinterpret_cast<const float4*>(v + q * 4);
+      uu.x = __fmaf_rn(p.momentum, uu.x, dev::sanitize(g[0]));
+      uu.y = __fmaf_rn(p.momentum, uu.y, dev::sanitize(g[1]));
+      uu.z = __fmaf_rn(p.momentum, uu.z, dev::sanitize(g[2]));
+      uu.w = __fmaf_rn(p.momentum, uu.w, dev::sanitize(g[3]));
+      vv.x += uu.x; vv.y += uu.y; vv.z += uu.z; vv.w += uu.w;
+      *reinterpret_cast<float4*>(u + q * 4) = uu;
+      *reinterpret_cast<float4*>(v + q * 4) = vv;
+      vn[0] = vv.x; vn[1] = vv.y; vn[2] = vv.z; vn[3] = vv.w;
+      valid = 4;
+    } else if (q < groups) {
+      for (int k = 0; k < 4; ++k) {
+        const int64_t i = q * 4 + k;
+        vn[k] = 0.0f;
+        if (i < n) {
+          const float un = __fmaf_rn(p.momentum, u[i], dev::sanitize(ldf(grad, i)));
+          vn[k] = v[i] + un;
+          u[i] = un;
+          v[i] = vn[k];
+          valid = k + 1;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) hist_add(sh_hist, (__float_as_uint(vn[k]) & 0x7fffffffu) >> 20, k < valid);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < kBins0; i += kThreads)
@@ -102,12 +160,25 @@ __global__ void __launch_bounds__(kThreads, 2) dgc_fused_kernel(const __grid_con
   uint32_t want = p.k, bin0, bin1, bin2;
   select_bin(scratch + kHist0, kBins0, want, bin0, sh_sel);
 
+  // bit patterns of |v| for one group (0 beyond the end: never selected, never counted)
+  auto load_bits = [&](int64_t q, uint32_t (&b)[4]) {
+    if (q < n4) {
+      const uint4 a = *reinterpret_cast<const uint4*>(v + q * 4);
+      b[0] = a.x & 0x7fffffffu; b[1] = a.y & 0x7fffffffu; b[2] = a.z & 0x7fffffffu; b[3] = a.w & 0x7fffffffu;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) b[k] = (q * 4 + k < n) ? (__float_as_uint(v[q * 4 + k]) & 0x7fffffffu) : 0xffffffffu;
+    }
+  };
+
   // ---- phase 2: bits [19:9] ----
   for (int i = threadIdx.x; i < kBins1; i += kThreads) sh_hist[i] = 0u;
   __syncthreads();
-  for (int64_t i = tid0; i < n; i += stride) {
-    uint32_t b = __float_as_uint(v[i]) & 0x7fffffffu;
-    if ((b >> 20) == bin0) atomicAdd(&sh_hist[(b >> 9) & 0x7ffu], 1u);
+  for (int64_t q = tid0; q < groups_rounded; q += stride) {
+    uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+    if (q < groups) load_bits(q, b);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) hist_add(sh_hist, (b[k] >> 9) & 0x7ffu, b[k] != 0xffffffffu && (b[k] >> 20) == bin0);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < kBins1; i += kThreads)
@@ -119,9 +190,11 @@ __global__ void __launch_bounds__(kThreads, 2) dgc_fused_kernel(const __grid_con
   for (int i = threadIdx.x; i < kBins2; i += kThreads) sh_hist[i] = 0u;
   __syncthreads();
   const uint32_t prefix = (bin0 << 11) | bin1;
-  for (int64_t i = tid0; i < n; i += stride) {
-    uint32_t b = __float_as_uint(v[i]) & 0x7fffffffu;
-    if ((b >> 9) == prefix) atomicAdd(&sh_hist[b & 0x1ffu], 1u);
+  for (int64_t q = tid0; q < groups_rounded; q += stride) {
+    uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+    if (q < groups) load_bits(q, b);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) hist_add(sh_hist, b[k] & 0x1ffu, b[k] != 0xffffffffu && (b[k] >> 9) == prefix);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < kBins2; i += kThreads)
@@ -131,30 +204,36 @@ __global__ void __launch_bounds__(kThreads, 2) dgc_fused_kernel(const __grid_con
   const uint32_t tau = (prefix << 9) | bin2;  // bit pattern of the k-th largest |v|
 
   // ---- phase 4: compaction + masking + clear the dense bucket ----
-  for (int64_t i0 = int64_t(blockIdx.x) * kThreads; i0 < n; i0 += stride) {
-    const int64_t i = i0 + threadIdx.x;
-    bool sel = false;
-    float val = 0.0f;
-    if (i < n) {
-      val = v[i];
-      uint32_t b = __float_as_uint(val) & 0x7fffffffu;
-      sel = b >= tau && (p.k > 0) && b != 0u;
-      grad[i] = dev::Vec16<T>::from_float(0.0f);
+  for (int64_t q = tid0; q < groups_rounded; q += stride) {
+    uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+    if (q < groups) {
+      load_bits(q, b);
+      if (q < n4) {
+        st4_zero<T>(grad, q * 4);
+      } else {
+        for (int k = 0; k < 4; ++k)
+          if (q * 4 + k < n) grad[q * 4 + k] = dev::Vec16<T>::from_float(0.0f);
+      }
     }
-    // warp-aggregated append
-    uint32_t mask = __ballot_sync(0xffffffffu, sel);
-    if (mask) {
-      int lane = threadIdx.x & 31;
-      uint32_t base = 0;
-      if (lane == __ffs(mask) - 1) base = atomicAdd(&scratch[kCursor], uint32_t(__popc(mask)));
-      base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
-      if (sel) {
-        uint32_t pos = base + uint32_t(__popc(mask & ((1u << lane) - 1u)));
-        if (pos < cap) {
-          my_idx[pos] = uint32_t(i);
-          my_val[pos] = val;
-          v[i] = 0.0f;
-          u[i] = 0.0f;
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const bool sel = b[k] != 0xffffffffu && b[k] >= tau && (p.k > 0) && b[k] != 0u;
+      // warp-aggregated append
+      const uint32_t mask = __ballot_sync(0xffffffffu, sel);
+      if (mask) {
+        uint32_t base = 0;
+        if (lane == __ffs(mask) - 1) base = atomicAdd(&scratch[kCursor], uint32_t(__popc(mask)));
+        base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
+        if (sel) {
+          const uint32_t pos = base + uint32_t(__popc(mask & ((1u << lane) - 1u)));
+          if (pos < cap) {
+            const int64_t i = q * 4 + k;
+            my_idx[pos] = uint32_t(i);
+            my_val[pos] = v[i];
+            v[i] = 0.0f;
+            u[i] = 0.0f;
+          }
         }
       }
     }

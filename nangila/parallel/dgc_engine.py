@@ -60,8 +60,8 @@ class DGCEngine:
         self._glue = _glue()
 
     def _grid(self, n: int) -> int:
-        cap = self.ctas or max(1, (148 * 2) // self.nvr)  # cooperative: all CTAs co-resident
-        return max(1, min(cap, (n + 255) // 256))
+        cap = self.ctas or max(1, (148 * 3) // self.nvr)  # cooperative: all CTAs co-resident (3 per SM)
+        return max(1, min(cap, (n + 1023) // 1024))  # 4 elements per thread and pass
 
     def bucket_state(self, index: int, grads: List[torch.Tensor]) -> DGCBucket:
         n = grads[0].numel()

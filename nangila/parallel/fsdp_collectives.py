@@ -38,7 +38,14 @@ except Exception:  # pragma: no cover - older torch
 
 
 def _chunk_for(shard: int) -> int:
-    c = 16384
+    """Chunk size for a shard: the power of two at or above shard / 1024 in [4096, 131072] (every chunk
+    costs a flag round trip), halved while the shard would give fewer than 4 chunks, never below 2048."""
+    env = os.environ.get("NANGILA_CHUNK")
+    if env:
+        return int(env)
+    c = 4096
+    while c < 131072 and c * 1024 < shard:
+        c *= 2
     while c > 2048 and shard < 4 * c:
         c //= 2
     return c
