@@ -69,6 +69,9 @@ void dgc_launch(const std::vector<at::Tensor>& grad, const std::vector<at::Tenso
     p.u[i] = u[i].data_ptr<float>();
     p.v[i] = v[i].data_ptr<float>();
     p.scratch[i] = reinterpret_cast<uint32_t*>(scratch[i].data_ptr<int32_t>());
+    // whatever follows the fixed scratch words is the candidate list (index, bits pairs)
+    const int64_t extra = (scratch[i].numel() - int64_t(nangila_dgc_scratch_words())) / 2;
+    if (i == 0 || extra < int64_t(p.cand_capacity)) p.cand_capacity = uint32_t(std::max<int64_t>(extra, 0));
     p.status[i] = reinterpret_cast<uint32_t*>(status[i].data_ptr<int32_t>());
     p.out_count[i] = reinterpret_cast<uint32_t*>(out_count[i].data_ptr<int32_t>());
   }

@@ -45,7 +45,8 @@ constexpr int kThreads = 256;
 // scratch layout (uint32 words)
 constexpr int kHist0 = 0, kHist1 = kHist0 + kBins0, kHist2 = kHist1 + kBins1;
 constexpr int kCursor = kHist2 + kBins2;  // number of selected entries
-constexpr int kScratchWords = kCursor + 8;
+constexpr int kCandCount = kCursor + 1;   // number of candidates seen in phase 1 (may exceed the capacity)
+constexpr int kScratchWords = kCursor + 8;  // the candidate list (index, bits pairs) follows
 
 template <typename T>
 __device__ __forceinline__ float ldf(const T* p, int64_t i) { return dev::Vec16<T>::to_float(p[i]); }
@@ -105,6 +106,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
 
   __shared__ uint32_t sh_hist[kBins0];
   __shared__ uint32_t sh_sel[2];
+  __shared__ uint32_t sh_cand_full;  // set once this CTA has seen the candidate list overflow
   const int64_t tid0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * kThreads;
   // The dense passes walk the bucket in groups of 4 elements; every warp keeps all 32 lanes in the loop
@@ -113,8 +115,22 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
   const int64_t groups = (n + 3) / 4;                // including the ragged last one
   const int64_t groups_rounded = (groups + 31) / 32 * 32;
 
+  // Candidates. Between two calls on the same bucket the threshold moves little, so phase 1 also
+  // collects every entry with |v| >= 0.9 * (previous threshold) into a short list. If that list holds
+  // at least k entries and did not overflow, the k largest entries of the bucket are all in it and the
+  // three selection passes and the compaction run over the list (a few thousand entries) instead of
+  // the dense state; otherwise (first call, threshold moved a lot) the dense passes run as before.
+  const uint32_t tau_prev = p.out_count[vr][1];
+  const uint32_t cand_cap = p.cand_capacity;
+  const uint32_t cand_thr = (cand_cap > 0 && tau_prev > 0 && tau_prev < 0x7f800000u)
+                                ? __float_as_uint(__uint_as_float(tau_prev) * 0.9f)
+                                : 0xffffffffu;  // nothing qualifies
+  uint32_t* cand_idx = scratch + kScratchWords;
+  uint32_t* cand_bits = cand_idx + cand_cap;
+
   // ---- phase 0 ----
   for (int i = int(tid0); i < kScratchWords; i += int(stride)) scratch[i] = 0u;
+  if (threadIdx.x == 0) sh_cand_full = 0u;
   grid.sync();
 
   // ---- phase 1: momentum correction + histogram of bits [30:20] ----
@@ -135,6 +151,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
       vv.x += uu.x; vv.y += uu.y; vv.z += uu.z; vv.w += uu.w;
       *reinterpret_cast<float4*>(u + q * 4) = uu;
       *reinterpret_cast<float4*>(v + q * 4) = vv;
+      st4_zero<T>(grad, q * 4);  // the dense result starts from zero; phase 6 scatters into it
       vn[0] = vv.x; vn[1] = vv.y; vn[2] = vv.z; vn[3] = vv.w;
       valid = 4;
     } else if (q < groups) {
@@ -146,12 +163,36 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
           vn[k] = v[i] + un;
           u[i] = un;
           v[i] = vn[k];
+          grad[i] = dev::Vec16<T>::from_float(0.0f);
           valid = k + 1;
         }
       }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) hist_add(sh_hist, (__float_as_uint(vn[k]) & 0x7fffffffu) >> 20, k < valid);
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t b = __float_as_uint(vn[k]) & 0x7fffffffu;
+      hist_add(sh_hist, b >> 20, k < valid);
+      // once the list has overflowed the dense passes will run anyway: stop counting (the shared flag
+      // is only a hint, a stale read costs one more atomic)
+      const bool cand = k < valid && b >= cand_thr && *reinterpret_cast<volatile uint32_t*>(&sh_cand_full) == 0u;
+      const uint32_t mask = __ballot_sync(0xffffffffu, cand);
+      if (mask) {
+        const int lane = threadIdx.x & 31;
+        uint32_t base = 0;
+        if (lane == __ffs(mask) - 1) {
+          base = atomicAdd(&scratch[kCandCount], uint32_t(__popc(mask)));
+          if (base + uint32_t(__popc(mask)) > cand_cap) sh_cand_full = 1u;
+        }
+        base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
+        if (cand) {
+          const uint32_t pos = base + uint32_t(__popc(mask & ((1u << lane) - 1u)));
+          if (pos < cand_cap) {
+            cand_idx[pos] = uint32_t(q * 4 + k);
+            cand_bits[pos] = b;
+          }
+        }
+      }
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < kBins0; i += kThreads)
@@ -160,79 +201,124 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
   uint32_t want = p.k, bin0, bin1, bin2;
   select_bin(scratch + kHist0, kBins0, want, bin0, sh_sel);
 
-  // bit patterns of |v| for one group (0 beyond the end: never selected, never counted)
-  auto load_bits = [&](int64_t q, uint32_t (&b)[4]) {
-    if (q < n4) {
-      const uint4 a = *reinterpret_cast<const uint4*>(v + q * 4);
-      b[0] = a.x & 0x7fffffffu; b[1] = a.y & 0x7fffffffu; b[2] = a.z & 0x7fffffffu; b[3] = a.w & 0x7fffffffu;
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) b[k] = (q * 4 + k < n) ? (__float_as_uint(v[q * 4 + k]) & 0x7fffffffu) : 0xffffffffu;
+  const uint32_t ncand = scratch[kCandCount];
+  const bool from_list = cand_cap > 0 && ncand >= p.k && ncand <= cand_cap;  // same on every CTA
+  uint32_t tau;
+  if (from_list) {
+    // ---- phases 2-4 over the candidate list ----
+    for (int i = threadIdx.x; i < kBins1; i += kThreads) sh_hist[i] = 0u;
+    __syncthreads();
+    const int64_t nc_rounded = (int64_t(ncand) + 31) / 32 * 32;
+    for (int64_t j = tid0; j < nc_rounded; j += stride) {
+      const uint32_t b = j < ncand ? cand_bits[j] : 0xffffffffu;
+      hist_add(sh_hist, (b >> 9) & 0x7ffu, b != 0xffffffffu && (b >> 20) == bin0);
     }
-  };
-
-  // ---- phase 2: bits [19:9] ----
-  for (int i = threadIdx.x; i < kBins1; i += kThreads) sh_hist[i] = 0u;
-  __syncthreads();
-  for (int64_t q = tid0; q < groups_rounded; q += stride) {
-    uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-    if (q < groups) load_bits(q, b);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) hist_add(sh_hist, (b[k] >> 9) & 0x7ffu, b[k] != 0xffffffffu && (b[k] >> 20) == bin0);
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < kBins1; i += kThreads)
-    if (sh_hist[i]) atomicAdd(&scratch[kHist1 + i], sh_hist[i]);
-  grid.sync();
-  select_bin(scratch + kHist1, kBins1, want, bin1, sh_sel);
-
-  // ---- phase 3: bits [8:0] ----
-  for (int i = threadIdx.x; i < kBins2; i += kThreads) sh_hist[i] = 0u;
-  __syncthreads();
-  const uint32_t prefix = (bin0 << 11) | bin1;
-  for (int64_t q = tid0; q < groups_rounded; q += stride) {
-    uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-    if (q < groups) load_bits(q, b);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) hist_add(sh_hist, b[k] & 0x1ffu, b[k] != 0xffffffffu && (b[k] >> 9) == prefix);
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < kBins2; i += kThreads)
-    if (sh_hist[i]) atomicAdd(&scratch[kHist2 + i], sh_hist[i]);
-  grid.sync();
-  select_bin(scratch + kHist2, kBins2, want, bin2, sh_sel);
-  const uint32_t tau = (prefix << 9) | bin2;  // bit pattern of the k-th largest |v|
-
-  // ---- phase 4: compaction + masking + clear the dense bucket ----
-  for (int64_t q = tid0; q < groups_rounded; q += stride) {
-    uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-    if (q < groups) {
-      load_bits(q, b);
-      if (q < n4) {
-        st4_zero<T>(grad, q * 4);
-      } else {
-        for (int k = 0; k < 4; ++k)
-          if (q * 4 + k < n) grad[q * 4 + k] = dev::Vec16<T>::from_float(0.0f);
-      }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins1; i += kThreads)
+      if (sh_hist[i]) atomicAdd(&scratch[kHist1 + i], sh_hist[i]);
+    grid.sync();
+    select_bin(scratch + kHist1, kBins1, want, bin1, sh_sel);
+    for (int i = threadIdx.x; i < kBins2; i += kThreads) sh_hist[i] = 0u;
+    __syncthreads();
+    const uint32_t prefix = (bin0 << 11) | bin1;
+    for (int64_t j = tid0; j < nc_rounded; j += stride) {
+      const uint32_t b = j < ncand ? cand_bits[j] : 0xffffffffu;
+      hist_add(sh_hist, b & 0x1ffu, b != 0xffffffffu && (b >> 9) == prefix);
     }
-    const int lane = threadIdx.x & 31;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const bool sel = b[k] != 0xffffffffu && b[k] >= tau && (p.k > 0) && b[k] != 0u;
-      // warp-aggregated append
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins2; i += kThreads)
+      if (sh_hist[i]) atomicAdd(&scratch[kHist2 + i], sh_hist[i]);
+    grid.sync();
+    select_bin(scratch + kHist2, kBins2, want, bin2, sh_sel);
+    tau = (prefix << 9) | bin2;
+    for (int64_t j = tid0; j < nc_rounded; j += stride) {
+      const uint32_t b = j < ncand ? cand_bits[j] : 0xffffffffu;
+      const bool sel = b != 0xffffffffu && b >= tau && (p.k > 0) && b != 0u;
       const uint32_t mask = __ballot_sync(0xffffffffu, sel);
       if (mask) {
+        const int lane = threadIdx.x & 31;
         uint32_t base = 0;
         if (lane == __ffs(mask) - 1) base = atomicAdd(&scratch[kCursor], uint32_t(__popc(mask)));
         base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
         if (sel) {
           const uint32_t pos = base + uint32_t(__popc(mask & ((1u << lane) - 1u)));
           if (pos < cap) {
-            const int64_t i = q * 4 + k;
-            my_idx[pos] = uint32_t(i);
+            const uint32_t i = cand_idx[j];
+            my_idx[pos] = i;
             my_val[pos] = v[i];
             v[i] = 0.0f;
             u[i] = 0.0f;
+          }
+        }
+      }
+    }
+  } else {
+    // bit patterns of |v| for one group (0 beyond the end: never selected, never counted)
+    auto load_bits = [&](int64_t q, uint32_t (&b)[4]) {
+      if (q < n4) {
+        const uint4 a = *reinterpret_cast<const uint4*>(v + q * 4);
+        b[0] = a.x & 0x7fffffffu; b[1] = a.y & 0x7fffffffu; b[2] = a.z & 0x7fffffffu; b[3] = a.w & 0x7fffffffu;
+      } else {
+  #pragma unroll
+        for (int k = 0; k < 4; ++k) b[k] = (q * 4 + k < n) ? (__float_as_uint(v[q * 4 + k]) & 0x7fffffffu) : 0xffffffffu;
+      }
+    };
+
+    // ---- phase 2: bits [19:9] ----
+    for (int i = threadIdx.x; i < kBins1; i += kThreads) sh_hist[i] = 0u;
+    __syncthreads();
+    for (int64_t q = tid0; q < groups_rounded; q += stride) {
+      uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+      if (q < groups) load_bits(q, b);
+  #pragma unroll
+      for (int k = 0; k < 4; ++k) hist_add(sh_hist, (b[k] >> 9) & 0x7ffu, b[k] != 0xffffffffu && (b[k] >> 20) == bin0);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins1; i += kThreads)
+      if (sh_hist[i]) atomicAdd(&scratch[kHist1 + i], sh_hist[i]);
+    grid.sync();
+    select_bin(scratch + kHist1, kBins1, want, bin1, sh_sel);
+
+    // ---- phase 3: bits [8:0] ----
+    for (int i = threadIdx.x; i < kBins2; i += kThreads) sh_hist[i] = 0u;
+    __syncthreads();
+    const uint32_t prefix = (bin0 << 11) | bin1;
+    for (int64_t q = tid0; q < groups_rounded; q += stride) {
+      uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+      if (q < groups) load_bits(q, b);
+  #pragma unroll
+      for (int k = 0; k < 4; ++k) hist_add(sh_hist, b[k] & 0x1ffu, b[k] != 0xffffffffu && (b[k] >> 9) == prefix);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins2; i += kThreads)
+      if (sh_hist[i]) atomicAdd(&scratch[kHist2 + i], sh_hist[i]);
+    grid.sync();
+    select_bin(scratch + kHist2, kBins2, want, bin2, sh_sel);
+    tau = (prefix << 9) | bin2;  // bit pattern of the k-th largest |v|
+
+    // ---- phase 4: compaction + masking ----
+    for (int64_t q = tid0; q < groups_rounded; q += stride) {
+      uint32_t b[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+      if (q < groups) load_bits(q, b);
+      const int lane = threadIdx.x & 31;
+  #pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const bool sel = b[k] != 0xffffffffu && b[k] >= tau && (p.k > 0) && b[k] != 0u;
+        // warp-aggregated append
+        const uint32_t mask = __ballot_sync(0xffffffffu, sel);
+        if (mask) {
+          uint32_t base = 0;
+          if (lane == __ffs(mask) - 1) base = atomicAdd(&scratch[kCursor], uint32_t(__popc(mask)));
+          base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
+          if (sel) {
+            const uint32_t pos = base + uint32_t(__popc(mask & ((1u << lane) - 1u)));
+            if (pos < cap) {
+              const int64_t i = q * 4 + k;
+              my_idx[pos] = uint32_t(i);
+              my_val[pos] = v[i];
+              v[i] = 0.0f;
+              u[i] = 0.0f;
+            }
           }
         }
       }
@@ -312,7 +398,7 @@ extern "C" int nangila_dgc_launch(const NangilaDgcParams* p, cudaStream_t stream
   if (p == nullptr || p->n <= 0 || p->n > 0x7fffffffll || p->world < 1 || p->world > NANGILA_MAX_RANKS ||
       p->nvr < 1 || p->nvr > NANGILA_MAX_VRANKS || p->rank0 < 0 || p->rank0 + p->nvr > p->world ||
       (p->nvr > 1 && p->nvr != p->world) || p->epoch == 0 || p->grid_x < 1 || p->capacity == 0 ||
-      p->capacity % 4 != 0 || p->k > p->capacity || !(p->momentum >= 0.0f && p->momentum < 1.0f))
+      p->capacity % 4 != 0 || p->k > p->capacity || (p->cand_capacity != 0 && p->cand_capacity < p->k) || !(p->momentum >= 0.0f && p->momentum < 1.0f))
     return int(cudaErrorInvalidValue);
   const void* fn;
   switch (p->grad_dtype) {

@@ -123,7 +123,7 @@ typedef struct NangilaDgcParams {
   void* grad[NANGILA_MAX_VRANKS];       /* in: gradient; out: dense mean of the selected entries */
   float* u[NANGILA_MAX_VRANKS];         /* momentum-corrected velocity, n floats */
   float* v[NANGILA_MAX_VRANKS];         /* accumulated (unsent) gradient, n floats */
-  uint32_t* scratch[NANGILA_MAX_VRANKS];/* nangila_dgc_scratch_words() words, any content */
+  uint32_t* scratch[NANGILA_MAX_VRANKS];/* nangila_dgc_scratch_words() + 2 * cand_capacity words, any content */
   uint32_t* status[NANGILA_MAX_VRANKS]; /* 8 words, zero before launch */
   uint32_t* out_count[NANGILA_MAX_VRANKS]; /* [0] entries sent by this rank, [1] threshold bit pattern */
   uint8_t* region[NANGILA_MAX_RANKS];
@@ -132,6 +132,8 @@ typedef struct NangilaDgcParams {
   int32_t world, rank0, nvr, grad_dtype;
   uint32_t k;                           /* entries to keep: ceil(n (1 - sparsity)) */
   uint32_t capacity;                    /* list capacity per rank, multiple of 4, >= k */
+  uint32_t cand_capacity;               /* candidate list entries behind the scratch words (0: always take the
+                                           dense selection passes) */
   uint32_t epoch;
   float momentum;                       /* momentum-correction factor m in [0, 1) */
   uint64_t timeout_ns;

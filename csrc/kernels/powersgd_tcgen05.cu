@@ -171,27 +171,68 @@ __global__ void __launch_bounds__(256) psgd_prep_kernel(const T* __restrict__ gr
   for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < numel; i += int64_t(gridDim.x) * 256)
     mef[i] = __float2bfloat16_rn(dev::sanitize(dev::Vec16<T>::to_float(grad[i])) + __bfloat162float(ef[i]));
 }
-template <typename T>
+// grad = P Q^T (rank r), ef = (m + ef) - grad. P and Q are the averaged factors, COLUMN-major
+// (P[k * m + row], Q[k * n + col]). Each thread owns 8 consecutive columns and walks down the rows of
+// its CTA's share; for r <= 4 its 8 x r slice of Q stays in registers, so per row it reads 16 bytes of
+// m + ef and r broadcast values of P and writes the 8 results twice (bucket, error memory).
+template <typename T, int RQ>
 __global__ void __launch_bounds__(256) psgd_reconstruct_kernel(T* __restrict__ grad, __nv_bfloat16* __restrict__ ef,
                                                               const __nv_bfloat16* __restrict__ mef,
                                                               const float* __restrict__ P, const float* __restrict__ Q,
                                                               int m, int n, int r) {
-  const int64_t numel = int64_t(m) * n;
-  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < numel; i += int64_t(gridDim.x) * 256) {
-    const int row = int(i / n), col = int(i % n);
-    float acc = 0.0f;
-    for (int k = 0; k < r; ++k) acc = __fmaf_rn(P[row * kCols + k], Q[col * kCols + k], acc);
-    const T o = dev::Vec16<T>::from_float(acc);
-    grad[i] = o;
-    ef[i] = __float2bfloat16_rn(__bfloat162float(mef[i]) - dev::Vec16<T>::to_float(o));
+  const int col = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (col >= n) return;  // n is a multiple of 8
+  float q[RQ > 0 ? RQ : 1][8];
+  if constexpr (RQ > 0) {
+#pragma unroll
+    for (int k = 0; k < RQ; ++k) {
+      if (k < r) dev::Vec8<float>::load(Q + int64_t(k) * n + col, q[k]);
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[k][j] = 0.0f;
+      }
+    }
+  }
+  for (int row = blockIdx.y; row < m; row += gridDim.y) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    if constexpr (RQ > 0) {
+#pragma unroll
+      for (int k = 0; k < RQ; ++k) {
+        const float pk = k < r ? P[int64_t(k) * m + row] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(pk, q[k][j], acc[j]);
+      }
+    } else {
+      for (int k = 0; k < r; ++k) {
+        const float pk = P[int64_t(k) * m + row];
+        float qk[8];
+        dev::Vec8<float>::load(Q + int64_t(k) * n + col, qk);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(pk, qk[j], acc[j]);
+      }
+    }
+    const int64_t i = int64_t(row) * n + col;
+    float x[8], o[8];
+    dev::Vec8<__nv_bfloat16>::load(mef + i, x);
+    // the error memory must see the value as the bucket will hold it (rounded to the bucket's type)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = dev::Vec16<T>::to_float(dev::Vec16<T>::from_float(acc[j]));
+    dev::Vec8<T>::store(grad + i, o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] -= o[j];
+    dev::Vec8<__nv_bfloat16>::store(ef + i, x);
   }
 }
 
 // ---- cross-rank mean of a (rows x 16) factor + Gram-Schmidt ----------------------------------------------
-// One CTA per rank. local: this rank's factor (rows x 16 fp32, columns >= r ignored).
-// mean_out (rows x 16 fp32): the averaged factor, orthonormalised in place when orth_mean != 0.
-// t_out (16 x rows bf16): the orthonormalised averaged factor, transposed (rows r..15 zero): the B
-// operand of the next GEMM.
+// One CTA per rank. local: this rank's factor as the GEMM leaves it (rows x 16 fp32, row-major, columns
+// >= r ignored). Everything after that is COLUMN-major (element (row, c) at [c * rows + row]) so that
+// every pass below is a coalesced stream:
+// mean_out (16 x rows fp32): the averaged factor, orthonormalised in place when orth_mean != 0;
+// t_out (16 x rows bf16): the orthonormalised averaged factor (rows r..15 zero): the B operand of the
+// next GEMM.
 __global__ void __launch_bounds__(1024) psgd_exchange_kernel(const __grid_constant__ NangilaPsgdExchangeParams p) {
   const int vr = blockIdx.x;
   const int me = p.rank0 + vr;
@@ -202,14 +243,15 @@ __global__ void __launch_bounds__(1024) psgd_exchange_kernel(const __grid_consta
   uint32_t* status = p.status[vr];
   const float* local = p.local[vr];
   float* mean = p.mean_out[vr];
+  const int used = rows * r;
   __shared__ float red[32];
   __shared__ float bc;
   __shared__ int s_ok;
 
-  // 1. store my factor (r columns) into every rank's slot [me]
+  // 1. store my factor (r columns, column-major) into every rank's slot [me]
   for (int d = 0; d < W; ++d) {
     float* dst = reinterpret_cast<float*>(p.region[(me + d) % W] + base + uint64_t(me) * slot_bytes);
-    for (int i = tid; i < rows * r; i += nthr) dst[i] = local[(i / r) * kCols + (i % r)];
+    for (int i = tid; i < used; i += nthr) dst[i] = local[(i % rows) * kCols + (i / rows)];
   }
   __syncthreads();
   if (tid < W) {
@@ -228,18 +270,18 @@ __global__ void __launch_bounds__(1024) psgd_exchange_kernel(const __grid_consta
   if (!s_ok) return;
   // 3. mean in rank order (identical on every rank)
   const float inv_w = 1.0f / float(W);
-  for (int i = tid; i < rows * r; i += nthr) {
+  for (int i = tid; i < used; i += nthr) {
     float acc = 0.0f;
     for (int src = 0; src < W; ++src)
       acc += reinterpret_cast<const float*>(p.region[me] + base + uint64_t(src) * slot_bytes)[i];
-    mean[(i / r) * kCols + (i % r)] = acc * inv_w;
+    mean[i] = acc * inv_w;
   }
-  for (int i = tid; i < rows * (kCols - r); i += nthr) mean[(i / (kCols - r)) * kCols + r + (i % (kCols - r))] = 0.0f;
+  for (int i = used + tid; i < rows * kCols; i += nthr) mean[i] = 0.0f;
   __syncthreads();
   // 4. Gram-Schmidt on the columns, into `work` (= mean when orth_mean, else the scratch copy)
   float* work = p.orth_mean ? mean : p.scratch[vr];
   if (!p.orth_mean) {
-    for (int i = tid; i < rows * kCols; i += nthr) work[i] = mean[i];
+    for (int i = tid; i < used; i += nthr) work[i] = mean[i];
     __syncthreads();
   }
   auto block_sum = [&](float v) -> float {
@@ -259,28 +301,27 @@ __global__ void __launch_bounds__(1024) psgd_exchange_kernel(const __grid_consta
     return out;
   };
   for (int c = 0; c < r; ++c) {
+    float* wc = work + int64_t(c) * rows;
     for (int j = 0; j < c; ++j) {
+      const float* wj = work + int64_t(j) * rows;
       float part = 0.0f;
-      for (int i = tid; i < rows; i += nthr) part = __fmaf_rn(work[i * kCols + c], work[i * kCols + j], part);
+      for (int i = tid; i < rows; i += nthr) part = __fmaf_rn(wc[i], wj[i], part);
       const float dot = block_sum(part);
-      for (int i = tid; i < rows; i += nthr) work[i * kCols + c] = __fmaf_rn(-dot, work[i * kCols + j], work[i * kCols + c]);
+      for (int i = tid; i < rows; i += nthr) wc[i] = __fmaf_rn(-dot, wj[i], wc[i]);
       __syncthreads();
     }
     float part = 0.0f;
-    for (int i = tid; i < rows; i += nthr) part = __fmaf_rn(work[i * kCols + c], work[i * kCols + c], part);
+    for (int i = tid; i < rows; i += nthr) part = __fmaf_rn(wc[i], wc[i], part);
     const float norm = sqrtf(block_sum(part));
     if (norm > 1e-10f) {
       const float inv = 1.0f / norm;
-      for (int i = tid; i < rows; i += nthr) work[i * kCols + c] *= inv;
+      for (int i = tid; i < rows; i += nthr) wc[i] *= inv;
     }
     __syncthreads();
   }
-  // 5. transposed bf16 copy for the next GEMM's B operand
+  // 5. bf16 copy for the next GEMM's B operand (same layout)
   __nv_bfloat16* t_out = static_cast<__nv_bfloat16*>(p.t_out[vr]);
-  for (int i = tid; i < rows * kCols; i += nthr) {
-    const int c = i / rows, row = i % rows;
-    t_out[i] = __float2bfloat16_rn(c < r ? work[row * kCols + c] : 0.0f);
-  }
+  for (int i = tid; i < rows * kCols; i += nthr) t_out[i] = __float2bfloat16_rn(i < used ? work[i] : 0.0f);
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -385,16 +426,20 @@ extern "C" int nangila_psgd_reconstruct(void* grad, int32_t dtype, void* ef, con
                                         const float* Q, int32_t m, int32_t n, int32_t r, cudaStream_t stream) {
   using namespace nangila;
   if (!grad || !ef || !mef || !P || !Q || m <= 0 || n <= 0 || r <= 0 || r > 16) return int(cudaErrorInvalidValue);
-  const int64_t numel = int64_t(m) * n;
-  const int blocks = int(std::min<int64_t>((numel + 255) / 256, 148 * 8));
+  if (n % 8 != 0) return int(cudaErrorInvalidValue);
+  const unsigned gx = unsigned((n / 8 + 255) / 256);
+  const unsigned gy = unsigned(std::max<int64_t>(1, std::min<int64_t>(m, (148 * 8 + gx - 1) / gx)));
+  const dim3 grid{gx, gy};
   auto* e = static_cast<__nv_bfloat16*>(ef);
   auto* f = static_cast<const __nv_bfloat16*>(mef);
+#define NANGILA_RECON(T, RQ) psgd_reconstruct_kernel<T, RQ><<<grid, 256, 0, stream>>>(static_cast<T*>(grad), e, f, P, Q, m, n, r)
   switch (dtype) {
-    case NANGILA_F32: psgd_reconstruct_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<float*>(grad), e, f, P, Q, m, n, r); break;
-    case NANGILA_BF16: psgd_reconstruct_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(grad), e, f, P, Q, m, n, r); break;
-    case NANGILA_F16: psgd_reconstruct_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<__half*>(grad), e, f, P, Q, m, n, r); break;
+    case NANGILA_F32: if (r <= 4) NANGILA_RECON(float, 4); else NANGILA_RECON(float, 0); break;
+    case NANGILA_BF16: if (r <= 4) NANGILA_RECON(__nv_bfloat16, 4); else NANGILA_RECON(__nv_bfloat16, 0); break;
+    case NANGILA_F16: if (r <= 4) NANGILA_RECON(__half, 4); else NANGILA_RECON(__half, 0); break;
     default: return int(cudaErrorInvalidValue);
   }
+#undef NANGILA_RECON
   return int(cudaGetLastError());
 }
 
