@@ -293,23 +293,36 @@ void ag_launch(const std::vector<at::Tensor>& input, const std::vector<at::Tenso
 // ---- PowerSGD (tcgen05) ----------------------------------------------------------------------------------
 // out (rows x 16 fp32) = M * Bt^T or M^T * Bt^T; zero-fills `out` first (the kernel may split K).
 void psgd_gemm(const at::Tensor& M, const at::Tensor& Bt, bool transposed, at::Tensor out, at::Tensor status,
-               double timeout_s) {
+               double timeout_s, bool zero_out) {
   TORCH_CHECK(M.is_cuda() && M.dim() == 2 && M.scalar_type() == at::kBFloat16 && M.is_contiguous(), "nangila: M must be a contiguous bf16 matrix");
   const int64_t m = M.size(0), n = M.size(1);
   const int64_t k = transposed ? m : n, rows = transposed ? n : m;
   TORCH_CHECK(Bt.scalar_type() == at::kBFloat16 && Bt.is_contiguous() && Bt.numel() == 16 * k, "nangila: Bt must be bf16[16, K]");
   TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == rows * 16, "nangila: out must be fp32[rows, 16]");
   c10::cuda::CUDAGuard guard(M.device());
-  out.zero_();
+  if (zero_out) out.zero_();  // split-K partial sums are added with atomics
   check_launch(nangila_psgd_gemm(M.data_ptr(), int32_t(m), int32_t(n), Bt.data_ptr(), transposed ? 1 : 0, out.data_ptr<float>(),
                                  reinterpret_cast<uint32_t*>(status.data_ptr<int32_t>()), uint64_t(timeout_s * 1e9),
                                  at::cuda::getCurrentCUDAStream()), "psgd_gemm");
 }
-void psgd_prep(const at::Tensor& grad, const at::Tensor& ef, at::Tensor mef) {
+void psgd_prep(const at::Tensor& grad, const at::Tensor& ef, at::Tensor mef, c10::optional<at::Tensor> clear0,
+               c10::optional<at::Tensor> clear1) {
   TORCH_CHECK(grad.is_cuda() && grad.is_contiguous() && ef.scalar_type() == at::kBFloat16 && mef.scalar_type() == at::kBFloat16 &&
                   ef.numel() == grad.numel() && mef.numel() == grad.numel(), "nangila: psgd_prep shapes");
   c10::cuda::CUDAGuard guard(grad.device());
-  check_launch(nangila_psgd_prep(grad.data_ptr(), dtype_code(grad), ef.data_ptr(), mef.data_ptr(), grad.numel(),
+  float *z0 = nullptr, *z1 = nullptr;
+  int64_t n0 = 0, n1 = 0;
+  if (clear0.has_value()) {
+    TORCH_CHECK(clear0->scalar_type() == at::kFloat && clear0->is_contiguous(), "nangila: clear0 must be fp32");
+    z0 = clear0->data_ptr<float>();
+    n0 = clear0->numel();
+  }
+  if (clear1.has_value()) {
+    TORCH_CHECK(clear1->scalar_type() == at::kFloat && clear1->is_contiguous(), "nangila: clear1 must be fp32");
+    z1 = clear1->data_ptr<float>();
+    n1 = clear1->numel();
+  }
+  check_launch(nangila_psgd_prep(grad.data_ptr(), dtype_code(grad), ef.data_ptr(), mef.data_ptr(), grad.numel(), z0, n0, z1, n1,
                                  at::cuda::getCurrentCUDAStream()), "psgd_prep");
 }
 void psgd_reconstruct(at::Tensor grad, at::Tensor ef, const at::Tensor& mef, const at::Tensor& P, const at::Tensor& Q,
@@ -369,8 +382,10 @@ void register_more(py::module_& m) {
         py::arg("out_count"), py::arg("region_ptrs"), py::arg("recv_off"), py::arg("flag_off"), py::arg("rank0"),
         py::arg("k"), py::arg("capacity"), py::arg("epoch"), py::arg("momentum"), py::arg("timeout_s"),
         py::arg("grid_x"));
-  m.def("psgd_gemm", &psgd_gemm);
-  m.def("psgd_prep", &psgd_prep);
+  m.def("psgd_gemm", &psgd_gemm, py::arg("M"), py::arg("Bt"), py::arg("transposed"), py::arg("out"), py::arg("status"),
+        py::arg("timeout_s"), py::arg("zero_out") = true);
+  m.def("psgd_prep", &psgd_prep, py::arg("grad"), py::arg("ef"), py::arg("mef"), py::arg("clear0") = py::none(),
+        py::arg("clear1") = py::none());
   m.def("psgd_reconstruct", &psgd_reconstruct);
   m.def("psgd_exchange_layout", &psgd_exchange_layout);
   m.def("psgd_exchange", &psgd_exchange);

@@ -96,7 +96,9 @@ int nangila_ag_launch(const NangilaAgParams* p, cudaStream_t stream);
  * (transposed = 1, rows = n). M: m x n bf16 row-major, m and n multiples of 8. Bt: 16 x K bf16. */
 int nangila_psgd_gemm(const void* M, int32_t m, int32_t n, const void* Bt, int32_t transposed, float* out,
                       uint32_t* status, uint64_t timeout_ns, cudaStream_t stream);
-int nangila_psgd_prep(const void* grad, int32_t dtype, const void* ef, void* mef, int64_t numel, cudaStream_t stream);
+/* mef = grad + ef; also clears z0[0..n0) and z1[0..n1) (the projections' accumulators; either may be NULL / 0) */
+int nangila_psgd_prep(const void* grad, int32_t dtype, const void* ef, void* mef, int64_t numel, float* z0, int64_t n0,
+                      float* z1, int64_t n1, cudaStream_t stream);
 int nangila_psgd_reconstruct(void* grad, int32_t dtype, void* ef, const void* mef, const float* P, const float* Q,
                              int32_t m, int32_t n, int32_t r, cudaStream_t stream);
 typedef struct NangilaPsgdExchangeParams {

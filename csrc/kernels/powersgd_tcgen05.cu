@@ -167,9 +167,15 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ---- prep / reconstruct (element-wise) -----------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) psgd_prep_kernel(const T* __restrict__ grad, const __nv_bfloat16* __restrict__ ef,
-                                                       __nv_bfloat16* __restrict__ mef, int64_t numel) {
-  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < numel; i += int64_t(gridDim.x) * 256)
+                                                       __nv_bfloat16* __restrict__ mef, int64_t numel,
+                                                       float* __restrict__ z0, int64_t n0, float* __restrict__ z1,
+                                                       int64_t n1) {
+  const int64_t t0 = int64_t(blockIdx.x) * 256 + threadIdx.x, stride = int64_t(gridDim.x) * 256;
+  for (int64_t i = t0; i < numel; i += stride)
     mef[i] = __float2bfloat16_rn(dev::sanitize(dev::Vec16<T>::to_float(grad[i])) + __bfloat162float(ef[i]));
+  // the two projections accumulate into these with atomics (split K): clear them here, not in launches of their own
+  for (int64_t i = t0; i < n0; i += stride) z0[i] = 0.0f;
+  for (int64_t i = t0; i < n1; i += stride) z1[i] = 0.0f;
 }
 // grad = P Q^T (rank r), ef = (m + ef) - grad. P and Q are the averaged factors, COLUMN-major
 // (P[k * m + row], Q[k * n + col]). Each thread owns 8 consecutive columns and walks down the rows of
@@ -406,7 +412,8 @@ extern "C" int nangila_psgd_gemm(const void* M, int32_t m, int32_t n, const void
   return int(e);
 }
 
-extern "C" int nangila_psgd_prep(const void* grad, int32_t dtype, const void* ef, void* mef, int64_t numel,
+extern "C" int nangila_psgd_prep(const void* grad, int32_t dtype, const void* ef, void* mef, int64_t numel, float* z0,
+                                 int64_t n0, float* z1, int64_t n1,
                                  cudaStream_t stream) {
   using namespace nangila;
   if (!grad || !ef || !mef || numel <= 0) return int(cudaErrorInvalidValue);
@@ -414,9 +421,9 @@ extern "C" int nangila_psgd_prep(const void* grad, int32_t dtype, const void* ef
   auto* e = static_cast<const __nv_bfloat16*>(ef);
   auto* o = static_cast<__nv_bfloat16*>(mef);
   switch (dtype) {
-    case NANGILA_F32: psgd_prep_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(grad), e, o, numel); break;
-    case NANGILA_BF16: psgd_prep_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(grad), e, o, numel); break;
-    case NANGILA_F16: psgd_prep_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(grad), e, o, numel); break;
+    case NANGILA_F32: psgd_prep_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(grad), e, o, numel, z0, n0, z1, n1); break;
+    case NANGILA_BF16: psgd_prep_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(grad), e, o, numel, z0, n0, z1, n1); break;
+    case NANGILA_F16: psgd_prep_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(grad), e, o, numel, z0, n0, z1, n1); break;
     default: return int(cudaErrorInvalidValue);
   }
   return int(cudaGetLastError());

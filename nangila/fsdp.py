@@ -78,5 +78,12 @@ def nangila_fsdp_hook(state: NangilaFSDPState, grad: torch.Tensor, *args) -> Non
         if state.sync_mode == 1 or (state.sync_mode == 2 and state._calls % 100 == 0):
             rs.check_status()
     else:
-        dist.reduce_scatter_tensor(output, grad, group=state.process_group)
-        output.div_(world)
+        try:
+            dist.reduce_scatter_tensor(output, grad, group=state.process_group)
+            output.div_(world)
+        except (RuntimeError, NotImplementedError):
+            # backends without reduce-scatter (gloo): all-reduce and keep this rank's shard
+            full = grad.detach().clone()
+            dist.all_reduce(full, group=state.process_group)
+            shard = output.numel()
+            output.copy_(full.reshape(-1)[state.rank * shard:(state.rank + 1) * shard].view_as(output)).div_(world)

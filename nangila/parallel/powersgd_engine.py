@@ -119,12 +119,12 @@ class PowerSGDEngine:
         rank0 = 0 if self.loopback else self.rank
         flat = [g.reshape(m, n) for g in grads]
         for v in range(self.nvr):
-            G.psgd_prep(flat[v], st.ef[v], st.mef[v])
-            G.psgd_gemm(st.mef[v], st.qt[v], False, st.p_local[v], self.status[v], self.timeout_s)
+            G.psgd_prep(flat[v], st.ef[v], st.mef[v], st.p_local[v], st.q_local[v])  # also clears both accumulators
+            G.psgd_gemm(st.mef[v], st.qt[v], False, st.p_local[v], self.status[v], self.timeout_s, False)
         G.psgd_exchange(st.p_local, st.p_mean, [s[:m] for s in st.scratch], st.pt, self.status, st.region_p.ptrs,
                         st.lay_p[0], st.lay_p[1], m, st.r, rank0, True, st.epoch, self.timeout_s)
         for v in range(self.nvr):
-            G.psgd_gemm(st.mef[v], st.pt[v], True, st.q_local[v], self.status[v], self.timeout_s)
+            G.psgd_gemm(st.mef[v], st.pt[v], True, st.q_local[v], self.status[v], self.timeout_s, False)
         G.psgd_exchange(st.q_local, st.q_mean, [s[:n] for s in st.scratch], st.qt, self.status, st.region_q.ptrs,
                         st.lay_q[0], st.lay_q[1], n, st.r, rank0, False, st.epoch, self.timeout_s)
         for v in range(self.nvr):
