@@ -116,14 +116,15 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
   const int64_t groups_rounded = (groups + 31) / 32 * 32;
 
   // Candidates. Between two calls on the same bucket the threshold moves little, so phase 1 also
-  // collects every entry with |v| >= 0.9 * (previous threshold) into a short list. If that list holds
+  // collects every entry with |v| >= 0.96 * (previous threshold) into a short list (unsent entries
+  // pile up just below the threshold, so the band has to be narrow). If that list holds
   // at least k entries and did not overflow, the k largest entries of the bucket are all in it and the
   // three selection passes and the compaction run over the list (a few thousand entries) instead of
   // the dense state; otherwise (first call, threshold moved a lot) the dense passes run as before.
   const uint32_t tau_prev = p.out_count[vr][1];
   const uint32_t cand_cap = p.cand_capacity;
   const uint32_t cand_thr = (cand_cap > 0 && tau_prev > 0 && tau_prev < 0x7f800000u)
-                                ? __float_as_uint(__uint_as_float(tau_prev) * 0.9f)
+                                ? __float_as_uint(__uint_as_float(tau_prev) * 0.96f)
                                 : 0xffffffffu;  // nothing qualifies
   uint32_t* cand_idx = scratch + kScratchWords;
   uint32_t* cand_bits = cand_idx + cand_cap;
@@ -330,6 +331,8 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     *reinterpret_cast<uint32_t*>(myslot) = count;
     p.out_count[vr][0] = count;
     p.out_count[vr][1] = tau;
+    scratch[kCursor + 2] = from_list ? 1u : 0u;  // which selection path ran (telemetry)
+    scratch[kCursor + 3] = ncand;
   }
 
   // ---- phase 5: copy the list into every other rank's slot for this rank, release flags ----

@@ -19,6 +19,7 @@
 // (nangila-core/src/power_sgd.rs:46-193: ndarray GEMMs on the host, per-rank factors shipped and W
 // dense reconstructions averaged). Here P and Q' are averaged across ranks (standard PowerSGD).
 #include <algorithm>
+#include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -31,6 +32,7 @@
 
 namespace nangila {
 namespace {
+namespace cg = cooperative_groups;
 
 using namespace sm100;
 using namespace comm;
@@ -232,39 +234,61 @@ __global__ void __launch_bounds__(256) psgd_reconstruct_kernel(T* __restrict__ g
   }
 }
 
-// ---- cross-rank mean of a (rows x 16) factor + Gram-Schmidt ----------------------------------------------
-// One CTA per rank. local: this rank's factor as the GEMM leaves it (rows x 16 fp32, row-major, columns
-// >= r ignored). Everything after that is COLUMN-major (element (row, c) at [c * rows + row]) so that
-// every pass below is a coalesced stream:
+// ---- cross-rank mean of a (rows x 16) factor + orthonormalisation ----------------------------------------
+// One thread-block CLUSTER of kXCtas CTAs per rank; every CTA owns a slice of the rows. local: this
+// rank's factor as the GEMM leaves it (rows x 16 fp32, row-major, columns >= r ignored). Everything after
+// that is COLUMN-major (element (row, c) at [c * rows + row]) so that every pass is a coalesced stream:
 // mean_out (16 x rows fp32): the averaged factor, orthonormalised in place when orth_mean != 0;
 // t_out (16 x rows bf16): the orthonormalised averaged factor (rows r..15 zero): the B operand of the
 // next GEMM.
-__global__ void __launch_bounds__(1024) psgd_exchange_kernel(const __grid_constant__ NangilaPsgdExchangeParams p) {
-  const int vr = blockIdx.x;
+// Orthonormalisation is Gram-Schmidt through the Gram matrix (Q = W R^-1 with R^T R = W^T W, the
+// Cholesky factor), applied twice ("CholeskyQR2"): each round is one pass that accumulates the r x r Gram
+// matrix, a cluster-wide sum over distributed shared memory in a fixed order (every CTA gets the same
+// bits), a 16 x 16 factorisation done redundantly by every CTA, and one pass that applies R^-1. A column
+// whose pivot vanishes (rank-deficient factor) becomes zero, as a column of norm 0 stays in classical
+// Gram-Schmidt. The second round removes the orthogonality loss of the first.
+constexpr int kXCtas = 8;
+constexpr int kXThreads = 512;
+constexpr int kPairs = kCols * (kCols + 1) / 2;
+
+// RMAX: compile-time bound on the rank (4 keeps the 10 pair sums and the row in registers).
+template <int RMAX>
+__global__ void __launch_bounds__(kXThreads) psgd_exchange_kernel(const __grid_constant__ NangilaPsgdExchangeParams p) {
+  constexpr int kAcc = RMAX * (RMAX + 1) / 2;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int g = int(cluster.block_rank());
+  const int vr = blockIdx.x / kXCtas;
   const int me = p.rank0 + vr;
   const int W = p.world, rows = p.rows, r = p.rank;
-  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int tid = threadIdx.x;
   const uint64_t slot_bytes = (uint64_t(rows) * r * 4 + 255) & ~uint64_t(255);
   const uint64_t base = p.recv_off + uint64_t(p.epoch & 1u) * W * slot_bytes;  // two slot sets, by launch parity
   uint32_t* status = p.status[vr];
   const float* local = p.local[vr];
   float* mean = p.mean_out[vr];
-  const int used = rows * r;
-  __shared__ float red[32];
-  __shared__ float bc;
+  // this CTA's rows
+  const int per = (rows + kXCtas - 1) / kXCtas;
+  const int r0 = min(rows, g * per), r1 = min(rows, r0 + per);
+  __shared__ float s_warp[kXThreads / 32][kPairs];  // per-warp partial sums (summed in warp order: no float atomics)
+  __shared__ float s_part[kPairs];          // this CTA's partial Gram matrix (lower triangle, packed)
+  __shared__ float s_gram[kPairs];          // cluster-wide sum
+  __shared__ float s_rinv[kCols][kCols];    // R^-1 (upper triangular); a zero column for a vanished pivot
   __shared__ int s_ok;
 
-  // 1. store my factor (r columns, column-major) into every rank's slot [me]
+  // 1. store my rows of my factor (r columns, column-major) into every rank's slot [me]
   for (int d = 0; d < W; ++d) {
     float* dst = reinterpret_cast<float*>(p.region[(me + d) % W] + base + uint64_t(me) * slot_bytes);
-    for (int i = tid; i < used; i += nthr) dst[i] = local[(i % rows) * kCols + (i / rows)];
+    for (int c = 0; c < r; ++c)
+      for (int i = r0 + tid; i < r1; i += kXThreads) dst[int64_t(c) * rows + i] = local[int64_t(i) * kCols + c];
   }
-  __syncthreads();
-  if (tid < W) {
+  __threadfence_system();
+  cluster.sync();
+  if (g == 0 && tid < W) {
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t*>(p.region[tid] + p.flag_off) + me, p.epoch);
   }
-  // 2. wait for every rank's factor
+  // 2. wait for every rank's factor (every CTA polls for itself; on failure all of them still take part in
+  //    the cluster barriers below, doing no work)
   if (tid == 0) s_ok = 1;
   __syncthreads();
   if (tid < W) {
@@ -273,61 +297,120 @@ __global__ void __launch_bounds__(1024) psgd_exchange_kernel(const __grid_consta
       s_ok = 0;
   }
   __syncthreads();
-  if (!s_ok) return;
-  // 3. mean in rank order (identical on every rank)
-  const float inv_w = 1.0f / float(W);
-  for (int i = tid; i < used; i += nthr) {
-    float acc = 0.0f;
-    for (int src = 0; src < W; ++src)
-      acc += reinterpret_cast<const float*>(p.region[me] + base + uint64_t(src) * slot_bytes)[i];
-    mean[i] = acc * inv_w;
-  }
-  for (int i = used + tid; i < rows * kCols; i += nthr) mean[i] = 0.0f;
-  __syncthreads();
-  // 4. Gram-Schmidt on the columns, into `work` (= mean when orth_mean, else the scratch copy)
+  const bool ok = s_ok != 0;
+  // 3. mean in rank order (identical on every rank); columns >= r are zero
   float* work = p.orth_mean ? mean : p.scratch[vr];
-  if (!p.orth_mean) {
-    for (int i = tid; i < used; i += nthr) work[i] = mean[i];
-    __syncthreads();
+  if (ok) {
+    const float inv_w = 1.0f / float(W);
+    for (int c = 0; c < kCols; ++c)
+      for (int i = r0 + tid; i < r1; i += kXThreads) {
+        float acc = 0.0f;
+        if (c < r)
+          for (int src = 0; src < W; ++src)
+            acc += reinterpret_cast<const float*>(p.region[me] + base + uint64_t(src) * slot_bytes)[int64_t(c) * rows + i];
+        acc *= inv_w;
+        mean[int64_t(c) * rows + i] = acc;
+        if (!p.orth_mean && c < r) work[int64_t(c) * rows + i] = acc;
+      }
   }
-  auto block_sum = [&](float v) -> float {
+  __syncthreads();
+  // 4. two rounds of Cholesky-QR on `work`
+  for (int round = 0; round < 2; ++round) {
+    for (int i = tid; i < (kXThreads / 32) * kPairs; i += kXThreads) (&s_warp[0][0])[i] = 0.0f;
+    __syncthreads();
+    if (ok) {
+      // every thread owns whole rows: all pair products of a row come from registers
+      float acc[kAcc];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    if ((tid & 31) == 0) red[tid >> 5] = v;
-    __syncthreads();
-    if (tid < 32) {
-      float t = tid < (nthr >> 5) ? red[tid] : 0.0f;
+      for (int q = 0; q < kAcc; ++q) acc[q] = 0.0f;
+      for (int i = r0 + tid; i < r1; i += kXThreads) {
+        float w[RMAX];
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-      if (tid == 0) bc = t;
+        for (int c = 0; c < RMAX; ++c) w[c] = c < r ? work[int64_t(c) * rows + i] : 0.0f;
+        int q = 0;
+#pragma unroll
+        for (int c = 0; c < RMAX; ++c)
+#pragma unroll
+          for (int j = 0; j <= c; ++j, ++q) acc[q] = __fmaf_rn(w[c], w[j], acc[q]);
+      }
+#pragma unroll
+      for (int q = 0; q < kAcc; ++q) {
+        float v = acc[q];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if ((tid & 31) == 0) s_warp[tid >> 5][q] = v;
+      }
     }
     __syncthreads();
-    const float out = bc;
-    __syncthreads();
-    return out;
-  };
-  for (int c = 0; c < r; ++c) {
-    float* wc = work + int64_t(c) * rows;
-    for (int j = 0; j < c; ++j) {
-      const float* wj = work + int64_t(j) * rows;
-      float part = 0.0f;
-      for (int i = tid; i < rows; i += nthr) part = __fmaf_rn(wc[i], wj[i], part);
-      const float dot = block_sum(part);
-      for (int i = tid; i < rows; i += nthr) wc[i] = __fmaf_rn(-dot, wj[i], wc[i]);
-      __syncthreads();
+    for (int q = tid; q < kPairs; q += kXThreads) {
+      float v = 0.0f;
+      for (int w = 0; w < kXThreads / 32; ++w) v += s_warp[w][q];  // fixed order: the same bits on every rank
+      s_part[q] = v;
     }
-    float part = 0.0f;
-    for (int i = tid; i < rows; i += nthr) part = __fmaf_rn(wc[i], wc[i], part);
-    const float norm = sqrtf(block_sum(part));
-    if (norm > 1e-10f) {
-      const float inv = 1.0f / norm;
-      for (int i = tid; i < rows; i += nthr) wc[i] *= inv;
+    cluster.sync();  // every CTA's partial matrix is complete
+    for (int q = tid; q < kPairs; q += kXThreads) {
+      float v = 0.0f;
+      for (int b = 0; b < kXCtas; ++b) v += *cluster.map_shared_rank(&s_part[q], b);  // fixed order
+      s_gram[q] = v;
     }
     __syncthreads();
+    if (tid == 0) {
+      // Cholesky of the r x r Gram matrix: L L^T; then R^-1 = (L^T)^-1 by back substitution
+      float L[kCols][kCols];
+      bool dead[kCols];
+      for (int c = 0; c < r; ++c) {
+        for (int j = 0; j <= c; ++j) {
+          float sum = s_gram[c * (c + 1) / 2 + j];
+          for (int k = 0; k < j; ++k) sum -= L[c][k] * L[j][k];
+          if (j < c) {
+            L[c][j] = dead[j] ? 0.0f : sum / L[j][j];
+          } else {
+            const float diag = s_gram[c * (c + 1) / 2 + c];
+            dead[c] = !(sum > 1e-20f) || !(sum > 1e-7f * diag);  // pivot vanished: dependent (or zero) column
+            L[c][c] = dead[c] ? 1.0f : sqrtf(sum);
+          }
+        }
+      }
+      // X = R^-1 where R = L^T (upper triangular): X[j][c] for j <= c
+      for (int c = 0; c < kCols; ++c)
+        for (int j = 0; j < kCols; ++j) s_rinv[j][c] = 0.0f;
+      for (int c = 0; c < r; ++c) {
+        if (dead[c]) continue;  // column of zeros
+        s_rinv[c][c] = 1.0f / L[c][c];
+        for (int j = c - 1; j >= 0; --j) {
+          if (dead[j]) continue;
+          float sum = 0.0f;
+          for (int k = j + 1; k <= c; ++k) sum += L[k][j] * s_rinv[k][c];  // R[j][k] = L[k][j]
+          s_rinv[j][c] = -sum / L[j][j];
+        }
+      }
+    }
+    __syncthreads();
+    if (ok) {
+      for (int i = r0 + tid; i < r1; i += kXThreads) {
+        float w[RMAX];
+#pragma unroll
+        for (int c = 0; c < RMAX; ++c) w[c] = c < r ? work[int64_t(c) * rows + i] : 0.0f;
+#pragma unroll
+        for (int c = 0; c < RMAX; ++c) {
+          if (c < r) {
+            float o = 0.0f;
+#pragma unroll
+            for (int j = 0; j <= c; ++j) o = __fmaf_rn(w[j], s_rinv[j][c], o);
+            work[int64_t(c) * rows + i] = o;
+          }
+        }
+      }
+    }
+    cluster.sync();  // nobody reads a neighbour's s_part after this; safe to clear it in the next round
   }
   // 5. bf16 copy for the next GEMM's B operand (same layout)
-  __nv_bfloat16* t_out = static_cast<__nv_bfloat16*>(p.t_out[vr]);
-  for (int i = tid; i < rows * kCols; i += nthr) t_out[i] = __float2bfloat16_rn(i < used ? work[i] : 0.0f);
+  if (ok) {
+    __nv_bfloat16* t_out = static_cast<__nv_bfloat16*>(p.t_out[vr]);
+    for (int c = 0; c < kCols; ++c)
+      for (int i = r0 + tid; i < r1; i += kXThreads)
+        t_out[int64_t(c) * rows + i] = __float2bfloat16_rn(c < r ? work[int64_t(c) * rows + i] : 0.0f);
+  }
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -467,9 +550,24 @@ extern "C" int nangila_psgd_exchange(const NangilaPsgdExchangeParams* p, cudaStr
   if (!p || p->rows <= 0 || p->rank <= 0 || p->rank > 16 || p->world < 1 || p->world > NANGILA_MAX_RANKS || p->nvr < 1 ||
       p->nvr > NANGILA_MAX_VRANKS || (p->nvr > 1 && p->nvr != p->world) || p->epoch == 0)
     return int(cudaErrorInvalidValue);
-  dim3 grid{unsigned(p->nvr)}, block{1024};
-  void* args[] = {const_cast<NangilaPsgdExchangeParams*>(p)};
-  const void* fn = reinterpret_cast<const void*>(&psgd_exchange_kernel);
-  if (p->nvr > 1) return int(cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream));
-  return int(cudaLaunchKernel(fn, grid, block, args, 0, stream));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3{unsigned(p->nvr * kXCtas), 1u, 1u};
+  cfg.blockDim = dim3{unsigned(kXThreads), 1u, 1u};
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = kXCtas;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  // several emulated ranks in one launch wait for one another: ask for a cooperative launch so that
+  // all their clusters are resident together
+  attrs[1].id = cudaLaunchAttributeCooperative;
+  attrs[1].val.cooperative = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = p->nvr > 1 ? 2 : 1;
+  const NangilaPsgdExchangeParams params = *p;
+  cudaError_t e = p->rank <= 4 ? cudaLaunchKernelEx(&cfg, psgd_exchange_kernel<4>, params)
+                               : cudaLaunchKernelEx(&cfg, psgd_exchange_kernel<kCols>, params);
+  return int(e);
 }

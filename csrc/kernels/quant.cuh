@@ -17,8 +17,6 @@ namespace nangila {
 namespace dev {
 
 constexpr int kQuantBlock = 64;      // elements per scale
-constexpr int kElemsPerThread = 16;  // one thread quantizes 16 consecutive elements
-constexpr int kLanesPerBlock = kQuantBlock / kElemsPerThread;  // 4 lanes share one scale
 
 __host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16;
@@ -128,26 +126,6 @@ struct Vec16<__half> {
 
 // Load 16 elements starting at element `base` of a tensor of `n` elements; elements at or beyond n
 // read as 0. `p` must be 16-byte aligned and `base` a multiple of 16.
-template <typename T>
-__device__ __forceinline__ void load16_guarded(const T* p, int64_t base, int64_t n, float (&v)[16]) {
-  if (base + 16 <= n) {
-    Vec16<T>::load(p + base, v);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = (base + i < n) ? Vec16<T>::to_float(p[base + i]) : 0.0f;
-  }
-}
-template <typename T>
-__device__ __forceinline__ void store16_guarded(T* p, int64_t base, int64_t n, const float (&v)[16]) {
-  if (base + 16 <= n) {
-    Vec16<T>::store(p + base, v);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (base + i < n) p[base + i] = Vec16<T>::from_float(v[i]);
-  }
-}
-
 __device__ __forceinline__ float sanitize(float x) { return (fabsf(x) <= 3.0e38f) ? x : 0.0f; }  // NaN/Inf -> 0
 
 // bf16 bit pattern of the smallest bf16 >= s (s >= 0, finite).
@@ -158,54 +136,6 @@ __device__ __forceinline__ uint32_t bf16_ceil_bits(float s) {
 }
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
-// Quantize the 16 values of this lane. The four lanes (lane & ~3 .. lane | 3) that hold one
-// 64-element block must call this together (it shuffles). On return `e` holds the quantization error
-// e - q * scale, `packed` the 16 nibbles and `scale_bits` the block's bf16 scale.
-// `pair0` = (global element index of e[0]) / 2, the counter for the random numbers.
-__device__ __forceinline__ void quantize16(float (&e)[16], uint32_t key, uint32_t pair0, bool stochastic,
-                                           uint2& packed, uint32_t& scale_bits, float (&deq)[16]) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(e[i]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  scale_bits = bf16_ceil_bits(__fmul_rn(amax, 0.14285715f));  // amax * fl(1/7), rounded up to bf16
-  const float s = bf16_bits_to_float(scale_bits);
-  const bool live = s > 1e-30f;
-  const float inv = live ? __frcp_rn(s) : 0.0f;
-  if (!live) scale_bits = 0;
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 16; i += 2) {
-    float u0 = 0.5f, u1 = 0.5f;
-    if (stochastic) {
-      uint32_t h = mix32(key + (pair0 + uint32_t(i >> 1)) * 0x9E3779B9u);
-      u0 = float(h & 0xffffu) * (1.0f / 65536.0f);
-      u1 = float(h >> 16) * (1.0f / 65536.0f);
-    }
-    float q0 = fminf(fmaxf(floorf(__fmaf_rn(e[i], inv, u0)), -8.0f), 7.0f);
-    float q1 = fminf(fmaxf(floorf(__fmaf_rn(e[i + 1], inv, u1)), -8.0f), 7.0f);
-    deq[i] = live ? q0 * s : 0.0f;
-    deq[i + 1] = live ? q1 * s : 0.0f;
-    e[i] -= deq[i];
-    e[i + 1] -= deq[i + 1];
-    uint32_t n0 = uint32_t(int(q0)) & 0xfu, n1 = uint32_t(int(q1)) & 0xfu;
-    w[i >> 3] |= (n0 << (4 * (i & 7))) | (n1 << (4 * ((i + 1) & 7)));
-  }
-  packed = make_uint2(w[0], w[1]);
-}
-
-// 16 nibbles (in `packed`) times `scale`, added to acc.
-__device__ __forceinline__ void dequant16_add(const uint2 packed, float scale, float (&acc)[16]) {
-  const uint32_t w[2] = {packed.x, packed.y};
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    int q = int(w[i >> 3] << (28 - 4 * (i & 7))) >> 28;
-    acc[i] = __fmaf_rn(float(q), scale, acc[i]);
-  }
-}
-
-// ---- 8-element variants: one 16-byte load per 16-bit tensor, eight lanes share a 64-element block ----
 constexpr int kElems8 = 8;
 constexpr int kLanes8 = kQuantBlock / kElems8;  // 8
 

@@ -75,8 +75,9 @@ class DGCEngine:
         z = lambda m, dt: torch.zeros(m, dtype=dt, device=self.device)  # noqa: E731
         st = DGCBucket(n=n, k=k, capacity=capacity, region=region, recv_off=recv_off, flag_off=flag_off,
                        u=[z(n, torch.float32) for _ in range(self.nvr)], v=[z(n, torch.float32) for _ in range(self.nvr)],
-                       # fixed words + room for 8 k + 1024 candidates (index, bits) of the list-based selection
-                       scratch=[z(scratch_words + 2 * (8 * k + 1024), torch.int32) for _ in range(self.nvr)],
+                       # fixed words + room for 4 k + 1024 candidates (index, bits) of the list-based selection; a longer
+                       # list would cost more to build than the dense passes it replaces
+                       scratch=[z(scratch_words + 2 * (4 * k + 1024), torch.int32) for _ in range(self.nvr)],
                        out_count=[z(2, torch.int32) for _ in range(self.nvr)])
         self.buckets[index] = st
         return st
