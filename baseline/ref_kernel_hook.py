@@ -11,8 +11,6 @@ quantization step ``gamma`` per bucket taken from the previous step's residual (
 read per bucket and step). It is a measuring stick for the fused kernels, not a reimplementation of the
 reference's API.
 """
-from __future__ import annotations
-
 import ctypes
 import os
 from typing import Dict

@@ -45,7 +45,8 @@ constexpr int kThreads = 256;
 // scratch layout (uint32 words)
 constexpr int kHist0 = 0, kHist1 = kHist0 + kBins0, kHist2 = kHist1 + kBins1;
 constexpr int kCursor = kHist2 + kBins2;  // number of selected entries
-constexpr int kCandCount = kCursor + 1;   // number of candidates seen in phase 1 (may exceed the capacity)
+constexpr int kCandCount = kCursor + 1;   // candidates collected in phase 1, summed over the CTAs
+constexpr int kCandOverflow = kCursor + 4;  // non-zero if a CTA ran out of room for its candidates
 constexpr int kScratchWords = kCursor + 8;  // the candidate list (index, bits pairs) follows
 
 template <typename T>
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
 
   __shared__ uint32_t sh_hist[kBins0];
   __shared__ uint32_t sh_sel[2];
-  __shared__ uint32_t sh_cand_full;  // set once this CTA has seen the candidate list overflow
+  __shared__ uint32_t sh_cand_cnt;  // candidates this CTA has appended to its segment of the list
   const int64_t tid0 = int64_t(blockIdx.x) * kThreads + threadIdx.x;
   const int64_t stride = int64_t(gridDim.x) * kThreads;
   // The dense passes walk the bucket in groups of 4 elements; every warp keeps all 32 lanes in the loop
@@ -126,12 +127,13 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
   const uint32_t cand_thr = (cand_cap > 0 && tau_prev > 0 && tau_prev < 0x7f800000u)
                                 ? __float_as_uint(__uint_as_float(tau_prev) * 0.96f)
                                 : 0xffffffffu;  // nothing qualifies
-  uint32_t* cand_idx = scratch + kScratchWords;
+  const uint32_t seg_cap = cand_cap / gridDim.x;  // entries per CTA
+  uint32_t* cand_idx = scratch + kScratchWords + uint64_t(blockIdx.x) * seg_cap;
   uint32_t* cand_bits = cand_idx + cand_cap;
 
   // ---- phase 0 ----
   for (int i = int(tid0); i < kScratchWords; i += int(stride)) scratch[i] = 0u;
-  if (threadIdx.x == 0) sh_cand_full = 0u;
+  if (threadIdx.x == 0) sh_cand_cnt = 0u;
   grid.sync();
 
   // ---- phase 1: momentum correction + histogram of bits [30:20] ----
@@ -173,21 +175,16 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     for (int k = 0; k < 4; ++k) {
       const uint32_t b = __float_as_uint(vn[k]) & 0x7fffffffu;
       hist_add(sh_hist, b >> 20, k < valid);
-      // once the list has overflowed the dense passes will run anyway: stop counting (the shared flag
-      // is only a hint, a stale read costs one more atomic)
-      const bool cand = k < valid && b >= cand_thr && *reinterpret_cast<volatile uint32_t*>(&sh_cand_full) == 0u;
+      const bool cand = k < valid && b >= cand_thr;
       const uint32_t mask = __ballot_sync(0xffffffffu, cand);
       if (mask) {
         const int lane = threadIdx.x & 31;
         uint32_t base = 0;
-        if (lane == __ffs(mask) - 1) {
-          base = atomicAdd(&scratch[kCandCount], uint32_t(__popc(mask)));
-          if (base + uint32_t(__popc(mask)) > cand_cap) sh_cand_full = 1u;
-        }
+        if (lane == __ffs(mask) - 1) base = atomicAdd(&sh_cand_cnt, uint32_t(__popc(mask)));
         base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
         if (cand) {
           const uint32_t pos = base + uint32_t(__popc(mask & ((1u << lane) - 1u)));
-          if (pos < cand_cap) {
+          if (pos < seg_cap) {
             cand_idx[pos] = uint32_t(q * 4 + k);
             cand_bits[pos] = b;
           }
@@ -198,20 +195,25 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
   __syncthreads();
   for (int i = threadIdx.x; i < kBins0; i += kThreads)
     if (sh_hist[i]) atomicAdd(&scratch[kHist0 + i], sh_hist[i]);
+  const uint32_t my_cand = min(sh_cand_cnt, seg_cap);  // entries of this CTA's segment
+  if (threadIdx.x == 0) {
+    atomicAdd(&scratch[kCandCount], my_cand);
+    if (sh_cand_cnt > seg_cap) atomicOr(&scratch[kCandOverflow], 1u);
+  }
   grid.sync();
   uint32_t want = p.k, bin0, bin1, bin2;
   select_bin(scratch + kHist0, kBins0, want, bin0, sh_sel);
 
   const uint32_t ncand = scratch[kCandCount];
-  const bool from_list = cand_cap > 0 && ncand >= p.k && ncand <= cand_cap;  // same on every CTA
+  const bool from_list = seg_cap > 0 && ncand >= p.k && scratch[kCandOverflow] == 0u;  // same on every CTA
   uint32_t tau;
   if (from_list) {
     // ---- phases 2-4 over the candidate list ----
     for (int i = threadIdx.x; i < kBins1; i += kThreads) sh_hist[i] = 0u;
     __syncthreads();
-    const int64_t nc_rounded = (int64_t(ncand) + 31) / 32 * 32;
-    for (int64_t j = tid0; j < nc_rounded; j += stride) {
-      const uint32_t b = j < ncand ? cand_bits[j] : 0xffffffffu;
+    const uint32_t nc_rounded = (my_cand + 31u) / 32u * 32u;  // this CTA scans its own segment
+    for (uint32_t j = threadIdx.x; j < nc_rounded; j += kThreads) {
+      const uint32_t b = j < my_cand ? cand_bits[j] : 0xffffffffu;
       hist_add(sh_hist, (b >> 9) & 0x7ffu, b != 0xffffffffu && (b >> 20) == bin0);
     }
     __syncthreads();
@@ -222,8 +224,8 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     for (int i = threadIdx.x; i < kBins2; i += kThreads) sh_hist[i] = 0u;
     __syncthreads();
     const uint32_t prefix = (bin0 << 11) | bin1;
-    for (int64_t j = tid0; j < nc_rounded; j += stride) {
-      const uint32_t b = j < ncand ? cand_bits[j] : 0xffffffffu;
+    for (uint32_t j = threadIdx.x; j < nc_rounded; j += kThreads) {
+      const uint32_t b = j < my_cand ? cand_bits[j] : 0xffffffffu;
       hist_add(sh_hist, b & 0x1ffu, b != 0xffffffffu && (b >> 9) == prefix);
     }
     __syncthreads();
@@ -232,8 +234,8 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     grid.sync();
     select_bin(scratch + kHist2, kBins2, want, bin2, sh_sel);
     tau = (prefix << 9) | bin2;
-    for (int64_t j = tid0; j < nc_rounded; j += stride) {
-      const uint32_t b = j < ncand ? cand_bits[j] : 0xffffffffu;
+    for (uint32_t j = threadIdx.x; j < nc_rounded; j += kThreads) {
+      const uint32_t b = j < my_cand ? cand_bits[j] : 0xffffffffu;
       const bool sel = b != 0xffffffffu && b >= tau && (p.k > 0) && b != 0u;
       const uint32_t mask = __ballot_sync(0xffffffffu, sel);
       if (mask) {

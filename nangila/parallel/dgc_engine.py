@@ -75,9 +75,10 @@ class DGCEngine:
         z = lambda m, dt: torch.zeros(m, dtype=dt, device=self.device)  # noqa: E731
         st = DGCBucket(n=n, k=k, capacity=capacity, region=region, recv_off=recv_off, flag_off=flag_off,
                        u=[z(n, torch.float32) for _ in range(self.nvr)], v=[z(n, torch.float32) for _ in range(self.nvr)],
-                       # fixed words + room for 4 k + 1024 candidates (index, bits) of the list-based selection; a longer
-                       # list would cost more to build than the dense passes it replaces
-                       scratch=[z(scratch_words + 2 * (4 * k + 1024), torch.int32) for _ in range(self.nvr)],
+                       # fixed words + the candidate list (index, bits) of the list-based selection. Unsent entries
+                       # pile up just below the threshold (about 17 k of them within 4 % of it), and every CTA owns an
+                       # equal segment of the list, hence the slack.
+                       scratch=[z(scratch_words + 2 * (32 * k + 128 * 444), torch.int32) for _ in range(self.nvr)],
                        out_count=[z(2, torch.int32) for _ in range(self.nvr)])
         self.buckets[index] = st
         return st
