@@ -23,7 +23,7 @@ from nangila.ddp import register_nangila_hook  # noqa: E402
 from nangila.models.gpt2 import GPT2, GPT2Config  # noqa: E402
 from nangila.utils import init_distributed, seed_everything  # noqa: E402
 
-COMPRESSORS = {"predres": CompressorType.PREDICTION_RESIDUAL, "dgc": CompressorType.DGC, "powersgd": CompressorType.POWER_SGD}
+COMPRESSORS = {"predres": CompressorType.PredictionResidual, "dgc": CompressorType.DGC, "powersgd": CompressorType.PowerSGD}
 
 
 def main() -> int:

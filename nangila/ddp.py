@@ -67,9 +67,11 @@ if CPP_HOOK_AVAILABLE:
         """
 
         def __init__(self, num_layers: int = 1000, warmup_steps: int = 100, process_group: Optional[Any] = None, *,
-                     momentum: float = 0.9, error_feedback: bool = True, stochastic: bool = True, seed: int = 42,
+                     momentum: float = 0.9, error_feedback: bool = True, stochastic: Optional[bool] = None, seed: int = 42,
                      reserve_bytes: Optional[int] = None):
             super().__init__(int(num_layers), int(warmup_steps))
+            if stochastic is None:  # round to nearest when the error memory is there to remove the bias
+                stochastic = not error_feedback
             self.configure(momentum=momentum, error_feedback=error_feedback, stochastic=stochastic, seed=seed)
             self.process_group = process_group
             self._reserve_bytes = reserve_bytes
@@ -133,8 +135,8 @@ class NangilaDDPHook:
 
     Args mirror the reference (ddp.py:100-112). ``num_layers`` is only the size of the all-Driver
     mask of the host-side state machine; device state is created per bucket on first use.
-    Extra keyword-only knobs: ``momentum``, ``error_feedback``, ``stochastic`` (False = round to
-    nearest, for reproducible tests), ``dgc_momentum`` (momentum correction factor of the DGC path).
+    Extra keyword-only knobs: ``momentum``, ``error_feedback``, ``stochastic`` (rounding of the INT4 codes;
+    default: round to nearest with error feedback, stochastic without), ``dgc_momentum`` (momentum correction factor of the DGC path).
     """
 
     def __init__(
@@ -151,7 +153,7 @@ class NangilaDDPHook:
         power_sgd_rank: int = 1,
         momentum: float = 0.9,
         error_feedback: bool = True,
-        stochastic: bool = True,
+        stochastic: Optional[bool] = None,
         dgc_momentum: float = 0.9,
         total_numel: Optional[int] = None,
     ):
@@ -167,7 +169,11 @@ class NangilaDDPHook:
         self.power_sgd_rank = int(power_sgd_rank)
         self.momentum = float(momentum)
         self.error_feedback = error_feedback
-        self.stochastic = stochastic
+        # Rounding of the INT4 codes: with error feedback the default is round-to-nearest (half the noise power;
+        # the error memory removes the bias), without it stochastic rounding (unbiased). NANGILA_STOCHASTIC=0/1 overrides.
+        if stochastic is None:
+            stochastic = not error_feedback
+        self.stochastic = bool(int(os.environ.get("NANGILA_STOCHASTIC", int(bool(stochastic)))))
         self.dgc_momentum = float(dgc_momentum)
         self.config = NangilaConfig(
             momentum=momentum, threshold=threshold, warmup_steps=self.warmup_steps, shadow_run_steps=0,
