@@ -68,6 +68,8 @@ struct Bucket {
   uint32_t epoch = 0;
   uint64_t calls = 0;
   uint64_t compressed_calls = 0;
+  uint64_t probe_every = 0;  // calls between history probes while the gain is 0 (0: not initialised)
+  uint64_t next_probe = 0;
   double totals[4] = {0, 0, 0, 0};
   // NANGILA_TIMING=1: events around the most recent launch of this bucket
   std::shared_ptr<at::cuda::CUDAEvent> t0, t1;
@@ -159,7 +161,16 @@ class DdpHook {
     p.state_dtype = b.grad_dtype == NANGILA_F32 ? NANGILA_F32 : NANGILA_BF16;
     p.mode = compressed ? 0 : 1;
     p.stochastic = stochastic_ ? 1 : 0;
-    p.measure = (b.calls % uint64_t(probe_every_)) == 0 ? 1 : 0;
+    // probes that keep finding nothing to predict are spaced out (8, 16, ... 64 calls); see adapt()
+    if (b.probe_every == 0) {
+      b.probe_every = uint64_t(probe_every_);
+      b.next_probe = b.probe_every;
+    }
+    p.measure = 0;
+    if (b.calls >= b.next_probe) {
+      p.measure = 1;
+      b.next_probe = b.calls + b.probe_every;
+    }
     p.gather = (compressed && world_ >= 2 && world_ <= gather_max_world_) ? 1 : 0;
     p.uniform_gain = 1;  // the statistics are summed over the group before the controller reads them
     p.epoch = b.epoch;
@@ -387,7 +398,9 @@ class DdpHook {
     if (pp <= 0.0) return;  // not a probe step
     const double best = std::min(std::max(xp / pp, 0.0), 1.0);
     const double gain = 0.5 * b.pred_gain + 0.5 * best;
-    b.pred_gain = gain >= 0.2 ? gain : 0.0;  // below 0.2 (< 4 % less residual energy) the history loads cost more than they save
+    b.pred_gain = gain >= 0.2 ? gain : 0.0;
+    if (b.probe_every != 0)
+      b.probe_every = b.pred_gain > 0.0 ? uint64_t(probe_every_) : std::min<uint64_t>(2 * b.probe_every, std::max<uint64_t>(64, uint64_t(probe_every_)));  // below 0.2 (< 4 % less residual energy) the history loads cost more than they save
   }
 
   int64_t num_layers_;

@@ -89,8 +89,9 @@ __global__ void __launch_bounds__(kThreads, 4) fsdp_ag_kernel(const __grid_const
             w0 |= (uint32_t(q) & 0xfu) << (4 * i);
           }
         }
-        for (int r = 0; r < W; ++r) {
-          uint8_t* dst = p.region[(me + 1 + r) % W] + recv + (uint64_t(me) * cps + j) * slot;
+        int rr = me + 1 == W ? 0 : me + 1;  // peers first, this rank last; no division in the loop
+        for (int r = 0; r < W; ++r, rr = (rr + 1 == W ? 0 : rr + 1)) {
+          uint8_t* dst = p.region[rr] + recv + (uint64_t(me) * cps + j) * slot;
           if (BITS == 8) reinterpret_cast<uint2*>(dst + uint64_t(it) * kPerIter)[tid] = make_uint2(w0, w1);
           else reinterpret_cast<uint32_t*>(dst + uint64_t(it) * (kPerIter / 2))[tid] = w0;
           if ((tid & 7) == 0)
@@ -113,25 +114,43 @@ __global__ void __launch_bounds__(kThreads, 4) fsdp_ag_kernel(const __grid_const
                        p.timeout_ns, status, kTimeoutPhase3, uint32_t(me), uint32_t(o), 3u, uint32_t(j));
       if (!__syncthreads_and(ok ? 1 : 0)) break;
       const uint8_t* src = myreg + recv + (uint64_t(o) * cps + j) * slot;
-      for (int it = 0; it < iters; ++it) {
-        const int64_t local = int64_t(j) * C + int64_t(it) * kPerIter + tid * kE;
-        if (local >= shard) continue;
-        const float s = bf16_bits_to_float(
-            reinterpret_cast<const uint16_t*>(src + uint64_t(C) * BITS / 8)[it * (kPerIter / kQuantBlock) + tid / 8]);
-        float y[kE];
-        if (BITS == 8) {
-          const uint2 w = reinterpret_cast<const uint2*>(src + uint64_t(it) * kPerIter)[tid];
+      // The packed words and scales of kB iterations are fetched before any of them is expanded: the
+      // stores to `out` may alias the slot as far as the compiler knows, so without this every load
+      // would wait for the previous iteration's stores.
+      constexpr int kB = 4;
+      for (int it0 = 0; it0 < iters; it0 += kB) {
+        uint2 w[kB];
+        uint16_t sc[kB];
 #pragma unroll
-          for (int i = 0; i < kE; ++i) {
-            const uint32_t ww = i < 4 ? w.x : w.y;
-            y[i] = float(int(ww << (24 - 8 * (i & 3))) >> 24) * s;
+        for (int b = 0; b < kB; ++b) {
+          const int it = it0 + b;
+          w[b] = make_uint2(0u, 0u);
+          sc[b] = 0;
+          if (it < iters && int64_t(j) * C + int64_t(it) * kPerIter + tid * kE < shard) {
+            sc[b] = reinterpret_cast<const uint16_t*>(src + uint64_t(C) * BITS / 8)[it * (kPerIter / kQuantBlock) + tid / 8];
+            if (BITS == 8) w[b] = reinterpret_cast<const uint2*>(src + uint64_t(it) * kPerIter)[tid];
+            else w[b].x = reinterpret_cast<const uint32_t*>(src + uint64_t(it) * (kPerIter / 2))[tid];
           }
-        } else {
-          const uint32_t w = reinterpret_cast<const uint32_t*>(src + uint64_t(it) * (kPerIter / 2))[tid];
-#pragma unroll
-          for (int i = 0; i < kE; ++i) y[i] = float(int(w << (28 - 4 * i)) >> 28) * s;
         }
-        store8_guarded<T>(out + int64_t(o) * shard, local, shard, y);
+#pragma unroll
+        for (int b = 0; b < kB; ++b) {
+          const int it = it0 + b;
+          const int64_t local = int64_t(j) * C + int64_t(it) * kPerIter + tid * kE;
+          if (it >= iters || local >= shard) continue;
+          const float s = bf16_bits_to_float(sc[b]);
+          float y[kE];
+          if (BITS == 8) {
+#pragma unroll
+            for (int i = 0; i < kE; ++i) {
+              const uint32_t ww = i < 4 ? w[b].x : w[b].y;
+              y[i] = float(int(ww << (24 - 8 * (i & 3))) >> 24) * s;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < kE; ++i) y[i] = float(int(w[b].x << (28 - 4 * i)) >> 28) * s;
+          }
+          store8_guarded<T>(out + int64_t(o) * shard, local, shard, y);
+        }
       }
     }
   }

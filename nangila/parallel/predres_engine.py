@@ -75,6 +75,8 @@ class BucketState:
     pred_gain: float = 1.0              # kappa: 1 = full momentum prediction, 0 = none
     miss_ema: Optional[float] = None    # running ||g - g_hat||^2 / ||g||^2
     cooldown: int = 0
+    probe_every: int = 0                # calls between probes of the history while the gain is 0 (0: engine default)
+    next_probe: int = 0                 # call number of the next probe
     totals: List[float] = field(default_factory=lambda: [0.0, 0.0, 0.0, 0.0])
     epoch: int = 0
     calls: int = 0
@@ -203,7 +205,7 @@ class PredResEngine:
             grad=grads, prev=st.prev, curr=st.curr, ef=st.ef, ef2=st.ef2, stats=st.stats, status=self.status,
             region_ptrs=st.region.ptrs, recv1_off=r1, recv2_off=r2, flag1_off=f1, flag2_off=f2,
             rank0=0 if self.loopback else self.rank, chunk_elems=st.chunk, mode=0 if compressed else 1,
-            stochastic=self.stochastic, measure=(st.calls % self.probe_every == 0), epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
+            stochastic=self.stochastic, measure=self._probe_due(st), epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
             mu=self.momentum, pred_gain=self._gains(st), timeout_s=self.timeout_s, grid_x=self._grid(st),
             uniform_gain=st.extra.get("pred_gain_per_rank") is None,
             gather=compressed and 2 <= self.world <= self.gather_max_world,
@@ -240,6 +242,18 @@ class PredResEngine:
             if e1.query():
                 out[idx] = e0.elapsed_time(e1)
         return out
+
+    def _probe_due(self, st: BucketState) -> bool:
+        """While the gain is 0 the kernel looks at the history only on probe calls. Probes that keep finding
+        nothing to predict are spaced out (every 8th call, then 16th, ... up to 64th); a probe that finds
+        something resets the spacing."""
+        if st.probe_every == 0:
+            st.probe_every = self.probe_every
+            st.next_probe = st.probe_every
+        if st.calls < st.next_probe:
+            return False
+        st.next_probe = st.calls + st.probe_every
+        return True
 
     def _gains(self, st: BucketState) -> List[float]:
         g = st.extra.get("pred_gain_per_rank")
@@ -287,6 +301,8 @@ class PredResEngine:
                 best = min(max(xp / pp, 0.0), 1.0)
                 gain = 0.5 * st.pred_gain + 0.5 * best
                 st.pred_gain = gain if gain >= 0.2 else 0.0  # below 0.2 (< 4 % less residual energy) the history loads cost more than they save
+                if st.probe_every:
+                    st.probe_every = self.probe_every if st.pred_gain > 0.0 else min(2 * st.probe_every, max(64, self.probe_every))
         stream = self.stream if self.stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(stream):
             if self.world > 1 and not self.loopback and self.adaptive_gain:
