@@ -1,0 +1,248 @@
+// Circuit description of one partition: source waveforms, elements, device models and the netlist
+// record with its JSON form.
+//
+// The JSON layout is the one the reference's partition files use (externally tagged variants:
+// {"Resistor": {"a": 1, "b": 2, "r": 1000.0}}, {"Dc": 1.8}; ghost_map entries are
+// [net_id, local_node, owner]); reference: nangila-spice/nangila-node/src/mna.rs:30-106 (Element,
+// SourceWaveform), ngspice_ffi.rs:35-48 (PartitionNetlist), device_model.rs:24-225 (models).
+// Node 0 is ground; node k > 0 is unknown k-1 of the system.
+#pragma once
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "json.hpp"
+
+namespace nspice {
+
+struct SourceWaveform {
+    enum Kind { Dc, Pulse } kind = Dc;
+    double dc = 0.0;
+    double v1 = 0, v2 = 0, td = 0, tr = 0, tf = 0, pw = 0, per = 0;
+
+    static SourceWaveform make_dc(double v) { SourceWaveform s; s.kind = Dc; s.dc = v; return s; }
+    static SourceWaveform make_pulse(double v1, double v2, double td, double tr, double tf, double pw, double per) {
+        SourceWaveform s; s.kind = Pulse; s.v1 = v1; s.v2 = v2; s.td = td; s.tr = tr; s.tf = tf; s.pw = pw; s.per = per;
+        return s;
+    }
+    double value_at(double t) const {
+        if (kind == Dc) return dc;
+        if (per <= 0.0 || t < td) return v1;
+        double local = std::fmod(t - td, per);
+        if (local < tr) return tr <= 0.0 ? v2 : v1 + (v2 - v1) * (local / tr);
+        if (local < tr + pw) return v2;
+        if (local < tr + pw + tf) return tf <= 0.0 ? v1 : v2 + (v1 - v2) * ((local - tr - pw) / tf);
+        return v1;
+    }
+    // Times in (t0, t1] where the waveform has a corner; the transient loop can land steps on them.
+    bool has_corner_in(double t0, double t1) const {
+        if (kind != Pulse || per <= 0.0) return false;
+        const double offs[4] = {0.0, tr, tr + pw, tr + pw + tf};
+        double base = td + std::floor(std::max(0.0, t0 - td) / per) * per;
+        for (int cyc = 0; cyc < 2; ++cyc)
+            for (double o : offs) {
+                double c = base + cyc * per + o;
+                if (c > t0 && c <= t1) return true;
+            }
+        return false;
+    }
+    Json to_json() const {
+        Json j = Json::object();
+        if (kind == Dc) { j.set("Dc", dc); return j; }
+        Json p = Json::object();
+        p.set("v1", v1).set("v2", v2).set("td", td).set("tr", tr).set("tf", tf).set("pw", pw).set("per", per);
+        j.set("Pulse", p);
+        return j;
+    }
+    static SourceWaveform from_json(const Json& j) {
+        if (j.is_num()) return make_dc(j.num);
+        if (const Json* d = j.find("Dc")) return make_dc(d->as_num());
+        const Json& p = j.at("Pulse");
+        return make_pulse(p.number("v1", 0), p.number("v2", 0), p.number("td", 0), p.number("tr", 0),
+                          p.number("tf", 0), p.number("pw", 0), p.number("per", 0));
+    }
+};
+
+struct DiodeModel {
+    double is = 1e-14, vt = 0.02585, n = 1.0;
+    // Current and conductance at junction voltage vd; the exponent is capped at 40 and the
+    // conductance floored at 1e-12 S so the matrix pattern never loses the entry.
+    void eval(double vd, double& current, double& g) const {
+        double nvt = n * vt;
+        double e = std::exp(std::min(vd / nvt, 40.0));
+        current = is * (e - 1.0);
+        g = std::max(is * e / nvt, 1e-12);
+    }
+    // Norton companion: i = g * vd + ieq
+    void companion(double vd, double& g, double& ieq) const {
+        double cur;
+        eval(vd, cur, g);
+        ieq = cur - g * vd;
+    }
+};
+
+enum class MosType { Nmos, Pmos };
+enum class MosRegion { Cutoff, Linear, Saturation };
+
+struct MosfetLevel1 {
+    MosType kind = MosType::Nmos;
+    double vth = 0.5, beta = 1e-3, lambda = 0.1;
+
+    // Drain current (into the drain for NMOS) and its derivatives w.r.t. vgs and vds.
+    void evaluate(double vgs, double vds, double& id, double& gm, double& gds, MosRegion& region) const {
+        double sign = kind == MosType::Nmos ? 1.0 : -1.0;
+        double vc = sign * vgs, vo = sign * vds;
+        double vov = vc - std::fabs(vth);
+        if (vov <= 0.0) { id = 0.0; gm = 1e-12; gds = 1e-12; region = MosRegion::Cutoff; return; }
+        if (vo < vov) {
+            id = sign * beta * (vov * vo - 0.5 * vo * vo);
+            gm = std::max(beta * vo, 1e-12);
+            gds = std::max(beta * (vov - vo), 1e-12);
+            region = MosRegion::Linear;
+        } else {
+            double clm = 1.0 + lambda * std::max(vo, 0.0);
+            id = sign * 0.5 * beta * vov * vov * clm;
+            gm = std::max(beta * vov * clm, 1e-12);
+            gds = std::max(0.5 * beta * vov * vov * lambda, 1e-12);
+            region = MosRegion::Saturation;
+        }
+    }
+    // Linearisation around (vgs, vds): id ~ gm*vgs + gds*vds + ieq
+    void companion(double vgs, double vds, double& gm, double& gds, double& ieq) const {
+        double id;
+        MosRegion r;
+        evaluate(vgs, vds, id, gm, gds, r);
+        ieq = id - gm * vgs - gds * vds;
+    }
+};
+
+struct Element {
+    enum Kind { Resistor, Capacitor, Inductor, VSource, ISource, Ghost, Diode, Mosfet } kind = Resistor;
+    // two-terminal parts use (a, b); sources (a = pos, b = neg); ghost uses a; diode (a = anode,
+    // b = cathode); MOSFET uses (d, g, s, bulk)
+    int a = 0, b = 0, d = 0, g = 0, s = 0, bulk = 0;
+    double value = 0.0;  // ohms / farads / henries / ghost voltage
+    SourceWaveform source;
+    DiodeModel diode;
+    MosfetLevel1 mos;
+
+    static Element resistor(int a, int b, double r) { Element e; e.kind = Resistor; e.a = a; e.b = b; e.value = r; return e; }
+    static Element capacitor(int a, int b, double c) { Element e; e.kind = Capacitor; e.a = a; e.b = b; e.value = c; return e; }
+    static Element inductor(int a, int b, double l) { Element e; e.kind = Inductor; e.a = a; e.b = b; e.value = l; return e; }
+    static Element vsource(int p, int n, SourceWaveform w) { Element e; e.kind = VSource; e.a = p; e.b = n; e.source = w; return e; }
+    static Element isource(int p, int n, SourceWaveform w) { Element e; e.kind = ISource; e.a = p; e.b = n; e.source = w; return e; }
+    static Element ghost(int node, double v) { Element e; e.kind = Ghost; e.a = node; e.value = v; return e; }
+    static Element make_diode(int p, int n, DiodeModel m) { Element e; e.kind = Diode; e.a = p; e.b = n; e.diode = m; return e; }
+    static Element mosfet(int d, int g, int s, int b, MosfetLevel1 m) {
+        Element e; e.kind = Mosfet; e.d = d; e.g = g; e.s = s; e.bulk = b; e.mos = m; return e;
+    }
+
+    Json to_json() const {
+        Json body = Json::object(), j = Json::object();
+        switch (kind) {
+            case Resistor: body.set("a", a).set("b", b).set("r", value); j.set("Resistor", body); break;
+            case Capacitor: body.set("a", a).set("b", b).set("c", value); j.set("Capacitor", body); break;
+            case Inductor: body.set("a", a).set("b", b).set("l", value); j.set("Inductor", body); break;
+            case VSource: body.set("pos", a).set("neg", b).set("source", source.to_json()); j.set("VoltageSource", body); break;
+            case ISource: body.set("pos", a).set("neg", b).set("source", source.to_json()); j.set("CurrentSource", body); break;
+            case Ghost: body.set("node", a).set("voltage", value); j.set("GhostSource", body); break;
+            case Diode: {
+                Json m = Json::object();
+                m.set("is", diode.is).set("vt", diode.vt).set("n", diode.n).set("node_p", a).set("node_n", b);
+                body.set("p", a).set("n", b).set("model", m);
+                j.set("Diode", body);
+                break;
+            }
+            case Mosfet: {
+                Json m = Json::object();
+                m.set("kind", mos.kind == MosType::Nmos ? "Nmos" : "Pmos").set("vth", mos.vth).set("beta", mos.beta)
+                    .set("lambda", mos.lambda).set("node_g", g).set("node_d", d).set("node_s", s);
+                body.set("d", d).set("g", g).set("s", s).set("b", bulk).set("model", m);
+                j.set("Mosfet", body);
+                break;
+            }
+        }
+        return j;
+    }
+    static Element from_json(const Json& j) {
+        if (!j.is_obj() || j.obj.size() != 1) throw std::runtime_error("element: expected a single-key object");
+        const std::string& tag = j.obj[0].first;
+        const Json& o = j.obj[0].second;
+        auto I = [&](const char* k) { return int(o.number(k, 0)); };
+        if (tag == "Resistor") return resistor(I("a"), I("b"), o.number("r", 1.0));
+        if (tag == "Capacitor") return capacitor(I("a"), I("b"), o.number("c", 0.0));
+        if (tag == "Inductor") return inductor(I("a"), I("b"), o.number("l", 0.0));
+        if (tag == "VoltageSource") return vsource(I("pos"), I("neg"), SourceWaveform::from_json(o.at("source")));
+        if (tag == "CurrentSource") return isource(I("pos"), I("neg"), SourceWaveform::from_json(o.at("source")));
+        if (tag == "GhostSource") return ghost(I("node"), o.number("voltage", 0.0));
+        if (tag == "Diode") {
+            DiodeModel m;
+            if (const Json* mj = o.find("model")) { m.is = mj->number("is", m.is); m.vt = mj->number("vt", m.vt); m.n = mj->number("n", m.n); }
+            return make_diode(I("p"), I("n"), m);
+        }
+        if (tag == "Mosfet") {
+            MosfetLevel1 m;
+            if (const Json* mj = o.find("model")) {
+                if (const Json* k = mj->find("kind")) m.kind = (k->is_str() && k->str == "Pmos") ? MosType::Pmos : MosType::Nmos;
+                m.vth = mj->number("vth", m.vth); m.beta = mj->number("beta", m.beta); m.lambda = mj->number("lambda", m.lambda);
+            }
+            return mosfet(I("d"), I("g"), I("s"), I("b"), m);
+        }
+        throw std::runtime_error("element: unknown kind '" + tag + "'");
+    }
+};
+
+struct GhostLink { uint64_t net_id = 0; int local_node = 0; uint32_t owner = 0; };
+
+struct Netlist {
+    std::string name;
+    int num_nodes = 0;
+    std::vector<Element> elements;
+    std::vector<GhostLink> ghost_map;
+    std::vector<std::string> node_names;
+    std::vector<std::pair<int, double>> initial_conditions;
+
+    std::vector<std::string> names_or_default() const {
+        if (!node_names.empty()) return node_names;
+        std::vector<std::string> out;
+        for (int i = 1; i <= num_nodes; ++i) out.push_back("node_" + std::to_string(i));
+        return out;
+    }
+    Json to_json() const {
+        Json j = Json::object();
+        j.set("name", name).set("num_nodes", num_nodes);
+        Json els = Json::array();
+        for (auto& e : elements) els.push(e.to_json());
+        j.set("elements", els);
+        Json gm = Json::array();
+        for (auto& g : ghost_map) { Json t = Json::array(); t.push(g.net_id).push(g.local_node).push(uint64_t(g.owner)); gm.push(t); }
+        j.set("ghost_map", gm);
+        Json nn = Json::array();
+        for (auto& n : node_names) nn.push(n);
+        j.set("node_names", nn);
+        Json ic = Json::array();
+        for (auto& p : initial_conditions) { Json t = Json::array(); t.push(p.first).push(p.second); ic.push(t); }
+        j.set("initial_conditions", ic);
+        return j;
+    }
+    static Netlist from_json(const Json& j) {
+        Netlist n;
+        if (const Json* p = j.find("name")) n.name = p->is_str() ? p->str : "";
+        n.num_nodes = int(j.number("num_nodes", 0));
+        for (auto& e : j.at("elements").arr) n.elements.push_back(Element::from_json(e));
+        if (const Json* gm = j.find("ghost_map"))
+            for (auto& t : gm->arr)
+                if (t.arr.size() >= 3) n.ghost_map.push_back({uint64_t(t.arr[0].as_num()), int(t.arr[1].as_num()), uint32_t(t.arr[2].as_num())});
+        if (const Json* nn = j.find("node_names"))
+            for (auto& s : nn->arr) n.node_names.push_back(s.as_str());
+        if (const Json* ic = j.find("initial_conditions"))
+            for (auto& t : ic->arr)
+                if (t.arr.size() >= 2) n.initial_conditions.emplace_back(int(t.arr[0].as_num()), t.arr[1].as_num());
+        return n;
+    }
+};
+
+}  // namespace nspice

@@ -1,0 +1,168 @@
+// nangila-node: solver process of one partition.
+//
+//   nangila-node --partition deck.sp|part.json [--node-id N] [-k TOTAL] [--predict-depth D]
+//                [--reltol R] [--tstop T] [--dt DT] [--process TT|FF|SS|FS|SF] [--vdd V] [--temp C]
+//                [--waveform-json out.json] [--waveform-nz out.nz] [--solver lu|dense|krylov]
+//                [--record-every K] [--demo]
+//
+// Flag set and the waveform JSON layout ({netlist, node_names, waveform: [{time, voltages{}}],
+// stats{}}) follow the reference's CLI (nangila-spice/nangila-node/src/main.rs:21-132).
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <functional>
+#include <iostream>
+
+#include "nz.hpp"
+#include "parser.hpp"
+#include "transient.hpp"
+
+using namespace nspice;
+
+struct Args {
+    std::string partition, process = "TT", waveform_json, waveform_nz, solver = "lu";
+    uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1;
+    double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
+    bool demo = false;
+};
+
+static void usage() {
+    std::fprintf(stderr,
+                 "usage: nangila-node [--partition FILE | --demo] [--node-id N] [-k TOTAL] [--predict-depth D]\n"
+                 "                    [--reltol R] [--tstop T] [--dt DT] [--process P] [--vdd V] [--temp C]\n"
+                 "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov]\n"
+                 "                    [--record-every K]\n");
+}
+
+static bool parse_args(int argc, char** argv, Args& a) {
+    for (int i = 1; i < argc; ++i) {
+        std::string f = argv[i];
+        auto need = [&](const char* name) -> const char* {
+            if (i + 1 >= argc) { std::fprintf(stderr, "missing value for %s\n", name); return nullptr; }
+            return argv[++i];
+        };
+        const char* v = nullptr;
+        if (f == "--demo") a.demo = true;
+        else if (f == "-h" || f == "--help") { usage(); std::exit(0); }
+        else if (f == "--partition" || f == "-p") { if (!(v = need("--partition"))) return false; a.partition = v; }
+        else if (f == "--node-id" || f == "-n") { if (!(v = need("--node-id"))) return false; a.node_id = uint32_t(std::atoi(v)); }
+        else if (f == "-k" || f == "--total-partitions") { if (!(v = need("-k"))) return false; a.total = uint32_t(std::atoi(v)); }
+        else if (f == "--predict-depth") { if (!(v = need("--predict-depth"))) return false; a.predict_depth = uint32_t(std::atoi(v)); }
+        else if (f == "--record-every") { if (!(v = need("--record-every"))) return false; a.record_every = std::max(1, std::atoi(v)); }
+        else if (f == "--reltol") { if (!(v = need("--reltol"))) return false; a.reltol = std::atof(v); }
+        else if (f == "--tstop") { if (!(v = need("--tstop"))) return false; a.tstop = std::atof(v); }
+        else if (f == "--dt") { if (!(v = need("--dt"))) return false; a.dt = std::atof(v); }
+        else if (f == "--vdd") { if (!(v = need("--vdd"))) return false; a.vdd = std::atof(v); }
+        else if (f == "--temp") { if (!(v = need("--temp"))) return false; a.temp = std::atof(v); }
+        else if (f == "--nz-tol") { if (!(v = need("--nz-tol"))) return false; a.nz_tol = std::atof(v); }
+        else if (f == "--process") { if (!(v = need("--process"))) return false; a.process = v; }
+        else if (f == "--solver") { if (!(v = need("--solver"))) return false; a.solver = v; }
+        else if (f == "--waveform-json") { if (!(v = need("--waveform-json"))) return false; a.waveform_json = v; }
+        else if (f == "--waveform-nz") { if (!(v = need("--waveform-nz"))) return false; a.waveform_nz = v; }
+        else { std::fprintf(stderr, "unknown flag %s\n", f.c_str()); return false; }
+    }
+    return true;
+}
+
+static Netlist demo_netlist() {
+    Netlist n;
+    n.name = "RC Demo";
+    n.num_nodes = 2;
+    n.elements = {Element::vsource(1, 0, SourceWaveform::make_dc(1.8)), Element::resistor(1, 2, 1000.0), Element::capacitor(2, 0, 10e-15)};
+    n.node_names = {"vdd", "cap"};
+    // start from a discharged capacitor so the demo shows the charging curve
+    n.initial_conditions = {{1, 1.8}, {2, 0.0}};
+    return n;
+}
+
+static void write_json(const std::string& path, const std::string& name, const std::vector<std::string>& names,
+                       const std::vector<WaveformPoint>& wf, const SimStats& st) {
+    std::ofstream f(path);
+    if (!f) throw std::runtime_error("cannot write '" + path + "'");
+    // streamed by hand: a waveform can hold millions of points
+    f << "{\n  \"netlist\": " << Json(name).dump() << ",\n  \"node_names\": [";
+    for (size_t i = 0; i < names.size(); ++i) f << (i ? ", " : "") << Json(names[i]).dump();
+    f << "],\n  \"waveform\": [";
+    char buf[64];
+    for (size_t p = 0; p < wf.size(); ++p) {
+        std::snprintf(buf, sizeof buf, "%.17g", wf[p].time);
+        f << (p ? ",\n    " : "\n    ") << "{\"time\": " << buf << ", \"voltages\": {";
+        size_t n = std::min(names.size(), wf[p].values.size());
+        for (size_t i = 0; i < n; ++i) {
+            std::snprintf(buf, sizeof buf, "%.17g", wf[p].values[i]);
+            f << (i ? ", " : "") << Json(names[i]).dump() << ": " << buf;
+        }
+        f << "}}";
+    }
+    f << "\n  ],\n  \"stats\": {\"total_steps\": " << st.total_steps;
+    std::snprintf(buf, sizeof buf, "%.9g", st.wall_time_secs);
+    f << ", \"wall_time_secs\": " << buf << ", \"prediction_hits\": " << st.prediction_hits << ", \"prediction_misses\": "
+      << st.prediction_misses << ", \"rollbacks\": " << st.rollbacks << ", \"completed\": " << (st.completed ? "true" : "false") << "}\n}\n";
+}
+
+int main(int argc, char** argv) {
+    Args a;
+    if (!parse_args(argc, argv, a)) { usage(); return 2; }
+    Netlist nl;
+    try {
+        if (a.demo) nl = demo_netlist();
+        else if (a.partition.empty()) { std::fprintf(stderr, "nothing to do: give --partition FILE or --demo\n"); return 0; }
+        else if (a.partition.size() > 5 && a.partition.substr(a.partition.size() - 5) == ".json") {
+            std::ifstream f(a.partition);
+            if (!f) throw std::runtime_error("cannot open '" + a.partition + "'");
+            std::stringstream ss;
+            ss << f.rdbuf();
+            nl = Netlist::from_json(Json::parse(ss.str()));
+        } else {
+            Corner c;
+            c.process = a.process; c.vdd = a.vdd; c.temp_c = a.temp;
+            SpiceParser p(c);
+            std::ifstream f(a.partition);
+            if (!f) throw std::runtime_error("cannot open '" + a.partition + "'");
+            std::stringstream ss;
+            ss << f.rdbuf();
+            std::string base = a.partition.substr(a.partition.find_last_of('/') == std::string::npos ? 0 : a.partition.find_last_of('/') + 1);
+            nl = p.parse_text(ss.str(), base);
+            for (auto& w : p.warnings) std::fprintf(stderr, "warning: %s\n", w.c_str());
+        }
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ERROR: failed to load netlist '%s': %s\n", a.partition.c_str(), e.what());
+        return 1;
+    }
+    std::fprintf(stderr, "nangila-node %u of %u: '%s', %d nodes, %zu elements, %zu ghost nodes\n", a.node_id, a.total, nl.name.c_str(),
+                 nl.num_nodes, nl.elements.size(), nl.ghost_map.size());
+    GhostBuffer ghosts(a.predict_depth);
+    for (auto& g : nl.ghost_map) ghosts.add(GhostNode(g.net_id, g.owner));
+    SimConfig cfg;
+    cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
+    std::vector<std::string> names = nl.names_or_default();
+    std::string name = nl.name;
+    TransientSolver solver(std::move(nl), std::move(ghosts), CommLayer(a.node_id, a.total), cfg);
+    solver.engine().newton.config.reltol = a.reltol;
+    if (a.solver == "dense") solver.engine().newton.linear.backend = LinearBackend::Dense;
+    else if (a.solver == "krylov") solver.engine().newton.linear.backend = LinearBackend::Krylov;
+    PartitionState fin = solver.run();
+    const SimStats& st = solver.stats;
+    std::fprintf(stderr, "steps %llu%s, wall %.3f s, NR iterations/step %.2f, hit rate %.1f%%, rollbacks %llu\n",
+                 (unsigned long long)st.total_steps, st.completed ? "" : " (stopped early: Newton did not converge)", st.wall_time_secs,
+                 st.total_steps ? double(solver.engine().newton.stats.total_iterations) / double(st.total_steps) : 0.0, st.hit_rate() * 100.0,
+                 (unsigned long long)st.rollbacks);
+    for (size_t i = 0; i < names.size() && i < fin.voltages.size() && i < 16; ++i) std::fprintf(stderr, "  V(%s) = %.6f\n", names[i].c_str(), fin.voltages[i]);
+    try {
+        if (!a.waveform_json.empty()) write_json(a.waveform_json, name, names, solver.waveform, st);
+        if (!a.waveform_nz.empty()) {
+            std::vector<double> t;
+            std::vector<std::vector<double>> sig(names.size());
+            for (auto& p : solver.waveform) {
+                t.push_back(p.time);
+                for (size_t i = 0; i < names.size(); ++i) sig[i].push_back(i < p.values.size() ? p.values[i] : 0.0);
+            }
+            NzWriter w(a.nz_tol);
+            w.write_file(a.waveform_nz, names, t, sig);
+        }
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ERROR: %s\n", e.what());
+        return 1;
+    }
+    return st.completed ? 0 : 3;
+}

@@ -1,0 +1,405 @@
+// SPICE-subset reader: R, C, L, V, I, D, M and X lines, `.subckt` flattening (hierarchical names
+// `inst.node`), `.param`, `.model`, `.ic`, PULSE / DC / SIN sources, engineering suffixes, `+`
+// continuation lines, and the partition directives `.ghost <net> <local node> <owner>` and
+// `.nodemap <name> <index>`. MOSFET cards are reduced to Level-1 parameters with process corner,
+// supply and temperature scaling applied at parse time.
+// Behavioural reference: nangila-spice/nangila-node/src/parser.rs:13-738.
+#pragma once
+#include <cctype>
+#include <fstream>
+#include <map>
+#include <sstream>
+#include <unordered_map>
+
+#include "circuit.hpp"
+
+namespace nspice {
+
+inline std::string lower(std::string s) { for (auto& c : s) c = char(std::tolower((unsigned char)c)); return s; }
+inline std::string upper(std::string s) { for (auto& c : s) c = char(std::toupper((unsigned char)c)); return s; }
+
+// "10k" -> 1e4, "2.5meg" -> 2.5e6, "1e-9" -> 1e-9, "10pF" -> 1e-11. Returns false on a non-number.
+inline bool parse_scaled(const std::string& raw, double& out) {
+    std::string s = lower(raw);
+    while (!s.empty() && std::string("(),;'{}").find(s.front()) != std::string::npos) s.erase(s.begin());
+    while (!s.empty() && std::string("(),;'{}").find(s.back()) != std::string::npos) s.pop_back();
+    if (s.empty()) return false;
+    const char* b = s.c_str();
+    char* e = nullptr;
+    double v = std::strtod(b, &e);
+    if (e == b) return false;
+    std::string suf(e);
+    double mul = 1.0;
+    if (suf.rfind("meg", 0) == 0) mul = 1e6;
+    else if (suf.rfind("mil", 0) == 0) mul = 25.4e-6;
+    else if (!suf.empty()) {
+        switch (suf[0]) {
+            case 'f': mul = 1e-15; break;
+            case 'p': mul = 1e-12; break;
+            case 'n': mul = 1e-9; break;
+            case 'u': mul = 1e-6; break;
+            case 'm': mul = 1e-3; break;
+            case 'k': mul = 1e3; break;
+            case 'g': mul = 1e9; break;
+            case 't': mul = 1e12; break;
+            default: mul = 1.0;
+        }
+    }
+    out = v * mul;
+    return true;
+}
+
+inline uint64_t net_name_hash(const std::string& name) {  // FNV-1a 64 over the lower-cased name
+    uint64_t h = 1469598103934665603ull;
+    for (char c : lower(name)) { h ^= uint64_t((unsigned char)c); h *= 1099511628211ull; }
+    return h;
+}
+
+struct ModelCard { std::string name, type; std::map<std::string, double> params; };
+
+struct Corner {
+    std::string process = "TT";
+    double vdd = 1.8, temp_c = 27.0;
+};
+
+class SpiceParser {
+public:
+    std::map<std::string, ModelCard> models;
+    std::vector<std::string> warnings;
+
+    explicit SpiceParser(Corner c = {}) : corner_(std::move(c)) {
+        corner_.process = upper(corner_.process);
+        node_map_["0"] = 0;
+        node_map_["gnd"] = 0;
+    }
+
+    static Netlist parse_file(const std::string& path, const Corner& c = {}) {
+        std::ifstream f(path);
+        if (!f) throw std::runtime_error("cannot open netlist '" + path + "'");
+        std::stringstream ss;
+        ss << f.rdbuf();
+        std::string name = path;
+        size_t slash = name.find_last_of('/');
+        if (slash != std::string::npos) name = name.substr(slash + 1);
+        SpiceParser p(c);
+        return p.parse_text(ss.str(), name);
+    }
+
+    Netlist parse_text(const std::string& text, const std::string& name = "netlist") {
+        std::vector<std::string> stmts = statements(text);
+        // pass 1: definitions (.subckt bodies, .param, .model), which may follow their first use
+        {
+            Subckt* cur = nullptr;
+            int depth = 0;
+            for (auto& st : stmts) {
+                auto tok = split(st);
+                if (tok.empty()) continue;
+                std::string first = upper(tok[0]);
+                if (first == ".SUBCKT") {
+                    if (depth++ == 0 && tok.size() >= 2) {
+                        cur = &subckts_[upper(tok[1])];
+                        cur->ports.clear();
+                        for (size_t i = 2; i < tok.size(); ++i) {
+                            if (tok[i].find('=') != std::string::npos) break;
+                            cur->ports.push_back(lower(tok[i]));
+                        }
+                        continue;
+                    }
+                } else if (first == ".ENDS") {
+                    if (--depth <= 0) { depth = 0; cur = nullptr; continue; }
+                }
+                if (cur) { cur->lines.push_back(st); continue; }
+                if (first == ".PARAM") {
+                    for (size_t i = 1; i < tok.size(); ++i) {
+                        size_t eq = tok[i].find('=');
+                        double v;
+                        if (eq != std::string::npos && parse_scaled(tok[i].substr(eq + 1), v)) params_[lower(tok[i].substr(0, eq))] = v;
+                    }
+                } else if (first == ".MODEL" && tok.size() >= 3) {
+                    ModelCard mc;
+                    mc.name = upper(tok[1]);
+                    std::string type = upper(tok[2]);
+                    size_t paren = type.find('(');
+                    std::vector<std::string> rest(tok.begin() + 3, tok.end());
+                    if (paren != std::string::npos) { rest.insert(rest.begin(), tok[2].substr(paren + 1)); type = type.substr(0, paren); }
+                    mc.type = type;
+                    for (auto& t : rest) {
+                        size_t eq = t.find('=');
+                        double v;
+                        if (eq != std::string::npos && parse_scaled(t.substr(eq + 1), v)) {
+                            std::string k = lower(t.substr(0, eq));
+                            while (!k.empty() && k.front() == '(') k.erase(k.begin());
+                            mc.params[k] = v;
+                        }
+                    }
+                    models[mc.name] = mc;
+                }
+            }
+        }
+        // pass 2: top-level elements
+        {
+            int depth = 0;
+            bool title_checked = false;
+            for (auto& st : stmts) {
+                auto tok = split(st);
+                if (tok.empty()) continue;
+                std::string first = upper(tok[0]);
+                if (first == ".SUBCKT") { ++depth; continue; }
+                if (first == ".ENDS") { if (depth > 0) --depth; continue; }
+                if (depth > 0) continue;
+                if (first == ".END") break;
+                (void)title_checked;
+                element_line(tok, "", {});
+            }
+        }
+        Netlist nl;
+        nl.name = name;
+        nl.num_nodes = next_node_ - 1;
+        nl.elements = std::move(elements_);
+        nl.ghost_map = std::move(ghosts_);
+        nl.node_names.assign(size_t(nl.num_nodes), "");
+        for (auto& kv : node_map_)
+            if (kv.second > 0 && kv.second <= nl.num_nodes) {
+                std::string& slot = nl.node_names[size_t(kv.second - 1)];
+                if (slot.empty() || kv.first < slot) slot = kv.first;
+            }
+        for (int i = 0; i < nl.num_nodes; ++i)
+            if (nl.node_names[size_t(i)].empty()) nl.node_names[size_t(i)] = "node_" + std::to_string(i + 1);
+        for (auto& ic : ic_raw_) {
+            auto it = node_map_.find(ic.first);
+            if (it != node_map_.end() && it->second > 0) nl.initial_conditions.emplace_back(it->second, ic.second);
+            else warnings.push_back(".ic names unknown node '" + ic.first + "'");
+        }
+        return nl;
+    }
+
+private:
+    struct Subckt { std::vector<std::string> ports, lines; };
+    Corner corner_;
+    std::unordered_map<std::string, int> node_map_;
+    int next_node_ = 1;
+    std::vector<Element> elements_;
+    std::map<std::string, Subckt> subckts_;
+    std::map<std::string, double> params_;
+    std::vector<GhostLink> ghosts_;
+    std::vector<std::pair<std::string, double>> ic_raw_;
+
+    // Joins `+` continuations, drops comment lines and trailing `;` / `$` comments. The first line of
+    // a deck is its title unless it already looks like an element or a directive.
+    static std::vector<std::string> statements(const std::string& text) {
+        std::vector<std::string> out;
+        std::istringstream in(text);
+        std::string line;
+        bool first_line = true;
+        while (std::getline(in, line)) {
+            if (!line.empty() && line.back() == '\r') line.pop_back();
+            size_t c = line.find_first_of(";$");
+            if (c != std::string::npos) line = line.substr(0, c);
+            size_t b = line.find_first_not_of(" \t");
+            if (b == std::string::npos) { first_line = false; continue; }
+            line = line.substr(b);
+            if (line[0] == '*') { first_line = false; continue; }
+            if (first_line) {
+                first_line = false;
+                char ch = char(std::toupper((unsigned char)line[0]));
+                bool looks_like_card = ch == '.' || ((std::string("RCLVIDMX").find(ch) != std::string::npos) && split(line).size() >= 3 &&
+                                                     line.find(' ') != std::string::npos && std::isalnum((unsigned char)line[1]));
+                if (!looks_like_card) continue;
+            }
+            if (line[0] == '+') {
+                if (!out.empty()) out.back() += " " + line.substr(1);
+                continue;
+            }
+            out.push_back(line);
+        }
+        return out;
+    }
+    static std::vector<std::string> split(const std::string& s) {
+        // parentheses and commas become separators except that "PULSE(" keeps its name as a token
+        std::string t;
+        for (char c : s) t += (c == '(' || c == ')' || c == ',') ? ' ' : c;
+        std::istringstream in(t);
+        std::vector<std::string> out;
+        std::string w;
+        while (in >> w) out.push_back(w);
+        // re-join "name = value" and "name= value"
+        std::vector<std::string> merged;
+        for (size_t i = 0; i < out.size(); ++i) {
+            if (out[i] == "=" && !merged.empty() && i + 1 < out.size()) { merged.back() += "=" + out[++i]; continue; }
+            if (!out[i].empty() && out[i].back() == '=' && i + 1 < out.size()) { merged.push_back(out[i] + out[i + 1]); ++i; continue; }
+            if (!out[i].empty() && out[i].front() == '=' && !merged.empty()) { merged.back() += out[i]; continue; }
+            merged.push_back(out[i]);
+        }
+        return merged;
+    }
+    double value(const std::string& raw) const {
+        std::string s = lower(raw);
+        while (!s.empty() && (s.front() == '\'' || s.front() == '{')) s.erase(s.begin());
+        while (!s.empty() && (s.back() == '\'' || s.back() == '}')) s.pop_back();
+        auto it = params_.find(s);
+        if (it != params_.end()) return it->second;
+        double v = 0.0;
+        return parse_scaled(s, v) ? v : 0.0;
+    }
+    int node(const std::string& raw, const std::string& prefix, const std::map<std::string, std::string>& alias) {
+        std::string n = lower(raw);
+        if (n == "0" || n == "gnd" || n == "gnd!" || n == "vss!") return 0;
+        std::string full;
+        auto al = alias.find(n);
+        if (al != alias.end()) full = al->second;
+        else if (prefix.empty()) full = n;
+        else full = prefix + "." + n;
+        if (full == "0" || full == "gnd") return 0;
+        auto it = node_map_.find(full);
+        if (it != node_map_.end()) return it->second;
+        node_map_[full] = next_node_;
+        return next_node_++;
+    }
+    std::string resolved_name(const std::string& raw, const std::string& prefix, const std::map<std::string, std::string>& alias) const {
+        std::string n = lower(raw);
+        if (n == "0" || n == "gnd") return "0";
+        auto al = alias.find(n);
+        if (al != alias.end()) return al->second;
+        return prefix.empty() ? n : prefix + "." + n;
+    }
+    SourceWaveform source(const std::vector<std::string>& tok, size_t from, bool scale_supply) const {
+        SourceWaveform w = SourceWaveform::make_dc(0.0);
+        size_t i = from;
+        bool have = false;
+        while (i < tok.size()) {
+            std::string u = upper(tok[i]);
+            if (u == "DC" && i + 1 < tok.size()) { w = SourceWaveform::make_dc(value(tok[i + 1])); have = true; i += 2; continue; }
+            if (u == "PULSE") {
+                double p[7] = {0, 0, 0, 0, 0, 0, 0};
+                size_t k = 0;
+                for (size_t j = i + 1; j < tok.size() && k < 7; ++j, ++k) p[k] = value(tok[j]);
+                if (k >= 7) return SourceWaveform::make_pulse(p[0], p[1], p[2], p[3], p[4], p[5], p[6]);
+                if (k >= 2) return SourceWaveform::make_pulse(p[0], p[1], p[2], p[3], p[4], k > 5 ? p[5] : 1e30, 0.0);
+                return w;
+            }
+            if (u == "SIN") {  // held at its peak: the element set has no sinusoid
+                double off = i + 1 < tok.size() ? value(tok[i + 1]) : 0.0, amp = i + 2 < tok.size() ? value(tok[i + 2]) : 0.0;
+                return SourceWaveform::make_dc(off + amp);
+            }
+            if (u == "AC") { i += 2; continue; }
+            if (!have) { w = SourceWaveform::make_dc(value(tok[i])); have = true; }
+            ++i;
+        }
+        // decks written for a 1.8 V (or 1.0 V) supply follow the requested supply voltage
+        if (scale_supply && w.kind == SourceWaveform::Dc && (std::fabs(w.dc - 1.8) < 0.2 || std::fabs(w.dc - 1.0) < 0.2)) w.dc *= corner_.vdd / 1.8;
+        return w;
+    }
+    MosfetLevel1 mos_model(const std::string& model_name, double w, double l) const {
+        MosfetLevel1 m;
+        m.kind = model_name.find('P') != std::string::npos ? MosType::Pmos : MosType::Nmos;
+        double vth = 0.5, u0 = 0.04, tox = 2e-9, lambda = 0.0, kp = -1.0;
+        auto it = models.find(model_name);
+        if (it != models.end()) {
+            if (it->second.type.find("PMOS") != std::string::npos) m.kind = MosType::Pmos;
+            else if (it->second.type.find("NMOS") != std::string::npos) m.kind = MosType::Nmos;
+            auto& p = it->second.params;
+            if (p.count("vto")) vth = p.at("vto");
+            if (p.count("kp")) kp = std::fabs(p.at("kp"));
+            if (p.count("u0")) u0 = p.at("u0") * 1e-4;
+            if (p.count("tox")) tox = p.at("tox");
+            if (p.count("lambda")) lambda = std::max(0.0, p.at("lambda"));
+        }
+        double mob = std::pow(300.15 / (corner_.temp_c + 273.15), 1.5);
+        vth -= 0.002 * (corner_.temp_c - 27.0);
+        const bool is_n = m.kind == MosType::Nmos;
+        double cm = 1.0, dv = 0.0;
+        const std::string& pr = corner_.process;
+        if (pr == "FF") { cm = 1.15; dv = -0.1; }
+        else if (pr == "SS") { cm = 0.85; dv = 0.1; }
+        else if (pr == "FS") { cm = is_n ? 1.10 : 0.90; dv = is_n ? -0.1 : 0.1; }
+        else if (pr == "SF") { cm = is_n ? 0.90 : 1.10; dv = is_n ? 0.1 : -0.1; }
+        mob *= cm;
+        // thresholds are stored as magnitudes for both polarities
+        m.vth = std::fabs(vth) + dv;
+        const double cox = 3.9 * 8.854e-12 / tox;
+        m.beta = (kp > 0 ? kp * mob : u0 * mob * cox) * (w / l);
+        m.lambda = lambda;
+        return m;
+    }
+
+    void element_line(const std::vector<std::string>& tok, const std::string& prefix, const std::map<std::string, std::string>& alias) {
+        std::string kw = upper(tok[0]);
+        char ch = kw[0];
+        auto N = [&](size_t i) { return node(tok[i], prefix, alias); };
+        switch (ch) {
+            case 'R': if (tok.size() >= 4) { double r = value(tok[3]); elements_.push_back(Element::resistor(N(1), N(2), r != 0.0 ? r : 1e-3)); } return;
+            case 'C': if (tok.size() >= 4) elements_.push_back(Element::capacitor(N(1), N(2), value(tok[3]))); return;
+            case 'L': if (tok.size() >= 4) elements_.push_back(Element::inductor(N(1), N(2), value(tok[3]))); return;
+            case 'V': if (tok.size() >= 4) { int p = N(1), n = N(2); elements_.push_back(Element::vsource(p, n, source(tok, 3, true))); } return;
+            case 'I': if (tok.size() >= 4) { int p = N(1), n = N(2); elements_.push_back(Element::isource(p, n, source(tok, 3, false))); } return;
+            case 'D':
+                if (tok.size() >= 4) {
+                    DiodeModel dm;
+                    auto it = models.find(upper(tok[3]));
+                    if (it != models.end()) {
+                        if (it->second.params.count("is")) dm.is = it->second.params.at("is");
+                        if (it->second.params.count("n")) dm.n = it->second.params.at("n");
+                    }
+                    dm.vt = 8.617333e-5 * (corner_.temp_c + 273.15);
+                    int a = N(1), c = N(2);
+                    elements_.push_back(Element::make_diode(a, c, dm));
+                }
+                return;
+            case 'M':
+                if (tok.size() >= 6) {
+                    int d = N(1), g = N(2), s = N(3), b = N(4);
+                    double w = 1e-6, l = 100e-9;
+                    for (size_t i = 6; i < tok.size(); ++i) {
+                        size_t eq = tok[i].find('=');
+                        if (eq == std::string::npos) continue;
+                        std::string k = lower(tok[i].substr(0, eq));
+                        if (k == "w") w = value(tok[i].substr(eq + 1));
+                        else if (k == "l") l = value(tok[i].substr(eq + 1));
+                    }
+                    elements_.push_back(Element::mosfet(d, g, s, b, mos_model(upper(tok[5]), w, l)));
+                }
+                return;
+            case 'X': {
+                if (tok.size() < 3) return;
+                size_t last = tok.size() - 1;
+                while (last > 1 && tok[last].find('=') != std::string::npos) --last;  // instance parameters
+                auto it = subckts_.find(upper(tok[last]));
+                if (it == subckts_.end()) { warnings.push_back("unknown subcircuit '" + tok[last] + "'"); return; }
+                const Subckt& def = it->second;
+                if (def.ports.size() != last - 1) { warnings.push_back("port count mismatch on '" + tok[0] + "'"); return; }
+                std::map<std::string, std::string> inner;
+                for (size_t i = 0; i < def.ports.size(); ++i) {
+                    node(tok[i + 1], prefix, alias);
+                    inner[def.ports[i]] = resolved_name(tok[i + 1], prefix, alias);
+                }
+                std::string np = prefix.empty() ? lower(tok[0]) : prefix + "." + lower(tok[0]);
+                for (auto& ln : def.lines) {
+                    auto t = split(ln);
+                    if (!t.empty()) element_line(t, np, inner);
+                }
+                return;
+            }
+            default: break;
+        }
+        if (kw == ".IC") {
+            for (size_t i = 1; i < tok.size(); ++i) {
+                // after splitting, "V(out)=0.5" arrives as "V", "out", "=0.5" or "out=0.5"
+                std::string t = tok[i];
+                if (upper(t) == "V") continue;
+                size_t eq = t.find('=');
+                if (eq == std::string::npos || eq == 0) continue;
+                ic_raw_.emplace_back(resolved_name(t.substr(0, eq), prefix, alias), value(t.substr(eq + 1)));
+            }
+        } else if (kw == ".GHOST" && tok.size() >= 4) {
+            ghosts_.push_back({net_name_hash(tok[1]), std::atoi(tok[2].c_str()), uint32_t(std::atoi(tok[3].c_str()))});
+        } else if (kw == ".NODEMAP" && tok.size() >= 3) {
+            int idx = std::atoi(tok[2].c_str());
+            node_map_[lower(tok[1])] = idx;
+            if (idx >= next_node_) next_node_ = idx + 1;
+        } else if (kw == ".INCLUDE" || kw == ".LIB") {
+            warnings.push_back(kw + " is not followed: " + (tok.size() > 1 ? tok[1] : std::string("?")));
+        }
+    }
+};
+
+}  // namespace nspice
