@@ -1,0 +1,309 @@
+// FP64 CSR sparse matrix-vector product for the circuit simulator, with the matrix resident on the
+// device, and a Jacobi-preconditioned BiCGSTAB built on it.
+//
+// Role in the reference: nangila-spice/nangila-node/cuda/cusparse_solver.cu:17-123 (a cuSPARSE SpMV
+// behind four C calls: init / load_matrix / spmv / free, with the vectors copied over PCIe on every
+// call). Here the product is a hand-written kernel and the vectors can stay on the device.
+//
+// Kernel design ("row blocks"): at load time the host packs consecutive rows into blocks of at most
+// kCap non-zeros. A CTA streams its block's values and column indices with coalesced loads, gathers
+// x through the read-only path, parks the products in shared memory and then reduces each row from
+// there with 1..32 lanes per row (chosen from the block's mean row length), so short rows
+// (3 entries for an RC ladder) cost no idle lanes and long rows still reduce in parallel. A row
+// longer than kCap gets a block of its own and a CTA-wide strided reduction.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include <new>
+#include <vector>
+
+#include "nangila_spice_kernels.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kCap = 2048;  // products staged per CTA: 16 KB of shared memory
+
+__global__ void __launch_bounds__(kThreads) spmv_row_blocks_kernel(const int* __restrict__ row_ptr, const int* __restrict__ col,
+                                                                    const double* __restrict__ val, const double* __restrict__ x,
+                                                                    double* __restrict__ y, const int* __restrict__ row_blocks) {
+    __shared__ double prod[kCap];
+    __shared__ double warp_sums[kThreads / 32];
+    const int tid = threadIdx.x;
+    const int r0 = row_blocks[blockIdx.x], r1 = row_blocks[blockIdx.x + 1];
+    const int k0 = row_ptr[r0], k1 = row_ptr[r1];
+    const int nnz = k1 - k0, nrows = r1 - r0;
+    if (nnz <= kCap) {
+        // stage products; four independent loads per thread in flight
+        int k = tid;
+        for (; k + 3 * kThreads < nnz; k += 4 * kThreads) {
+            int c0 = __ldg(col + k0 + k), c1 = __ldg(col + k0 + k + kThreads), c2 = __ldg(col + k0 + k + 2 * kThreads),
+                c3 = __ldg(col + k0 + k + 3 * kThreads);
+            double v0 = __ldg(val + k0 + k), v1 = __ldg(val + k0 + k + kThreads), v2 = __ldg(val + k0 + k + 2 * kThreads),
+                   v3 = __ldg(val + k0 + k + 3 * kThreads);
+            prod[k] = v0 * __ldg(x + c0);
+            prod[k + kThreads] = v1 * __ldg(x + c1);
+            prod[k + 2 * kThreads] = v2 * __ldg(x + c2);
+            prod[k + 3 * kThreads] = v3 * __ldg(x + c3);
+        }
+        for (; k < nnz; k += kThreads) prod[k] = __ldg(val + k0 + k) * __ldg(x + __ldg(col + k0 + k));
+        __syncthreads();
+        // lanes per row: largest power of two not above the mean row length, 1..32
+        int mean = nrows > 0 ? nnz / nrows : 1;
+        int lanes = 1;
+        while (lanes < 32 && lanes * 2 <= mean) lanes *= 2;
+        const int group = tid / lanes, lane = tid % lanes, groups = kThreads / lanes;
+        // every lane of a warp runs the same number of iterations, so the shuffles below are uniform
+        const int iters = (nrows + groups - 1) / groups;
+        for (int it = 0; it < iters; ++it) {
+            const int r = r0 + it * groups + group;
+            double acc = 0.0;
+            if (r < r1) {
+                const int s = __ldg(row_ptr + r) - k0, e = __ldg(row_ptr + r + 1) - k0;
+                for (int j = s + lane; j < e; j += lanes) acc += prod[j];
+            }
+            for (int off = lanes >> 1; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off, lanes);
+            if (lane == 0 && r < r1) y[r] = acc;
+        }
+    } else {
+        // one long row (the builder never mixes a long row with others)
+        double acc = 0.0;
+        for (int k = tid; k < nnz; k += kThreads) acc += __ldg(val + k0 + k) * __ldg(x + __ldg(col + k0 + k));
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
+        if ((tid & 31) == 0) warp_sums[tid >> 5] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double s = 0.0;
+            for (int w = 0; w < kThreads / 32; ++w) s += warp_sums[w];
+            y[r0] = s;
+        }
+    }
+}
+
+// ---- vector kernels of the Krylov solver -------------------------------------------------------
+
+constexpr int kRedBlocks = 296;  // two CTAs per SM
+
+// partial[2 * b + {0, 1}] = sum over the CTA's slice of a1*b1 and a2*b2 (a2 may be null)
+__global__ void __launch_bounds__(kThreads) dot2_partial_kernel(const double* __restrict__ a1, const double* __restrict__ b1,
+                                                                 const double* __restrict__ a2, const double* __restrict__ b2, int n,
+                                                                 double* __restrict__ partial) {
+    __shared__ double s1[kThreads / 32], s2[kThreads / 32];
+    double p = 0.0, q = 0.0;
+    for (int i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
+        p += a1[i] * b1[i];
+        if (a2) q += a2[i] * b2[i];
+    }
+    for (int off = 16; off > 0; off >>= 1) { p += __shfl_down_sync(0xffffffffu, p, off); q += __shfl_down_sync(0xffffffffu, q, off); }
+    if ((threadIdx.x & 31) == 0) { s1[threadIdx.x >> 5] = p; s2[threadIdx.x >> 5] = q; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t1 = 0.0, t2 = 0.0;
+        for (int w = 0; w < kThreads / 32; ++w) { t1 += s1[w]; t2 += s2[w]; }
+        partial[2 * blockIdx.x] = t1;
+        partial[2 * blockIdx.x + 1] = t2;
+    }
+}
+
+// fixed-order sum of the partials: the same inputs give the same bits on every run
+__global__ void dot2_final_kernel(const double* __restrict__ partial, int blocks, double* __restrict__ out) {
+    if (threadIdx.x < 2) {
+        double s = 0.0;
+        for (int b = 0; b < blocks; ++b) s += partial[2 * b + threadIdx.x];
+        out[threadIdx.x] = s;
+    }
+}
+
+// p = r + beta (p - omega v);  ph = p / diag
+__global__ void update_p_kernel(double* p, double* ph, const double* r, const double* v, const double* inv_diag, double beta,
+                                double omega, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { double t = r[i] + beta * (p[i] - omega * v[i]); p[i] = t; ph[i] = t * inv_diag[i]; }
+}
+// s = r - alpha v;  sh = s / diag
+__global__ void update_s_kernel(double* s, double* sh, const double* r, const double* v, const double* inv_diag, double alpha, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { double t = r[i] - alpha * v[i]; s[i] = t; sh[i] = t * inv_diag[i]; }
+}
+// x += alpha ph + omega sh;  r = s - omega t
+__global__ void update_xr_kernel(double* x, double* r, const double* ph, const double* sh, const double* s, const double* t, double alpha,
+                                 double omega, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { x[i] += alpha * ph[i] + omega * sh[i]; r[i] = s[i] - omega * t[i]; }
+}
+__global__ void residual_init_kernel(double* r, double* r0, const double* b, const double* ax, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { double t = b[i] - ax[i]; r[i] = t; r0[i] = t; }
+}
+
+}  // namespace
+
+struct NangilaSpmv {
+    int n = 0, nnz = 0, n_blocks = 0;
+    int *d_row_ptr = nullptr, *d_col = nullptr, *d_blocks = nullptr;
+    double *d_val = nullptr, *d_x = nullptr, *d_y = nullptr;
+    double* d_work = nullptr;   // 9 solver vectors + inverse diagonal, allocated on first solve
+    double* d_partial = nullptr;  // reduction scratch: 2 * kRedBlocks + 2
+    std::vector<double> h_inv_diag;
+};
+
+static void free_arrays(NangilaSpmv* c) {
+    cudaFree(c->d_row_ptr); cudaFree(c->d_col); cudaFree(c->d_blocks); cudaFree(c->d_val); cudaFree(c->d_x); cudaFree(c->d_y);
+    cudaFree(c->d_work); cudaFree(c->d_partial);
+    c->d_row_ptr = c->d_col = c->d_blocks = nullptr;
+    c->d_val = c->d_x = c->d_y = c->d_work = c->d_partial = nullptr;
+}
+
+extern "C" int nangila_spmv_build_row_blocks(const int* row_ptr, int n, int* out, int max_out) {
+    // out[0] = 0, out[b + 1] = first row after block b; returns the number of blocks (or the number
+    // needed when out is null / too small)
+    int count = 0, r = 0;
+    auto emit = [&](int v) { if (out && count + 1 < max_out) out[count + 1] = v; ++count; };
+    if (out && max_out > 0) out[0] = 0;
+    while (r < n) {
+        int start = r;
+        int base = row_ptr[r];
+        if (row_ptr[r + 1] - base > kCap) { ++r; emit(r); continue; }
+        while (r < n && row_ptr[r + 1] - base <= kCap) ++r;
+        if (r == start) ++r;
+        emit(r);
+    }
+    return count;
+}
+
+extern "C" NangilaSpmv* nangila_spmv_create(void) { return new (std::nothrow) NangilaSpmv(); }
+
+extern "C" void nangila_spmv_destroy(NangilaSpmv* c) {
+    if (!c) return;
+    free_arrays(c);
+    delete c;
+}
+
+extern "C" int nangila_spmv_load(NangilaSpmv* c, int n, int nnz, const int* row_ptr, const int* col, const double* val) {
+    if (!c || n <= 0 || nnz < 0 || !row_ptr || !col || !val) return int(cudaErrorInvalidValue);
+    if (row_ptr[0] != 0 || row_ptr[n] != nnz) return int(cudaErrorInvalidValue);
+    for (int r = 0; r < n; ++r) if (row_ptr[r + 1] < row_ptr[r]) return int(cudaErrorInvalidValue);
+    for (int k = 0; k < nnz; ++k) if (col[k] < 0 || col[k] >= n) return int(cudaErrorInvalidValue);
+    free_arrays(c);
+    c->n = n; c->nnz = nnz;
+    int nb = nangila_spmv_build_row_blocks(row_ptr, n, nullptr, 0);
+    std::vector<int> blocks(size_t(nb) + 1);
+    nangila_spmv_build_row_blocks(row_ptr, n, blocks.data(), nb + 1);
+    c->n_blocks = nb;
+    c->h_inv_diag.assign(size_t(n), 1.0);
+    for (int r = 0; r < n; ++r)
+        for (int k = row_ptr[r]; k < row_ptr[r + 1]; ++k)
+            if (col[k] == r && fabs(val[k]) > 1e-300) c->h_inv_diag[size_t(r)] = 1.0 / val[k];
+    cudaError_t e;
+#define NG_TRY(call) do { e = (call); if (e != cudaSuccess) { free_arrays(c); return int(e); } } while (0)
+    NG_TRY(cudaMalloc(&c->d_row_ptr, sizeof(int) * (size_t(n) + 1)));
+    NG_TRY(cudaMalloc(&c->d_col, sizeof(int) * size_t(nnz > 0 ? nnz : 1)));
+    NG_TRY(cudaMalloc(&c->d_val, sizeof(double) * size_t(nnz > 0 ? nnz : 1)));
+    NG_TRY(cudaMalloc(&c->d_blocks, sizeof(int) * (size_t(nb) + 1)));
+    NG_TRY(cudaMalloc(&c->d_x, sizeof(double) * size_t(n)));
+    NG_TRY(cudaMalloc(&c->d_y, sizeof(double) * size_t(n)));
+    NG_TRY(cudaMemcpy(c->d_row_ptr, row_ptr, sizeof(int) * (size_t(n) + 1), cudaMemcpyHostToDevice));
+    NG_TRY(cudaMemcpy(c->d_col, col, sizeof(int) * size_t(nnz), cudaMemcpyHostToDevice));
+    NG_TRY(cudaMemcpy(c->d_val, val, sizeof(double) * size_t(nnz), cudaMemcpyHostToDevice));
+    NG_TRY(cudaMemcpy(c->d_blocks, blocks.data(), sizeof(int) * (size_t(nb) + 1), cudaMemcpyHostToDevice));
+    return 0;
+}
+
+extern "C" int nangila_spmv_update_values(NangilaSpmv* c, const double* val) {
+    if (!c || !c->d_val || !val) return int(cudaErrorInvalidValue);
+    return int(cudaMemcpy(c->d_val, val, sizeof(double) * size_t(c->nnz), cudaMemcpyHostToDevice));
+}
+
+extern "C" int nangila_spmv_launch(const int* d_row_ptr, const int* d_col, const double* d_val, const double* d_x, double* d_y,
+                                   const int* d_row_blocks, int n_blocks, cudaStream_t stream) {
+    if (n_blocks <= 0) return 0;
+    spmv_row_blocks_kernel<<<n_blocks, kThreads, 0, stream>>>(d_row_ptr, d_col, d_val, d_x, d_y, d_row_blocks);
+    return int(cudaGetLastError());
+}
+
+extern "C" int nangila_spmv_device(NangilaSpmv* c, const double* d_x, double* d_y, cudaStream_t stream) {
+    if (!c || !c->d_val || !d_x || !d_y) return int(cudaErrorInvalidValue);
+    return nangila_spmv_launch(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y, c->d_blocks, c->n_blocks, stream);
+}
+
+extern "C" int nangila_spmv_host(NangilaSpmv* c, const double* h_x, double* h_y) {
+    if (!c || !c->d_val || !h_x || !h_y) return int(cudaErrorInvalidValue);
+    cudaError_t e = cudaMemcpy(c->d_x, h_x, sizeof(double) * size_t(c->n), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return int(e);
+    int rc = nangila_spmv_device(c, c->d_x, c->d_y, 0);
+    if (rc) return rc;
+    return int(cudaMemcpy(h_y, c->d_y, sizeof(double) * size_t(c->n), cudaMemcpyDeviceToHost));
+}
+
+extern "C" int nangila_spmv_dims(const NangilaSpmv* c, int* n, int* nnz, int* n_blocks) {
+    if (!c) return int(cudaErrorInvalidValue);
+    if (n) *n = c->n;
+    if (nnz) *nnz = c->nnz;
+    if (n_blocks) *n_blocks = c->n_blocks;
+    return 0;
+}
+
+// Solves A x = b (x starts at 0) with vectors resident on the device; per iteration two SpMVs, three
+// fused vector kernels and two 16-byte reads of reduction results by the host.
+extern "C" int nangila_spmv_bicgstab(NangilaSpmv* c, const double* h_b, double* h_x, double tol, int max_iter, int* iterations,
+                                     double* rel_residual) {
+    if (!c || !c->d_val || !h_b || !h_x) return int(cudaErrorInvalidValue);
+    const int n = c->n;
+    const size_t N = size_t(n);
+    cudaError_t e;
+    if (!c->d_work) {
+        e = cudaMalloc(&c->d_work, sizeof(double) * N * 11);
+        if (e != cudaSuccess) return int(e);
+        e = cudaMalloc(&c->d_partial, sizeof(double) * (2 * kRedBlocks + 2));
+        if (e != cudaSuccess) return int(e);
+    }
+    double *x = c->d_work, *r = x + N, *r0 = r + N, *p = r0 + N, *v = p + N, *s = v + N, *t = s + N, *ph = t + N, *sh = ph + N, *b = sh + N,
+           *inv = b + N;
+    double* out = c->d_partial + 2 * kRedBlocks;
+    const int grid = (n + kThreads - 1) / kThreads;
+    auto dots = [&](const double* a1, const double* b1, const double* a2, const double* b2, double res[2]) -> cudaError_t {
+        dot2_partial_kernel<<<kRedBlocks, kThreads>>>(a1, b1, a2, b2, n, c->d_partial);
+        dot2_final_kernel<<<1, 32>>>(c->d_partial, kRedBlocks, out);
+        return cudaMemcpy(res, out, 2 * sizeof(double), cudaMemcpyDeviceToHost);
+    };
+    if ((e = cudaMemcpy(b, h_b, sizeof(double) * N, cudaMemcpyHostToDevice)) != cudaSuccess) return int(e);
+    if ((e = cudaMemcpy(inv, c->h_inv_diag.data(), sizeof(double) * N, cudaMemcpyHostToDevice)) != cudaSuccess) return int(e);
+    if ((e = cudaMemset(x, 0, sizeof(double) * N * 9)) != cudaSuccess) return int(e);
+    residual_init_kernel<<<grid, kThreads>>>(r, r0, b, v, n);  // x = 0, so A x = v = 0
+    double d[2];
+    if ((e = dots(b, b, r, r, d)) != cudaSuccess) return int(e);
+    double bnorm = sqrt(d[0]);
+    if (bnorm == 0.0) bnorm = 1.0;
+    double rel = sqrt(d[1]) / bnorm, rho = 1.0, alpha = 1.0, omega = 1.0;
+    int it = 0;
+    bool ok = rel < tol;
+    while (!ok && it < max_iter) {
+        if ((e = dots(r0, r, nullptr, nullptr, d)) != cudaSuccess) return int(e);
+        double rho_new = d[0];
+        if (fabs(rho_new) < 1e-300) break;
+        double beta = (rho_new / rho) * (alpha / omega);
+        rho = rho_new;
+        update_p_kernel<<<grid, kThreads>>>(p, ph, r, v, inv, beta, omega, n);
+        nangila_spmv_device(c, ph, v, 0);
+        if ((e = dots(r0, v, nullptr, nullptr, d)) != cudaSuccess) return int(e);
+        if (fabs(d[0]) < 1e-300) break;
+        alpha = rho / d[0];
+        update_s_kernel<<<grid, kThreads>>>(s, sh, r, v, inv, alpha, n);
+        nangila_spmv_device(c, sh, t, 0);
+        if ((e = dots(t, s, t, t, d)) != cudaSuccess) return int(e);
+        omega = d[1] > 0.0 ? d[0] / d[1] : 0.0;
+        update_xr_kernel<<<grid, kThreads>>>(x, r, ph, sh, s, t, alpha, omega, n);
+        ++it;
+        if ((e = dots(r, r, nullptr, nullptr, d)) != cudaSuccess) return int(e);
+        rel = sqrt(d[0]) / bnorm;
+        if (rel < tol) { ok = true; break; }
+        if (omega == 0.0) break;
+    }
+    if ((e = cudaMemcpy(h_x, x, sizeof(double) * N, cudaMemcpyDeviceToHost)) != cudaSuccess) return int(e);
+    if (iterations) *iterations = it;
+    if (rel_residual) *rel_residual = rel;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return int(e);
+    return ok ? 0 : -1;
+}

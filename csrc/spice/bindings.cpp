@@ -1,0 +1,284 @@
+// Python module nangila_spice._native: the simulator core for tests, the orchestrator and notebooks.
+// Netlists cross the boundary as JSON text (the partition-file form), numeric data as lists.
+#include <pybind11/functional.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "balancer.hpp"
+#include "nz.hpp"
+#include "parser.hpp"
+#include "partitioned.hpp"
+#include "pvt.hpp"
+#include "transient.hpp"
+
+namespace py = pybind11;
+using namespace nspice;
+
+static LinearBackend backend_of(const std::string& s) {
+    if (s == "dense") return LinearBackend::Dense;
+    if (s == "krylov") return LinearBackend::Krylov;
+    if (s == "lu" || s.empty()) return LinearBackend::SparseLU;
+    throw std::invalid_argument("solver must be 'lu', 'dense' or 'krylov'");
+}
+
+static py::dict stats_dict(const SimStats& s) {
+    py::dict d;
+    d["total_steps"] = s.total_steps; d["wall_time_secs"] = s.wall_time_secs; d["prediction_hits"] = s.prediction_hits;
+    d["prediction_misses"] = s.prediction_misses; d["rollbacks"] = s.rollbacks; d["completed"] = s.completed;
+    d["hit_rate"] = s.hit_rate();
+    return d;
+}
+
+static const char* class_name(SignalClass c) {
+    switch (c) {
+        case SignalClass::Smooth: return "Smooth";
+        case SignalClass::Decaying: return "Decaying";
+        case SignalClass::Stiff: return "Stiff";
+        default: return "Unknown";
+    }
+}
+
+PYBIND11_MODULE(_native, m) {
+    m.doc() = "nangila-spice native core";
+
+    m.def("parse_scaled", [](const std::string& s) -> py::object { double v; if (!parse_scaled(s, v)) return py::none(); return py::float_(v); });
+    m.def("net_name_hash", &net_name_hash);
+    m.def("parse_spice", [](const std::string& text, const std::string& name, const std::string& process, double vdd, double temp) {
+        Corner c; c.process = process; c.vdd = vdd; c.temp_c = temp;
+        SpiceParser p(c);
+        Netlist nl = p.parse_text(text, name);
+        return py::make_tuple(nl.to_json().dump(), p.warnings);
+    }, py::arg("text"), py::arg("name") = "netlist", py::arg("process") = "TT", py::arg("vdd") = 1.8, py::arg("temp") = 27.0);
+    m.def("netlist_roundtrip", [](const std::string& js) { return Netlist::from_json(Json::parse(js)).to_json().dump(); });
+    m.def("source_value", [](const std::string& js, double t) { return SourceWaveform::from_json(Json::parse(js)).value_at(t); });
+
+    // ---- simulation ---------------------------------------------------------------------------
+    m.def("simulate", [](const std::string& netlist_json, double tstop, double dt, double reltol, const std::string& solver, uint32_t record_every,
+                         uint32_t predict_depth, std::vector<std::tuple<uint32_t, double, std::vector<std::pair<uint64_t, double>>>> inject,
+                         std::vector<double> rollbacks) {
+        Netlist nl = Netlist::from_json(Json::parse(netlist_json));
+        std::vector<std::string> names = nl.names_or_default();
+        GhostBuffer ghosts(predict_depth);
+        for (auto& g : nl.ghost_map) ghosts.add(GhostNode(g.net_id, g.owner));
+        SimConfig cfg;
+        cfg.tstop = tstop; cfg.dt = dt; cfg.reltol = reltol; cfg.record_every = std::max(1u, record_every); cfg.predict_depth = predict_depth;
+        CommLayer comm(0, 1);
+        for (auto& msg : inject) { ResidualMessage r; r.from = std::get<0>(msg); r.time = std::get<1>(msg); r.updates = std::get<2>(msg); comm.inject_message(r); }
+        for (double t : rollbacks) comm.inject_rollback({1, t});
+        TransientSolver s(std::move(nl), std::move(ghosts), std::move(comm), cfg);
+        s.engine().newton.config.reltol = reltol;
+        s.engine().newton.linear.backend = backend_of(solver);
+        PartitionState fin(0);
+        {
+            py::gil_scoped_release rel;
+            fin = s.run();
+        }
+        std::vector<double> t;
+        std::vector<std::vector<double>> v;
+        for (auto& p : s.waveform) { t.push_back(p.time); v.push_back(p.values); }
+        py::dict out;
+        out["node_names"] = names; out["time"] = t; out["values"] = v; out["final"] = fin.voltages; out["stats"] = stats_dict(s.stats);
+        py::dict nr;
+        nr["total_iterations"] = s.engine().newton.stats.total_iterations; nr["linear_solves"] = s.engine().newton.stats.linear_solves;
+        nr["failed"] = s.engine().newton.stats.failed_count; nr["be_fallbacks"] = s.engine().be_fallbacks;
+        out["newton"] = nr;
+        return out;
+    }, py::arg("netlist_json"), py::arg("tstop"), py::arg("dt"), py::arg("reltol") = 1e-3, py::arg("solver") = "lu", py::arg("record_every") = 1,
+       py::arg("predict_depth") = 5, py::arg("inject") = std::vector<std::tuple<uint32_t, double, std::vector<std::pair<uint64_t, double>>>>{},
+       py::arg("rollbacks") = std::vector<double>{});
+
+    m.def("dc_operating_point", [](const std::string& netlist_json) {
+        SolverEngine e(Netlist::from_json(Json::parse(netlist_json)));
+        PartitionState out(0);
+        bool ok = e.solve_dc(e.seeded_state(), out);
+        return py::make_tuple(ok, ok ? out.voltages : e.seeded_state().voltages);
+    });
+
+    m.def("simulate_partitioned", [](std::vector<std::string> parts_json, double tstop, double dt, double reltol, uint32_t predict_depth, bool compress,
+                                     uint32_t record_every) {
+        std::vector<Netlist> parts;
+        for (auto& js : parts_json) parts.push_back(Netlist::from_json(Json::parse(js)));
+        PartitionedConfig cfg;
+        cfg.tstop = tstop; cfg.dt = dt; cfg.reltol = reltol; cfg.predict_depth = predict_depth; cfg.compress = compress; cfg.record_every = std::max(1u, record_every);
+        PartitionedRunner r(std::move(parts), cfg);
+        {
+            py::gil_scoped_release rel;
+            r.run();
+        }
+        std::vector<double> t;
+        std::vector<std::vector<double>> v;
+        for (auto& p : r.waveform) { t.push_back(p.time); v.push_back(p.values); }
+        py::dict st;
+        st["steps"] = r.stats.steps; st["prediction_hits"] = r.stats.prediction_hits; st["prediction_misses"] = r.stats.prediction_misses;
+        st["resolves"] = r.stats.resolves; st["messages"] = r.stats.messages; st["bytes_sent"] = r.stats.bytes_sent; st["codec_ratio"] = r.stats.codec_ratio;
+        st["completed"] = r.stats.completed; st["wall_time_secs"] = r.stats.wall_time_secs; st["unconverged_steps"] = r.stats.unconverged_steps;
+        st["final_depth"] = r.stats.final_depth;
+        py::dict out;
+        out["node_names"] = r.names; out["time"] = t; out["values"] = v; out["stats"] = st;
+        return out;
+    }, py::arg("partitions"), py::arg("tstop"), py::arg("dt"), py::arg("reltol") = 1e-3, py::arg("predict_depth") = 5, py::arg("compress") = true,
+       py::arg("record_every") = 1);
+
+    // ---- linear algebra -----------------------------------------------------------------------
+    m.def("solve_csr", [](int n, std::vector<int> row_ptr, std::vector<int> col, std::vector<double> val, std::vector<double> rhs, const std::string& solver) {
+        CsrMatrix a(n);
+        a.row_ptr = std::move(row_ptr); a.col = std::move(col); a.val = std::move(val); a.rhs = std::move(rhs);
+        if (int(a.row_ptr.size()) != n + 1 || a.col.size() != a.val.size() || int(a.rhs.size()) != n) throw std::invalid_argument("inconsistent CSR arrays");
+        LinearSolver s;
+        s.backend = backend_of(solver);
+        bool ok = s.solve(a);
+        return py::make_tuple(ok, a.solution, s.stats.krylov_iterations);
+    }, py::arg("n"), py::arg("row_ptr"), py::arg("col"), py::arg("val"), py::arg("rhs"), py::arg("solver") = "lu");
+    m.def("csr_spmv", [](int n, std::vector<int> row_ptr, std::vector<int> col, std::vector<double> val, std::vector<double> x) {
+        CsrMatrix a(n);
+        a.row_ptr = std::move(row_ptr); a.col = std::move(col); a.val = std::move(val);
+        return a.spmv(x);
+    });
+    m.def("mna_matrix", [](const std::string& netlist_json, double dt, double time) {
+        Netlist nl = Netlist::from_json(Json::parse(netlist_json));
+        Assembler as(nl);
+        std::vector<double> zero(size_t(as.size), 0.0);
+        as.stamp_linear(zero, {}, dt, time, Integration::BackwardEuler, {});
+        as.stamp_nonlinear(zero);
+        return py::make_tuple(as.size, as.m.row_ptr, as.m.col, as.m.val, as.m.rhs);
+    });
+
+    // ---- devices ------------------------------------------------------------------------------
+    m.def("diode_eval", [](double vd, double is, double n, double vt) { DiodeModel d; d.is = is; d.n = n; d.vt = vt; double i, g; d.eval(vd, i, g); return py::make_tuple(i, g); },
+          py::arg("vd"), py::arg("is_") = 1e-14, py::arg("n") = 1.0, py::arg("vt") = 0.02585);
+    m.def("mosfet_eval", [](double vgs, double vds, bool pmos, double vth, double beta, double lambda) {
+        MosfetLevel1 f; f.kind = pmos ? MosType::Pmos : MosType::Nmos; f.vth = vth; f.beta = beta; f.lambda = lambda;
+        double id, gm, gds; MosRegion r;
+        f.evaluate(vgs, vds, id, gm, gds, r);
+        return py::make_tuple(id, gm, gds, r == MosRegion::Cutoff ? "Cutoff" : r == MosRegion::Linear ? "Linear" : "Saturation");
+    }, py::arg("vgs"), py::arg("vds"), py::arg("pmos") = false, py::arg("vth") = 0.5, py::arg("beta") = 1e-3, py::arg("lambda_") = 0.1);
+
+    // ---- prediction ---------------------------------------------------------------------------
+    py::class_<GhostNode>(m, "GhostNode")
+        .def(py::init<uint64_t, uint32_t>())
+        .def("predict", &GhostNode::predict)
+        .def("predict_named", [](const GhostNode& g, double t) { Prediction p = g.predict_named(t); return py::make_tuple(p.value, std::string(p.predictor)); })
+        .def("apply_correction", &GhostNode::apply_correction)
+        .def("signal_class", [](const GhostNode& g) { return std::string(class_name(classify_signal(g.signal))); })
+        .def_readonly("confidence", &GhostNode::confidence)
+        .def_readonly("gradient", &GhostNode::gradient)
+        .def_readonly("last_known_voltage", &GhostNode::last_known_voltage);
+    py::class_<AdaptiveConfidence>(m, "AdaptiveConfidence")
+        .def(py::init<uint32_t>(), py::arg("base_depth") = 5)
+        .def("update", &AdaptiveConfidence::update)
+        .def("effective_depth", &AdaptiveConfidence::effective_depth)
+        .def("confidence_for", &AdaptiveConfidence::confidence_for);
+    py::class_<SpeculativeDepthController>(m, "SpeculativeDepthController")
+        .def(py::init<uint32_t, uint32_t, uint32_t>())
+        .def("record_prediction", &SpeculativeDepthController::record_prediction)
+        .def("record_rollback", &SpeculativeDepthController::record_rollback)
+        .def("depth", &SpeculativeDepthController::depth);
+
+    // ---- codec --------------------------------------------------------------------------------
+    m.def("codec_roundtrip", [](std::vector<std::pair<uint64_t, double>> updates, std::vector<std::pair<uint64_t, double>> predicted, int quant_bits) {
+        ResidualCodec c;
+        c.quant_bits = quant_bits;
+        ResidualMessage msg;
+        msg.from = 0; msg.to = 1; msg.time = 1e-9; msg.updates = std::move(updates);
+        std::string bytes = c.encode_to_bytes(msg, predicted);
+        ResidualMessage out;
+        bool ok = c.decode_from_bytes(bytes, out);
+        py::dict d;
+        d["ok"] = ok; d["updates"] = out.updates; d["bytes"] = py::bytes(bytes); d["ratio"] = c.stats.compression_ratio(); d["skipped"] = c.stats.skipped;
+        return d;
+    }, py::arg("updates"), py::arg("predicted"), py::arg("quant_bits") = 16);
+    m.def("fabric_selftest", [](uint32_t n, int rounds) {
+        // every node sends one residual to every other node per round, from its own thread
+        auto mesh = create_mesh(n);
+        std::vector<std::thread> th;
+        for (uint32_t i = 0; i < n; ++i)
+            th.emplace_back([&, i] {
+                for (int r = 0; r < rounds; ++r)
+                    for (uint32_t j = 0; j < n; ++j)
+                        if (j != i) { ResidualMessage msg; msg.from = i; msg.to = j; msg.time = r; msg.updates = {{uint64_t(i), double(r) + 0.5}}; mesh[i]->send_residual(msg, {{uint64_t(i), double(r)}}); }
+                mesh[i]->broadcast_done();
+            });
+        for (auto& t : th) t.join();
+        uint64_t residuals = 0, done = 0;
+        double sum = 0;
+        for (uint32_t i = 0; i < n; ++i)
+            for (auto& fm : mesh[i]->drain_inbox()) {
+                if (fm.kind == FabricMessage::Done) ++done;
+                else if (fm.kind == FabricMessage::Residual) { ++residuals; for (auto& u : mesh[i]->decode_residual(fm.residual).updates) sum += u.second; }
+            }
+        return py::make_tuple(residuals, done, sum);
+    });
+
+    // ---- .nz ----------------------------------------------------------------------------------
+    m.def("nz_compress", [](std::vector<std::string> names, std::vector<double> time, std::vector<std::vector<double>> signals, double error_bound) {
+        NzWriter w(error_bound);
+        std::string bytes = NzWriter::to_bytes(w.compress(names, time, signals));
+        py::dict st;
+        st["compression_ratio"] = w.stats.compression_ratio(); st["prediction_rate"] = w.stats.prediction_rate();
+        st["predicted_blocks"] = w.stats.predicted_blocks; st["raw_blocks"] = w.stats.raw_blocks;
+        return py::make_tuple(py::bytes(bytes), st);
+    }, py::arg("names"), py::arg("time"), py::arg("signals"), py::arg("error_bound") = 1e-6);
+    m.def("nz_decompress", [](const std::string& bytes) {
+        NzFile f = NzReader::from_bytes(bytes);
+        py::dict h;
+        h["version"] = f.version; h["t_start"] = f.t_start; h["t_end"] = f.t_end; h["error_bound"] = f.error_bound; h["num_blocks"] = f.blocks.size();
+        return py::make_tuple(f.names, f.time, NzReader::decompress(f), h);
+    });
+
+    // ---- PVT ----------------------------------------------------------------------------------
+    m.def("pvt_delta", [](std::vector<double> time, std::vector<std::vector<double>> golden, const std::string& process, double vdd, double temp) {
+        GoldenTrajectory g(CornerSpec(), time.size() > 1 ? time[1] - time[0] : 0.0);
+        for (size_t k = 0; k < time.size(); ++k) g.push(time[k], golden[k]);
+        std::string bytes = g.to_bytes();
+        GoldenTrajectory back;
+        bool rt = GoldenTrajectory::from_bytes(bytes, g.corner, back) && back.points.size() == g.points.size();
+        DeltaSolver s(std::move(g));
+        CornerSpec c(corner_from_name(process), vdd, temp);
+        DeltaSolveResult r = s.solve_corner(c);
+        std::vector<std::vector<double>> rec;
+        for (auto& p : s.reconstruct(r)) rec.push_back(p.voltages);
+        py::dict d;
+        d["name"] = c.name; d["used_delta_mode"] = r.used_delta_mode; d["peak_delta_v"] = r.peak_delta_v; d["waveform"] = rec; d["bytes_roundtrip"] = rt;
+        return d;
+    });
+    m.def("pvt_cache_selftest", [](size_t cap, std::vector<std::string> inserts, std::vector<std::string> lookups) {
+        PvtCache c(cap);
+        for (auto& n : inserts) { GoldenTrajectory g; g.corner.name = n; c.insert(std::move(g)); }
+        std::vector<bool> found;
+        for (auto& n : lookups) found.push_back(c.get(n) != nullptr);
+        return py::make_tuple(found, c.size(), c.stats.hits, c.stats.misses, c.stats.evictions);
+    });
+
+    // ---- balancer / benchmarks ----------------------------------------------------------------
+    m.def("balance_plan", [](std::vector<std::tuple<uint32_t, uint32_t, std::vector<double>>> partitions) {
+        // (partition id, element count, step times) -> (stragglers, plans, score)
+        BalanceMonitor mon{uint32_t(partitions.size())};
+        mon.check_interval = 1;
+        for (size_t i = 0; i < partitions.size(); ++i) {
+            mon.metrics[i].partition_id = std::get<0>(partitions[i]);
+            mon.metrics[i].element_count = std::get<1>(partitions[i]);
+            for (double t : std::get<2>(partitions[i])) mon.metrics[i].record_solve_time(t);
+        }
+        std::vector<std::pair<uint32_t, double>> st;
+        for (auto& s : detect_stragglers(mon.metrics, mon.detector)) st.emplace_back(s.partition, s.ratio);
+        std::vector<std::tuple<uint32_t, uint32_t, uint32_t, double>> plans;
+        for (auto& p : mon.check_balance()) plans.emplace_back(p.from_partition, p.to_partition, p.elements_to_move, p.expected_speedup);
+        return py::make_tuple(st, plans, mon.balance_score());
+    });
+    m.def("generate_circuit", [](const std::string& kind, int a, int b, double r, double c) {
+        if (kind == "rc_ladder") return generate_rc_ladder(a, r, c).to_json().dump();
+        if (kind == "cim_array") return generate_cim_array(a, b).to_json().dump();
+        if (kind == "resistor_mesh") return generate_resistor_mesh(a, r).to_json().dump();
+        throw std::invalid_argument("kind must be rc_ladder, cim_array or resistor_mesh");
+    }, py::arg("kind"), py::arg("a"), py::arg("b") = 0, py::arg("r") = 1e3, py::arg("c") = 10e-15);
+    m.def("run_benchmark_suite", [](int scale) {
+        std::vector<py::dict> out;
+        for (auto& r : run_benchmark_suite(scale)) {
+            py::dict d;
+            d["name"] = r.name; d["num_nodes"] = r.num_nodes; d["num_elements"] = r.num_elements; d["steps"] = r.steps; d["wall_time_secs"] = r.wall_time_secs;
+            d["steps_per_sec"] = r.steps_per_sec; d["completed"] = r.completed; d["summary"] = r.summary();
+            out.push_back(d);
+        }
+        return out;
+    }, py::arg("scale") = 1);
+}

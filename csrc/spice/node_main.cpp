@@ -13,17 +13,19 @@
 #include <functional>
 #include <iostream>
 
+#include "balancer.hpp"
 #include "nz.hpp"
 #include "parser.hpp"
+#include "partitioned.hpp"
 #include "transient.hpp"
 
 using namespace nspice;
 
 struct Args {
-    std::string partition, process = "TT", waveform_json, waveform_nz, solver = "lu";
+    std::string partition, partitions, process = "TT", waveform_json, waveform_nz, solver = "lu";
     uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1;
     double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
-    bool demo = false;
+    bool demo = false, bench = false;
 };
 
 static void usage() {
@@ -43,6 +45,8 @@ static bool parse_args(int argc, char** argv, Args& a) {
         };
         const char* v = nullptr;
         if (f == "--demo") a.demo = true;
+        else if (f == "--bench") a.bench = true;
+        else if (f == "--partitions") { if (!(v = need("--partitions"))) return false; a.partitions = v; }
         else if (f == "-h" || f == "--help") { usage(); std::exit(0); }
         else if (f == "--partition" || f == "-p") { if (!(v = need("--partition"))) return false; a.partition = v; }
         else if (f == "--node-id" || f == "-n") { if (!(v = need("--node-id"))) return false; a.node_id = uint32_t(std::atoi(v)); }
@@ -100,9 +104,58 @@ static void write_json(const std::string& path, const std::string& name, const s
       << st.prediction_misses << ", \"rollbacks\": " << st.rollbacks << ", \"completed\": " << (st.completed ? "true" : "false") << "}\n}\n";
 }
 
+static Netlist load_any(const std::string& path, const Args& a) {
+    std::ifstream f(path);
+    if (!f) throw std::runtime_error("cannot open '" + path + "'");
+    std::stringstream ss;
+    ss << f.rdbuf();
+    if (path.size() > 5 && path.substr(path.size() - 5) == ".json") return Netlist::from_json(Json::parse(ss.str()));
+    Corner c;
+    c.process = a.process; c.vdd = a.vdd; c.temp_c = a.temp;
+    SpiceParser p(c);
+    return p.parse_text(ss.str(), path.substr(path.find_last_of('/') == std::string::npos ? 0 : path.find_last_of('/') + 1));
+}
+
+// All partitions of a design in one process: --partitions p0.json,p1.json,...
+static int run_partitioned(const Args& a) {
+    std::vector<Netlist> parts;
+    try {
+        size_t pos = 0;
+        while (pos <= a.partitions.size()) {
+            size_t comma = a.partitions.find(',', pos);
+            std::string one = a.partitions.substr(pos, comma == std::string::npos ? std::string::npos : comma - pos);
+            if (!one.empty()) parts.push_back(load_any(one, a));
+            if (comma == std::string::npos) break;
+            pos = comma + 1;
+        }
+        PartitionedConfig cfg;
+        cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
+        PartitionedRunner runner(std::move(parts), cfg);
+        runner.run();
+        const PartitionedStats& st = runner.stats;
+        std::fprintf(stderr, "partitioned run: %llu steps%s, %.3f s, hits %llu, misses %llu, extra solves %llu, messages %llu (%llu bytes, codec ratio %.2f), depth %u\n",
+                     (unsigned long long)st.steps, st.completed ? "" : " (stopped early)", st.wall_time_secs, (unsigned long long)st.prediction_hits,
+                     (unsigned long long)st.prediction_misses, (unsigned long long)st.resolves, (unsigned long long)st.messages,
+                     (unsigned long long)st.bytes_sent, st.codec_ratio, st.final_depth);
+        SimStats ss;
+        ss.total_steps = st.steps; ss.wall_time_secs = st.wall_time_secs; ss.prediction_hits = st.prediction_hits;
+        ss.prediction_misses = st.prediction_misses; ss.rollbacks = st.resolves; ss.completed = st.completed;
+        if (!a.waveform_json.empty()) write_json(a.waveform_json, "partitioned", runner.names, runner.waveform, ss);
+        return st.completed ? 0 : 3;
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ERROR: %s\n", e.what());
+        return 1;
+    }
+}
+
 int main(int argc, char** argv) {
     Args a;
     if (!parse_args(argc, argv, a)) { usage(); return 2; }
+    if (a.bench) {
+        for (auto& r : run_benchmark_suite()) std::printf("%s\n", r.summary().c_str());
+        return 0;
+    }
+    if (!a.partitions.empty()) return run_partitioned(a);
     Netlist nl;
     try {
         if (a.demo) nl = demo_netlist();

@@ -1,0 +1,240 @@
+// In-process partitioned transient simulation: every partition owns a set of nets, sees foreign
+// nets as ghost nodes, and the partitions advance in lockstep. Each step a partition solves with
+// *predicted* ghost voltages, publishes the voltages of the nets it owns through the fabric (delta +
+// quantization codec against the receiver's prediction), and every receiver checks its predictions.
+// A step whose predictions were all within tolerance is accepted as it stands; otherwise the step is
+// solved again with the received values (block Gauss-Jacobi relaxation) until two sweeps agree.
+//
+// The reference ships this mode as an experiment that falls back to a single node
+// (nangila-spice/src/nangila_spice/orchestrator.py:222-233; solver loop solver.rs:104-245); the
+// message types, codec and depth controller used here are the ones of comm.hpp.
+//
+// Partition files must overlap on cut elements: an element between a net of partition A and a net of
+// partition B appears in both, with the foreign net listed in ghost_map. Net identity across
+// partitions is the node *name* (ghost net id = net_name_hash(name)).
+#pragma once
+#include <map>
+#include <memory>
+#include <set>
+
+#include "parser.hpp"
+#include "transient.hpp"
+
+namespace nspice {
+
+struct PartitionedConfig {
+    double tstop = 1e-9, dt = 1e-12, reltol = 1e-3, abstol = 1e-6;
+    uint32_t predict_depth = 5;
+    int max_sweeps = 50;
+    uint32_t record_every = 1;
+    bool compress = true;
+};
+
+struct PartitionedStats {
+    uint64_t steps = 0, prediction_hits = 0, prediction_misses = 0, resolves = 0, messages = 0, bytes_sent = 0, unconverged_steps = 0;
+    double wall_time_secs = 0, codec_ratio = 1.0;
+    bool completed = false;
+    uint32_t final_depth = 0;
+};
+
+class PartitionedRunner {
+public:
+    PartitionedStats stats;
+    std::vector<std::string> names;            // merged net names (owned nets of every partition)
+    std::vector<WaveformPoint> waveform;       // merged, values in `names` order
+
+    PartitionedRunner(std::vector<Netlist> parts, PartitionedConfig cfg) : cfg_(cfg), depth_(cfg.predict_depth, 1, cfg.predict_depth * 3) {
+        const uint32_t k = uint32_t(parts.size());
+        FabricConfig fc;
+        fc.compress = cfg.compress;
+        mesh_ = create_mesh(k, fc);
+        for (uint32_t p = 0; p < k; ++p) {
+            Part part;
+            part.names = parts[p].names_or_default();
+            for (auto& g : parts[p].ghost_map) { part.ghosts.add(GhostNode(g.net_id, g.owner)); part.ghost_nodes.insert(g.local_node); }
+            part.engine.reset(new SolverEngine(std::move(parts[p])));
+            parts_.push_back(std::move(part));
+        }
+        // exports: for every ghost link of q owned by p, find p's local node of that name
+        for (uint32_t q = 0; q < k; ++q)
+            for (auto& g : parts_[q].engine->netlist.ghost_map) {
+                if (g.owner >= k) throw std::runtime_error("ghost owner outside the partition set");
+                Part& owner = parts_[g.owner];
+                int local = -1;
+                for (size_t i = 0; i < owner.names.size(); ++i)
+                    if (net_name_hash(owner.names[i]) == g.net_id && !owner.ghost_nodes.count(int(i) + 1)) { local = int(i) + 1; break; }
+                if (local < 0) throw std::runtime_error("partition " + std::to_string(g.owner) + " does not own a net that partition " + std::to_string(q) + " lists as ghost");
+                owner.exports[q].emplace_back(g.net_id, local);
+            }
+        for (uint32_t p = 0; p < k; ++p)
+            for (size_t i = 0; i < parts_[p].names.size(); ++i)
+                if (!parts_[p].ghost_nodes.count(int(i) + 1)) { merged_.push_back({p, i}); names.push_back(parts_[p].names[i]); }
+    }
+
+    void run() {
+        auto t0 = std::chrono::steady_clock::now();
+        const uint32_t k = uint32_t(parts_.size());
+        for (auto& p : parts_) p.state = p.engine->seeded_state();
+        // consistent start: relax the DC point (or the seeded state when .ic lines exist) across partitions
+        relax(/*dc=*/true, 0.0);
+        record(0.0);
+        const uint64_t planned = cfg_.dt > 0 ? uint64_t(std::ceil(cfg_.tstop / cfg_.dt - 1e-9)) : 0;
+        uint64_t step = 0;
+        bool failed = false;
+        for (; step < planned && !failed; ++step) {
+            const double t_next = double(step + 1) * cfg_.dt;
+            // speculative solve with predicted ghosts
+            for (uint32_t p = 0; p < k && !failed; ++p) {
+                Part& part = parts_[p];
+                part.pins = part.ghosts.predict_all(t_next);
+                if (!part.engine->solve_step(part.state, part.pins, cfg_.dt, part.next)) failed = true;
+            }
+            if (failed) break;
+            bool all_ok = exchange(t_next, /*count=*/true);
+            int sweeps = 0;
+            while (!all_ok && sweeps < cfg_.max_sweeps) {
+                // solve again with the received (true, as of the last sweep) ghost values
+                std::vector<std::vector<double>> before;
+                for (auto& part : parts_) before.push_back(part.next.voltages);
+                for (uint32_t p = 0; p < k && !failed; ++p) {
+                    Part& part = parts_[p];
+                    part.pins = part.latest;
+                    if (!part.engine->solve_step(part.state, part.pins, cfg_.dt, part.next)) failed = true;
+                    ++stats.resolves;
+                }
+                if (failed) break;
+                exchange(t_next, /*count=*/false);
+                all_ok = true;
+                for (uint32_t p = 0; p < k; ++p)
+                    for (size_t i = 0; i < parts_[p].next.voltages.size() && i < before[p].size(); ++i) {
+                        double a = parts_[p].next.voltages[i], b = before[p][i];
+                        if (std::fabs(a - b) > cfg_.reltol * 0.1 * std::max(std::fabs(a), std::fabs(b)) + cfg_.abstol * 0.1) { all_ok = false; break; }
+                    }
+                ++sweeps;
+            }
+            if (failed) break;
+            if (!all_ok) ++stats.unconverged_steps;
+            for (auto& part : parts_) part.state = part.next;
+            if ((step + 1) % cfg_.record_every == 0 || step + 1 == planned) record(t_next);
+        }
+        stats.steps = step;
+        stats.completed = !failed && step == planned;
+        stats.final_depth = depth_.depth();
+        uint64_t raw = 0, comp = 0;
+        for (auto& n : mesh_) { stats.messages += n->stats.sent; stats.bytes_sent += n->stats.bytes_sent; raw += n->codec.stats.raw_bytes; comp += n->codec.stats.compressed_bytes; }
+        stats.codec_ratio = comp ? double(raw) / double(comp) : 1.0;
+        stats.wall_time_secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    }
+
+private:
+    struct Part {
+        std::unique_ptr<SolverEngine> engine;
+        GhostBuffer ghosts;
+        std::set<int> ghost_nodes;
+        std::vector<std::string> names;
+        std::map<uint32_t, std::vector<std::pair<uint64_t, int>>> exports;  // consumer -> (net id, local node)
+        PartitionState state{0}, next{0};
+        std::vector<std::pair<uint64_t, double>> pins, latest;
+    };
+    struct MergedRef { uint32_t part; size_t index; };
+    PartitionedConfig cfg_;
+    std::vector<Part> parts_;
+    std::vector<std::unique_ptr<FabricNode>> mesh_;
+    std::vector<MergedRef> merged_;
+    SpeculativeDepthController depth_;
+
+    // Every owner publishes its boundary voltages of `next`; receivers decode, remember them and
+    // (when count is set) score their predictions. Returns whether every prediction was a hit.
+    bool exchange(double t, bool count) {
+        const uint32_t k = uint32_t(parts_.size());
+        for (auto& part : parts_) part.latest.clear();
+        for (uint32_t p = 0; p < k; ++p)
+            for (auto& ex : parts_[p].exports) {
+                ResidualMessage m;
+                m.from = p; m.to = ex.first; m.time = t;
+                for (auto& e : ex.second) m.updates.emplace_back(e.first, parts_[p].next.voltages[size_t(e.second - 1)]);
+                // the sender encodes against what the receiver pinned, which both sides know after the
+                // previous exchange; on the first sweep that is the receiver's prediction
+                std::vector<std::pair<uint64_t, double>> base;
+                for (auto& u : m.updates)
+                    for (auto& pin : parts_[ex.first].pins) if (pin.first == u.first) { base.push_back(pin); break; }
+                mesh_[p]->send_residual(m, base);
+            }
+        bool all_ok = true;
+        for (uint32_t q = 0; q < k; ++q) {
+            Part& part = parts_[q];
+            for (auto& fm : mesh_[q]->drain_inbox()) {
+                if (fm.kind != FabricMessage::Residual) continue;
+                ResidualMessage m = mesh_[q]->decode_residual(fm.residual);
+                // nets whose delta was below the codec's floor keep the pinned value
+                for (auto& u : m.updates) set_latest(part, u.first, u.second);
+                if (count) {
+                    std::vector<Correction> cs;
+                    for (auto& u : m.updates) cs.push_back({u.first, u.second, t});
+                    bool ok = part.ghosts.apply_corrections(cs, cfg_.reltol);
+                    (ok ? stats.prediction_hits : stats.prediction_misses) += cs.size();
+                    depth_.record_prediction(ok);
+                    all_ok = all_ok && ok;
+                }
+            }
+            // pinned values that no message corrected are carried over
+            for (auto& pin : part.pins) {
+                bool have = false;
+                for (auto& l : part.latest) if (l.first == pin.first) { have = true; break; }
+                if (!have) part.latest.push_back(pin);
+            }
+        }
+        return all_ok;
+    }
+    static void set_latest(Part& part, uint64_t id, double v) {
+        for (auto& l : part.latest) if (l.first == id) { l.second = v; return; }
+        part.latest.emplace_back(id, v);
+    }
+    // Block relaxation of the DC point: each partition solves its operating point with the ghosts
+    // pinned to the neighbours' latest values.
+    void relax(bool dc, double) {
+        if (!dc) return;
+        const uint32_t k = uint32_t(parts_.size());
+        for (auto& part : parts_) { part.next = part.state; part.pins.clear(); part.latest.clear(); }
+        for (int sweep = 0; sweep < 200; ++sweep) {
+            double change = 0.0;
+            for (uint32_t p = 0; p < k; ++p) {
+                Part& part = parts_[p];
+                if (!part.engine->netlist.initial_conditions.empty()) continue;
+                // pin ghosts by writing them as Ghost elements through solve_step's pin path at dt = 0
+                PartitionState out{0};
+                std::vector<std::pair<uint64_t, double>> pins;
+                for (auto& g : part.engine->netlist.ghost_map) {
+                    const Part& owner = parts_[g.owner];
+                    for (auto& ex : owner.exports.at(p))
+                        if (ex.first == g.net_id) pins.emplace_back(g.net_id, owner.next.voltages[size_t(ex.second - 1)]);
+                }
+                PartitionState seed = part.next;
+                seed.cap_currents.clear();
+                if (part.engine->solve_step(seed, pins, 0.0, out)) {
+                    for (size_t i = 0; i < out.voltages.size(); ++i) change = std::max(change, std::fabs(out.voltages[i] - part.next.voltages[i]));
+                    part.next.voltages = out.voltages;
+                }
+            }
+            if (change < 1e-9) break;
+        }
+        for (auto& part : parts_) {
+            part.state.voltages = part.next.voltages;
+            part.state.cap_currents.clear();
+            part.state.time = 0.0;
+            // ghosts start from the neighbours' initial values
+        }
+        for (uint32_t p = 0; p < k; ++p)
+            for (auto& ex : parts_[p].exports)
+                for (auto& e : ex.second)
+                    for (auto& g : parts_[ex.first].ghosts.nodes)
+                        if (g.net_id == e.first) g.apply_correction(parts_[p].state.voltages[size_t(e.second - 1)], 0.0, cfg_.reltol);
+    }
+    void record(double t) {
+        WaveformPoint pt{t, {}};
+        for (auto& r : merged_) pt.values.push_back(parts_[r.part].state.voltages[r.index]);
+        waveform.push_back(std::move(pt));
+    }
+};
+
+}  // namespace nspice

@@ -257,12 +257,33 @@ public:
         if (backend == LinearBackend::Dense) {
             ok = dense_solve(m.to_dense(), m.rhs, m.n, m.solution);
         } else if (backend == LinearBackend::Krylov) {
+            // rows are equilibrated (divided by their largest entry) so that supply rows (entries of
+            // 1) and stiff node rows (C / dt, ghost pins of 1e12) weigh the same in the residual norm
+            CsrMatrix eq = m;
+            for (int r = 0; r < m.n; ++r) {
+                double mx = 0.0;
+                for (int k = m.row_ptr[size_t(r)]; k < m.row_ptr[size_t(r) + 1]; ++k) mx = std::max(mx, std::fabs(m.val[size_t(k)]));
+                if (mx > 0.0) {
+                    for (int k = m.row_ptr[size_t(r)]; k < m.row_ptr[size_t(r) + 1]; ++k) eq.val[size_t(k)] /= mx;
+                    eq.rhs[size_t(r)] /= mx;
+                }
+            }
             std::vector<double> diag(size_t(m.n), 1.0);
-            for (int r = 0; r < m.n; ++r) { int s = m.slot(r, r); if (s >= 0) diag[size_t(r)] = m.val[size_t(s)]; }
+            for (int r = 0; r < m.n; ++r) { int s = eq.slot(r, r); if (s >= 0 && std::fabs(eq.val[size_t(s)]) > 1e-3) diag[size_t(r)] = eq.val[size_t(s)]; }
             m.solution.assign(size_t(m.n), 0.0);
-            KrylovResult kr = bicgstab(m.n, [&](const double* x, double* y) { m.spmv(x, y); }, diag, m.rhs, m.solution);
+            KrylovResult kr = bicgstab(m.n, [&](const double* x, double* y) { eq.spmv(x, y); }, diag, eq.rhs, m.solution, 1e-12, 4 * m.n + 50);
             stats.krylov_iterations += uint64_t(kr.iterations);
+            // accept only a small componentwise backward error: |A x - b|_i <= 1e-8 (|A||x| + |b|)_i
             ok = kr.converged;
+            for (int r = 0; ok && r < m.n; ++r) {
+                double ax = 0.0, mag = std::fabs(eq.rhs[size_t(r)]);
+                for (int k = eq.row_ptr[size_t(r)]; k < eq.row_ptr[size_t(r) + 1]; ++k) {
+                    double t = eq.val[size_t(k)] * m.solution[size_t(eq.col[size_t(k)])];
+                    ax += t;
+                    mag += std::fabs(t);
+                }
+                if (!(std::fabs(ax - eq.rhs[size_t(r)]) <= 1e-8 * mag + 1e-300)) ok = false;
+            }
             if (!ok) { ++stats.krylov_fallbacks; ok = sparse_lu_solve(m, m.solution); }
         } else {
             ok = sparse_lu_solve(m, m.solution);

@@ -8,7 +8,8 @@ without an install step:
 * ``nangila/_cuda*.so``     torch glue: tensor-typed wrappers of the launchers and the C++ DDP
   communication hook (g++ against libtorch).
 
-Plus two small executables, ``nangila/cli/nangila-dump`` and ``nangila/cli/nangila-profile``.
+Plus two small executables, ``nangila/cli/nangila-dump`` and ``nangila/cli/nangila-profile``, and the
+circuit simulator's module and solver process (``nangila_spice/_native*.so``, ``nangila_spice/bin/nangila-node``).
 
 The role of the reference's ``nangila-cuda/build.rs:15-156`` (find CUDA, compile every kernel for a
 list of architectures, archive and link) is played by :func:`build_kernels`; the only architecture
@@ -175,16 +176,48 @@ def build_cli(force: bool = False) -> list[Path]:
     return outs
 
 
+SPICE_PKG = ROOT / "nangila_spice"
+
+
+def spice_native_path() -> Path:
+    return SPICE_PKG / f"_native{EXT_SUFFIX}"
+
+
+def build_spice(force: bool = False) -> list[Path]:
+    """The circuit simulator: ``nangila_spice/_native*.so`` (pybind11 module over ``csrc/spice``) and
+    the ``nangila_spice/bin/nangila-node`` executable. Host code only; its device kernel
+    (``csrc/kernels/spmv_csr.cu``) is part of ``libnangila_kernels.so``."""
+    import pybind11
+
+    hdrs = _headers(CSRC / "spice")
+    outs = []
+    mod = spice_native_path()
+    src = CSRC / "spice" / "bindings.cpp"
+    if force or _stale(mod, [src] + hdrs):
+        _run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread",
+              f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{CSRC / 'spice'}",
+              str(src), "-o", str(mod)])
+    outs.append(mod)
+    exe = SPICE_PKG / "bin" / "nangila-node"
+    exe.parent.mkdir(exist_ok=True)
+    src = CSRC / "spice" / "node_main.cpp"
+    if force or _stale(exe, [src] + hdrs):
+        _run(["g++", "-O2", "-std=c++17", "-Wall", "-pthread", f"-I{CSRC / 'spice'}", str(src), "-o", str(exe)])
+    outs.append(exe)
+    return outs
+
+
 def build_all(force: bool = False) -> None:
     build_core(force)
     build_cli(force)
+    build_spice(force)
     build_kernels(force)
     build_glue(force)
 
 
 def main(argv: list[str]) -> int:
     force = "--force" in argv
-    parts = [a for a in argv if a in ("--core", "--kernels", "--glue", "--cli")]
+    parts = [a for a in argv if a in ("--core", "--kernels", "--glue", "--cli", "--spice")]
     if not parts:
         build_all(force)
     else:
@@ -192,6 +225,8 @@ def main(argv: list[str]) -> int:
             build_core(force)
         if "--cli" in parts:
             build_cli(force)
+        if "--spice" in parts:
+            build_spice(force)
         if "--kernels" in parts:
             build_kernels(force, verbose_ptxas="--ptxas-v" in argv)
         if "--glue" in parts:
