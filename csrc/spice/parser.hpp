@@ -49,10 +49,12 @@ inline bool parse_scaled(const std::string& raw, double& out) {
     return true;
 }
 
-inline uint64_t net_name_hash(const std::string& name) {  // FNV-1a 64 over the lower-cased name
+// FNV-1a over the lower-cased name, folded to 53 bits so the id survives JSON readers that keep
+// numbers as doubles.
+inline uint64_t net_name_hash(const std::string& name) {
     uint64_t h = 1469598103934665603ull;
     for (char c : lower(name)) { h ^= uint64_t((unsigned char)c); h *= 1099511628211ull; }
-    return h;
+    return (h ^ (h >> 53)) & ((uint64_t(1) << 53) - 1);
 }
 
 struct ModelCard { std::string name, type; std::map<std::string, double> params; };

@@ -91,10 +91,10 @@ struct CsrMatrix {
     }
 };
 
-// Row-wise sparse Gaussian elimination with threshold partial pivoting: among the rows whose entry
+// Row-wise sparse Gaussian elimination on row-equilibrated data with threshold partial pivoting: among the rows whose entry
 // in the pivot column is within a factor 10 of the largest, the shortest row wins (limits fill).
 // One right-hand side is carried along, because a Newton iteration changes the matrix every solve.
-inline bool sparse_lu_solve(const CsrMatrix& m, std::vector<double>& x) {
+inline bool sparse_lu_solve_once(const CsrMatrix& m, std::vector<double>& x) {
     const int n = m.n;
     using Row = std::vector<std::pair<int, double>>;
     std::vector<Row> rows(static_cast<size_t>(n));
@@ -106,6 +106,14 @@ inline bool sparse_lu_solve(const CsrMatrix& m, std::vector<double>& x) {
         for (int k = m.row_ptr[size_t(r)]; k < m.row_ptr[size_t(r) + 1]; ++k) {
             row.emplace_back(m.col[size_t(k)], m.val[size_t(k)]);
             col_rows[size_t(m.col[size_t(k)])].push_back(r);
+        }
+        // row equilibration: a row that pins a node with 1e12 S must not offer its 1e-3 S coupling
+        // entry as a pivot, or the elimination loses every digit of the other rows
+        double mx = 0.0;
+        for (auto& e : row) mx = std::max(mx, std::fabs(e.second));
+        if (mx > 0.0 && mx != 1.0) {
+            for (auto& e : row) e.second /= mx;
+            b[size_t(r)] /= mx;
         }
     }
     std::vector<int> pivot_row(size_t(n), -1);
@@ -167,6 +175,32 @@ inline bool sparse_lu_solve(const CsrMatrix& m, std::vector<double>& x) {
             else if (e.first > k) acc -= e.second * x[size_t(e.first)];
         }
         x[size_t(k)] = acc / pv;
+    }
+    return true;
+}
+
+// The elimination above plus iterative refinement: while the componentwise backward error is above
+// 1e-10 the residual system is solved again (at most three rounds). Circuit matrices pass at once;
+// the refinement is for badly column-scaled systems.
+inline bool sparse_lu_solve(const CsrMatrix& m, std::vector<double>& x) {
+    if (!sparse_lu_solve_once(m, x)) return false;
+    CsrMatrix res = m;
+    std::vector<double> dx;
+    for (int round = 0; round < 3; ++round) {
+        double worst = 0.0;
+        for (int r = 0; r < m.n; ++r) {
+            double ax = 0.0, mag = std::fabs(m.rhs[size_t(r)]);
+            for (int k = m.row_ptr[size_t(r)]; k < m.row_ptr[size_t(r) + 1]; ++k) {
+                double t = m.val[size_t(k)] * x[size_t(m.col[size_t(k)])];
+                ax += t;
+                mag += std::fabs(t);
+            }
+            res.rhs[size_t(r)] = m.rhs[size_t(r)] - ax;
+            if (mag > 0.0) worst = std::max(worst, std::fabs(res.rhs[size_t(r)]) / mag);
+        }
+        if (!(worst > 1e-10)) break;
+        if (!sparse_lu_solve_once(res, dx)) break;
+        for (int i = 0; i < m.n; ++i) x[size_t(i)] += dx[size_t(i)];
     }
     return true;
 }

@@ -1,0 +1,104 @@
+"""GPU tests of the circuit simulator's CSR SpMV kernel and device BiCGSTAB against FP64 references
+computed on the host (NumPy / SciPy)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _random_csr(n, row_lengths, seed):
+    rng = np.random.default_rng(seed)
+    row_ptr = np.zeros(n + 1, dtype=np.int32)
+    cols, vals = [], []
+    for r in range(n):
+        k = min(n, int(row_lengths[r]))
+        c = np.sort(rng.choice(n, size=k, replace=False)) if k else np.zeros(0, dtype=np.int64)
+        cols.append(c.astype(np.int32))
+        vals.append(rng.standard_normal(k))
+        row_ptr[r + 1] = row_ptr[r] + k
+    return row_ptr, np.concatenate(cols) if cols else np.zeros(0, np.int32), np.concatenate(vals) if vals else np.zeros(0)
+
+
+def _reference(row_ptr, col, val, x):
+    y = np.zeros(row_ptr.size - 1)
+    prod = val * x[col]
+    nz = np.flatnonzero(np.diff(row_ptr))
+    y[nz] = np.add.reduceat(prod, row_ptr[:-1][nz]) if prod.size else 0.0
+    return y
+
+
+@pytest.mark.parametrize("case", ["short", "mixed", "long", "empty_rows", "dense_ish"])
+def test_spmv_matches_host(case):
+    from nangila_spice.gpu import DeviceCsr
+
+    rng = np.random.default_rng(1)
+    n = 5003
+    if case == "short":
+        lens = rng.integers(1, 5, n)
+    elif case == "mixed":
+        lens = rng.integers(0, 70, n)
+    elif case == "long":
+        lens = rng.integers(1, 6, n)
+        lens[[7, 2500, n - 1]] = [3000, 5003, 2049]  # rows longer than one block's capacity
+    elif case == "empty_rows":
+        lens = np.where(rng.random(n) < 0.7, 0, 3)
+    else:
+        n = 600
+        lens = rng.integers(100, 400, n)
+    row_ptr, col, val = _random_csr(n, lens, 2)
+    x = rng.standard_normal(n)
+    m = DeviceCsr(row_ptr, col, val)
+    y = m.matvec(x)
+    ref = _reference(row_ptr, col, val, x)
+    scale = np.abs(ref).max() + 1.0
+    assert np.abs(y - ref).max() / scale < 1e-13
+    # device-resident path on torch tensors, and a values-only update
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.full((n,), float("nan"), dtype=torch.float64, device="cuda")
+    m.update_values(val * 2.0)
+    m.matvec_device(xd, yd, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert np.abs(yd.cpu().numpy() - 2.0 * ref).max() / scale < 1e-13
+    m.close()
+
+
+def test_tridiagonal_like_reference_benchmark():
+    from nangila_spice.gpu import DeviceCsr, tridiagonal
+
+    n = 200_000
+    row_ptr, col, val = tridiagonal(n)
+    m = DeviceCsr(row_ptr, col, val)
+    y = m.matvec(np.ones(n))
+    assert y[0] == 1.0 and y[-1] == 1.0 and np.all(y[1:-1] == 0.0)
+
+
+def test_device_bicgstab_solves_rc_ladder_system():
+    from nangila_spice.gpu import DeviceCsr, tridiagonal
+
+    n = 4000
+    row_ptr, col, val = tridiagonal(n, diag=2.5, off=-1.0)  # diagonally dominant: G + C/dt of a ladder
+    b = np.random.default_rng(3).standard_normal(n)
+    m = DeviceCsr(row_ptr, col, val)
+    x, iters, rel, ok = m.solve(b, tol=1e-11, max_iter=500)
+    assert ok and rel < 1e-11 and iters > 0
+    import scipy.sparse as sp
+    import scipy.sparse.linalg as spla
+
+    ref = spla.spsolve(sp.csr_matrix((val, col, row_ptr), shape=(n, n)).tocsc(), b)
+    assert np.abs(x - ref).max() < 1e-8 * (np.abs(ref).max() + 1.0)
+    # the same inputs give the same bits (fixed-order reductions)
+    x2, _, _, _ = m.solve(b, tol=1e-11, max_iter=500)
+    assert np.array_equal(x, x2)
+
+
+def test_mna_system_from_the_simulator_on_the_device():
+    """The assembled MNA matrix of a generated circuit: device product against the host product."""
+    from nangila_spice import _native as N
+    from nangila_spice.gpu import DeviceCsr
+
+    size, row_ptr, col, val, rhs = N.mna_matrix(N.generate_circuit("resistor_mesh", 30), 1e-12, 0.0)
+    x = np.random.default_rng(4).standard_normal(size)
+    m = DeviceCsr(row_ptr, col, val)
+    host = np.array(N.csr_spmv(size, row_ptr, col, val, list(x)))
+    assert np.abs(m.matvec(x) - host).max() <= 1e-12 * (np.abs(host).max() + 1.0)
