@@ -23,6 +23,9 @@ int nangila_spmv_update_values(NangilaSpmv* ctx, const double* val);
 int nangila_spmv_host(NangilaSpmv* ctx, const double* h_x, double* h_y);
 /* y = A x with device vectors, queued on `stream`; no copies, no synchronisation. */
 int nangila_spmv_device(NangilaSpmv* ctx, const double* d_x, double* d_y, cudaStream_t stream);
+/* 0, or cudaErrorTimeout when a kernel of this context gave up waiting for one of its own bulk copies
+ * (reads one word back from the device, so it synchronises). */
+int nangila_spmv_status(NangilaSpmv* ctx);
 int nangila_spmv_dims(const NangilaSpmv* ctx, int* n, int* nnz, int* n_blocks);
 
 /* Row-block table for a CSR pattern: out[0] = 0, out[b + 1] = first row after block b. Returns the

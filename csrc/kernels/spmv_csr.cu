@@ -11,14 +11,23 @@
 // there with 1..32 lanes per row (chosen from the block's mean row length), so short rows
 // (3 entries for an RC ladder) cost no idle lanes and long rows still reduce in parallel. A row
 // longer than kCap gets a block of its own and a CTA-wide strided reduction.
+//
+// Two variants of the staging step. The context-owned matrix (nangila_spmv_load) is stored padded
+// to a multiple of four entries, so a CTA fetches its slice of `val` and `col` with two
+// cp.async.bulk copies completing on an mbarrier: the copy engine keeps 24 KB per CTA in flight
+// without spending registers or issue slots, where the plain-load variant was bound by load latency
+// (long-scoreboard stalls at 41 % of DRAM throughput). Arrays owned by the caller
+// (nangila_spmv_launch) carry no padding guarantee and use the plain-load variant.
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <new>
 #include <vector>
 
 #include "nangila_spice_kernels.h"
+#include "ptx_sm100.cuh"
 
 namespace {
 
@@ -77,6 +86,82 @@ __global__ void __launch_bounds__(kThreads) spmv_row_blocks_kernel(const int* __
             double s = 0.0;
             for (int w = 0; w < kThreads / 32; ++w) s += warp_sums[w];
             y[r0] = s;
+        }
+    }
+}
+
+// Bulk-copy variant: `val` and `col` must be readable up to the next multiple of four entries past
+// the end of every block (the context pads its arrays). status[0] is set to 1 when a copy did not
+// land within the time limit; the CTA then leaves its rows unwritten.
+__global__ void __launch_bounds__(kThreads) spmv_row_blocks_bulk_kernel(const int* __restrict__ row_ptr, const int* __restrict__ col,
+                                                                         const double* __restrict__ val, const double* __restrict__ x,
+                                                                         double* __restrict__ y, const int* __restrict__ row_blocks,
+                                                                         int* __restrict__ status, unsigned long long timeout_ns) {
+    __shared__ __align__(16) double s_val[kCap + 8];
+    __shared__ __align__(16) int s_col[kCap + 8];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ double warp_sums[kThreads / 32];
+    const int tid = threadIdx.x;
+    const int r0 = row_blocks[blockIdx.x], r1 = row_blocks[blockIdx.x + 1];
+    const int k0 = row_ptr[r0], k1 = row_ptr[r1];
+    const int nnz = k1 - k0, nrows = r1 - r0;
+    if (nnz <= kCap) {
+        const int ka = k0 & ~3, kb = (k1 + 3) & ~3;  // 16-byte aligned in both arrays
+        const int cnt = kb - ka, off = k0 - ka;
+        if (tid == 0) {
+            nangila::sm100::mbar_init(&bar, 1);
+            nangila::sm100::fence_barrier_init();
+        }
+        __syncthreads();
+        if (tid == 0 && cnt > 0) {
+            nangila::sm100::mbar_arrive_expect_tx(&bar, uint32_t(cnt) * 12u);
+            nangila::sm100::bulk_load(s_val, val + ka, uint32_t(cnt) * 8u, &bar);
+            nangila::sm100::bulk_load(s_col, col + ka, uint32_t(cnt) * 4u, &bar);
+        }
+        if (cnt > 0 && !nangila::sm100::mbar_wait(&bar, 0, timeout_ns)) {
+            if (tid == 0) atomicExch(status, 1);
+            // the copies still target this CTA's shared memory: give them one more bounded wait
+            nangila::sm100::mbar_wait(&bar, 0, timeout_ns);
+            return;
+        }
+        int k = tid;
+        for (; k + 3 * kThreads < nnz; k += 4 * kThreads) {
+            const int j = off + k;
+            double x0 = __ldg(x + s_col[j]), x1 = __ldg(x + s_col[j + kThreads]), x2 = __ldg(x + s_col[j + 2 * kThreads]),
+                   x3 = __ldg(x + s_col[j + 3 * kThreads]);
+            s_val[j] *= x0;
+            s_val[j + kThreads] *= x1;
+            s_val[j + 2 * kThreads] *= x2;
+            s_val[j + 3 * kThreads] *= x3;
+        }
+        for (; k < nnz; k += kThreads) s_val[off + k] *= __ldg(x + s_col[off + k]);
+        __syncthreads();
+        const double* prod = s_val + off;
+        int mean = nrows > 0 ? nnz / nrows : 1;
+        int lanes = 1;
+        while (lanes < 32 && lanes * 2 <= mean) lanes *= 2;
+        const int group = tid / lanes, lane = tid % lanes, groups = kThreads / lanes;
+        const int iters = (nrows + groups - 1) / groups;
+        for (int it = 0; it < iters; ++it) {
+            const int r = r0 + it * groups + group;
+            double acc = 0.0;
+            if (r < r1) {
+                const int s = __ldg(row_ptr + r) - k0, e = __ldg(row_ptr + r + 1) - k0;
+                for (int j = s + lane; j < e; j += lanes) acc += prod[j];
+            }
+            for (int o = lanes >> 1; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o, lanes);
+            if (lane == 0 && r < r1) y[r] = acc;
+        }
+    } else {
+        double acc = 0.0;
+        for (int k = tid; k < nnz; k += kThreads) acc += __ldg(val + k0 + k) * __ldg(x + __ldg(col + k0 + k));
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+        if ((tid & 31) == 0) warp_sums[tid >> 5] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double t = 0.0;
+            for (int w = 0; w < kThreads / 32; ++w) t += warp_sums[w];
+            y[r0] = t;
         }
     }
 }
@@ -143,6 +228,8 @@ struct NangilaSpmv {
     int n = 0, nnz = 0, n_blocks = 0;
     int *d_row_ptr = nullptr, *d_col = nullptr, *d_blocks = nullptr;
     double *d_val = nullptr, *d_x = nullptr, *d_y = nullptr;
+    int* d_status = nullptr;  // set by a kernel whose bulk copy timed out
+    bool plain_loads = false;  // NANGILA_SPMV_PLAIN=1: use the plain-load kernel
     double* d_work = nullptr;   // 9 solver vectors + inverse diagonal, allocated on first solve
     double* d_partial = nullptr;  // reduction scratch: 2 * kRedBlocks + 2
     std::vector<double> h_inv_diag;
@@ -150,7 +237,8 @@ struct NangilaSpmv {
 
 static void free_arrays(NangilaSpmv* c) {
     cudaFree(c->d_row_ptr); cudaFree(c->d_col); cudaFree(c->d_blocks); cudaFree(c->d_val); cudaFree(c->d_x); cudaFree(c->d_y);
-    cudaFree(c->d_work); cudaFree(c->d_partial);
+    cudaFree(c->d_work); cudaFree(c->d_partial); cudaFree(c->d_status);
+    c->d_status = nullptr;
     c->d_row_ptr = c->d_col = c->d_blocks = nullptr;
     c->d_val = c->d_x = c->d_y = c->d_work = c->d_partial = nullptr;
 }
@@ -198,8 +286,18 @@ extern "C" int nangila_spmv_load(NangilaSpmv* c, int n, int nnz, const int* row_
     cudaError_t e;
 #define NG_TRY(call) do { e = (call); if (e != cudaSuccess) { free_arrays(c); return int(e); } } while (0)
     NG_TRY(cudaMalloc(&c->d_row_ptr, sizeof(int) * (size_t(n) + 1)));
-    NG_TRY(cudaMalloc(&c->d_col, sizeof(int) * size_t(nnz > 0 ? nnz : 1)));
-    NG_TRY(cudaMalloc(&c->d_val, sizeof(double) * size_t(nnz > 0 ? nnz : 1)));
+    // padded so that a block's slice can be fetched in whole 16-byte units
+    const size_t padded = (size_t(nnz) + 3) / 4 * 4 + 4;
+    NG_TRY(cudaMalloc(&c->d_col, sizeof(int) * padded));
+    NG_TRY(cudaMalloc(&c->d_val, sizeof(double) * padded));
+    NG_TRY(cudaMemset(c->d_col, 0, sizeof(int) * padded));
+    NG_TRY(cudaMemset(c->d_val, 0, sizeof(double) * padded));
+    NG_TRY(cudaMalloc(&c->d_status, sizeof(int)));
+    NG_TRY(cudaMemset(c->d_status, 0, sizeof(int)));
+    {
+        const char* env = getenv("NANGILA_SPMV_PLAIN");
+        c->plain_loads = env && env[0] == '1';
+    }
     NG_TRY(cudaMalloc(&c->d_blocks, sizeof(int) * (size_t(nb) + 1)));
     NG_TRY(cudaMalloc(&c->d_x, sizeof(double) * size_t(n)));
     NG_TRY(cudaMalloc(&c->d_y, sizeof(double) * size_t(n)));
@@ -224,7 +322,11 @@ extern "C" int nangila_spmv_launch(const int* d_row_ptr, const int* d_col, const
 
 extern "C" int nangila_spmv_device(NangilaSpmv* c, const double* d_x, double* d_y, cudaStream_t stream) {
     if (!c || !c->d_val || !d_x || !d_y) return int(cudaErrorInvalidValue);
-    return nangila_spmv_launch(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y, c->d_blocks, c->n_blocks, stream);
+    if (c->plain_loads) return nangila_spmv_launch(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y, c->d_blocks, c->n_blocks, stream);
+    if (c->n_blocks <= 0) return 0;
+    spmv_row_blocks_bulk_kernel<<<c->n_blocks, kThreads, 0, stream>>>(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y, c->d_blocks, c->d_status,
+                                                                      2000000000ull);
+    return int(cudaGetLastError());
 }
 
 extern "C" int nangila_spmv_host(NangilaSpmv* c, const double* h_x, double* h_y) {
@@ -233,7 +335,17 @@ extern "C" int nangila_spmv_host(NangilaSpmv* c, const double* h_x, double* h_y)
     if (e != cudaSuccess) return int(e);
     int rc = nangila_spmv_device(c, c->d_x, c->d_y, 0);
     if (rc) return rc;
-    return int(cudaMemcpy(h_y, c->d_y, sizeof(double) * size_t(c->n), cudaMemcpyDeviceToHost));
+    cudaError_t e2 = cudaMemcpy(h_y, c->d_y, sizeof(double) * size_t(c->n), cudaMemcpyDeviceToHost);
+    if (e2 != cudaSuccess) return int(e2);
+    return nangila_spmv_status(c);
+}
+
+extern "C" int nangila_spmv_status(NangilaSpmv* c) {
+    if (!c || !c->d_status) return int(cudaErrorInvalidValue);
+    int st = 0;
+    cudaError_t e = cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return int(e);
+    return st ? int(cudaErrorTimeout) : 0;
 }
 
 extern "C" int nangila_spmv_dims(const NangilaSpmv* c, int* n, int* nnz, int* n_blocks) {
@@ -305,5 +417,6 @@ extern "C" int nangila_spmv_bicgstab(NangilaSpmv* c, const double* h_b, double* 
     if (rel_residual) *rel_residual = rel;
     e = cudaGetLastError();
     if (e != cudaSuccess) return int(e);
+    if (int st = nangila_spmv_status(c)) return st;
     return ok ? 0 : -1;
 }

@@ -30,6 +30,7 @@ def kernels_library() -> ctypes.CDLL:
         lib.nangila_spmv_update_values.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         lib.nangila_spmv_host.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         lib.nangila_spmv_device.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        lib.nangila_spmv_status.argtypes = [ctypes.c_void_p]
         lib.nangila_spmv_dims.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         lib.nangila_spmv_build_row_blocks.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
         lib.nangila_spmv_launch.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int, ctypes.c_void_p]
@@ -58,8 +59,23 @@ def build_row_blocks(row_ptr: np.ndarray) -> np.ndarray:
 class DeviceCsr:
     """An ``n x n`` FP64 CSR matrix kept on the current CUDA device."""
 
-    def __init__(self, row_ptr: Sequence[int], col: Sequence[int], val: Sequence[float]):
+    def __init__(self, row_ptr: Sequence[int], col: Sequence[int], val: Sequence[float], plain_loads: bool = False):
+        """``plain_loads`` selects the kernel variant that stages with ordinary loads instead of bulk
+        copies (the default); it exists for comparison and for debugging."""
+        import os
+
         self._lib = kernels_library()
+        previous = os.environ.get("NANGILA_SPMV_PLAIN")
+        os.environ["NANGILA_SPMV_PLAIN"] = "1" if plain_loads else "0"
+        try:
+            self._load(row_ptr, col, val)
+        finally:
+            if previous is None:
+                os.environ.pop("NANGILA_SPMV_PLAIN", None)
+            else:
+                os.environ["NANGILA_SPMV_PLAIN"] = previous
+
+    def _load(self, row_ptr, col, val) -> None:
         self._ctx = self._lib.nangila_spmv_create()
         if not self._ctx:
             raise MemoryError("nangila_spmv_create")
@@ -76,6 +92,10 @@ class DeviceCsr:
         nb = ctypes.c_int(0)
         self._lib.nangila_spmv_dims(self._ctx, None, None, ctypes.byref(nb))
         return nb.value
+
+    def check_status(self) -> None:
+        """Raises if a kernel of this matrix gave up waiting for one of its copies (synchronises)."""
+        _check(self._lib.nangila_spmv_status(self._ctx), "spmv kernel (bulk copy wait)")
 
     def update_values(self, val: Sequence[float]) -> None:
         va = np.ascontiguousarray(val, dtype=np.float64)

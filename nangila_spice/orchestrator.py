@@ -1,0 +1,234 @@
+"""Simulation front end: hardware discovery, partition-count choice, running the solver (one
+process per partition file, or every partition inside one process), merging and validation.
+
+API counterpart: ``nangila-spice/src/nangila_spice/orchestrator.py:47-688`` of the reference. There a
+partitioned request falls back to the single-node solver by default because independent solver
+processes cannot exchange boundary values; here partitions exchange boundary voltages every step
+(``mode="in_process"``, the default for more than one partition), and the merged result is checked
+against a single-matrix run of the same deck when ``validate_partitioned_against_reference`` is set.
+``mode="processes"`` keeps the process-per-partition launch for decks whose partitions do not
+interact (or for ghost-free debugging) and reports the result as experimental.
+"""
+from __future__ import annotations
+
+import json
+import os
+import platform
+import socket
+import subprocess
+import tempfile
+import time
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Optional
+
+from .correctness import WaveformComparison, compare_waveforms, find_nangila_binary, waveform_to_data, within_v1_contract
+from .merger import PartitionWaveform, Waveform, export_csv, export_json, merge_waveforms
+from .parser import Netlist, parse_netlist
+from .partitioner import PartitionResult, partition_netlist
+
+
+@dataclass
+class HardwareTopology:
+    cpu_count: int
+    numa_nodes: int
+    total_ram_gb: float
+    gpu_count: int
+    hostname: str
+    os_name: str
+
+    def summary(self) -> str:
+        return (f"{self.cpu_count} cores, {self.total_ram_gb:.1f}GB RAM, {self.numa_nodes} NUMA nodes, {self.gpu_count} GPUs, "
+                f"{self.hostname} ({self.os_name})")
+
+
+@dataclass
+class SimulationConfig:
+    netlist_path: str
+    partitions: Optional[int] = None
+    method: str = "auto"
+    reltol: float = 1e-3
+    tstop: float = 1e-6
+    dt: float = 1e-12
+    predict_depth: int = 5
+    output_dir: Optional[str] = None
+    output_format: str = "csv"
+    validate_partitioned_against_reference: bool = True
+    reference_vdd: float = 1.8
+    prefer_single_node_fallback_for_partitioned: bool = False
+    verbose: bool = False
+    mode: str = "auto"  # 'auto' | 'in_process' | 'processes'
+    process: str = "TT"
+    vdd: float = 1.8
+    temp: float = 27.0
+    solver: str = "lu"
+    record_every: int = 1
+
+
+@dataclass
+class SimulationResult:
+    waveform: Waveform
+    partition_result: PartitionResult
+    hardware: HardwareTopology
+    wall_time_secs: float
+    per_partition_times: list[float] = field(default_factory=list)
+    success: bool = True
+    error: Optional[str] = None
+    experimental: bool = False
+    validation_status: str = "validated_single_node"
+    warnings: list[str] = field(default_factory=list)
+    reference_comparison: Optional[WaveformComparison] = None
+    solver_stats: dict = field(default_factory=dict)
+
+    def summary(self) -> str:
+        status = "SUCCESS" if self.success else "FAILED"
+        if self.experimental:
+            status += " (EXPERIMENTAL)"
+        lines = ["=== Nangila SPICE Simulation Results ===", f"Status: {status}", f"Validation: {self.validation_status}",
+                 f"Wall time: {self.wall_time_secs:.3f}s", f"Hardware: {self.hardware.summary()}",
+                 f"Partitions: {len(self.partition_result.partitions)} ({self.partition_result.method})",
+                 f"Ghost nodes: {self.partition_result.total_boundary_nodes}", "", self.waveform.summary()]
+        if self.reference_comparison is not None:
+            c = self.reference_comparison
+            lines.append(f"vs single matrix: max {c.max_abs_error:.3e} V, rms {c.rms_error:.3e} V over {len(c.shared_nodes)} nets")
+        lines += [f"warning: {w}" for w in self.warnings]
+        if self.error:
+            lines.append(f"error: {self.error}")
+        return "\n".join(lines)
+
+
+def discover_hardware() -> HardwareTopology:
+    cpus = os.cpu_count() or 1
+    ram = 0.0
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemTotal:"):
+                    ram = float(line.split()[1]) / 1024 / 1024
+                    break
+    except OSError:
+        pass
+    numa = 1
+    try:
+        numa = max(1, len([d for d in os.listdir("/sys/devices/system/node") if d.startswith("node")]))
+    except OSError:
+        pass
+    gpus = 0
+    try:
+        import torch
+
+        gpus = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    except Exception:
+        pass
+    return HardwareTopology(cpus, numa, ram, gpus, socket.gethostname(), platform.system())
+
+
+def auto_partition_count(hw: HardwareTopology, num_devices: int) -> int:
+    """One partition per ~500 devices, at most one per core, at least one."""
+    return max(1, min(hw.cpu_count, num_devices // 500))
+
+
+def _is_nonlinear_netlist(netlist: Netlist) -> bool:
+    return any(d.dev_type in ("M", "D", "Q", "J") for d in netlist.flatten().devices)
+
+
+def _log(config: SimulationConfig, msg: str) -> None:
+    if config.verbose:
+        print(f"[nangila] {msg}")
+
+
+def _single_run(config: SimulationConfig, flat: dict) -> tuple[Waveform, dict]:
+    from . import _native
+
+    r = _native.simulate(json.dumps(flat), config.tstop, config.dt, config.reltol, config.solver, config.record_every, config.predict_depth)
+    return Waveform.from_native(r, title=flat.get("name", "")), {"stats": r["stats"], "newton": r["newton"]}
+
+
+def _run_processes(config: SimulationConfig, pr: PartitionResult, workdir: str) -> tuple[Waveform, list[float]]:
+    exe = find_nangila_binary()
+    if exe is None:
+        raise FileNotFoundError("nangila-node is not built: run `python -m nangila._build --spice`")
+
+    def one(part) -> tuple[PartitionWaveform, float]:
+        pfile = os.path.join(workdir, f"partition_{part.partition_id}.json")
+        out = os.path.join(workdir, f"waveform_{part.partition_id}.json")
+        Path(pfile).write_text(json.dumps(part.netlist))
+        t0 = time.perf_counter()
+        proc = subprocess.run([exe, "--partition", pfile, "--node-id", str(part.partition_id), "-k", str(len(pr.partitions)),
+                               "--tstop", repr(config.tstop), "--dt", repr(config.dt), "--reltol", repr(config.reltol),
+                               "--predict-depth", str(config.predict_depth), "--record-every", str(config.record_every),
+                               "--waveform-json", out], capture_output=True, text=True)
+        dt = time.perf_counter() - t0
+        if proc.returncode not in (0, 3) or not os.path.exists(out):
+            raise RuntimeError(f"partition {part.partition_id}: nangila-node exit {proc.returncode}: {proc.stderr[-300:]}")
+        w = Waveform.from_json_file(out)
+        return PartitionWaveform(part.partition_id, w.times.tolist(), {n: v.tolist() for n, v in w.traces.items()}, set(part.boundary_nodes)), dt
+
+    with ThreadPoolExecutor(max_workers=min(len(pr.partitions), os.cpu_count() or 1)) as ex:
+        results = list(ex.map(one, pr.partitions))
+    return merge_waveforms([r[0] for r in results], title=Path(config.netlist_path).name), [r[1] for r in results]
+
+
+def run_simulation(config: SimulationConfig) -> SimulationResult:
+    """Parse, partition, solve, merge, validate, export."""
+    from . import _native
+
+    t_start = time.perf_counter()
+    hw = discover_hardware()
+    netlist = parse_netlist(config.netlist_path)
+    k = config.partitions if config.partitions else auto_partition_count(hw, netlist.flatten().num_devices)
+    nonlinear = _is_nonlinear_netlist(netlist)
+    flat = netlist.to_native(config.process, config.vdd, config.temp)
+    warnings = [f"parser: {w}" for w in flat.pop("warnings", [])]
+    pr = partition_netlist(netlist, k, config.method, process=config.process, vdd=config.vdd, temp=config.temp)
+    k = len(pr.partitions)
+    _log(config, f"{flat['num_nodes']} nets, {len(flat['elements'])} elements, {k} partition(s)")
+    result = SimulationResult(Waveform(), pr, hw, 0.0)
+    result.warnings = warnings
+    try:
+        if k == 1 or config.prefer_single_node_fallback_for_partitioned:
+            result.waveform, result.solver_stats = _single_run(config, flat)
+            result.validation_status = "validated_single_node" if k == 1 else "single_node_fallback"
+            if k > 1:
+                result.warnings.append("partitioned request served by the single-matrix solver (prefer_single_node_fallback_for_partitioned)")
+            result.success = bool(result.solver_stats["stats"]["completed"])
+        else:
+            mode = "in_process" if config.mode == "auto" else config.mode
+            if mode == "in_process":
+                r = _native.simulate_partitioned(pr.partition_files(), config.tstop, config.dt, config.reltol, config.predict_depth, True, config.record_every)
+                result.waveform = Waveform.from_native(r, title=Path(config.netlist_path).name)
+                result.solver_stats = {"stats": r["stats"]}
+                result.success = bool(r["stats"]["completed"])
+                if r["stats"]["unconverged_steps"]:
+                    result.warnings.append(f"{r['stats']['unconverged_steps']} steps hit the relaxation sweep limit")
+            elif mode == "processes":
+                with tempfile.TemporaryDirectory() as tmp:
+                    result.waveform, result.per_partition_times = _run_processes(config, pr, config.output_dir or tmp)
+                result.experimental = True
+                result.warnings.append("process-per-partition run: partitions did not exchange boundary values")
+            else:
+                raise ValueError(f"unknown mode '{config.mode}'")
+            result.validation_status = "partitioned_unvalidated"
+            if config.validate_partitioned_against_reference:
+                ref, _ = _single_run(config, flat)
+                cmp_ = compare_waveforms(waveform_to_data(ref, "single"), waveform_to_data(result.waveform, "partitioned"), vdd=config.reference_vdd)
+                result.reference_comparison = cmp_
+                ok, profile = within_v1_contract(cmp_, nonlinear=nonlinear, vdd=config.reference_vdd)
+                result.validation_status = "partitioned_validated" if ok else "partitioned_outside_contract"
+                if not ok:
+                    result.warnings.append(f"partitioned result differs from the single-matrix run by {cmp_.max_abs_error:.3e} V "
+                                           f"(contract {profile.max_abs_tol:.1e} V); returning the single-matrix waveform")
+                    result.waveform = ref
+    except Exception as e:  # surfaced in the result, as the reference's front end does
+        result.success = False
+        result.error = f"{type(e).__name__}: {e}"
+    result.wall_time_secs = time.perf_counter() - t_start
+    if config.output_dir and result.success:
+        os.makedirs(config.output_dir, exist_ok=True)
+        stem = Path(config.netlist_path).stem
+        if config.output_format == "json":
+            export_json(result.waveform, os.path.join(config.output_dir, f"{stem}.json"))
+        else:
+            export_csv(result.waveform, os.path.join(config.output_dir, f"{stem}.csv"))
+    return result

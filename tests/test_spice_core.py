@@ -1,0 +1,300 @@
+"""CPU tests of the circuit simulator's native core (nangila_spice._native): devices, sources, MNA,
+linear solvers, Newton, transient accuracy against closed forms, parser, predictors, codec, fabric,
+.nz container, PVT, balancer, generators. Test plan modelled on the unit tests beside each module of
+the reference's nangila-node crate."""
+import json
+import math
+
+import numpy as np
+import pytest
+
+N = pytest.importorskip("nangila_spice._native")
+
+
+def _rc(ic=True):
+    nl = {"name": "rc", "num_nodes": 2, "elements": [
+        {"VoltageSource": {"pos": 1, "neg": 0, "source": {"Dc": 1.8}}},
+        {"Resistor": {"a": 1, "b": 2, "r": 1000.0}},
+        {"Capacitor": {"a": 2, "b": 0, "c": 1e-14}}],
+        "ghost_map": [], "node_names": ["vdd", "out"], "initial_conditions": [[1, 1.8], [2, 0.0]] if ic else []}
+    return json.dumps(nl)
+
+
+def test_scale_suffixes():
+    assert N.parse_scaled("10k") == 1e4
+    assert N.parse_scaled("2.5meg") == 2.5e6
+    assert math.isclose(N.parse_scaled("10pF"), 1e-11)
+    assert math.isclose(N.parse_scaled("1e-9"), 1e-9)
+    assert math.isclose(N.parse_scaled("100f"), 1e-13)
+    assert N.parse_scaled("abc") is None
+
+
+def test_pulse_source_shape():
+    src = json.dumps({"Pulse": {"v1": 0.0, "v2": 1.8, "td": 1e-9, "tr": 1e-10, "tf": 2e-10, "pw": 5e-10, "per": 2e-9}})
+    assert N.source_value(src, 0.5e-9) == 0.0
+    assert math.isclose(N.source_value(src, 1.05e-9), 0.9)
+    assert N.source_value(src, 1.3e-9) == 1.8
+    assert math.isclose(N.source_value(src, 1.7e-9), 0.9)
+    assert N.source_value(src, 1.9e-9) == 0.0
+    assert N.source_value(src, 3.3e-9) == 1.8  # second period
+    assert N.source_value(json.dumps({"Dc": 0.7}), 123.0) == 0.7
+
+
+def test_diode_and_mosfet_models():
+    i_f, g_f = N.diode_eval(0.7)
+    i_l, _ = N.diode_eval(0.1)
+    i_r, g_r = N.diode_eval(-1.0)
+    assert i_f > 100 * i_l > 0 and g_f > 0
+    assert -2e-14 < i_r < 0 and g_r >= 1e-12
+    assert N.mosfet_eval(0.2, 1.0)[3] == "Cutoff" and N.mosfet_eval(0.2, 1.0)[0] == 0.0
+    id_sat, gm, gds, reg = N.mosfet_eval(1.0, 1.5)
+    assert reg == "Saturation" and id_sat > 0 and gm > 0 and gds > 0
+    assert math.isclose(id_sat, 0.5 * 1e-3 * 0.25 * (1 + 0.1 * 1.5))
+    id_lin, _, _, reg = N.mosfet_eval(1.0, 0.2)
+    assert reg == "Linear" and 0 < id_lin < id_sat
+    # derivatives match finite differences
+    h = 1e-6
+    for vgs, vds in ((1.0, 1.5), (1.0, 0.2), (1.2, 0.45)):
+        _, gm, gds, _ = N.mosfet_eval(vgs, vds)
+        assert math.isclose(gm, (N.mosfet_eval(vgs + h, vds)[0] - N.mosfet_eval(vgs - h, vds)[0]) / (2 * h), rel_tol=1e-4)
+        assert math.isclose(gds, (N.mosfet_eval(vgs, vds + h)[0] - N.mosfet_eval(vgs, vds - h)[0]) / (2 * h), rel_tol=1e-4)
+    # a PMOS mirrors the NMOS
+    idp = N.mosfet_eval(-1.0, -1.5, pmos=True)[0]
+    assert math.isclose(idp, -id_sat)
+
+
+def test_netlist_json_roundtrip_keeps_every_element_kind():
+    nl = {"name": "all", "num_nodes": 5, "elements": [
+        {"Resistor": {"a": 1, "b": 2, "r": 50.0}}, {"Capacitor": {"a": 2, "b": 0, "c": 1e-12}}, {"Inductor": {"a": 2, "b": 3, "l": 1e-9}},
+        {"VoltageSource": {"pos": 1, "neg": 0, "source": {"Pulse": {"v1": 0, "v2": 1, "td": 0, "tr": 1e-12, "tf": 1e-12, "pw": 1e-9, "per": 2e-9}}}},
+        {"CurrentSource": {"pos": 0, "neg": 3, "source": {"Dc": 1e-3}}}, {"GhostSource": {"node": 4, "voltage": 0.5}},
+        {"Diode": {"p": 3, "n": 0, "model": {"is": 2e-14, "vt": 0.02585, "n": 1.1, "node_p": 3, "node_n": 0}}},
+        {"Mosfet": {"d": 5, "g": 3, "s": 0, "b": 0, "model": {"kind": "Pmos", "vth": 0.4, "beta": 2e-3, "lambda": 0.02, "node_g": 3, "node_d": 5, "node_s": 0}}}],
+        "ghost_map": [[12345, 4, 1]], "node_names": ["a", "b", "c", "d", "e"], "initial_conditions": [[2, 0.25]]}
+    back = json.loads(N.netlist_roundtrip(json.dumps(nl)))
+    assert back == nl
+
+
+@pytest.mark.parametrize("solver", ["lu", "dense", "krylov"])
+def test_rc_charging_matches_closed_form(solver):
+    r = N.simulate(_rc(), 100e-12, 0.25e-12, solver=solver)
+    assert r["stats"]["completed"] and r["stats"]["total_steps"] == 400
+    t = np.array(r["time"])
+    v = np.array(r["values"])[:, 1]
+    assert np.abs(v - 1.8 * (1 - np.exp(-t / 10e-12))).max() < 1e-3
+    assert np.allclose(np.array(r["values"])[:, 0], 1.8)
+
+
+def test_dc_operating_point_is_the_start_without_ic():
+    ok, v = N.dc_operating_point(_rc(ic=False))
+    assert ok and math.isclose(v[0], 1.8) and math.isclose(v[1], 1.8, rel_tol=1e-6)
+    r = N.simulate(_rc(ic=False), 10e-12, 1e-12)
+    assert np.allclose(np.array(r["values"])[:, 1], 1.8, atol=1e-6)
+
+
+def test_rlc_ringing_matches_closed_form():
+    # series RLC driven by a step: underdamped response of the capacitor voltage
+    R, L, C = 10.0, 1e-9, 1e-12
+    nl = {"name": "rlc", "num_nodes": 3, "elements": [
+        {"VoltageSource": {"pos": 1, "neg": 0, "source": {"Dc": 1.0}}}, {"Resistor": {"a": 1, "b": 2, "r": R}},
+        {"Inductor": {"a": 2, "b": 3, "l": L}}, {"Capacitor": {"a": 3, "b": 0, "c": C}}],
+        "ghost_map": [], "node_names": ["in", "m", "out"], "initial_conditions": [[1, 1.0], [2, 1.0], [3, 0.0]]}
+    r = N.simulate(json.dumps(nl), 400e-12, 0.05e-12)
+    t = np.array(r["time"])
+    v = np.array(r["values"])[:, 2]
+    alpha, w0 = R / (2 * L), 1 / math.sqrt(L * C)
+    wd = math.sqrt(w0 * w0 - alpha * alpha)
+    exact = 1 - np.exp(-alpha * t) * (np.cos(wd * t) + alpha / wd * np.sin(wd * t))
+    assert np.abs(v - exact).max() < 0.02 and v.max() > 1.5  # it rings above the supply
+
+
+def test_diode_clamp_and_inverter_converge():
+    deck = "* clamp\nV1 in 0 DC 1.8\nR1 in out 1k\nD1 out 0 dm\n.model dm D (is=1e-14 n=1)\n.end\n"
+    js, warnings = N.parse_spice(deck)
+    ok, v = N.dc_operating_point(js)
+    nl = json.loads(js)
+    out = v[nl["node_names"].index("out")]
+    assert ok and 0.55 < out < 0.8
+    i_d, _ = N.diode_eval(out, vt=8.617333e-5 * 300.15)
+    assert math.isclose(i_d, (1.8 - out) / 1e3, rel_tol=1e-3)  # KCL at the junction
+    inv = ("* inv\nVDD vdd 0 DC 1.8\nVIN in 0 DC {vin}\nM1 out in vdd vdd pch w=2u l=180n\nM2 out in 0 0 nch w=1u l=180n\n"
+           ".model nch NMOS (vto=0.45 kp=200u lambda=0.05)\n.model pch PMOS (vto=-0.45 kp=100u lambda=0.05)\n.end\n")
+    outs = []
+    for vin in (0.0, 0.9, 1.8):
+        js, _ = N.parse_spice(inv.format(vin=vin))
+        ok, v = N.dc_operating_point(js)
+        assert ok
+        outs.append(v[json.loads(js)["node_names"].index("out")])
+    assert outs[0] > 1.79 and outs[2] < 0.01 and outs[0] > outs[1] > outs[2]
+
+
+def test_parser_subcircuits_params_continuations_and_ic():
+    deck = """my title line
+.param rval=2k cval=5f
+.subckt stage a b
+R1 a b rval
+C1 b 0 cval
+.ends
+V1 in 0 PULSE(0 1.8 0 10p
++ 10p 100p 300p)
+X1 in n1 stage
+X2 n1 n2 stage
+.ic V(n1)=0.3 V(n2)=0.1
+.ghost n2 3 1
+.end
+"""
+    js, warnings = N.parse_spice(deck, "t.sp")
+    nl = json.loads(js)
+    assert warnings == []
+    assert nl["node_names"] == ["in", "n1", "n2"] and nl["num_nodes"] == 3
+    kinds = [next(iter(e)) for e in nl["elements"]]
+    assert kinds == ["VoltageSource", "Resistor", "Capacitor", "Resistor", "Capacitor"]
+    assert nl["elements"][1]["Resistor"] == {"a": 1, "b": 2, "r": 2000.0}
+    assert math.isclose(nl["elements"][4]["Capacitor"]["c"], 5e-15)
+    assert nl["elements"][0]["VoltageSource"]["source"]["Pulse"]["per"] == 300e-12
+    assert sorted(map(tuple, nl["initial_conditions"])) == [(2, 0.3), (3, 0.1)]
+    assert nl["ghost_map"] == [[N.net_name_hash("N2"), 3, 1]]
+
+
+def test_parser_pvt_scaling():
+    deck = "* m\nVDD vdd 0 DC 1.8\nM1 d g 0 0 nch w=1u l=100n\n.model nch NMOS (vto=0.5 kp=100u)\n.end\n"
+    tt = json.loads(N.parse_spice(deck, "m", "TT", 1.8, 27.0)[0])["elements"]
+    ff = json.loads(N.parse_spice(deck, "m", "FF", 1.98, 27.0)[0])["elements"]
+    hot = json.loads(N.parse_spice(deck, "m", "TT", 1.8, 125.0)[0])["elements"]
+    m = lambda els: els[1]["Mosfet"]["model"]  # noqa: E731
+    assert math.isclose(m(tt)["vth"], 0.5) and math.isclose(m(tt)["beta"], 100e-6 * 10)
+    assert math.isclose(m(ff)["vth"], 0.4) and math.isclose(m(ff)["beta"], 1.15 * m(tt)["beta"])
+    assert math.isclose(ff[0]["VoltageSource"]["source"]["Dc"], 1.98)
+    assert m(hot)["vth"] < m(tt)["vth"] and m(hot)["beta"] < m(tt)["beta"]
+
+
+def test_sparse_solvers_agree_and_refine_bad_scaling():
+    import scipy.sparse as sp
+
+    rng = np.random.default_rng(0)
+    n = 120
+    a = (sp.random(n, n, density=0.05, random_state=1, format="csr") + sp.diags(rng.uniform(1, 2, n) * 10.0 ** rng.integers(-6, 12, n))).tocsr()
+    a.sort_indices()
+    b = rng.standard_normal(n)
+    for solver in ("lu", "dense", "krylov"):
+        ok, x, _ = N.solve_csr(n, a.indptr.tolist(), a.indices.tolist(), a.data.tolist(), b.tolist(), solver)
+        x = np.array(x)
+        assert ok
+        assert (np.abs(a @ x - b) / (abs(a) @ np.abs(x) + np.abs(b))).max() < (1e-9 if solver == "lu" else 1e-6)
+    ok, _, _ = N.solve_csr(2, [0, 1, 2], [0, 0], [1.0, 1.0], [1.0, 1.0], "lu")  # singular
+    assert not ok
+    y = N.csr_spmv(n, a.indptr.tolist(), a.indices.tolist(), a.data.tolist(), b.tolist())
+    assert np.allclose(y, a @ b)
+
+
+def test_ghost_pin_and_corrections_and_rollback():
+    nl = json.loads(_rc())
+    nl["elements"] = nl["elements"][1:]  # no source: node 1 becomes a ghost driven from outside
+    nl["ghost_map"] = [[777, 1, 1]]
+    nl["initial_conditions"] = [[2, 0.0]]
+    inject = [(1, 0.0, [(777, 1.0)])]
+    r = N.simulate(json.dumps(nl), 60e-12, 1e-12, inject=inject)
+    v = np.array(r["values"])
+    assert np.allclose(v[1:, 0], 1.0, atol=1e-6)  # pinned to the corrected value (first prediction is flat)
+    assert 0.99 < v[-1, 1] < 1.0
+    assert r["stats"]["prediction_hits"] + r["stats"]["prediction_misses"] == 1
+    # a rollback request before any checkpoint exists is ignored; the run still completes
+    r = N.simulate(json.dumps(nl), 10e-12, 1e-12, inject=inject, rollbacks=[0.0])
+    assert r["stats"]["completed"]
+
+
+def test_predictors_classifier_and_confidence():
+    g = N.GhostNode(1, 0)
+    for k in range(8):  # a ramp is predicted exactly by the linear predictor
+        g.apply_correction(0.1 * k, k * 1e-12, 1e-3)
+    assert g.signal_class() == "Smooth"
+    v, name = g.predict_named(10e-12)
+    assert name == "Linear" and math.isclose(v, 1.0, rel_tol=1e-9)
+    d = N.GhostNode(2, 0)
+    for k in range(10):  # decaying exponential
+        d.apply_correction(math.exp(-k / 3.0), k * 1e-12, 1e-3)
+    assert d.signal_class() == "Decaying" and d.predict_named(10e-12)[1] == "Exponential"
+    assert abs(d.predict(10e-12) - math.exp(-10 / 3.0)) < 0.01
+    s = N.GhostNode(3, 0)
+    for k in range(10):  # alternating signal
+        s.apply_correction((-1) ** k * 0.5, k * 1e-12, 1e-3)
+    assert s.signal_class() == "Stiff" and s.predict_named(10e-12)[1] == "RungeKutta"
+    c = N.AdaptiveConfidence(6)
+    assert c.effective_depth() == 6 and c.confidence_for(9) == 0.5
+    for _ in range(40):
+        c.update(1, True)
+    deep = c.effective_depth()
+    c.update(2, False)
+    assert deep > 6 and c.effective_depth() < deep and c.effective_depth() >= 1
+    ctl = N.SpeculativeDepthController(8, 1, 16)
+    for _ in range(64):
+        ctl.record_prediction(True)
+    assert ctl.depth() == 16
+    ctl.record_rollback()
+    assert ctl.depth() == 12
+    for _ in range(32):
+        ctl.record_prediction(False)
+    assert ctl.depth() == 1
+
+
+def test_codec_roundtrip_and_fabric():
+    updates = [(1, 1.2345), (2, -0.5), (3, 0.70000000001)]
+    predicted = [(1, 1.2), (2, -0.45), (3, 0.7)]
+    r = N.codec_roundtrip(updates, predicted)
+    got = dict(r["updates"])
+    assert r["ok"] and json.loads(r["bytes"])["scale"] > 0
+    for k, v in updates:
+        assert abs(got[k] - v) <= 0.05 / 32767 + 1e-15  # one quantization step of the largest delta
+    assert r["ratio"] > 1.3
+    r = N.codec_roundtrip([(1, 1.0)], [(1, 1.0)])
+    assert r["skipped"] == 1 and r["updates"] == []
+    residuals, done, total = N.fabric_selftest(4, 10)
+    assert residuals == 4 * 3 * 10 and done == 4 * 3
+    assert math.isclose(total, sum((r + 0.5) * 12 for r in range(10)), rel_tol=1e-4)
+
+
+def test_nz_container_bound_and_raw_fallback():
+    t = np.linspace(0, 1e-9, 1000)
+    smooth = 0.9 * (1 - np.exp(-t / 2e-10))
+    spiky = np.where((np.arange(1000) % 97) == 0, 50.0, 0.0) * np.sign(np.sin(np.arange(1000)))
+    data, st = N.nz_compress(["smooth", "spiky"], t.tolist(), [smooth.tolist(), spiky.tolist()], 1e-5)
+    names, time, sig, hdr = N.nz_decompress(data)
+    assert names == ["smooth", "spiky"] and hdr["version"] == 2 and np.array_equal(time, t)
+    assert np.abs(np.array(sig[0]) - smooth).max() <= 1e-5 * (1 + 1e-9)
+    assert np.abs(np.array(sig[1]) - spiky).max() <= 1e-5 * (1 + 1e-9)
+    assert st["raw_blocks"] >= 1 and st["predicted_blocks"] >= 4 and st["compression_ratio"] > 2.0
+    with pytest.raises(RuntimeError):
+        N.nz_decompress(b"XXXX" + data[4:])
+    with pytest.raises(RuntimeError):
+        N.nz_decompress(data[: len(data) // 2])
+
+
+def test_pvt_delta_cache_and_balancer():
+    t = [k * 1e-12 for k in range(5)]
+    golden = [[1.8, 0.1 * k] for k in range(5)]
+    near = N.pvt_delta(t, golden, "FF", 1.89, 40.0)
+    assert near["used_delta_mode"] and near["bytes_roundtrip"]
+    scale = 1.89 / 1.8 * math.sqrt(1.15)
+    assert math.isclose(near["waveform"][4][1], 0.4 * scale - 0.5e-3 * 13.0)
+    far = N.pvt_delta(t, golden, "SS", 1.2, 125.0)
+    assert not far["used_delta_mode"] and far["peak_delta_v"] == 0.0
+    found, size, hits, misses, evictions = N.pvt_cache_selftest(2, ["a", "b", "c"], ["a", "b", "c"])
+    assert found == [False, True, True] and size == 2 and hits == 2 and misses == 1 and evictions == 1
+    fast = [1e-3] * 20
+    st, plans, score = N.balance_plan([(0, 1000, fast), (1, 1000, fast), (2, 1000, fast), (3, 1000, [4e-3] * 20)])
+    assert [s[0] for s in st] == [3] and math.isclose(st[0][1], 4.0)
+    assert plans and plans[0][0] == 3 and plans[0][1] in (0, 1, 2) and plans[0][2] == int(1000 * 0.25 * 0.75)
+    assert math.isclose(score, 0.75)
+    assert N.balance_plan([(0, 10, fast), (1, 10, fast)])[0] == []
+
+
+def test_generators_and_benchmark_suite():
+    lad = json.loads(N.generate_circuit("rc_ladder", 10))
+    assert lad["num_nodes"] == 11 and len(lad["elements"]) == 21
+    cim = json.loads(N.generate_circuit("cim_array", 4, 5))
+    assert cim["num_nodes"] == 9 and len(cim["elements"]) == 4 + 20 + 5
+    mesh = N.generate_circuit("resistor_mesh", 6)
+    ok, v = N.dc_operating_point(mesh)
+    assert ok and math.isclose(v[0], 1.8) and min(v[:36]) == v[35] < 1.8  # the sink corner is the lowest node
+    rows = N.run_benchmark_suite()
+    assert len(rows) == 4 and all(r["completed"] and r["steps"] == 100 for r in rows)

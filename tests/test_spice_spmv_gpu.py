@@ -28,8 +28,9 @@ def _reference(row_ptr, col, val, x):
     return y
 
 
+@pytest.mark.parametrize("plain", [False, True], ids=["bulk", "plain"])
 @pytest.mark.parametrize("case", ["short", "mixed", "long", "empty_rows", "dense_ish"])
-def test_spmv_matches_host(case):
+def test_spmv_matches_host(case, plain):
     from nangila_spice.gpu import DeviceCsr
 
     rng = np.random.default_rng(1)
@@ -48,7 +49,7 @@ def test_spmv_matches_host(case):
         lens = rng.integers(100, 400, n)
     row_ptr, col, val = _random_csr(n, lens, 2)
     x = rng.standard_normal(n)
-    m = DeviceCsr(row_ptr, col, val)
+    m = DeviceCsr(row_ptr, col, val, plain_loads=plain)
     y = m.matvec(x)
     ref = _reference(row_ptr, col, val, x)
     scale = np.abs(ref).max() + 1.0
@@ -59,6 +60,7 @@ def test_spmv_matches_host(case):
     m.update_values(val * 2.0)
     m.matvec_device(xd, yd, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+    m.check_status()
     assert np.abs(yd.cpu().numpy() - 2.0 * ref).max() / scale < 1e-13
     m.close()
 
