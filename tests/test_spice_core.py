@@ -262,7 +262,9 @@ def test_nz_container_bound_and_raw_fallback():
     assert names == ["smooth", "spiky"] and hdr["version"] == 2 and np.array_equal(time, t)
     assert np.abs(np.array(sig[0]) - smooth).max() <= 1e-5 * (1 + 1e-9)
     assert np.abs(np.array(sig[1]) - spiky).max() <= 1e-5 * (1 + 1e-9)
-    assert st["raw_blocks"] >= 1 and st["predicted_blocks"] >= 4 and st["compression_ratio"] > 2.0
+    assert st["raw_blocks"] >= 1 and st["predicted_blocks"] >= 4 and st["compression_ratio"] > 1.4
+    _, st_smooth = N.nz_compress(["smooth"], t.tolist(), [smooth.tolist()], 1e-5)
+    assert st_smooth["raw_blocks"] == 0 and st_smooth["compression_ratio"] > 3.5
     with pytest.raises(RuntimeError):
         N.nz_decompress(b"XXXX" + data[4:])
     with pytest.raises(RuntimeError):

@@ -1,0 +1,281 @@
+"""CPU tests of the circuit simulator's Python front end: text-level parser, circuit graph,
+partitioner, in-process and process-per-partition runs, merging, correctness contract, PVT sweep,
+.nz reader, gate-level synthesis, report and command line. Plan modelled on the reference's
+``nangila-spice/src/tests`` suites (partitioner, integration, correctness, PVT orchestrator)."""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+pytest.importorskip("nangila_spice._native")
+
+import nangila_spice as ns  # noqa: E402
+from nangila_spice import _native as N  # noqa: E402
+from nangila_spice.benchmark import generate_cim_netlist, generate_rc_ladder_netlist, run_scaling_study  # noqa: E402
+from nangila_spice.parser import parse_netlist_text  # noqa: E402
+from nangila_spice.partitioner import partition_flat  # noqa: E402
+
+LATCH = """* cross-coupled inverters plus a passive tail
+VDD vdd 0 DC 1.8
+M1 q qb vdd vdd pch w=2u l=180n
+M2 q qb 0 0 nch w=1u l=180n
+M3 qb q vdd vdd pch w=2u l=180n
+M4 qb q 0 0 nch w=1u l=180n
+R1 q t1 20k
+C1 t1 0 5f
+R2 t1 t2 1k
+C2 t2 0 5f
+R3 t2 t3 1k
+C3 t3 0 5f
+.model nch NMOS (vto=0.45 kp=200u lambda=0.05)
+.model pch PMOS (vto=-0.45 kp=100u lambda=0.05)
+.ic V(q)=1.8 V(qb)=0 V(t1)=0 V(t2)=0 V(t3)=0
+.end
+"""
+
+
+def _write(tmp_path, name, text):
+    p = tmp_path / name
+    p.write_text(text)
+    return str(p)
+
+
+def test_text_parser_and_flatten():
+    nl = parse_netlist_text("""title
+.global vdd
+.subckt inv a y
+M1 y a vdd vdd pch w=2u l=180n
+M2 y a 0 0 nch
+.ends
+X1 in mid inv
+X2 mid out inv
+R1 out 0 10k
+C1 out 0 1f
+""")
+    assert nl.title == "title" and nl.num_devices == 4 and "INV" in nl.subcircuits and nl.global_nodes == {"vdd"}
+    flat = nl.flatten()
+    assert [d.name for d in flat.devices] == ["x1.m1", "x1.m2", "x2.m1", "x2.m2", "R1", "C1"]
+    assert flat.devices[0].nodes == ["mid", "in", "vdd", "vdd"] and flat.devices[0].params == {"w": "2u", "l": "180n"}
+    assert flat.devices[2].nodes[0] == "out" and flat.devices[1].model == "nch"
+    assert flat.num_nodes == 5  # in, mid, out, vdd, 0
+    with pytest.raises(FileNotFoundError):
+        ns.parse_netlist("/nonexistent/deck.sp")
+
+
+def test_circuit_graph_and_feedback_detection():
+    nl = parse_netlist_text(LATCH)
+    cg = ns.build_circuit_graph(nl)
+    assert cg.num_devices == 11 and cg.num_nets == 7 and cg.num_edges > 20
+    assert len(cg.feedback_groups) == 1 and cg.feedback_groups[0] == {"M1", "M2", "M3", "M4"}
+    assert cg.graph["D:M1"]["N:qb"]["weight"] == 10 and cg.graph["D:M1"]["N:vdd"]["weight"] == 2  # source + bulk on the supply
+    ladder = ns.build_circuit_graph(parse_netlist_text(generate_rc_ladder_netlist(20)))
+    assert ladder.feedback_groups == []
+
+
+@pytest.mark.parametrize("method", ["spectral", "bisect"])
+def test_partitioner_properties(method):
+    flat = json.loads(N.generate_circuit("rc_ladder", 63))
+    res = partition_flat(flat, 4, method)
+    assert len(res.partitions) == 4 and res.method == method
+    owned = [p.internal_nodes for p in res.partitions]
+    assert sum(len(o) for o in owned) == 63 and len(set().union(*owned)) == 63  # node_1 is held by the source and replicated
+    assert max(len(o) for o in owned) - min(len(o) for o in owned) <= 2
+    assert res.total_cut_edges == 3 and res.total_boundary_nodes == 6  # a chain cut three times
+    assert 1.0 <= res.balance_ratio < 1.15
+    for p in res.partitions:
+        nl = p.netlist
+        assert nl["num_nodes"] == len(nl["node_names"]) == len(p.internal_nodes) + len(p.boundary_nodes) + (1 if "node_1" in nl["node_names"] else 0)
+        for net_id, local, owner in nl["ghost_map"]:
+            name = nl["node_names"][local - 1]
+            assert net_id == N.net_name_hash(name) and name in res.partitions[owner].internal_nodes
+    assert "Partitions: 4" in res.summary()
+    with pytest.raises(ValueError):
+        partition_flat(flat, 0)
+    assert len(partition_flat(flat, 1).partitions) == 1
+
+
+def test_partitioner_keeps_feedback_loop_together(tmp_path):
+    res = ns.partition_netlist(ns.parse_netlist(_write(tmp_path, "latch.sp", LATCH)), 2, "spectral")
+    assert res.feedback_groups_enforced == 1
+    assert res.net_assignment["q"] == res.net_assignment["qb"]
+    assert {"M1", "M2", "M3", "M4"} <= set(res.partitions[res.net_assignment["q"]].device_names)
+
+
+@pytest.mark.parametrize("k", [2, 3, 5])
+def test_partitioned_run_matches_single_matrix(tmp_path, k):
+    path = _write(tmp_path, "ladder.sp", generate_rc_ladder_netlist(40, 1e3, 10e-15))
+    res = ns.simulate(path, partitions=k, tstop=300e-12, dt=1e-12, method="bisect")
+    assert res.success and res.validation_status == "partitioned_validated", res.summary()
+    assert res.reference_comparison.max_abs_error < 1e-5 and len(res.partition_result.partitions) == k
+    assert res.waveform.num_nodes == 41 and res.waveform.num_points == 301
+    st = res.solver_stats["stats"]
+    assert st["messages"] > 0 and st["codec_ratio"] > 1.0 and st["unconverged_steps"] == 0
+    assert "partitioned_validated" in res.summary()
+
+
+def test_partitioned_nonlinear_latch_with_tail(tmp_path):
+    res = ns.simulate(_write(tmp_path, "latch.sp", LATCH), partitions=2, tstop=200e-12, dt=0.5e-12, method="spectral")
+    assert res.success and res.validation_status == "partitioned_validated", res.summary()
+    assert res.waveform.voltage("q", 200e-12) > 1.6 and res.waveform.voltage("t3", 200e-12) > 0.5
+    assert res.waveform.voltage("nope", 0.0) is None and res.waveform.voltage("q", 1.0) is None
+
+
+def test_single_partition_exports_and_processes_mode(tmp_path):
+    path = _write(tmp_path, "cim.sp", generate_cim_netlist(4, 4))
+    out = tmp_path / "out"
+    res = ns.simulate(path, partitions=1, tstop=1e-9, dt=5e-12, output_dir=str(out), output_format="csv")
+    assert res.success and res.validation_status == "validated_single_node"
+    rows = (out / "cim.csv").read_text().splitlines()
+    assert rows[0].split(",")[0] == "time" and len(rows) == 202
+    ns.export_json(res.waveform, str(out / "w.json"))
+    assert json.loads((out / "w.json").read_text())["num_points"] == 201
+    # process-per-partition launch of the solver binary: bit lines are only coupled through the held word lines
+    res2 = ns.simulate(path, partitions=2, tstop=1e-9, dt=5e-12, mode="processes", method="bisect")
+    assert res2.success and res2.experimental, res2.summary()
+    assert res2.reference_comparison is not None and res2.reference_comparison.max_abs_error < 1e-6
+
+
+def test_merge_prefers_owner_over_ghost_copy():
+    from nangila_spice.merger import PartitionWaveform, merge_waveforms
+
+    a = PartitionWaveform(0, [0.0, 1.0, 2.0], {"x": [0.0, 1.0, 2.0], "g": [9.0, 9.0, 9.0]}, {"g"})
+    b = PartitionWaveform(1, [0.0, 2.0], {"g": [0.0, 4.0], "y": [1.0, 3.0]}, set())
+    w = merge_waveforms([a, b])
+    assert w.node_names == ["x", "g", "y"] or set(w.node_names) == {"x", "g", "y"}
+    assert w.traces["g"].tolist() == [0.0, 2.0, 4.0] and w.traces["y"].tolist() == [1.0, 2.0, 3.0]
+    assert w.time_range == (0.0, 2.0) and w.voltage("x", 0.5) == 0.5 and len(w.points) == 3
+
+
+def test_correctness_contract():
+    t = np.linspace(0, 1e-9, 101)
+    ref = ns.WaveformData("ref", "", ["a"], t.tolist(), {"a": (1.8 * t / 1e-9).tolist()})
+    good = ns.WaveformData("c", "", ["a"], t.tolist(), {"a": (1.8 * t / 1e-9 + 2e-4).tolist()})
+    late = ns.WaveformData("c", "", ["a"], t.tolist(), {"a": (1.8 * np.clip(t - 30e-12, 0, None) / 1e-9).tolist()})
+    c = ns.compare_waveforms(ref, good)
+    assert math.isclose(c.max_abs_error, 2e-4, rel_tol=1e-6) and c.sample_count == 101 and c.max_edge_timing_error < 1e-12
+    assert ns.within_v1_contract(c, nonlinear=False)[0]
+    c2 = ns.compare_waveforms(ref, late)
+    assert math.isclose(c2.max_edge_timing_error, 30e-12, rel_tol=1e-3)
+    assert not ns.within_v1_contract(c2, nonlinear=True)[0]
+    assert ns.v1_tolerance_profile(nonlinear=True).edge_tol == 10e-12 and math.isclose(ns.v1_tolerance_profile(nonlinear=False).max_abs_tol, 1.8e-3)
+    empty = ns.compare_waveforms(ref, ns.WaveformData("c", "", ["b"], t.tolist(), {"b": t.tolist()}))
+    assert empty.sample_count == 0 and not empty.within_tolerance(max_abs_tol=1, rms_tol=1, final_abs_tol=1)
+    assert ns.find_nangila_binary() is not None
+
+
+def test_solver_binary_json_and_nz_outputs(tmp_path):
+    exe = ns.find_nangila_binary()
+    deck = _write(tmp_path, "rc.sp", "* rc\nV1 vdd 0 DC 1.8\nR1 vdd out 1k\nC1 out 0 10f\n.ic V(out)=0\n.end\n")
+    wj, wz = tmp_path / "w.json", tmp_path / "w.nz"
+    proc = subprocess.run([exe, "--partition", deck, "--tstop", "1e-10", "--dt", "1e-12", "--waveform-json", str(wj), "--waveform-nz", str(wz),
+                           "--nz-tol", "1e-6"], capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stderr
+    d = json.loads(wj.read_text())
+    assert d["node_names"] == ["vdd", "out"] and len(d["waveform"]) == 101 and d["stats"]["total_steps"] == 100
+    nz = ns.read_nz(str(wz))
+    assert nz.header.version == 2 and nz.node_names == ["vdd", "out"] and nz.header.num_points == 101
+    direct = np.array([p["voltages"]["out"] for p in d["waveform"]])
+    assert np.abs(nz.signals["out"] - direct).max() <= 1e-6 * (1 + 1e-9)
+    from nangila_spice.nz_viewer import compare_waveforms, plot_nz
+
+    assert compare_waveforms(nz, {"out": direct})["within_bound"]
+    assert "out" in plot_nz(str(wz), ["out"], output=str(tmp_path / "p.png")) or os.path.exists(tmp_path / "p.png")
+    assert subprocess.run([exe, "--partition", "/nonexistent.sp"], capture_output=True).returncode == 1
+    assert subprocess.run([exe, "--bogus"], capture_output=True).returncode == 2
+    demo = subprocess.run([exe, "--demo", "--tstop", "5e-11"], capture_output=True, text=True)
+    assert demo.returncode == 0 and "V(cap)" in demo.stderr
+    # every partition of a design in one solver process
+    flat = json.loads(N.generate_circuit("rc_ladder", 12))
+    files = []
+    for i, text in enumerate(partition_flat(flat, 2, "bisect").partition_files()):
+        files.append(_write(tmp_path, f"p{i}.json", text))
+    out = tmp_path / "merged.json"
+    proc = subprocess.run([exe, "--partitions", ",".join(files), "--tstop", "2e-11", "--dt", "1e-12", "--waveform-json", str(out)], capture_output=True, text=True)
+    assert proc.returncode == 0 and "partitioned run: 20 steps" in proc.stderr
+    assert len(json.loads(out.read_text())["waveform"]) == 21
+
+
+def test_pvt_sweep(tmp_path):
+    grid = ns.generate_corner_grid()
+    assert len(grid) == 200 and grid[0].name == "TT_1.62V_-40C"
+    from nangila_spice.pvt_orchestrator import generate_1000_corner_grid
+
+    assert len(generate_1000_corner_grid()) == 1000
+    nominal = ns.CornerSpec.nominal()
+    assert nominal.is_nominal and math.isclose(nominal.thermal_voltage, 8.617e-5 * 300.15)
+    far = ns.CornerSpec(ns.ProcessCorner.SS, 1.2, 125.0)
+    assert not far.is_linearisable(nominal) and ns.CornerSpec(ns.ProcessCorner.FF, 1.89, 40.0).is_linearisable(nominal)
+    corners = [ns.CornerSpec(ns.ProcessCorner.FF, 1.89, 40.0), ns.CornerSpec(ns.ProcessCorner.TT, 1.71, 27.0), far]
+    res = ns.PvtOrchestrator(ns.SweepConfig(max_workers=2, tstop=50e-12)).run_sweep(corners)
+    assert res.total_corners == 4 and res.completed == 4 and res.failed == 0
+    assert res.delta_mode_used == 2 and res.full_sim_used == 2 and res.peak_delta_v > 0.05
+    assert "4/4 corners" in res.summary() and res.success_rate == 1.0
+    res.to_json(str(tmp_path / "sweep.json"))
+    assert json.loads((tmp_path / "sweep.json").read_text())["completed"] == 4
+    # the delta model against a real simulation of the same corner: supply scaling is exact for a passive stage
+    golden = ns.simulate_corner(nominal, None, False, None, 50e-12, 1e-12)
+    c = ns.CornerSpec(ns.ProcessCorner.TT, 1.71, 27.0)
+    approx = ns.simulate_corner(c, golden, True, None, 50e-12, 1e-12)
+    exact = ns.simulate_corner(c, golden, False, None, 50e-12, 1e-12)
+    assert approx["used_delta"] and not exact["used_delta"]
+    assert np.abs(np.array(approx["values"]) - np.array(exact["values"])).max() < 1e-9
+
+
+def test_gate_level_synthesis_computes_c17(tmp_path):
+    from nangila_spice.synth import C17_BENCH, bench_to_spice
+
+    def nand(a, b):
+        return 1 - (a & b)
+
+    for bits in ((0, 0, 0, 0, 0), (1, 1, 1, 1, 1), (1, 0, 1, 1, 0), (0, 1, 0, 1, 1)):
+        i1, i2, i3, i6, i7 = bits
+        stim = [f"VIN{k} n{name} 0 DC {1.8 * b}" for k, (name, b) in enumerate(zip(("1", "2", "3", "6", "7"), bits))]
+        deck = bench_to_spice(C17_BENCH, "c17", stimulus=stim)
+        js, warnings = N.parse_spice(deck, "c17")
+        ok, v = N.dc_operating_point(js)
+        names = json.loads(js)["node_names"]
+        g10, g11 = nand(i1, i3), nand(i3, i6)
+        g16, g19 = nand(i2, g11), nand(g11, i7)
+        want = {"n22": nand(g10, g16), "n23": nand(g16, g19)}
+        assert ok and warnings == []
+        for net, bit in want.items():
+            assert abs(v[names.index(net)] - 1.8 * bit) < 0.05, (bits, net)
+    xor = bench_to_spice("INPUT(a)\nINPUT(b)\nOUTPUT(y)\nOUTPUT(z)\ny = XOR(a, b)\nz = NOR(a, b)\n",
+                         stimulus=["VA na 0 DC 1.8", "VB nb 0 DC 0"])
+    js, _ = N.parse_spice(xor)
+    ok, v = N.dc_operating_point(js)
+    names = json.loads(js)["node_names"]
+    assert ok and v[names.index("ny")] > 1.75 and v[names.index("nz")] < 0.05
+
+
+def test_scaling_study_report_and_cli(tmp_path):
+    suite = run_scaling_study(generate_rc_ladder_netlist(30, 1e3, 10e-15), "ladder30", [1, 2], tstop=100e-12, dt=1e-12, method="bisect")
+    assert [r.partition_count for r in suite.results] == [1, 2] and suite.results[1].max_abs_error_vs_single < 1e-5
+    from nangila_spice.benchmark import generate_performance_report
+
+    md = generate_performance_report(suite, str(tmp_path / "perf"))
+    assert os.path.exists(md) and "ladder30_k2" in open(md).read() and "Average speedup" in suite.summary()
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    deck = _write(tmp_path, "rc.sp", generate_rc_ladder_netlist(8, 1e3, 10e-15))
+    run = subprocess.run([sys.executable, "-m", "nangila_spice.cli", "run", deck, "--partitions", "2", "--tstop", "5e-11", "--method", "bisect",
+                          "--output-dir", str(tmp_path / "o"), "--output-format", "json"], capture_output=True, text=True, env=env)
+    assert run.returncode == 0 and "partitioned_validated" in run.stdout, run.stdout + run.stderr
+    assert os.path.exists(tmp_path / "o" / "rc.json")
+    synth = subprocess.run([sys.executable, "-m", "nangila_spice.cli", "synth"], capture_output=True, text=True, env=env)
+    assert synth.returncode == 0 and synth.stdout.count("\nM") == 24  # six two-input NANDs
+    rep = subprocess.run([sys.executable, "-m", "nangila_spice.cli", "phase1-report", "--output-json", str(tmp_path / "r.json"), "--output-md",
+                          str(tmp_path / "r.md")], capture_output=True, text=True, env=env)
+    assert rep.returncode == 0, rep.stdout + rep.stderr
+    report = json.loads((tmp_path / "r.json").read_text())
+    assert report["all_passed"] and len(report["cases"]) == 6
+    from nangila_spice.visualizer import visualize_partitions
+
+    nl = ns.parse_netlist(deck)
+    dot = visualize_partitions(nl, ns.partition_netlist(nl, 2, "bisect"))
+    assert dot.startswith("graph partitions {") and "style=dashed" in dot
+    hw = ns.discover_hardware()
+    assert hw.cpu_count >= 1 and "cores" in hw.summary()
