@@ -63,6 +63,13 @@ def main() -> int:
         ours = timed(lambda: m.matvec_device(x, y, stream), args.iters)
         clocks = sampler.stop()
         m.check_status()
+        os.environ["NANGILA_SPMV_TILE"] = "1024"
+        ms_ = DeviceCsr(row_ptr, col, val)
+        os.environ.pop("NANGILA_SPMV_TILE")
+        y3 = torch.empty_like(x)
+        small = timed(lambda: ms_.matvec_device(x, y3, stream), args.iters)
+        assert torch.equal(y, y3)
+        ms_.close()
         mp = DeviceCsr(row_ptr, col, val, plain_loads=True)
         y2 = torch.empty_like(x)
         plain = timed(lambda: mp.matvec_device(x, y2, stream), args.iters)
@@ -75,7 +82,7 @@ def main() -> int:
         lib = timed(lambda: torch.mv(A, x), args.iters)
         # algorithmic traffic: values + column indices + row pointers + x read once + y written once
         bytes_moved = nnz * 12 + (n + 1) * 4 + n * 16
-        rec = {"kernel": "spmv_row_blocks_bulk_kernel", "rows": n, "nnz": nnz, "ms": ours, "plain_load_variant_ms": plain, "gbs": bytes_moved / ours / 1e6,
+        rec = {"kernel": "spmv_row_blocks_bulk_kernel", "rows": n, "nnz": nnz, "ms": ours, "plain_load_variant_ms": plain, "tile_1024_variant_ms": small, "gbs": bytes_moved / ours / 1e6,
                f"frac_of_{src}_hbm": bytes_moved / ours / 1e6 / hbm, "cusparse_ms": lib, "speedup_vs_cusparse": lib / ours,
                "max_abs_diff_vs_cusparse": err, "working_set_mb": bytes_moved / 1e6, "fits_l2": bytes_moved < 126e6, "clocks": clocks}
         print(json.dumps(rec), flush=True)

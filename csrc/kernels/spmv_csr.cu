@@ -16,7 +16,11 @@
 // to a multiple of four entries, so a CTA fetches its slice of `val` and `col` with two
 // cp.async.bulk copies completing on an mbarrier: the copy engine keeps 24 KB per CTA in flight
 // without spending registers or issue slots, where the plain-load variant was bound by load latency
-// (long-scoreboard stalls at 41 % of DRAM throughput). Arrays owned by the caller
+// (long-scoreboard stalls at 41 % of DRAM throughput). A further variant that also staged the
+// block's window of x in shared memory was measured and dropped: 41 KB and 48 registers per CTA cut
+// residency from 8 to 5 CTAs per SM and the 16 M-row product went from 0.199 ms to 0.254 ms; with
+// one copy per CTA the overlap comes from resident CTAs, so residency matters more than the
+// gathers. Arrays owned by the caller
 // (nangila_spmv_launch) carry no padding guarantee and use the plain-load variant.
 #include <cuda_runtime.h>
 #include <math.h>
@@ -93,19 +97,20 @@ __global__ void __launch_bounds__(kThreads) spmv_row_blocks_kernel(const int* __
 // Bulk-copy variant: `val` and `col` must be readable up to the next multiple of four entries past
 // the end of every block (the context pads its arrays). status[0] is set to 1 when a copy did not
 // land within the time limit; the CTA then leaves its rows unwritten.
-__global__ void __launch_bounds__(kThreads) spmv_row_blocks_bulk_kernel(const int* __restrict__ row_ptr, const int* __restrict__ col,
+template <int T, int CAP>
+__global__ void __launch_bounds__(T) spmv_row_blocks_bulk_kernel(const int* __restrict__ row_ptr, const int* __restrict__ col,
                                                                          const double* __restrict__ val, const double* __restrict__ x,
                                                                          double* __restrict__ y, const int* __restrict__ row_blocks,
                                                                          int* __restrict__ status, unsigned long long timeout_ns) {
-    __shared__ __align__(16) double s_val[kCap + 8];
-    __shared__ __align__(16) int s_col[kCap + 8];
+    __shared__ __align__(16) double s_val[CAP + 8];
+    __shared__ __align__(16) int s_col[CAP + 8];
     __shared__ __align__(8) uint64_t bar;
-    __shared__ double warp_sums[kThreads / 32];
+    __shared__ double warp_sums[T / 32];
     const int tid = threadIdx.x;
     const int r0 = row_blocks[blockIdx.x], r1 = row_blocks[blockIdx.x + 1];
     const int k0 = row_ptr[r0], k1 = row_ptr[r1];
     const int nnz = k1 - k0, nrows = r1 - r0;
-    if (nnz <= kCap) {
+    if (nnz <= CAP) {
         const int ka = k0 & ~3, kb = (k1 + 3) & ~3;  // 16-byte aligned in both arrays
         const int cnt = kb - ka, off = k0 - ka;
         if (tid == 0) {
@@ -125,22 +130,22 @@ __global__ void __launch_bounds__(kThreads) spmv_row_blocks_bulk_kernel(const in
             return;
         }
         int k = tid;
-        for (; k + 3 * kThreads < nnz; k += 4 * kThreads) {
+        for (; k + 3 * T < nnz; k += 4 * T) {
             const int j = off + k;
-            double x0 = __ldg(x + s_col[j]), x1 = __ldg(x + s_col[j + kThreads]), x2 = __ldg(x + s_col[j + 2 * kThreads]),
-                   x3 = __ldg(x + s_col[j + 3 * kThreads]);
+            double x0 = __ldg(x + s_col[j]), x1 = __ldg(x + s_col[j + T]), x2 = __ldg(x + s_col[j + 2 * T]),
+                   x3 = __ldg(x + s_col[j + 3 * T]);
             s_val[j] *= x0;
-            s_val[j + kThreads] *= x1;
-            s_val[j + 2 * kThreads] *= x2;
-            s_val[j + 3 * kThreads] *= x3;
+            s_val[j + T] *= x1;
+            s_val[j + 2 * T] *= x2;
+            s_val[j + 3 * T] *= x3;
         }
-        for (; k < nnz; k += kThreads) s_val[off + k] *= __ldg(x + s_col[off + k]);
+        for (; k < nnz; k += T) s_val[off + k] *= __ldg(x + s_col[off + k]);
         __syncthreads();
         const double* prod = s_val + off;
         int mean = nrows > 0 ? nnz / nrows : 1;
         int lanes = 1;
         while (lanes < 32 && lanes * 2 <= mean) lanes *= 2;
-        const int group = tid / lanes, lane = tid % lanes, groups = kThreads / lanes;
+        const int group = tid / lanes, lane = tid % lanes, groups = T / lanes;
         const int iters = (nrows + groups - 1) / groups;
         for (int it = 0; it < iters; ++it) {
             const int r = r0 + it * groups + group;
@@ -154,13 +159,13 @@ __global__ void __launch_bounds__(kThreads) spmv_row_blocks_bulk_kernel(const in
         }
     } else {
         double acc = 0.0;
-        for (int k = tid; k < nnz; k += kThreads) acc += __ldg(val + k0 + k) * __ldg(x + __ldg(col + k0 + k));
+        for (int k = tid; k < nnz; k += T) acc += __ldg(val + k0 + k) * __ldg(x + __ldg(col + k0 + k));
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
         if ((tid & 31) == 0) warp_sums[tid >> 5] = acc;
         __syncthreads();
         if (tid == 0) {
             double t = 0.0;
-            for (int w = 0; w < kThreads / 32; ++w) t += warp_sums[w];
+            for (int w = 0; w < T / 32; ++w) t += warp_sums[w];
             y[r0] = t;
         }
     }
@@ -230,6 +235,7 @@ struct NangilaSpmv {
     double *d_val = nullptr, *d_x = nullptr, *d_y = nullptr;
     int* d_status = nullptr;  // set by a kernel whose bulk copy timed out
     bool plain_loads = false;  // NANGILA_SPMV_PLAIN=1: use the plain-load kernel
+    int cap = kCap;            // non-zeros per row block: 2048 (256 threads) or 1024 (128 threads, NANGILA_SPMV_TILE=1024)
     double* d_work = nullptr;   // 9 solver vectors + inverse diagonal, allocated on first solve
     double* d_partial = nullptr;  // reduction scratch: 2 * kRedBlocks + 2
     std::vector<double> h_inv_diag;
@@ -243,7 +249,13 @@ static void free_arrays(NangilaSpmv* c) {
     c->d_val = c->d_x = c->d_y = c->d_work = c->d_partial = nullptr;
 }
 
+static int build_row_blocks(const int* row_ptr, int n, int cap, int* out, int max_out);
+
 extern "C" int nangila_spmv_build_row_blocks(const int* row_ptr, int n, int* out, int max_out) {
+    return build_row_blocks(row_ptr, n, kCap, out, max_out);
+}
+
+static int build_row_blocks(const int* row_ptr, int n, int cap, int* out, int max_out) {
     // out[0] = 0, out[b + 1] = first row after block b; returns the number of blocks (or the number
     // needed when out is null / too small)
     int count = 0, r = 0;
@@ -252,8 +264,8 @@ extern "C" int nangila_spmv_build_row_blocks(const int* row_ptr, int n, int* out
     while (r < n) {
         int start = r;
         int base = row_ptr[r];
-        if (row_ptr[r + 1] - base > kCap) { ++r; emit(r); continue; }
-        while (r < n && row_ptr[r + 1] - base <= kCap) ++r;
+        if (row_ptr[r + 1] - base > cap) { ++r; emit(r); continue; }
+        while (r < n && row_ptr[r + 1] - base <= cap) ++r;
         if (r == start) ++r;
         emit(r);
     }
@@ -275,9 +287,13 @@ extern "C" int nangila_spmv_load(NangilaSpmv* c, int n, int nnz, const int* row_
     for (int k = 0; k < nnz; ++k) if (col[k] < 0 || col[k] >= n) return int(cudaErrorInvalidValue);
     free_arrays(c);
     c->n = n; c->nnz = nnz;
-    int nb = nangila_spmv_build_row_blocks(row_ptr, n, nullptr, 0);
+    {
+        const char* tile = getenv("NANGILA_SPMV_TILE");
+        c->cap = (tile && atoi(tile) == 1024) ? 1024 : kCap;
+    }
+    int nb = build_row_blocks(row_ptr, n, c->cap, nullptr, 0);
     std::vector<int> blocks(size_t(nb) + 1);
-    nangila_spmv_build_row_blocks(row_ptr, n, blocks.data(), nb + 1);
+    build_row_blocks(row_ptr, n, c->cap, blocks.data(), nb + 1);
     c->n_blocks = nb;
     c->h_inv_diag.assign(size_t(n), 1.0);
     for (int r = 0; r < n; ++r)
@@ -324,8 +340,12 @@ extern "C" int nangila_spmv_device(NangilaSpmv* c, const double* d_x, double* d_
     if (!c || !c->d_val || !d_x || !d_y) return int(cudaErrorInvalidValue);
     if (c->plain_loads) return nangila_spmv_launch(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y, c->d_blocks, c->n_blocks, stream);
     if (c->n_blocks <= 0) return 0;
-    spmv_row_blocks_bulk_kernel<<<c->n_blocks, kThreads, 0, stream>>>(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y, c->d_blocks, c->d_status,
-                                                                      2000000000ull);
+    if (c->cap == 1024)
+        spmv_row_blocks_bulk_kernel<128, 1024><<<c->n_blocks, 128, 0, stream>>>(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y, c->d_blocks,
+                                                                               c->d_status, 2000000000ull);
+    else
+        spmv_row_blocks_bulk_kernel<kThreads, kCap><<<c->n_blocks, kThreads, 0, stream>>>(c->d_row_ptr, c->d_col, c->d_val, d_x, d_y,
+                                                                                         c->d_blocks, c->d_status, 2000000000ull);
     return int(cudaGetLastError());
 }
 
@@ -363,15 +383,16 @@ extern "C" int nangila_spmv_bicgstab(NangilaSpmv* c, const double* h_b, double* 
     if (!c || !c->d_val || !h_b || !h_x) return int(cudaErrorInvalidValue);
     const int n = c->n;
     const size_t N = size_t(n);
+    const size_t S = (N + 1) & ~size_t(1);  // vector stride: keeps every work vector 16-byte aligned
     cudaError_t e;
     if (!c->d_work) {
-        e = cudaMalloc(&c->d_work, sizeof(double) * N * 11);
+        e = cudaMalloc(&c->d_work, sizeof(double) * S * 11);
         if (e != cudaSuccess) return int(e);
         e = cudaMalloc(&c->d_partial, sizeof(double) * (2 * kRedBlocks + 2));
         if (e != cudaSuccess) return int(e);
     }
-    double *x = c->d_work, *r = x + N, *r0 = r + N, *p = r0 + N, *v = p + N, *s = v + N, *t = s + N, *ph = t + N, *sh = ph + N, *b = sh + N,
-           *inv = b + N;
+    double *x = c->d_work, *r = x + S, *r0 = r + S, *p = r0 + S, *v = p + S, *s = v + S, *t = s + S, *ph = t + S, *sh = ph + S, *b = sh + S,
+           *inv = b + S;
     double* out = c->d_partial + 2 * kRedBlocks;
     const int grid = (n + kThreads - 1) / kThreads;
     auto dots = [&](const double* a1, const double* b1, const double* a2, const double* b2, double res[2]) -> cudaError_t {
@@ -381,7 +402,7 @@ extern "C" int nangila_spmv_bicgstab(NangilaSpmv* c, const double* h_b, double* 
     };
     if ((e = cudaMemcpy(b, h_b, sizeof(double) * N, cudaMemcpyHostToDevice)) != cudaSuccess) return int(e);
     if ((e = cudaMemcpy(inv, c->h_inv_diag.data(), sizeof(double) * N, cudaMemcpyHostToDevice)) != cudaSuccess) return int(e);
-    if ((e = cudaMemset(x, 0, sizeof(double) * N * 9)) != cudaSuccess) return int(e);
+    if ((e = cudaMemset(x, 0, sizeof(double) * S * 9)) != cudaSuccess) return int(e);
     residual_init_kernel<<<grid, kThreads>>>(r, r0, b, v, n);  // x = 0, so A x = v = 0
     double d[2];
     if ((e = dots(b, b, r, r, d)) != cudaSuccess) return int(e);

@@ -65,14 +65,28 @@ def test_spmv_matches_host(case, plain):
     m.close()
 
 
-def test_tridiagonal_like_reference_benchmark():
+@pytest.mark.parametrize("n", [200_000, 200_001, 7, 2])
+def test_tridiagonal_like_reference_benchmark(n):
+    """Banded pattern at even, odd and tiny sizes."""
     from nangila_spice.gpu import DeviceCsr, tridiagonal
 
-    n = 200_000
     row_ptr, col, val = tridiagonal(n)
     m = DeviceCsr(row_ptr, col, val)
     y = m.matvec(np.ones(n))
     assert y[0] == 1.0 and y[-1] == 1.0 and np.all(y[1:-1] == 0.0)
+    x = np.random.default_rng(n).standard_normal(n)
+    ref = 2.0 * x
+    ref[1:] -= x[:-1]
+    ref[:-1] -= x[1:]
+    assert np.abs(m.matvec(x) - ref).max() < 1e-14
+    # an x vector that is only 8-byte aligned
+    buf = torch.zeros(n + 1, dtype=torch.float64, device="cuda")
+    buf[1:] = torch.from_numpy(x).cuda()
+    yd = torch.empty(n, dtype=torch.float64, device="cuda")
+    m.matvec_device(buf[1:], yd, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    m.check_status()
+    assert np.abs(yd.cpu().numpy() - ref).max() < 1e-14
 
 
 def test_device_bicgstab_solves_rc_ladder_system():
