@@ -28,3 +28,9 @@ def test_ddp_example_on_cpu(tmp_path):
     r = _run("examples/train_ddp_gpt2.py", "--tiny", "--steps", "14", "--warmup-steps", "2", "--micro-batch", "2",
              "--checkpoint", ck)
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_spice_partitioned_example():
+    r = _run("examples/spice_partitioned.py", "--stages", "40", "--partitions", "3", "--tstop", "1e-10")
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "partitioned_validated" in r.stdout and ".nz v2" in r.stdout

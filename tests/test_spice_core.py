@@ -300,3 +300,18 @@ def test_generators_and_benchmark_suite():
     assert ok and math.isclose(v[0], 1.8) and min(v[:36]) == v[35] < 1.8  # the sink corner is the lowest node
     rows = N.run_benchmark_suite()
     assert len(rows) == 4 and all(r["completed"] and r["steps"] == 100 for r in rows)
+
+
+def test_spmv_row_block_table():
+    """Host part of the device SpMV: rows are packed into blocks of at most 2048 non-zeros; a longer
+    row stands alone."""
+    from nangila_spice.gpu import build_row_blocks, tridiagonal
+
+    rp, col, val = tridiagonal(5000)
+    b = build_row_blocks(rp)
+    assert b[0] == 0 and b[-1] == 5000 and np.all(np.diff(b) > 0)
+    assert np.diff(rp[b]).max() <= 2048 and np.diff(rp[b])[:-1].min() > 2048 - 4
+    rp = np.array([0, 3, 5000, 5001, 5001, 9000], dtype=np.int32)
+    assert build_row_blocks(rp).tolist() == [0, 1, 2, 4, 5]
+    assert build_row_blocks(np.array([0, 0, 0], dtype=np.int32)).tolist() == [0, 2]
+    assert col.size == val.size == rp.size * 0 + 3 * 5000 - 2
