@@ -23,7 +23,7 @@ using namespace nspice;
 
 struct Args {
     std::string partition, partitions, process = "TT", waveform_json, waveform_nz, solver = "lu";
-    uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1;
+    uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1, threads = 1;
     double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
     bool demo = false, bench = false;
 };
@@ -33,7 +33,7 @@ static void usage() {
                  "usage: nangila-node [--partition FILE | --demo] [--node-id N] [-k TOTAL] [--predict-depth D]\n"
                  "                    [--reltol R] [--tstop T] [--dt DT] [--process P] [--vdd V] [--temp C]\n"
                  "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov]\n"
-                 "                    [--record-every K]\n");
+                 "                    [--record-every K] [--partitions A.json,B.json,... [--threads T]] [--bench]\n");
 }
 
 static bool parse_args(int argc, char** argv, Args& a) {
@@ -52,6 +52,7 @@ static bool parse_args(int argc, char** argv, Args& a) {
         else if (f == "--node-id" || f == "-n") { if (!(v = need("--node-id"))) return false; a.node_id = uint32_t(std::atoi(v)); }
         else if (f == "-k" || f == "--total-partitions") { if (!(v = need("-k"))) return false; a.total = uint32_t(std::atoi(v)); }
         else if (f == "--predict-depth") { if (!(v = need("--predict-depth"))) return false; a.predict_depth = uint32_t(std::atoi(v)); }
+        else if (f == "--threads") { if (!(v = need("--threads"))) return false; a.threads = uint32_t(std::max(1, std::atoi(v))); }
         else if (f == "--record-every") { if (!(v = need("--record-every"))) return false; a.record_every = std::max(1, std::atoi(v)); }
         else if (f == "--reltol") { if (!(v = need("--reltol"))) return false; a.reltol = std::atof(v); }
         else if (f == "--tstop") { if (!(v = need("--tstop"))) return false; a.tstop = std::atof(v); }
@@ -130,6 +131,7 @@ static int run_partitioned(const Args& a) {
         }
         PartitionedConfig cfg;
         cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
+        cfg.threads = a.threads;
         PartitionedRunner runner(std::move(parts), cfg);
         runner.run();
         const PartitionedStats& st = runner.stats;

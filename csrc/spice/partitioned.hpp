@@ -13,16 +13,72 @@
 // partition B appears in both, with the foreign net listed in ghost_map. Net identity across
 // partitions is the node *name* (ghost net id = net_name_hash(name)).
 #pragma once
+#include <atomic>
 #include <map>
 #include <memory>
 #include <set>
+#include <thread>
 
 #include "parser.hpp"
 #include "transient.hpp"
 
 namespace nspice {
 
+// Persistent worker threads for the per-partition solves of one sweep. Workers spin briefly on a
+// generation counter and then yield, because a sweep is often only microseconds of work.
+class SweepPool {
+public:
+    explicit SweepPool(unsigned threads) {
+        for (unsigned i = 1; i < threads; ++i) workers_.emplace_back([this, i] { loop(i); });
+        nthreads_ = threads ? threads : 1;
+    }
+    ~SweepPool() {
+        stop_.store(true);
+        gen_.fetch_add(1);
+        for (auto& t : workers_) t.join();
+    }
+    // Calls fn(i) for i in [0, count); the caller's thread takes part.
+    void run(unsigned count, const std::function<void(unsigned)>& fn) {
+        if (nthreads_ <= 1 || count <= 1) { for (unsigned i = 0; i < count; ++i) fn(i); return; }
+        fn_ = &fn;
+        count_ = count;
+        next_.store(0);
+        pending_.store(int(workers_.size()));
+        gen_.fetch_add(1);
+        work();
+        int spins = 0;
+        while (pending_.load(std::memory_order_acquire) != 0) { if (++spins > 200) std::this_thread::yield(); }
+    }
+    unsigned threads() const { return nthreads_; }
+private:
+    std::vector<std::thread> workers_;
+    unsigned nthreads_ = 1, count_ = 0;
+    const std::function<void(unsigned)>* fn_ = nullptr;
+    std::atomic<unsigned> next_{0};
+    std::atomic<int> pending_{0};
+    std::atomic<uint64_t> gen_{0};
+    std::atomic<bool> stop_{false};
+    void work() {
+        for (unsigned i = next_.fetch_add(1); i < count_; i = next_.fetch_add(1)) (*fn_)(i);
+    }
+    void loop(unsigned) {
+        uint64_t seen = 0;
+        while (true) {
+            int spins = 0;
+            while (gen_.load(std::memory_order_acquire) == seen) {
+                if (++spins > 2000) { std::this_thread::sleep_for(std::chrono::microseconds(20)); spins = 1000; }
+                else if (spins > 200) std::this_thread::yield();
+            }
+            seen = gen_.load();
+            if (stop_.load()) return;
+            work();
+            pending_.fetch_sub(1, std::memory_order_release);
+        }
+    }
+};
+
 struct PartitionedConfig {
+    unsigned threads = 1;  // worker threads for the per-partition solves (1 = all on the calling thread)
     double tstop = 1e-9, dt = 1e-12, reltol = 1e-3, abstol = 1e-6;
     uint32_t predict_depth = 5;
     int max_sweeps = 50;
@@ -43,7 +99,8 @@ public:
     std::vector<std::string> names;            // merged net names (owned nets of every partition)
     std::vector<WaveformPoint> waveform;       // merged, values in `names` order
 
-    PartitionedRunner(std::vector<Netlist> parts, PartitionedConfig cfg) : cfg_(cfg), depth_(cfg.predict_depth, 1, cfg.predict_depth * 3) {
+    PartitionedRunner(std::vector<Netlist> parts, PartitionedConfig cfg)
+        : cfg_(cfg), depth_(cfg.predict_depth, 1, cfg.predict_depth * 3), pool_(std::min<unsigned>(std::max(1u, cfg.threads), unsigned(parts.size()))) {
         const uint32_t k = uint32_t(parts.size());
         FabricConfig fc;
         fc.compress = cfg.compress;
@@ -84,11 +141,13 @@ public:
         for (; step < planned && !failed; ++step) {
             const double t_next = double(step + 1) * cfg_.dt;
             // speculative solve with predicted ghosts
-            for (uint32_t p = 0; p < k && !failed; ++p) {
+            std::atomic<bool> bad{false};
+            pool_.run(k, [&](unsigned p) {
                 Part& part = parts_[p];
                 part.pins = part.ghosts.predict_all(t_next);
-                if (!part.engine->solve_step(part.state, part.pins, cfg_.dt, part.next)) failed = true;
-            }
+                if (!part.engine->solve_step(part.state, part.pins, cfg_.dt, part.next)) bad.store(true);
+            });
+            failed = bad.load();
             if (failed) break;
             bool all_ok = exchange(t_next, /*count=*/true);
             int sweeps = 0;
@@ -96,12 +155,13 @@ public:
                 // solve again with the received (true, as of the last sweep) ghost values
                 std::vector<std::vector<double>> before;
                 for (auto& part : parts_) before.push_back(part.next.voltages);
-                for (uint32_t p = 0; p < k && !failed; ++p) {
+                pool_.run(k, [&](unsigned p) {
                     Part& part = parts_[p];
                     part.pins = part.latest;
-                    if (!part.engine->solve_step(part.state, part.pins, cfg_.dt, part.next)) failed = true;
-                    ++stats.resolves;
-                }
+                    if (!part.engine->solve_step(part.state, part.pins, cfg_.dt, part.next)) bad.store(true);
+                });
+                stats.resolves += k;
+                failed = bad.load();
                 if (failed) break;
                 exchange(t_next, /*count=*/false);
                 all_ok = true;
@@ -142,6 +202,7 @@ private:
     std::vector<std::unique_ptr<FabricNode>> mesh_;
     std::vector<MergedRef> merged_;
     SpeculativeDepthController depth_;
+    SweepPool pool_;
 
     // Every owner publishes its boundary voltages of `next`; receivers decode, remember them and
     // (when count is set) score their predictions. Returns whether every prediction was a hit.

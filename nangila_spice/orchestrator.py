@@ -64,6 +64,7 @@ class SimulationConfig:
     temp: float = 27.0
     solver: str = "lu"
     record_every: int = 1
+    threads: Optional[int] = None  # worker threads of the in-process partitioned run (default: one per partition, at most the core count)
 
 
 @dataclass
@@ -196,7 +197,9 @@ def run_simulation(config: SimulationConfig) -> SimulationResult:
         else:
             mode = "in_process" if config.mode == "auto" else config.mode
             if mode == "in_process":
-                r = _native.simulate_partitioned(pr.partition_files(), config.tstop, config.dt, config.reltol, config.predict_depth, True, config.record_every)
+                threads = config.threads or max(1, min(k, hw.cpu_count))
+                r = _native.simulate_partitioned(pr.partition_files(), config.tstop, config.dt, config.reltol, config.predict_depth, True,
+                                                 config.record_every, threads)
                 result.waveform = Waveform.from_native(r, title=Path(config.netlist_path).name)
                 result.solver_stats = {"stats": r["stats"]}
                 result.success = bool(r["stats"]["completed"])
