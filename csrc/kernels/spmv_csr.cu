@@ -239,7 +239,23 @@ struct NangilaSpmv {
     double* d_work = nullptr;   // 9 solver vectors + inverse diagonal, allocated on first solve
     double* d_partial = nullptr;  // reduction scratch: 2 * kRedBlocks + 2
     std::vector<double> h_inv_diag;
+    std::vector<int> h_row_ptr, h_diag_slot;  // kept on the host to refresh the preconditioner when values change
 };
+
+// Jacobi preconditioner: 1 / diagonal where the diagonal carries weight in its row (at least 1e-3 of
+// the row's largest entry), else 1 / that largest entry (branch-current rows of an MNA matrix have a
+// zero or tiny diagonal).
+static void refresh_preconditioner(NangilaSpmv* c, const double* val) {
+    const int n = c->n;
+    c->h_inv_diag.assign(size_t(n), 1.0);
+    for (int r = 0; r < n; ++r) {
+        double mx = 0.0;
+        for (int k = c->h_row_ptr[size_t(r)]; k < c->h_row_ptr[size_t(r) + 1]; ++k) mx = fmax(mx, fabs(val[k]));
+        const int d = c->h_diag_slot[size_t(r)];
+        if (d >= 0 && fabs(val[d]) >= 1e-3 * mx && fabs(val[d]) > 1e-300) c->h_inv_diag[size_t(r)] = 1.0 / val[d];
+        else if (mx > 1e-300) c->h_inv_diag[size_t(r)] = 1.0 / mx;
+    }
+}
 
 static void free_arrays(NangilaSpmv* c) {
     cudaFree(c->d_row_ptr); cudaFree(c->d_col); cudaFree(c->d_blocks); cudaFree(c->d_val); cudaFree(c->d_x); cudaFree(c->d_y);
@@ -295,10 +311,12 @@ extern "C" int nangila_spmv_load(NangilaSpmv* c, int n, int nnz, const int* row_
     std::vector<int> blocks(size_t(nb) + 1);
     build_row_blocks(row_ptr, n, c->cap, blocks.data(), nb + 1);
     c->n_blocks = nb;
-    c->h_inv_diag.assign(size_t(n), 1.0);
+    c->h_row_ptr.assign(row_ptr, row_ptr + n + 1);
+    c->h_diag_slot.assign(size_t(n), -1);
     for (int r = 0; r < n; ++r)
         for (int k = row_ptr[r]; k < row_ptr[r + 1]; ++k)
-            if (col[k] == r && fabs(val[k]) > 1e-300) c->h_inv_diag[size_t(r)] = 1.0 / val[k];
+            if (col[k] == r) c->h_diag_slot[size_t(r)] = k;
+    refresh_preconditioner(c, val);
     cudaError_t e;
 #define NG_TRY(call) do { e = (call); if (e != cudaSuccess) { free_arrays(c); return int(e); } } while (0)
     NG_TRY(cudaMalloc(&c->d_row_ptr, sizeof(int) * (size_t(n) + 1)));
@@ -326,6 +344,7 @@ extern "C" int nangila_spmv_load(NangilaSpmv* c, int n, int nnz, const int* row_
 
 extern "C" int nangila_spmv_update_values(NangilaSpmv* c, const double* val) {
     if (!c || !c->d_val || !val) return int(cudaErrorInvalidValue);
+    refresh_preconditioner(c, val);
     return int(cudaMemcpy(c->d_val, val, sizeof(double) * size_t(c->nnz), cudaMemcpyHostToDevice));
 }
 

@@ -17,8 +17,9 @@ using namespace nspice;
 static LinearBackend backend_of(const std::string& s) {
     if (s == "dense") return LinearBackend::Dense;
     if (s == "krylov") return LinearBackend::Krylov;
+    if (s == "cuda") return LinearBackend::Cuda;
     if (s == "lu" || s.empty()) return LinearBackend::SparseLU;
-    throw std::invalid_argument("solver must be 'lu', 'dense' or 'krylov'");
+    throw std::invalid_argument("solver must be 'lu', 'dense', 'krylov' or 'cuda'");
 }
 
 static py::dict stats_dict(const SimStats& s) {
@@ -43,6 +44,7 @@ PYBIND11_MODULE(_native, m) {
 
     m.def("parse_scaled", [](const std::string& s) -> py::object { double v; if (!parse_scaled(s, v)) return py::none(); return py::float_(v); });
     m.def("net_name_hash", &net_name_hash);
+    m.def("set_cuda_library", &CudaKrylov::set_library, "path of libnangila_kernels.so for solver='cuda'");
     m.def("parse_spice", [](const std::string& text, const std::string& name, const std::string& process, double vdd, double temp) {
         Corner c; c.process = process; c.vdd = vdd; c.temp_c = temp;
         SpiceParser p(c);
@@ -81,6 +83,8 @@ PYBIND11_MODULE(_native, m) {
         py::dict nr;
         nr["total_iterations"] = s.engine().newton.stats.total_iterations; nr["linear_solves"] = s.engine().newton.stats.linear_solves;
         nr["failed"] = s.engine().newton.stats.failed_count; nr["be_fallbacks"] = s.engine().be_fallbacks;
+        nr["device_solves"] = s.engine().newton.linear.stats.device_solves; nr["krylov_iterations"] = s.engine().newton.linear.stats.krylov_iterations;
+        nr["krylov_fallbacks"] = s.engine().newton.linear.stats.krylov_fallbacks; nr["cuda_error"] = s.engine().newton.linear.cuda_error;
         out["newton"] = nr;
         return out;
     }, py::arg("netlist_json"), py::arg("tstop"), py::arg("dt"), py::arg("reltol") = 1e-3, py::arg("solver") = "lu", py::arg("record_every") = 1,

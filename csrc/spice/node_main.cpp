@@ -2,7 +2,7 @@
 //
 //   nangila-node --partition deck.sp|part.json [--node-id N] [-k TOTAL] [--predict-depth D]
 //                [--reltol R] [--tstop T] [--dt DT] [--process TT|FF|SS|FS|SF] [--vdd V] [--temp C]
-//                [--waveform-json out.json] [--waveform-nz out.nz] [--solver lu|dense|krylov]
+//                [--waveform-json out.json] [--waveform-nz out.nz] [--solver lu|dense|krylov|cuda]
 //                [--record-every K] [--demo]
 //
 // Flag set and the waveform JSON layout ({netlist, node_names, waveform: [{time, voltages{}}],
@@ -32,7 +32,7 @@ static void usage() {
     std::fprintf(stderr,
                  "usage: nangila-node [--partition FILE | --demo] [--node-id N] [-k TOTAL] [--predict-depth D]\n"
                  "                    [--reltol R] [--tstop T] [--dt DT] [--process P] [--vdd V] [--temp C]\n"
-                 "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov]\n"
+                 "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov|cuda]\n"
                  "                    [--record-every K] [--partitions A.json,B.json,... [--threads T]] [--bench]\n");
 }
 
@@ -196,6 +196,7 @@ int main(int argc, char** argv) {
     solver.engine().newton.config.reltol = a.reltol;
     if (a.solver == "dense") solver.engine().newton.linear.backend = LinearBackend::Dense;
     else if (a.solver == "krylov") solver.engine().newton.linear.backend = LinearBackend::Krylov;
+    else if (a.solver == "cuda") solver.engine().newton.linear.backend = LinearBackend::Cuda;  // needs NANGILA_KERNELS_LIB
     PartitionState fin = solver.run();
     const SimStats& st = solver.stats;
     std::fprintf(stderr, "steps %llu%s, wall %.3f s, NR iterations/step %.2f, hit rate %.1f%%, rollbacks %llu\n",

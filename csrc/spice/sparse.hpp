@@ -7,10 +7,14 @@
 // matrices), and the Krylov solver is the host twin of the device solver built on the CSR SpMV
 // kernel (csrc/kernels/spmv_csr.cu).
 #pragma once
+#include <dlfcn.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <map>
+#include <string>
 #include <numeric>
 #include <stdexcept>
 #include <utility>
@@ -276,21 +280,81 @@ KrylovResult bicgstab(int n, Spmv&& spmv, const std::vector<double>& diag, const
     return res;
 }
 
-enum class LinearBackend { SparseLU, Dense, Krylov };
+enum class LinearBackend { SparseLU, Dense, Krylov, Cuda };
 
-struct LinearSolverStats { uint64_t solves = 0, failures = 0, krylov_iterations = 0, krylov_fallbacks = 0; };
+// The device solver (FP64 CSR matrix resident on the GPU + BiCGSTAB, csrc/kernels/spmv_csr.cu) bound
+// at run time with dlopen, so the simulator itself has no link-time CUDA dependency. The library is
+// looked up at $NANGILA_KERNELS_LIB, else at the path given to set_library().
+class CudaKrylov {
+public:
+    static std::string& library_path() { static std::string p; return p; }
+    static void set_library(const std::string& p) { library_path() = p; }
+
+    ~CudaKrylov() {
+        if (ctx_ && destroy_) destroy_(ctx_);
+        // the library stays loaded: unloading a CUDA library at exit is not worth the risk
+    }
+    bool available() {
+        if (tried_) return create_ != nullptr;
+        tried_ = true;
+        const char* env = std::getenv("NANGILA_KERNELS_LIB");
+        std::string path = env && *env ? env : library_path();
+        if (path.empty()) return false;
+        void* h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
+        if (!h) return false;
+        create_ = reinterpret_cast<void* (*)()>(dlsym(h, "nangila_spmv_create"));
+        destroy_ = reinterpret_cast<void (*)(void*)>(dlsym(h, "nangila_spmv_destroy"));
+        load_ = reinterpret_cast<int (*)(void*, int, int, const int*, const int*, const double*)>(dlsym(h, "nangila_spmv_load"));
+        update_ = reinterpret_cast<int (*)(void*, const double*)>(dlsym(h, "nangila_spmv_update_values"));
+        solve_ = reinterpret_cast<int (*)(void*, const double*, double*, double, int, int*, double*)>(dlsym(h, "nangila_spmv_bicgstab"));
+        if (!create_ || !destroy_ || !load_ || !update_ || !solve_) create_ = nullptr;
+        return create_ != nullptr;
+    }
+    // Solves the row-equilibrated system; the pattern is uploaded once and only values afterwards.
+    // Returns 0 = solved, 1 = did not converge, 2 = device error / library missing.
+    int solve(const CsrMatrix& eq, std::vector<double>& x, double tol, int max_iter, int& iterations) {
+        iterations = 0;
+        if (!available()) return 2;
+        if (!ctx_) ctx_ = create_();
+        if (!ctx_) return 2;
+        if (loaded_n_ != eq.n || loaded_nnz_ != eq.nnz() || pattern_ != eq.col || rows_ != eq.row_ptr) {
+            if (load_(ctx_, eq.n, eq.nnz(), eq.row_ptr.data(), eq.col.data(), eq.val.data()) != 0) return 2;
+            loaded_n_ = eq.n; loaded_nnz_ = eq.nnz(); pattern_ = eq.col; rows_ = eq.row_ptr;
+        } else if (update_(ctx_, eq.val.data()) != 0) {
+            return 2;
+        }
+        x.assign(size_t(eq.n), 0.0);
+        double rel = 0.0;
+        int rc = solve_(ctx_, eq.rhs.data(), x.data(), tol, max_iter, &iterations, &rel);
+        return rc == 0 ? 0 : (rc == -1 ? 1 : 2);
+    }
+private:
+    bool tried_ = false;
+    void* ctx_ = nullptr;
+    int loaded_n_ = -1, loaded_nnz_ = -1;
+    std::vector<int> pattern_, rows_;
+    void* (*create_)() = nullptr;
+    void (*destroy_)(void*) = nullptr;
+    int (*load_)(void*, int, int, const int*, const int*, const double*) = nullptr;
+    int (*update_)(void*, const double*) = nullptr;
+    int (*solve_)(void*, const double*, double*, double, int, int*, double*) = nullptr;
+};
+
+struct LinearSolverStats { uint64_t solves = 0, failures = 0, krylov_iterations = 0, krylov_fallbacks = 0, device_solves = 0; };
 
 // Solver facade (the reference's GpuSolver::solve role): fills m.solution from m.rhs.
 class LinearSolver {
 public:
     LinearBackend backend = LinearBackend::SparseLU;
     LinearSolverStats stats;
+    CudaKrylov cuda;
+    bool cuda_error = false;  // the device solver could not be loaded or reported a CUDA error; solves fell back to the sparse LU
     bool solve(CsrMatrix& m) {
         ++stats.solves;
         bool ok = false;
         if (backend == LinearBackend::Dense) {
             ok = dense_solve(m.to_dense(), m.rhs, m.n, m.solution);
-        } else if (backend == LinearBackend::Krylov) {
+        } else if (backend == LinearBackend::Krylov || backend == LinearBackend::Cuda) {
             // rows are equilibrated (divided by their largest entry) so that supply rows (entries of
             // 1) and stiff node rows (C / dt, ghost pins of 1e12) weigh the same in the residual norm
             CsrMatrix eq = m;
@@ -302,13 +366,23 @@ public:
                     eq.rhs[size_t(r)] /= mx;
                 }
             }
-            std::vector<double> diag(size_t(m.n), 1.0);
-            for (int r = 0; r < m.n; ++r) { int s = eq.slot(r, r); if (s >= 0 && std::fabs(eq.val[size_t(s)]) > 1e-3) diag[size_t(r)] = eq.val[size_t(s)]; }
-            m.solution.assign(size_t(m.n), 0.0);
-            KrylovResult kr = bicgstab(m.n, [&](const double* x, double* y) { eq.spmv(x, y); }, diag, eq.rhs, m.solution, 1e-12, 4 * m.n + 50);
-            stats.krylov_iterations += uint64_t(kr.iterations);
+            bool converged = false;
+            if (backend == LinearBackend::Cuda) {
+                int its = 0;
+                int rc = cuda.solve(eq, m.solution, 1e-12, 4 * m.n + 50, its);
+                stats.krylov_iterations += uint64_t(its);
+                if (rc == 2) { cuda_error = true; converged = false; m.solution.assign(size_t(m.n), 0.0); }
+                else { ++stats.device_solves; converged = rc == 0; }
+            } else {
+                std::vector<double> diag(size_t(m.n), 1.0);
+                for (int r = 0; r < m.n; ++r) { int s = eq.slot(r, r); if (s >= 0 && std::fabs(eq.val[size_t(s)]) > 1e-3) diag[size_t(r)] = eq.val[size_t(s)]; }
+                m.solution.assign(size_t(m.n), 0.0);
+                KrylovResult kr = bicgstab(m.n, [&](const double* x, double* y) { eq.spmv(x, y); }, diag, eq.rhs, m.solution, 1e-12, 4 * m.n + 50);
+                stats.krylov_iterations += uint64_t(kr.iterations);
+                converged = kr.converged;
+            }
             // accept only a small componentwise backward error: |A x - b|_i <= 1e-8 (|A||x| + |b|)_i
-            ok = kr.converged;
+            ok = converged;
             for (int r = 0; ok && r < m.n; ++r) {
                 double ax = 0.0, mag = std::fabs(eq.rhs[size_t(r)]);
                 for (int k = eq.row_ptr[size_t(r)]; k < eq.row_ptr[size_t(r) + 1]; ++k) {

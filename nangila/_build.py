@@ -202,7 +202,7 @@ def build_spice(force: bool = False) -> list[Path]:
     exe.parent.mkdir(exist_ok=True)
     src = CSRC / "spice" / "node_main.cpp"
     if force or _stale(exe, [src] + hdrs):
-        _run(["g++", "-O2", "-std=c++17", "-Wall", "-pthread", f"-I{CSRC / 'spice'}", str(src), "-o", str(exe)])
+        _run(["g++", "-O2", "-std=c++17", "-Wall", "-pthread", f"-I{CSRC / 'spice'}", str(src), "-o", str(exe), "-ldl"])
     outs.append(exe)
     return outs
 

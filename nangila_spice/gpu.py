@@ -40,6 +40,19 @@ def kernels_library() -> ctypes.CDLL:
     return _LIB
 
 
+def enable_device_solver() -> str:
+    """Points the simulator core at the kernel library, so ``solver="cuda"`` (the linear systems of the
+    Newton iteration solved by BiCGSTAB on the GPU, matrix resident, values refreshed per iteration)
+    can bind it at run time. Returns the path."""
+    from . import _native
+
+    path = Path(__file__).resolve().parent.parent / "nangila" / "libnangila_kernels.so"
+    if not path.exists():
+        raise RuntimeError(f"{path} is missing: run `python -m nangila._build --kernels`")
+    _native.set_cuda_library(str(path))
+    return str(path)
+
+
 def _check(rc: int, what: str) -> None:
     if rc != 0:
         raise RuntimeError(f"{what} failed with CUDA error {rc}")

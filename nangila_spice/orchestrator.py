@@ -142,6 +142,10 @@ def _log(config: SimulationConfig, msg: str) -> None:
 def _single_run(config: SimulationConfig, flat: dict) -> tuple[Waveform, dict]:
     from . import _native
 
+    if config.solver == "cuda":
+        from .gpu import enable_device_solver
+
+        enable_device_solver()
     r = _native.simulate(json.dumps(flat), config.tstop, config.dt, config.reltol, config.solver, config.record_every, config.predict_depth)
     return Waveform.from_native(r, title=flat.get("name", "")), {"stats": r["stats"], "newton": r["newton"]}
 
