@@ -381,8 +381,11 @@ public:
                 stats.krylov_iterations += uint64_t(kr.iterations);
                 converged = kr.converged;
             }
-            // accept only a small componentwise backward error: |A x - b|_i <= 1e-8 (|A||x| + |b|)_i
+            // accept only a small backward error: |A x - b|_i <= 1e-8 (|A||x| + |b|)_i + 1e-10 max|b| on the
+            // equilibrated system (Newton itself stops at 1e-3 relative, so this is ample)
             ok = converged;
+            double bmax = 0.0;
+            for (double v : eq.rhs) bmax = std::max(bmax, std::fabs(v));
             for (int r = 0; ok && r < m.n; ++r) {
                 double ax = 0.0, mag = std::fabs(eq.rhs[size_t(r)]);
                 for (int k = eq.row_ptr[size_t(r)]; k < eq.row_ptr[size_t(r) + 1]; ++k) {
@@ -390,7 +393,7 @@ public:
                     ax += t;
                     mag += std::fabs(t);
                 }
-                if (!(std::fabs(ax - eq.rhs[size_t(r)]) <= 1e-8 * mag + 1e-300)) ok = false;
+                if (!(std::fabs(ax - eq.rhs[size_t(r)]) <= 1e-8 * mag + 1e-10 * bmax + 1e-300)) ok = false;
             }
             if (!ok) { ++stats.krylov_fallbacks; ok = sparse_lu_solve(m, m.solution); }
         } else {
