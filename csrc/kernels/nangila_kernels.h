@@ -182,6 +182,12 @@ int nangila_predict_quantize_gamma(const float* grad, const float* g_curr, const
 int nangila_dequant_reconstruct_gamma(const uint8_t* packed, const float* g_curr, const float* g_prev, float mu,
                                       float gamma, float* out, int64_t n, cudaStream_t stream);
 
+/* ---- fused softmax cross-entropy over bf16 logits with padded columns (fused_ce.cu) ---------------- */
+int nangila_ce_forward(const void* logits, const int64_t* targets, float* losses, float* lse, int64_t rows, int v, int64_t stride,
+                       cudaStream_t stream);
+int nangila_ce_backward(const void* logits, const int64_t* targets, const float* lse, const float* grad_out, void* grad, int64_t rows,
+                        int v, int64_t stride, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -106,7 +106,9 @@ class BertMLM(nn.Module):
         logits = F.linear(h, self.tok.weight, self.head_bias)
         if labels is None:
             return logits
-        return F.cross_entropy(logits[:, : self.cfg.vocab_size].float(), tgt)
+        from ..ops.fused_ce import fused_cross_entropy  # fused kernels for bf16 logits on a GPU, PyTorch's path otherwise
+
+        return fused_cross_entropy(logits, tgt, self.cfg.vocab_size)
 
     def num_params(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -6,7 +6,8 @@ The reference ships no model; its examples train Hugging Face causal LMs through
 12 layers, d_model 768, 12 heads, MLP 3072, vocabulary 50257, context 1024.
 
 GEMMs go to cuBLAS through ``torch.nn.functional.linear`` and attention to the fused
-``scaled_dot_product_attention`` kernel; the gradient exchange is what this framework replaces.
+``scaled_dot_product_attention`` kernel; the loss over the padded vocabulary is this framework's fused
+cross-entropy kernel pair (``nangila/ops/fused_ce.py``); the gradient exchange is what this framework replaces.
 """
 from __future__ import annotations
 
@@ -90,9 +91,11 @@ class GPT2(nn.Module):
         logits = F.linear(x, self.wte.weight)  # tied head over the padded vocabulary
         if targets is None:
             return logits
-        v = self.cfg.vocab_size
-        # the padded columns are excluded from the softmax, so the model has exactly `vocab_size` classes
-        return F.cross_entropy(logits.view(-1, logits.size(-1))[:, :v].float(), targets.reshape(-1))
+        # the padded columns are excluded from the softmax, so the model has exactly `vocab_size` classes;
+        # bf16 logits on a GPU take the fused kernel pair (no fp32 copy of the logits), the rest PyTorch's path
+        from ..ops.fused_ce import fused_cross_entropy
+
+        return fused_cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1), self.cfg.vocab_size)
 
     def num_params(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -111,7 +111,9 @@ class Llama(nn.Module):
         logits = self.head(self.norm(x))
         if targets is None:
             return logits
-        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))
+        from ..ops.fused_ce import fused_cross_entropy  # fused kernels for bf16 logits on a GPU, PyTorch's path otherwise
+
+        return fused_cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1))
 
     def num_params(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -131,3 +131,26 @@ def test_compat_gamma_kernels_roundtrip():
         ex.cuda_predict_and_quantize(0, 0, 0, 0.9, 0.1, 0, 8, sync_mode=5)
     with pytest.raises(RuntimeError):
         ex.cuda_predict_and_quantize(0, 0, 0, 0.9, 0.1, 0, 8, sync_mode=0)  # null pointers are rejected
+
+
+@pytest.mark.parametrize("rows,cols,classes", [(64, 50304, 50257), (33, 1024, 1000), (7, 8, 8), (5, 136, 129)])
+def test_fused_cross_entropy_matches_fp32_reference(rows, cols, classes):
+    """Loss and gradient of the fused kernel pair against F.cross_entropy on fp32 copies of the same bf16 logits."""
+    import torch.nn.functional as F
+
+    from nangila.ops.fused_ce import fused_cross_entropy
+
+    torch.manual_seed(rows)
+    logits = (torch.randn(rows, cols, device="cuda") * 3.0).to(torch.bfloat16).requires_grad_(True)
+    targets = torch.randint(0, classes, (rows,), device="cuda")
+    loss = fused_cross_entropy(logits, targets, classes)
+    (loss * 2.5).backward()
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = F.cross_entropy(ref_in[:, :classes], targets)
+    (ref * 2.5).backward()
+    assert abs(loss.item() - ref.item()) < 2e-5 * max(1.0, abs(ref.item()))
+    g, gr = logits.grad.float(), ref_in.grad
+    assert torch.all(g[:, classes:] == 0)
+    assert (g - gr).abs().max().item() <= 2 ** -8 * gr.abs().max().item() + 1e-7  # bf16 rounding of the gradient
+    # rows sum to zero up to bf16 rounding
+    assert g.sum(dim=1).abs().max().item() < 0.02 * 2.5 / rows + 1e-6
