@@ -141,7 +141,6 @@ public:
         // pass 2: top-level elements
         {
             int depth = 0;
-            bool title_checked = false;
             for (auto& st : stmts) {
                 auto tok = split(st);
                 if (tok.empty()) continue;
@@ -150,7 +149,6 @@ public:
                 if (first == ".ENDS") { if (depth > 0) --depth; continue; }
                 if (depth > 0) continue;
                 if (first == ".END") break;
-                (void)title_checked;
                 element_line(tok, "", {});
             }
         }

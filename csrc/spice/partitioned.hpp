@@ -29,7 +29,7 @@ namespace nspice {
 class SweepPool {
 public:
     explicit SweepPool(unsigned threads) {
-        for (unsigned i = 1; i < threads; ++i) workers_.emplace_back([this, i] { loop(i); });
+        for (unsigned i = 1; i < threads; ++i) workers_.emplace_back([this] { loop(); });
         nthreads_ = threads ? threads : 1;
     }
     ~SweepPool() {
@@ -61,7 +61,7 @@ private:
     void work() {
         for (unsigned i = next_.fetch_add(1); i < count_; i = next_.fetch_add(1)) (*fn_)(i);
     }
-    void loop(unsigned) {
+    void loop() {
         uint64_t seen = 0;
         while (true) {
             int spins = 0;
@@ -133,7 +133,7 @@ public:
         const uint32_t k = uint32_t(parts_.size());
         for (auto& p : parts_) p.state = p.engine->seeded_state();
         // consistent start: relax the DC point (or the seeded state when .ic lines exist) across partitions
-        relax(/*dc=*/true, 0.0);
+        relax_dc();
         record(0.0);
         const uint64_t planned = cfg_.dt > 0 ? uint64_t(std::ceil(cfg_.tstop / cfg_.dt - 1e-9)) : 0;
         uint64_t step = 0;
@@ -253,8 +253,7 @@ private:
     }
     // Block relaxation of the DC point: each partition solves its operating point with the ghosts
     // pinned to the neighbours' latest values.
-    void relax(bool dc, double) {
-        if (!dc) return;
+    void relax_dc() {
         const uint32_t k = uint32_t(parts_.size());
         for (auto& part : parts_) { part.next = part.state; part.pins.clear(); part.latest.clear(); }
         for (int sweep = 0; sweep < 200; ++sweep) {
