@@ -37,14 +37,14 @@ except Exception:  # pragma: no cover - older torch
     ReduceScatter = object  # type: ignore
 
 
-def _chunk_for(shard: int) -> int:
-    """Chunk size for a shard: the power of two at or above shard / 1024 in [4096, 131072] (every chunk
+def _chunk_for(shard: int, per_shard: int = 1024, cap: int = 131072) -> int:
+    """Chunk size for a shard: the power of two at or above shard / per_shard in [4096, cap] (every chunk
     costs a flag round trip), halved while the shard would give fewer than 4 chunks, never below 2048."""
     env = os.environ.get("NANGILA_CHUNK")
     if env:
         return int(env)
     c = 4096
-    while c < 131072 and c * 1024 < shard:
+    while c < cap and c * per_shard < shard:
         c *= 2
     while c > 2048 and shard < 4 * c:
         c //= 2
@@ -116,7 +116,9 @@ class NangilaReduceScatter(_Base, ReduceScatter):
         key = (n, inputs[0].dtype)
         st = self._regions.get(key)
         if st is None:
-            chunk = _chunk_for(n // self.world)
+            # 256 chunks per shard, at most 64 K elements: at 8 ranks and 256 MB this took the launch from 0.519 ms
+            # (1024 chunks of 16 K per shard) to 0.353 ms; NCCL's reduce-scatter needs 0.407 ms there
+            chunk = _chunk_for(n // self.world, per_shard=256, cap=65536)
             total, r1, f1, nchunks = self._glue.rs_region_layout(n, self.world, chunk)
             st = dict(region=arena.allocate(int(total)), r1=r1, f1=f1, nchunks=nchunks, chunk=chunk, epoch=0, index=len(self._regions),
                       ef=[torch.zeros(n, dtype=torch.bfloat16, device=inputs[0].device) if self.error_feedback else None
