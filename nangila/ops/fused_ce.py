@@ -8,6 +8,7 @@ once more and writes the bf16 gradient with zeros in the padded columns.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 from typing import Optional
 
@@ -67,12 +68,13 @@ class _FusedCrossEntropy(torch.autograd.Function):
 
 def fused_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, num_classes: Optional[int] = None) -> torch.Tensor:
     """Mean cross-entropy of ``logits[:, :num_classes]`` against ``targets``. CUDA bf16 logits with a
-    row length that is a multiple of 8 take the fused kernels; anything else takes PyTorch's path."""
+    row length that is a multiple of 8 take the fused kernels; anything else (or ``NANGILA_FUSED_CE=0``) takes
+    PyTorch's path."""
     if logits.dim() != 2:
         logits = logits.reshape(-1, logits.size(-1))
     targets = targets.reshape(-1)
     v = logits.size(1) if num_classes is None else int(num_classes)
-    if (logits.is_cuda and logits.dtype == torch.bfloat16 and logits.size(1) % 8 == 0 and logits.is_contiguous()
+    if (os.environ.get("NANGILA_FUSED_CE", "1") != "0" and logits.is_cuda and logits.dtype == torch.bfloat16 and logits.size(1) % 8 == 0 and logits.is_contiguous()
             and logits.data_ptr() % 16 == 0 and 0 < v <= logits.size(1)):
         return _FusedCrossEntropy.apply(logits, targets.to(torch.int64).contiguous(), v)
     return F.cross_entropy(logits[:, :v].float(), targets)
