@@ -305,8 +305,12 @@ def test_generators_and_benchmark_suite():
 def test_spmv_row_block_table():
     """Host part of the device SpMV: rows are packed into blocks of at most 2048 non-zeros; a longer
     row stands alone."""
-    from nangila_spice.gpu import build_row_blocks, tridiagonal
+    from nangila_spice.gpu import build_row_blocks, kernels_library, tridiagonal
 
+    try:
+        kernels_library()
+    except (RuntimeError, OSError):
+        pytest.skip("kernel library not built (needs nvcc)")
     rp, col, val = tridiagonal(5000)
     b = build_row_blocks(rp)
     assert b[0] == 0 and b[-1] == 5000 and np.all(np.diff(b) > 0)
