@@ -260,9 +260,9 @@ def main() -> int:
     def timed(fn, steps: int):
         dist.barrier()
         torch.cuda.synchronize()
-        from nangila.ops import fused_ce
+        from nangila.ops import fused_ce, fused_grads
 
-        launches0 = (hook.get_kernel_launches() if hook is not None else 0) + fused_ce.launch_count
+        launches0 = (hook.get_kernel_launches() if hook is not None else 0) + fused_ce.launch_count + fused_grads.launch_count
         sampler = ClockSampler(local_rank)
         sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -278,7 +278,7 @@ def main() -> int:
         clocks = sampler.stop()
         ms = torch.tensor([e0.elapsed_time(e1), wall * 1e3], device=dev, dtype=torch.float64)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        launches = (hook.get_kernel_launches() if hook is not None else 0) + fused_ce.launch_count - launches0
+        launches = (hook.get_kernel_launches() if hook is not None else 0) + fused_ce.launch_count + fused_grads.launch_count - launches0
         return ms[0].item(), ms[1].item(), clocks, launches, last
 
     ms_dev, _, clocks, launches, last = timed(step_device, args.steps)

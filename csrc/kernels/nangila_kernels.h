@@ -188,6 +188,10 @@ int nangila_ce_forward(const void* logits, const int64_t* targets, float* losses
 int nangila_ce_backward(const void* logits, const int64_t* targets, const float* lse, const float* grad_out, void* grad, int64_t rows,
                         int v, int64_t stride, cudaStream_t stream);
 
+/* ---- column sums of a [R, C] bf16 matrix and of its product with a second one (colsum.cu) -------- */
+int64_t nangila_colsum_scratch_floats(int C);
+int nangila_colsum(const void* a, const void* b, int64_t R, int C, float* scratch, float* out, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,6 +18,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import fused_grads as FG
+
 
 @dataclass
 class GPT2Config:
@@ -50,12 +52,14 @@ class Block(nn.Module):
         self.out = nn.Linear(cfg.d_mlp, cfg.d_model)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        # same modules and parameters as plain nn.Linear / nn.LayerNorm calls; with NANGILA_FUSED_GRADS=1 the bias and
+        # LayerNorm parameter gradients of bf16 CUDA tensors come from the column-sum kernel (nangila/ops/fused_grads.py)
         b, t, c = x.shape
-        qkv = self.qkv(self.ln1(x)).view(b, t, 3, self.n_head, c // self.n_head)
+        qkv = FG.linear(FG.layer_norm(x, self.ln1), self.qkv).view(b, t, 3, self.n_head, c // self.n_head)
         q, k, v = qkv.unbind(dim=2)
         y = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
-        x = x + self.proj(y.transpose(1, 2).reshape(b, t, c))
-        x = x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+        x = x + FG.linear(y.transpose(1, 2).reshape(b, t, c), self.proj)
+        x = x + FG.linear(F.gelu(FG.linear(FG.layer_norm(x, self.ln2), self.fc), approximate="tanh"), self.out)
         return x
 
 
@@ -87,7 +91,7 @@ class GPT2(nn.Module):
         x = self.wte(idx) + self.wpe(pos)
         for blk in self.blocks:
             x = blk(x)
-        x = self.ln_f(x)
+        x = FG.layer_norm(x, self.ln_f)
         logits = F.linear(x, self.wte.weight)  # tied head over the padded vocabulary
         if targets is None:
             return logits

@@ -154,3 +154,45 @@ def test_fused_cross_entropy_matches_fp32_reference(rows, cols, classes):
     assert (g - gr).abs().max().item() <= 2 ** -8 * gr.abs().max().item() + 1e-7  # bf16 rounding of the gradient
     # rows sum to zero up to bf16 rounding
     assert g.sum(dim=1).abs().max().item() < 0.02 * 2.5 / rows + 1e-6
+
+
+@pytest.mark.parametrize("rows,cols", [(8192, 768), (1000, 3072), (37, 2304), (5, 4), (300, 132)])
+def test_colsum_matches_fp32_reference(rows, cols):
+    from nangila.ops.fused_grads import colsum
+
+    torch.manual_seed(rows + cols)
+    a = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    b = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    s, none = colsum(a)
+    assert none is None
+    ref_s = a.float().sum(0)
+    assert (s - ref_s).abs().max().item() <= 1e-4 * (a.float().abs().sum(0).max().item() + 1.0)
+    s2, p = colsum(a, b)
+    assert torch.equal(s, s2)  # fixed summation order: same bits
+    ref_p = (a.float() * b.float()).sum(0)
+    assert (p - ref_p).abs().max().item() <= 1e-4 * ((a.float() * b.float()).abs().sum(0).max().item() + 1.0)
+
+
+def test_gpt2_gradients_with_and_without_the_fused_gradient_kernels(monkeypatch):
+    """Same weights, same batch: parameter gradients with the column-sum kernel against PyTorch's own backward."""
+    from nangila.models.gpt2 import GPT2, GPT2Config
+
+    torch.manual_seed(0)
+    model = GPT2(GPT2Config.tiny()).cuda().to(torch.bfloat16)
+    tok = torch.randint(0, 1000, (4, 65), device="cuda")
+    grads = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("NANGILA_FUSED_GRADS", flag)
+        model.zero_grad(set_to_none=True)
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        grads[flag] = {n: p.grad.float().clone() for n, p in model.named_parameters()}
+        grads[flag]["loss"] = loss.detach().float()
+    from nangila.ops import fused_grads
+
+    assert fused_grads.launch_count > 0
+    assert torch.equal(grads["0"]["loss"], grads["1"]["loss"])  # forward is the same computation
+    for n in grads["0"]:
+        a, b = grads["0"][n], grads["1"][n]
+        tol = 0.02 * a.abs().max().item() + 1e-6  # bf16 rounding of reductions done in a different order
+        assert (a - b).abs().max().item() <= tol, n
