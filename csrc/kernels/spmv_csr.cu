@@ -227,6 +227,61 @@ __global__ void residual_init_kernel(double* r, double* r0, const double* b, con
     if (i < n) { double t = b[i] - ax[i]; r[i] = t; r0[i] = t; }
 }
 
+
+// ---- graph-captured iteration: scalars live on the device --------------------------------------------
+// sc[0] rho, [1] alpha, [2] omega, [3] beta, [4] r.r, [5] state (0 running, 1 stopped, 2 stop after this
+// iteration), [6] iterations done. A breakdown (a vanishing denominator) stops the iteration on the
+// device: the remaining kernels of the graph become no-ops.
+__global__ void dot_final_step_kernel(const double* __restrict__ partial, int blocks, double* __restrict__ sc, int step) {
+    __shared__ double d[2];
+    if (threadIdx.x < 2) {
+        double t = 0.0;
+        for (int b = 0; b < blocks; ++b) t += partial[2 * b + threadIdx.x];
+        d[threadIdx.x] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    const bool running = sc[5] == 0.0;
+    if (step == 1) {
+        if (!running) return;
+        if (fabs(d[0]) < 1e-300) { sc[5] = 1.0; return; }
+        sc[3] = (d[0] / sc[0]) * (sc[1] / sc[2]);
+        sc[0] = d[0];
+    } else if (step == 2) {
+        if (!running) return;
+        if (fabs(d[0]) < 1e-300) { sc[5] = 1.0; return; }
+        sc[1] = sc[0] / d[0];
+    } else if (step == 3) {
+        if (!running) return;
+        sc[2] = d[1] > 0.0 ? d[0] / d[1] : 0.0;
+        if (sc[2] == 0.0) sc[5] = 2.0;
+    } else {
+        if (sc[5] == 1.0) return;
+        sc[4] = d[0];
+        sc[6] += 1.0;
+        if (sc[5] == 2.0) sc[5] = 1.0;
+    }
+}
+__global__ void update_p_dev_kernel(double* p, double* ph, const double* r, const double* v, const double* inv_diag, const double* sc, int n) {
+    if (sc[5] != 0.0) return;
+    const double beta = sc[3], omega = sc[2];
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { double t = r[i] + beta * (p[i] - omega * v[i]); p[i] = t; ph[i] = t * inv_diag[i]; }
+}
+__global__ void update_s_dev_kernel(double* s, double* sh, const double* r, const double* v, const double* inv_diag, const double* sc, int n) {
+    if (sc[5] != 0.0) return;
+    const double alpha = sc[1];
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { double t = r[i] - alpha * v[i]; s[i] = t; sh[i] = t * inv_diag[i]; }
+}
+__global__ void update_xr_dev_kernel(double* x, double* r, const double* ph, const double* sh, const double* s, const double* t, const double* sc,
+                                     int n) {
+    if (sc[5] == 1.0) return;
+    const double alpha = sc[1], omega = sc[2];
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { x[i] += alpha * ph[i] + omega * sh[i]; r[i] = s[i] - omega * t[i]; }
+}
+
 }  // namespace
 
 struct NangilaSpmv {
@@ -239,6 +294,9 @@ struct NangilaSpmv {
     double* d_work = nullptr;   // 9 solver vectors + inverse diagonal, allocated on first solve
     double* d_partial = nullptr;  // reduction scratch: 2 * kRedBlocks + 2
     std::vector<double> h_inv_diag;
+    double* d_sc = nullptr;           // device scalars of the graph-captured solver iteration
+    cudaStream_t solve_stream = nullptr;
+    cudaGraphExec_t iter_graph = nullptr;
     std::vector<int> h_row_ptr, h_diag_slot;  // kept on the host to refresh the preconditioner when values change
 };
 
@@ -259,7 +317,12 @@ static void refresh_preconditioner(NangilaSpmv* c, const double* val) {
 
 static void free_arrays(NangilaSpmv* c) {
     cudaFree(c->d_row_ptr); cudaFree(c->d_col); cudaFree(c->d_blocks); cudaFree(c->d_val); cudaFree(c->d_x); cudaFree(c->d_y);
-    cudaFree(c->d_work); cudaFree(c->d_partial); cudaFree(c->d_status);
+    cudaFree(c->d_work); cudaFree(c->d_partial); cudaFree(c->d_status); cudaFree(c->d_sc);
+    if (c->iter_graph) cudaGraphExecDestroy(c->iter_graph);
+    if (c->solve_stream) cudaStreamDestroy(c->solve_stream);
+    c->iter_graph = nullptr;
+    c->solve_stream = nullptr;
+    c->d_sc = nullptr;
     c->d_status = nullptr;
     c->d_row_ptr = c->d_col = c->d_blocks = nullptr;
     c->d_val = c->d_x = c->d_y = c->d_work = c->d_partial = nullptr;
@@ -395,8 +458,9 @@ extern "C" int nangila_spmv_dims(const NangilaSpmv* c, int* n, int* nnz, int* n_
     return 0;
 }
 
-// Solves A x = b (x starts at 0) with vectors resident on the device; per iteration two SpMVs, three
-// fused vector kernels and two 16-byte reads of reduction results by the host.
+// Solves A x = b (x starts at 0) with vectors resident on the device. Default: the iteration is a CUDA graph
+// with its scalars on the device (below). NANGILA_SPMV_GRAPH=0: per iteration two SpMVs, three fused vector
+// kernels and four 16-byte reads of reduction results by the host.
 extern "C" int nangila_spmv_bicgstab(NangilaSpmv* c, const double* h_b, double* h_x, double tol, int max_iter, int* iterations,
                                      double* rel_residual) {
     if (!c || !c->d_val || !h_b || !h_x) return int(cudaErrorInvalidValue);
@@ -430,6 +494,60 @@ extern "C" int nangila_spmv_bicgstab(NangilaSpmv* c, const double* h_b, double* 
     double rel = sqrt(d[1]) / bnorm, rho = 1.0, alpha = 1.0, omega = 1.0;
     int it = 0;
     bool ok = rel < tol;
+    const char* genv = getenv("NANGILA_SPMV_GRAPH");
+    if (!ok && !(genv && genv[0] == '0')) {
+        // One iteration (2 SpMVs, 3 vector kernels, 4 reductions with their scalar updates) is captured
+        // once per loaded matrix as a CUDA graph and replayed; the host reads 24 bytes every 4th
+        // iteration to test convergence, so the loop is not bound by launch or copy latency.
+        if (!c->d_sc) {
+            if ((e = cudaMalloc(&c->d_sc, sizeof(double) * 8)) != cudaSuccess) return int(e);
+            if ((e = cudaStreamCreateWithFlags(&c->solve_stream, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
+        }
+        cudaStream_t st = c->solve_stream;
+        double* sc = c->d_sc;
+        if (!c->iter_graph) {
+            cudaGraph_t graph = nullptr;
+            if ((e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal)) != cudaSuccess) return int(e);
+            dot2_partial_kernel<<<kRedBlocks, kThreads, 0, st>>>(r0, r, nullptr, nullptr, n, c->d_partial);
+            dot_final_step_kernel<<<1, 32, 0, st>>>(c->d_partial, kRedBlocks, sc, 1);
+            update_p_dev_kernel<<<grid, kThreads, 0, st>>>(p, ph, r, v, inv, sc, n);
+            nangila_spmv_device(c, ph, v, st);
+            dot2_partial_kernel<<<kRedBlocks, kThreads, 0, st>>>(r0, v, nullptr, nullptr, n, c->d_partial);
+            dot_final_step_kernel<<<1, 32, 0, st>>>(c->d_partial, kRedBlocks, sc, 2);
+            update_s_dev_kernel<<<grid, kThreads, 0, st>>>(s, sh, r, v, inv, sc, n);
+            nangila_spmv_device(c, sh, t, st);
+            dot2_partial_kernel<<<kRedBlocks, kThreads, 0, st>>>(t, s, t, t, n, c->d_partial);
+            dot_final_step_kernel<<<1, 32, 0, st>>>(c->d_partial, kRedBlocks, sc, 3);
+            update_xr_dev_kernel<<<grid, kThreads, 0, st>>>(x, r, ph, sh, s, t, sc, n);
+            dot2_partial_kernel<<<kRedBlocks, kThreads, 0, st>>>(r, r, nullptr, nullptr, n, c->d_partial);
+            dot_final_step_kernel<<<1, 32, 0, st>>>(c->d_partial, kRedBlocks, sc, 4);
+            e = cudaStreamEndCapture(st, &graph);
+            if (e != cudaSuccess || !graph) return int(e != cudaSuccess ? e : cudaErrorUnknown);
+            e = cudaGraphInstantiate(&c->iter_graph, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) { c->iter_graph = nullptr; return int(e); }
+        }
+        const double init[8] = {1.0, 1.0, 1.0, 0.0, d[1], 0.0, 0.0, 0.0};
+        if ((e = cudaMemcpy(sc, init, sizeof init, cudaMemcpyHostToDevice)) != cudaSuccess) return int(e);
+        const int check_every = 4;
+        double tail[3] = {d[1], 0.0, 0.0};  // r.r, state, iterations
+        while (it < max_iter) {
+            for (int k = 0; k < check_every; ++k)
+                if ((e = cudaGraphLaunch(c->iter_graph, st)) != cudaSuccess) return int(e);
+            if ((e = cudaMemcpyAsync(tail, sc + 4, sizeof tail, cudaMemcpyDeviceToHost, st)) != cudaSuccess) return int(e);
+            if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return int(e);
+            it = int(tail[2]);
+            rel = sqrt(tail[0]) / bnorm;
+            if (rel < tol) { ok = true; break; }
+            if (tail[1] != 0.0) break;
+        }
+        if ((e = cudaMemcpy(h_x, x, sizeof(double) * N, cudaMemcpyDeviceToHost)) != cudaSuccess) return int(e);
+        if (iterations) *iterations = it;
+        if (rel_residual) *rel_residual = rel;
+        if ((e = cudaGetLastError()) != cudaSuccess) return int(e);
+        if (int stt = nangila_spmv_status(c)) return stt;
+        return ok ? 0 : -1;
+    }
     while (!ok && it < max_iter) {
         if ((e = dots(r0, r, nullptr, nullptr, d)) != cudaSuccess) return int(e);
         double rho_new = d[0];

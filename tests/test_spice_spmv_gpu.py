@@ -138,3 +138,26 @@ def test_transient_simulation_with_the_device_linear_solver():
     assert dev["newton"]["device_solves"] == dev["newton"]["linear_solves"] > 150
     assert dev["newton"]["krylov_fallbacks"] <= dev["newton"]["linear_solves"] // 10
     assert np.abs(np.array(dev["values"]) - np.array(ref["values"])).max() < 1e-6
+
+
+def test_graph_captured_iteration_agrees_with_the_host_driven_loop(monkeypatch):
+    """The CUDA-graph form of the BiCGSTAB iteration (scalars on the device, convergence read every 4th
+    iteration) against the loop whose scalars go through the host."""
+    from nangila_spice.gpu import DeviceCsr, tridiagonal
+
+    n = 30_001
+    row_ptr, col, val = tridiagonal(n, diag=2.2, off=-1.0)
+    b = np.random.default_rng(5).standard_normal(n)
+    m = DeviceCsr(row_ptr, col, val)
+    x_graph, it_graph, rel_graph, ok_graph = m.solve(b, tol=1e-10, max_iter=400)
+    monkeypatch.setenv("NANGILA_SPMV_GRAPH", "0")
+    x_host, it_host, rel_host, ok_host = m.solve(b, tol=1e-10, max_iter=400)
+    assert ok_graph and ok_host and rel_graph < 1e-10 and rel_host < 1e-10
+    assert it_host <= it_graph <= it_host + 3  # the graph form tests convergence every 4th iteration
+    assert np.abs(x_graph - x_host).max() < 1e-8 * (np.abs(x_host).max() + 1.0)
+    # a right-hand side of zeros is solved before the first iteration; an unreachable tolerance stops at max_iter
+    monkeypatch.delenv("NANGILA_SPMV_GRAPH")
+    x0, it0, _, ok0 = m.solve(np.zeros(n))
+    assert ok0 and it0 == 0 and not x0.any()
+    _, it_cap, _, ok_cap = m.solve(b, tol=1e-30, max_iter=8)
+    assert not ok_cap and it_cap <= 8 + 3
