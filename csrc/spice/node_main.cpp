@@ -7,6 +7,8 @@
 //
 // Flag set and the waveform JSON layout ({netlist, node_names, waveform: [{time, voltages{}}],
 // stats{}}) follow the reference's CLI (nangila-spice/nangila-node/src/main.rs:21-132).
+#include <unistd.h>
+
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -196,13 +198,30 @@ int main(int argc, char** argv) {
     solver.engine().newton.config.reltol = a.reltol;
     if (a.solver == "dense") solver.engine().newton.linear.backend = LinearBackend::Dense;
     else if (a.solver == "krylov") solver.engine().newton.linear.backend = LinearBackend::Krylov;
-    else if (a.solver == "cuda") solver.engine().newton.linear.backend = LinearBackend::Cuda;  // needs NANGILA_KERNELS_LIB
+    else if (a.solver == "cuda") {
+        // the kernel library: $NANGILA_KERNELS_LIB, else the in-tree build next to this executable's package
+        if (!std::getenv("NANGILA_KERNELS_LIB")) {
+            char buf[4096];
+            ssize_t len = readlink("/proc/self/exe", buf, sizeof buf - 1);
+            if (len > 0) {
+                std::string exe(buf, size_t(len));
+                size_t cut = exe.rfind("/nangila_spice/bin/");
+                if (cut != std::string::npos) CudaKrylov::set_library(exe.substr(0, cut) + "/nangila/libnangila_kernels.so");
+            }
+        }
+        solver.engine().newton.linear.backend = LinearBackend::Cuda;
+    }
     PartitionState fin = solver.run();
     const SimStats& st = solver.stats;
     std::fprintf(stderr, "steps %llu%s, wall %.3f s, NR iterations/step %.2f, hit rate %.1f%%, rollbacks %llu\n",
                  (unsigned long long)st.total_steps, st.completed ? "" : " (stopped early: Newton did not converge)", st.wall_time_secs,
                  st.total_steps ? double(solver.engine().newton.stats.total_iterations) / double(st.total_steps) : 0.0, st.hit_rate() * 100.0,
                  (unsigned long long)st.rollbacks);
+    if (a.solver == "cuda") {
+        const auto& ls = solver.engine().newton.linear;
+        std::fprintf(stderr, "device linear solver: %llu solves on the GPU, %llu fell back to the sparse LU%s\n", (unsigned long long)ls.stats.device_solves,
+                     (unsigned long long)ls.stats.krylov_fallbacks, ls.cuda_error ? " (kernel library not usable: every solve ran on the host)" : "");
+    }
     for (size_t i = 0; i < names.size() && i < fin.voltages.size() && i < 16; ++i) std::fprintf(stderr, "  V(%s) = %.6f\n", names[i].c_str(), fin.voltages[i]);
     try {
         if (!a.waveform_json.empty()) write_json(a.waveform_json, name, names, solver.waveform, st);

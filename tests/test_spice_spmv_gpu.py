@@ -161,3 +161,18 @@ def test_graph_captured_iteration_agrees_with_the_host_driven_loop(monkeypatch):
     assert ok0 and it0 == 0 and not x0.any()
     _, it_cap, _, ok_cap = m.solve(b, tol=1e-30, max_iter=8)
     assert not ok_cap and it_cap <= 8 + 3
+
+
+def test_solver_process_with_the_device_linear_solver():
+    """``nangila-node --solver cuda`` finds the in-tree kernel library by itself and reports where its solves ran."""
+    import re
+    import subprocess
+
+    from nangila_spice.correctness import find_nangila_binary
+
+    proc = subprocess.run([find_nangila_binary(), "--demo", "--tstop", "3e-11", "--solver", "cuda"], capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0, proc.stderr
+    m = re.search(r"device linear solver: (\d+) solves on the GPU, (\d+) fell back", proc.stderr)
+    assert m and int(m.group(1)) >= 30 and "not usable" not in proc.stderr, proc.stderr
+    v = float(re.search(r"V\(cap\) = ([0-9.]+)", proc.stderr).group(1))
+    assert abs(v - 1.8 * (1 - 2.718281828 ** -3.0)) < 0.02
