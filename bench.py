@@ -22,10 +22,8 @@ import argparse
 import json
 import os
 import socket
-import statistics
 import subprocess
 import sys
-import threading
 import time
 
 BASELINE_TOKENS_PER_S = None  # the reference publishes no throughput number
@@ -39,132 +37,27 @@ def _free_port() -> int:
     return p
 
 
-class ClockSampler:
-    """Samples SM clock, power and throttle reasons of one GPU while a region runs: NVML from a
-    thread every 20 ms (no start-up delay, so even a sub-second region gets samples), ``nvidia-smi``
-    every 200 ms where NVML cannot be loaded."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
-    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-    # NVML clocks-event-reason bits, in the order of NAMES
-    BITS = (0x8, 0x40, 0x20, 0x4)
-
-    def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.lines = []
-        self.samples = []  # (sm MHz, power W, reason mask)
-        self.sm_max = None
-        self._stop = threading.Event()
-        self._thread = None
-        self._nvml = None
-
-    def _nvml_handle(self):
-        import pynvml
-
-        pynvml.nvmlInit()
-        try:
-            import torch
-
-            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
-            if not uuid.startswith("GPU-"):
-                uuid = "GPU-" + uuid
-            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
-        except Exception:
-            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-        return pynvml, handle
-
-    def _poll(self, pynvml, handle):
-        reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
-            pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
-        while not self._stop.is_set():
-            try:
-                sm = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
-                power = pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
-                mask = int(reasons_fn(handle))
-                self.samples.append((float(sm), power, mask))
-            except Exception:
-                pass
-            self._stop.wait(0.02)
-
-    def start(self):
-        try:
-            pynvml, handle = self._nvml_handle()
-            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
-            self._nvml = pynvml
-            self._thread = threading.Thread(target=self._poll, args=(pynvml, handle), daemon=True)
-            self._thread.start()
-            return self
-        except Exception:
-            self._nvml = None
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except Exception:
-            self.proc = None
-        return self
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self._nvml is not None:
-            self._stop.set()
-            self._thread.join(timeout=2)
-            sm = [s[0] for s in self.samples]
-            power = [s[1] for s in self.samples]
-            reasons = sorted({n for _, _, m in self.samples for n, b in zip(self.NAMES, self.BITS) if m & b})
-            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.sm_max,
-                    "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": reasons,
-                    "source": "nvml"}
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, power, reasons = [], [], [], set()
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 8:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-                power.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(self.NAMES, parts[4:8]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons),
-                "source": "nvidia-smi"}
-
-
 def reference_arm(args) -> int:
-    why = None
-    ref = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
-    sys.path.insert(0, ref)
-    try:
-        import importlib
-
-        importlib.import_module("nangila.nangila")
-        why = "reference imported unexpectedly; its GPU hook path is known broken (header size / ABI mismatches)"
-    except Exception:
+    """The reference implementation, unmodified, from ``baseline/_ref`` through its own public API
+    (``nangila.ddp.register_nangila_hook`` on a plain-PyTorch GPT-2 of the same shape): it runs in a child
+    process whose import path holds ``baseline/_ref`` and not this repository, so the name ``nangila`` can
+    only resolve to the reference. Whether the reference is installed is decided from the files alone;
+    nothing named ``nangila`` is imported in this process."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref = os.path.join(here, "baseline", "_ref")
+    pkg = os.path.join(ref, "nangila")
+    native = [f for f in (os.listdir(pkg) if os.path.isdir(pkg) else []) if f.startswith("nangila") and f.endswith(".so")]
+    if not native:
         why = ("reference cannot be installed offline: its build backend is maturin over a Rust workspace and the "
-               "image has no maturin, cargo or rustc (pip: ModuleNotFoundError: No module named 'maturin')")
-    finally:
-        sys.path.remove(ref)
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+               "image has no maturin, cargo or rustc (pip: ModuleNotFoundError: No module named 'maturin'); "
+               "baseline/_ref holds no nangila package")
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    env = dict(os.environ, PYTHONPATH=ref, PYTHONNOUSERSITE="1")
+    cmd = [sys.executable, os.path.join(here, "baseline", "reference_runner.py"), "--steps", str(args.steps),
+           "--warmup", str(args.warmup), "--micro-batch", str(args.micro_batch), "--seq-len", str(args.seq_len)]
+    return subprocess.call(cmd, env=env, cwd=ref)
 
 
 def main() -> int:
@@ -189,6 +82,7 @@ def main() -> int:
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from nangila.ddp import register_nangila_hook
     from nangila.models.gpt2 import GPT2, GPT2Config
+    from nangila.utils.benchmarking import ClockSampler
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -236,7 +130,7 @@ def main() -> int:
         opt.zero_grad(set_to_none=True)
         if hook is not None:
             hook.step()
-        return loss
+        return loss.detach()
 
     def step_e2e(i: int) -> float:
         tok = host_tokens[i % n_batches].to(dev, non_blocking=True)

@@ -7,6 +7,13 @@
 // step, fed from a pinned host copy of the kernels' statistics) and the safe-mode monitor run in
 // `step()` / `report_validation_loss()`.
 //
+// Phase deferral. With more than one rank the compressed exchange of a bucket is queued as separate
+// launches of the same kernel, one per phase: phase 1 (quantize and push, never waits for a peer) at once,
+// the phases that wait for peers' flags only when the NEXT bucket arrives (or, for the last bucket of
+// the iteration, right away). Nothing consumes a bucket before the end of backward, so the delay is free,
+// and by the time a waiting phase starts the peers have usually delivered: the kernel no longer sits on
+// the SMs spinning while ranks are skewed. The bucket's future completes after its last phase.
+//
 // Counterpart of nangila::NangilaDDPHook in the reference (nangila_ddp/src/ddp_hook.cpp:45-372),
 // which per bucket ran a compress kernel, two all-gathers with host synchronisation, one reconstruct
 // kernel per rank, an accumulate / divide and two history copies.
@@ -21,6 +28,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <deque>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -37,7 +45,6 @@ namespace py = pybind11;
 namespace {
 
 constexpr int kStatsWidth = 8;
-constexpr int kSmCount = 148;
 
 int grad_dtype_code(const at::Tensor& t) {
   switch (t.scalar_type()) {
@@ -70,9 +77,20 @@ struct Bucket {
   uint64_t compressed_calls = 0;
   uint64_t probe_every = 0;  // calls between history probes while the gain is 0 (0: not initialised)
   uint64_t next_probe = 0;
+  uint64_t last_probe = 0;
   double totals[4] = {0, 0, 0, 0};
   // NANGILA_TIMING=1: events around the most recent launch of this bucket
   std::shared_ptr<at::cuda::CUDAEvent> t0, t1;
+};
+
+// A bucket whose later phases are still to be queued.
+struct Pending {
+  NangilaPredResParams p;
+  int next_bit;   // phase bit to launch next (2 or 4)
+  int last_bit;   // final phase bit of this exchange (2 in gather mode, 4 otherwise)
+  std::shared_ptr<torch::jit::PythonFutureWrapper> fut;
+  at::Tensor tensor;
+  Bucket* bucket;
 };
 
 class DdpHook {
@@ -87,6 +105,8 @@ class DdpHook {
     probe_every_ = std::max<int64_t>(1, int64_t(env_double("NANGILA_PROBE_EVERY", 8)));
     chunk_override_ = int32_t(env_double("NANGILA_CHUNK", 0));
     ctas_ = int32_t(env_double("NANGILA_COMM_CTAS", 0));
+    ctas_wait_ = int32_t(env_double("NANGILA_COMM_CTAS_WAIT", 0));
+    defer_ = env_double("NANGILA_DEFER", 1) != 0;
     timing_ = env_double("NANGILA_TIMING", 0) != 0;
     nvtx_ = env_double("NANGILA_NVTX", 0) != 0;
     gather_max_world_ = std::min<int32_t>(NANGILA_GATHER_MAX_WORLD, int32_t(env_double("NANGILA_GATHER_MAX_WORLD", NANGILA_GATHER_MAX_WORLD)));
@@ -116,7 +136,8 @@ class DdpHook {
   py::object run(py::object bucket) {
     at::Tensor tensor = bucket.attr("buffer")().cast<at::Tensor>();
     const int64_t index = bucket.attr("index")().cast<int64_t>();
-    return run_tensor(index, tensor);
+    const bool is_last = bucket.attr("is_last")().cast<bool>();
+    return run_tensor(index, tensor, is_last);
   }
 
   // Create the device state of a bucket without launching anything (checkpoint restore fills it in).
@@ -131,11 +152,14 @@ class DdpHook {
     bucket_for(index, tensor);
   }
 
-  py::object run_tensor(int64_t index, at::Tensor tensor) {
+  // `is_last`: no further bucket follows in this iteration, so nothing may stay deferred.
+  py::object run_tensor(int64_t index, at::Tensor tensor, bool is_last) {
     TORCH_CHECK(attached_, "nangila: attach() was not called");
     TORCH_CHECK(tensor.is_cuda() && tensor.is_contiguous(), "nangila: the C++ hook needs a contiguous CUDA bucket");
     TORCH_CHECK((reinterpret_cast<uintptr_t>(tensor.data_ptr()) & 15u) == 0, "nangila: bucket must be 16-byte aligned");
     c10::cuda::CUDAGuard guard(tensor.device());
+    std::vector<Pending> finished;  // futures to complete once the state lock is released
+    std::shared_ptr<torch::jit::PythonFutureWrapper> wrapper;
     {
     std::lock_guard<std::mutex> lock(mutex_);
     ensure_device(tensor);
@@ -169,8 +193,14 @@ class DdpHook {
     p.measure = 0;
     if (b.calls >= b.next_probe) {
       p.measure = 1;
+      b.last_probe = b.calls;
       b.next_probe = b.calls + b.probe_every;
     }
+    // the history is read by a probe and by a non-zero gain only: while the gain is 0 it is written on the
+    // two calls before a probe (the predictor needs two steps) and the two after it (until the controller
+    // has seen the probe's statistics), and left alone in between
+    p.skip_history = (compressed && b.pred_gain == 0.0 && p.measure == 0 && b.calls + 2 < b.next_probe &&
+                      b.calls > b.last_probe + 2) ? 1 : 0;
     p.gather = (compressed && world_ >= 2 && world_ <= gather_max_world_) ? 1 : 0;
     p.uniform_gain = 1;  // the statistics are summed over the group before the controller reads them
     p.epoch = b.epoch;
@@ -180,7 +210,7 @@ class DdpHook {
     p.mu = float(momentum_);
     p.pred_gain[0] = float(b.pred_gain);
     p.timeout_ns = uint64_t(timeout_s_ * 1e9);
-    p.grid_x = grid_for(b);
+    p.grid_x = grid_for(b, false);
     p.recv1_off = b.r1;
     p.recv2_off = b.r2;
     p.flag1_off = b.f1;
@@ -206,31 +236,56 @@ class DdpHook {
       }
       b.t0->record(*stream_);
     }
+    // split into per-phase launches when there are peers to wait for; otherwise one fused launch
+    const bool split = defer_ && compressed && world_ > 1;
+    p.phase_mask = split ? 1 : 0;
     const int err = nangila_predres_launch(&p, stream_->stream());
-    if (timing_) b.t1->record(*stream_);
     if (nvtx_) nvtxRangePop();
     TORCH_CHECK(err == 0, "nangila: predres_launch failed: ", cudaGetErrorString(static_cast<cudaError_t>(err)));
     std::swap(b.prev, b.curr);
-    }  // state lock released: completing the future below drops and re-takes the GIL
 
     // DDP's Python-hook adapter expects the future's value to be a Python object (the bucket tensor).
-    // Completing it while the exchange stream is current records the stream's event in the future,
-    // so the reducer's wait orders its own stream after the kernel.
     auto fut = c10::make_intrusive<c10::ivalue::Future>(c10::PyObjectType::get(), std::vector<c10::Device>{tensor.device()});
-    auto wrapper = std::make_shared<torch::jit::PythonFutureWrapper>(fut);
-    {
-      c10::cuda::CUDAStreamGuard sg(*stream_);
-      wrapper->markCompleted(py::cast(tensor));
+    wrapper = std::make_shared<torch::jit::PythonFutureWrapper>(fut);
+    // older buckets advance by one phase each (oldest first); then this one joins the queue
+    advance_pending(finished, /*drain=*/false);
+    if (split) {
+      Pending q;
+      q.p = p;
+      q.p.grid_x = grid_for(b, true);
+      q.next_bit = 2;
+      q.last_bit = p.gather != 0 ? 2 : 4;
+      q.fut = wrapper;
+      q.tensor = tensor;
+      q.bucket = &b;
+      pending_.push_back(std::move(q));
+    } else {
+      if (timing_) b.t1->record(*stream_);
+      Pending q;
+      q.fut = wrapper;
+      q.tensor = tensor;
+      q.bucket = &b;
+      finished.push_back(std::move(q));
     }
+    if (is_last) advance_pending(finished, /*drain=*/true);
+    }  // state lock released: completing a future below drops and re-takes the GIL
+
+    // Completing a future while the exchange stream is current records the stream's event in it, so
+    // the reducer's wait orders its own stream after everything queued on the exchange stream so far,
+    // which includes the bucket's last phase.
+    complete(finished);
     return py::cast(wrapper);
   }
 
   // Once per optimizer step, after the last bucket was queued.
   void step() {
+    std::vector<Pending> finished;
+    {
     std::lock_guard<std::mutex> lock(mutex_);
     step_ += 1;
     if (!stream_) return;
     c10::cuda::CUDAGuard guard(device_);
+    advance_pending(finished, /*drain=*/true);  // nothing should be left; a caller that bypassed is_last ends here
     if (stats_pending_) {
       stats_event_.synchronize();
       const float* host = stats_host_.data_ptr<float>();
@@ -242,6 +297,11 @@ class DdpHook {
       stats_dev_.zero_();
       stats_event_.record(*stream_);
       stats_pending_ = true;
+    }
+    }
+    if (!finished.empty()) {
+      c10::cuda::CUDAGuard guard(device_);
+      complete(finished);
     }
   }
 
@@ -271,6 +331,18 @@ class DdpHook {
   // Blocks until the exchange stream is idle; raises if a kernel gave up waiting for a peer.
   void check_status() {
     if (!stream_) return;
+    {
+      std::vector<Pending> finished;
+      {
+        std::lock_guard<std::mutex> lock(mutex_);
+        c10::cuda::CUDAGuard guard(device_);
+        advance_pending(finished, /*drain=*/true);
+      }
+      if (!finished.empty()) {
+        c10::cuda::CUDAGuard guard(device_);
+        complete(finished);
+      }
+    }
     stream_->synchronize();
     at::Tensor host = status_.cpu();
     const int32_t* w = host.data_ptr<int32_t>();
@@ -332,6 +404,36 @@ class DdpHook {
   }
 
  private:
+  // Queue the next phase of every deferred bucket (oldest first); with `drain`, keep going until nothing
+  // is deferred. Buckets whose last phase has been queued move to `finished`. Caller holds the lock.
+  void advance_pending(std::vector<Pending>& finished, bool drain) {
+    do {
+      const size_t count = pending_.size();
+      for (size_t i = 0; i < count; ++i) {
+        Pending q = std::move(pending_.front());
+        pending_.pop_front();
+        q.p.phase_mask = q.next_bit;
+        launches_ += 1;
+        const int err = nangila_predres_launch(&q.p, stream_->stream());
+        TORCH_CHECK(err == 0, "nangila: predres_launch failed: ", cudaGetErrorString(static_cast<cudaError_t>(err)));
+        if (q.next_bit == q.last_bit) {
+          if (timing_ && q.bucket->t1) q.bucket->t1->record(*stream_);
+          finished.push_back(std::move(q));
+        } else {
+          q.next_bit <<= 1;
+          pending_.push_back(std::move(q));
+        }
+      }
+    } while (drain && !pending_.empty());
+  }
+
+  void complete(std::vector<Pending>& finished) {
+    if (finished.empty()) return;
+    c10::cuda::CUDAStreamGuard sg(*stream_);
+    for (auto& q : finished) q.fut->markCompleted(py::cast(q.tensor));
+    finished.clear();
+  }
+
   void ensure_device(const at::Tensor& t) {
     if (stream_) return;
     device_ = t.device();
@@ -378,10 +480,12 @@ class DdpHook {
     return buckets_[index];
   }
 
-  int32_t grid_for(const Bucket& b) const {
+  // CTAs for a launch: no more than there are chunks; the launcher clamps to what the device can hold at
+  // once. `waiting`: a launch of phases 2 / 3 only (NANGILA_COMM_CTAS_WAIT), which may spend time polling flags.
+  int32_t grid_for(const Bucket& b, bool waiting) const {
     const int64_t owned = (b.nchunks + world_ - 1) / world_;
     const int64_t want = owned * world_;  // = chunks of the bucket, rounded up to whole rounds
-    const int64_t cap = ctas_ > 0 ? ctas_ : kSmCount * 4;
+    const int64_t cap = waiting && ctas_wait_ > 0 ? ctas_wait_ : ctas_ > 0 ? ctas_ : (int64_t(1) << 20);
     return int32_t(std::max<int64_t>(1, std::min(want, cap)));
   }
 
@@ -423,6 +527,9 @@ class DdpHook {
   int64_t probe_every_;
   int32_t chunk_override_;
   int32_t ctas_;
+  int32_t ctas_wait_ = 0;
+  bool defer_ = true;
+  std::deque<Pending> pending_;
   int32_t gather_max_world_;
   bool timing_ = false;
   bool nvtx_ = false;
@@ -449,7 +556,7 @@ void register_ddp_hook(py::module_& m) {
       .def("configure", &DdpHook::configure, py::arg("momentum") = 0.9, py::arg("error_feedback") = true,
            py::arg("stochastic") = true, py::arg("seed") = 42, py::arg("max_buckets") = 512)
       .def("run", &DdpHook::run, py::arg("bucket"))
-      .def("run_tensor", &DdpHook::run_tensor, py::arg("index"), py::arg("tensor"))
+      .def("run_tensor", &DdpHook::run_tensor, py::arg("index"), py::arg("tensor"), py::arg("is_last") = true)
       .def("ensure_bucket", &DdpHook::ensure_bucket, py::arg("bucket"))
       .def("step", &DdpHook::step)
       .def("current_step", &DdpHook::current_step)

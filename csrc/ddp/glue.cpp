@@ -46,7 +46,7 @@ void predres_launch(const std::vector<at::Tensor>& grad, const std::vector<at::T
                     int64_t recv1_off, int64_t recv2_off, int64_t flag1_off, int64_t flag2_off, int64_t rank0,
                     int64_t chunk_elems, int64_t mode, bool stochastic, bool measure, int64_t epoch, int64_t seed, int64_t step,
                     int64_t bucket_id, double mu, const std::vector<double>& pred_gain, double timeout_s, int64_t grid_x,
-                    bool uniform_gain, bool gather) {
+                    bool uniform_gain, bool gather, int64_t phase_mask, bool skip_history) {
   const size_t nvr = grad.size();
   TORCH_CHECK(nvr >= 1 && nvr <= NANGILA_MAX_VRANKS, "nangila: bad number of emulated ranks");
   TORCH_CHECK(prev.size() == nvr && curr.size() == nvr && ef.size() == nvr && ef2.size() == nvr &&
@@ -69,6 +69,8 @@ void predres_launch(const std::vector<at::Tensor>& grad, const std::vector<at::T
   p.measure = measure ? 1 : 0;
   p.uniform_gain = uniform_gain ? 1 : 0;
   p.gather = gather ? 1 : 0;
+  p.phase_mask = int32_t(phase_mask);
+  p.skip_history = skip_history ? 1 : 0;
   p.epoch = uint32_t(epoch);
   p.seed = uint32_t(seed);
   p.step = uint32_t(step);
@@ -172,7 +174,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("recv2_off"), py::arg("flag1_off"), py::arg("flag2_off"), py::arg("rank0"), py::arg("chunk_elems"),
         py::arg("mode"), py::arg("stochastic"), py::arg("measure"), py::arg("epoch"), py::arg("seed"), py::arg("step"),
         py::arg("bucket_id"), py::arg("mu"), py::arg("pred_gain"), py::arg("timeout_s"), py::arg("grid_x"),
-        py::arg("uniform_gain") = false, py::arg("gather") = false);
+        py::arg("uniform_gain") = false, py::arg("gather") = false, py::arg("phase_mask") = 0,
+        py::arg("skip_history") = false);
   m.def("predict_quantize_gamma", &predict_quantize_gamma);
   m.def("dequant_reconstruct_gamma", &dequant_reconstruct_gamma);
   m.def("raw_predict_and_quantize", &raw_predict_and_quantize);

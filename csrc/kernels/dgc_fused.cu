@@ -27,6 +27,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "launch_util.cuh"
 #include "nangila_kernels.h"
 #include "quant.cuh"
 #include "radix_select.cuh"
@@ -402,7 +403,7 @@ extern "C" int nangila_dgc_launch(const NangilaDgcParams* p, cudaStream_t stream
   using namespace nangila;
   if (p == nullptr || p->n <= 0 || p->n > 0x7fffffffll || p->world < 1 || p->world > NANGILA_MAX_RANKS ||
       p->nvr < 1 || p->nvr > NANGILA_MAX_VRANKS || p->rank0 < 0 || p->rank0 + p->nvr > p->world ||
-      (p->nvr > 1 && p->nvr != p->world) || p->epoch == 0 || p->grid_x < 1 || p->capacity == 0 ||
+      (p->nvr > 1 && p->nvr != p->world) || p->epoch == 0 || p->capacity == 0 ||
       p->capacity % 4 != 0 || p->k > p->capacity || (p->cand_capacity != 0 && p->cand_capacity < p->k) || !(p->momentum >= 0.0f && p->momentum < 1.0f))
     return int(cudaErrorInvalidValue);
   const void* fn;
@@ -412,7 +413,10 @@ extern "C" int nangila_dgc_launch(const NangilaDgcParams* p, cudaStream_t stream
     case NANGILA_F16: fn = reinterpret_cast<const void*>(&dgc_fused_kernel<__half>); break;
     default: return int(cudaErrorInvalidValue);
   }
-  dim3 grid(unsigned(p->grid_x), unsigned(p->nvr)), block(kThreads);
+  int grid_x = 0;
+  const cudaError_t ce = clamp_grid(fn, kThreads, 0, p->grid_x, p->nvr, &grid_x);
+  if (ce != cudaSuccess) return int(ce);
+  dim3 grid(unsigned(grid_x), unsigned(p->nvr)), block(kThreads);
   void* args[] = {const_cast<NangilaDgcParams*>(p)};
   return int(cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream));
 }

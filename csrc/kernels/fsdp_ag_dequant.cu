@@ -17,6 +17,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "launch_util.cuh"
 #include "nangila_kernels.h"
 #include "quant.cuh"
 #include "signal.cuh"
@@ -176,7 +177,7 @@ extern "C" int nangila_ag_launch(const NangilaAgParams* p, cudaStream_t stream) 
   if (p == nullptr || p->shard_elems <= 0 || p->shard_elems % 8 != 0 || p->world < 1 || p->world > NANGILA_MAX_RANKS ||
       p->nvr < 1 || p->nvr > NANGILA_MAX_VRANKS || p->rank0 < 0 || p->rank0 + p->nvr > p->world ||
       (p->nvr > 1 && p->nvr != p->world) || p->chunk_elems <= 0 || p->chunk_elems % kPerIter != 0 || p->epoch == 0 ||
-      p->grid_x < 1 || (p->bits != 8 && p->bits != 4))
+      (p->bits != 8 && p->bits != 4))
     return int(cudaErrorInvalidValue);
   const void* fn = nullptr;
 #define NANGILA_AG_PICK(TYPE)                                                                  \
@@ -189,7 +190,10 @@ extern "C" int nangila_ag_launch(const NangilaAgParams* p, cudaStream_t stream) 
     default: return int(cudaErrorInvalidValue);
   }
 #undef NANGILA_AG_PICK
-  dim3 grid(unsigned(p->grid_x), unsigned(p->nvr)), block(kThreads);
+  int grid_x = 0;
+  const cudaError_t ce = clamp_grid(fn, kThreads, 0, p->grid_x, p->nvr, &grid_x);
+  if (ce != cudaSuccess) return int(ce);
+  dim3 grid(unsigned(grid_x), unsigned(p->nvr)), block(kThreads);
   void* args[] = {const_cast<NangilaAgParams*>(p)};
   if (p->nvr > 1) return int(cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream));
   return int(cudaLaunchKernel(fn, grid, block, args, 0, stream));

@@ -28,6 +28,8 @@ enum NangilaDType { NANGILA_F32 = 0, NANGILA_F16 = 1, NANGILA_BF16 = 2 };
  *
  * Multi-GPU: nvr = 1, rank0 = this rank, `region[r]` = rank r's mapping of the bucket's symmetric
  * region. Single-GPU loopback: nvr = world, rank0 = 0, grid.y = nvr, launched cooperatively.
+ * grid_x is clamped to the number of CTAs of the chosen variant that the device can hold at once
+ * (occupancy x SM count, divided by nvr); grid_x <= 0 asks for exactly that number.
  */
 typedef struct NangilaPredResParams {
   void* grad[NANGILA_MAX_VRANKS];      /* in/out: bucket, n elements of grad_dtype */
@@ -62,6 +64,13 @@ typedef struct NangilaPredResParams {
   int32_t grid_x;                      /* CTAs per rank */
   void* out_shard[NANGILA_MAX_VRANKS]; /* mode 2: n / world elements of grad_dtype, this rank's reduced shard */
   float out_scale;                     /* mode 2: result = sum of all ranks' values * out_scale (1/W for a mean) */
+  int32_t phase_mask;                  /* 0 or 7: all phases in this launch. Otherwise a contiguous set of bits
+                                          (1: phase 1, 2: phase 2, 4: phase 3): the launch runs only those phases
+                                          of the epoch. The caller queues the remaining phases of the same epoch
+                                          later on the same stream with otherwise identical parameters, which lets
+                                          it put other buckets' non-waiting phase 1 in between. */
+  int32_t skip_history;                /* 1: do not write the new history (allowed while the gain is 0 and no probe
+                                          is near: nothing reads it); the caller still swaps prev / curr */
 } NangilaPredResParams;
 
 /* Bytes one rank's symmetric region must have for a bucket. */

@@ -27,6 +27,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "launch_util.cuh"
 #include "nangila_kernels.h"
 #include "ptx_sm100.cuh"
 #include "quant.cuh"
@@ -125,7 +126,8 @@ __device__ __forceinline__ void phase1_compressed(T* __restrict__ grad, S* __res
                                                   const S* __restrict__ curr, S* __restrict__ ef, uint8_t* dst,
                                                   int64_t tbase, int64_t lim, int iters, int C, int tid, float mu,
                                                   float kappa, bool use_history, uint32_t key1, bool stochastic,
-                                                  Stats& st, int ndst, uint8_t* const* regions, uint64_t dst_off) {
+                                                  Stats& st, int ndst, uint8_t* const* regions, uint64_t dst_off,
+                                                  bool keep_history) {
 #pragma unroll 2
   for (int it = 0; it < iters; ++it) {
     const int64_t base = tbase + int64_t(it) * kElemsPerIter + tid * kE;
@@ -184,7 +186,7 @@ __device__ __forceinline__ void phase1_compressed(T* __restrict__ grad, S* __res
         for (int i = 0; i < kE; ++i) out[i] = __fmaf_rn(kappa, pred[i], out[i]);
       }
       store8<T, GUARD>(grad, base, lim, out);
-      store8<S, GUARD>(prev, base, lim, out);
+      if (keep_history) store8<S, GUARD>(prev, base, lim, out);
     } else if (ndst == 1) {
       *packed_ptr(dst, C, it, tid) = packed;
       if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
@@ -226,7 +228,7 @@ __device__ __forceinline__ bool phase1_bulk(T* __restrict__ grad, S* __restrict_
                                             int64_t tbase, int iters, int C, int tid, float mu, float kappa,
                                             bool use_history, uint32_t key1, bool stochastic, Stats& st,
                                             uint8_t* ring, uint64_t* bars, uint32_t& kuse, uint64_t timeout_ns,
-                                            int ndst, uint8_t* const* regions, uint64_t dst_off) {
+                                            int ndst, uint8_t* const* regions, uint64_t dst_off, bool keep_history) {
   using R = Ring<T, S, LEAN>;
   constexpr int D = R::D;
   const int lane = tid & 31, warp = tid >> 5;
@@ -326,7 +328,7 @@ __device__ __forceinline__ bool phase1_bulk(T* __restrict__ grad, S* __restrict_
         for (int i = 0; i < kE; ++i) out[i] = __fmaf_rn(kappa, __fmaf_rn(mu, cu[i] - pv[i], cu[i]), out[i]);
       }
       Vec8<T>::store(grad + base, out);
-      Vec8<S>::store(prev + base, out);  // becomes g(t) after the caller swaps prev and curr
+      if (keep_history) Vec8<S>::store(prev + base, out);  // becomes g(t) after the caller swaps prev and curr
     } else if (ndst == 1) {
       *packed_ptr(dst, C, it, tid) = packed;
       if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
@@ -431,10 +433,21 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   // With a zero gain the history only matters for the statistics that steer the gain; the host asks
   // for them on probe steps (p.measure) and the loads are skipped otherwise.
   const bool use_history = !RS && (kappa != 0.0f || p.measure != 0);
+  // The new history may be left unwritten only where nothing will read it: the caller asks for that
+  // while the gain is 0 and no probe is near. A non-zero gain or a probe always writes it.
+  const bool keep_history = !COMPRESSED || p.skip_history == 0 || use_history;
   Stats acc_stats;
 
+  // Phases of the epoch this launch runs (see NangilaPredResParams::phase_mask): tasks are ordered by
+  // phase, so a contiguous set of phases is a contiguous task range.
+  const int pm = (p.phase_mask & 7) == 0 ? 7 : (p.phase_mask & 7);
+  const int end1 = GATHER ? NC : T1;
+  const int end2 = GATHER ? 2 * NC : SINGLE ? T1 : T1 + my_owned;
+  const int task_begin = (pm & 1) ? 0 : (pm & 2) ? end1 : end2;
+  const int task_end = (pm & 4) ? ntasks : (pm & 2) ? end2 : end1;
+
   int local = 0;  // number of the task within this CTA
-  for (int task = blockIdx.x; task < ntasks; task += gridDim.x, ++local) {
+  for (int task = task_begin + int(blockIdx.x); task < task_end; task += gridDim.x, ++local) {
     const TaskInfo t = decode_task<RS, GATHER>(task, me, W, NC, T1, my_owned, C, n, cps, shard);
     const int c = t.c, j = t.j;
     const int64_t lim = t.limit;
@@ -485,14 +498,15 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           const int warp = tid >> 5;
           if (!phase1_bulk<T, S, LEAN, SINGLE>(grad, prev, curr, ef, dst, t.base, iters, C, tid, mu, kappa, use_history, key1,
                                        stochastic, acc_stats, s_ring + warp * R::BYTES_PER_WARP, &s_bars[warp][0],
-                                       ring_uses, p.timeout_ns, ndst, p.region, dst_off)) {
+                                       ring_uses, p.timeout_ns, ndst, p.region, dst_off, keep_history)) {
             if (lane == 0)
               report_failure(status, kTimeoutBulk, uint32_t(me), 0xffffffffu, epoch, 0u, 1u, uint32_t(c));
             break;
           }
         } else
           phase1_compressed<T, S, LEAN, true, SINGLE>(grad, prev, curr, ef, dst, t.base, lim, iters, C, tid, mu, kappa,
-                                              use_history, key1, stochastic, acc_stats, ndst, p.region, dst_off);
+                                              use_history, key1, stochastic, acc_stats, ndst, p.region, dst_off,
+                                              keep_history);
         if (!SINGLE && !GATHER && tid == 0) *reinterpret_cast<float*>(dst + compressed_trailer_off(C)) = kappa;
         if (GATHER && tid < W) *reinterpret_cast<float*>(p.region[tid] + dst_off + compressed_trailer_off(C)) = kappa;
       } else {
@@ -547,7 +561,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
               for (int i = 0; i < kE; ++i) acc[i] = __fmaf_rn(gbar, __fmaf_rn(mu, cu[i] - pv[i], cu[i]), acc[i]);
             }
             store8_guarded<T>(grad, base, n, acc);
-            store8_guarded<S>(prev, base, n, acc);  // becomes g(t) after the caller swaps prev and curr
+            if (keep_history) store8_guarded<S>(prev, base, n, acc);  // becomes g(t) after the caller swaps prev and curr
           }
         } else if constexpr (COMPRESSED) {
           const int64_t obase = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
@@ -681,7 +695,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           Vec8<T>::load(reinterpret_cast<const T*>(src) + int64_t(it) * kElemsPerIter + tid * kE, out);
         }
         store8<T, GUARD>(grad, base, n, out);
-        store8<S, GUARD>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
+        if (keep_history) store8<S, GUARD>(prev, base, n, out);  // becomes g(t) after the caller swaps prev and curr
       };
       const bool whole = t.base + C <= n;
       bool batched = false;
@@ -777,7 +791,7 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
   }
 
   // per-rank telemetry: five atomics per CTA
-  if (p.stats[vr] != nullptr && COMPRESSED && !LEAN) {
+  if (p.stats[vr] != nullptr && COMPRESSED && !LEAN && (pm & 1)) {
     float v[5] = {acc_stats.e2, acc_stats.g2, acc_stats.xp, acc_stats.pp, acc_stats.f2};
 #pragma unroll
     for (int k = 0; k < 5; ++k) {
@@ -801,25 +815,11 @@ cudaError_t launch_mode(const NangilaPredResParams& p, cudaStream_t stream) {
   constexpr int smem = MODE == 0 ? 0 : kWarps * Ring<T, S, LEAN>::BYTES_PER_WARP;
   static_assert(Ring<T, S, LEAN>::D <= kMaxDepth, "ring depth");
   const void* fn = reinterpret_cast<const void*>(&predres_bucket_kernel<T, S, MODE>);
-  static bool configured[64] = {};  // per device: the opt-in for more than 48 KB of shared memory
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
+  // every CTA of a rank must be resident: an owner's wait may depend on a contribution that sits in a
+  // CTA which has not started yet
+  int grid_x = 0;
+  cudaError_t e = clamp_grid(fn, kThreads, size_t(smem), p.grid_x, p.nvr, &grid_x);
   if (e != cudaSuccess) return e;
-  if (smem > 0 && dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured[dev] = true;
-  }
-  int grid_x = p.grid_x;
-  if (p.nvr > 1) {
-    // cooperative launch: every CTA of every emulated rank must be resident at once
-    int per_sm = 0, sms = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem);
-    if (e != cudaSuccess) return e;
-    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
-    grid_x = std::max(1, std::min(grid_x, per_sm * sms / p.nvr));
-  }
   dim3 grid{unsigned(grid_x), unsigned(p.nvr)};
   dim3 block{unsigned(kThreads)};
   void* args[] = {const_cast<NangilaPredResParams*>(&p)};
@@ -883,8 +883,8 @@ extern "C" int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_
   using namespace nangila;
   if (p == nullptr || p->n <= 0 || p->world < 1 || p->world > NANGILA_MAX_RANKS || p->nvr < 1 ||
       p->nvr > NANGILA_MAX_VRANKS || p->rank0 < 0 || p->rank0 + p->nvr > p->world || p->chunk_elems <= 0 ||
-      p->chunk_elems % kElemsPerIter != 0 || p->epoch == 0 || p->grid_x < 1 || p->mode < 0 || p->mode > 2 ||
-      !(p->mu >= 0.0f && p->mu <= 1.0f))
+      p->chunk_elems % kElemsPerIter != 0 || p->epoch == 0 || p->mode < 0 || p->mode > 2 ||
+      !(p->mu >= 0.0f && p->mu <= 1.0f) || p->phase_mask < 0 || p->phase_mask > 7 || p->phase_mask == 5)
     return int(cudaErrorInvalidValue);
   if (p->mode == 2) {
     // reduce-scatter: W equal shards whose length keeps 16-byte vector accesses aligned

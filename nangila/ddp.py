@@ -100,6 +100,17 @@ if CPP_HOOK_AVAILABLE:
                 self._attach(bucket.buffer().device)
             return self.run(bucket)
 
+        def step(self) -> None:
+            """Call once per optimizer step. The kernels' per-bucket statistics are summed over the process
+            group (on the exchange stream, off the critical path) before the gain controller reads them, so
+            every rank derives the same prediction gains; the kernel is told that the gains are uniform and
+            applies its own value in the reconstruction, which is only right if they are."""
+            stats = self.stats_tensor()
+            if stats is not None and self._arena is not None and self._arena.world > 1:
+                with torch.cuda.stream(torch.cuda.ExternalStream(self.stream_ptr(), device=stats.device)):
+                    dist.all_reduce(stats, group=self._arena.group)
+            super().step()
+
 else:  # pragma: no cover
     NangilaCppHook = None
 
@@ -487,12 +498,7 @@ class NangilaDDPHook:
         if self._engine is not None:
             self._engine.end_step()
         if self._cpp is not None:
-            stats = self._cpp.stats_tensor()
-            if stats is not None and self.world_size > 1:
-                # sum the kernels' statistics over the group so that every rank derives the same gains
-                with torch.cuda.stream(torch.cuda.ExternalStream(self._cpp.stream_ptr(), device=stats.device)):
-                    dist.all_reduce(stats, group=self.process_group)
-            self._cpp.step()
+            self._cpp.step()  # sums the kernels' statistics over the group, then adapts the gains
         if self._force_uncompressed:
             self._force_uncompressed = False  # one uncompressed step re-seeded the history everywhere
         if self.step_count % 10 == 0 and self.step_count > self.warmup_steps and _LOG in ("info", "debug"):

@@ -26,12 +26,16 @@ class NangilaFSDPState:
     """State object for ``fsdp_model.register_comm_hook(state, nangila_fsdp_hook)``."""
 
     def __init__(self, process_group: Optional[dist.ProcessGroup], config: Optional[NangilaConfig] = None,
-                 sync_mode: int = 2):
+                 sync_mode: int = 2, *, predictor: bool = False, error_feedback: bool = False):
         self.process_group = process_group if process_group is not None else dist.group.WORLD
         self.config = config if config is not None else NangilaConfig()
         self.sync_mode = _validate_sync_mode(sync_mode)
         self.world_size = dist.get_world_size(self.process_group)
         self.rank = dist.get_rank(self.process_group)
+        # predictor=True: the reference's prediction-residual data flow (full-size history of the averaged gradient
+        # per unit on every rank); default: block-INT4 reduce-scatter without history
+        self.predictor = predictor
+        self.error_feedback = error_feedback
         self._step = 0
         self._calls = 0
         self.stream: Optional[torch.cuda.Stream] = None
@@ -43,10 +47,12 @@ class NangilaFSDPState:
         return self._step
 
     def step(self) -> None:
-        """Advance the step (keys the stochastic rounding); call once per optimizer step."""
+        """Advance the step; call once per optimizer step. The FSDP units reduced by the hook are told apart by
+        their position among the calls of a step (as the reference's ``layer_counter`` did,
+        python/nangila/fsdp.py:50-53,86-87), so this is also what keeps their states apart."""
         self._step += 1
         if self._rs is not None:
-            self._rs.step = self._step
+            self._rs.end_step()
 
     def get_history(self, key: int):
         return self.history.get(key)
@@ -58,7 +64,8 @@ class NangilaFSDPState:
 
     def reduce_scatter(self) -> NangilaReduceScatter:
         if self._rs is None:
-            self._rs = NangilaReduceScatter(group=self.process_group)
+            self._rs = NangilaReduceScatter(group=self.process_group, predictor=self.predictor,
+                                            error_feedback=self.error_feedback, momentum=float(self.config.momentum))
         return self._rs
 
 

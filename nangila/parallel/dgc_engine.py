@@ -16,6 +16,8 @@ import torch
 from .predres_engine import STATUS_MESSAGES, _glue
 from .symm import LoopbackArena, Region
 
+_LIST_CTAS = 444  # CTAs whose equal segments of the candidate list the scratch buffer has slack for
+
 
 @dataclass
 class DGCBucket:
@@ -60,7 +62,8 @@ class DGCEngine:
         self._glue = _glue()
 
     def _grid(self, n: int) -> int:
-        cap = self.ctas or max(1, (148 * 3) // self.nvr)  # cooperative: all CTAs co-resident (3 per SM)
+        # the candidate-list scratch is sized for _LIST_CTAS CTAs; the launcher clamps to what the device can hold at once
+        cap = self.ctas or max(1, _LIST_CTAS // self.nvr)
         return max(1, min(cap, (n + 1023) // 1024))  # 4 elements per thread and pass
 
     def bucket_state(self, index: int, grads: List[torch.Tensor]) -> DGCBucket:
@@ -78,7 +81,7 @@ class DGCEngine:
                        # fixed words + the candidate list (index, bits) of the list-based selection. Unsent entries
                        # pile up just below the threshold (about 17 k of them within 4 % of it), and every CTA owns an
                        # equal segment of the list, hence the slack.
-                       scratch=[z(scratch_words + 2 * (32 * k + 128 * 444), torch.int32) for _ in range(self.nvr)],
+                       scratch=[z(scratch_words + 2 * (32 * k + 128 * _LIST_CTAS), torch.int32) for _ in range(self.nvr)],
                        out_count=[z(2, torch.int32) for _ in range(self.nvr)])
         self.buckets[index] = st
         return st

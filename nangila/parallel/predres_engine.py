@@ -77,6 +77,7 @@ class BucketState:
     cooldown: int = 0
     probe_every: int = 0                # calls between probes of the history while the gain is 0 (0: engine default)
     next_probe: int = 0                 # call number of the next probe
+    last_probe: int = 0                 # call number of the most recent probe
     totals: List[float] = field(default_factory=lambda: [0.0, 0.0, 0.0, 0.0])
     epoch: int = 0
     calls: int = 0
@@ -143,10 +144,8 @@ class PredResEngine:
         want = owned * self.world
         if self.ctas > 0:
             cap = self.ctas
-        elif self.loopback:
-            cap = max(1, (148 * 4) // self.nvr)  # the cooperative launch must be co-resident
         else:
-            cap = 148 * 4
+            cap = 1 << 20  # the launcher clamps to what the device can hold at once (divided by the emulated ranks)
         return max(1, min(want, cap))
 
     def _take_slot(self, index: int) -> int:
@@ -192,32 +191,47 @@ class PredResEngine:
         self.buckets[index] = st
         return st
 
-    def reduce(self, index: int, grads: List[torch.Tensor], compressed: bool, step: int = 0) -> BucketState:
+    def reduce(self, index: int, grads: List[torch.Tensor], compressed: bool, step: int = 0,
+               split_phases: bool = False) -> BucketState:
         """Queue the fused exchange for one bucket. ``grads`` has one tensor per emulated rank (one
-        in a real group). The result overwrites ``grads`` in place; the history advances."""
+        in a real group). The result overwrites ``grads`` in place; the history advances.
+        ``split_phases`` queues the phases of the exchange as separate launches of the same kernel (what
+        the C++ DDP hook does to defer the waiting phases); the result is the same bytes."""
         st = self.bucket_state(index, grads)
         st.epoch += 1
         st.calls += 1
         st.compressed_calls += int(compressed)
-        self.launches += 1
         r1, r2, f1, f2 = st.layout
+        measure = self._probe_due(st)
+        gather = compressed and 2 <= self.world <= self.gather_max_world
+        # While the gain is 0 nothing reads the history except a probe: it is written on the two calls before a
+        # probe and the two after it (until the controller has seen the probe's statistics) and left alone otherwise.
+        skip_history = (compressed and st.pred_gain == 0.0 and st.extra.get("pred_gain_per_rank") is None
+                        and not measure and st.calls + 2 < st.next_probe and st.calls > st.last_probe + 2)
+        if split_phases and self.world > 1:
+            masks = [1, 2] if gather else [1, 2, 4]
+        else:
+            masks = [0]
+        self.launches += len(masks)
         args = dict(
             grad=grads, prev=st.prev, curr=st.curr, ef=st.ef, ef2=st.ef2, stats=st.stats, status=self.status,
             region_ptrs=st.region.ptrs, recv1_off=r1, recv2_off=r2, flag1_off=f1, flag2_off=f2,
             rank0=0 if self.loopback else self.rank, chunk_elems=st.chunk, mode=0 if compressed else 1,
-            stochastic=self.stochastic, measure=self._probe_due(st), epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
+            stochastic=self.stochastic, measure=measure, epoch=st.epoch, seed=self.seed, step=step, bucket_id=index,
             mu=self.momentum, pred_gain=self._gains(st), timeout_s=self.timeout_s, grid_x=self._grid(st),
             uniform_gain=st.extra.get("pred_gain_per_rank") is None,
-            gather=compressed and 2 <= self.world <= self.gather_max_world,
+            gather=gather, skip_history=skip_history,
         )
         if self.nvtx:
             torch.cuda.nvtx.range_push(f"nangila.bucket{index}.{'int4' if compressed else 'exact'}")
         if self.stream is not None:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.stream):
-                self._timed_launch(index, args)
+                for m in masks:
+                    self._timed_launch(index, dict(args, phase_mask=m))
         else:
-            self._timed_launch(index, args)
+            for m in masks:
+                self._timed_launch(index, dict(args, phase_mask=m))
         if self.nvtx:
             torch.cuda.nvtx.range_pop()
         st.swap()
@@ -252,6 +266,7 @@ class PredResEngine:
             st.next_probe = st.probe_every
         if st.calls < st.next_probe:
             return False
+        st.last_probe = st.calls
         st.next_probe = st.calls + st.probe_every
         return True
 
@@ -329,6 +344,25 @@ class PredResEngine:
                 raise RuntimeError(
                     f"nangila: fused exchange failed on rank {w[1]} ({STATUS_MESSAGES.get(w[0], 'code %d' % w[0])}); "
                     f"waiting for rank {w[2]}, epoch {w[3]} (last seen {w[4]}), phase {w[5]}, chunk {w[6]}")
+
+    def resync(self) -> None:
+        """Recovery after a failed exchange (``check_status`` raised on some rank, or a rank skipped a
+        call): every rank must call this at the same point. The ranks agree on the highest epoch any of
+        them reached for each bucket (one small MAX all-reduce through the process group), so the next
+        launch uses the same, fresh epoch everywhere and no flag left over from the failed exchange can
+        satisfy it; the status blocks are cleared. The caller should make the next call on every bucket
+        an uncompressed one, which re-seeds the history on all ranks (what the DDP hook does)."""
+        if self.stream is not None:
+            self.stream.synchronize()
+        for s_ in self.status:
+            s_.zero_()
+        if self.loopback or self.world == 1 or not self.buckets:
+            return
+        keys = sorted(self.buckets)
+        ep = torch.tensor([self.buckets[k].epoch + 1 for k in keys], dtype=torch.int64, device=self.device)
+        dist.all_reduce(ep, op=dist.ReduceOp.MAX, group=getattr(self.arena, "group", None))
+        for k, e in zip(keys, ep.tolist()):
+            self.buckets[k].epoch = int(e)
 
     def prediction_error(self, index: int) -> float:
         """sqrt(sum e^2 / sum g^2) accumulated over the compressed calls of a bucket (rank 0's view)."""

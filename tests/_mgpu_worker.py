@@ -1,5 +1,7 @@
 """Multi-GPU worker (one process per GPU, launched by torch.distributed.run): checks the fused
-exchange over real peer memory against NCCL, and DDP loss parity with and without the hook."""
+exchange over real peer memory against NCCL and against a PyTorch restatement of the kernel's own
+arithmetic, byte equality of the replicas, the C++ hook driven directly, recovery after a withheld
+launch, and DDP / FSDP2 loss parity with and without the hooks."""
 import json
 import os
 import sys
@@ -8,48 +10,197 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from _refmath import ref_quantize  # noqa: E402
+
+
+def same_bytes(t: torch.Tensor, world: int) -> bool:
+    """True when every rank holds exactly the same bytes in ``t`` (CRC32 computed on the device)."""
+    from nangila.ops.reductions import crc32
+
+    mine = torch.tensor([crc32(t.contiguous())], dtype=torch.int64, device=t.device)
+    allc = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(allc, mine)
+    return all(torch.equal(a, allc[0]) for a in allc)
+
+
+def gather_all(t: torch.Tensor, world: int):
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t.contiguous())
+    return out
 
 
 def check_exchange(dev, rank, world, results):
+    """Exact mode against NCCL; compressed mode (round to nearest, no error memory, gain 1) against
+    ``pred + mean_r deq(Q(g_r - pred))`` in gather mode and ``pred + deq(Q(mean_r deq(Q(g_r - pred))))`` in
+    the three-phase form, within one quantization step for a few ties and exactly otherwise."""
     from nangila.parallel.predres_engine import PredResEngine
     from nangila.parallel.symm import SymmArena
 
     arena = SymmArena(None, dev)
-    eng = PredResEngine(arena, dev, stochastic=True, error_feedback=True, adaptive_gain=False)
     results["provider"] = arena.provider
-    for dtype in (torch.float32, torch.bfloat16):
-        for n in (4096 * 3 + 5, 1 << 20, 5_000_000):
-            idx = hash((str(dtype), n)) % 1000
-            torch.manual_seed(100 + rank)
-            g = (torch.randn(n, device=dev) * 0.01).to(dtype)
-            want = g.float().clone()
-            dist.all_reduce(want)
-            want /= world
-            mine = g.clone()
-            eng.reduce(idx, [mine], compressed=False)
+    variants = [("default", None, False)]
+    if world <= 4:
+        variants.append(("three_phase", 1, False))  # force the 8-GPU product path over real peers
+    variants.append(("split", None, True))          # per-phase launches, as the C++ hook queues them
+    bucket = 0
+    outputs = {}
+    for name, gather_max, split in variants:
+        eng = PredResEngine(arena, dev, stochastic=False, error_feedback=False, adaptive_gain=False)
+        if gather_max is not None:
+            eng.gather_max_world = gather_max
+        gather = 2 <= world <= eng.gather_max_world
+        for dtype in (torch.float32, torch.bfloat16):
+            for n in (4096 * 3 + 5, 1 << 20, 3_000_000):
+                bucket += 1
+                torch.manual_seed(100 + rank)
+                g = (torch.randn(n, device=dev) * 0.01).to(dtype)
+                want = g.float().clone()
+                dist.all_reduce(want)
+                want /= world
+                mine = g.clone()
+                eng.reduce(bucket, [mine], compressed=False)
+                eng.check_status()
+                err = (mine.float() - want).abs().max().item()
+                tol = 1e-6 if dtype == torch.float32 else 8e-3 * want.abs().max().item() + 2e-4
+                assert err <= tol, (name, dtype, n, err)
+                assert same_bytes(mine, world), f"ranks disagree (uncompressed, {name})"
+                # compressed step: history is {0, mine}; gain 1
+                pred = mine.float() * (1.0 + eng.momentum)
+                g2 = (pred + torch.randn(n, device=dev) * 0.002).to(dtype)
+                inputs = gather_all(g2, world)
+                mine2 = g2.clone()
+                eng.reduce(bucket, [mine2], compressed=True, step=1, split_phases=split)
+                eng.check_status()
+                assert same_bytes(mine2, world), f"ranks disagree (compressed, {name})"
+                acc = torch.zeros(n, device=dev)
+                smax = None
+                for gi in inputs:
+                    deq, sc = ref_quantize(gi.float() - pred)
+                    acc += deq
+                    smax = sc if smax is None else torch.maximum(smax, sc)
+                if gather:
+                    deq2, scale2 = acc / world, smax
+                else:
+                    deq2, scale2 = ref_quantize(acc / world)
+                wanted = pred + deq2
+                got = mine2.float()
+                step_size = scale2.repeat_interleave(64)[:n]
+                exact_tol = 2e-6 if dtype == torch.float32 else 4e-3 * wanted.abs() + 1e-5
+                e = (got - wanted).abs()
+                assert bool((e <= step_size * 1.01 + exact_tol).all()), (name, dtype, n, e.max().item())
+                frac = (e > exact_tol).float().mean().item()
+                assert frac < 5e-3, (name, dtype, n, frac)
+                outputs[(name, str(dtype), n)] = mine2.clone()
+                results[f"ties_{name}_{str(dtype)[6:]}_{n}"] = frac
+    # per-phase launches reproduce the fused launch bit for bit
+    for (name, dt, n), t in outputs.items():
+        if name == "split":
+            assert torch.equal(t, outputs[("default", dt, n)]), ("split differs", dt, n)
+
+
+def check_nonfinite(dev, rank, world, results):
+    """NaN / Inf / denormal inputs on one rank: the kernels sanitise them to zero, the result is finite and
+    identical everywhere, in both the exact and the compressed mode."""
+    from nangila.parallel.predres_engine import PredResEngine
+    from nangila.parallel.symm import SymmArena
+
+    eng = PredResEngine(SymmArena(None, dev), dev, stochastic=False, error_feedback=True, adaptive_gain=False)
+    n = 4096 * 7 + 33
+    for step, compressed in enumerate((False, True, True)):
+        torch.manual_seed(7 + rank)
+        g = (torch.randn(n, device=dev) * 0.01).to(torch.bfloat16)
+        if rank == world - 1:
+            g[5] = float("nan")
+            g[4096 + 3] = float("inf")
+            g[2 * 4096 + 9] = float("-inf")
+            g[77] = 1e-40
+        eng.reduce(900, [g], compressed=compressed, step=step)
+        eng.check_status()
+        assert bool(torch.isfinite(g.float()).all()), f"non-finite output (step {step})"
+        assert same_bytes(g, world)
+    results["nonfinite_ok"] = True
+
+
+def check_cpp_hook(dev, rank, world, results):
+    """The C++ hook driven directly with different data per rank on a slowly drifting gradient: the gain
+    controller must switch the predictor on, every rank must hold the same gains and the same bytes."""
+    from nangila.ddp import NangilaCppHook
+
+    hook = NangilaCppHook(num_layers=4, warmup_steps=2)
+    n = 1 << 20
+    torch.manual_seed(3)
+    base = torch.randn(n, device=dev) * 0.02           # same on every rank
+    drift = torch.randn(n, device=dev) * 0.002
+    hook._attach(dev)
+    gains = []
+    for step in range(40):
+        futs, grads = [], []
+        for index in range(3):
+            torch.manual_seed(1000 * step + 10 * index + rank)
+            noise = torch.randn(n, device=dev) * 0.0005  # differs per rank
+            g = ((base + drift * step) * (1 + 0.1 * index) + noise).to(torch.bfloat16)
+            # a bucket's future completes only when a later bucket (or the last one) has been queued
+            futs.append(hook.run_tensor(index, g, index == 2))
+            grads.append(g)
+        for fut in futs:
+            fut.wait()
+        torch.cuda.current_stream().synchronize()
+        if step in (5, 20, 39):
+            for index, g in enumerate(grads):
+                assert same_bytes(g, world), f"replicas differ at step {step}, bucket {index}"
+        hook.step()
+        gains.append([hook.get_stats()["prediction_gain"][i] for i in range(3)])
+    hook.check_status()
+    mine = torch.tensor(gains[-1], dtype=torch.float64, device=dev)
+    allg = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(allg, mine)
+    assert all(torch.equal(a, allg[0]) for a in allg), f"prediction gains differ across ranks: {allg}"
+    results["cpp_hook_gains"] = gains[-1]
+    results["cpp_hook_launches"] = hook.get_kernel_launches()
+    assert min(gains[-1]) > 0.2, f"the predictor stayed off on a drifting gradient: {gains[-1]}"
+    for index in range(3):
+        st = hook.bucket_state(index)
+        assert same_bytes(st["curr"], world) and same_bytes(st["prev"], world)
+
+
+def check_withheld_rank(dev, rank, world, results):
+    """One rank skips a launch (a host-side failure: nothing faults on the device). The other ranks' bounded
+    waits expire, their kernels report what they were waiting for and return; the ranks then agree on the
+    outcome over NCCL, resynchronise the epochs and the next exchange works."""
+    from nangila.parallel.predres_engine import PredResEngine
+    from nangila.parallel.symm import SymmArena
+
+    eng = PredResEngine(SymmArena(None, dev), dev, stochastic=False, error_feedback=False, adaptive_gain=False,
+                        timeout_s=0.5)
+    n = 4096 * 9
+    g = torch.full((n,), float(rank + 1), device=dev)
+    eng.reduce(950, [g], compressed=False)
+    eng.check_status()
+    assert torch.allclose(g, torch.full_like(g, (world + 1) / 2))
+    g = torch.full((n,), float(rank + 1), device=dev)
+    failed = 0
+    if rank != world - 1:                      # the last rank withholds its launch
+        eng.reduce(950, [g], compressed=False)
+        try:
             eng.check_status()
-            tol = 1e-6 if dtype == torch.float32 else 2e-4
-            err = (mine.float() - want).abs().max().item()
-            assert err <= tol + 8e-3 * want.abs().max().item() * (dtype == torch.bfloat16), (dtype, n, err)
-            # every rank holds the same bytes
-            chk = mine.float().sum().double().reshape(1)
-            allc = [torch.zeros_like(chk) for _ in range(world)]
-            dist.all_gather(allc, chk)
-            assert all(torch.equal(a, allc[0]) for a in allc), "ranks disagree (uncompressed)"
-            # compressed step: bounded error against the exact mean, identical on all ranks
-            g2 = (want + torch.randn(n, device=dev) * 0.002).to(dtype)
-            want2 = g2.float().clone()
-            dist.all_reduce(want2)
-            want2 /= world
-            mine2 = g2.clone()
-            eng.reduce(idx, [mine2], compressed=True, step=1)
-            eng.check_status()
-            rel = ((mine2.float() - want2).norm() / want2.norm()).item()
-            assert rel < 0.2, (dtype, n, rel)
-            chk = mine2.float().sum().double().reshape(1)
-            dist.all_gather(allc, chk)
-            assert all(torch.equal(a, allc[0]) for a in allc), "ranks disagree (compressed)"
-            results[f"rel_err_{str(dtype)[6:]}_{n}"] = rel
+        except RuntimeError as exc:
+            failed = 1
+            assert "timeout" in str(exc), str(exc)
+    flag = torch.tensor([failed], device=dev)
+    dist.all_reduce(flag)                      # the context is still usable: NCCL runs
+    assert int(flag.item()) == world - 1, f"{int(flag.item())} ranks saw the timeout, expected {world - 1}"
+    eng.resync()
+    g = torch.full((n,), float(rank + 1), device=dev)
+    dist.all_reduce(g)                         # the fallback for the failed bucket
+    g /= world
+    assert torch.allclose(g, torch.full_like(g, (world + 1) / 2))
+    g2 = torch.full((n,), float(2 * rank), device=dev)
+    eng.reduce(950, [g2], compressed=False)
+    eng.check_status()
+    assert torch.allclose(g2, torch.full_like(g2, float(world - 1))), g2[:4]
+    results["withheld_rank_recovered"] = True
 
 
 def train(dev, rank, world, use_hook, steps, compressor_type=0, prefer_cpp=True):
@@ -88,15 +239,13 @@ def train(dev, rank, world, use_hook, steps, compressor_type=0, prefer_cpp=True)
     out = torch.stack(losses).float()
     dist.all_reduce(out)
     out /= world
-    p0 = next(model.parameters()).detach().float().sum().double().reshape(1)
-    allp = [torch.zeros_like(p0) for _ in range(world)]
-    dist.all_gather(allp, p0)
-    assert all(torch.equal(a, allp[0]) for a in allp), "model replicas diverged"
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    assert same_bytes(flat, world), "model replicas diverged"
     stats = hook.get_stats() if hook is not None else None
     return out.tolist(), stats
 
 
-def train_fsdp(dev, rank, world, compress, steps):
+def train_fsdp(dev, rank, world, compress, steps, **kw):
     """FSDP2 on a tiny Llama: per-block fully_shard, bf16 mixed precision, optional fused collectives."""
     from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
@@ -111,7 +260,7 @@ def train_fsdp(dev, rank, world, compress, steps):
     fully_shard(model, mp_policy=mp)
     rs = ag = None
     if compress:
-        rs, ag = apply_nangila_fsdp(model, parameter_bits=8)
+        rs, ag = apply_nangila_fsdp(model, parameter_bits=8, **kw)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
     gen = torch.Generator().manual_seed(7)
     data = torch.randint(0, 64, (64, 33), generator=gen)
@@ -123,8 +272,6 @@ def train_fsdp(dev, rank, world, compress, steps):
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
-        if rs is not None:
-            rs.step += 1
         losses.append(loss.detach())
     out = torch.stack(losses).float()
     dist.all_reduce(out)
@@ -133,7 +280,8 @@ def train_fsdp(dev, rank, world, compress, steps):
     if compress:
         rs.check_status()
         ag.check_status()
-        info = {"rs_launches": rs.launches, "ag_launches": ag.launches, "fallbacks": rs.fallbacks + ag.fallbacks}
+        info = {"rs_launches": rs.launches, "ag_launches": ag.launches, "fallbacks": rs.fallbacks + ag.fallbacks,
+                "rs_steps": rs.step, "rs_units": rs.units_seen}
     return out.tolist(), info
 
 
@@ -149,6 +297,11 @@ def main():
     results = {"world": world}
     if what in ("all", "exchange"):
         check_exchange(dev, rank, world, results)
+        check_nonfinite(dev, rank, world, results)
+    if what in ("all", "cpphook"):
+        check_cpp_hook(dev, rank, world, results)
+    if what in ("all", "failure"):
+        check_withheld_rank(dev, rank, world, results)
     if what in ("all", "train"):
         base, _ = train(dev, rank, world, False, 60)
         ours, stats = train(dev, rank, world, True, 60)
@@ -161,9 +314,10 @@ def main():
         py_losses, py_stats = train(dev, rank, world, True, 60, prefer_cpp=False)
         results["loss_ours_python_hook"] = sum(py_losses[-10:]) / 10
         assert not py_stats.get("cpp_hook") and py_stats["kernel_launches"] > 0
-        assert abs(results["loss_ours_python_hook"] - results["loss_base"]) < 0.15 * results["loss_base"] + 0.05, results
         assert results["loss_base"] < 0.8 * base[0], "baseline did not learn"
-        assert abs(results["loss_ours"] - results["loss_base"]) < 0.15 * results["loss_base"] + 0.05, results
+        tol = float(os.environ.get("NANGILA_TEST_LOSS_TOL", "0.03"))
+        assert abs(results["loss_ours_python_hook"] - results["loss_base"]) < tol * results["loss_base"] + 0.02, results
+        assert abs(results["loss_ours"] - results["loss_base"]) < tol * results["loss_base"] + 0.02, results
     if what in ("all", "compressors"):
         base, _ = train(dev, rank, world, False, 60)
         for ctype, name in ((1, "dgc"), (2, "powersgd")):
@@ -179,8 +333,9 @@ def main():
         results["fsdp_loss_ours"] = sum(ours[-10:]) / 10
         results["fsdp"] = info
         assert results["fsdp_loss_base"] < 0.8 * base[0], "FSDP baseline did not learn"
-        assert abs(results["fsdp_loss_ours"] - results["fsdp_loss_base"]) < 0.2 * results["fsdp_loss_base"] + 0.05, results
+        assert abs(results["fsdp_loss_ours"] - results["fsdp_loss_base"]) < 0.05 * results["fsdp_loss_base"] + 0.05, results
         assert info["rs_launches"] > 0 and info["ag_launches"] > 0
+        assert info["rs_steps"] >= 59, info  # the rounding key advances by itself, once per backward
     if rank == 0:
         print("MGPU_RESULT " + json.dumps(results), flush=True)
         if out_path:

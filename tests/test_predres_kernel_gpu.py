@@ -16,25 +16,12 @@ def _engine(world, **kw):
     return PredResEngine(LoopbackArena(world, dev), dev, **kw)
 
 
-def _bf16_ceil(x):
-    """Smallest bf16 >= x for x >= 0 (as float32)."""
-    b = x.float().view(torch.int32)
-    b = ((b + 0xFFFF) >> 16) << 16
-    return b.view(torch.float32)
+from _refmath import bf16_ceil as _bf16_ceil  # noqa: E402
+from _refmath import ref_quantize as _ref_quantize  # noqa: E402
 
 
 def ref_quantize(e, nearest=True):
-    """Block-64 INT4: scale = bf16_ceil(amax * fl32(1/7)), q = floor(e/scale + 0.5) clamped to [-8, 7]."""
-    n = e.numel()
-    pad = (-n) % 64
-    x = torch.cat([e.float(), e.new_zeros(pad, dtype=torch.float32)]).view(-1, 64)
-    amax = x.abs().amax(dim=1, keepdim=True)
-    s = _bf16_ceil(amax * 0.14285715)
-    live = s > 1e-30
-    inv = torch.where(live, 1.0 / s, torch.zeros_like(s))
-    q = torch.floor(x * inv + 0.5).clamp_(-8, 7)
-    deq = torch.where(live, q * s, torch.zeros_like(q))
-    return deq.view(-1)[:n], s.view(-1)
+    return _ref_quantize(e)
 
 
 @pytest.mark.parametrize("world", [1, 2, 4])
@@ -274,3 +261,67 @@ def test_cpp_hook_matches_python_engine_on_one_gpu(monkeypatch):
     finally:
         if created:
             dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("gain", [0.0, 1.0])
+def test_split_phase_launches_give_the_same_bytes(world, gain):
+    """The phases of one exchange queued as separate launches (what the C++ DDP hook does to defer the
+    waiting phases) must reproduce the fused launch bit for bit: same gradients, history and error memory."""
+    n = 4096 * 11 + 300
+    results = []
+    for split in (False, True):
+        eng = _engine(world, stochastic=False, error_feedback=True)
+        torch.manual_seed(11)
+        for step in range(2):
+            grads = [(torch.randn(n, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(world)]
+            eng.reduce(0, grads, compressed=False, step=step)
+        eng.buckets[0].pred_gain = gain
+        outs = []
+        for step in range(2, 5):
+            grads = [(torch.randn(n, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(world)]
+            eng.reduce(0, grads, compressed=True, step=step, split_phases=split)
+            outs.append(grads[0].clone())
+        eng.check_status()
+        st = eng.buckets[0]
+        results.append((outs, st.curr[0].clone(), st.prev[0].clone(), st.ef[0].clone()))
+        for g in grads[1:]:
+            assert torch.equal(g, grads[0])
+    (o0, c0, p0, e0), (o1, c1, p1, e1) = results
+    for a, b in zip(o0, o1):
+        assert torch.equal(a, b)
+    assert torch.equal(c0, c1) and torch.equal(p0, p1) and torch.equal(e0, e1)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_history_is_skipped_only_where_nothing_reads_it(world):
+    """With a zero gain the kernel may leave the history unwritten between probes. The gradients it
+    returns must not depend on that, and the history must be current again by the time a probe reads it."""
+    n = 4096 * 6 + 40
+    runs = []
+    for probe_every in (8, 1):  # 1: every call is a probe, so the history is always written
+        eng = _engine(world, stochastic=False, error_feedback=True, adaptive_gain=True)
+        eng.probe_every = probe_every
+        torch.manual_seed(5)
+        outs = []
+        skipped = 0
+        for step in range(20):
+            grads = [(torch.randn(n, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(world)]
+            st = eng.buckets.get(0)
+            if st is not None:
+                st.pred_gain = 0.0
+                st.probe_every = probe_every  # keep the spacing fixed for the test
+            eng.reduce(0, grads, compressed=step >= 2, step=step)
+            st = eng.buckets[0]
+            outs.append(grads[0].clone())
+            # curr (after the swap) holds this step's result unless the write was skipped
+            skipped += int(not torch.equal(st.curr[0].float(), grads[0].float()))
+            if probe_every > 1 and step >= 2 and st.calls + 1 >= st.next_probe:
+                # the next call is a probe: both history entries must be the last two results
+                assert torch.equal(st.curr[0].float(), outs[-1].float())
+                assert torch.equal(st.prev[0].float(), outs[-2].float())
+        eng.check_status()
+        runs.append((outs, skipped))
+    for a, b in zip(runs[0][0], runs[1][0]):
+        assert torch.equal(a, b)
+    assert runs[1][1] == 0 and runs[0][1] > 0
