@@ -653,7 +653,7 @@ PYBIND11_MODULE(_C, m) {
       .value("Normal", RecoveryMode::Normal)
       .value("Pending", RecoveryMode::Pending)
       .value("Active", RecoveryMode::Active);
-  py::class_<NangilaHook>(m, "NangilaHook")
+  py::class_<NangilaHook>(m, "NangilaHook", py::dynamic_attr())  // instances carry their device state (gpu_methods.py)
       .def(py::init([](const py::bytes& mask_bytes, py::object config) {
              auto v = from_bytes(mask_bytes);
              TopologyMask mk = TopologyMask::from_bytes(v.data(), v.size());

@@ -46,6 +46,27 @@ uint64_t nangila_predictor_hash(NangilaHandle handle);
 /* Upper bound of a packet for `count` FP32 values: 16 + 12 + 4 * count + 32. */
 size_t nangila_max_compressed_size(size_t count);
 
+/* ---- tensors that live on the GPU (reference: ffi.rs:526-840; argument order kept) ----------------------------
+ * The caller owns the two-step history (`g_current`, `g_previous`: FP32 device buffers of `count` elements) and
+ * updates it after the all-reduce, as with the reference. The kernels come from libnangila_kernels.so, bound
+ * at the first call (it sits next to this module; NANGILA_KERNELS_LIB overrides); without it the calls return
+ * an error code.
+ *
+ * compress: writes the payload (host wire format: block-64 scales, gain derived on the device) to
+ * `out_compressed_payload` (device, 4-byte aligned, nangila_gpu_payload_size(count) bytes) and the 32-byte packet
+ * header, with the payload's CRC32, to `out_header_cpu` (host). `*out_compressed_size` = 32 + payload bytes.
+ * `scratch_ptr`: 4 bytes of device memory. The call ends with a stream synchronisation (the checksum has to reach
+ * the host header). Payloads above 64 MiB (the fixed size of the checksum kernel's device table) are refused.
+ * decompress: `compressed` is the whole packet in device memory (header, then payload). Header and checksum are
+ * verified before anything is launched (sync_mode 0 skips the checksum); sync_mode 1 also waits for the kernel. */
+size_t nangila_gpu_payload_size(size_t count);
+int32_t nangila_compress_gpu(NangilaHandle handle, const float* gradient, const float* g_current, const float* g_previous,
+                             size_t count, uint32_t layer_id, uint8_t* out_compressed_payload, size_t* out_compressed_size,
+                             uint8_t* out_header_cpu, void* stream, uint32_t* scratch_ptr, int32_t sync_mode);
+int32_t nangila_decompress_gpu(NangilaHandle handle, const uint8_t* compressed, size_t compressed_size,
+                               const float* g_current, const float* g_previous, uint32_t layer_id, float* recvbuff,
+                               size_t count, void* stream, uint32_t* scratch_ptr, int32_t sync_mode);
+
 void nangila_enable_safe_mode(NangilaHandle handle, float divergence_threshold, size_t check_interval,
                               uint32_t max_consecutive_failures, size_t recovery_cooldown);
 /* 0 Continue, 1 TriggerFallback, 2 RecoveryComplete, 3 NoCheck, 4 CanaryTest */

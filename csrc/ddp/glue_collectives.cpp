@@ -106,6 +106,39 @@ at::Tensor crc32_device(const at::Tensor& t) {
                "crc32");
   return out;
 }
+// ---- device-side packet codec (host wire format) -------------------------------------------------------------
+int64_t packet_payload_bytes(int64_t n) { return nangila_packet_payload_bytes(n); }
+// Encodes `grad` into payload[0 : packet_payload_bytes(n)] (uint8, 4-byte aligned). gain < 0: derive kappa on the device.
+void packet_encode(const at::Tensor& grad, const c10::optional<at::Tensor>& curr, const c10::optional<at::Tensor>& prev,
+                   const c10::optional<at::Tensor>& ef, double mu, double gain, at::Tensor payload) {
+  TORCH_CHECK(grad.is_cuda() && grad.is_contiguous(), "nangila: packet_encode wants a contiguous CUDA gradient");
+  const int64_t n = grad.numel();
+  TORCH_CHECK(payload.is_cuda() && payload.scalar_type() == at::kByte && payload.is_contiguous() &&
+                  payload.numel() >= nangila_packet_payload_bytes(n), "nangila: payload buffer too small");
+  auto f32 = [&](const c10::optional<at::Tensor>& t, const char* what) -> float* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == n, "nangila: ", what,
+                " must be a contiguous FP32 CUDA tensor of the gradient's size");
+    return t->data_ptr<float>();
+  };
+  c10::cuda::CUDAGuard guard(grad.device());
+  check_launch(nangila_packet_encode(grad.data_ptr(), dtype_code(grad), f32(curr, "curr"), f32(prev, "prev"), f32(ef, "ef"),
+                                     float(mu), float(gain), n, payload.data_ptr<uint8_t>(), at::cuda::getCurrentCUDAStream()),
+               "packet_encode");
+}
+void packet_decode(const at::Tensor& payload, int64_t ndim, const c10::optional<at::Tensor>& curr,
+                   const c10::optional<at::Tensor>& prev, double mu, double gain, at::Tensor out) {
+  TORCH_CHECK(payload.is_cuda() && payload.scalar_type() == at::kByte && payload.is_contiguous(), "nangila: payload must be uint8 CUDA");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous(), "nangila: out must be FP32 CUDA");
+  const int64_t n = out.numel();
+  const float* c = curr.has_value() ? curr->data_ptr<float>() : nullptr;
+  const float* p = prev.has_value() ? prev->data_ptr<float>() : nullptr;
+  if (c) TORCH_CHECK(curr->numel() == n && prev.has_value() && prev->numel() == n, "nangila: history size mismatch");
+  c10::cuda::CUDAGuard guard(out.device());
+  check_launch(nangila_packet_decode(payload.data_ptr<uint8_t>(), payload.numel(), int32_t(ndim), c, p, float(mu), float(gain), n,
+                                     out.data_ptr<float>(), at::cuda::getCurrentCUDAStream()), "packet_decode");
+}
+
 // returns (float[4] = {max|x|, k-th largest |x|, gamma, non-finite count}, int32[256] histogram of |x|/max)
 py::tuple absmax_hist(const at::Tensor& x, int64_t k, double qmax) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "nangila: absmax_hist wants a contiguous CUDA tensor");
@@ -377,6 +410,11 @@ void psgd_exchange(const std::vector<at::Tensor>& local, const std::vector<at::T
 }  // namespace
 
 void register_more(py::module_& m) {
+  m.def("packet_payload_bytes", &packet_payload_bytes);
+  m.def("packet_encode", &packet_encode, py::arg("grad"), py::arg("curr"), py::arg("prev"), py::arg("ef"), py::arg("mu"),
+        py::arg("gain"), py::arg("payload"));
+  m.def("packet_decode", &packet_decode, py::arg("payload"), py::arg("ndim"), py::arg("curr"), py::arg("prev"), py::arg("mu"),
+        py::arg("gain"), py::arg("out"));
   m.def("dgc_region_layout", &dgc_region_layout);
   m.def("dgc_launch", &dgc_launch, py::arg("grad"), py::arg("u"), py::arg("v"), py::arg("scratch"), py::arg("status"),
         py::arg("out_count"), py::arg("region_ptrs"), py::arg("recv_off"), py::arg("flag_off"), py::arg("rank0"),

@@ -12,7 +12,7 @@
 
 namespace nangila {
 
-// Also opts the kernel in to `smem` bytes of dynamic shared memory when that exceeds the 48 KB default.
+// Also opts the kernel in to `smem` bytes of dynamic shared memory.
 inline cudaError_t resident_ctas(const void* fn, int threads, size_t smem, int* out) {
   static std::mutex mu;
   static std::map<std::pair<const void*, int>, int> cache;
@@ -25,7 +25,7 @@ inline cudaError_t resident_ctas(const void* fn, int threads, size_t smem, int* 
     *out = it->second;
     return cudaSuccess;
   }
-  if (smem > 48 * 1024) {
+  if (smem > 0) {  // static shared memory counts towards the 48 KB default limit too: always opt in
     e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
   }

@@ -191,6 +191,25 @@ int nangila_predict_quantize_gamma(const float* grad, const float* g_curr, const
 int nangila_dequant_reconstruct_gamma(const uint8_t* packed, const float* g_curr, const float* g_prev, float mu,
                                       float gamma, float* out, int64_t n, cudaStream_t stream);
 
+/* ---- device-side packet codec in the host core's wire format (packet_codec.cu) ---------------------------
+ * payload = f32 -64 | u32 numel | u32 ndim = 1 | u32 numel | f32 kappa | f32 scale[ceil(n/64)] | u8 packed[ceil(n/2)].
+ * encode: x = grad + ef - kappa (curr + mu (curr - prev)); scale = amax / 7 per 64 elements; round to nearest; ef <- x - q scale.
+ * gain >= 0 fixes kappa; gain < 0 derives it on the device as clip(<grad + ef, g_hat> / <g_hat, g_hat>, 0, 1) (no
+ * scratch needed: the sums sit in the payload's first bytes until the encoder has read them). curr / prev / ef are
+ * FP32 and may be NULL (no history: kappa = 0; no error memory). `payload` must be 4-byte aligned and hold
+ * nangila_packet_payload_bytes(n) bytes. */
+int64_t nangila_packet_payload_bytes(int64_t n);
+int nangila_packet_encode(const void* grad, int32_t dtype, const float* curr, const float* prev, float* ef, float mu,
+                          float gain, int64_t n, uint8_t* payload, cudaStream_t stream);
+/* decode: out = q scale + kappa (curr + mu (curr - prev)); gain < 0 takes kappa from the payload. `ndim` is the
+ * payload's dimension count (its third word), which fixes where the gain, scales and nibbles start. */
+int nangila_packet_decode(const uint8_t* payload, int64_t payload_bytes, int32_t ndim, const float* curr, const float* prev,
+                          float mu, float gain, int64_t n, float* out, cudaStream_t stream);
+/* runtime helpers for callers that bind this library without linking the CUDA runtime themselves */
+int nangila_copy_to_host(void* dst, const void* src, int64_t nbytes, cudaStream_t stream);   /* copies, then synchronises */
+int nangila_copy_to_device(void* dst, const void* src, int64_t nbytes, cudaStream_t stream); /* asynchronous */
+int nangila_stream_sync(cudaStream_t stream);
+
 /* ---- fused softmax cross-entropy over bf16 logits with padded columns (fused_ce.cu) ---------------- */
 int nangila_ce_forward(const void* logits, const int64_t* targets, float* losses, float* lse, int64_t rows, int v, int64_t stride,
                        cudaStream_t stream);

@@ -48,6 +48,9 @@ def cuda_available() -> bool:
 
 
 from .ddp import CPP_HOOK_AVAILABLE, NangilaCppHook, NangilaDDPHook, register_nangila_hook  # noqa: E402
+from . import gpu_methods as _gpu_methods  # noqa: E402
+
+_gpu_methods.install()  # NangilaHook.compress_gpu / decompress_gpu / update_gpu
 
 
 def __getattr__(name):

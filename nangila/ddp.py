@@ -37,7 +37,7 @@ import torch
 import torch.distributed as dist
 from torch.nn.parallel import DistributedDataParallel as DDP
 
-from ._C import CompressorType, NangilaConfig, NangilaHook, SyncMode
+from ._C import CompressorType, MetricsCollector, NangilaConfig, NangilaHook, SyncMode
 
 NANGILA_AVAILABLE = True
 
@@ -211,6 +211,11 @@ class NangilaDDPHook:
         self._packet_filter = None   # tests: callable(step, layer_id, src_rank, bytes) -> bytes
         self._cpp = None             # NangilaCppHook once the first CUDA bucket went through it
         self._param_ids: Dict[int, int] = {}
+        # production counters (Prometheus text / JSON): fed once per step from the byte counters of whichever
+        # path handled the buckets (reference: nangila-core/src/metrics.rs:12-232)
+        self._metrics = MetricsCollector()
+        self._metrics_bytes = (0, 0)
+        self._metrics_failures = 0
         _log(f"DDP hook: sync_mode={SyncMode(self.sync_mode)!r} compressor={self.compressor_type} "
              f"warmup={self.warmup_steps} world={self.world_size}")
 
@@ -364,6 +369,7 @@ class NangilaDDPHook:
             # leave the hook usable: the next buckets go through the uncompressed mode and re-seed
             # the history on every rank (FORCE_SYNC semantics of the packet protocol)
             self._force_uncompressed = True
+            self._metrics.record_fallback()
             for lid in range(min(10, self.hook.get_stats()["num_drivers"])):
                 self.hook.trigger_recovery(lid)
             raise
@@ -492,6 +498,7 @@ class NangilaDDPHook:
     # ------------------------------------------------------------------------------------------
     def step(self) -> None:
         """Call after each optimizer step."""
+        self._feed_metrics(self.compressing)
         self.step_count += 1
         self.layer_counter = 0
         self.hook.step()
@@ -508,6 +515,30 @@ class NangilaDDPHook:
                      f"{self.total_compressed_bytes / 1e6:.1f} MB ({ratio:.1f}x)")
         if self.step_count % 100 == 0 and self.step_count > 0:
             self._verify_predictor_hash()
+
+    def _byte_counters(self) -> tuple:
+        """(bytes the buckets held, bytes that would cross the wire per peer) so far, whichever path ran."""
+        if self._cpp is not None:
+            native = self._cpp.get_stats()
+            return int(native["total_original_bytes"]), int(native["total_compressed_bytes"])
+        return int(self.total_original_bytes), int(self.total_compressed_bytes)
+
+    def _feed_metrics(self, compressed: bool) -> None:
+        orig, comp = self._byte_counters()
+        d_orig, d_comp = orig - self._metrics_bytes[0], comp - self._metrics_bytes[1]
+        self._metrics_bytes = (orig, comp)
+        if d_orig > 0 or d_comp > 0:
+            self._metrics.record_bytes(max(d_orig, 0), max(d_comp, 0))
+        self._metrics.record_step(bool(compressed))
+        while self._metrics_failures < self.recovered_failures:
+            self._metrics.record_fallback()
+            self._metrics_failures += 1
+
+    def metrics(self) -> "MetricsCollector":
+        """The hook's metrics collector: ``.to_prometheus()`` gives the text exposition format
+        (``nangila_compression_ratio``, ``nangila_bytes_saved``, ``nangila_steps_compressed``, ...),
+        ``.to_json()`` the same figures as JSON, ``.snapshot()`` a dict."""
+        return self._metrics
 
     def get_stats(self) -> dict:
         stats = dict(self.hook.get_stats())

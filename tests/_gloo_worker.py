@@ -89,6 +89,8 @@ def run(rank, world, port, steps, use_hook, out_path, hook_kwargs, calib_steps=0
               "params": [p.detach().clone() for p in model.parameters()]}
     if hook is not None:
         result["stats"] = hook.get_stats()
+        result["metrics"] = dict(hook.metrics().snapshot())
+        result["prometheus"] = hook.metrics().to_prometheus()
     if rank == 0:
         torch.save(result, out_path)
     # every rank also saves its first parameter to check replicas stay identical

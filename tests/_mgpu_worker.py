@@ -89,7 +89,10 @@ def check_exchange(dev, rank, world, results):
                 step_size = scale2.repeat_interleave(64)[:n]
                 exact_tol = 2e-6 if dtype == torch.float32 else 4e-3 * wanted.abs() + 1e-5
                 e = (got - wanted).abs()
-                assert bool((e <= step_size * 1.01 + exact_tol).all()), (name, dtype, n, e.max().item())
+                # a tie that falls the other way in the first quantization moves the mean by step / W, and the second
+                # quantization can turn that into one more level
+                bound = step_size * (1.01 if gather else 1.01 + 1.0 / world) + exact_tol
+                assert bool((e <= bound).all()), (name, dtype, n, e.max().item())
                 frac = (e > exact_tol).float().mean().item()
                 assert frac < 5e-3, (name, dtype, n, frac)
                 outputs[(name, str(dtype), n)] = mine2.clone()

@@ -47,6 +47,12 @@ def test_mlp_200_steps_with_calibration(tmp_path):
     # Sculptor calibration ran over 50 steps; the four parameters differ in size, so all are Drivers
     nbytes, drivers, passengers, samples = ours["mask_info"]
     assert (drivers, passengers, samples) == (4, 0, 50) and nbytes == 4 + 4 * 5
+    # the metrics collector was fed by the hook: 200 steps, the second hundred compressed, bytes saved
+    m = ours["metrics"]
+    assert m["steps_total"] == 200 and m["steps_compressed"] == 100
+    assert m["bytes_received"] > m["bytes_transmitted"] > 0 and m["bytes_saved"] == m["bytes_received"] - m["bytes_transmitted"]
+    assert m["compression_ratio"] == pytest.approx(st["overall_compression_ratio"], rel=1e-3)
+    assert "nangila_steps_compressed 100" in ours["prometheus"] and "# TYPE nangila_bytes_saved counter" in ours["prometheus"]
 
 
 @pytest.mark.timeout(600)

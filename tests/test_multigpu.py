@@ -18,7 +18,10 @@ def _run(nproc, what, tmp_path, port):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_mgpu_worker.py"), what, str(out)]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    if proc.returncode != 0:
+        # the ranks' tracebacks come first in the launcher's output; its own summary comes last
+        lines = [ln for ln in (proc.stdout + proc.stderr).splitlines() if "Error" in ln or "assert" in ln.lower()]
+        raise AssertionError("worker failed:\n" + "\n".join(lines[:40]) + "\n...\n" + proc.stderr[-1500:])
     return json.loads(out.read_text())
 
 
