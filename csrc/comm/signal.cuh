@@ -21,6 +21,7 @@ enum StatusWord : int {
   kStatusSeen = 4,    // last flag value it saw
   kStatusPhase = 5,   // kernel phase (1, 2, 3)
   kStatusChunk = 6,   // chunk / task index
+  kStatusBarrier = 7, // counter of the in-kernel grid barrier (kernels launched without a cooperative launch)
   kStatusWords = 8,
 };
 enum StatusCode : uint32_t {
@@ -99,6 +100,50 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
     }
   }
 }
+
+// Barrier among all CTAs of one launch WITHOUT a cooperative launch, so the kernel can start while other
+// work still holds part of the GPU and share it afterwards. It needs every CTA of the launch to become
+// resident at some point, which holds when the grid is no larger than what the device can hold at once
+// (the launchers clamp to that) and the other kernels on the device terminate on their own. `word` is a
+// counter in global memory that is zero when the kernel starts and only grows: barrier number k is
+// complete when it reaches k * nblocks. Every thread of every CTA must call sync() the same number of
+// times. Returns false, on every CTA, once any waiter of this kernel has given up (time limit or a failure
+// recorded elsewhere in the status block); the caller then returns.
+struct GridBarrier {
+  uint32_t* word;
+  uint32_t nblocks;
+  uint32_t k;
+  __device__ __forceinline__ GridBarrier(uint32_t* w, uint32_t n) : word(w), nblocks(n), k(0u) {}
+  __device__ __forceinline__ bool sync(uint64_t timeout_ns, uint32_t* status, uint32_t rank, uint32_t epoch) {
+    k += 1u;
+    __syncthreads();
+    int ok = 1;
+    if (threadIdx.x == 0) {
+      __threadfence();
+      red_release_gpu_add(word, 1u);
+      const uint32_t target = k * nblocks;
+      uint64_t t0 = 0;
+      uint32_t spins = 0, seen;
+      while (int32_t((seen = ld_acquire_gpu(word)) - target) < 0) {
+        __nanosleep(spins < 32 ? 20 : 200);
+        if ((++spins & 31u) == 0u) {
+          if (*reinterpret_cast<volatile uint32_t*>(&status[kStatusCode]) != 0u) {
+            ok = 0;
+            break;
+          }
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > timeout_ns) {
+            report_failure(status, kTimeoutGrid, rank, 0xffffffffu, epoch, seen, k, 0u);
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+    return __syncthreads_and(ok) != 0;
+  }
+};
 
 }  // namespace comm
 }  // namespace nangila

@@ -10,8 +10,8 @@
 // the DGC paper the reference leaves out (dgc.rs:36-38); `momentum = 0` gives the reference's plain
 // accumulation.
 //
-// Phases (grid-wide barriers between them; all CTAs are co-resident because the launch is
-// cooperative):
+// Phases (grid-wide barriers between them: hardware barriers of a cooperative launch in the single-GPU
+// loopback world, counter barriers with a time limit otherwise, see comm/signal.cuh):
 //   0  clear the scratch histograms / cursor
 //   1  u = m u + g ; v = v + u ; histogram of bits [30:20] of |v|
 //   2  histogram of bits [19:9] among elements whose top bits equal the selected bin
@@ -86,6 +86,18 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_constant__ NangilaDgcParams p) {
   cg::grid_group grid = cg::this_grid();
   const int vr = blockIdx.y;
+  // Grid-wide barriers: the hardware one when several ranks are emulated in one (cooperative) launch; with a
+  // real process group a counter barrier over the CTAs of this launch, so the kernel needs no cooperative
+  // launch, can start while backward still holds part of the GPU, and runs with a capped number of CTAs.
+  const bool coop = p.nvr > 1;
+  GridBarrier soft(p.status[vr] + kStatusBarrier, gridDim.x);
+  auto gsync = [&]() -> bool {
+    if (coop) {
+      grid.sync();
+      return true;
+    }
+    return soft.sync(p.timeout_ns, p.status[vr], uint32_t(p.rank0 + vr), p.epoch);
+  };
   const int me = p.rank0 + vr;
   const int W = p.world;
   const int64_t n = p.n;
@@ -135,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
   // ---- phase 0 ----
   for (int i = int(tid0); i < kScratchWords; i += int(stride)) scratch[i] = 0u;
   if (threadIdx.x == 0) sh_cand_cnt = 0u;
-  grid.sync();
+  if (!gsync()) return;
 
   // ---- phase 1: momentum correction + histogram of bits [30:20] ----
   for (int i = threadIdx.x; i < kBins0; i += kThreads) sh_hist[i] = 0u;
@@ -201,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     atomicAdd(&scratch[kCandCount], my_cand);
     if (sh_cand_cnt > seg_cap) atomicOr(&scratch[kCandOverflow], 1u);
   }
-  grid.sync();
+  if (!gsync()) return;
   uint32_t want = p.k, bin0, bin1, bin2;
   select_bin(scratch + kHist0, kBins0, want, bin0, sh_sel);
 
@@ -220,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     __syncthreads();
     for (int i = threadIdx.x; i < kBins1; i += kThreads)
       if (sh_hist[i]) atomicAdd(&scratch[kHist1 + i], sh_hist[i]);
-    grid.sync();
+    if (!gsync()) return;
     select_bin(scratch + kHist1, kBins1, want, bin1, sh_sel);
     for (int i = threadIdx.x; i < kBins2; i += kThreads) sh_hist[i] = 0u;
     __syncthreads();
@@ -232,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     __syncthreads();
     for (int i = threadIdx.x; i < kBins2; i += kThreads)
       if (sh_hist[i]) atomicAdd(&scratch[kHist2 + i], sh_hist[i]);
-    grid.sync();
+    if (!gsync()) return;
     select_bin(scratch + kHist2, kBins2, want, bin2, sh_sel);
     tau = (prefix << 9) | bin2;
     for (uint32_t j = threadIdx.x; j < nc_rounded; j += kThreads) {
@@ -280,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     __syncthreads();
     for (int i = threadIdx.x; i < kBins1; i += kThreads)
       if (sh_hist[i]) atomicAdd(&scratch[kHist1 + i], sh_hist[i]);
-    grid.sync();
+    if (!gsync()) return;
     select_bin(scratch + kHist1, kBins1, want, bin1, sh_sel);
 
     // ---- phase 3: bits [8:0] ----
@@ -296,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     __syncthreads();
     for (int i = threadIdx.x; i < kBins2; i += kThreads)
       if (sh_hist[i]) atomicAdd(&scratch[kHist2 + i], sh_hist[i]);
-    grid.sync();
+    if (!gsync()) return;
     select_bin(scratch + kHist2, kBins2, want, bin2, sh_sel);
     tau = (prefix << 9) | bin2;  // bit pattern of the k-th largest |v|
 
@@ -328,7 +340,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
       }
     }
   }
-  grid.sync();
+  if (!gsync()) return;
   const uint32_t count = min(scratch[kCursor], cap);
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     *reinterpret_cast<uint32_t*>(myslot) = count;
@@ -351,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
     if (blockIdx.x == 0 && threadIdx.x == 0) *reinterpret_cast<uint32_t*>(dst) = count;
   }
   __threadfence_system();
-  grid.sync();
+  if (!gsync()) return;
   if (blockIdx.x == 0 && threadIdx.x < W) {
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t*>(p.region[threadIdx.x] + p.flag_off) + me, p.epoch);
@@ -380,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 3) dgc_fused_kernel(const __grid_con
         if (idx < n) grad[idx] = dev::Vec16<T>::from_float(__fmaf_rn(s_val[j], inv_w, ldf(grad, idx)));
       }
     }
-    grid.sync();
+    if (!gsync()) return;
   }
 }
 
@@ -418,5 +430,9 @@ extern "C" int nangila_dgc_launch(const NangilaDgcParams* p, cudaStream_t stream
   if (ce != cudaSuccess) return int(ce);
   dim3 grid(unsigned(grid_x), unsigned(p->nvr)), block(kThreads);
   void* args[] = {const_cast<NangilaDgcParams*>(p)};
-  return int(cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream));
+  if (p->nvr > 1) return int(cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream));
+  // real process group: plain launch; the counter of the in-kernel grid barrier starts from zero
+  const cudaError_t me = cudaMemsetAsync(p->status[0] + comm::kStatusBarrier, 0, sizeof(uint32_t), stream);
+  if (me != cudaSuccess) return int(me);
+  return int(cudaLaunchKernel(fn, grid, block, args, 0, stream));
 }

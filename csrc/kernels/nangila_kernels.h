@@ -129,7 +129,8 @@ int nangila_psgd_exchange(const NangilaPsgdExchangeParams* p, cudaStream_t strea
 /* ---- fused DGC exchange (see dgc_fused.cu) ------------------------------------------------------------
  * u = m u + g; v += u; exact k-th largest |v| by radix select; (index, value) compaction with masking
  * of u and v; sparse all-gather into every rank's receive slots; scatter-add value / W into the
- * bucket. Cooperative launch; grid_x * nvr CTAs must be co-resident. */
+ * bucket. nvr > 1 (loopback world): cooperative launch. nvr == 1: plain launch with counter barriers between
+ * the phases (status[0][7] is the counter; the launcher clears it); grid_x is clamped to device residency. */
 typedef struct NangilaDgcParams {
   void* grad[NANGILA_MAX_VRANKS];       /* in: gradient; out: dense mean of the selected entries */
   float* u[NANGILA_MAX_VRANKS];         /* momentum-corrected velocity, n floats */

@@ -55,7 +55,7 @@ class DGCEngine:
         self.momentum = float(momentum)
         self.stream = stream
         self.timeout_s = float(os.environ.get("NANGILA_WAIT_TIMEOUT_MS", "2000")) / 1e3 if timeout_s is None else timeout_s
-        self.ctas = ctas
+        self.ctas = ctas or int(os.environ.get("NANGILA_DGC_CTAS", "0")) or None  # CTAs per launch (default: as many as the candidate list is sized for)
         self.buckets: Dict[int, DGCBucket] = {}
         self.status = [torch.zeros(8, dtype=torch.int32, device=self.device) for _ in range(self.nvr)]
         self.launches = 0

@@ -88,7 +88,7 @@ def test_error_memory_recovers_what_quantization_dropped():
     for t in range(8):
         acc += hook.decompress_gpu(0, hook.compress_gpu(0, g), g.numel())
         hook.step()
-    first = (hook.decompress_gpu(0, hook.compress_gpu(3, g), g.numel(), sync_mode=0) - g).norm()  # fresh layer: no memory yet
+    first = (hook.decompress_gpu(3, hook.compress_gpu(3, g), g.numel(), sync_mode=0) - g).norm()  # fresh layer: no memory yet
     assert (acc / 8 - g).norm() < 0.3 * first
 
 
