@@ -73,9 +73,9 @@ def build_bert(args, dev, world):
 
     cfg = BertConfig.tiny() if args.small else BertConfig.large()
     model = BertMLM(cfg).to(dev)
-    # 100 MB buckets (both arms): the fused DGC kernel makes several grid-wide passes per bucket, and the
-    # selection is taken per bucket, so fewer, larger buckets amortise that and select more globally
-    ddp = DDP(model, device_ids=[dev.index], bucket_cap_mb=100, gradient_as_bucket_view=True)
+    # the fused DGC kernel makes several grid-wide passes per bucket and the selection is taken per bucket, so
+    # fewer, larger buckets amortise that and select more globally (--bucket-mb, same in both arms)
+    ddp = DDP(model, device_ids=[dev.index], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
     hook = None
     if args.impl == "ours":
         with warnings.catch_warnings():
@@ -100,7 +100,7 @@ def build_bert(args, dev, world):
     info = {"model": "bert-tiny" if args.small else "bert-large 24L d1024 h16 mlp4096 vocab30522", "unit": "tokens/s",
             "items_per_step": b * t * world, "global_batch": b * world, "seq_len": t, "parallelism": f"dp{world}",
             "compressor": "DGC sparsity 0.999 with momentum correction" if hook else "stock DDP all-reduce",
-            "bucket_mb": 100, "optimizer": "AdamW(fused)"}
+            "bucket_mb": args.bucket_mb, "optimizer": "AdamW(fused)"}
     return ddp, opt, hook, host, put, loss_fn, info
 
 
@@ -168,6 +168,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--bucket-mb", type=int, default=25, help="DDP bucket size of the BERT configuration")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, dev = init_distributed()

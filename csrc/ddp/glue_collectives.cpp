@@ -376,7 +376,7 @@ void psgd_exchange(const std::vector<at::Tensor>& local, const std::vector<at::T
                    const std::vector<at::Tensor>& scratch, const std::vector<at::Tensor>& t_out,
                    const std::vector<at::Tensor>& status, const std::vector<int64_t>& region_ptrs, int64_t recv_off,
                    int64_t flag_off, int64_t rows, int64_t rank, int64_t rank0, bool orth_mean, int64_t epoch,
-                   double timeout_s) {
+                   double timeout_s, const c10::optional<at::Tensor>& epoch_word) {
   const size_t nvr = local.size();
   TORCH_CHECK(nvr >= 1 && nvr <= NANGILA_MAX_VRANKS && mean_out.size() == nvr && scratch.size() == nvr && t_out.size() == nvr &&
                   status.size() == nvr, "nangila: list length mismatch");
@@ -389,6 +389,11 @@ void psgd_exchange(const std::vector<at::Tensor>& local, const std::vector<at::T
   p.nvr = int32_t(nvr);
   p.orth_mean = orth_mean ? 1 : 0;
   p.epoch = uint32_t(epoch);
+  if (epoch_word.has_value()) {
+    TORCH_CHECK(epoch_word->is_cuda() && epoch_word->scalar_type() == at::kInt && epoch_word->numel() >= 1,
+                "nangila: the epoch word must be an int32 CUDA tensor");
+    p.epoch_dev = reinterpret_cast<const uint32_t*>(epoch_word->data_ptr<int32_t>());
+  }
   p.timeout_ns = uint64_t(timeout_s * 1e9);
   p.recv_off = uint64_t(recv_off);
   p.flag_off = uint64_t(flag_off);
@@ -426,7 +431,9 @@ void register_more(py::module_& m) {
         py::arg("clear1") = py::none());
   m.def("psgd_reconstruct", &psgd_reconstruct);
   m.def("psgd_exchange_layout", &psgd_exchange_layout);
-  m.def("psgd_exchange", &psgd_exchange);
+  m.def("psgd_exchange", &psgd_exchange, py::arg("local"), py::arg("mean_out"), py::arg("scratch"), py::arg("t_out"),
+        py::arg("status"), py::arg("region_ptrs"), py::arg("recv_off"), py::arg("flag_off"), py::arg("rows"), py::arg("rank"),
+        py::arg("rank0"), py::arg("orth_mean"), py::arg("epoch"), py::arg("timeout_s"), py::arg("epoch_word") = py::none());
   m.def("rs_region_layout", &rs_region_layout);
   m.def("rs_launch", &rs_launch);
   m.def("ag_region_layout", &ag_region_layout);

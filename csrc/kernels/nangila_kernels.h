@@ -121,6 +121,9 @@ typedef struct NangilaPsgdExchangeParams {
   int32_t rows, rank, world, rank0, nvr, orth_mean;
   uint32_t epoch;
   uint64_t timeout_ns;
+  const uint32_t* epoch_dev;                /* if not NULL the epoch is read from this device word instead of `epoch`:
+                                               a launch recorded in a CUDA graph then sees a new epoch at every replay
+                                               (the graph increments the word before the first exchange) */
 } NangilaPsgdExchangeParams;
 uint64_t nangila_psgd_exchange_region_bytes(int32_t rows, int32_t rank, int32_t world, uint64_t* recv_off,
                                             uint64_t* flag_off);

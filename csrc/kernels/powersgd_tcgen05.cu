@@ -262,7 +262,8 @@ __global__ void __launch_bounds__(kXThreads) psgd_exchange_kernel(const __grid_c
   const int W = p.world, rows = p.rows, r = p.rank;
   const int tid = threadIdx.x;
   const uint64_t slot_bytes = (uint64_t(rows) * r * 4 + 255) & ~uint64_t(255);
-  const uint64_t base = p.recv_off + uint64_t(p.epoch & 1u) * W * slot_bytes;  // two slot sets, by launch parity
+  const uint32_t epoch = p.epoch_dev != nullptr ? *p.epoch_dev : p.epoch;
+  const uint64_t base = p.recv_off + uint64_t(epoch & 1u) * W * slot_bytes;  // two slot sets, by launch parity
   uint32_t* status = p.status[vr];
   const float* local = p.local[vr];
   float* mean = p.mean_out[vr];
@@ -285,14 +286,14 @@ __global__ void __launch_bounds__(kXThreads) psgd_exchange_kernel(const __grid_c
   cluster.sync();
   if (g == 0 && tid < W) {
     __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(p.region[tid] + p.flag_off) + me, p.epoch);
+    st_release_sys(reinterpret_cast<uint32_t*>(p.region[tid] + p.flag_off) + me, epoch);
   }
   // 2. wait for every rank's factor (every CTA polls for itself; on failure all of them still take part in
   //    the cluster barriers below, doing no work)
   if (tid == 0) s_ok = 1;
   __syncthreads();
   if (tid < W) {
-    if (!wait_flag(reinterpret_cast<const uint32_t*>(p.region[me] + p.flag_off) + tid, p.epoch, p.timeout_ns, status,
+    if (!wait_flag(reinterpret_cast<const uint32_t*>(p.region[me] + p.flag_off) + tid, epoch, p.timeout_ns, status,
                    kTimeoutPhase2, uint32_t(me), uint32_t(tid), 8u, 0u))
       s_ok = 0;
   }
@@ -548,7 +549,7 @@ extern "C" uint64_t nangila_psgd_exchange_region_bytes(int32_t rows, int32_t ran
 extern "C" int nangila_psgd_exchange(const NangilaPsgdExchangeParams* p, cudaStream_t stream) {
   using namespace nangila;
   if (!p || p->rows <= 0 || p->rank <= 0 || p->rank > 16 || p->world < 1 || p->world > NANGILA_MAX_RANKS || p->nvr < 1 ||
-      p->nvr > NANGILA_MAX_VRANKS || (p->nvr > 1 && p->nvr != p->world) || p->epoch == 0)
+      p->nvr > NANGILA_MAX_VRANKS || (p->nvr > 1 && p->nvr != p->world) || (p->epoch == 0 && p->epoch_dev == nullptr))
     return int(cudaErrorInvalidValue);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3{unsigned(p->nvr * kXCtas), 1u, 1u};

@@ -16,6 +16,7 @@ import torch
 from .predres_engine import STATUS_MESSAGES, _glue
 from .symm import LoopbackArena, Region
 
+_GROUP_CTAS = 296  # default CTAs per launch in a real process group
 _LIST_CTAS = 444  # CTAs whose equal segments of the candidate list the scratch buffer has slack for
 
 
@@ -62,8 +63,9 @@ class DGCEngine:
         self._glue = _glue()
 
     def _grid(self, n: int) -> int:
-        # the candidate-list scratch is sized for _LIST_CTAS CTAs; the launcher clamps to what the device can hold at once
-        cap = self.ctas or max(1, _LIST_CTAS // self.nvr)
+        # the candidate-list scratch is sized for _LIST_CTAS CTAs; the launcher clamps to what the device can hold at once.
+        # A real group runs two thirds of that: the kernel then shares the GPU with backward instead of queueing for it.
+        cap = self.ctas or (max(1, _LIST_CTAS // self.nvr) if self.loopback else _GROUP_CTAS)
         return max(1, min(cap, (n + 1023) // 1024))  # 4 elements per thread and pass
 
     def bucket_state(self, index: int, grads: List[torch.Tensor]) -> DGCBucket:
