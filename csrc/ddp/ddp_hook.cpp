@@ -107,6 +107,7 @@ class DdpHook {
     ctas_ = int32_t(env_double("NANGILA_COMM_CTAS", 0));
     ctas_wait_ = int32_t(env_double("NANGILA_COMM_CTAS_WAIT", 0));
     defer_ = env_double("NANGILA_DEFER", 1) != 0;
+    dry_run_ = env_double("NANGILA_DRY_RUN", 0) != 0;
     timing_ = env_double("NANGILA_TIMING", 0) != 0;
     nvtx_ = env_double("NANGILA_NVTX", 0) != 0;
     gather_max_world_ = std::min<int32_t>(NANGILA_GATHER_MAX_WORLD, int32_t(env_double("NANGILA_GATHER_MAX_WORLD", NANGILA_GATHER_MAX_WORLD)));
@@ -239,7 +240,8 @@ class DdpHook {
     // split into per-phase launches when there are peers to wait for; otherwise one fused launch
     const bool split = defer_ && compressed && world_ > 1;
     p.phase_mask = split ? 1 : 0;
-    const int err = nangila_predres_launch(&p, stream_->stream());
+    // NANGILA_DRY_RUN=1 (diagnostics): everything but the launch, to time the host side of the hook on its own
+    const int err = dry_run_ ? 0 : nangila_predres_launch(&p, stream_->stream());
     if (nvtx_) nvtxRangePop();
     TORCH_CHECK(err == 0, "nangila: predres_launch failed: ", cudaGetErrorString(static_cast<cudaError_t>(err)));
     std::swap(b.prev, b.curr);
@@ -529,6 +531,7 @@ class DdpHook {
   int32_t ctas_;
   int32_t ctas_wait_ = 0;
   bool defer_ = true;
+  bool dry_run_ = false;
   std::deque<Pending> pending_;
   int32_t gather_max_world_;
   bool timing_ = false;

@@ -201,6 +201,12 @@ __device__ __forceinline__ void phase1_compressed(T* __restrict__ grad, S* __res
   }
 }
 
+// Packed-bf16 fast path: bf16 gradients with bf16 state in the variants that neither read the history nor
+// keep statistics (the gain is zero, which is where a run spends nearly all its calls once the controller
+// has found nothing to predict).
+template <typename T, typename S, bool LEAN>
+constexpr bool kFastBf16 = LEAN && std::is_same_v<T, __nv_bfloat16> && std::is_same_v<S, __nv_bfloat16>;
+
 constexpr int kWarpElems = 32 * kE;  // elements one warp handles per iteration (contiguous)
 constexpr int kRingBytesPerWarp = 6144;
 
@@ -268,6 +274,44 @@ __device__ __forceinline__ bool phase1_bulk(T* __restrict__ grad, S* __restrict_
     }
     const uint8_t* sp = ring + (k % D) * R::STAGE;
     const int64_t base = tbase + int64_t(it) * kElemsPerIter + tid * kE;
+    if constexpr (kFastBf16<T, S, LEAN>) {
+      // packed bf16 arithmetic (quant.cuh): two elements per instruction, no FP32 round trip
+      const uint4 gv = *reinterpret_cast<const uint4*>(sp + lane * 16);
+      uint4 ev = make_uint4(0u, 0u, 0u, 0u);
+      if (has_ef) ev = *reinterpret_cast<const uint4*>(sp + R::GB + lane * 16);
+      uint32_t x[4] = {gv.x, gv.y, gv.z, gv.w};
+      if (has_ef) {
+        const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = as_u32(__hadd2(as_bf162(x[j]), as_bf162(ew[j])));
+      }
+      if (!__any_sync(0xffffffffu, maybe_nonfinite8(x))) {
+        __syncwarp();  // every lane has read the stage: lane 0 may refill it
+        if (it + D < iters) {
+          issue(it + D, k + uint32_t(D));
+          issued = it + D + 1;
+        }
+        uint32_t packed, sb, qs[4];
+        quantize8_bf16(x, packed, sb, qs);
+        if (has_ef) *reinterpret_cast<uint4*>(ef + base) = make_uint4(x[0], x[1], x[2], x[3]);
+        if constexpr (SINGLE) {
+          const uint4 o = make_uint4(qs[0], qs[1], qs[2], qs[3]);
+          *reinterpret_cast<uint4*>(grad + base) = o;
+          if (keep_history) *reinterpret_cast<uint4*>(prev + base) = o;
+        } else if (ndst == 1) {
+          *packed_ptr(dst, C, it, tid) = packed;
+          if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+        } else {
+          for (int r = 0; r < ndst; ++r) {
+            uint8_t* d = regions[r] + dst_off;
+            *packed_ptr(d, C, it, tid) = packed;
+            if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(d, C, it, tid) = uint16_t(sb);
+          }
+        }
+        continue;
+      }
+      // a NaN / Inf somewhere in the warp's slice (or magnitudes >= 2): the FP32 path below sanitises it
+    }
     float g[kE], e[kE], pv[kE], cu[kE];
     Vec8<T>::load(reinterpret_cast<const T*>(sp) + lane * kE, g);
     if (has_ef) Vec8<S>::load(reinterpret_cast<const S*>(sp + R::GB) + lane * kE, e);
@@ -591,6 +635,34 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
           }
         }
       };
+      // packed-bf16 form of the same (quant.cuh): the mean's factor 1 / W (or out_scale) is folded into each
+      // rank's block scale, so the sum of the dequantized codes is already the result
+      [[maybe_unused]] const bool fast2 = kFastBf16<T, S, LEAN> && t.base + C <= lim && (!GATHER || gbar == 0.0f) &&
+                                          (RS || GATHER || ef2 == nullptr);
+      [[maybe_unused]] auto finish_fast = [&](int it, uint32_t (&acc)[4]) {
+        if constexpr (kFastBf16<T, S, LEAN>) {
+          const uint4 o = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+          if constexpr (RS) {
+            const int64_t local_i = int64_t(j) * C + int64_t(it) * kElemsPerIter + tid * kE;
+            *reinterpret_cast<uint4*>(static_cast<T*>(p.out_shard[vr]) + local_i) = o;
+          } else if constexpr (GATHER) {
+            const int64_t base = t.base + int64_t(it) * kElemsPerIter + tid * kE;
+            *reinterpret_cast<uint4*>(grad + base) = o;
+            if (keep_history) *reinterpret_cast<uint4*>(prev + base) = o;
+          } else {
+            uint32_t packed, sb, qs[4];
+            quantize8_bf16(acc, packed, sb, qs);
+            int rr = me + 1 == W ? 0 : me + 1;
+            for (int r = 0; r < W; ++r) {
+              uint8_t* dst = p.region[rr] + off2;
+              *packed_ptr(dst, C, it, tid) = packed;
+              if ((tid & (kLanes8 - 1)) == 0) *scale_ptr(dst, C, it, tid) = uint16_t(sb);
+              rr = rr + 1 == W ? 0 : rr + 1;
+            }
+          }
+        }
+      };
+      [[maybe_unused]] const float mulw = RS ? p.out_scale : inv_w;
       bool batched = false;
       if constexpr (COMPRESSED) {
         const int ib = min(iters, kHalf / (W * kIterBytes)) & ~1;
@@ -622,6 +694,19 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
             bat_parity ^= 1u << h;
             const uint8_t* buf = wring + h * kHalf;
             for (int i = 0; i < m; ++i) {
+              if constexpr (kFastBf16<T, S, LEAN>) {
+                if (fast2) {
+                  uint32_t acc2[4] = {0u, 0u, 0u, 0u};
+#pragma unroll 4
+                  for (int r = 0; r < W; ++r) {
+                    const uint32_t pk = reinterpret_cast<const uint32_t*>(buf + r * ib * 128)[i * 32 + lane];
+                    const uint16_t sc = reinterpret_cast<const uint16_t*>(buf + W * ib * 128 + r * ib * 8)[i * 4 + (lane >> 3)];
+                    dequant8_bf16_fma(pk, bf16_rn_bits(bf16_bits_to_float(sc) * mulw), acc2);
+                  }
+                  finish_fast(it0 + i, acc2);
+                  continue;
+                }
+              }
               float acc[kE];
 #pragma unroll
               for (int q = 0; q < kE; ++q) acc[q] = 0.0f;
@@ -738,6 +823,17 @@ predres_bucket_kernel(const __grid_constant__ NangilaPredResParams p) {
             for (int i = 0; i < m; ++i) {
               const uint32_t pk = reinterpret_cast<const uint32_t*>(buf)[i * 32 + lane];
               const uint16_t sc = reinterpret_cast<const uint16_t*>(buf + ib * 128)[i * 4 + (lane >> 3)];
+              if constexpr (kFastBf16<T, S, LEAN>) {
+                if (whole && kbar == 0.0f) {  // packed-bf16 form: q * scale straight into the bucket's type
+                  uint32_t o[4] = {0u, 0u, 0u, 0u};
+                  dequant8_bf16_fma(pk, sc, o);
+                  const int64_t base = t.base + int64_t(it0 + i) * kElemsPerIter + tid * kE;
+                  const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+                  *reinterpret_cast<uint4*>(grad + base) = ov;
+                  if (keep_history) *reinterpret_cast<uint4*>(prev + base) = ov;
+                  continue;
+                }
+              }
               const uint8_t* hs = hist ? buf + ib * kIterBytes + i * 2 * kStateBytes : nullptr;
               if (whole) emit(std::false_type{}, it0 + i, pk, sc, hs);
               else emit(std::true_type{}, it0 + i, pk, sc, hs);

@@ -279,6 +279,102 @@ __device__ __forceinline__ void dequant8_add(uint32_t packed, float scale, float
   }
 }
 
+
+// ---- packed bf16x2 variants (gradient and state both bf16) ----------------------------------------------------
+// The quantizer bounds the exchange kernels' instruction issue rate, and FP32 arithmetic on values that
+// arrive as bf16 and leave as 4-bit codes or bf16 spends most of it on conversions. These variants stay
+// in packed bf16: one instruction handles two elements. What that costs in accuracy: g + ef and the
+// error e - q s are rounded to 8 significant bits (they are stored as bf16 anyway), which is ~1.4 % of a
+// quantization step at the block's largest element; a code may land on the other side of a tie. Every
+// rank executes the same instructions on the same bytes, so replicas stay bit-identical.
+//
+// Tricks: (1) rounding to the nearest integer is one fused multiply-add, t = x * (1/s) + 192: in
+// [128, 256) a bf16 has unit spacing, so t is the integer 192 + q (round-to-nearest-even); 1/s is
+// truncated to bf16 so that |x / s| cannot exceed 7.03; (2) the two's complement nibble of q is the
+// low nibble of t's bit pattern (0x4300 | (64 + q)); (3) the reverse: the bit pattern 0x4300 | n is the
+// bf16 number 128 + n.
+using bf162 = __nv_bfloat162;
+__device__ __forceinline__ bf162 as_bf162(uint32_t w) { return *reinterpret_cast<bf162*>(&w); }
+__device__ __forceinline__ uint32_t as_u32(bf162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// True if any of the eight bf16 values in w[0..3] may be Inf or NaN (exponent all ones). May also fire when
+// values of magnitude >= 2 with different exponents share the words; the caller then takes the FP32 path.
+__device__ __forceinline__ bool maybe_nonfinite8(const uint32_t (&w)[4]) {
+  const uint32_t t = (w[0] | w[1] | w[2] | w[3]) & 0x7F807F80u;
+  return ((t + 0x00800080u) & 0x80008000u) != 0u;
+}
+
+// x[0..3]: eight values as bf16x2 words (element 2j in the low half of word j). On return x holds the error
+// x - q * scale, `qs` the dequantized values q * scale, `packed` the eight codes, `scale_bits` the block's
+// bf16 scale. The eight lanes holding one 64-element block call it together; all values must be finite.
+__device__ __forceinline__ void quantize8_bf16(uint32_t (&x)[4], uint32_t& packed, uint32_t& scale_bits, uint32_t (&qs)[4]) {
+  const uint32_t m01 = as_u32(__hmax2(__habs2(as_bf162(x[0])), __habs2(as_bf162(x[1]))));
+  const uint32_t m23 = as_u32(__hmax2(__habs2(as_bf162(x[2])), __habs2(as_bf162(x[3]))));
+  const uint32_t m = as_u32(__hmax2(as_bf162(m01), as_bf162(m23)));
+  float amax = fmaxf(__uint_as_float(m << 16), __uint_as_float(m & 0xffff0000u));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  scale_bits = bf16_ceil_bits(__fmul_rn(amax, 0.14285715f));
+  const float s = bf16_bits_to_float(scale_bits);
+  const bool live = s > 1e-30f;
+  if (!live) scale_bits = 0u;
+  const uint32_t inv_bits = live ? (__float_as_uint(__frcp_rn(s)) >> 16) : 0u;  // truncated: never above 1 / s
+  const bf162 inv2 = as_bf162(inv_bits | (inv_bits << 16));
+  const uint32_t s2_bits = scale_bits | (scale_bits << 16);
+  const bf162 s2 = as_bf162(s2_bits), neg_s2 = as_bf162(s2_bits ^ 0x80008000u);
+  const bf162 magic = as_bf162(0x43404340u);   // 192, 192
+  uint32_t t[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const bf162 xj = as_bf162(x[j]);
+    const bf162 tj = __hfma2(xj, inv2, magic);             // 192 + q
+    const bf162 qj = __hsub2(tj, magic);                   // q, exact
+    t[j] = as_u32(tj);
+    qs[j] = as_u32(__hmul2(qj, s2));                       // q * s
+    x[j] = as_u32(__hfma2(qj, neg_s2, xj));                // x - q * s
+  }
+  // nibbles: byte 0 of each half of t holds the code in its low four bits
+  const uint32_t a = __byte_perm(t[0], t[1], 0x6420) & 0x0F0F0F0Fu;   // codes of elements 0, 1, 2, 3 (one per byte)
+  const uint32_t b = __byte_perm(t[2], t[3], 0x6420) & 0x0F0F0F0Fu;   // elements 4, 5, 6, 7
+  const uint32_t a2 = (a | (a >> 4)) & 0x00FF00FFu;                   // bytes 0 and 2: two codes each
+  const uint32_t b2 = (b | (b >> 4)) & 0x00FF00FFu;
+  packed = __byte_perm(a2, b2, 0x6420);
+}
+
+// Unpack eight bf16 values held in four words into floats (element 2j in the low half of word j).
+__device__ __forceinline__ void words_to_float8(const uint32_t (&w)[4], float (&v)[8]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(w[j] << 16);
+    v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+  }
+}
+// bf16 bit pattern (round to nearest even) of a finite float.
+__device__ __forceinline__ uint32_t bf16_rn_bits(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+}
+
+// acc[j] += q * scale for the eight codes in `packed` (two's complement nibbles), as bf16x2 words.
+__device__ __forceinline__ void dequant8_bf16_fma(uint32_t packed, uint32_t scale_bits, uint32_t (&acc)[4]) {
+  const uint32_t w = packed ^ 0x88888888u;                 // offset codes n = q + 8 in [0, 15]
+  const uint32_t lo = w & 0x0F0F0F0Fu;                     // elements 0, 2, 4, 6
+  const uint32_t hi = (w >> 4) & 0x0F0F0F0Fu;              // elements 1, 3, 5, 7
+  const bf162 s2 = as_bf162(scale_bits | (scale_bits << 16));
+  const bf162 off = as_bf162(0x43084308u);                 // 136 = 128 + 8
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // bytes {lo.byte j, 0, hi.byte j, 0} (selector nibbles 8..15 replicate the byte's sign bit, which is 0 here)
+    const uint32_t sel = uint32_t(j) | (uint32_t(8 + j) << 4) | (uint32_t(4 + j) << 8) | (uint32_t(12 + j) << 12);
+    uint32_t v;  // prmt in PTX: the CUDA intrinsic ignores bit 3 of a selector nibble (the sign-replicate flag)
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(lo), "r"(hi), "r"(sel));
+    v |= 0x43004300u;                                       // 128 + n in both halves
+    const bf162 q = __hsub2(as_bf162(v), off);              // exact
+    acc[j] = as_u32(__hfma2(q, s2, as_bf162(acc[j])));
+  }
+}
+
 template <typename T, bool GUARD>
 __device__ __forceinline__ void store8(T* p, int64_t base, int64_t n, const float (&v)[8]) {
   if constexpr (GUARD) store8_guarded<T>(p, base, n, v);

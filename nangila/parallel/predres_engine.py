@@ -119,6 +119,8 @@ class PredResEngine:
         self.probe_every = max(1, int(os.environ.get("NANGILA_PROBE_EVERY", "8")))
         # small worlds use the kernel's gather mode (one quantization, two phases)
         self.gather_max_world = min(4, int(os.environ.get("NANGILA_GATHER_MAX_WORLD", "4")))
+        # leave the history unwritten between probes while the gain is 0 (NANGILA_SKIP_HISTORY=0: always write it)
+        self.skip_history = os.environ.get("NANGILA_SKIP_HISTORY", "1") != "0"
         self.buckets: Dict[int, BucketState] = {}
         # one row of 8 floats per (bucket, emulated rank): {sum e^2, sum g^2, sum miss^2, sum ef^2, ...}
         self.max_buckets = max_buckets
@@ -206,7 +208,7 @@ class PredResEngine:
         gather = compressed and 2 <= self.world <= self.gather_max_world
         # While the gain is 0 nothing reads the history except a probe: it is written on the two calls before a
         # probe and the two after it (until the controller has seen the probe's statistics) and left alone otherwise.
-        skip_history = (compressed and st.pred_gain == 0.0 and st.extra.get("pred_gain_per_rank") is None
+        skip_history = (self.skip_history and compressed and st.pred_gain == 0.0 and st.extra.get("pred_gain_per_rank") is None
                         and not measure and st.calls + 2 < st.next_probe and st.calls > st.last_probe + 2)
         if split_phases and self.world > 1:
             masks = [1, 2] if gather else [1, 2, 4]
