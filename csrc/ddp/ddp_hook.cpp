@@ -110,7 +110,9 @@ class DdpHook {
     dry_run_ = env_double("NANGILA_DRY_RUN", 0) != 0;
     timing_ = env_double("NANGILA_TIMING", 0) != 0;
     nvtx_ = env_double("NANGILA_NVTX", 0) != 0;
-    gather_max_world_ = std::min<int32_t>(NANGILA_GATHER_MAX_WORLD, int32_t(env_double("NANGILA_GATHER_MAX_WORLD", NANGILA_GATHER_MAX_WORLD)));
+    // gather mode (every rank sums all contributions itself) only pays at two ranks: at four, the three-phase
+    // form with deferred waiting phases was 3 % faster per step and the gather kernel alone slower than NCCL
+    gather_max_world_ = std::min<int32_t>(NANGILA_GATHER_MAX_WORLD, int32_t(env_double("NANGILA_GATHER_MAX_WORLD", 2)));
   }
 
   // `allocate(bytes)` returns the addresses (one per rank, as ints) of a fresh zero-initialised
@@ -238,7 +240,8 @@ class DdpHook {
       b.t0->record(*stream_);
     }
     // split into per-phase launches when there are peers to wait for; otherwise one fused launch
-    const bool split = defer_ && compressed && world_ > 1;
+    // (two launches of the gather form gained nothing over the fused one at two ranks, so it stays fused)
+    const bool split = defer_ && compressed && world_ > 1 && p.gather == 0;
     p.phase_mask = split ? 1 : 0;
     // NANGILA_DRY_RUN=1 (diagnostics): everything but the launch, to time the host side of the hook on its own
     const int err = dry_run_ ? 0 : nangila_predres_launch(&p, stream_->stream());
@@ -454,13 +457,13 @@ class DdpHook {
     Bucket b;
     b.n = t.numel();
     b.grad_dtype = code;
-    // the power of two at or above n / 1024 in [4096, 131072], at least 4 chunks per rank
-    int32_t c = 4096;
+    // sized against the CTAs the device holds at once, so that each phase is whole, equally loaded waves
+    int32_t c;
     if (chunk_override_ > 0) {
       c = chunk_override_;
     } else {
-      while (c < 131072 && int64_t(c) * 1024 < b.n) c *= 2;
-      while (c > 4096 && (b.n + c - 1) / c < 4 * int64_t(world_)) c /= 2;
+      if (resident_ <= 0) resident_ = nangila_predres_resident_ctas();
+      c = nangila_predres_chunk_elems(b.n, resident_);
     }
     b.chunk = c;
     b.nchunks = int32_t((b.n + c - 1) / c);
@@ -532,6 +535,7 @@ class DdpHook {
   int32_t ctas_wait_ = 0;
   bool defer_ = true;
   bool dry_run_ = false;
+  int resident_ = 0;  // CTAs of the bucket kernel the device holds at once (queried once)
   std::deque<Pending> pending_;
   int32_t gather_max_world_;
   bool timing_ = false;

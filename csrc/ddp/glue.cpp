@@ -169,6 +169,8 @@ void register_ddp_hook(py::module_& m);  // ddp_hook.cpp  // other glue translat
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "nangila torch glue over the sm_100a kernels";
   m.def("predres_region_layout", &predres_region_layout);
+  m.def("predres_resident_ctas", []() { return nangila_predres_resident_ctas(); });
+  m.def("predres_chunk_elems", [](int64_t n, int64_t resident) { return nangila_predres_chunk_elems(n, int32_t(resident)); });
   m.def("predres_launch", &predres_launch, py::arg("grad"), py::arg("prev"), py::arg("curr"), py::arg("ef"),
         py::arg("ef2"), py::arg("stats"), py::arg("status"), py::arg("region_ptrs"), py::arg("recv1_off"),
         py::arg("recv2_off"), py::arg("flag1_off"), py::arg("flag2_off"), py::arg("rank0"), py::arg("chunk_elems"),

@@ -80,6 +80,12 @@ uint64_t nangila_predres_region_bytes(int64_t n, int32_t world, int32_t chunk_el
 uint64_t nangila_rs_region_bytes(int64_t n, int32_t world, int32_t chunk_elems, uint64_t* recv1_off,
                                  uint64_t* flag1_off, int32_t* nchunks);
 int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_t stream);
+/* CTAs of the compressed variants that the current device holds at once (occupancy x SM count): what a host
+ * sizes chunks against so that every phase is a whole number of equally loaded waves. <= 0 on error. */
+int nangila_predres_resident_ctas(void);
+/* Chunk size (elements, a multiple of 4096) for a bucket of n elements: the smallest that covers the bucket
+ * with at most `waves x resident` chunks, waves = the least that keeps a chunk at or below 131072 elements. */
+int32_t nangila_predres_chunk_elems(int64_t n, int32_t resident_ctas);
 
 /* ---- quantizing parameter all-gather (fsdp_ag_dequant.cu) ------------------------------------------------ */
 typedef struct NangilaAgParams {

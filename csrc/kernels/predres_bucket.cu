@@ -975,6 +975,29 @@ extern "C" uint64_t nangila_rs_region_bytes(int64_t n, int32_t world, int32_t ch
   return off;
 }
 
+extern "C" int nangila_predres_resident_ctas(void) {
+  using namespace nangila;
+  // every compressed variant has the same launch bounds and the same 48 KB of dynamic shared memory
+  const void* fn = reinterpret_cast<const void*>(&predres_bucket_kernel<__nv_bfloat16, __nv_bfloat16, 3>);
+  int resident = 0;
+  const size_t smem = size_t(kWarps) * Ring<__nv_bfloat16, __nv_bfloat16, true>::BYTES_PER_WARP;
+  if (resident_ctas(fn, kThreads, smem, &resident) != cudaSuccess) return -1;
+  return resident;
+}
+
+extern "C" int32_t nangila_predres_chunk_elems(int64_t n, int32_t resident) {
+  // Each phase walks the chunks in waves of `resident` CTAs. A chunk count just above a multiple of that
+  // leaves most of the GPU idle in the last wave (800 chunks on 592 CTAs: 68 % busy), so the chunk size is
+  // derived from the wave count instead of being a fixed power of two.
+  constexpr int64_t kMaxChunk = 131072, kGrain = 4096;  // an even number of 2048-element iterations
+  if (n <= 0) return int32_t(kGrain);
+  const int64_t g = resident > 0 ? resident : 1;
+  const int64_t waves = std::max<int64_t>(1, (n + g * kMaxChunk - 1) / (g * kMaxChunk));
+  const int64_t per = (n + g * waves - 1) / (g * waves);
+  const int64_t chunk = std::max(kGrain, (per + kGrain - 1) / kGrain * kGrain);
+  return int32_t(std::min(chunk, kMaxChunk));
+}
+
 extern "C" int nangila_predres_launch(const NangilaPredResParams* p, cudaStream_t stream) {
   using namespace nangila;
   if (p == nullptr || p->n <= 0 || p->world < 1 || p->world > NANGILA_MAX_RANKS || p->nvr < 1 ||

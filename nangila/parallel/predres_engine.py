@@ -43,19 +43,15 @@ def _glue():
     return _cuda
 
 
-def default_chunk_elems(n: int, world: int) -> int:
-    """Chunk size (elements): the power of two at or above n / 1024, between 4096 and 131072, halved
-    while the bucket would give fewer than 4 chunks per rank. Every chunk costs one flag round trip per
-    phase, so large buckets want large chunks; small ones want enough chunks to fill the GPU."""
+def default_chunk_elems(n: int, world: int, resident: int = 0) -> int:
+    """Chunk size (elements). Each phase of the kernel walks the chunks in waves of ``resident`` CTAs (what the
+    device holds at once, divided by the emulated ranks): the size is the smallest multiple of 4096 that covers
+    the bucket in whole waves with no chunk above 131072 elements, so the last wave is as full as the others.
+    ``NANGILA_CHUNK`` overrides."""
     env = os.environ.get("NANGILA_CHUNK")
     if env:
         return int(env)
-    c = 4096
-    while c < 131072 and c * 1024 < n:
-        c *= 2
-    while c > 4096 and (n + c - 1) // c < 4 * world:
-        c //= 2
-    return c
+    return int(_glue().predres_chunk_elems(int(n), int(resident)))
 
 
 @dataclass
@@ -117,8 +113,9 @@ class PredResEngine:
         self.fixed_gain = float(os.environ.get("NANGILA_PRED_GAIN", "1"))
         # with a zero gain the kernel skips the history loads except on every probe_every-th call
         self.probe_every = max(1, int(os.environ.get("NANGILA_PROBE_EVERY", "8")))
-        # small worlds use the kernel's gather mode (one quantization, two phases)
-        self.gather_max_world = min(4, int(os.environ.get("NANGILA_GATHER_MAX_WORLD", "4")))
+        # two ranks use the kernel's gather mode (one quantization, two phases); from three ranks on the
+        # three-phase form is faster (at four: 13.37 against 13.82 ms per GPT-2 step)
+        self.gather_max_world = min(4, int(os.environ.get("NANGILA_GATHER_MAX_WORLD", "2")))
         # leave the history unwritten between probes while the gain is 0 (NANGILA_SKIP_HISTORY=0: always write it)
         self.skip_history = os.environ.get("NANGILA_SKIP_HISTORY", "1") != "0"
         self.buckets: Dict[int, BucketState] = {}
@@ -138,6 +135,7 @@ class PredResEngine:
         if use_side_stream:
             self.stream = torch.cuda.Stream(device=self.device, priority=-1)
         self._glue = _glue()
+        self._resident: Optional[int] = None  # CTAs per (emulated) rank the device holds at once
 
     # ------------------------------------------------------------------------------------------
     def _grid(self, st: BucketState) -> int:
@@ -172,7 +170,9 @@ class PredResEngine:
             return st
         if g0.dtype not in _DTYPE_CODE:
             raise TypeError(f"nangila: unsupported gradient dtype {g0.dtype}")
-        chunk = default_chunk_elems(n, self.world)
+        if self._resident is None:
+            self._resident = max(1, int(self._glue.predres_resident_ctas()) // self.nvr)
+        chunk = default_chunk_elems(n, self.world, self._resident)
         total, r1, r2, f1, f2 = self._glue.predres_region_layout(n, self.world, chunk, _DTYPE_CODE[g0.dtype])
         region = self.arena.allocate(int(total))
         sdt = self._state_dtype_for(g0.dtype)

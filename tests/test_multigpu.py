@@ -25,12 +25,31 @@ def _run(nproc, what, tmp_path, port):
     return json.loads(out.read_text())
 
 
-@pytest.mark.parametrize("nproc", [2, 4])
+@pytest.mark.parametrize("nproc", [2, 4, 8])
 def test_exchange_matches_nccl(nproc, tmp_path):
     if torch.cuda.device_count() < nproc:
         pytest.skip(f"needs {nproc} GPUs")
     res = _run(nproc, "exchange", tmp_path, 29731 + nproc)
     assert res["world"] == nproc
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_cpp_hook_driven_directly(nproc, tmp_path):
+    """Different data per rank on a drifting gradient: the predictor switches on, gains and bytes are the same on
+    every rank, bucket futures complete although their waiting phases are deferred."""
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    res = _run(nproc, "cpphook", tmp_path, 29771 + nproc)
+    assert min(res["cpp_hook_gains"]) > 0.2 and res["cpp_hook_launches"] > 0
+
+
+def test_withheld_rank_times_out_and_recovers(tmp_path):
+    """A rank that skips a launch (host-side failure): bounded waits expire on the others, the status says what they
+    waited for, the ranks agree over NCCL, resynchronise the epochs, and the next exchange works."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, "failure", tmp_path, 29781)
+    assert res["withheld_rank_recovered"]
 
 
 def test_ddp_loss_parity_two_gpus(tmp_path):
