@@ -117,6 +117,14 @@ else:  # pragma: no cover
 _LOG = os.environ.get("NANGILA_LOG", "warn").lower()
 
 
+class _NullContext:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
 def _log(msg: str) -> None:
     if _LOG in ("info", "debug") and (not dist.is_initialized() or dist.get_rank() == 0):
         print(f"[nangila] {msg}", flush=True)
@@ -167,6 +175,7 @@ class NangilaDDPHook:
         stochastic: Optional[bool] = None,
         dgc_momentum: float = 0.9,
         total_numel: Optional[int] = None,
+        mask: Any = None,
     ):
         _warn_if_advanced_ddp_options(compressor_type, dgc_sparsity, power_sgd_rank)
         self.process_group = process_group or dist.distributed_c10d._get_default_group()
@@ -192,7 +201,16 @@ class NangilaDDPHook:
         )
         self.__name__ = "nangila_hook"
         self.__qualname__ = "nangila_hook"
-        self.hook = NangilaHook.all_drivers(max(int(num_layers), 1), self.config)
+        # Topology mask (Sculptor output): Passenger parameters are not exchanged at all; their averaged gradient is
+        # synthesised from their Driver's as alpha * g_driver + beta (nangila-core/src/reconstructor.rs:96-152).
+        # Layer ids are positions in ``ddp_model.parameters()``.
+        mask_bytes, self._passengers = self._parse_mask(mask)
+        self._masked_values: Dict[int, torch.Tensor] = {}   # reconstructed Driver gradients of this iteration
+        self._masked_todo: List[tuple] = []                 # (passenger view, source id, alpha, beta)
+        self._masked_futures: List[tuple] = []              # (future, tensor) completed after the synthesis
+        self.passenger_elements = 0                         # elements synthesised instead of exchanged (per iteration)
+        self.hook = (NangilaHook(mask_bytes, self.config) if self._passengers
+                     else NangilaHook.all_drivers(max(int(num_layers), 1), self.config))
         self.layer_counter = 0
         self.total_original_bytes = 0
         self.total_compressed_bytes = 0
@@ -229,6 +247,8 @@ class NangilaDDPHook:
             index = self.layer_counter - 1
         if self.step_count < self._exact_until_step:
             return self._run_plain_allreduce(tensor)
+        if self._passengers:
+            return self._run_masked(bucket, tensor, index)
         if tensor.is_cuda:
             if self.prefer_cpp and CPP_HOOK_AVAILABLE and self.compressor_type == 0:
                 return self._run_cpp(bucket, tensor)
@@ -277,6 +297,131 @@ class NangilaDDPHook:
         fut = cpp(None, bucket)
         self._bucket_calls += 1
         if self.sync_mode == 1 or (self.sync_mode == 2 and self._bucket_calls % 100 == 0):
+            self._check_device_status()
+        return fut
+
+    @staticmethod
+    def _parse_mask(mask: Any) -> tuple:
+        if mask is None:
+            return None, {}
+        mask_bytes = bytes(mask.to_bytes()) if hasattr(mask, "to_bytes") else bytes(mask)
+        from ._C import TopologyMask
+
+        passengers = {int(lid): (int(source), float(alpha), float(beta))
+                      for lid, source, alpha, beta in TopologyMask.from_bytes(mask_bytes).passengers()}
+        return mask_bytes, passengers
+
+    def set_mask(self, mask: Any) -> int:
+        """Apply a topology mask (``TopologyMask`` or its bytes) to a hook that is already registered, e.g. at the end
+        of a Sculptor calibration that ran during warm-up. Call it between steps, on every rank, before compression
+        starts: the host-side predictor state of the old mask is dropped. Returns the number of Passengers."""
+        mask_bytes, passengers = self._parse_mask(mask)
+        self._passengers = passengers
+        if passengers:
+            new = NangilaHook(mask_bytes, self.config)
+            while new.current_step() < self.hook.current_step():
+                new.step()
+            new.set_gpu_mode(self.hook.gpu_mode())
+            self.hook = new
+        return len(passengers)
+
+    # ---- buckets under a topology mask ---------------------------------------------------------------
+    def _run_masked(self, bucket: GradBucket, tensor: torch.Tensor, index: int) -> torch.futures.Future:
+        """A bucket whose parameters may be Passengers. Driver parameters are exchanged as usual: on CUDA every
+        maximal run of consecutive Driver parameters goes through the fused kernel as a bucket of its own
+        (own history and error memory), on CPU every Driver parameter goes through the packet path.
+        Passenger parameters cost nothing on the wire. Their Driver may sit in a bucket that is reduced
+        later, so the synthesis is queued when the last bucket of the iteration arrives, and every bucket's
+        future completes after it."""
+        grads = bucket.gradients()
+        params = bucket.parameters()
+        base = tensor.storage_offset()
+        esize = tensor.element_size()
+        segs = []   # (layer id, first element, elements, gradient view)
+        for prm, g in zip(params, grads):
+            lid = self._param_ids.get(id(prm), -1)
+            segs.append((lid, g.storage_offset() - base, g.numel(), g))
+        is_cuda = tensor.is_cuda
+        compressing = self.compressing
+        if is_cuda:
+            engine = self._ensure_engine(tensor.device)
+            run_no = 0
+            i = 0
+            while i < len(segs):
+                lid, off, numel, g = segs[i]
+                if lid in self._passengers and numel > 0:
+                    i += 1
+                    continue
+                # a run of Drivers; a Passenger whose successor would start misaligned is carried along as a Driver
+                j, end = i, off + numel
+                while j + 1 < len(segs):
+                    nlid, noff, nnum, _ = segs[j + 1]
+                    if nlid in self._passengers:
+                        after = noff + nnum
+                        stop_ok = (tensor.data_ptr() + after * esize) % 16 == 0 or j + 2 >= len(segs)
+                        if stop_ok:
+                            break
+                    j += 1
+                    end = noff + nnum
+                if (tensor.data_ptr() + off * esize) % 16 != 0:   # cannot start a kernel range here: exact all-reduce
+                    piece = tensor[off:end]
+                    dist.all_reduce(piece, group=self.process_group)
+                    piece.div_(self.world_size)
+                else:
+                    engine.reduce(20_000_000 + index * 4096 + run_no, [tensor[off:end]], compressed=compressing and self.compressor_type == 0,
+                                  step=self.step_count)
+                nb = (end - off) * esize
+                self.total_original_bytes += nb
+                self.total_compressed_bytes += int((end - off) * (0.5 + 2.0 / 64.0)) if compressing else nb
+                for k in range(i, j + 1):
+                    self._masked_values[segs[k][0]] = segs[k][3]
+                run_no += 1
+                i = j + 1
+        else:
+            for lid, off, numel, g in segs:
+                if lid in self._passengers:
+                    continue
+                if self.step_count < self.warmup_steps or self.hook.is_paused():
+                    dist.all_reduce(g, group=self.process_group)
+                    g.div_(self.world_size)
+                    if self.step_count + 2 >= self.warmup_steps:
+                        self.hook.update(lid, g.detach().float().contiguous().numpy().reshape(-1))
+                    nb = g.numel() * g.element_size()
+                    self.total_original_bytes += nb
+                    self.total_compressed_bytes += nb
+                else:
+                    flat = g.detach().float().contiguous().numpy().reshape(-1)
+                    averaged = self._exchange_cpu(lid, flat, g.device)
+                    g.copy_(torch.from_numpy(averaged).view_as(g).to(g.dtype))
+                self._masked_values[lid] = g
+        for lid, off, numel, g in segs:
+            if lid in self._passengers and lid not in self._masked_values:
+                source, alpha, beta = self._passengers[lid]
+                self._masked_todo.append((g, source, alpha, beta))
+                self.total_original_bytes += numel * esize
+        stream = self._engine.stream if (is_cuda and self._engine is not None) else None
+        fut: torch.futures.Future = torch.futures.Future(devices=[tensor.device]) if is_cuda else torch.futures.Future()
+        self._masked_futures.append((fut, tensor))
+        if bucket.is_last():
+            ctx = torch.cuda.stream(stream) if stream is not None else _NullContext()
+            with ctx:
+                count = 0
+                for g, source, alpha, beta in self._masked_todo:
+                    src = self._masked_values.get(source)
+                    if src is None or src.numel() != g.numel():
+                        raise RuntimeError(f"nangila: Passenger gradient needs Driver {source}, which was not reduced in this iteration")
+                    torch.mul(src.view_as(g), alpha, out=g)
+                    if abs(beta) > 1e-8:
+                        g.add_(beta)
+                    count += g.numel()
+                self.passenger_elements = count
+                for f, t in self._masked_futures:
+                    f.set_result(t)
+            self._masked_todo.clear()
+            self._masked_futures.clear()
+            self._masked_values.clear()
+        self._bucket_calls += 1
+        if is_cuda and (self.sync_mode == 1 or (self.sync_mode == 2 and self._bucket_calls % 100 == 0)):
             self._check_device_status()
         return fut
 
@@ -692,14 +837,24 @@ def register_nangila_hook(
     compressor_type: int = 0,
     dgc_sparsity: float = 0.999,
     power_sgd_rank: int = 1,
+    mask: Any = None,
+    mask_path: Optional[str] = None,
     **extra: Any,
 ) -> "NangilaDDPHook":
     """Register the Nangila compression hook on a DDP model and return it (call ``.step()`` after
-    every optimizer step). Signature and defaults as the reference (ddp.py:415-426)."""
+    every optimizer step). Signature and defaults as the reference (ddp.py:415-426).
+
+    ``mask`` (a ``TopologyMask``, or its bytes as ``Sculptor.generate_mask()`` returns them) or ``mask_path`` (a
+    file holding those bytes) applies a calibrated topology: Passenger parameters (layer id = position in
+    ``ddp_model.parameters()``) are not exchanged; their averaged gradient is ``alpha * g_driver + beta``. The
+    reference accepted no mask here and treated every layer as a Driver (ddp.py:151)."""
     if not isinstance(ddp_model, DDP):
         raise TypeError(f"Expected DistributedDataParallel, got {type(ddp_model)}")
     _warn_if_advanced_ddp_options(compressor_type, dgc_sparsity, power_sgd_rank)
     sync_mode = _validate_sync_mode(sync_mode)
+    if mask is None and mask_path is not None:
+        with open(mask_path, "rb") as fh:
+            mask = fh.read()
     params = [p for p in ddp_model.parameters() if p.requires_grad]
     num_layers = len(list(ddp_model.parameters()))
     # bytes of symmetric memory the bucket regions will need: two areas per bucket, each holding the
@@ -709,7 +864,7 @@ def register_nangila_hook(
         process_group=ddp_model.process_group, threshold=threshold, warmup_steps=warmup_steps,
         num_layers=num_layers, sync_mode=sync_mode, enable_gpu_native=enable_gpu_native,
         compressor_type=compressor_type, dgc_sparsity=dgc_sparsity, power_sgd_rank=power_sgd_rank,
-        total_numel=total, **extra,
+        total_numel=total, mask=mask, **extra,
     )
     # NANGILA_PREFER_CPP=0/1 overrides the argument (to compare the two hook implementations)
     hook.prefer_cpp = bool(int(os.environ.get("NANGILA_PREFER_CPP", int(bool(prefer_cpp)))))

@@ -81,6 +81,8 @@ def run(rank, world, port, steps, use_hook, out_path, hook_kwargs, calib_steps=0
                 h = nangila.NangilaHook(mask)
                 st = h.get_stats()
                 mask_info = (len(mask), st["num_drivers"], st["num_passengers"], sculptor.num_samples())
+                if hook is not None:  # the calibrated topology goes to the hook that is already running
+                    assert hook.set_mask(mask) == st["num_passengers"]
         opt.step()
         if hook is not None:
             hook.step()

@@ -72,3 +72,11 @@ def test_fsdp2_fused_collectives_two_gpus(tmp_path):
         pytest.skip("needs 2 GPUs")
     res = _run(2, "fsdp", tmp_path, 29761)
     assert res["fsdp"]["rs_launches"] > 0 and res["fsdp"]["ag_launches"] > 0
+
+
+def test_fsdp_truth_and_speed_tiers_two_gpus(tmp_path):
+    """Single-step gradients against FSDP2's own reduce-scatter, overfitting one batch, peak memory, step time."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, "fsdp_truth", tmp_path, 29791)
+    assert res["fsdp_grad_rel_int4"] < 0.15 and res["fsdp_overfit_ours"] < 0.15 * res["fsdp_loss0"]
