@@ -7,6 +7,8 @@
 // payload with a single thread, and matches the host table CRC (nangila-core/src/packet.rs:241-274).
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "nangila_kernels.h"
 #include "nangila_noalloc.h"
 
@@ -118,7 +120,8 @@ constexpr int64_t kNoAllocWords = kNoAllocMaxBytes / kChunk + 1;           // 13
 static __device__ __align__(256) uint32_t g_crc_scratch[kNoAllocWords];
 
 constexpr int kMaxDevices = 64;
-uint32_t* g_scratch_addr[kMaxDevices] = {};  // device address of g_crc_scratch, per device ordinal
+// device address of g_crc_scratch, per device ordinal; host threads that race on the first call store the same value
+std::atomic<uint32_t*> g_scratch_addr[kMaxDevices];
 
 }  // namespace
 }  // namespace nangila
@@ -133,15 +136,15 @@ extern "C" int nangila_crc32_noalloc(const void* data, int64_t nbytes, uint32_t*
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return int(e);
   if (dev < 0 || dev >= kMaxDevices) return int(cudaErrorInvalidDevice);
-  if (g_scratch_addr[dev] == nullptr) {
+  if (g_scratch_addr[dev].load(std::memory_order_acquire) == nullptr) {
     // In host code `g_crc_scratch` is only a handle for the symbol, not an address a kernel could
     // use; the address inside the current device's copy of the image has to be asked for.
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_crc_scratch);
     if (e != cudaSuccess) return int(e);
-    g_scratch_addr[dev] = static_cast<uint32_t*>(p);
+    g_scratch_addr[dev].store(static_cast<uint32_t*>(p), std::memory_order_release);
   }
-  uint32_t* scratch = g_scratch_addr[dev];
+  uint32_t* scratch = g_scratch_addr[dev].load(std::memory_order_acquire);
   if (nbytes == 0) {
     // nothing to hash: the result is 0; written by a kernel so that no memset node is needed either
     crc_combine_kernel<<<1, 32, 0, stream>>>(scratch, 0, 0, out);

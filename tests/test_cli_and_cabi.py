@@ -152,3 +152,11 @@ def test_c_abi_roundtrip_and_safe_mode(tmp_path):
     assert h is not None
     lib.nangila_free(h)
     assert lib.nangila_init(b"/nonexistent/mask") is None
+
+
+def test_release_manifest_is_consistent():
+    from nangila.cli import release_check
+
+    assert release_check.check() == []
+    assert release_check.check(tag="v0.0.0") != []
+    assert release_check.main(["--tag", "v" + __import__("nangila").__version__]) == 0

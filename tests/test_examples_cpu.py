@@ -34,3 +34,11 @@ def test_spice_partitioned_example():
     r = _run("examples/spice_partitioned.py", "--stages", "40", "--partitions", "3", "--tstop", "1e-10")
     assert r.returncode == 0, r.stderr[-2000:]
     assert "partitioned_validated" in r.stdout and ".nz v2" in r.stdout
+
+
+def test_manual_reducer_example_on_cpu():
+    r = _run("examples/train_manual_reducer.py", "--cpu", "--steps", "16", "--warmup-steps", "4")
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "bytes held / bytes sent" in r.stdout
+    first, last = (float(x) for x in (r.stdout.split("first loss ")[1].split()[0], r.stdout.split("last loss ")[1].split()[0]))
+    assert last < first   # it learns through the packet path
