@@ -209,8 +209,13 @@ def main() -> int:
         }
         if hook is not None:
             st = hook.get_stats()
+            gains = st.get("pred_gain_per_bucket") or {}
             out["compression"] = {"ratio": st.get("overall_compression_ratio"), "compressing": st["compression_enabled"],
-                                  "pred_gain": st.get("pred_gain_per_bucket"),
+                                  "pred_gain": gains,
+                                  # uniform random tokens give gradients with nothing to predict from step to step: the
+                                  # controller finds that out and holds the gain at 0 (bench/predictor_effect.py has a
+                                  # workload where it does not)
+                                  "buckets_with_prediction": (sum(1 for g in gains.values() if g > 0) / len(gains)) if gains else None,
                                   "hook_impl": "c++" if st.get("cpp_hook") else "python"}
         print(json.dumps(out))
     dist.barrier()
