@@ -419,6 +419,25 @@ def main():
     if what in ("all", "fsdp_truth"):
         fsdp_truth(dev, rank, world, results)
     if what in ("all", "fsdp"):
+        # the FSDP1 hook form (reference signature) on device tensors: fills `output` with this rank's reduced shard
+        from nangila.fsdp import NangilaFSDPState, nangila_fsdp_hook
+
+        state = NangilaFSDPState(None)
+        torch.manual_seed(50 + rank)
+        shard_n = 4096 * 5
+        for unit in range(2):                       # two units of the same size in one step
+            full = (torch.randn(shard_n * world, device=dev) * 0.01).to(torch.bfloat16)
+            want = full.float().clone()
+            dist.all_reduce(want)
+            want = (want / world)[rank * shard_n:(rank + 1) * shard_n]
+            shard = torch.empty(shard_n, device=dev, dtype=torch.bfloat16)
+            nangila_fsdp_hook(state, full, shard)
+            state.reduce_scatter().check_status()
+            rel = ((shard.float() - want).norm() / want.norm()).item()
+            assert rel < 0.15, rel
+        state.step()
+        assert state.reduce_scatter().units_seen == 2 and state.step_counter() == 1
+        results["fsdp1_hook_rel"] = rel
         base, _ = train_fsdp(dev, rank, world, False, 60)
         ours, info = train_fsdp(dev, rank, world, True, 60)
         results["fsdp_loss_base"] = sum(base[-10:]) / 10
