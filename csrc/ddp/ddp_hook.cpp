@@ -14,6 +14,11 @@
 // and by the time a waiting phase starts the peers have usually delivered: the kernel no longer sits on
 // the SMs spinning while ranks are skewed. The bucket's future completes after its last phase.
 //
+// Two ways in. `run(bucket)` is what a Python comm hook calls (DDP then wants a Python future). With
+// `register_native(reducer)` the hook is installed on DDP's reducer as a C++ CommHookInterface: the reducer
+// calls it from the autograd thread without entering the interpreter at all; Python is touched only when
+// a bucket is seen for the first time (its symmetric memory comes from a Python allocator).
+//
 // Counterpart of nangila::NangilaDDPHook in the reference (nangila_ddp/src/ddp_hook.cpp:45-372),
 // which per bucket ran a compress kernel, two all-gathers with host synchronisation, one reconstruct
 // kernel per rank, an accumulate / divide and two history copies.
@@ -21,6 +26,8 @@
 #include <ATen/cuda/CUDAEvent.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <torch/csrc/distributed/c10d/comm.hpp>
+#include <torch/csrc/distributed/c10d/reducer.hpp>
 #include <torch/csrc/jit/python/pybind_utils.h>
 #include <torch/extension.h>
 
@@ -88,7 +95,8 @@ struct Pending {
   NangilaPredResParams p;
   int next_bit;   // phase bit to launch next (2 or 4)
   int last_bit;   // final phase bit of this exchange (2 in gather mode, 4 otherwise)
-  std::shared_ptr<torch::jit::PythonFutureWrapper> fut;
+  std::shared_ptr<torch::jit::PythonFutureWrapper> fut;      // Python entry: the future's value is a Python object
+  c10::intrusive_ptr<c10::ivalue::Future> native_fut;        // native entry: the value is the bucket tensor
   at::Tensor tensor;
   Bucket* bucket;
 };
@@ -157,12 +165,30 @@ class DdpHook {
 
   // `is_last`: no further bucket follows in this iteration, so nothing may stay deferred.
   py::object run_tensor(int64_t index, at::Tensor tensor, bool is_last) {
+    std::shared_ptr<torch::jit::PythonFutureWrapper> wrapper;
+    run_impl(index, std::move(tensor), is_last, &wrapper, nullptr);
+    return py::cast(wrapper);
+  }
+
+  // Entry of the reducer-level hook: no interpreter involved.
+  c10::intrusive_ptr<c10::ivalue::Future> run_native(int64_t index, at::Tensor tensor, bool is_last) {
+    c10::intrusive_ptr<c10::ivalue::Future> fut;
+    run_impl(index, std::move(tensor), is_last, nullptr, &fut);
+    return fut;
+  }
+
+  // Installs this hook on a DDP reducer (``ddp_model.reducer``) as a C++ communication hook.
+  static void register_native(std::shared_ptr<DdpHook> self, py::object reducer);
+
+  void run_impl(int64_t index, at::Tensor tensor, bool is_last, std::shared_ptr<torch::jit::PythonFutureWrapper>* py_out,
+                c10::intrusive_ptr<c10::ivalue::Future>* native_out) {
     TORCH_CHECK(attached_, "nangila: attach() was not called");
     TORCH_CHECK(tensor.is_cuda() && tensor.is_contiguous(), "nangila: the C++ hook needs a contiguous CUDA bucket");
     TORCH_CHECK((reinterpret_cast<uintptr_t>(tensor.data_ptr()) & 15u) == 0, "nangila: bucket must be 16-byte aligned");
     c10::cuda::CUDAGuard guard(tensor.device());
     std::vector<Pending> finished;  // futures to complete once the state lock is released
     std::shared_ptr<torch::jit::PythonFutureWrapper> wrapper;
+    c10::intrusive_ptr<c10::ivalue::Future> native_fut;
     {
     std::lock_guard<std::mutex> lock(mutex_);
     ensure_device(tensor);
@@ -249,9 +275,14 @@ class DdpHook {
     TORCH_CHECK(err == 0, "nangila: predres_launch failed: ", cudaGetErrorString(static_cast<cudaError_t>(err)));
     std::swap(b.prev, b.curr);
 
-    // DDP's Python-hook adapter expects the future's value to be a Python object (the bucket tensor).
-    auto fut = c10::make_intrusive<c10::ivalue::Future>(c10::PyObjectType::get(), std::vector<c10::Device>{tensor.device()});
-    wrapper = std::make_shared<torch::jit::PythonFutureWrapper>(fut);
+    apply_restore(index, b, tensor);
+    if (py_out != nullptr) {
+      // DDP's Python-hook adapter expects the future's value to be a Python object (the bucket tensor).
+      auto fut = c10::make_intrusive<c10::ivalue::Future>(c10::PyObjectType::get(), std::vector<c10::Device>{tensor.device()});
+      wrapper = std::make_shared<torch::jit::PythonFutureWrapper>(fut);
+    } else {
+      native_fut = c10::make_intrusive<c10::ivalue::Future>(c10::TensorType::get(), std::vector<c10::Device>{tensor.device()});
+    }
     // older buckets advance by one phase each (oldest first); then this one joins the queue
     advance_pending(finished, /*drain=*/false);
     if (split) {
@@ -261,6 +292,7 @@ class DdpHook {
       q.next_bit = 2;
       q.last_bit = p.gather != 0 ? 2 : 4;
       q.fut = wrapper;
+      q.native_fut = native_fut;
       q.tensor = tensor;
       q.bucket = &b;
       pending_.push_back(std::move(q));
@@ -268,6 +300,7 @@ class DdpHook {
       if (timing_) b.t1->record(*stream_);
       Pending q;
       q.fut = wrapper;
+      q.native_fut = native_fut;
       q.tensor = tensor;
       q.bucket = &b;
       finished.push_back(std::move(q));
@@ -279,7 +312,8 @@ class DdpHook {
     // the reducer's wait orders its own stream after everything queued on the exchange stream so far,
     // which includes the bucket's last phase.
     complete(finished);
-    return py::cast(wrapper);
+    if (py_out != nullptr) *py_out = wrapper;
+    if (native_out != nullptr) *native_out = native_fut;
   }
 
   // Once per optimizer step, after the last bucket was queued.
@@ -311,7 +345,17 @@ class DdpHook {
   }
 
   int64_t current_step() const { return step_; }
-  bool is_compression_enabled() const { return step_ >= warmup_steps_ && !paused_ && !paused_override_; }
+  bool is_compression_enabled() const {
+    return step_ >= warmup_steps_ && step_ >= exact_until_ && !paused_ && !paused_override_;
+  }
+  // Resume: gradients are exchanged uncompressed before `step` (a new DDP instance lays its buckets out in
+  // construction order for one iteration); saved bucket state given to restore_bucket() is copied into a
+  // bucket the first time it appears with the saved size at or after that step.
+  void set_exact_until(int64_t step) { exact_until_ = step; }
+  void restore_bucket(int64_t index, at::Tensor prev, at::Tensor curr, c10::optional<at::Tensor> ef) {
+    std::lock_guard<std::mutex> lock(mutex_);
+    restore_[index] = Restore{std::move(prev), std::move(curr), std::move(ef)};
+  }
   void fast_forward(int64_t to_step) { step_ = std::max(step_, to_step); }
   // Uncompressed exchange while set (safe-mode fallback, history re-seed after a failure).
   void set_paused(bool paused) { paused_override_ = paused; }
@@ -409,6 +453,26 @@ class DdpHook {
   }
 
  private:
+  struct Restore {
+    at::Tensor prev, curr;
+    c10::optional<at::Tensor> ef;
+  };
+  // Copies saved state into the bucket (on the exchange stream, before its kernel). Caller holds the lock.
+  void apply_restore(int64_t index, Bucket& b, const at::Tensor& tensor) {
+    if (restore_.empty() || step_ < exact_until_) return;
+    auto it = restore_.find(index);
+    if (it == restore_.end()) return;
+    if (it->second.prev.numel() == b.n && it->second.curr.numel() == b.n) {
+      c10::cuda::CUDAStreamGuard sg(*stream_);
+      b.prev.copy_(it->second.prev.to(b.prev.scalar_type()), /*non_blocking=*/true);
+      b.curr.copy_(it->second.curr.to(b.curr.scalar_type()), /*non_blocking=*/true);
+      if (error_feedback_ && it->second.ef.has_value() && it->second.ef->numel() == b.n)
+        b.ef.copy_(it->second.ef->to(b.ef.scalar_type()), /*non_blocking=*/true);
+    }
+    (void)tensor;
+    restore_.erase(it);
+  }
+
   // Queue the next phase of every deferred bucket (oldest first); with `drain`, keep going until nothing
   // is deferred. Buckets whose last phase has been queued move to `finished`. Caller holds the lock.
   void advance_pending(std::vector<Pending>& finished, bool drain) {
@@ -435,7 +499,10 @@ class DdpHook {
   void complete(std::vector<Pending>& finished) {
     if (finished.empty()) return;
     c10::cuda::CUDAStreamGuard sg(*stream_);
-    for (auto& q : finished) q.fut->markCompleted(py::cast(q.tensor));
+    for (auto& q : finished) {
+      if (q.native_fut) q.native_fut->markCompleted(c10::IValue(q.tensor));
+      else q.fut->markCompleted(py::cast(q.tensor));
+    }
     finished.clear();
   }
 
@@ -515,6 +582,8 @@ class DdpHook {
   int64_t num_layers_;
   int64_t warmup_steps_;
   int64_t step_ = 0;
+  int64_t exact_until_ = 0;
+  std::map<int64_t, Restore> restore_;
   bool paused_ = false;
   bool paused_override_ = false;
   std::optional<nangila::SafeMode> safe_mode_;
@@ -556,8 +625,38 @@ class DdpHook {
 
 }  // namespace
 
+// The reducer-level hook: what DDP's reducer calls for every ready bucket when the hook was installed with
+// register_native(). It shares ownership of the DdpHook with the Python object.
+class NativeCommHook : public c10d::CommHookInterface {
+ public:
+  explicit NativeCommHook(std::shared_ptr<DdpHook> owner) : owner_(std::move(owner)) {}
+  ~NativeCommHook() override {
+    // the DdpHook holds Python objects (the allocator callback): release it with the interpreter lock, and not
+    // at all once the interpreter is gone
+    if (Py_IsInitialized()) {
+      py::gil_scoped_acquire gil;
+      owner_.reset();
+    } else {
+      new std::shared_ptr<DdpHook>(std::move(owner_));  // deliberately leaked at process exit
+    }
+  }
+  c10::intrusive_ptr<c10::ivalue::Future> runHook(c10d::GradBucket& bucket) override {
+    return owner_->run_native(int64_t(bucket.getIndex()), bucket.getBufferRef(), bucket.isLast());
+  }
+  at::Tensor parseHookResult(const c10::IValue& result) override { return result.toTensor(); }
+
+ private:
+  std::shared_ptr<DdpHook> owner_;
+};
+
+void DdpHook::register_native(std::shared_ptr<DdpHook> self, py::object reducer) {
+  auto r = reducer.cast<std::shared_ptr<c10d::Reducer>>();
+  TORCH_CHECK(r != nullptr, "nangila: register_native() wants ddp_model.reducer");
+  r->register_comm_hook(std::make_unique<NativeCommHook>(std::move(self)));
+}
+
 void register_ddp_hook(py::module_& m) {
-  py::class_<DdpHook>(m, "NangilaDDPHook")
+  py::class_<DdpHook, std::shared_ptr<DdpHook>>(m, "NangilaDDPHook")
       .def(py::init<int64_t, int64_t>(), py::arg("num_layers"), py::arg("warmup_steps"))
       .def("attach", &DdpHook::attach, py::arg("rank"), py::arg("world"), py::arg("allocate"))
       .def("configure", &DdpHook::configure, py::arg("momentum") = 0.9, py::arg("error_feedback") = true,
@@ -565,6 +664,9 @@ void register_ddp_hook(py::module_& m) {
       .def("run", &DdpHook::run, py::arg("bucket"))
       .def("run_tensor", &DdpHook::run_tensor, py::arg("index"), py::arg("tensor"), py::arg("is_last") = true)
       .def("ensure_bucket", &DdpHook::ensure_bucket, py::arg("bucket"))
+      .def("register_native", &DdpHook::register_native, py::arg("reducer"))
+      .def("set_exact_until", &DdpHook::set_exact_until)
+      .def("restore_bucket", &DdpHook::restore_bucket, py::arg("index"), py::arg("prev"), py::arg("curr"), py::arg("ef") = py::none())
       .def("step", &DdpHook::step)
       .def("current_step", &DdpHook::current_step)
       .def("is_compression_enabled", &DdpHook::is_compression_enabled)

@@ -228,6 +228,7 @@ class NangilaDDPHook:
         self._pending_state: Dict[int, dict] = {}  # restored device state, applied when its bucket appears
         self._packet_filter = None   # tests: callable(step, layer_id, src_rank, bytes) -> bytes
         self._cpp = None             # NangilaCppHook once the first CUDA bucket went through it
+        self._native = False         # the C++ hook sits on DDP's reducer itself: __call__ is never reached
         self._param_ids: Dict[int, int] = {}
         # production counters (Prometheus text / JSON): fed once per step from the byte counters of whichever
         # path handled the buckets (reference: nangila-core/src/metrics.rs:12-232)
@@ -276,16 +277,32 @@ class NangilaDDPHook:
             if isinstance(src, torch.Tensor) and isinstance(dst, torch.Tensor) and src.numel() == dst.numel():
                 dst.copy_(src.to(dst.dtype))
 
+    def _make_cpp(self) -> "NangilaCppHook":
+        cpp = self._cpp = NangilaCppHook(
+            1, self.warmup_steps, self.process_group, momentum=self.momentum, error_feedback=self.error_feedback,
+            stochastic=self.stochastic,
+            reserve_bytes=(int(self._total_numel * 1.02) + (8 << 20)) if self._total_numel else None)
+        cpp.fast_forward(self.step_count)
+        self.hook.set_gpu_mode(True)
+        return cpp
+
+    def install_native(self, ddp_model: DDP) -> None:
+        """Put the C++ hook on DDP's reducer as a C++ communication hook: every bucket then goes from the reducer
+        to the fused kernel launch without entering the interpreter (``__call__`` of this object is never reached).
+        What this class does per bucket in Python moves to ``step()``: the pause flag of Safe Mode / recovery is
+        handed over once per step, and the device status is checked once per step (``sync_mode`` ALWAYS) or every
+        16th step (PERIODIC). Only for the prediction-residual compressor on CUDA parameters without a topology mask."""
+        device = next(p for p in ddp_model.parameters() if p.requires_grad).device
+        cpp = self._make_cpp()
+        cpp._attach(device)
+        cpp.register_native(ddp_model.reducer)
+        self._native = True
+
     def _run_cpp(self, bucket: GradBucket, tensor: torch.Tensor) -> torch.futures.Future:
         """Prediction-residual compressor through the C++ hook: everything per bucket is native."""
         cpp = self._cpp
         if cpp is None:
-            cpp = self._cpp = NangilaCppHook(
-                1, self.warmup_steps, self.process_group, momentum=self.momentum, error_feedback=self.error_feedback,
-                stochastic=self.stochastic,
-                reserve_bytes=(int(self._total_numel * 1.02) + (8 << 20)) if self._total_numel else None)
-            cpp.fast_forward(self.step_count)
-            self.hook.set_gpu_mode(True)
+            cpp = self._make_cpp()
         cpp.set_paused(self._force_uncompressed or self.hook.is_paused())
         if self._pending_state:
             index = int(bucket.index())
@@ -643,15 +660,24 @@ class NangilaDDPHook:
     # ------------------------------------------------------------------------------------------
     def step(self) -> None:
         """Call after each optimizer step."""
-        self._feed_metrics(self.compressing)
+        self._feed_metrics(self._cpp.is_compression_enabled() if self._native else self.compressing)
         self.step_count += 1
         self.layer_counter = 0
         self.hook.step()
         if self._engine is not None:
             self._engine.end_step()
+        failure: Optional[BaseException] = None
+        if self._native:
+            # the step that just ran was the uncompressed one a failure asked for (if any)
+            self._force_uncompressed = False
         if self._cpp is not None:
             self._cpp.step()  # sums the kernels' statistics over the group, then adapts the gains
-        if self._force_uncompressed:
+            if self._native and (self.sync_mode == 1 or (self.sync_mode == 2 and self.step_count % 16 == 0)):
+                try:
+                    self._check_device_status()   # sets _force_uncompressed when a kernel gave up waiting
+                except RuntimeError as exc:
+                    failure = exc
+        if self._force_uncompressed and not self._native:
             self._force_uncompressed = False  # one uncompressed step re-seeded the history everywhere
         if self.step_count % 10 == 0 and self.step_count > self.warmup_steps and _LOG in ("info", "debug"):
             ratio = self.compression_ratio
@@ -660,6 +686,12 @@ class NangilaDDPHook:
                      f"{self.total_compressed_bytes / 1e6:.1f} MB ({ratio:.1f}x)")
         if self.step_count % 100 == 0 and self.step_count > 0:
             self._verify_predictor_hash()
+        if self._native:
+            # whatever pauses compression for the coming step (Safe Mode, recovery after a failed exchange, a
+            # predictor-hash mismatch) is handed to the reducer-level hook here, once per step
+            self._cpp.set_paused(self._force_uncompressed or self.hook.is_paused())
+        if failure is not None:
+            raise failure
 
     def _byte_counters(self) -> tuple:
         """(bytes the buckets held, bytes that would cross the wire per peer) so far, whichever path ran."""
@@ -816,6 +848,13 @@ class NangilaDDPHook:
         self._exact_until_step = self.step_count + 1
         if self._cpp is not None:
             self._cpp.fast_forward(self.step_count)
+        if self._native:
+            # the reducer-level hook does the same in C++: one uncompressed step, then saved state per bucket
+            self._cpp.set_exact_until(self._exact_until_step)
+            for idx, st in self._pending_state.items():
+                if isinstance(st.get("prev"), torch.Tensor) and isinstance(st.get("curr"), torch.Tensor):
+                    self._cpp.restore_bucket(idx, st["prev"], st["curr"], st.get("ef") if isinstance(st.get("ef"), torch.Tensor) else None)
+            self._pending_state = {}
 
     def enable_safe_mode(self, config=None) -> None:
         from ._C import SafeModeConfig
@@ -869,7 +908,12 @@ def register_nangila_hook(
     # NANGILA_PREFER_CPP=0/1 overrides the argument (to compare the two hook implementations)
     hook.prefer_cpp = bool(int(os.environ.get("NANGILA_PREFER_CPP", int(bool(prefer_cpp)))))
     hook._param_ids = {id(p): i for i, p in enumerate(ddp_model.parameters())}
-    ddp_model.register_comm_hook(state=None, hook=hook)
+    native = (hook.prefer_cpp and CPP_HOOK_AVAILABLE and int(compressor_type) == 0 and not hook._passengers
+              and bool(params) and all(p.is_cuda for p in params) and os.environ.get("NANGILA_NATIVE_HOOK", "1") != "0")
+    if native:
+        hook.install_native(ddp_model)   # C++ hook on the reducer: no Python per bucket
+    else:
+        ddp_model.register_comm_hook(state=None, hook=hook)
     return hook
 
 

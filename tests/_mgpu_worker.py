@@ -405,7 +405,7 @@ def main():
         results["loss_ours_python_hook"] = sum(py_losses[-10:]) / 10
         assert not py_stats.get("cpp_hook") and py_stats["kernel_launches"] > 0
         assert results["loss_base"] < 0.8 * base[0], "baseline did not learn"
-        tol = float(os.environ.get("NANGILA_TEST_LOSS_TOL", "0.03"))
+        tol = float(os.environ.get("NANGILA_TEST_LOSS_TOL", "0.02"))  # measured: 1e-5 at 4 GPUs, 1e-3 at 2
         assert abs(results["loss_ours_python_hook"] - results["loss_base"]) < tol * results["loss_base"] + 0.02, results
         assert abs(results["loss_ours"] - results["loss_base"]) < tol * results["loss_base"] + 0.02, results
     if what in ("all", "compressors"):
