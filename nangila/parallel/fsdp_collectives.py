@@ -199,8 +199,12 @@ class NangilaReduceScatter(_Base, ReduceScatter):
         key = (n, inputs[0].dtype)
         st = self._regions.get(key)
         if st is None:
-            # 256 chunks per shard, at most 64 K elements each (every chunk costs a flag round trip)
-            chunk = _chunk_for(n // self.world, per_shard=256, cap=65536)
+            # Phase 2 has one task per chunk of this rank's shard: the chunk size is chosen so that those tasks fill
+            # the CTAs the device holds at once in whole waves (256 chunks of 64 K elements per shard left more than
+            # half of them idle in that phase)
+            env = os.environ.get("NANGILA_CHUNK")
+            resident = max(1, int(self._glue.predres_resident_ctas()) // self.nvr)
+            chunk = int(env) if env else int(self._glue.predres_chunk_elems(n // self.world, resident))
             total, r1, f1, nchunks = self._glue.rs_region_layout(n, self.world, chunk)
             st = dict(region=arena.allocate(int(total)), r1=r1, f1=f1, nchunks=nchunks, chunk=chunk, epoch=0)
             self._regions[key] = st
