@@ -325,8 +325,12 @@ void ag_launch(const std::vector<at::Tensor>& input, const std::vector<at::Tenso
 
 // ---- PowerSGD (tcgen05) ----------------------------------------------------------------------------------
 // out (rows x 16 fp32) = M * Bt^T or M^T * Bt^T; zero-fills `out` first (the kernel may split K).
+// With `counters` (int32, tiles + 1 zero words) the GEMM's epilogue also starts the cross-rank exchange of its result:
+// see nangila_psgd_gemm_push(). The remaining push_* arguments describe the exchange region of this factor.
 void psgd_gemm(const at::Tensor& M, const at::Tensor& Bt, bool transposed, at::Tensor out, at::Tensor status,
-               double timeout_s, bool zero_out) {
+               double timeout_s, bool zero_out, const c10::optional<at::Tensor>& counters,
+               const std::vector<int64_t>& push_region_ptrs, int64_t push_recv_off, int64_t push_flag_off, int64_t push_me,
+               int64_t push_rank, int64_t push_epoch, const c10::optional<at::Tensor>& push_epoch_word) {
   TORCH_CHECK(M.is_cuda() && M.dim() == 2 && M.scalar_type() == at::kBFloat16 && M.is_contiguous(), "nangila: M must be a contiguous bf16 matrix");
   const int64_t m = M.size(0), n = M.size(1);
   const int64_t k = transposed ? m : n, rows = transposed ? n : m;
@@ -334,9 +338,30 @@ void psgd_gemm(const at::Tensor& M, const at::Tensor& Bt, bool transposed, at::T
   TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == rows * 16, "nangila: out must be fp32[rows, 16]");
   c10::cuda::CUDAGuard guard(M.device());
   if (zero_out) out.zero_();  // split-K partial sums are added with atomics
-  check_launch(nangila_psgd_gemm(M.data_ptr(), int32_t(m), int32_t(n), Bt.data_ptr(), transposed ? 1 : 0, out.data_ptr<float>(),
-                                 reinterpret_cast<uint32_t*>(status.data_ptr<int32_t>()), uint64_t(timeout_s * 1e9),
-                                 at::cuda::getCurrentCUDAStream()), "psgd_gemm");
+  NangilaPsgdPush push;
+  std::memset(&push, 0, sizeof push);
+  const bool pushing = counters.has_value();
+  if (pushing) {
+    const int64_t tiles = (rows + 127) / 128;
+    TORCH_CHECK(counters->is_cuda() && counters->scalar_type() == at::kInt && counters->is_contiguous() && counters->numel() >= tiles + 1,
+                "nangila: counters must be an int32 CUDA tensor of tiles + 1 words");
+    TORCH_CHECK(!push_region_ptrs.empty() && int64_t(push_region_ptrs.size()) <= NANGILA_MAX_RANKS, "nangila: bad push regions");
+    push.counters = reinterpret_cast<uint32_t*>(counters->data_ptr<int32_t>());
+    push.world = int32_t(push_region_ptrs.size());
+    push.me = int32_t(push_me);
+    push.rank = int32_t(push_rank);
+    push.recv_off = uint64_t(push_recv_off);
+    push.flag_off = uint64_t(push_flag_off);
+    push.epoch = uint32_t(push_epoch);
+    if (push_epoch_word.has_value()) {
+      TORCH_CHECK(push_epoch_word->is_cuda() && push_epoch_word->scalar_type() == at::kInt, "nangila: the epoch word must be an int32 CUDA tensor");
+      push.epoch_dev = reinterpret_cast<const uint32_t*>(push_epoch_word->data_ptr<int32_t>());
+    }
+    for (size_t r = 0; r < push_region_ptrs.size(); ++r) push.region[r] = as_ptr(push_region_ptrs[r]);
+  }
+  check_launch(nangila_psgd_gemm_push(M.data_ptr(), int32_t(m), int32_t(n), Bt.data_ptr(), transposed ? 1 : 0, out.data_ptr<float>(),
+                                      pushing ? &push : nullptr, reinterpret_cast<uint32_t*>(status.data_ptr<int32_t>()),
+                                      uint64_t(timeout_s * 1e9), at::cuda::getCurrentCUDAStream()), "psgd_gemm");
 }
 void psgd_prep(const at::Tensor& grad, const at::Tensor& ef, at::Tensor mef, c10::optional<at::Tensor> clear0,
                c10::optional<at::Tensor> clear1) {
@@ -376,7 +401,7 @@ void psgd_exchange(const std::vector<at::Tensor>& local, const std::vector<at::T
                    const std::vector<at::Tensor>& scratch, const std::vector<at::Tensor>& t_out,
                    const std::vector<at::Tensor>& status, const std::vector<int64_t>& region_ptrs, int64_t recv_off,
                    int64_t flag_off, int64_t rows, int64_t rank, int64_t rank0, bool orth_mean, int64_t epoch,
-                   double timeout_s, const c10::optional<at::Tensor>& epoch_word) {
+                   double timeout_s, const c10::optional<at::Tensor>& epoch_word, bool pushed) {
   const size_t nvr = local.size();
   TORCH_CHECK(nvr >= 1 && nvr <= NANGILA_MAX_VRANKS && mean_out.size() == nvr && scratch.size() == nvr && t_out.size() == nvr &&
                   status.size() == nvr, "nangila: list length mismatch");
@@ -388,6 +413,7 @@ void psgd_exchange(const std::vector<at::Tensor>& local, const std::vector<at::T
   p.rank0 = int32_t(rank0);
   p.nvr = int32_t(nvr);
   p.orth_mean = orth_mean ? 1 : 0;
+  p.pushed = pushed ? 1 : 0;
   p.epoch = uint32_t(epoch);
   if (epoch_word.has_value()) {
     TORCH_CHECK(epoch_word->is_cuda() && epoch_word->scalar_type() == at::kInt && epoch_word->numel() >= 1,
@@ -426,14 +452,17 @@ void register_more(py::module_& m) {
         py::arg("k"), py::arg("capacity"), py::arg("epoch"), py::arg("momentum"), py::arg("timeout_s"),
         py::arg("grid_x"));
   m.def("psgd_gemm", &psgd_gemm, py::arg("M"), py::arg("Bt"), py::arg("transposed"), py::arg("out"), py::arg("status"),
-        py::arg("timeout_s"), py::arg("zero_out") = true);
+        py::arg("timeout_s"), py::arg("zero_out") = true, py::arg("counters") = py::none(),
+        py::arg("push_region_ptrs") = std::vector<int64_t>{}, py::arg("push_recv_off") = 0, py::arg("push_flag_off") = 0,
+        py::arg("push_me") = 0, py::arg("push_rank") = 0, py::arg("push_epoch") = 0, py::arg("push_epoch_word") = py::none());
   m.def("psgd_prep", &psgd_prep, py::arg("grad"), py::arg("ef"), py::arg("mef"), py::arg("clear0") = py::none(),
         py::arg("clear1") = py::none());
   m.def("psgd_reconstruct", &psgd_reconstruct);
   m.def("psgd_exchange_layout", &psgd_exchange_layout);
   m.def("psgd_exchange", &psgd_exchange, py::arg("local"), py::arg("mean_out"), py::arg("scratch"), py::arg("t_out"),
         py::arg("status"), py::arg("region_ptrs"), py::arg("recv_off"), py::arg("flag_off"), py::arg("rows"), py::arg("rank"),
-        py::arg("rank0"), py::arg("orth_mean"), py::arg("epoch"), py::arg("timeout_s"), py::arg("epoch_word") = py::none());
+        py::arg("rank0"), py::arg("orth_mean"), py::arg("epoch"), py::arg("timeout_s"), py::arg("epoch_word") = py::none(),
+        py::arg("pushed") = false);
   m.def("rs_region_layout", &rs_region_layout);
   m.def("rs_launch", &rs_launch);
   m.def("ag_region_layout", &ag_region_layout);

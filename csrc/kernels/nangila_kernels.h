@@ -111,6 +111,21 @@ int nangila_ag_launch(const NangilaAgParams* p, cudaStream_t stream);
  * (transposed = 1, rows = n). M: m x n bf16 row-major, m and n multiples of 8. Bt: 16 x K bf16. */
 int nangila_psgd_gemm(const void* M, int32_t m, int32_t n, const void* Bt, int32_t transposed, float* out,
                       uint32_t* status, uint64_t timeout_ns, cudaStream_t stream);
+/* The same GEMM with the cross-rank exchange of its result started from the epilogue: the CTA that completes a
+ * 128-row tile of `out` (the last of the tile's K splits to arrive) stores the tile's first `rank` columns, column-major,
+ * into slot [me] of EVERY rank's exchange region (peer stores over NVLink, this rank's own region included), and the CTA
+ * that completes the last tile releases the flags. nangila_psgd_exchange() is then launched with `pushed = 1` and only
+ * waits, averages and orthonormalises. `counters`: tiles + 1 zero words (arrivals per tile, finished tiles). */
+typedef struct NangilaPsgdPush {
+  uint8_t* region[NANGILA_MAX_RANKS];
+  uint64_t recv_off, flag_off;             /* layout of nangila_psgd_exchange_region_bytes(rows, rank, world) */
+  int32_t world, me, rank;
+  uint32_t epoch;
+  const uint32_t* epoch_dev;               /* if not NULL the epoch is read from this device word */
+  uint32_t* counters;
+} NangilaPsgdPush;
+int nangila_psgd_gemm_push(const void* M, int32_t m, int32_t n, const void* Bt, int32_t transposed, float* out,
+                           const NangilaPsgdPush* push, uint32_t* status, uint64_t timeout_ns, cudaStream_t stream);
 /* mef = grad + ef; also clears z0[0..n0) and z1[0..n1) (the projections' accumulators; either may be NULL / 0) */
 int nangila_psgd_prep(const void* grad, int32_t dtype, const void* ef, void* mef, int64_t numel, float* z0, int64_t n0,
                       float* z1, int64_t n1, cudaStream_t stream);
@@ -125,6 +140,8 @@ typedef struct NangilaPsgdExchangeParams {
   uint8_t* region[NANGILA_MAX_RANKS];
   uint64_t recv_off, flag_off;
   int32_t rows, rank, world, rank0, nvr, orth_mean;
+  int32_t pushed;                           /* 1: the factors are already in the slots and the flags released (or being
+                                               released) by nangila_psgd_gemm_push(); `local` is not read */
   uint32_t epoch;
   uint64_t timeout_ns;
   const uint32_t* epoch_dev;                /* if not NULL the epoch is read from this device word instead of `epoch`:

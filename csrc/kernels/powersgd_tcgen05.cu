@@ -19,6 +19,7 @@
 // (nangila-core/src/power_sgd.rs:46-193: ndarray GEMMs on the host, per-rank factors shipped and W
 // dense reconstructions averaged). Here P and Q' are averaged across ranks (standard PowerSGD).
 #include <algorithm>
+#include <cstring>
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -46,7 +47,7 @@ constexpr int kBBytes = kCols * kSlabK * 2;      // 2 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kGemmThreads = 128;
 constexpr int kTmemCols = 32;
-constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers and flags*/;
 
 // One CTA computes out[row0 .. row0+127][0..15] (+)= sum over its K range.
 //  A_MN = false: tmA is a map of M (inner dim = K), box {64, 128}; the A stage is one box.
@@ -57,7 +58,7 @@ template <bool A_MN>
 __global__ void __launch_bounds__(kGemmThreads)
 psgd_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  float* __restrict__ out, int rows_out, int k_total, int k_per_split, int use_atomics,
-                 uint32_t* status, uint64_t timeout_ns) {
+                 uint32_t* status, uint64_t timeout_ns, const __grid_constant__ NangilaPsgdPush push) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -65,6 +66,7 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* accum_done = empty + kStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_done + 1);
   uint32_t* failed = tmem_slot + 1;
+  uint32_t* last_of_tile = failed + 1;   // this CTA completed its row tile (epilogue push)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = blockIdx.x * kTileRows;
@@ -164,6 +166,48 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+
+  // ---------------- exchange started from the epilogue ----------------
+  // Whichever of a tile's K splits arrives last finds the complete tile in `out` (its own part went there above,
+  // the others' were fenced before they counted themselves in) and stores it into every rank's slot for this
+  // rank. A CTA whose pipeline failed still counts itself in, so that nobody waits for it; the status block says
+  // that the data is not to be trusted.
+  if (push.counters != nullptr) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *last_of_tile = atomicAdd(&push.counters[blockIdx.x], 1u) == gridDim.y - 1 ? 1u : 0u;
+    __syncthreads();
+    if (*last_of_tile != 0u) {
+      __threadfence();
+      const uint32_t epoch = push.epoch_dev != nullptr ? *push.epoch_dev : push.epoch;
+      const int W = push.world, r = push.rank;
+      const uint64_t slot_bytes = (uint64_t(rows_out) * r * 4 + 255) & ~uint64_t(255);
+      const uint64_t base = push.recv_off + uint64_t(epoch & 1u) * W * slot_bytes + uint64_t(push.me) * slot_bytes;
+      const int row = row0 + warp * 32 + lane;
+      if (row < rows_out) {
+        float v[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; c += 4) {
+          const float4 a = __ldcg(reinterpret_cast<const float4*>(out + int64_t(row) * kCols + c));
+          v[c] = a.x; v[c + 1] = a.y; v[c + 2] = a.z; v[c + 3] = a.w;
+        }
+        for (int d = 0; d < W; ++d) {
+          float* dst = reinterpret_cast<float*>(push.region[(push.me + d) % W] + base);
+          for (int c = 0; c < r; ++c) dst[int64_t(c) * rows_out + row] = v[c];   // adjacent rows: adjacent addresses
+        }
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const uint32_t tiles = gridDim.x;
+        if (atomicAdd(&push.counters[tiles], 1u) == tiles - 1) {
+          __threadfence_system();  // every tile's stores were fenced before its CTA counted itself in
+          for (int d = 0; d < W; ++d)
+            st_release_sys(reinterpret_cast<uint32_t*>(push.region[d] + push.flag_off) + push.me, epoch);
+        }
+      }
+    }
+  }
 }
 
 // ---- prep / reconstruct (element-wise) -----------------------------------------------------------------
@@ -276,15 +320,18 @@ __global__ void __launch_bounds__(kXThreads) psgd_exchange_kernel(const __grid_c
   __shared__ float s_rinv[kCols][kCols];    // R^-1 (upper triangular); a zero column for a vanished pivot
   __shared__ int s_ok;
 
-  // 1. store my rows of my factor (r columns, column-major) into every rank's slot [me]
-  for (int d = 0; d < W; ++d) {
-    float* dst = reinterpret_cast<float*>(p.region[(me + d) % W] + base + uint64_t(me) * slot_bytes);
-    for (int c = 0; c < r; ++c)
-      for (int i = r0 + tid; i < r1; i += kXThreads) dst[int64_t(c) * rows + i] = local[int64_t(i) * kCols + c];
+  // 1. store my rows of my factor (r columns, column-major) into every rank's slot [me] (unless the GEMM's
+  //    epilogue has done that already)
+  if (p.pushed == 0) {
+    for (int d = 0; d < W; ++d) {
+      float* dst = reinterpret_cast<float*>(p.region[(me + d) % W] + base + uint64_t(me) * slot_bytes);
+      for (int c = 0; c < r; ++c)
+        for (int i = r0 + tid; i < r1; i += kXThreads) dst[int64_t(c) * rows + i] = local[int64_t(i) * kCols + c];
+    }
+    __threadfence_system();
   }
-  __threadfence_system();
   cluster.sync();
-  if (g == 0 && tid < W) {
+  if (p.pushed == 0 && g == 0 && tid < W) {
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t*>(p.region[tid] + p.flag_off) + me, epoch);
   }
@@ -455,7 +502,23 @@ int pick_splits(int tiles, int k_total) {
 // `out` must be zero-filled when the launch splits K (it always may: zero it).
 extern "C" int nangila_psgd_gemm(const void* M, int32_t m, int32_t n, const void* Bt, int32_t transposed, float* out,
                                  uint32_t* status, uint64_t timeout_ns, cudaStream_t stream) {
+  return nangila_psgd_gemm_push(M, m, n, Bt, transposed, out, nullptr, status, timeout_ns, stream);
+}
+
+extern "C" int nangila_psgd_gemm_push(const void* M, int32_t m, int32_t n, const void* Bt, int32_t transposed, float* out,
+                                      const NangilaPsgdPush* push_in, uint32_t* status, uint64_t timeout_ns,
+                                      cudaStream_t stream) {
   using namespace nangila;
+  NangilaPsgdPush push;
+  std::memset(&push, 0, sizeof push);
+  if (push_in != nullptr) {
+    push = *push_in;
+    if (push.counters == nullptr || push.world < 1 || push.world > NANGILA_MAX_RANKS || push.me < 0 || push.me >= push.world ||
+        push.rank < 1 || push.rank > 16 || (push.epoch == 0 && push.epoch_dev == nullptr))
+      return int(cudaErrorInvalidValue);
+    for (int r = 0; r < push.world; ++r)
+      if (push.region[r] == nullptr) return int(cudaErrorInvalidValue);
+  }
   if (!M || !Bt || !out || !status || m <= 0 || n <= 0 || (n % 8) != 0 || (m % 8) != 0 ||
       (reinterpret_cast<uintptr_t>(M) & 15u) || (reinterpret_cast<uintptr_t>(Bt) & 15u) ||
       (reinterpret_cast<uintptr_t>(out) & 15u))
@@ -482,7 +545,7 @@ extern "C" int nangila_psgd_gemm(const void* M, int32_t m, int32_t n, const void
       attr1 = true;
     }
     psgd_gemm_kernel<true><<<grid, block, kGemmSmem, stream>>>(tmA, tmB, out, rows, k_total, k_per_split, nsplit > 1, status,
-                                                              timeout_ns);
+                                                              timeout_ns, push);
   } else {
     static bool attr0 = false;
     if (!attr0) {
@@ -490,7 +553,7 @@ extern "C" int nangila_psgd_gemm(const void* M, int32_t m, int32_t n, const void
       attr0 = true;
     }
     psgd_gemm_kernel<false><<<grid, block, kGemmSmem, stream>>>(tmA, tmB, out, rows, k_total, k_per_split, nsplit > 1, status,
-                                                               timeout_ns);
+                                                               timeout_ns, push);
   }
   e = cudaGetLastError();
   return int(e);

@@ -48,6 +48,10 @@ class MatrixState:
     pt: List[torch.Tensor]       # bf16 [16, m]
     p_local: List[torch.Tensor]  # fp32 [m, 16]
     q_local: List[torch.Tensor]  # fp32 [n, 16]
+    p_full: List[torch.Tensor]   # p_local plus the tile counters of the GEMM's epilogue push, cleared together
+    q_full: List[torch.Tensor]
+    p_cnt: List[torch.Tensor]    # int32 view of the counters
+    q_cnt: List[torch.Tensor]
     p_mean: List[torch.Tensor]
     q_mean: List[torch.Tensor]
     scratch: List[torch.Tensor]  # fp32 [max(m, n), 16]
@@ -93,6 +97,7 @@ class PowerSGDEngine:
         self.timeout_s = float(os.environ.get("NANGILA_WAIT_TIMEOUT_MS", "2000")) / 1e3 if timeout_s is None else timeout_s
         self.states: Dict[tuple, MatrixState] = {}
         self.use_graphs = os.environ.get("NANGILA_PSGD_GRAPH", "1") != "0"
+        self.push_from_gemm = os.environ.get("NANGILA_PSGD_PUSH", "1") != "0"
         self._graphs: Dict[int, tuple] = {}   # bucket index -> (key, CUDAGraph, epoch word, launches recorded)
         self.graph_replays = 0
         self._capture_stream: Optional[torch.cuda.Stream] = None
@@ -113,9 +118,16 @@ class PowerSGDEngine:
         tot_p, rp, fp = self._glue.psgd_exchange_layout(m, r, self.world)
         tot_q, rq, fq = self._glue.psgd_exchange_layout(n, r, self.world)
         q0 = initial_qt(n, r, dev)
+        # accumulators of the two projections, each followed by its tile counters (tiles + 1 words, padded)
+        pt_words, qt_words = (m + 127) // 128 + 1, (n + 127) // 128 + 1
+        p_full = z(m * 16 + (pt_words + 3) // 4 * 4)
+        q_full = z(n * 16 + (qt_words + 3) // 4 * 4)
         st = MatrixState(m=m, n=n, r=r, mef=z(m, n, dt=torch.bfloat16), ef=z(m, n, dt=torch.bfloat16),
                          qt=[q0.clone() for _ in range(self.nvr)], pt=z(16, m, dt=torch.bfloat16),
-                         p_local=z(m, 16), q_local=z(n, 16), p_mean=z(m, 16), q_mean=z(n, 16),
+                         p_local=[t[:m * 16].view(m, 16) for t in p_full], q_local=[t[:n * 16].view(n, 16) for t in q_full],
+                         p_full=p_full, q_full=q_full,
+                         p_cnt=[t[m * 16:].view(torch.int32) for t in p_full], q_cnt=[t[n * 16:].view(torch.int32) for t in q_full],
+                         p_mean=z(m, 16), q_mean=z(n, 16),
                          scratch=z(max(m, n), 16), region_p=self.arena.allocate(int(tot_p)),
                          region_q=self.arena.allocate(int(tot_q)), lay_p=(rp, fp), lay_q=(rq, fq))
         self.states[key] = st
@@ -134,15 +146,25 @@ class PowerSGDEngine:
         G = self._glue
         rank0 = 0 if self.loopback else self.rank
         flat = [g.reshape(m, n) for g in grads]
+        # The GEMMs start the exchange of their result from the epilogue: the CTA that completes a 128-row tile stores
+        # it into every rank's slot over NVLink, the one that completes the last tile releases the flags; the exchange
+        # kernel then only waits, averages and orthonormalises (NANGILA_PSGD_PUSH=0: it also does the stores).
+        push = self.push_from_gemm
         for v in range(self.nvr):
-            G.psgd_prep(flat[v], st.ef[v], st.mef[v], st.p_local[v], st.q_local[v])  # also clears both accumulators
-            G.psgd_gemm(st.mef[v], st.qt[v], False, st.p_local[v], self.status[v], self.timeout_s, False)
+            G.psgd_prep(flat[v], st.ef[v], st.mef[v], st.p_full[v], st.q_full[v])  # also clears accumulators and counters
+            G.psgd_gemm(st.mef[v], st.qt[v], False, st.p_local[v], self.status[v], self.timeout_s, False,
+                        **(dict(counters=st.p_cnt[v], push_region_ptrs=st.region_p.ptrs, push_recv_off=st.lay_p[0],
+                                push_flag_off=st.lay_p[1], push_me=rank0 + v, push_rank=st.r, push_epoch=st.epoch,
+                                push_epoch_word=epoch_word) if push else {}))
         G.psgd_exchange(st.p_local, st.p_mean, [s[:m] for s in st.scratch], st.pt, self.status, st.region_p.ptrs,
-                        st.lay_p[0], st.lay_p[1], m, st.r, rank0, True, st.epoch, self.timeout_s, epoch_word)
+                        st.lay_p[0], st.lay_p[1], m, st.r, rank0, True, st.epoch, self.timeout_s, epoch_word, push)
         for v in range(self.nvr):
-            G.psgd_gemm(st.mef[v], st.pt[v], True, st.q_local[v], self.status[v], self.timeout_s, False)
+            G.psgd_gemm(st.mef[v], st.pt[v], True, st.q_local[v], self.status[v], self.timeout_s, False,
+                        **(dict(counters=st.q_cnt[v], push_region_ptrs=st.region_q.ptrs, push_recv_off=st.lay_q[0],
+                                push_flag_off=st.lay_q[1], push_me=rank0 + v, push_rank=st.r, push_epoch=st.epoch,
+                                push_epoch_word=epoch_word) if push else {}))
         G.psgd_exchange(st.q_local, st.q_mean, [s[:n] for s in st.scratch], st.qt, self.status, st.region_q.ptrs,
-                        st.lay_q[0], st.lay_q[1], n, st.r, rank0, False, st.epoch, self.timeout_s, epoch_word)
+                        st.lay_q[0], st.lay_q[1], n, st.r, rank0, False, st.epoch, self.timeout_s, epoch_word, push)
         for v in range(self.nvr):
             G.psgd_reconstruct(flat[v], st.ef[v], st.mef[v], st.p_mean[v], st.q_mean[v], m, n, st.r)
         self.launches += 3 * self.nvr + 2 + self.nvr
