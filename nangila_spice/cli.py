@@ -35,6 +35,19 @@ def invoke_run(args) -> int:
 def invoke_synth(args) -> int:
     from .synth import C17_BENCH, bench_to_spice
 
+    if args.suite:
+        # the generated benchmark suite: one deck per ISCAS-class circuit plus the small reference circuits
+        from .benchcircuits import SUITE, write_suite
+
+        names = [n for n in (args.only.split(",") if args.only else SUITE)]
+        paths = write_suite(args.suite, names=names)
+        print(f"wrote {len(paths)} decks under {args.suite}")
+        return 0
+    if args.circuit:
+        from .benchcircuits import deck as suite_deck
+
+        sys.stdout.write(suite_deck(args.circuit))
+        return 0
     text = open(args.bench).read() if args.bench else C17_BENCH
     deck = bench_to_spice(text, title=os.path.basename(args.bench) if args.bench else "c17")
     if args.output:
@@ -97,6 +110,9 @@ def main(argv=None) -> int:
     s = sub.add_parser("synth", help="translate an ISCAS .bench gate list into a transistor-level deck")
     s.add_argument("bench", nargs="?", default=None)
     s.add_argument("-o", "--output", default=None)
+    s.add_argument("--suite", default=None, metavar="DIR", help="write the generated benchmark suite (auto_synth/, reference_circuits/) to DIR")
+    s.add_argument("--only", default=None, help="with --suite: comma list of circuit names (default: all 26)")
+    s.add_argument("--circuit", default=None, help="print the deck of one generated benchmark circuit (e.g. c6288, s1238)")
     w = sub.add_parser("sweep", help="PVT sweep over a deck")
     w.add_argument("netlist")
     w.add_argument("--corners", type=int, default=1000)

