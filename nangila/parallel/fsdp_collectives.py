@@ -65,6 +65,10 @@ class _Base:
         self.launches = 0
         self.fallbacks = 0
         self._glue = None
+        # CTAs per launch (NANGILA_FSDP_CTAS; 0: as many as there are chunks, clamped by the launcher to what the device
+        # holds at once). The collectives overlap with the layers' compute, so a cap trades their own speed for the SMs
+        # they take from it.
+        self.ctas = int(os.environ.get("NANGILA_FSDP_CTAS", "0"))
 
     def _ensure(self, device: torch.device, group: Optional[dist.ProcessGroup]):
         if self._glue is None:
@@ -216,7 +220,8 @@ class NangilaReduceScatter(_Base, ReduceScatter):
         cps = st["nchunks"] // self.world
         self._glue.rs_launch(inputs, outputs, ef, self._status, st["region"].ptrs, st["r1"], st["f1"], st["nchunks"],
                              0 if self.loopback else self.rank, st["chunk"], self.stochastic, st["epoch"], self.seed,
-                             self.step + u.calls, u.index, scale, self.timeout_s, max(1, cps * self.world))
+                             self.step + u.calls, u.index, scale, self.timeout_s,
+                             max(1, min(cps * self.world, self.ctas) if self.ctas > 0 else cps * self.world))
 
     def _reduce_predicted(self, u: _RsUnit, outputs: List[torch.Tensor], inputs: List[torch.Tensor], scale: float) -> None:
         from .predres_engine import PredResEngine
@@ -301,7 +306,7 @@ class NangilaAllGather(_Base, AllGather):
         cps = (shard + st["chunk"] - 1) // st["chunk"]
         self._glue.ag_launch(inputs, outputs, self._status, st["region"].ptrs, st["r"], st["f"],
                              0 if self.loopback else self.rank, st["chunk"], self.bits, st["epoch"], self.timeout_s,
-                             max(1, cps * (self.world + 1)))
+                             max(1, min(cps * (self.world + 1), self.ctas) if self.ctas > 0 else cps * (self.world + 1)))
 
     def __call__(self, output_tensor: torch.Tensor, input_tensor: torch.Tensor, group: dist.ProcessGroup,
                  async_op: bool = False):
