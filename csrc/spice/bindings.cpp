@@ -83,6 +83,7 @@ PYBIND11_MODULE(_native, m) {
         py::dict nr;
         nr["total_iterations"] = s.engine().newton.stats.total_iterations; nr["linear_solves"] = s.engine().newton.stats.linear_solves;
         nr["failed"] = s.engine().newton.stats.failed_count; nr["be_fallbacks"] = s.engine().be_fallbacks;
+        nr["step_cuts"] = s.engine().step_cuts; nr["dc_gmin_stepping"] = s.engine().dc_gmin_stepping;
         nr["device_solves"] = s.engine().newton.linear.stats.device_solves; nr["krylov_iterations"] = s.engine().newton.linear.stats.krylov_iterations;
         nr["krylov_fallbacks"] = s.engine().newton.linear.stats.krylov_fallbacks; nr["cuda_error"] = s.engine().newton.linear.cuda_error;
         out["newton"] = nr;

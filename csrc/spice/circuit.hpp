@@ -91,24 +91,23 @@ struct MosfetLevel1 {
     MosType kind = MosType::Nmos;
     double vth = 0.5, beta = 1e-3, lambda = 0.1;
 
-    // Drain current (into the drain for NMOS) and its derivatives w.r.t. vgs and vds.
+    // Drain current (into the drain for NMOS) and its derivatives w.r.t. vgs and vds. The device is
+    // symmetric: with vds < 0 drain and source trade places, so the current is the forward expression of
+    // (vgd, -vds), negated. Channel-length modulation multiplies the linear region too, which keeps the
+    // current continuous across the linear / saturation boundary (a jump there makes Newton oscillate
+    // whenever the solution sits on the boundary).
     void evaluate(double vgs, double vds, double& id, double& gm, double& gds, MosRegion& region) const {
-        double sign = kind == MosType::Nmos ? 1.0 : -1.0;
-        double vc = sign * vgs, vo = sign * vds;
-        double vov = vc - std::fabs(vth);
-        if (vov <= 0.0) { id = 0.0; gm = 1e-12; gds = 1e-12; region = MosRegion::Cutoff; return; }
-        if (vo < vov) {
-            id = sign * beta * (vov * vo - 0.5 * vo * vo);
-            gm = std::max(beta * vo, 1e-12);
-            gds = std::max(beta * (vov - vo), 1e-12);
-            region = MosRegion::Linear;
+        const double sign = kind == MosType::Nmos ? 1.0 : -1.0;
+        const double vc = sign * vgs, vo = sign * vds;
+        double i, fc, fo;
+        if (vo >= 0.0) {
+            forward(vc, vo, i, fc, fo, region);
+            id = sign * i; gm = fc; gds = fo;
         } else {
-            double clm = 1.0 + lambda * std::max(vo, 0.0);
-            id = sign * 0.5 * beta * vov * vov * clm;
-            gm = std::max(beta * vov * clm, 1e-12);
-            gds = std::max(0.5 * beta * vov * vov * lambda, 1e-12);
-            region = MosRegion::Saturation;
+            forward(vc - vo, -vo, i, fc, fo, region);
+            id = -sign * i; gm = -fc; gds = fc + fo;
         }
+        gds = std::max(gds, 1e-12);
     }
     // Linearisation around (vgs, vds): id ~ gm*vgs + gds*vds + ieq
     void companion(double vgs, double vds, double& gm, double& gds, double& ieq) const {
@@ -116,6 +115,26 @@ struct MosfetLevel1 {
         MosRegion r;
         evaluate(vgs, vds, id, gm, gds, r);
         ieq = id - gm * vgs - gds * vds;
+    }
+
+private:
+    // I(vc, vo) for vo >= 0 with its partial derivatives.
+    void forward(double vc, double vo, double& i, double& d_vc, double& d_vo, MosRegion& region) const {
+        const double vov = vc - std::fabs(vth);
+        if (vov <= 0.0) { i = d_vc = d_vo = 0.0; region = MosRegion::Cutoff; return; }
+        const double clm = 1.0 + lambda * vo;
+        if (vo < vov) {
+            const double core = vov * vo - 0.5 * vo * vo;
+            i = beta * core * clm;
+            d_vc = beta * vo * clm;
+            d_vo = beta * ((vov - vo) * clm + core * lambda);
+            region = MosRegion::Linear;
+        } else {
+            i = 0.5 * beta * vov * vov * clm;
+            d_vc = beta * vov * clm;
+            d_vo = 0.5 * beta * vov * vov * lambda;
+            region = MosRegion::Saturation;
+        }
     }
 };
 

@@ -34,6 +34,11 @@ struct NrConfig {
     double reltol = 1e-3;
     double abstol = 1e-6;
     double damping = 1.0;
+    // Largest change of one node voltage per iteration; the exponential and square-law devices are only
+    // linearised locally, so an unlimited update can jump into a region from which the iteration oscillates.
+    double max_dv = 0.6;
+    // How often solve_step may halve a step that did not converge (2^k sub-steps at most).
+    int max_cuts = 8;
 };
 
 struct NrStats {
@@ -55,8 +60,9 @@ public:
     NrStats stats;
     LinearSolver linear;
 
+    // The first `limited` unknowns are node voltages and get the per-iteration step limit.
     template <class Build>
-    NrOutcome solve(std::vector<double> guess, CsrMatrix& m, Build&& build) {
+    NrOutcome solve(std::vector<double> guess, CsrMatrix& m, Build&& build, int limited = 0) {
         NrOutcome out;
         out.x = std::move(guess);
         out.x.resize(size_t(m.n), 0.0);
@@ -69,7 +75,9 @@ public:
                 double vn = m.solution[size_t(i)], vo = out.x[size_t(i)];
                 double tol = config.reltol * std::max(std::fabs(vn), std::fabs(vo)) + config.abstol;
                 max_err = std::max(max_err, std::fabs(vn - vo) / std::max(tol, config.abstol));
-                out.x[size_t(i)] = vo + config.damping * (vn - vo);
+                double step = config.damping * (vn - vo);
+                if (i < limited && config.max_dv > 0.0) step = std::max(-config.max_dv, std::min(config.max_dv, step));
+                out.x[size_t(i)] = vo + step;
             }
             out.iterations = it + 1;
             out.final_error = max_err;
@@ -311,8 +319,24 @@ public:
         return solve_dc(seeded, dc) ? dc : seeded;
     }
 
+    // Plain Newton from the seeded state first; if that fails, conductance stepping: solve with a large
+    // conductance from every node to ground, then lower it by decades with the last solution as the guess.
     bool solve_dc(const PartitionState& seeded, PartitionState& out) {
         NrOutcome r = run_newton(seeded, {}, 0.0, 0.0, Integration::BackwardEuler);
+        if (!r.converged) {
+            const double target = asm_.gmin;
+            PartitionState g = seeded;
+            bool ok = true;
+            for (double gm = 1e-2; ok && gm > target * 1.5; gm *= 0.1) {
+                asm_.gmin = gm;
+                r = run_newton(g, {}, 0.0, 0.0, Integration::BackwardEuler);
+                ok = r.converged;
+                if (ok) g.voltages = r.x;
+            }
+            asm_.gmin = target;
+            if (ok) r = run_newton(g, {}, 0.0, 0.0, Integration::BackwardEuler);
+            ++dc_gmin_stepping;
+        }
         if (!r.converged) return false;
         out = PartitionState{0};
         out.voltages = r.x;
@@ -322,13 +346,31 @@ public:
 
     // One step of size dt from `cur`; ghost nodes are pinned to the given voltages. Trapezoidal when
     // capacitor currents are known, Backward-Euler on the first step and as the retry when the
-    // trapezoidal Newton does not converge.
+    // trapezoidal Newton does not converge. A step that still does not converge is taken as two half
+    // steps (recursively, NrConfig::max_cuts deep) with the pins held.
     bool solve_step(const PartitionState& cur, const std::vector<std::pair<uint64_t, double>>& ghost_voltages, double dt,
                     PartitionState& out) {
         std::vector<std::pair<int, double>> pins;
         for (auto& gv : ghost_voltages)
             for (auto& link : netlist.ghost_map)
                 if (link.net_id == gv.first) { pins.emplace_back(link.local_node, gv.second); break; }
+        return advance(cur, pins, dt, 0, out);
+    }
+
+    uint64_t be_fallbacks = 0, step_cuts = 0, dc_gmin_stepping = 0;
+
+private:
+    Assembler asm_;
+
+    bool advance(const PartitionState& cur, const std::vector<std::pair<int, double>>& pins, double dt, int depth, PartitionState& out) {
+        if (single_step(cur, pins, dt, out)) return true;
+        if (depth >= newton.config.max_cuts || dt <= 0.0) return false;
+        ++step_cuts;
+        PartitionState mid{0};
+        return advance(cur, pins, 0.5 * dt, depth + 1, mid) && advance(mid, pins, 0.5 * dt, depth + 1, out);
+    }
+
+    bool single_step(const PartitionState& cur, const std::vector<std::pair<int, double>>& pins, double dt, PartitionState& out) {
         Integration method = cur.cap_currents.empty() ? Integration::BackwardEuler : Integration::Trapezoidal;
         NrOutcome r = run_newton(cur, pins, dt, cur.time + dt, method);
         if (!r.converged && method == Integration::Trapezoidal) {
@@ -353,11 +395,6 @@ public:
         return true;
     }
 
-    uint64_t be_fallbacks = 0;
-
-private:
-    Assembler asm_;
-
     NrOutcome run_newton(const PartitionState& cur, const std::vector<std::pair<int, double>>& pins, double dt, double t,
                          Integration method) {
         asm_.stamp_linear(cur.voltages, cur.cap_currents, dt, t, method, pins);
@@ -365,7 +402,7 @@ private:
         std::vector<double> guess = cur.voltages;
         return newton.solve(std::move(guess), asm_.m, [&](const std::vector<double>& x, CsrMatrix&) {
             if (nonlinear) asm_.stamp_nonlinear(x);
-        });
+        }, nonlinear ? asm_.num_nodes : 0);
     }
 };
 

@@ -35,6 +35,13 @@ _EXPORT_MAP = {
     "find_ngspice_binary": (".correctness", "find_ngspice_binary"), "find_nangila_binary": (".correctness", "find_nangila_binary"),
     "run_ngspice_waveform": (".correctness", "run_ngspice_waveform"), "run_nangila_waveform": (".correctness", "run_nangila_waveform"),
     "v1_tolerance_profile": (".correctness", "v1_tolerance_profile"), "within_v1_contract": (".correctness", "within_v1_contract"),
+    "CorrectnessCase": (".correctness", "CorrectnessCase"), "BlockedCorrectnessCase": (".correctness", "BlockedCorrectnessCase"),
+    "official_correctness_cases": (".correctness", "official_correctness_cases"),
+    "phase1_automated_correctness_cases": (".correctness", "phase1_automated_correctness_cases"),
+    "extended_phase1_correctness_cases": (".correctness", "extended_phase1_correctness_cases"),
+    "blocked_official_correctness_cases": (".correctness", "blocked_official_correctness_cases"),
+    "collect_flattened_nodes": (".correctness", "collect_flattened_nodes"), "collect_observable_nodes": (".correctness", "collect_observable_nodes"),
+    "check_logic_levels": (".correctness", "check_logic_levels"), "evaluate_bench": (".benchcircuits", "evaluate_bench"),
     "read_nz": (".nz_reader", "read_nz"), "DeviceCsr": (".gpu", "DeviceCsr"),
 }
 

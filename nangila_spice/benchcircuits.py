@@ -14,6 +14,7 @@ netlists themselves, whose gate-for-gate text is not reproduced; c17 and s27, a 
 from __future__ import annotations
 
 import os
+import re
 from typing import Callable, Dict, List, Tuple
 
 from .synth import C17_BENCH, bench_to_spice
@@ -352,6 +353,33 @@ def reference_circuits() -> Dict[str, str]:
     return {"inverter": INVERTER_SP, "sram_6t": SRAM_6T_SP,
             "c17_full": bench_to_spice(C17_BENCH, "c17, pulsed inputs", period=1e-9) .replace(".end\n", ".tran 2p 16n\n.end\n"),
             "c17_synth": bench_to_spice(C17_BENCH, "c17, all inputs high", stimulus=dc)}
+
+
+_LOGIC = {"AND": lambda v: int(all(v)), "NAND": lambda v: 1 - int(all(v)), "OR": lambda v: int(any(v)), "NOR": lambda v: 1 - int(any(v)),
+          "NOT": lambda v: 1 - v[0], "BUFF": lambda v: v[0], "BUF": lambda v: v[0], "XOR": lambda v: sum(v) & 1, "XNOR": lambda v: 1 - (sum(v) & 1)}
+
+
+def evaluate_bench(bench: str, values: Dict[str, int]) -> Dict[str, int]:
+    """Logic value of every net of a ``.bench`` description for the given primary-input values. Flip-flop outputs
+    are inputs of the combinational cloud and are read from ``values`` as well. The logic-level oracle of the
+    transistor-level correctness cases."""
+    nets = dict(values)
+    pending = []
+    for line in bench.splitlines():
+        m = re.match(r"([^=\s]+)\s*=\s*([A-Za-z]+)\s*\(([^)]*)\)", line.split("#")[0].strip())
+        if m and m.group(2).upper() != "DFF":
+            pending.append((m.group(1), m.group(2).upper(), [a.strip() for a in m.group(3).split(",") if a.strip()]))
+    while pending:
+        rest = []
+        for out, kind, ins in pending:
+            if all(i in nets for i in ins):
+                nets[out] = _LOGIC[kind]([nets[i] for i in ins])
+            else:
+                rest.append((out, kind, ins))
+        if len(rest) == len(pending):
+            raise ValueError("combinational loop or undriven net: " + ", ".join(o for o, _, _ in rest[:5]))
+        pending = rest
+    return nets
 
 
 def bench_text(name: str) -> str:

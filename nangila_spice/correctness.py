@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import json
 import os
+import re
 import shutil
 import subprocess
 import tempfile
@@ -120,14 +121,17 @@ def find_ngspice_binary() -> Optional[str]:
 
 def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: float = 1e-3, process: str = "TT", vdd: float = 1.8,
                          temp: float = 27.0, solver: str = "lu", binary: Optional[str] = None, in_process: bool = False,
-                         record_every: int = 1) -> WaveformData:
-    """Runs this simulator on a deck: through the ``nangila-node`` process (default) or in-process."""
+                         record_every: int = 1, allow_partial: bool = False) -> WaveformData:
+    """Runs this simulator on a deck: through the ``nangila-node`` process (default) or in-process. A run that
+    stops before ``tstop`` (Newton did not converge even after step cutting) raises unless ``allow_partial``."""
     if in_process:
         from . import _native
 
         text = Path(netlist_path).read_text()
         js, _ = _native.parse_spice(text, Path(netlist_path).name, process, vdd, temp)
         r = _native.simulate(js, tstop, dt, reltol, solver, record_every)
+        if not r["stats"]["completed"] and not allow_partial:
+            raise RuntimeError(f"{netlist_path}: stopped at t = {r['time'][-1]:.4g} s of {tstop:.4g} s: Newton did not converge")
         vals = np.asarray(r["values"], float)
         return WaveformData("nangila", netlist_path, list(r["node_names"]), list(r["time"]),
                             {n: vals[:, j].tolist() for j, n in enumerate(r["node_names"]) if j < vals.shape[1]})
@@ -139,6 +143,8 @@ def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: 
         cmd = [exe, "--partition", netlist_path, "--tstop", repr(tstop), "--dt", repr(dt), "--reltol", repr(reltol), "--process", process,
                "--vdd", repr(vdd), "--temp", repr(temp), "--solver", solver, "--record-every", str(record_every), "--waveform-json", out]
         proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode == 3 and not allow_partial:
+            raise RuntimeError(f"{netlist_path}: stopped before tstop: {proc.stderr[-300:]}")
         if proc.returncode not in (0, 3) or not os.path.exists(out):
             raise RuntimeError(f"nangila-node failed ({proc.returncode}): {proc.stderr[-500:]}")
         with open(out) as f:
@@ -171,3 +177,163 @@ def run_ngspice_waveform(netlist_path: str, nodes: list[str], *, tstop: float, d
 def waveform_to_data(waveform, tool: str = "nangila", netlist: str = "") -> WaveformData:
     """``merger.Waveform`` -> ``WaveformData``."""
     return WaveformData(tool, netlist, waveform.node_names, waveform.times.tolist(), {n: v.tolist() for n, v in waveform.traces.items()})
+
+
+# ---- case registry ------------------------------------------------------------------------------------------
+# The reference keeps its correctness cases as lists of deck paths inside its repository
+# (correctness.py:112-420: official, phase-1 automated, extended and blocked cases). The decks here are
+# generated (benchmark.py, benchcircuits.py), so a case carries its deck text; ``materialize`` writes it out.
+@dataclass(frozen=True)
+class CorrectnessCase:
+    """One deck with what to observe and how to step it. ``expected_levels`` (net -> 0 / 1) is the logic-level
+    oracle of a synthesised case: the settled voltage of those nets must sit at the matching rail."""
+    name: str
+    deck: str
+    nodes: tuple
+    tstop: float
+    dt: float
+    nonlinear: bool
+    tier: str = "passive"
+    use_initial_conditions: bool = False
+    vdd: float = 1.8
+    expected_levels: tuple = ()
+
+    def materialize(self, directory: str) -> str:
+        """Writes the deck to ``directory/<name>.sp`` and returns the path."""
+        os.makedirs(directory, exist_ok=True)
+        path = os.path.join(directory, self.name + ".sp")
+        with open(path, "w") as fh:
+            fh.write(self.deck)
+        return path
+
+
+@dataclass(frozen=True)
+class BlockedCorrectnessCase:
+    name: str
+    reason: str
+
+
+def check_logic_levels(case: CorrectnessCase, waveform: "WaveformData", margin: float = 0.1) -> list:
+    """Nets of ``case.expected_levels`` whose last sample is further than ``margin * vdd`` from the expected rail,
+    as ``(net, expected volts, measured volts)``."""
+    bad = []
+    for net, bit in case.expected_levels:
+        if net not in waveform.traces:
+            bad.append((net, bit * case.vdd, float("nan")))
+            continue
+        v = float(waveform.traces[net][-1])
+        if abs(v - bit * case.vdd) > margin * case.vdd:
+            bad.append((net, bit * case.vdd, v))
+    return bad
+
+
+def _logic_case(name: str, bench: str, title: str, inputs: dict, observe: list, tstop: float = 2e-9, dt: float = 1e-12) -> CorrectnessCase:
+    """A synthesised block whose inputs step from 0 to their value at 50 ps; the observed outputs must settle to the
+    levels the gate-level description gives. Every gate drives 20 fF, which puts some twenty 1 ps steps on an edge:
+    with the 2 fF default an edge lasts three steps and the comparison measures the step size, not the solver."""
+    from .benchcircuits import evaluate_bench
+    from .synth import bench_to_spice
+
+    stim = [f"VS{k} n{net} 0 PULSE(0 {1.8 * bit!r} 50p 20p 20p 1 2)" for k, (net, bit) in enumerate(inputs.items())]
+    levels = evaluate_bench(bench, inputs)
+    if observe is None:
+        observe = re.findall(r"OUTPUT\(\s*([^)\s]+)\s*\)", bench)
+    return CorrectnessCase(name, bench_to_spice(bench, title, stimulus=stim, cload="20f"), tuple("n" + o for o in observe), tstop, dt, True, tier="logic",
+                           expected_levels=tuple(("n" + o, int(levels[o])) for o in observe))
+
+
+def _bits(prefix: str, value: int, n: int) -> dict:
+    return {f"{prefix}{i}": (value >> i) & 1 for i in range(n)}
+
+
+def official_correctness_cases() -> list:
+    """The mandatory suite (13 cases, as many as the reference's): passive networks with closed forms or a
+    half-step oracle, single devices, the hand-written circuits, and small generated logic blocks at transistor level."""
+    from . import benchcircuits as bc
+    from .benchmark import generate_cim_netlist, generate_rc_ladder_netlist
+
+    ref = bc.reference_circuits()
+    rc_step = "* RC step\nV1 vdd 0 DC 1.8\nR1 vdd out 1k\nC1 out 0 10f\n.ic V(out)=0\n.end\n"
+    diode = ("* diode clamp\nV1 in 0 PULSE(0 1.8 0 100p 100p 500p 2n)\nR1 in out 1k\nD1 out 0 dm\nC1 out 0 5f\n"
+             ".model dm D (is=1e-14 n=1)\n.end\n")
+    return [
+        CorrectnessCase("rc_step", rc_step, ("out",), 100e-12, 0.25e-12, False, use_initial_conditions=True),
+        CorrectnessCase("rc_ladder_50", generate_rc_ladder_netlist(50, 1e3, 10e-15), ("n1", "n25", "n50"), 500e-12, 0.25e-12, False),
+        CorrectnessCase("cim_8x8", generate_cim_netlist(8, 8), ("bl0", "bl3", "bl7"), 2e-9, 5e-12, False),
+        CorrectnessCase("diode_clamp", diode, ("out",), 1e-9, 1e-12, True, tier="nonlinear"),
+        CorrectnessCase("cmos_inverter", ref["inverter"], ("out",), 1e-9, 1e-12, True, tier="nonlinear"),
+        CorrectnessCase("sram_6t", ref["sram_6t"], ("q", "qb"), 2e-9, 1e-12, True, tier="nonlinear", use_initial_conditions=True),
+        CorrectnessCase("c17_synth", ref["c17_synth"], ("n22", "n23"), 0.5e-9, 1e-12, True, tier="nonlinear",
+                        expected_levels=tuple(("n" + o, bc.evaluate_bench(bc.C17_BENCH, {k: 1 for k in "12367"})[o]) for o in ("22", "23"))),
+        CorrectnessCase("c17_full", ref["c17_full"], ("n22", "n23"), 4e-9, 0.5e-12, True, tier="nonlinear"),
+        _logic_case("adder2", bc.adder(2), "2-bit adder", {**_bits("a", 3, 2), **_bits("b", 1, 2), "cin": 0}, ["s0", "s1", "cout"]),
+        _logic_case("priority4", bc.priority(4), "4-channel priority encoder", {**_bits("req", 0b1010, 4), **_bits("en", 0b1111, 4)},
+                    ["idx0", "idx1", "any"], dt=0.5e-12),
+        _logic_case("s27_cut", bc.S27_BENCH, "s27 with the flip-flops cut", {"G0": 1, "G1": 0, "G2": 1, "G3": 0, "G5": 0, "G6": 1, "G7": 0},
+                    ["G17", "G10", "G11", "G13"]),
+        _logic_case("sec4", bc.parity_sec(4), "4-bit single-error corrector", {**_bits("d", 0b1101, 4), **_bits("r", 0b010, 3), "en": 1},
+                    ["q0", "q1", "q2", "q3"]),
+        _logic_case("alu2", bc.alu(2), "2-bit ALU", {**_bits("a", 1, 2), **_bits("b", 3, 2), **_bits("op", 3, 2), "cin": 0},
+                    ["y0", "y1", "zero", "carry"]),
+    ]
+
+
+def phase1_automated_correctness_cases() -> list:
+    """What the automated report runs by default: the mandatory suite."""
+    return official_correctness_cases()
+
+
+def extended_phase1_correctness_cases() -> list:
+    """Larger cases for ``--include-extended``: a long ladder, a wider array and generated logic of a few hundred devices."""
+    from . import benchcircuits as bc
+    from .benchmark import generate_cim_netlist, generate_rc_ladder_netlist
+
+    return [
+        CorrectnessCase("rc_ladder_400", generate_rc_ladder_netlist(400, 1e3, 10e-15), ("n1", "n200", "n400"), 500e-12, 0.25e-12, False),
+        CorrectnessCase("cim_16x16", generate_cim_netlist(16, 16), ("bl0", "bl7", "bl15"), 2e-9, 5e-12, False),
+        _logic_case("adder8", bc.adder(8), "8-bit adder", {**_bits("a", 0xB5, 8), **_bits("b", 0x6E, 8), "cin": 1},
+                    [f"s{i}" for i in range(8)] + ["cout"], tstop=3e-9, dt=0.5e-12),
+        _logic_case("mult3", bc.multiplier(3), "3 x 3 multiplier", {**_bits("a", 5, 3), **_bits("b", 6, 3)}, [f"p{i}" for i in range(6)],
+                    tstop=3e-9, dt=0.5e-12),
+        _logic_case("priority8", bc.priority(8), "8-channel priority encoder", {**_bits("req", 0b01001101, 8), **_bits("en", 0b00101000, 8)},
+                    ["idx0", "idx1", "idx2", "any"], tstop=3e-9, dt=0.5e-12),
+        _logic_case("comparator_adder4", bc.comparator_adder(4), "4-bit comparator and adder", {**_bits("a", 0b1011, 4), **_bits("b", 0b1100, 4), "cin": 0},
+                    None, tstop=3e-9, dt=0.5e-12),
+    ]
+
+
+def blocked_official_correctness_cases() -> list:
+    """Suite entries that the automated report does not run, with the reason."""
+    from . import benchcircuits as bc
+
+    why = ("thousands of devices: a transient run of the full deck belongs to the scaling study (nangila_spice.benchmark), "
+           "not to the per-commit correctness report")
+    glitch = ("all eight inputs switch at once and the middle product bits carry runt pulses whose height moves by 50 mV between 0.25 ps "
+              "and 0.125 ps steps: a study of glitch sensitivity, not a check of the solver")
+    return [BlockedCorrectnessCase("mult4", glitch)] + [BlockedCorrectnessCase(name, why) for name in bc.SUITE if name not in ("c17", "s27")]
+
+
+def _is_ground(node: str) -> bool:
+    return node.lower() in ("0", "gnd")
+
+
+def collect_flattened_nodes(netlist_path: str) -> list:
+    """Names of all nets of a deck after sub-circuit expansion, ground excluded (reference: correctness.py:220-230)."""
+    from .parser import parse_netlist
+
+    return sorted({n.lower() for dev in parse_netlist(netlist_path).flatten().devices for n in dev.nodes if not _is_ground(n)})
+
+
+def collect_observable_nodes(netlist_path: str, *, exclude_zero_volt_alias_sinks: bool = False) -> list:
+    """Top-level nets of a deck; optionally without nets that a 0 V source merely ties to another net
+    (reference: correctness.py:233-261)."""
+    from .parser import parse_netlist
+
+    nodes, aliases = set(), set()
+    for dev in parse_netlist(netlist_path).devices:
+        nodes.update(n.lower() for n in dev.nodes if not _is_ground(n))
+        if exclude_zero_volt_alias_sinks and dev.dev_type.upper() == "V" and len(dev.nodes) >= 2 and not _is_ground(dev.nodes[1]):
+            value = " ".join(str(x) for x in (dev.value, dev.params.get("dc")) if x is not None).strip().lower()
+            if value in ("0", "0.0", "dc 0", "dc 0.0"):
+                aliases.add(dev.nodes[1].lower())
+    return sorted(nodes - aliases)

@@ -20,63 +20,44 @@ from typing import Iterable, Optional
 
 import numpy as np
 
-from .benchmark import generate_cim_netlist, generate_rc_ladder_netlist
-from .correctness import (WaveformData, compare_waveforms, find_ngspice_binary, run_nangila_waveform, run_ngspice_waveform,
-                          within_v1_contract)
-from .synth import C17_BENCH, bench_to_spice
+from .correctness import (CorrectnessCase, WaveformData, blocked_official_correctness_cases, check_logic_levels, compare_waveforms,
+                          extended_phase1_correctness_cases, find_ngspice_binary, phase1_automated_correctness_cases, run_nangila_waveform,
+                          run_ngspice_waveform, within_v1_contract)
 
-_INVERTER = """* CMOS inverter
-VDD vdd 0 DC 1.8
-VIN in 0 PULSE(0 1.8 100p 50p 50p 400p 1n)
-M1 out in vdd vdd pch w=2u l=180n
-M2 out in 0 0 nch w=1u l=180n
-CL out 0 5f
-.model nch NMOS (vto=0.45 kp=200u lambda=0.05)
-.model pch PMOS (vto=-0.45 kp=100u lambda=0.05)
-.end
-"""
-_RC_STEP = "* RC step\nV1 vdd 0 DC 1.8\nR1 vdd out 1k\nC1 out 0 10f\n.ic V(out)=0\n.end\n"
-_DIODE = "* diode clamp\nV1 in 0 PULSE(0 1.8 0 100p 100p 500p 2n)\nR1 in out 1k\nD1 out 0 dm\nC1 out 0 5f\n.model dm D (is=1e-14 n=1)\n.end\n"
+# Closed-form solutions, by case name.
+_ANALYTIC = {"rc_step": lambda t: {"out": 1.8 * (1.0 - np.exp(-t / 10e-12))}}
 
 
-def _cases() -> list[dict]:
-    return [
-        {"name": "rc_step", "tier": "passive", "deck": _RC_STEP, "tstop": 100e-12, "dt": 0.25e-12, "nonlinear": False, "nodes": ["out"],
-         "analytic": lambda t: {"out": 1.8 * (1.0 - np.exp(-t / 10e-12))}},
-        {"name": "rc_ladder_50", "tier": "passive", "deck": generate_rc_ladder_netlist(50, 1e3, 10e-15), "tstop": 500e-12, "dt": 0.25e-12,
-         "nonlinear": False, "nodes": ["n1", "n25", "n50"]},
-        {"name": "cim_8x8", "tier": "passive", "deck": generate_cim_netlist(8, 8), "tstop": 2e-9, "dt": 5e-12, "nonlinear": False,
-         "nodes": ["bl0", "bl3", "bl7"]},
-        {"name": "diode_clamp", "tier": "nonlinear", "deck": _DIODE, "tstop": 1e-9, "dt": 1e-12, "nonlinear": True, "nodes": ["out"]},
-        {"name": "cmos_inverter", "tier": "nonlinear", "deck": _INVERTER, "tstop": 1e-9, "dt": 1e-12, "nonlinear": True, "nodes": ["out"]},
-        {"name": "c17_transistor_level", "tier": "nonlinear", "deck": bench_to_spice(C17_BENCH, "c17"), "tstop": 4e-9, "dt": 0.5e-12,
-         "nonlinear": True, "nodes": ["n22", "n23"]},
-    ]
-
-
-def _run_case(case: dict, ngspice_bin: Optional[str]) -> dict:
+def _run_case(case: CorrectnessCase, ngspice_bin: Optional[str]) -> dict:
     with tempfile.TemporaryDirectory() as tmp:
-        path = os.path.join(tmp, case["name"] + ".sp")
-        Path(path).write_text(case["deck"])
+        path = case.materialize(tmp)
         t0 = time.perf_counter()
-        cand = run_nangila_waveform(path, tstop=case["tstop"], dt=case["dt"], in_process=True)
+        cand = run_nangila_waveform(path, tstop=case.tstop, dt=case.dt, in_process=True)
         wall = time.perf_counter() - t0
         if ngspice_bin:
-            ref, oracle = run_ngspice_waveform(path, case["nodes"], tstop=case["tstop"], dt=case["dt"], binary=ngspice_bin), "ngspice"
-        elif "analytic" in case:
+            ref, oracle = run_ngspice_waveform(path, list(case.nodes), tstop=case.tstop, dt=case.dt, binary=ngspice_bin), "ngspice"
+        elif case.name in _ANALYTIC:
             t = np.asarray(cand.times)
-            tr = case["analytic"](t)
+            tr = _ANALYTIC[case.name](t)
             ref, oracle = WaveformData("analytic", path, list(tr), t.tolist(), {k: v.tolist() for k, v in tr.items()}), "closed form"
         else:
-            ref = run_nangila_waveform(path, tstop=case["tstop"], dt=case["dt"] / 2, in_process=True, solver="dense")
+            ref = run_nangila_waveform(path, tstop=case.tstop, dt=case.dt / 2, in_process=True, solver="dense")
             oracle = "dense solver, dt / 2"
-        keep = [n for n in case["nodes"] if n in cand.traces and n in ref.traces]
-        ref = WaveformData(ref.tool, ref.netlist, keep, ref.times, {n: ref.traces[n] for n in keep})
-        cmp_ = compare_waveforms(ref, cand)
-        ok, profile = within_v1_contract(cmp_, nonlinear=case["nonlinear"])
-    return {"name": case["name"], "tier": case["tier"], "oracle": oracle, "nodes": keep, "samples": cmp_.sample_count,
+        lower = {n.lower(): n for n in cand.traces}
+        cand_l = WaveformData(cand.tool, cand.netlist, list(lower), cand.times, {k: cand.traces[v] for k, v in lower.items()})
+        ref_l = {n.lower(): v for n, v in ref.traces.items()}
+        keep = [n.lower() for n in case.nodes if n.lower() in cand_l.traces and n.lower() in ref_l]
+        ref = WaveformData(ref.tool, ref.netlist, keep, ref.times, {n: ref_l[n] for n in keep})
+        cmp_ = compare_waveforms(ref, cand_l)
+        ok, profile = within_v1_contract(cmp_, nonlinear=case.nonlinear)
+        wrong = check_logic_levels(CorrectnessCase(**{**case.__dict__, "expected_levels": tuple((n.lower(), b) for n, b in case.expected_levels)}), cand_l)
+        if case.expected_levels:
+            oracle += " + gate-level logic"
+    return {"name": case.name, "tier": case.tier, "oracle": oracle, "nodes": keep, "samples": cmp_.sample_count,
             "max_abs_error_v": cmp_.max_abs_error, "rms_error_v": cmp_.rms_error, "final_abs_error_v": cmp_.final_abs_error,
-            "edge_timing_error_s": cmp_.max_edge_timing_error, "max_abs_tol_v": profile.max_abs_tol, "passed": bool(ok), "wall_time_secs": wall}
+            "edge_timing_error_s": cmp_.max_edge_timing_error, "max_abs_tol_v": profile.max_abs_tol,
+            "logic_levels_checked": len(case.expected_levels), "logic_levels_wrong": [list(w) for w in wrong],
+            "passed": bool(ok) and not wrong and len(keep) == len(case.nodes), "wall_time_secs": wall}
 
 
 def _tier_summary(cases: list[dict]) -> dict:
@@ -87,15 +68,15 @@ def _tier_summary(cases: list[dict]) -> dict:
 
 def generate_phase1_benchmark_report(include_extended: bool = False) -> dict:
     ngspice = find_ngspice_binary()
-    cases = _cases()
+    cases = phase1_automated_correctness_cases()
     if include_extended:
-        cases.append({"name": "rc_ladder_400", "tier": "passive", "deck": generate_rc_ladder_netlist(400, 1e3, 10e-15), "tstop": 500e-12,
-                      "dt": 1e-12, "nonlinear": False, "nodes": ["n1", "n200", "n400"]})
+        cases += extended_phase1_correctness_cases()
     rows = [_run_case(c, ngspice) for c in cases]
     tiers = sorted({r["tier"] for r in rows})
     return {"generated": time.strftime("%Y-%m-%d %H:%M:%S"), "platform": f"{platform.system()} {platform.machine()}",
             "oracle_tool": "ngspice" if ngspice else "built-in oracles (ngspice not installed)", "cases": rows,
             "tiers": {t: _tier_summary([r for r in rows if r["tier"] == t]) for t in tiers},
+            "blocked": [{"name": b.name, "reason": b.reason} for b in blocked_official_correctness_cases()],
             "all_passed": all(r["passed"] for r in rows)}
 
 
@@ -112,6 +93,11 @@ def render_markdown_report(report: dict) -> str:
     for tier, s in report["tiers"].items():
         out += [f"## {tier}: {s['passed']}/{s['cases']} within contract", "", "| case | oracle | max error | rms error | edge timing | verdict | time |",
                 "|---|---|---|---|---|---|---|", *_iter_tier_rows(report, tier), ""]
+    if report.get("blocked"):
+        reasons = {}
+        for b in report["blocked"]:
+            reasons.setdefault(b["reason"], []).append(b["name"])
+        out += ["## not run", "", *(f"- {', '.join(names)}: {why}" for why, names in reasons.items()), ""]
     return "\n".join(out)
 
 

@@ -154,3 +154,77 @@ def test_suite_decks_and_reference_circuits(tmp_path):
     for name in ("inverter", "sram_6t"):
         js, warnings = N.parse_spice(ref[name], name)
         assert warnings == []
+
+
+def test_evaluate_bench_matches_the_local_evaluator():
+    rng = random.Random(3)
+    text = bc.alu(3)
+    ins = re.findall(r"INPUT\((.*?)\)", text)
+    for _ in range(10):
+        vals = {i: rng.randint(0, 1) for i in ins}
+        assert bc.evaluate_bench(text, vals) == evaluate(text, vals)
+    with pytest.raises(ValueError):
+        bc.evaluate_bench("INPUT(a)\nx = AND(a, y)\ny = OR(x, a)\n", {"a": 1})
+
+
+def test_mosfet_model_is_continuous_and_symmetric():
+    beta, vth, lam = 1e-3, 0.45, 0.05
+    for pmos in (False, True):
+        sg = -1.0 if pmos else 1.0
+        # no jump of the current at the linear / saturation boundary, derivatives agree with finite differences
+        vgs = sg * 1.2
+        for vds in (0.2, 0.7499, 0.7501, 1.5, -0.3, -0.9):
+            i0, gm, gds, _ = N.mosfet_eval(vgs, sg * vds, pmos, vth, beta, lam)
+            h = 1e-6
+            ip, _, _, _ = N.mosfet_eval(vgs, sg * vds + h, pmos, vth, beta, lam)
+            ig, _, _, _ = N.mosfet_eval(vgs + h, sg * vds, pmos, vth, beta, lam)
+            assert abs((ip - i0) / h - gds) < 1e-6 + 1e-4 * abs(gds), (pmos, vds)
+            assert abs((ig - i0) / h - gm) < 1e-6 + 1e-4 * abs(gm), (pmos, vds)
+        lo, _, _, _ = N.mosfet_eval(vgs, sg * (0.75 - 1e-9), pmos, vth, beta, lam)
+        hi, _, _, _ = N.mosfet_eval(vgs, sg * (0.75 + 1e-9), pmos, vth, beta, lam)
+        assert abs(lo - hi) < 1e-11
+        # drain and source trade places: I(vg - vs, vd - vs) = -I(vg - vd, vs - vd)
+        fwd, _, _, _ = N.mosfet_eval(sg * 1.0, sg * 0.4, pmos, vth, beta, lam)
+        rev, _, _, _ = N.mosfet_eval(sg * 0.6, sg * -0.4, pmos, vth, beta, lam)
+        assert abs(fwd + rev) < 1e-15 and (fwd > 0) == (not pmos)
+
+
+def test_correctness_registry_and_logic_oracle(tmp_path):
+    from nangila_spice import correctness as cx
+
+    official = cx.official_correctness_cases()
+    assert len(official) == 13 and len({c.name for c in official}) == 13
+    assert [c.name for c in cx.phase1_automated_correctness_cases()] == [c.name for c in official]
+    assert {c.tier for c in official} == {"passive", "nonlinear", "logic"}
+    assert len(cx.extended_phase1_correctness_cases()) >= 4
+    blocked = cx.blocked_official_correctness_cases()
+    assert {"c6288", "s38417", "mult4"} <= {b.name for b in blocked} and all(b.reason for b in blocked)
+    case = next(c for c in official if c.name == "priority4")
+    path = case.materialize(str(tmp_path))
+    # this deck used to stop at 68 ps (Newton oscillating across the jump of the old model); now it completes without a single retry
+    js, _ = N.parse_spice(case.deck)
+    r = N.simulate(js, case.tstop, 1e-12)
+    assert r["stats"]["completed"] and r["newton"]["failed"] == 0 and r["newton"]["step_cuts"] == 0
+    wave = cx.run_nangila_waveform(path, tstop=case.tstop, dt=case.dt, in_process=True)
+    lower = cx.WaveformData(wave.tool, wave.netlist, [n.lower() for n in wave.node_names], wave.times, {k.lower(): v for k, v in wave.traces.items()})
+    assert cx.check_logic_levels(case, lower) == []
+    wrong = cx.CorrectnessCase(**{**case.__dict__, "expected_levels": (("nany", 0),)})
+    assert [w[0] for w in cx.check_logic_levels(wrong, lower)] == ["nany"]
+    flat = cx.collect_flattened_nodes(path)
+    assert "nany" in flat and "0" not in flat and "vdd" in flat
+    alias = tmp_path / "alias.sp"
+    alias.write_text("* alias\nV1 in 0 DC 1\nVA in out 0\nR1 out 0 1k\n.end\n")
+    assert cx.collect_observable_nodes(str(alias)) == ["in", "out"]
+    assert cx.collect_observable_nodes(str(alias), exclude_zero_volt_alias_sinks=True) == ["in"]
+
+
+def test_partial_run_raises_unless_allowed(tmp_path):
+    from nangila_spice import correctness as cx
+
+    # 1e30 A into a diode: the junction voltage that carries it is out of reach of the limited Newton steps, at any step size
+    deck = tmp_path / "hard.sp"
+    deck.write_text("* unreachable\nI1 0 a DC 1e30\nD1 a 0 dm\n.model dm D (is=1e-14 n=1)\n.ic V(a)=0\n.end\n")
+    with pytest.raises(RuntimeError, match="did not converge"):
+        cx.run_nangila_waveform(str(deck), tstop=5e-12, dt=1e-12, in_process=True)
+    w = cx.run_nangila_waveform(str(deck), tstop=5e-12, dt=1e-12, in_process=True, allow_partial=True)
+    assert len(w.times) == 1 and w.times[0] == 0.0
