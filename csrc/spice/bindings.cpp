@@ -83,6 +83,10 @@ PYBIND11_MODULE(_native, m) {
         py::dict nr;
         nr["total_iterations"] = s.engine().newton.stats.total_iterations; nr["linear_solves"] = s.engine().newton.stats.linear_solves;
         nr["failed"] = s.engine().newton.stats.failed_count; nr["be_fallbacks"] = s.engine().be_fallbacks;
+        { auto& lu = s.engine().newton.linear.lu.stats;
+          nr["lu_analyses"] = lu.analyses; nr["lu_refactors"] = lu.refactors; nr["lu_repivots"] = lu.repivots;
+          nr["lu_refinement_rounds"] = lu.refinement_rounds; nr["lu_factor_nnz"] = lu.factor_nnz; nr["lu_singletons"] = lu.singletons;
+          nr["lu_fallbacks"] = s.engine().newton.linear.stats.lu_fallbacks; }
         nr["step_cuts"] = s.engine().step_cuts; nr["dc_gmin_stepping"] = s.engine().dc_gmin_stepping;
         nr["device_solves"] = s.engine().newton.linear.stats.device_solves; nr["krylov_iterations"] = s.engine().newton.linear.stats.krylov_iterations;
         nr["krylov_fallbacks"] = s.engine().newton.linear.stats.krylov_fallbacks; nr["cuda_error"] = s.engine().newton.linear.cuda_error;
@@ -134,19 +138,36 @@ PYBIND11_MODULE(_native, m) {
         bool ok = s.solve(a);
         return py::make_tuple(ok, a.solution, s.stats.krylov_iterations);
     }, py::arg("n"), py::arg("row_ptr"), py::arg("col"), py::arg("val"), py::arg("rhs"), py::arg("solver") = "lu");
+    py::class_<FactoredLU>(m, "FactoredLU", "sparse LU that keeps its ordering and pattern between solves of one sparsity pattern")
+        .def(py::init<>())
+        .def("solve", [](FactoredLU& lu, int n, const std::vector<int>& row_ptr, const std::vector<int>& col, const std::vector<double>& val,
+                         const std::vector<double>& rhs) {
+            if (int(row_ptr.size()) != n + 1 || col.size() != val.size() || int(rhs.size()) != n) throw std::invalid_argument("inconsistent CSR arrays");
+            std::vector<double> x;
+            bool ok = lu.solve(n, row_ptr, col, val, rhs, x);
+            return py::make_tuple(ok, x);
+        })
+        .def("stats", [](const FactoredLU& lu) {
+            py::dict d;
+            d["orderings"] = lu.stats.orderings; d["analyses"] = lu.stats.analyses; d["refactors"] = lu.stats.refactors; d["repivots"] = lu.stats.repivots;
+            d["refinement_rounds"] = lu.stats.refinement_rounds; d["factor_nnz"] = lu.stats.factor_nnz; d["singletons"] = lu.stats.singletons;
+            return d;
+        });
+    m.def("singleton_pivots", [](int n, const std::vector<int>& row_ptr, const std::vector<int>& col) { return singleton_pivots(n, row_ptr, col); });
+    m.def("minimum_degree_order", [](int n, const std::vector<int>& row_ptr, const std::vector<int>& col) { return minimum_degree_order(n, row_ptr, col); });
     m.def("csr_spmv", [](int n, std::vector<int> row_ptr, std::vector<int> col, std::vector<double> val, std::vector<double> x) {
         CsrMatrix a(n);
         a.row_ptr = std::move(row_ptr); a.col = std::move(col); a.val = std::move(val);
         return a.spmv(x);
     });
-    m.def("mna_matrix", [](const std::string& netlist_json, double dt, double time) {
+    m.def("mna_matrix", [](const std::string& netlist_json, double dt, double time, std::vector<double> guess) {
         Netlist nl = Netlist::from_json(Json::parse(netlist_json));
         Assembler as(nl);
-        std::vector<double> zero(size_t(as.size), 0.0);
-        as.stamp_linear(zero, {}, dt, time, Integration::BackwardEuler, {});
-        as.stamp_nonlinear(zero);
+        guess.resize(size_t(as.size), 0.0);
+        as.stamp_linear(guess, {}, dt, time, Integration::BackwardEuler, {});
+        as.stamp_nonlinear(guess);
         return py::make_tuple(as.size, as.m.row_ptr, as.m.col, as.m.val, as.m.rhs);
-    });
+    }, py::arg("netlist_json"), py::arg("dt"), py::arg("time"), py::arg("guess") = std::vector<double>{});
 
     // ---- devices ------------------------------------------------------------------------------
     m.def("diode_eval", [](double vd, double is, double n, double vt) { DiodeModel d; d.is = is; d.n = n; d.vt = vt; double i, g; d.eval(vd, i, g); return py::make_tuple(i, g); },

@@ -111,7 +111,10 @@ public:
         size = num_nodes + num_vs + num_ind;
         std::vector<std::tuple<int, int, double>> t;
         auto add = [&](int r, int c) { if (r >= 0 && c >= 0) t.emplace_back(r, c, 0.0); };
-        for (int i = 0; i < size; ++i) add(i, i);
+        // every node row and every inductor row has a diagonal entry; the branch row of a voltage source has none
+        // (it reads v(a) - v(b) = V), which lets the factorisation take source rows and columns as free pivots
+        for (int i = 0; i < num_nodes; ++i) add(i, i);
+        for (int i = num_nodes + num_vs; i < size; ++i) add(i, i);
         int vs = 0, ind = 0;
         for (auto& e : nl.elements) {
             switch (e.kind) {
@@ -123,7 +126,7 @@ public:
                 case Element::VSource: case Element::Inductor: {
                     int br = e.kind == Element::VSource ? num_nodes + vs++ : num_nodes + num_vs + ind++;
                     int a = e.a - 1, b = e.b - 1;
-                    add(a, br); add(br, a); add(b, br); add(br, b); add(br, br);
+                    add(a, br); add(br, a); add(b, br); add(br, b);
                     break;
                 }
                 case Element::Mosfet: {
@@ -152,7 +155,7 @@ public:
                 case Element::VSource: case Element::Inductor: {
                     int br = e.kind == Element::VSource ? num_nodes + vs++ : num_nodes + num_vs + ind++;
                     int a = e.a - 1, b = e.b - 1;
-                    s[0] = S(a, br); s[1] = S(br, a); s[2] = S(b, br); s[3] = S(br, b); s[4] = S(br, br); s[5] = br;
+                    s[0] = S(a, br); s[1] = S(br, a); s[2] = S(b, br); s[3] = S(br, b); s[4] = e.kind == Element::Inductor ? S(br, br) : -1; s[5] = br;
                     break;
                 }
                 case Element::Mosfet: {
@@ -276,7 +279,7 @@ private:
         if (s[1] >= 0) m.val[size_t(s[1])] += 1.0;
         if (s[2] >= 0) m.val[size_t(s[2])] -= 1.0;
         if (s[3] >= 0) m.val[size_t(s[3])] -= 1.0;
-        m.val[size_t(s[4])] += r;
+        if (s[4] >= 0) m.val[size_t(s[4])] += r;
         m.rhs[size_t(s[5])] += rhs;
     }
     void pin(int node, double v) {

@@ -20,6 +20,8 @@
 #include <utility>
 #include <vector>
 
+#include "sparse_lu.hpp"
+
 namespace nspice {
 
 struct CsrMatrix {
@@ -95,6 +97,8 @@ struct CsrMatrix {
     }
 };
 
+// One-off solver (no state kept between calls); the transient loop uses FactoredLU (sparse_lu.hpp), which
+// analyses a pattern once and refactors. This one stays as the fallback and as an independent check.
 // Row-wise sparse Gaussian elimination on row-equilibrated data with threshold partial pivoting: among the rows whose entry
 // in the pivot column is within a factor 10 of the largest, the shortest row wins (limits fill).
 // One right-hand side is carried along, because a Newton iteration changes the matrix every solve.
@@ -340,7 +344,7 @@ private:
     int (*solve_)(void*, const double*, double*, double, int, int*, double*) = nullptr;
 };
 
-struct LinearSolverStats { uint64_t solves = 0, failures = 0, krylov_iterations = 0, krylov_fallbacks = 0, device_solves = 0; };
+struct LinearSolverStats { uint64_t solves = 0, failures = 0, krylov_iterations = 0, krylov_fallbacks = 0, device_solves = 0, lu_fallbacks = 0; };
 
 // Solver facade (the reference's GpuSolver::solve role): fills m.solution from m.rhs.
 class LinearSolver {
@@ -348,6 +352,7 @@ public:
     LinearBackend backend = LinearBackend::SparseLU;
     LinearSolverStats stats;
     CudaKrylov cuda;
+    FactoredLU lu;
     bool cuda_error = false;  // the device solver could not be loaded or reported a CUDA error; solves fell back to the sparse LU
     bool solve(CsrMatrix& m) {
         ++stats.solves;
@@ -395,15 +400,26 @@ public:
                 }
                 if (!(std::fabs(ax - eq.rhs[size_t(r)]) <= 1e-8 * mag + 1e-10 * bmax + 1e-300)) ok = false;
             }
-            if (!ok) { ++stats.krylov_fallbacks; ok = sparse_lu_solve(m, m.solution); }
+            if (!ok) { ++stats.krylov_fallbacks; ok = direct(m); }
         } else {
-            ok = sparse_lu_solve(m, m.solution);
+            ok = direct(m);
         }
         if (ok)
             for (double v : m.solution)
                 if (!std::isfinite(v)) { ok = false; break; }
         if (!ok) ++stats.failures;
         return ok;
+    }
+
+private:
+    bool direct(CsrMatrix& m) {
+        if (lu.solve(m.n, m.row_ptr, m.col, m.val, m.rhs, m.solution)) return true;
+        // Neither pivoting strategy gave a small backward error: the system is singular to working precision
+        // (a DC iterate with chains of floating nets does that). Small systems get one more try with the one-off
+        // elimination; large ones report the failure, which sends the DC solve to conductance stepping.
+        if (m.n > 400) return false;
+        ++stats.lu_fallbacks;
+        return sparse_lu_solve(m, m.solution);
     }
 };
 

@@ -1,0 +1,416 @@
+// Sparse LU that is analysed once and refactored many times.
+//
+// A transient run solves thousands of systems with one sparsity pattern and slowly changing values
+// (every Newton iteration of every step). The work is therefore split the way circuit solvers split it:
+//
+//   analyse  (once per pattern, again only when a pivot degrades)
+//            column order by minimum degree on the pattern of A + A^T, rows of very high degree (supply
+//            nets) set aside and ordered last; row order by one elimination with threshold partial
+//            pivoting on the current values (the diagonal is taken whenever it is within a factor 10 of
+//            the largest candidate, so the minimum-degree order keeps its meaning; strict partial
+//            pivoting is the second try when that is not stable enough); symbolic elimination
+//            of the permuted pattern, which fixes the positions of every fill-in
+//   refactor (every solve) scatter the row-equilibrated values into the fixed pattern and eliminate row by
+//            row without searching, allocating or pivoting
+//   solve    two triangular sweeps, then iterative refinement against the original matrix with the same
+//            factors while the componentwise backward error is above 1e-10
+//
+// A refactorisation that meets a tiny pivot, or a solve whose backward error does not come down, triggers a
+// new analysis with the values of that moment. The reference densifies the matrix and runs Gaussian
+// elimination on it for every solve (nangila-spice/nangila-node/src/gpu_solver.rs:22-330).
+#pragma once
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <queue>
+#include <set>
+#include <utility>
+#include <vector>
+
+namespace nspice {
+
+// Elimination order of the symmetric pattern (row_ptr, col) by minimum degree. Vertices whose degree exceeds
+// `dense_limit` are left out of the graph and come last, highest degree at the very end. Vertices flagged in
+// `removed` are not part of the graph and not part of the result.
+inline std::vector<int> minimum_degree_order(int n, const std::vector<int>& row_ptr, const std::vector<int>& col,
+                                             const std::vector<char>& removed = {}) {
+    auto out = [&](int v) { return !removed.empty() && removed[size_t(v)] != 0; };
+    std::vector<std::vector<int>> adj(static_cast<size_t>(n));
+    for (int r = 0; r < n; ++r) {
+        if (out(r)) continue;
+        for (int k = row_ptr[size_t(r)]; k < row_ptr[size_t(r) + 1]; ++k) {
+            int c = col[size_t(k)];
+            if (c != r && !out(c)) { adj[size_t(r)].push_back(c); adj[size_t(c)].push_back(r); }
+        }
+    }
+    for (auto& a : adj) { std::sort(a.begin(), a.end()); a.erase(std::unique(a.begin(), a.end()), a.end()); }
+    const size_t dense_limit = std::max<size_t>(16, size_t(10.0 * std::sqrt(double(std::max(n, 1)))));
+    std::vector<char> gone(static_cast<size_t>(n), 0);
+    for (int v = 0; v < n; ++v) gone[size_t(v)] = out(v) ? 1 : 0;
+    std::vector<std::pair<size_t, int>> dense;
+    for (int v = 0; v < n; ++v)
+        if (!gone[size_t(v)] && adj[size_t(v)].size() > dense_limit) { dense.emplace_back(adj[size_t(v)].size(), v); gone[size_t(v)] = 1; }
+    if (!dense.empty())
+        for (int v = 0; v < n; ++v) {
+            auto& a = adj[size_t(v)];
+            a.erase(std::remove_if(a.begin(), a.end(), [&](int u) { return gone[size_t(u)] != 0; }), a.end());
+        }
+    std::set<std::pair<size_t, int>> queue;
+    for (int v = 0; v < n; ++v)
+        if (!gone[size_t(v)]) queue.emplace(adj[size_t(v)].size(), v);
+    std::vector<int> order;
+    order.reserve(size_t(n));
+    std::vector<int> merged;
+    while (!queue.empty()) {
+        if (queue.begin()->first + 1 >= queue.size()) {
+            // what is left is a clique: any order gives the same fill, and eliminating it vertex by vertex
+            // would cost the cube of its size in list merges
+            for (auto& dv : queue) order.push_back(dv.second);
+            break;
+        }
+        const int v = queue.begin()->second;
+        queue.erase(queue.begin());
+        gone[size_t(v)] = 1;
+        order.push_back(v);
+        const std::vector<int> nb = std::move(adj[size_t(v)]);
+        adj[size_t(v)].clear();
+        for (int u : nb) {
+            auto& a = adj[size_t(u)];
+            queue.erase({a.size(), u});
+            // a := (a + nb) without u and v; both lists are sorted
+            merged.clear();
+            size_t i = 0, j = 0;
+            while (i < a.size() || j < nb.size()) {
+                int x;
+                if (j >= nb.size() || (i < a.size() && a[i] < nb[j])) x = a[i++];
+                else if (i >= a.size() || nb[j] < a[i]) x = nb[j++];
+                else { x = a[i]; ++i; ++j; }
+                if (x != u && x != v) merged.push_back(x);
+            }
+            a.swap(merged);
+            queue.emplace(a.size(), u);
+        }
+    }
+    std::sort(dense.begin(), dense.end());
+    for (auto& d : dense) order.push_back(d.second);
+    return order;
+}
+
+// Pivots that cost nothing: a column with a single entry (that entry's row can be eliminated without touching any
+// other row) and a row with a single entry (its column is eliminated without fill). Found repeatedly on what is left;
+// in a circuit matrix this removes every net held by an ideal source together with the source's branch current, and
+// with them the supply rows that touch thousands of devices. Returns the (row, column) pairs in elimination order.
+inline std::vector<std::pair<int, int>> singleton_pivots(int n, const std::vector<int>& row_ptr, const std::vector<int>& col) {
+    std::vector<int> cptr(size_t(n) + 1, 0), crow(col.size());
+    for (int c : col) ++cptr[size_t(c) + 1];
+    for (int c = 0; c < n; ++c) cptr[size_t(c) + 1] += cptr[size_t(c)];
+    {
+        std::vector<int> fill(cptr.begin(), cptr.end() - 1);
+        for (int r = 0; r < n; ++r)
+            for (int k = row_ptr[size_t(r)]; k < row_ptr[size_t(r) + 1]; ++k) crow[size_t(fill[size_t(col[size_t(k)])]++)] = r;
+    }
+    std::vector<int> rcount(static_cast<size_t>(n)), ccount(static_cast<size_t>(n));
+    std::vector<char> rdead(static_cast<size_t>(n), 0), cdead(static_cast<size_t>(n), 0);
+    std::vector<std::pair<int, int>> work, out;  // (index, 0 = row / 1 = column)
+    for (int i = 0; i < n; ++i) {
+        rcount[size_t(i)] = row_ptr[size_t(i) + 1] - row_ptr[size_t(i)];
+        ccount[size_t(i)] = cptr[size_t(i) + 1] - cptr[size_t(i)];
+        if (ccount[size_t(i)] == 1) work.emplace_back(i, 1);
+    }
+    for (int i = 0; i < n; ++i)
+        if (rcount[size_t(i)] == 1) work.emplace_back(i, 0);
+    for (size_t w = 0; w < work.size(); ++w) {
+        int r = -1, c = -1;
+        if (work[w].second == 1) {
+            c = work[w].first;
+            if (cdead[size_t(c)] || ccount[size_t(c)] != 1) continue;
+            for (int k = cptr[size_t(c)]; k < cptr[size_t(c) + 1]; ++k)
+                if (!rdead[size_t(crow[size_t(k)])]) { r = crow[size_t(k)]; break; }
+        } else {
+            r = work[w].first;
+            if (rdead[size_t(r)] || rcount[size_t(r)] != 1) continue;
+            for (int k = row_ptr[size_t(r)]; k < row_ptr[size_t(r) + 1]; ++k)
+                if (!cdead[size_t(col[size_t(k)])]) { c = col[size_t(k)]; break; }
+        }
+        if (r < 0 || c < 0) continue;
+        rdead[size_t(r)] = cdead[size_t(c)] = 1;
+        out.emplace_back(r, c);
+        for (int k = row_ptr[size_t(r)]; k < row_ptr[size_t(r) + 1]; ++k) {
+            const int cc = col[size_t(k)];
+            if (!cdead[size_t(cc)] && --ccount[size_t(cc)] == 1) work.emplace_back(cc, 1);
+        }
+        for (int k = cptr[size_t(c)]; k < cptr[size_t(c) + 1]; ++k) {
+            const int rr = crow[size_t(k)];
+            if (!rdead[size_t(rr)] && --rcount[size_t(rr)] == 1) work.emplace_back(rr, 0);
+        }
+    }
+    return out;
+}
+
+struct FactoredLuStats { uint64_t orderings = 0, analyses = 0, refactors = 0, repivots = 0, refinement_rounds = 0; size_t factor_nnz = 0, singletons = 0; };
+
+class FactoredLU {
+public:
+    FactoredLuStats stats;
+
+    // Solves A x = rhs for the matrix given by (n, row_ptr, col, val). Returns false for a singular system.
+    bool solve(int n, const std::vector<int>& row_ptr, const std::vector<int>& col, const std::vector<double>& val,
+               const std::vector<double>& rhs, std::vector<double>& x) {
+        if (n == 0) { x.clear(); return true; }
+        if (valid_ && n == n_ && row_ptr == a_ptr_ && col == a_col_) {
+            if (refactor(val) && solve_refined(val, rhs, x)) return true;
+            ++stats.repivots;  // the row order chosen for earlier values no longer suits these
+        }
+        // threshold pivoting first (keeps the minimum-degree order, least fill); strict partial pivoting if that
+        // is not stable enough for this matrix
+        for (double threshold : {0.1, 1.0}) {
+            if (!analyse(n, row_ptr, col, val, threshold)) continue;
+            if (refactor(val) && solve_refined(val, rhs, x)) return true;
+        }
+        valid_ = false;
+        return false;
+    }
+
+private:
+    int n_ = 0;
+    bool valid_ = false, order_ready_ = false;
+    std::vector<int> a_ptr_, a_col_;
+    std::vector<int> q_, qinv_, p_, pinv_;       // position -> original column / row, and back
+    std::vector<int> lu_ptr_, lu_col_, diag_;    // pattern of L + U in permuted indices, columns ascending
+    std::vector<double> lu_val_, scale_, y_, res_, dx_;
+    std::vector<int> a_to_lu_, pos_, prefer_;    // prefer_[k]: the row the ordering had in mind for column position k, or -1
+
+    // ---- analysis -----------------------------------------------------------------------------------
+    bool analyse(int n, const std::vector<int>& row_ptr, const std::vector<int>& col, const std::vector<double>& val, double threshold) {
+        ++stats.analyses;
+        valid_ = false;
+        // free pivots first, minimum degree on what is left; the order depends on the pattern only, so a new
+        // analysis of the same pattern (new row choice for new values) reuses it
+        if (!(n == n_ && order_ready_ && row_ptr == a_ptr_ && col == a_col_)) {
+            const auto single = singleton_pivots(n, row_ptr, col);
+            std::vector<char> removed(static_cast<size_t>(n), 0), row_taken(static_cast<size_t>(n), 0);
+            q_.clear();
+            prefer_.assign(size_t(n), -1);
+            for (auto& rc : single) {
+                prefer_[q_.size()] = rc.first;
+                q_.push_back(rc.second);
+                removed[size_t(rc.second)] = 1;
+                row_taken[size_t(rc.first)] = 1;
+            }
+            for (int c : minimum_degree_order(n, row_ptr, col, removed)) {
+                if (!row_taken[size_t(c)]) prefer_[q_.size()] = c;
+                q_.push_back(c);
+            }
+            stats.singletons = single.size();
+            ++stats.orderings;
+            order_ready_ = true;
+        }
+        n_ = n;
+        a_ptr_ = row_ptr;
+        a_col_ = col;
+        qinv_.assign(size_t(n), 0);
+        for (int j = 0; j < n; ++j) qinv_[size_t(q_[size_t(j)])] = j;
+        if (!choose_rows(val, threshold)) return false;
+        pinv_.assign(size_t(n), 0);
+        for (int i = 0; i < n; ++i) pinv_[size_t(p_[size_t(i)])] = i;
+        symbolic();
+        a_to_lu_.assign(col.size(), -1);
+        for (int r = 0; r < n; ++r) {
+            const int i = pinv_[size_t(r)];
+            auto b = lu_col_.begin() + lu_ptr_[size_t(i)], e = lu_col_.begin() + lu_ptr_[size_t(i) + 1];
+            for (int k = row_ptr[size_t(r)]; k < row_ptr[size_t(r) + 1]; ++k) {
+                auto it = std::lower_bound(b, e, qinv_[size_t(col[size_t(k)])]);
+                a_to_lu_[size_t(k)] = int(it - lu_col_.begin());
+            }
+        }
+        lu_val_.assign(lu_col_.size(), 0.0);
+        scale_.assign(size_t(n), 1.0);
+        pos_.assign(size_t(n), -1);
+        stats.factor_nnz = lu_col_.size();
+        valid_ = true;
+        return true;
+    }
+
+    // One elimination with threshold partial pivoting, columns in the order q_: fills p_.
+    bool choose_rows(const std::vector<double>& val, const double thr) {
+        const int n = n_;
+        using Row = std::vector<std::pair<int, double>>;
+        std::vector<Row> rows(static_cast<size_t>(n));
+        std::vector<std::vector<int>> col_rows(static_cast<size_t>(n));
+        for (int r = 0; r < n; ++r) {
+            Row& row = rows[size_t(r)];
+            double mx = 0.0;
+            for (int k = a_ptr_[size_t(r)]; k < a_ptr_[size_t(r) + 1]; ++k) {
+                row.emplace_back(qinv_[size_t(a_col_[size_t(k)])], val[size_t(k)]);
+                mx = std::max(mx, std::fabs(val[size_t(k)]));
+            }
+            std::sort(row.begin(), row.end());
+            if (mx > 0.0)
+                for (auto& e : row) e.second /= mx;
+            for (auto& e : row) col_rows[size_t(e.first)].push_back(r);
+        }
+        auto entry = [](const Row& row, int c) -> double {
+            auto it = std::lower_bound(row.begin(), row.end(), c, [](const std::pair<int, double>& p, int cc) { return p.first < cc; });
+            return (it != row.end() && it->first == c) ? it->second : 0.0;
+        };
+        p_.assign(size_t(n), -1);
+        std::vector<char> used(static_cast<size_t>(n), 0);
+        Row merged;
+        for (int k = 0; k < n; ++k) {
+            auto& cands = col_rows[size_t(k)];
+            std::sort(cands.begin(), cands.end());
+            cands.erase(std::unique(cands.begin(), cands.end()), cands.end());
+            double best = 0.0;
+            for (int r : cands)
+                if (!used[size_t(r)]) best = std::max(best, std::fabs(entry(rows[size_t(r)], k)));
+            if (!(best > 1e-300)) return false;
+            const int want = prefer_[size_t(k)];
+            int p = -1;
+            size_t plen = 0;
+            if (want >= 0 && !used[size_t(want)] && std::fabs(entry(rows[size_t(want)], k)) >= thr * best) p = want;
+            else
+                for (int r : cands) {
+                    if (used[size_t(r)]) continue;
+                    double a = std::fabs(entry(rows[size_t(r)], k));
+                    if (a >= thr * best && (p < 0 || rows[size_t(r)].size() < plen)) { p = r; plen = rows[size_t(r)].size(); }
+                }
+            used[size_t(p)] = 1;
+            p_[size_t(k)] = p;
+            const Row& prow = rows[size_t(p)];
+            const double pv = entry(prow, k);
+            for (int r : cands) {
+                if (used[size_t(r)]) continue;
+                Row& row = rows[size_t(r)];
+                const double a = entry(row, k);
+                if (a == 0.0) continue;
+                const double f = a / pv;
+                merged.clear();
+                size_t i = 0, j = 0;
+                while (i < row.size() || j < prow.size()) {
+                    if (j >= prow.size() || (i < row.size() && row[i].first < prow[j].first)) merged.push_back(row[i++]);
+                    else if (i >= row.size() || prow[j].first < row[i].first) {
+                        if (prow[j].first > k) { merged.emplace_back(prow[j].first, -f * prow[j].second); col_rows[size_t(prow[j].first)].push_back(r); }
+                        ++j;
+                    } else {
+                        if (row[i].first != k) merged.emplace_back(row[i].first, row[i].second - f * prow[j].second);
+                        ++i; ++j;
+                    }
+                }
+                row.swap(merged);
+            }
+        }
+        return true;
+    }
+
+    // Pattern of L + U of the permuted matrix, row by row: a row starts as its own entries and takes over the
+    // upper part of every earlier row it has an entry under.
+    void symbolic() {
+        const int n = n_;
+        lu_ptr_.assign(size_t(n) + 1, 0);
+        lu_col_.clear();
+        diag_.assign(size_t(n), -1);
+        std::vector<int> mark(static_cast<size_t>(n), -1), cols;
+        std::priority_queue<int, std::vector<int>, std::greater<int>> lower;
+        std::vector<std::vector<int>> upper(static_cast<size_t>(n));  // columns right of the diagonal, ascending
+        for (int i = 0; i < n; ++i) {
+            const int r = p_[size_t(i)];
+            cols.clear();
+            auto add = [&](int c) {
+                if (mark[size_t(c)] == i) return;
+                mark[size_t(c)] = i;
+                cols.push_back(c);
+                if (c < i) lower.push(c);
+            };
+            add(i);  // the pivot position exists even where A has a structural zero there
+            for (int k = a_ptr_[size_t(r)]; k < a_ptr_[size_t(r) + 1]; ++k) add(qinv_[size_t(a_col_[size_t(k)])]);
+            while (!lower.empty()) {
+                const int k = lower.top();
+                lower.pop();
+                for (int c : upper[size_t(k)]) add(c);
+            }
+            std::sort(cols.begin(), cols.end());
+            for (int c : cols) {
+                if (c == i) diag_[size_t(i)] = int(lu_col_.size());
+                if (c > i) upper[size_t(i)].push_back(c);
+                lu_col_.push_back(c);
+            }
+            lu_ptr_[size_t(i) + 1] = int(lu_col_.size());
+        }
+    }
+
+    // ---- numeric ------------------------------------------------------------------------------------
+    bool refactor(const std::vector<double>& val) {
+        ++stats.refactors;
+        const int n = n_;
+        std::fill(lu_val_.begin(), lu_val_.end(), 0.0);
+        for (int r = 0; r < n; ++r) {
+            double mx = 0.0;
+            for (int k = a_ptr_[size_t(r)]; k < a_ptr_[size_t(r) + 1]; ++k) mx = std::max(mx, std::fabs(val[size_t(k)]));
+            const double s = mx > 0.0 ? 1.0 / mx : 1.0;
+            scale_[size_t(r)] = s;
+            for (int k = a_ptr_[size_t(r)]; k < a_ptr_[size_t(r) + 1]; ++k) lu_val_[size_t(a_to_lu_[size_t(k)])] = val[size_t(k)] * s;
+        }
+        for (int i = 0; i < n; ++i) {
+            const int b = lu_ptr_[size_t(i)], e = lu_ptr_[size_t(i) + 1], d = diag_[size_t(i)];
+            for (int t = b; t < e; ++t) pos_[size_t(lu_col_[size_t(t)])] = t;
+            for (int t = b; t < d; ++t) {
+                const int k = lu_col_[size_t(t)];
+                const double lik = lu_val_[size_t(t)] / lu_val_[size_t(diag_[size_t(k)])];
+                lu_val_[size_t(t)] = lik;
+                if (lik == 0.0) continue;
+                for (int u = diag_[size_t(k)] + 1; u < lu_ptr_[size_t(k) + 1]; ++u) lu_val_[size_t(pos_[size_t(lu_col_[size_t(u)])])] -= lik * lu_val_[size_t(u)];
+            }
+            for (int t = b; t < e; ++t) pos_[size_t(lu_col_[size_t(t)])] = -1;
+            const double pv = std::fabs(lu_val_[size_t(d)]);
+            if (!(pv > 1e-300) || !std::isfinite(pv)) return false;
+        }
+        return true;
+    }
+
+    // x := A^-1 b through the factors (b in original row order, x in original column order).
+    void apply(const std::vector<double>& b, std::vector<double>& x) {
+        const int n = n_;
+        y_.resize(size_t(n));
+        for (int i = 0; i < n; ++i) {
+            const int r = p_[size_t(i)];
+            double acc = b[size_t(r)] * scale_[size_t(r)];
+            for (int t = lu_ptr_[size_t(i)]; t < diag_[size_t(i)]; ++t) acc -= lu_val_[size_t(t)] * y_[size_t(lu_col_[size_t(t)])];
+            y_[size_t(i)] = acc;
+        }
+        for (int i = n - 1; i >= 0; --i) {
+            double acc = y_[size_t(i)];
+            for (int t = diag_[size_t(i)] + 1; t < lu_ptr_[size_t(i) + 1]; ++t) acc -= lu_val_[size_t(t)] * y_[size_t(lu_col_[size_t(t)])];
+            y_[size_t(i)] = acc / lu_val_[size_t(diag_[size_t(i)])];
+        }
+        x.resize(size_t(n));
+        for (int j = 0; j < n; ++j) x[size_t(q_[size_t(j)])] = y_[size_t(j)];
+    }
+
+    bool solve_refined(const std::vector<double>& val, const std::vector<double>& rhs, std::vector<double>& x) {
+        const int n = n_;
+        apply(rhs, x);
+        res_.resize(size_t(n));
+        for (int round = 0; round < 4; ++round) {
+            double worst = 0.0;
+            for (int r = 0; r < n; ++r) {
+                double ax = 0.0, mag = std::fabs(rhs[size_t(r)]);
+                for (int k = a_ptr_[size_t(r)]; k < a_ptr_[size_t(r) + 1]; ++k) {
+                    const double t = val[size_t(k)] * x[size_t(a_col_[size_t(k)])];
+                    ax += t;
+                    mag += std::fabs(t);
+                }
+                res_[size_t(r)] = rhs[size_t(r)] - ax;
+                if (mag > 0.0) worst = std::max(worst, std::fabs(res_[size_t(r)]) / mag);
+            }
+            if (!std::isfinite(worst)) return false;
+            if (!(worst > 1e-10)) return true;
+            if (round == 3) return worst < 1e-6;
+            ++stats.refinement_rounds;
+            apply(res_, dx_);
+            for (int i = 0; i < n; ++i) x[size_t(i)] += dx_[size_t(i)];
+        }
+        return true;
+    }
+};
+
+}  // namespace nspice

@@ -14,8 +14,10 @@ from __future__ import annotations
 import json
 import os
 import platform
+import re
 import socket
 import subprocess
+import sys
 import tempfile
 import time
 from concurrent.futures import ThreadPoolExecutor
@@ -115,11 +117,14 @@ def discover_hardware() -> HardwareTopology:
         numa = max(1, len([d for d in os.listdir("/sys/devices/system/node") if d.startswith("node")]))
     except OSError:
         pass
+    # GPUs are counted from the driver's device nodes: importing torch for this costs seconds per process
     gpus = 0
     try:
-        import torch
-
-        gpus = torch.cuda.device_count() if torch.cuda.is_available() else 0
+        torch = sys.modules.get("torch")
+        if torch is not None:
+            gpus = torch.cuda.device_count() if torch.cuda.is_available() else 0
+        else:
+            gpus = len([d for d in os.listdir("/dev") if re.fullmatch(r"nvidia\d+", d)])
     except Exception:
         pass
     return HardwareTopology(cpus, numa, ram, gpus, socket.gethostname(), platform.system())

@@ -227,8 +227,11 @@ def _partition_metis(adj: list[dict[int, float]], nodes: list[int], k: int) -> d
 
 # ---- main entry points --------------------------------------------------------------------------------
 
-def partition_flat(flat: dict, k: int, method: str = "auto", feedback_nets: Optional[list[set[str]]] = None) -> PartitionResult:
-    """Partitions a numeric netlist (native JSON form as a dict) into ``k`` partition files."""
+def partition_flat(flat: dict, k: int, method: str = "auto", feedback_nets: Optional[list[set[str]]] = None,
+                   keep_channels: bool = True) -> PartitionResult:
+    """Partitions a numeric netlist (native JSON form as a dict) into ``k`` partition files. With ``keep_channels``
+    nets joined by a transistor channel always land in the same partition (fewer than ``k`` partitions result when
+    the deck has fewer channel-connected components than that)."""
     from . import _native
 
     if k <= 0:
@@ -251,6 +254,16 @@ def partition_flat(flat: dict, k: int, method: str = "auto", feedback_nets: Opti
             b = el["VoltageSource"]
             if b["pos"] > 0 and b["neg"] > 0:
                 uf.union(b["pos"], b["neg"])
+    # Channel-connected components stay whole: the drain and source of a transistor are coupled in both
+    # directions through the channel conductance, and internal nets of a series stack carry no capacitance
+    # at all, so block relaxation across such a cut converges slowly or not at all. A cut through a gate
+    # is one-directional (no gate current in the level-1 model) and relaxes in one sweep.
+    if keep_channels:
+        for el in elements:
+            if _kind(el) == "Mosfet":
+                b = el["Mosfet"]
+                if b["d"] > 0 and b["s"] > 0 and b["d"] not in held and b["s"] not in held:
+                    uf.union(b["d"], b["s"])
     enforced = 0
     name_to_net = {nm: i + 1 for i, nm in enumerate(names)}
     for group in feedback_nets or []:
@@ -266,7 +279,8 @@ def partition_flat(flat: dict, k: int, method: str = "auto", feedback_nets: Opti
     adj: list[dict[int, float]] = [dict() for _ in range(n + 1)]
     for el in elements:
         t = [uf.find(x) for x in _terminals(el) if x > 0 and x not in held]
-        w = 10.0 if _kind(el) == "Mosfet" else 5.0
+        # with whole channels a transistor only contributes its gate edge, the cheapest place to cut
+        w = (1.0 if keep_channels else 10.0) if _kind(el) == "Mosfet" else 5.0
         for i in range(len(t)):
             for j in range(i + 1, len(t)):
                 if t[i] != t[j]:

@@ -143,7 +143,7 @@ def bench_to_spice(bench_text: str, title: str = "synthesised", vdd: float = 1.8
     for i, name in enumerate(inputs):
         if name.lower() in given:
             continue
-        per = period * (2 ** i)
+        per = period * (2 ** min(i, 24))  # beyond 2^24 periods an input never toggles within any run; also keeps the float finite
         lines.append(f"VIN{i} {name} 0 PULSE(0 {vdd} {per / 4!r} 20p 20p {per / 2!r} {per!r})")
     lines += list(stimulus) + deck.lines + [_MODELS.rstrip(), f"* outputs: {' '.join(outputs)}", ".end"]
     return "\n".join(lines) + "\n"

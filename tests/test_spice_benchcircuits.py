@@ -228,3 +228,30 @@ def test_partial_run_raises_unless_allowed(tmp_path):
         cx.run_nangila_waveform(str(deck), tstop=5e-12, dt=1e-12, in_process=True)
     w = cx.run_nangila_waveform(str(deck), tstop=5e-12, dt=1e-12, in_process=True, allow_partial=True)
     assert len(w.times) == 1 and w.times[0] == 0.0
+
+
+def test_partitions_keep_transistor_channels_whole_and_logic_runs_partitioned(tmp_path):
+    import nangila_spice as ns
+    from nangila_spice import correctness as cx
+    from nangila_spice.partitioner import partition_flat
+
+    case = next(c for c in cx.official_correctness_cases() if c.name == "alu2")
+    path = case.materialize(str(tmp_path))
+    flat = ns.parse_netlist(path).to_native()
+    flat.pop("warnings", None)
+    names = flat["node_names"]
+    held = {names.index("vdd") + 1}
+    for keep, want_cut in ((True, False), (False, True)):
+        pr = partition_flat(flat, 4, "spectral", keep_channels=keep)
+        assert len(pr.partitions) == 4
+        cut = 0
+        for el in flat["elements"]:
+            if "Mosfet" in el:
+                d, s = el["Mosfet"]["d"], el["Mosfet"]["s"]
+                if d > 0 and s > 0 and d not in held and s not in held:
+                    cut += pr.net_assignment[names[d - 1]] != pr.net_assignment[names[s - 1]]
+        assert (cut > 0) == want_cut, (keep, cut)
+    res = ns.simulate(path, partitions=4, tstop=1e-9, dt=1e-12)
+    assert res.success and res.validation_status == "partitioned_validated", res.warnings
+    assert res.solver_stats["stats"]["completed"] and res.solver_stats["stats"]["unconverged_steps"] == 0
+    assert res.reference_comparison.max_abs_error < 5e-3

@@ -319,3 +319,89 @@ def test_spmv_row_block_table():
     assert build_row_blocks(rp).tolist() == [0, 1, 2, 4, 5]
     assert build_row_blocks(np.array([0, 0, 0], dtype=np.int32)).tolist() == [0, 2]
     assert col.size == val.size == rp.size * 0 + 3 * 5000 - 2
+
+
+def _csr(a):
+    rp, col, val = [0], [], []
+    for row in a:
+        nz = np.nonzero(row)[0]
+        col += nz.tolist()
+        val += row[nz].tolist()
+        rp.append(len(col))
+    return rp, col, val
+
+
+def test_factored_lu_matches_numpy_and_reuses_its_analysis():
+    rng = np.random.default_rng(7)
+    n = 120
+    a = np.zeros((n, n))
+    for i in range(n):
+        a[i, i] = rng.uniform(0.5, 2.0) if rng.random() > 0.25 else 0.0  # zero diagonals need a row exchange
+        for j in rng.integers(0, n, 3):
+            a[i, j] += rng.normal()
+            a[j, i] += rng.normal()
+    rp, col, val = _csr(a)
+    lu = N.FactoredLU()
+    for trial in range(6):
+        scale = 1.0 + 0.05 * trial * rng.normal(size=len(val))      # same pattern, drifting values
+        v = (np.array(val) * scale).tolist()
+        m = np.zeros((n, n))
+        for r in range(n):
+            for k in range(rp[r], rp[r + 1]):
+                m[r, col[k]] = v[k]
+        b = rng.normal(size=n)
+        ok, x = lu.solve(n, rp, col, v, b.tolist())
+        want = np.linalg.solve(m, b)
+        assert ok and np.abs(np.array(x) - want).max() <= 1e-9 * np.abs(want).max()
+    st = lu.stats()
+    assert st["orderings"] == 1 and st["refactors"] >= 6 and st["analyses"] < 6 and st["factor_nnz"] >= len(val)
+    # a singular matrix is reported, not solved
+    z = np.array([[1.0, 2.0], [2.0, 4.0]])
+    rp2, col2, val2 = _csr(z)
+    ok, _ = N.FactoredLU().solve(2, rp2, col2, val2, [1.0, 1.0])
+    assert not ok
+    # a new pattern on the same object starts over
+    ok, x = lu.solve(2, [0, 1, 2], [0, 1], [2.0, 4.0], [2.0, 4.0])
+    assert ok and x == [1.0, 1.0] and lu.stats()["orderings"] == 2
+
+
+def test_singleton_pivots_take_out_sources_and_order_is_a_permutation():
+    # v1 -- R -- v2 -- R -- ground, source on v1: unknowns (v1, v2, i_src); the source rows are free pivots
+    g = 1e-3
+    a = np.array([[g, -g, 1.0], [-g, 2 * g, 0.0], [1.0, 0.0, 0.0]])
+    rp, col, val = _csr(a)
+    piv = N.singleton_pivots(3, rp, col)
+    assert (0, 2) in piv or (2, 0) in piv          # column i_src only appears in row v1; row i_src only has column v1
+    assert len(piv) == 3                            # everything cascades here
+    ok, x = N.FactoredLU().solve(3, rp, col, val, [0.0, 0.0, 1.8])
+    assert ok and abs(x[0] - 1.8) < 1e-12 and abs(x[1] - 0.9) < 1e-12
+    # a 2-D grid Laplacian: nothing is a singleton, and the order must be a permutation with less fill than the natural one
+    k = 12
+    n = k * k
+    lap = np.zeros((n, n))
+    for i in range(k):
+        for j in range(k):
+            v = i * k + j
+            lap[v, v] = 4.1
+            for di, dj in ((1, 0), (-1, 0), (0, 1), (0, -1)):
+                if 0 <= i + di < k and 0 <= j + dj < k:
+                    lap[v, (i + di) * k + j + dj] = -1.0
+    rp, col, val = _csr(lap)
+    assert N.singleton_pivots(n, rp, col) == []
+    order = N.minimum_degree_order(n, rp, col)
+    assert sorted(order) == list(range(n))
+    lu = N.FactoredLU()
+    ok, x = lu.solve(n, rp, col, val, np.ones(n).tolist())
+    assert ok and np.abs(lap @ np.array(x) - 1.0).max() < 1e-10
+    natural = np.linalg.cholesky(lap)
+    assert lu.stats()["factor_nnz"] < 2 * np.count_nonzero(np.abs(natural) > 1e-14)
+
+
+def test_large_logic_deck_runs_on_the_refactoring_path():
+    from nangila_spice import benchcircuits as bc
+
+    js, _ = N.parse_spice(bc.deck("c1355", cload="20f"))
+    r = N.simulate(js, 50e-12, 1e-12)
+    nr = r["newton"]
+    assert r["stats"]["completed"] and nr["lu_fallbacks"] == 0 and nr["lu_singletons"] > 40
+    assert nr["lu_analyses"] < nr["lu_refactors"] / 5
