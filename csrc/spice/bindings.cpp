@@ -1,6 +1,7 @@
 // Python module nangila_spice._native: the simulator core for tests, the orchestrator and notebooks.
 // Netlists cross the boundary as JSON text (the partition-file form), numeric data as lists.
 #include <pybind11/functional.h>
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -37,6 +38,18 @@ static const char* class_name(SignalClass c) {
         case SignalClass::Stiff: return "Stiff";
         default: return "Unknown";
     }
+}
+
+// Waveform samples as one (points x nets) float64 array: a list of lists costs a Python float per sample.
+static py::array_t<double> waveform_array(const std::vector<WaveformPoint>& w) {
+    const py::ssize_t rows = py::ssize_t(w.size()), cols = rows ? py::ssize_t(w[0].values.size()) : 0;
+    py::array_t<double> a({rows, cols});
+    double* dst = a.mutable_data();
+    for (py::ssize_t r = 0; r < rows; ++r) {
+        const auto& v = w[size_t(r)].values;
+        for (py::ssize_t c = 0; c < cols; ++c) dst[r * cols + c] = size_t(c) < v.size() ? v[size_t(c)] : 0.0;
+    }
+    return a;
 }
 
 PYBIND11_MODULE(_native, m) {
@@ -76,15 +89,15 @@ PYBIND11_MODULE(_native, m) {
             fin = s.run();
         }
         std::vector<double> t;
-        std::vector<std::vector<double>> v;
-        for (auto& p : s.waveform) { t.push_back(p.time); v.push_back(p.values); }
+        for (auto& p : s.waveform) t.push_back(p.time);
+        py::array_t<double> v = waveform_array(s.waveform);
         py::dict out;
         out["node_names"] = names; out["time"] = t; out["values"] = v; out["final"] = fin.voltages; out["stats"] = stats_dict(s.stats);
         py::dict nr;
         nr["total_iterations"] = s.engine().newton.stats.total_iterations; nr["linear_solves"] = s.engine().newton.stats.linear_solves;
         nr["failed"] = s.engine().newton.stats.failed_count; nr["be_fallbacks"] = s.engine().be_fallbacks;
         { auto& lu = s.engine().newton.linear.lu.stats;
-          nr["lu_analyses"] = lu.analyses; nr["lu_refactors"] = lu.refactors; nr["lu_repivots"] = lu.repivots;
+          nr["lu_analyses"] = lu.analyses; nr["lu_refactors"] = lu.refactors; nr["lu_reuses"] = lu.reuses; nr["lu_repivots"] = lu.repivots;
           nr["lu_refinement_rounds"] = lu.refinement_rounds; nr["lu_factor_nnz"] = lu.factor_nnz; nr["lu_singletons"] = lu.singletons;
           nr["lu_fallbacks"] = s.engine().newton.linear.stats.lu_fallbacks; }
         nr["step_cuts"] = s.engine().step_cuts; nr["dc_gmin_stepping"] = s.engine().dc_gmin_stepping;
@@ -115,8 +128,8 @@ PYBIND11_MODULE(_native, m) {
             r.run();
         }
         std::vector<double> t;
-        std::vector<std::vector<double>> v;
-        for (auto& p : r.waveform) { t.push_back(p.time); v.push_back(p.values); }
+        for (auto& p : r.waveform) t.push_back(p.time);
+        py::array_t<double> v = waveform_array(r.waveform);
         py::dict st;
         st["steps"] = r.stats.steps; st["prediction_hits"] = r.stats.prediction_hits; st["prediction_misses"] = r.stats.prediction_misses;
         st["resolves"] = r.stats.resolves; st["messages"] = r.stats.messages; st["bytes_sent"] = r.stats.bytes_sent; st["codec_ratio"] = r.stats.codec_ratio;
@@ -149,7 +162,7 @@ PYBIND11_MODULE(_native, m) {
         })
         .def("stats", [](const FactoredLU& lu) {
             py::dict d;
-            d["orderings"] = lu.stats.orderings; d["analyses"] = lu.stats.analyses; d["refactors"] = lu.stats.refactors; d["repivots"] = lu.stats.repivots;
+            d["orderings"] = lu.stats.orderings; d["analyses"] = lu.stats.analyses; d["refactors"] = lu.stats.refactors; d["reuses"] = lu.stats.reuses; d["repivots"] = lu.stats.repivots;
             d["refinement_rounds"] = lu.stats.refinement_rounds; d["factor_nnz"] = lu.stats.factor_nnz; d["singletons"] = lu.stats.singletons;
             return d;
         });

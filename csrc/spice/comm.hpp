@@ -76,9 +76,15 @@ public:
         out.from = msg.from; out.to = msg.to; out.time = msg.time;
         std::vector<std::pair<uint64_t, double>> raw;
         double max_delta = 0.0;
+        // the caller usually lists predictions in the order of the updates: look there first, else search from
+        // where the last match was found
+        size_t at = 0;
         for (auto& u : msg.updates) {
             double pred = 0.0;
-            for (auto& p : predicted) if (p.first == u.first) { pred = p.second; break; }
+            for (size_t tries = 0; tries < predicted.size(); ++tries) {
+                const size_t i = (at + tries) % predicted.size();
+                if (predicted[i].first == u.first) { pred = predicted[i].second; at = i + 1; break; }
+            }
             double d = u.second - pred;
             if (std::fabs(d) < min_delta) { ++stats.skipped; continue; }
             max_delta = std::max(max_delta, std::fabs(d));
@@ -99,9 +105,12 @@ public:
     ResidualMessage decode(const CompressedResidual& c) {
         ResidualMessage m;
         m.from = c.from; m.to = c.to; m.time = c.time;
-        for (auto& d : c.deltas) {
+        for (size_t k = 0; k < c.deltas.size(); ++k) {
+            auto& d = c.deltas[k];
             double base = 0.0;
-            for (auto& b : c.base_values) if (b.first == d.first) { base = b.second; break; }
+            if (k < c.base_values.size() && c.base_values[k].first == d.first) base = c.base_values[k].second;  // the encoder writes both in step
+            else
+                for (auto& b : c.base_values) if (b.first == d.first) { base = b.second; break; }
             m.updates.emplace_back(d.first, base + double(d.second) * c.scale);
         }
         ++stats.decoded;

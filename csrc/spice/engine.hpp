@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <map>
 #include <tuple>
+#include <unordered_map>
 
 #include "circuit.hpp"
 #include "sparse.hpp"
@@ -60,9 +61,10 @@ public:
     NrStats stats;
     LinearSolver linear;
 
-    // The first `limited` unknowns are node voltages and get the per-iteration step limit.
+    // The first `limited` unknowns are node voltages and get the per-iteration step limit. A system that does
+    // not depend on the guess (`linear_system`) is solved once: the first solution is exact.
     template <class Build>
-    NrOutcome solve(std::vector<double> guess, CsrMatrix& m, Build&& build, int limited = 0) {
+    NrOutcome solve(std::vector<double> guess, CsrMatrix& m, Build&& build, int limited = 0, bool linear_system = false) {
         NrOutcome out;
         out.x = std::move(guess);
         out.x.resize(size_t(m.n), 0.0);
@@ -81,7 +83,7 @@ public:
             }
             out.iterations = it + 1;
             out.final_error = max_err;
-            if (max_err < 1.0) { out.converged = true; break; }
+            if (max_err < 1.0 || (linear_system && config.damping == 1.0)) { out.converged = true; break; }
         }
         stats.total_iterations += uint64_t(out.iterations);
         if (out.converged) ++stats.converged_count; else ++stats.failed_count;
@@ -324,20 +326,22 @@ public:
 
     // Plain Newton from the seeded state first; if that fails, conductance stepping: solve with a large
     // conductance from every node to ground, then lower it by decades with the last solution as the guess.
-    bool solve_dc(const PartitionState& seeded, PartitionState& out) {
-        NrOutcome r = run_newton(seeded, {}, 0.0, 0.0, Integration::BackwardEuler);
+    // `ghost_voltages` pins foreign nets of a partition.
+    bool solve_dc(const PartitionState& seeded, PartitionState& out, const std::vector<std::pair<uint64_t, double>>& ghost_voltages = {}) {
+        const std::vector<std::pair<int, double>> pins = node_pins(ghost_voltages);
+        NrOutcome r = run_newton(seeded, pins, 0.0, 0.0, Integration::BackwardEuler);
         if (!r.converged) {
             const double target = asm_.gmin;
             PartitionState g = seeded;
             bool ok = true;
             for (double gm = 1e-2; ok && gm > target * 1.5; gm *= 0.1) {
                 asm_.gmin = gm;
-                r = run_newton(g, {}, 0.0, 0.0, Integration::BackwardEuler);
+                r = run_newton(g, pins, 0.0, 0.0, Integration::BackwardEuler);
                 ok = r.converged;
                 if (ok) g.voltages = r.x;
             }
             asm_.gmin = target;
-            if (ok) r = run_newton(g, {}, 0.0, 0.0, Integration::BackwardEuler);
+            if (ok) r = run_newton(g, pins, 0.0, 0.0, Integration::BackwardEuler);
             ++dc_gmin_stepping;
         }
         if (!r.converged) return false;
@@ -353,17 +357,29 @@ public:
     // steps (recursively, NrConfig::max_cuts deep) with the pins held.
     bool solve_step(const PartitionState& cur, const std::vector<std::pair<uint64_t, double>>& ghost_voltages, double dt,
                     PartitionState& out) {
-        std::vector<std::pair<int, double>> pins;
-        for (auto& gv : ghost_voltages)
-            for (auto& link : netlist.ghost_map)
-                if (link.net_id == gv.first) { pins.emplace_back(link.local_node, gv.second); break; }
-        return advance(cur, pins, dt, 0, out);
+        return advance(cur, node_pins(ghost_voltages), dt, 0, out);
     }
 
     uint64_t be_fallbacks = 0, step_cuts = 0, dc_gmin_stepping = 0;
 
 private:
     Assembler asm_;
+    std::unordered_map<uint64_t, int> ghost_node_;  // net id -> local node, built on first use
+
+    std::vector<std::pair<int, double>> node_pins(const std::vector<std::pair<uint64_t, double>>& ghost_voltages) {
+        std::vector<std::pair<int, double>> pins;
+        if (ghost_voltages.empty()) return pins;
+        if (ghost_node_.size() != netlist.ghost_map.size()) {
+            ghost_node_.clear();
+            for (auto& link : netlist.ghost_map) ghost_node_.emplace(link.net_id, link.local_node);
+        }
+        pins.reserve(ghost_voltages.size());
+        for (auto& gv : ghost_voltages) {
+            auto it = ghost_node_.find(gv.first);
+            if (it != ghost_node_.end()) pins.emplace_back(it->second, gv.second);
+        }
+        return pins;
+    }
 
     bool advance(const PartitionState& cur, const std::vector<std::pair<int, double>>& pins, double dt, int depth, PartitionState& out) {
         if (single_step(cur, pins, dt, out)) return true;
@@ -405,7 +421,7 @@ private:
         std::vector<double> guess = cur.voltages;
         return newton.solve(std::move(guess), asm_.m, [&](const std::vector<double>& x, CsrMatrix&) {
             if (nonlinear) asm_.stamp_nonlinear(x);
-        }, nonlinear ? asm_.num_nodes : 0);
+        }, nonlinear ? asm_.num_nodes : 0, !nonlinear);
     }
 };
 

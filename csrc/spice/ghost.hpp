@@ -7,6 +7,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <unordered_map>
 #include <utility>
 #include <vector>
 
@@ -227,7 +228,13 @@ public:
     AccuracyLogger accuracy;
     AdaptiveConfidence adaptive;
     explicit GhostBuffer(uint32_t base_depth = 5) : adaptive(base_depth) {}
-    void add(GhostNode n) { nodes.push_back(std::move(n)); }
+    void add(GhostNode n) { index_.emplace(n.net_id, nodes.size()); nodes.push_back(std::move(n)); }
+    // Position of a net in `nodes`, or size() when the buffer does not hold it.
+    size_t index_of(uint64_t net_id) const {
+        if (index_.size() != nodes.size()) rebuild_index();  // `nodes` is public; tolerate direct pushes
+        auto it = index_.find(net_id);
+        return it == index_.end() ? nodes.size() : it->second;
+    }
     size_t size() const { return nodes.size(); }
     std::vector<std::pair<uint64_t, double>> predict_all(double t) const {
         std::vector<std::pair<uint64_t, double>> out;
@@ -236,20 +243,27 @@ public:
     }
     bool apply_corrections(const std::vector<Correction>& cs, double reltol) {
         bool all_ok = true;
-        for (auto& c : cs)
-            for (auto& g : nodes)
-                if (g.net_id == c.net_id) {
-                    Prediction p = g.predict_named(c.time);
-                    bool ok = g.apply_correction(c.voltage, c.time, reltol);
-                    g.active_predictor = p.predictor;
-                    accuracy.record(c.net_id, p.predictor, p.value, c.voltage, reltol);
-                    adaptive.update(c.net_id, ok);
-                    all_ok = all_ok && ok;
-                    break;
-                }
+        for (auto& c : cs) {
+            const size_t i = index_of(c.net_id);
+            if (i >= nodes.size()) continue;
+            GhostNode& g = nodes[i];
+            Prediction p = g.predict_named(c.time);
+            bool ok = g.apply_correction(c.voltage, c.time, reltol);
+            g.active_predictor = p.predictor;
+            accuracy.record(c.net_id, p.predictor, p.value, c.voltage, reltol);
+            adaptive.update(c.net_id, ok);
+            all_ok = all_ok && ok;
+        }
         return all_ok;
     }
     uint32_t effective_depth() const { return adaptive.effective_depth(); }
+
+private:
+    mutable std::unordered_map<uint64_t, size_t> index_;
+    void rebuild_index() const {
+        index_.clear();
+        for (size_t i = 0; i < nodes.size(); ++i) index_.emplace(nodes[i].net_id, i);
+    }
 };
 
 }  // namespace nspice

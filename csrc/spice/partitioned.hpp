@@ -18,6 +18,7 @@
 #include <memory>
 #include <set>
 #include <thread>
+#include <unordered_map>
 
 #include "parser.hpp"
 #include "transient.hpp"
@@ -108,7 +109,11 @@ public:
         for (uint32_t p = 0; p < k; ++p) {
             Part part;
             part.names = parts[p].names_or_default();
-            for (auto& g : parts[p].ghost_map) { part.ghosts.add(GhostNode(g.net_id, g.owner)); part.ghost_nodes.insert(g.local_node); }
+            for (auto& g : parts[p].ghost_map) {
+                part.ghost_index.emplace(g.net_id, part.ghosts.size());
+                part.ghosts.add(GhostNode(g.net_id, g.owner));
+                part.ghost_nodes.insert(g.local_node);
+            }
             part.engine.reset(new SolverEngine(std::move(parts[p])));
             parts_.push_back(std::move(part));
         }
@@ -117,11 +122,14 @@ public:
             for (auto& g : parts_[q].engine->netlist.ghost_map) {
                 if (g.owner >= k) throw std::runtime_error("ghost owner outside the partition set");
                 Part& owner = parts_[g.owner];
-                int local = -1;
-                for (size_t i = 0; i < owner.names.size(); ++i)
-                    if (net_name_hash(owner.names[i]) == g.net_id && !owner.ghost_nodes.count(int(i) + 1)) { local = int(i) + 1; break; }
+                if (owner.owned_by_hash.empty())
+                    for (size_t i = 0; i < owner.names.size(); ++i)
+                        if (!owner.ghost_nodes.count(int(i) + 1)) owner.owned_by_hash.emplace(net_name_hash(owner.names[i]), int(i) + 1);
+                auto found = owner.owned_by_hash.find(g.net_id);
+                const int local = found == owner.owned_by_hash.end() ? -1 : found->second;
                 if (local < 0) throw std::runtime_error("partition " + std::to_string(g.owner) + " does not own a net that partition " + std::to_string(q) + " lists as ghost");
                 owner.exports[q].emplace_back(g.net_id, local);
+                parts_[q].ghost_src.push_back({g.owner, local});
             }
         for (uint32_t p = 0; p < k; ++p)
             for (size_t i = 0; i < parts_[p].names.size(); ++i)
@@ -194,7 +202,11 @@ private:
         std::vector<std::string> names;
         std::map<uint32_t, std::vector<std::pair<uint64_t, int>>> exports;  // consumer -> (net id, local node)
         PartitionState state{0}, next{0};
-        std::vector<std::pair<uint64_t, double>> pins, latest;
+        std::vector<std::pair<uint64_t, double>> pins, latest;              // in the order of ghosts.nodes
+        struct GhostSrc { uint32_t owner; int local; };
+        std::vector<GhostSrc> ghost_src;                                      // where each ghost's value lives, same order
+        std::unordered_map<uint64_t, size_t> ghost_index;                     // net id -> position in ghosts.nodes
+        std::unordered_map<uint64_t, int> owned_by_hash;                      // name hash -> local node of the nets this partition owns
     };
     struct MergedRef { uint32_t part; size_t index; };
     PartitionedConfig cfg_;
@@ -208,17 +220,23 @@ private:
     // (when count is set) score their predictions. Returns whether every prediction was a hit.
     bool exchange(double t, bool count) {
         const uint32_t k = uint32_t(parts_.size());
-        for (auto& part : parts_) part.latest.clear();
+        // `pins` and `latest` are in the order of the partition's ghost list; a value that no message corrects
+        // (its delta was below the codec's floor) stays what was pinned
+        for (auto& part : parts_) part.latest = part.pins;
         for (uint32_t p = 0; p < k; ++p)
             for (auto& ex : parts_[p].exports) {
                 ResidualMessage m;
                 m.from = p; m.to = ex.first; m.time = t;
-                for (auto& e : ex.second) m.updates.emplace_back(e.first, parts_[p].next.voltages[size_t(e.second - 1)]);
                 // the sender encodes against what the receiver pinned, which both sides know after the
                 // previous exchange; on the first sweep that is the receiver's prediction
+                const Part& to = parts_[ex.first];
                 std::vector<std::pair<uint64_t, double>> base;
-                for (auto& u : m.updates)
-                    for (auto& pin : parts_[ex.first].pins) if (pin.first == u.first) { base.push_back(pin); break; }
+                base.reserve(ex.second.size());
+                for (auto& e : ex.second) {
+                    m.updates.emplace_back(e.first, parts_[p].next.voltages[size_t(e.second - 1)]);
+                    auto it = to.ghost_index.find(e.first);
+                    if (it != to.ghost_index.end() && it->second < to.pins.size()) base.push_back(to.pins[it->second]);
+                }
                 mesh_[p]->send_residual(m, base);
             }
         bool all_ok = true;
@@ -227,8 +245,10 @@ private:
             for (auto& fm : mesh_[q]->drain_inbox()) {
                 if (fm.kind != FabricMessage::Residual) continue;
                 ResidualMessage m = mesh_[q]->decode_residual(fm.residual);
-                // nets whose delta was below the codec's floor keep the pinned value
-                for (auto& u : m.updates) set_latest(part, u.first, u.second);
+                for (auto& u : m.updates) {
+                    auto it = part.ghost_index.find(u.first);
+                    if (it != part.ghost_index.end() && it->second < part.latest.size()) part.latest[it->second].second = u.second;
+                }
                 if (count) {
                     std::vector<Correction> cs;
                     for (auto& u : m.updates) cs.push_back({u.first, u.second, t});
@@ -238,18 +258,8 @@ private:
                     all_ok = all_ok && ok;
                 }
             }
-            // pinned values that no message corrected are carried over
-            for (auto& pin : part.pins) {
-                bool have = false;
-                for (auto& l : part.latest) if (l.first == pin.first) { have = true; break; }
-                if (!have) part.latest.push_back(pin);
-            }
         }
         return all_ok;
-    }
-    static void set_latest(Part& part, uint64_t id, double v) {
-        for (auto& l : part.latest) if (l.first == id) { l.second = v; return; }
-        part.latest.emplace_back(id, v);
     }
     // Block relaxation of the DC point: each partition solves its operating point with the ghosts
     // pinned to the neighbours' latest values.
@@ -261,17 +271,15 @@ private:
             for (uint32_t p = 0; p < k; ++p) {
                 Part& part = parts_[p];
                 if (!part.engine->netlist.initial_conditions.empty()) continue;
-                // pin ghosts by writing them as Ghost elements through solve_step's pin path at dt = 0
+                // ghosts pinned to what their owners hold now; the partition's own DC solve may step its conductance
                 PartitionState out{0};
                 std::vector<std::pair<uint64_t, double>> pins;
-                for (auto& g : part.engine->netlist.ghost_map) {
-                    const Part& owner = parts_[g.owner];
-                    for (auto& ex : owner.exports.at(p))
-                        if (ex.first == g.net_id) pins.emplace_back(g.net_id, owner.next.voltages[size_t(ex.second - 1)]);
-                }
+                pins.reserve(part.ghost_src.size());
+                for (size_t g = 0; g < part.ghost_src.size(); ++g)
+                    pins.emplace_back(part.ghosts.nodes[g].net_id, parts_[part.ghost_src[g].owner].next.voltages[size_t(part.ghost_src[g].local - 1)]);
                 PartitionState seed = part.next;
                 seed.cap_currents.clear();
-                if (part.engine->solve_step(seed, pins, 0.0, out)) {
+                if (part.engine->solve_dc(seed, out, pins)) {
                     for (size_t i = 0; i < out.voltages.size(); ++i) change = std::max(change, std::fabs(out.voltages[i] - part.next.voltages[i]));
                     part.next.voltages = out.voltages;
                 }
@@ -284,11 +292,9 @@ private:
             part.state.time = 0.0;
             // ghosts start from the neighbours' initial values
         }
-        for (uint32_t p = 0; p < k; ++p)
-            for (auto& ex : parts_[p].exports)
-                for (auto& e : ex.second)
-                    for (auto& g : parts_[ex.first].ghosts.nodes)
-                        if (g.net_id == e.first) g.apply_correction(parts_[p].state.voltages[size_t(e.second - 1)], 0.0, cfg_.reltol);
+        for (auto& part : parts_)
+            for (size_t g = 0; g < part.ghost_src.size(); ++g)
+                part.ghosts.nodes[g].apply_correction(parts_[part.ghost_src[g].owner].state.voltages[size_t(part.ghost_src[g].local - 1)], 0.0, cfg_.reltol);
     }
     void record(double t) {
         WaveformPoint pt{t, {}};

@@ -10,7 +10,7 @@
 //            the largest candidate, so the minimum-degree order keeps its meaning; strict partial
 //            pivoting is the second try when that is not stable enough); symbolic elimination
 //            of the permuted pattern, which fixes the positions of every fill-in
-//   refactor (every solve) scatter the row-equilibrated values into the fixed pattern and eliminate row by
+//   refactor (every solve with new values; identical values reuse the factors) scatter the row-equilibrated values into the fixed pattern and eliminate row by
 //            row without searching, allocating or pivoting
 //   solve    two triangular sweeps, then iterative refinement against the original matrix with the same
 //            factors while the componentwise backward error is above 1e-10
@@ -147,7 +147,7 @@ inline std::vector<std::pair<int, int>> singleton_pivots(int n, const std::vecto
     return out;
 }
 
-struct FactoredLuStats { uint64_t orderings = 0, analyses = 0, refactors = 0, repivots = 0, refinement_rounds = 0; size_t factor_nnz = 0, singletons = 0; };
+struct FactoredLuStats { uint64_t orderings = 0, analyses = 0, refactors = 0, reuses = 0, repivots = 0, refinement_rounds = 0; size_t factor_nnz = 0, singletons = 0; };
 
 class FactoredLU {
 public:
@@ -158,6 +158,11 @@ public:
                const std::vector<double>& rhs, std::vector<double>& x) {
         if (n == 0) { x.clear(); return true; }
         if (valid_ && n == n_ && row_ptr == a_ptr_ && col == a_col_) {
+            // a linear circuit at a fixed step presents the same values every time: the factors still stand
+            if (factored_ && val == last_val_) {
+                ++stats.reuses;
+                if (solve_refined(val, rhs, x)) return true;
+            }
             if (refactor(val) && solve_refined(val, rhs, x)) return true;
             ++stats.repivots;  // the row order chosen for earlier values no longer suits these
         }
@@ -173,7 +178,8 @@ public:
 
 private:
     int n_ = 0;
-    bool valid_ = false, order_ready_ = false;
+    bool valid_ = false, order_ready_ = false, factored_ = false;
+    std::vector<double> last_val_;
     std::vector<int> a_ptr_, a_col_;
     std::vector<int> q_, qinv_, p_, pinv_;       // position -> original column / row, and back
     std::vector<int> lu_ptr_, lu_col_, diag_;    // pattern of L + U in permuted indices, columns ascending
@@ -341,6 +347,7 @@ private:
     // ---- numeric ------------------------------------------------------------------------------------
     bool refactor(const std::vector<double>& val) {
         ++stats.refactors;
+        factored_ = false;
         const int n = n_;
         std::fill(lu_val_.begin(), lu_val_.end(), 0.0);
         for (int r = 0; r < n; ++r) {
@@ -364,6 +371,8 @@ private:
             const double pv = std::fabs(lu_val_[size_t(d)]);
             if (!(pv > 1e-300) || !std::isfinite(pv)) return false;
         }
+        last_val_ = val;
+        factored_ = true;
         return true;
     }
 

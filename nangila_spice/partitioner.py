@@ -308,31 +308,44 @@ def partition_flat(flat: dict, k: int, method: str = "auto", feedback_nets: Opti
     result = PartitionResult(method=method, feedback_groups_enforced=enforced)
     result.net_assignment = {names[v - 1]: p for v, p in owner.items()}
     ic = {int(node): float(val) for node, val in flat.get("initial_conditions", [])}
+    # one pass over the elements: which partitions take each (every partition that owns one of its current-carrying
+    # terminals), and which sources hold which replicated net
     cut_elements = 0
-    for el in elements:
+    chosen_by_part: list[list[int]] = [[] for _ in range(k_eff)]
+    terminals = [_terminals(el) for el in elements]
+    holders: dict[int, list[int]] = {}
+    for idx, el in enumerate(elements):
         ps = {owner[x] for x in _current_terminals(el) if x in owner}
         cut_elements += 1 if len(ps) > 1 else 0
+        for p in ps:
+            chosen_by_part[p].append(idx)
+        if "VoltageSource" in el:
+            b = el["VoltageSource"]
+            if b["neg"] == 0 and b["pos"] in held:
+                holders.setdefault(b["pos"], []).append(idx)
+            elif b["pos"] == 0 and b["neg"] in held:
+                holders.setdefault(b["neg"], []).append(idx)
+    own_by_part: list[list[int]] = [[] for _ in range(k_eff)]
+    for v in free:
+        own_by_part[owner[v]].append(v)
     for p in range(k_eff):
-        own = [v for v in free if owner[v] == p]
-        own_set = set(own)
-        chosen = []
-        for idx, el in enumerate(elements):
-            if any(x in own_set for x in _current_terminals(el)):
-                chosen.append(idx)
+        own = own_by_part[p]
+        chosen = chosen_by_part[p]
         touched: list[int] = []
         seen = set(own)
         for idx in chosen:
-            for x in _terminals(elements[idx]):
+            for x in terminals[idx]:
                 if x > 0 and x not in seen:
                     seen.add(x)
                     touched.append(x)
         local_held = [x for x in touched if x in held]
         ghosts = [x for x in touched if x not in held]
         # sources that hold a replicated net come along
-        for idx, el in enumerate(elements):
-            if _kind(el) == "VoltageSource" and idx not in chosen:
-                b = el["VoltageSource"]
-                if (b["neg"] == 0 and b["pos"] in local_held) or (b["pos"] == 0 and b["neg"] in local_held):
+        have = set(chosen)
+        for x in local_held:
+            for idx in holders.get(x, ()):
+                if idx not in have:
+                    have.add(idx)
                     chosen.append(idx)
         chosen.sort()
         order = own + local_held + ghosts
