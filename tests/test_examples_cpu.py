@@ -1,4 +1,5 @@
 """The example scripts run end to end on CPU (tiny models, gloo group of one)."""
+import json
 import os
 import subprocess
 import sys
@@ -42,3 +43,10 @@ def test_manual_reducer_example_on_cpu():
     assert "bytes held / bytes sent" in r.stdout
     first, last = (float(x) for x in (r.stdout.split("first loss ")[1].split()[0], r.stdout.split("last loss ")[1].split()[0]))
     assert last < first   # it learns through the packet path
+
+
+def test_hook_benchmark_example_reports_ratio_and_error():
+    r = _run("examples/benchmark.py", "--size", "50000", "--iterations", "8", "--warmup-steps", "2")
+    assert r.returncode == 0, r.stdout + r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["compression_ratio"] > 6.0 and out["relative_rms_error"] < 5e-3 and out["compress_melem_per_s"] > 0
