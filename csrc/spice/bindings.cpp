@@ -280,6 +280,34 @@ PYBIND11_MODULE(_native, m) {
         d["name"] = c.name; d["used_delta_mode"] = r.used_delta_mode; d["peak_delta_v"] = r.peak_delta_v; d["waveform"] = rec; d["bytes_roundtrip"] = rt;
         return d;
     });
+    // The golden run is handed over once; every corner after that is one call with three numbers.
+    py::class_<DeltaSolver>(m, "PvtDeltaSolver", "delta reconstruction of corner waveforms from one golden run")
+        .def(py::init([](const std::vector<double>& time, py::array_t<double, py::array::c_style | py::array::forcecast> golden) {
+            if (golden.ndim() != 2 || size_t(golden.shape(0)) != time.size()) throw std::invalid_argument("golden must be (len(time), nets)");
+            GoldenTrajectory g(CornerSpec(), time.size() > 1 ? time[1] - time[0] : 0.0);
+            const py::ssize_t cols = golden.shape(1);
+            const double* src = golden.data();
+            for (size_t k = 0; k < time.size(); ++k) g.push(time[k], std::vector<double>(src + py::ssize_t(k) * cols, src + (py::ssize_t(k) + 1) * cols));
+            return new DeltaSolver(std::move(g));
+        }), py::arg("time"), py::arg("golden"))
+        .def("solve", [](DeltaSolver& s, const std::string& process, double vdd, double temp, bool want_waveform) {
+            CornerSpec c(corner_from_name(process), vdd, temp);
+            DeltaSolveResult r = s.solve_corner(c);
+            py::dict d;
+            d["name"] = c.name; d["used_delta_mode"] = r.used_delta_mode; d["peak_delta_v"] = r.peak_delta_v;
+            if (want_waveform) {
+                std::vector<WaveformPoint> w;
+                for (auto& p : s.reconstruct(r)) w.push_back({p.time, std::move(p.voltages)});
+                d["waveform"] = waveform_array(w);
+            }
+            return d;
+        }, py::arg("process"), py::arg("vdd"), py::arg("temp"), py::arg("want_waveform") = true)
+        .def("stats", [](const DeltaSolver& s) {
+            py::dict d;
+            d["corners_solved"] = s.stats.corners_solved; d["delta_mode_used"] = s.stats.delta_mode_used; d["full_sim_fallback"] = s.stats.full_sim_fallback;
+            d["total_wall_time"] = s.stats.total_wall_time;
+            return d;
+        });
     m.def("pvt_cache_selftest", [](size_t cap, std::vector<std::string> inserts, std::vector<std::string> lookups) {
         PvtCache c(cap);
         for (auto& n : inserts) { GoldenTrajectory g; g.corner.name = n; c.insert(std::move(g)); }

@@ -91,17 +91,22 @@ C1 out 0 10f
 
 
 def simulate_corner(corner: CornerSpec, golden_waveform: Optional[dict] = None, use_delta: bool = True, netlist_path: Optional[str] = None,
-                    tstop: float = 200e-12, dt: float = 1e-12) -> dict:
+                    tstop: float = 200e-12, dt: float = 1e-12, want_waveform: bool = True) -> dict:
     """One corner: a delta reconstruction from ``golden_waveform`` when allowed and close enough,
-    else a full simulation of the deck (a built-in RC stage when no deck is given)."""
+    else a full simulation of the deck (a built-in RC stage when no deck is given). The golden run is handed to
+    the native delta solver once and kept in ``golden_waveform["_solver"]``."""
     from . import _native
 
     t0 = time.perf_counter()
     nominal = CornerSpec.nominal()
     if use_delta and golden_waveform is not None and corner.is_linearisable(nominal):
-        r = _native.pvt_delta(golden_waveform["time"], golden_waveform["values"], corner.process.value, corner.vdd, corner.temperature)
+        solver = golden_waveform.get("_solver")
+        if solver is None:
+            solver = _native.PvtDeltaSolver(list(golden_waveform["time"]), np.asarray(golden_waveform["values"], dtype=np.float64))
+            golden_waveform["_solver"] = solver
+        r = solver.solve(corner.process.value, corner.vdd, corner.temperature, want_waveform)
         return {"corner": corner.name, "used_delta": bool(r["used_delta_mode"]), "peak_delta_v": float(r["peak_delta_v"]),
-                "time": golden_waveform["time"], "values": r["waveform"], "node_names": golden_waveform["node_names"],
+                "time": golden_waveform["time"], "values": r.get("waveform"), "node_names": golden_waveform["node_names"],
                 "wall_time": time.perf_counter() - t0}
     text = Path(netlist_path).read_text() if netlist_path else _RC_DECK
     js, _ = _native.parse_spice(text, Path(netlist_path).name if netlist_path else "rc_stage", corner.process.value, corner.vdd, corner.temperature)
@@ -184,7 +189,7 @@ class PvtOrchestrator:
         rest = [c for c in corners if not c.is_nominal]
 
         def one(c: CornerSpec) -> dict:
-            return simulate_corner(c, self.golden_waveform, cfg.delta_mode, netlist_path, cfg.tstop, cfg.dt)
+            return simulate_corner(c, self.golden_waveform, cfg.delta_mode, netlist_path, cfg.tstop, cfg.dt, want_waveform=cfg.save_waveforms)
 
         with ThreadPoolExecutor(max_workers=max(1, cfg.max_workers)) as ex:
             futures = [ex.submit(one, c) for c in rest]
@@ -209,5 +214,5 @@ class PvtOrchestrator:
 
     def _strip(self, res: dict) -> dict:
         if self.config.save_waveforms:
-            return res
-        return {k: v for k, v in res.items() if k not in ("time", "values")}
+            return {k: v for k, v in res.items() if k != "_solver"}
+        return {k: v for k, v in res.items() if k not in ("time", "values", "_solver")}
