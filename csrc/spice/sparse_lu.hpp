@@ -400,9 +400,14 @@ private:
         apply(rhs, x);
         res_.resize(size_t(n));
         for (int round = 0; round < 4; ++round) {
+            // Componentwise backward error |b - A x|_i / (|b| + |A||x|)_i. A row whose terms have all decayed far below
+            // what the largest unknown would contribute to it (the far end of a long RC line holds 1e-300 V) is measured
+            // against that contribution instead: down there the quotient compares rounding noise with underflow.
+            double xmax = 0.0;
+            for (int i = 0; i < n; ++i) xmax = std::max(xmax, std::fabs(x[size_t(i)]));
             double worst = 0.0;
             for (int r = 0; r < n; ++r) {
-                double ax = 0.0, mag = std::fabs(rhs[size_t(r)]);
+                double ax = 0.0, mag = std::fabs(rhs[size_t(r)]) + 1e-16 * xmax / scale_[size_t(r)];
                 for (int k = a_ptr_[size_t(r)]; k < a_ptr_[size_t(r) + 1]; ++k) {
                     const double t = val[size_t(k)] * x[size_t(a_col_[size_t(k)])];
                     ax += t;

@@ -405,3 +405,17 @@ def test_large_logic_deck_runs_on_the_refactoring_path():
     nr = r["newton"]
     assert r["stats"]["completed"] and nr["lu_fallbacks"] == 0 and nr["lu_singletons"] > 40
     assert nr["lu_analyses"] < nr["lu_refactors"] / 5
+
+
+def test_long_line_with_underflowing_far_end_stays_on_the_direct_path():
+    # 400 RC stages, 100 ps: the far nodes hold voltages that underflow. The backward-error test of the LU must not take
+    # that for a bad solve (it once did: the run fell back to cut Backward-Euler steps and was 3.7 mV off).
+    from nangila_spice.benchmark import generate_rc_ladder_netlist
+
+    js, _ = N.parse_spice(generate_rc_ladder_netlist(400, 1e3, 10e-15))
+    lu = N.simulate(js, 100e-12, 1e-12, 1e-3, "lu")
+    dense = N.simulate(js, 100e-12, 1e-12, 1e-3, "dense")
+    nr = lu["newton"]
+    assert np.abs(np.asarray(lu["values"]) - np.asarray(dense["values"])).max() < 1e-12
+    assert nr["step_cuts"] == 0 and nr["be_fallbacks"] == 0 and nr["lu_fallbacks"] == 0 and nr["lu_repivots"] == 0
+    assert nr["lu_analyses"] <= 3 and nr["lu_refactors"] <= 4 and nr["lu_reuses"] >= 90   # DC, first (BE) step, trapezoidal steps
