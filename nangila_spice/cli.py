@@ -7,6 +7,11 @@ import os
 import sys
 
 
+def get_project_root() -> str:
+    """The directory that holds ``nangila_spice`` and the native sources (``csrc/spice``)."""
+    return os.path.abspath(os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+
+
 def invoke_build(args) -> int:
     from nangila import _build
 

@@ -33,6 +33,26 @@ class NzWaveform:
         return self.header.node_names
 
     @property
+    def num_points(self) -> int:
+        return int(len(self.time))
+
+    def voltage(self, node: str, time: "float | None" = None) -> float:
+        """Voltage of ``node`` at the sample nearest to ``time`` (the last sample when no time is given)."""
+        if node not in self.signals:
+            raise KeyError(f"no net '{node}' in the file; it holds {', '.join(self.node_names[:8])}{' ...' if len(self.node_names) > 8 else ''}")
+        values = self.signals[node]
+        if len(values) == 0:
+            return 0.0
+        if time is None:
+            return float(values[-1])
+        i = int(np.searchsorted(self.time, time))
+        if i <= 0:
+            return float(values[0])
+        if i >= len(self.time):
+            return float(values[-1])
+        return float(values[i] if abs(self.time[i] - time) < abs(time - self.time[i - 1]) else values[i - 1])
+
+    @property
     def compression_ratio(self) -> float:
         raw = 8 * self.header.num_points * (self.header.num_nodes + 1)
         return raw / self.file_bytes if self.file_bytes else 1.0

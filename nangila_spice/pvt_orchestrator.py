@@ -34,6 +34,10 @@ class ProcessCorner(Enum):
     def mobility_factor(self) -> float:
         return {"TT": 1.0, "FF": 1.15, "SS": 0.85, "FS": 1.1, "SF": 0.9}[self.value]
 
+    @property
+    def is_nominal(self) -> bool:
+        return self is ProcessCorner.TT
+
 
 @dataclass
 class CornerSpec:

@@ -280,3 +280,26 @@ def test_scaling_study_report_and_cli(tmp_path):
     assert dot.startswith("graph partitions {") and "style=dashed" in dot
     hw = ns.discover_hardware()
     assert hw.cpu_count >= 1 and "cores" in hw.summary()
+
+
+def test_small_api_members_of_the_reference_front_end(tmp_path):
+    from nangila_spice import cli
+    from nangila_spice.nz_reader import read_nz
+    from nangila_spice.pvt_orchestrator import ProcessCorner
+
+    assert os.path.isdir(os.path.join(cli.get_project_root(), "csrc", "spice"))
+    assert ProcessCorner.TT.is_nominal and not ProcessCorner.SS.is_nominal
+    deck = _write(tmp_path, "rc.sp", "* rc\nV1 in 0 DC 1.0\nR1 in out 1k\nC1 out 0 10f\n.ic V(out)=0\n.end\n")
+    out = tmp_path / "w.nz"
+    from nangila_spice.correctness import find_nangila_binary
+
+    run = subprocess.run([find_nangila_binary(), "--partition", deck, "--tstop", "1e-10", "--dt", "1e-12", "--waveform-nz", str(out)],
+                         capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr
+    w = read_nz(str(out))
+    assert w.num_points == 101 and abs(w.voltage("in") - 1.0) < 1e-5
+    tau = 10e-12
+    assert abs(w.voltage("out", 20e-12) - (1 - math.exp(-20e-12 / tau))) < 5e-3
+    assert w.voltage("out", -1.0) == w.signals["out"][0] and w.voltage("out", 1.0) == w.signals["out"][-1]
+    with pytest.raises(KeyError):
+        w.voltage("nope")
