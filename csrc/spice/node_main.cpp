@@ -4,6 +4,10 @@
 //                [--reltol R] [--tstop T] [--dt DT] [--process TT|FF|SS|FS|SF] [--vdd V] [--temp C]
 //                [--waveform-json out.json] [--waveform-nz out.nz] [--solver lu|dense|krylov|cuda]
 //                [--record-every K] [--demo]
+//                [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T]]
+//
+// With --rendezvous and -k > 1 the process is one of TOTAL that advance in lockstep and exchange boundary voltages
+// over TCP (distributed.hpp); its waveform file then holds the nets this partition owns.
 //
 // Flag set and the waveform JSON layout ({netlist, node_names, waveform: [{time, voltages{}}],
 // stats{}}) follow the reference's CLI (nangila-spice/nangila-node/src/main.rs:21-132).
@@ -16,6 +20,7 @@
 #include <iostream>
 
 #include "balancer.hpp"
+#include "distributed.hpp"
 #include "nz.hpp"
 #include "parser.hpp"
 #include "partitioned.hpp"
@@ -24,7 +29,8 @@
 using namespace nspice;
 
 struct Args {
-    std::string partition, partitions, process = "TT", waveform_json, waveform_nz, solver = "lu";
+    std::string partition, partitions, process = "TT", waveform_json, waveform_nz, solver = "lu", rendezvous, bind_host = "127.0.0.1";
+    int connect_timeout_ms = 30000, io_timeout_ms = 30000;
     uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1, threads = 1;
     double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
     bool demo = false, bench = false;
@@ -35,7 +41,8 @@ static void usage() {
                  "usage: nangila-node [--partition FILE | --demo] [--node-id N] [-k TOTAL] [--predict-depth D]\n"
                  "                    [--reltol R] [--tstop T] [--dt DT] [--process P] [--vdd V] [--temp C]\n"
                  "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov|cuda]\n"
-                 "                    [--record-every K] [--partitions A.json,B.json,... [--threads T]] [--bench]\n");
+                 "                    [--record-every K] [--partitions A.json,B.json,... [--threads T]] [--bench]\n"
+                 "                    [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T]]\n");
 }
 
 static bool parse_args(int argc, char** argv, Args& a) {
@@ -65,6 +72,10 @@ static bool parse_args(int argc, char** argv, Args& a) {
         else if (f == "--process") { if (!(v = need("--process"))) return false; a.process = v; }
         else if (f == "--solver") { if (!(v = need("--solver"))) return false; a.solver = v; }
         else if (f == "--waveform-json") { if (!(v = need("--waveform-json"))) return false; a.waveform_json = v; }
+        else if (f == "--rendezvous") { if (!(v = need("--rendezvous"))) return false; a.rendezvous = v; }
+        else if (f == "--bind") { if (!(v = need("--bind"))) return false; a.bind_host = v; }
+        else if (f == "--connect-timeout-ms") { if (!(v = need("--connect-timeout-ms"))) return false; a.connect_timeout_ms = std::atoi(v); }
+        else if (f == "--io-timeout-ms") { if (!(v = need("--io-timeout-ms"))) return false; a.io_timeout_ms = std::atoi(v); }
         else if (f == "--waveform-nz") { if (!(v = need("--waveform-nz"))) return false; a.waveform_nz = v; }
         else { std::fprintf(stderr, "unknown flag %s\n", f.c_str()); return false; }
     }
@@ -152,6 +163,38 @@ static int run_partitioned(const Args& a) {
     }
 }
 
+// One of several processes of a partitioned run: --partition part.json --node-id N -k TOTAL --rendezvous DIR
+static int run_distributed(const Args& a) {
+    try {
+        Netlist nl = load_any(a.partition, a);
+        std::string name = nl.name;
+        SocketMesh mesh(a.node_id, a.total, a.rendezvous, a.bind_host);
+        if (!mesh.connect_all(a.connect_timeout_ms)) { std::fprintf(stderr, "ERROR: process %u: %s\n", a.node_id, mesh.error.c_str()); return 4; }
+        DistributedConfig cfg;
+        cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
+        cfg.io_timeout_ms = a.io_timeout_ms;
+        DistributedRunner runner(std::move(nl), mesh, cfg);
+        runner.engine().newton.config.reltol = a.reltol;
+        if (a.solver == "dense") runner.engine().newton.linear.backend = LinearBackend::Dense;
+        else if (a.solver == "krylov") runner.engine().newton.linear.backend = LinearBackend::Krylov;
+        const bool ok = runner.run();
+        const DistributedStats& st = runner.stats;
+        std::fprintf(stderr, "process %u of %u: %llu steps%s, %.3f s, %llu DC sweeps, hits %llu, misses %llu, extra solves %llu, %llu messages (%llu bytes)%s%s\n",
+                     a.node_id, a.total, (unsigned long long)st.steps, ok ? "" : " (stopped early)", st.wall_time_secs, (unsigned long long)st.dc_sweeps,
+                     (unsigned long long)st.prediction_hits, (unsigned long long)st.prediction_misses, (unsigned long long)st.resolves,
+                     (unsigned long long)mesh.stats.messages_sent, (unsigned long long)mesh.stats.bytes_sent, st.error.empty() ? "" : ": ", st.error.c_str());
+        SimStats ss;
+        ss.total_steps = st.steps; ss.wall_time_secs = st.wall_time_secs; ss.prediction_hits = st.prediction_hits;
+        ss.prediction_misses = st.prediction_misses; ss.rollbacks = st.resolves; ss.completed = ok;
+        if (!a.waveform_json.empty()) write_json(a.waveform_json, name, runner.names, runner.waveform, ss);
+        // 3: this partition's solve failed; 5: the run stopped because of a peer or the network
+        return ok ? 0 : (st.error.find("Newton") != std::string::npos ? 3 : 5);
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ERROR: process %u: %s\n", a.node_id, e.what());
+        return 1;
+    }
+}
+
 int main(int argc, char** argv) {
     Args a;
     if (!parse_args(argc, argv, a)) { usage(); return 2; }
@@ -160,6 +203,10 @@ int main(int argc, char** argv) {
         return 0;
     }
     if (!a.partitions.empty()) return run_partitioned(a);
+    if (!a.rendezvous.empty() && a.total > 1) {
+        if (a.partition.empty()) { std::fprintf(stderr, "--rendezvous needs --partition FILE\n"); return 2; }
+        return run_distributed(a);
+    }
     Netlist nl;
     try {
         if (a.demo) nl = demo_netlist();

@@ -60,7 +60,8 @@ class SimulationConfig:
     reference_vdd: float = 1.8
     prefer_single_node_fallback_for_partitioned: bool = False
     verbose: bool = False
-    mode: str = "auto"  # 'auto' | 'in_process' | 'processes'
+    mode: str = "auto"  # 'auto' | 'in_process' | 'processes' (one nangila-node per partition, boundary values over TCP)
+    io_timeout_secs: float = 30.0  # processes mode: how long a process waits for a peer before it gives up
     process: str = "TT"
     vdd: float = 1.8
     temp: float = 27.0
@@ -155,29 +156,48 @@ def _single_run(config: SimulationConfig, flat: dict) -> tuple[Waveform, dict]:
     return Waveform.from_native(r, title=flat.get("name", "")), {"stats": r["stats"], "newton": r["newton"]}
 
 
-def _run_processes(config: SimulationConfig, pr: PartitionResult, workdir: str) -> tuple[Waveform, list[float]]:
+def _run_processes(config: SimulationConfig, pr: PartitionResult, workdir: str) -> tuple[Waveform, list[float], dict]:
+    """One ``nangila-node`` process per partition. The processes find each other through a rendezvous directory,
+    advance in lockstep and exchange boundary voltages over TCP every sweep; each writes the nets it owns."""
     exe = find_nangila_binary()
     if exe is None:
         raise FileNotFoundError("nangila-node is not built: run `python -m nangila._build --spice`")
-
-    def one(part) -> tuple[PartitionWaveform, float]:
+    k = len(pr.partitions)
+    rendezvous = os.path.join(workdir, "rendezvous")
+    os.makedirs(rendezvous, exist_ok=True)
+    for name in os.listdir(rendezvous):  # addresses of an earlier run in the same directory would mislead the new processes
+        if name.endswith(".addr"):
+            os.unlink(os.path.join(rendezvous, name))
+    procs, outs = [], []
+    t0 = time.perf_counter()
+    for part in pr.partitions:
         pfile = os.path.join(workdir, f"partition_{part.partition_id}.json")
         out = os.path.join(workdir, f"waveform_{part.partition_id}.json")
         Path(pfile).write_text(json.dumps(part.netlist))
-        t0 = time.perf_counter()
-        proc = subprocess.run([exe, "--partition", pfile, "--node-id", str(part.partition_id), "-k", str(len(pr.partitions)),
-                               "--tstop", repr(config.tstop), "--dt", repr(config.dt), "--reltol", repr(config.reltol),
-                               "--predict-depth", str(config.predict_depth), "--record-every", str(config.record_every),
-                               "--waveform-json", out], capture_output=True, text=True)
-        dt = time.perf_counter() - t0
-        if proc.returncode not in (0, 3) or not os.path.exists(out):
-            raise RuntimeError(f"partition {part.partition_id}: nangila-node exit {proc.returncode}: {proc.stderr[-300:]}")
+        outs.append(out)
+        cmd = [exe, "--partition", pfile, "--node-id", str(part.partition_id), "-k", str(k), "--tstop", repr(config.tstop), "--dt", repr(config.dt),
+               "--reltol", repr(config.reltol), "--predict-depth", str(config.predict_depth), "--record-every", str(config.record_every),
+               "--waveform-json", out, "--io-timeout-ms", str(int(config.io_timeout_secs * 1000)),
+               "--connect-timeout-ms", str(int(config.io_timeout_secs * 1000))]
+        if k > 1:
+            cmd += ["--rendezvous", rendezvous]
+        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    logs, times = [], []
+    for proc in procs:
+        _, err = proc.communicate()
+        logs.append(err)
+        times.append(time.perf_counter() - t0)
+    bad = [(i, p.returncode) for i, p in enumerate(procs) if p.returncode != 0]
+    if bad:
+        i, rc = bad[0]
+        tail = logs[i].strip().splitlines()[-1] if logs[i].strip() else ""
+        raise RuntimeError(f"partition {i}: nangila-node exit {rc}: {tail[-300:]}")
+    waves = []
+    for part, out in zip(pr.partitions, outs):
         w = Waveform.from_json_file(out)
-        return PartitionWaveform(part.partition_id, w.times.tolist(), {n: v.tolist() for n, v in w.traces.items()}, set(part.boundary_nodes)), dt
-
-    with ThreadPoolExecutor(max_workers=min(len(pr.partitions), os.cpu_count() or 1)) as ex:
-        results = list(ex.map(one, pr.partitions))
-    return merge_waveforms([r[0] for r in results], title=Path(config.netlist_path).name), [r[1] for r in results]
+        waves.append(PartitionWaveform(part.partition_id, w.times.tolist(), {n: v.tolist() for n, v in w.traces.items()}, set()))
+    stats = {"completed": True, "processes": k, "log_tail": [lg.strip().splitlines()[-1] if lg.strip() else "" for lg in logs]}
+    return merge_waveforms(waves, title=Path(config.netlist_path).name), times, stats
 
 
 def run_simulation(config: SimulationConfig) -> SimulationResult:
@@ -216,9 +236,9 @@ def run_simulation(config: SimulationConfig) -> SimulationResult:
                     result.warnings.append(f"{r['stats']['unconverged_steps']} steps hit the relaxation sweep limit")
             elif mode == "processes":
                 with tempfile.TemporaryDirectory() as tmp:
-                    result.waveform, result.per_partition_times = _run_processes(config, pr, config.output_dir or tmp)
-                result.experimental = True
-                result.warnings.append("process-per-partition run: partitions did not exchange boundary values")
+                    result.waveform, result.per_partition_times, pstats = _run_processes(config, pr, config.output_dir or tmp)
+                result.solver_stats = {"stats": pstats}
+                result.success = True
             else:
                 raise ValueError(f"unknown mode '{config.mode}'")
             result.validation_status = "partitioned_unvalidated"

@@ -3,6 +3,7 @@ partitioner, in-process and process-per-partition runs, merging, correctness con
 .nz reader, gate-level synthesis, report and command line. Plan modelled on the reference's
 ``nangila-spice/src/tests`` suites (partitioner, integration, correctness, PVT orchestrator)."""
 import json
+import time
 import math
 import os
 import subprocess
@@ -133,9 +134,9 @@ def test_single_partition_exports_and_processes_mode(tmp_path):
     assert rows[0].split(",")[0] == "time" and len(rows) == 202
     ns.export_json(res.waveform, str(out / "w.json"))
     assert json.loads((out / "w.json").read_text())["num_points"] == 201
-    # process-per-partition launch of the solver binary: bit lines are only coupled through the held word lines
+    # one solver process per partition
     res2 = ns.simulate(path, partitions=2, tstop=1e-9, dt=5e-12, mode="processes", method="bisect")
-    assert res2.success and res2.experimental, res2.summary()
+    assert res2.success and res2.validation_status == "partitioned_validated", res2.summary()
     assert res2.reference_comparison is not None and res2.reference_comparison.max_abs_error < 1e-6
 
 
@@ -303,3 +304,61 @@ def test_small_api_members_of_the_reference_front_end(tmp_path):
     assert w.voltage("out", -1.0) == w.signals["out"][0] and w.voltage("out", 1.0) == w.signals["out"][-1]
     with pytest.raises(KeyError):
         w.voltage("nope")
+
+
+def _partition_files(tmp_path, text, k, method="spectral"):
+    nl = ns.parse_netlist(_write(tmp_path, "deck.sp", text))
+    pr = ns.partition_netlist(nl, k, method)
+    files = []
+    for i, js in enumerate(pr.partition_files()):
+        path = tmp_path / f"p{i}.json"
+        path.write_text(js)
+        files.append(str(path))
+    return files
+
+
+def test_partitions_as_processes_exchange_boundaries_over_tcp(tmp_path):
+    deck = _write(tmp_path, "ladder.sp", generate_rc_ladder_netlist(45, 1e3, 10e-15))
+    res = ns.simulate(deck, partitions=3, tstop=150e-12, dt=1e-12, mode="processes", method="bisect", output_dir=str(tmp_path / "run"))
+    assert res.success and res.validation_status == "partitioned_validated", (res.error, res.warnings)
+    assert res.reference_comparison.max_abs_error < 1e-6
+    assert res.solver_stats["stats"]["processes"] == 3 and "messages" in res.solver_stats["stats"]["log_tail"][0]
+    # transistor-level logic across four processes
+    from nangila_spice import correctness as cx
+
+    case = next(c for c in cx.official_correctness_cases() if c.name == "adder2")
+    path = case.materialize(str(tmp_path))
+    res = ns.simulate(path, partitions=4, tstop=0.6e-9, dt=1e-12, mode="processes", output_dir=str(tmp_path / "run2"))
+    assert res.success and res.validation_status == "partitioned_validated", (res.error, res.warnings)
+    assert res.reference_comparison.max_abs_error < 5e-3
+
+
+def test_process_mesh_notices_absent_and_dead_peers(tmp_path):
+    from nangila_spice.correctness import find_nangila_binary
+
+    exe = find_nangila_binary()
+    files = _partition_files(tmp_path, generate_rc_ladder_netlist(60, 1e3, 10e-15), 3, "bisect")
+    common = ["-k", "3", "--dt", "1e-12"]
+    # a peer that never starts: the others give up at the connection deadline
+    rv = tmp_path / "rv_absent"
+    procs = [subprocess.Popen([exe, "--partition", files[i], "--node-id", str(i), *common, "--tstop", "1e-10", "--rendezvous", str(rv),
+                               "--connect-timeout-ms", "700"], stderr=subprocess.PIPE, text=True) for i in (0, 2)]
+    errs = [p.communicate(timeout=30)[1] for p in procs]
+    assert [p.returncode for p in procs] == [4, 4], errs
+    assert "process 1" in errs[1] or "never connected" in errs[0]
+    # a peer that dies in the middle of a long run: the others stop with an error that names it, well inside their I/O deadline
+    rv = tmp_path / "rv_dead"
+    procs = [subprocess.Popen([exe, "--partition", files[i], "--node-id", str(i), *common, "--tstop", "1e-6", "--rendezvous", str(rv),
+                               "--io-timeout-ms", "5000", "--waveform-json", str(tmp_path / f"dead{i}.json")], stderr=subprocess.PIPE, text=True)
+             for i in range(3)]
+    time.sleep(1.0)
+    assert all(p.poll() is None for p in procs), "the run ended before the fault was injected"
+    procs[1].kill()
+    t0 = time.time()
+    errs = [p.communicate(timeout=30)[1] for p in procs]
+    assert time.time() - t0 < 8.0
+    assert procs[0].returncode == 5 and procs[2].returncode == 5, errs
+    assert any("process 1" in e for e in (errs[0], errs[2])) and all("stopped early" in e for e in (errs[0], errs[2]))
+    # what the survivors had computed up to then is on disk
+    partial = json.loads((tmp_path / "dead0.json").read_text())
+    assert partial["stats"]["completed"] is False and len(partial["waveform"]) > 10
