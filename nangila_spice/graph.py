@@ -60,11 +60,11 @@ def detect_feedback_loops(netlist: Netlist) -> list[set[str]]:
                 flow.add_edge(gate, out)
                 drivers.setdefault(out, []).append(d.name)
     groups: list[set[str]] = []
+    gate_of = {d.name: d.nodes[1].lower() for d in netlist.devices if d.dev_type == "M" and len(d.nodes) >= 3}
     for comp in nx.strongly_connected_components(flow):
         if len(comp) < 2:
             continue
-        devs = {name for net in comp for name in drivers.get(net, [])
-                if any(dd.name == name and dd.nodes[1].lower() in comp for dd in netlist.devices)}
+        devs = {name for net in comp for name in drivers.get(net, []) if gate_of.get(name) in comp}
         if len(devs) >= 2:
             groups.append(devs)
     return _merge_overlapping_groups(groups)

@@ -32,10 +32,11 @@ class PartitionWaveform:
 class Waveform:
     def __init__(self, times: Iterable[float] = (), traces: Optional[dict[str, Iterable[float]]] = None, title: str = ""):
         self.title = title
-        self.times = np.asarray(list(times), dtype=np.float64)
+        as_array = lambda x: np.ascontiguousarray(x if isinstance(x, np.ndarray) else list(x), dtype=np.float64)  # noqa: E731
+        self.times = as_array(times)
         self.traces: dict[str, np.ndarray] = {}
         for name, values in (traces or {}).items():
-            arr = np.asarray(list(values), dtype=np.float64)
+            arr = as_array(values)
             if arr.size != self.times.size:
                 raise ValueError(f"trace '{name}' has {arr.size} samples for {self.times.size} time points")
             self.traces[name] = arr
@@ -90,11 +91,12 @@ class Waveform:
         names = result["node_names"]
         if values.ndim != 2:
             values = values.reshape(len(result["time"]), -1)
+        by_net = np.ascontiguousarray(values.T)  # one transpose: each trace is then a contiguous row
         traces = {}
         for j, name in enumerate(names):
-            if name not in traces and j < values.shape[1]:
-                traces[name] = values[:, j]
-        return cls(result["time"], traces, title)
+            if name not in traces and j < by_net.shape[0]:
+                traces[name] = by_net[j]
+        return cls(np.asarray(result["time"], dtype=np.float64), traces, title)
 
     @classmethod
     def from_json_file(cls, path: str) -> "Waveform":

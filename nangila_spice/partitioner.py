@@ -21,7 +21,7 @@ from typing import Optional
 
 import numpy as np
 
-from .graph import build_circuit_graph
+from .graph import detect_feedback_loops
 from .parser import Netlist
 
 
@@ -377,10 +377,9 @@ def partition_netlist(netlist: Netlist, k: int, method: str = "auto", imbalance_
     if k <= 0:
         raise ValueError(f"k must be positive, got {k}")
     flat_text = netlist.flatten()
-    cg = build_circuit_graph(flat_text)
     dev_by_name = {d.name: d for d in flat_text.devices}
     groups = []
-    for g in cg.feedback_groups:
+    for g in detect_feedback_loops(flat_text):  # the loops only: the star-expansion graph is not needed to partition
         nets: set[str] = set()
         for name in g:
             d = dev_by_name.get(name)
