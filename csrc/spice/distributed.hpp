@@ -232,6 +232,8 @@ private:
                 ++sweeps;
             }
             if (!all.ok) ++stats.unconverged_steps;
+            if (sweeps > 0)  // the predictors learn from what the relaxation settled on, not from the first speculative values
+                for (size_t g = 0; g < ghosts_.nodes.size(); ++g) ghosts_.nodes[g].amend(latest_[g].second);
             state_ = next_;
             stats.steps = step + 1;
             if ((step + 1) % cfg_.record_every == 0 || step + 1 == planned) record(t_next);

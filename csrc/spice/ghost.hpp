@@ -16,8 +16,10 @@ namespace nspice {
 struct SignalState {
     double value = 0, gradient = 0, second_derivative = 0, time = 0;
     std::vector<std::pair<double, double>> history;  // (time, voltage), newest last, at most 16
+    double gradient_before = 0;  // slope before the newest sample was recorded (amend() needs it)
     void record(double t, double v) {
         double old = gradient;
+        gradient_before = old;
         if (t > time) {
             double dt = t - time;
             gradient = (v - value) / dt;
@@ -29,6 +31,22 @@ struct SignalState {
         if (history.size() > 16) history.erase(history.begin());
     }
 };
+
+// Replaces the value of the newest sample (the first value received for a time point was a speculative one and the
+// relaxation has since settled on another): slopes are taken again from the sample before it.
+inline void amend_newest(SignalState& s, double v) {
+    if (s.history.empty()) { s.value = v; return; }
+    s.history.back().second = v;
+    s.value = v;
+    if (s.history.size() >= 2) {
+        const auto& prev = s.history[s.history.size() - 2];
+        const double dt = s.time - prev.first;
+        if (dt > 0.0) {
+            s.gradient = (v - prev.second) / dt;
+            s.second_derivative = (s.gradient - s.gradient_before) / dt;
+        }
+    }
+}
 
 inline double predict_linear(const SignalState& s, double t) { return s.value + s.gradient * (t - s.time); }
 
@@ -143,12 +161,18 @@ struct NodeAccuracy {
 struct AccuracyLogger {
     std::vector<NodeAccuracy> nodes;
     NodeAccuracy& get(uint64_t id, const std::string& predictor) {
-        for (auto& n : nodes) if (n.net_id == id) { n.predictor = predictor; return n; }
+        auto it = index_.find(id);
+        if (it != index_.end() && it->second < nodes.size() && nodes[it->second].net_id == id) {
+            nodes[it->second].predictor = predictor;
+            return nodes[it->second];
+        }
+        index_[id] = nodes.size();
         nodes.emplace_back();
         nodes.back().net_id = id;
         nodes.back().predictor = predictor;
         return nodes.back();
     }
+    std::unordered_map<uint64_t, size_t> index_;
     void record(uint64_t id, const std::string& predictor, double predicted, double actual, double reltol) {
         get(id, predictor).record(predicted, actual, reltol);
     }
@@ -171,14 +195,17 @@ struct AdaptiveConfidence {
     std::vector<std::pair<uint64_t, double>> conf;
     explicit AdaptiveConfidence(uint32_t base = 5) : base_depth(base), max_depth(base * 3) {}
     void update(uint64_t id, bool accurate) {
-        for (auto& c : conf)
-            if (c.first == id) {
-                c.second = accurate ? c.second * 0.9 + 0.1 : c.second * 0.7;
-                c.second = std::min(1.0, std::max(0.0, c.second));
-                return;
-            }
+        auto it = index_.find(id);
+        if (it != index_.end() && it->second < conf.size() && conf[it->second].first == id) {
+            auto& c = conf[it->second];
+            c.second = accurate ? c.second * 0.9 + 0.1 : c.second * 0.7;
+            c.second = std::min(1.0, std::max(0.0, c.second));
+            return;
+        }
+        index_[id] = conf.size();
         conf.emplace_back(id, accurate ? 0.5 : 0.1);
     }
+    std::unordered_map<uint64_t, size_t> index_;
     uint32_t effective_depth() const {
         if (conf.empty()) return base_depth;
         double mn = 1.0;
@@ -217,6 +244,16 @@ struct GhostNode {
         double rel = std::fabs(v) > 1e-15 ? err / std::fabs(v) : err;
         confidence = std::min(1.0, std::max(0.0, 1.0 - rel));
         return rel < reltol;
+    }
+    // The value recorded for the newest time point is replaced by `v`; no prediction is scored.
+    void amend(double v) {
+        if (signal.history.size() >= 2) {
+            const auto& prev = signal.history[signal.history.size() - 2];
+            const double dt = last_update_time - prev.first;
+            if (dt > 0.0) gradient = (v - prev.second) / dt;
+        }
+        last_known_voltage = v;
+        amend_newest(signal, v);
     }
 };
 

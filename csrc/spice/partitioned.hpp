@@ -182,6 +182,9 @@ public:
             }
             if (failed) break;
             if (!all_ok) ++stats.unconverged_steps;
+            if (sweeps > 0)  // the predictors learn from what the relaxation settled on, not from the first speculative values
+                for (auto& part : parts_)
+                    for (size_t g = 0; g < part.ghosts.nodes.size() && g < part.latest.size(); ++g) part.ghosts.nodes[g].amend(part.latest[g].second);
             for (auto& part : parts_) part.state = part.next;
             if ((step + 1) % cfg_.record_every == 0 || step + 1 == planned) record(t_next);
         }
