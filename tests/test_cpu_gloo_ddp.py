@@ -117,3 +117,16 @@ def test_checkpoint_resume_continues_the_run(tmp_path):
     assert resumed["losses"][-1] == pytest.approx(full["losses"][-1], abs=1e-3)
     # 15 compressed steps were resumed: the byte counters keep counting from the saved values
     assert resumed["stats"]["total_original_bytes"] == full["stats"]["total_original_bytes"]
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("kwargs", [dict(warmup_steps=10), dict(warmup_steps=10, compressor_type=1, dgc_sparsity=0.99),
+                                    dict(warmup_steps=10, compressor_type=2, power_sgd_rank=2)], ids=["predres", "dgc", "powersgd"])
+def test_three_ranks_stay_identical_and_learn(tmp_path, kwargs):
+    """An odd world size: the packet path gathers from two peers, and the mean divides by three."""
+    out = str(tmp_path / "w3.pt")
+    mp.spawn(run, args=(3, _port(), 60, True, out, kwargs, 0, True), nprocs=3, join=True)
+    res = torch.load(out, weights_only=False)
+    params = [torch.load(out + f".rank{i}") for i in range(3)]
+    assert torch.equal(params[0], params[1]) and torch.equal(params[0], params[2])
+    assert res["losses"][-1] < res["losses"][0] - 0.3 and res["stats"]["overall_compression_ratio"] > 2.0
