@@ -7,7 +7,8 @@
 //                [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T]]
 //
 // With --rendezvous and -k > 1 the process is one of TOTAL that advance in lockstep and exchange boundary voltages
-// over TCP (distributed.hpp); its waveform file then holds the nets this partition owns.
+// over TCP (distributed.hpp); its waveform file then holds the nets this partition owns. DIR must be empty of earlier
+// runs' address files; the processes must run on machines of one byte order.
 //
 // Flag set and the waveform JSON layout ({netlist, node_names, waveform: [{time, voltages{}}],
 // stats{}}) follow the reference's CLI (nangila-spice/nangila-node/src/main.rs:21-132).
@@ -118,6 +119,17 @@ static void write_json(const std::string& path, const std::string& name, const s
       << st.prediction_misses << ", \"rollbacks\": " << st.rollbacks << ", \"completed\": " << (st.completed ? "true" : "false") << "}\n}\n";
 }
 
+static void write_nz(const std::string& path, const std::vector<std::string>& names, const std::vector<WaveformPoint>& wf, double tol) {
+    std::vector<double> t;
+    std::vector<std::vector<double>> sig(names.size());
+    for (auto& p : wf) {
+        t.push_back(p.time);
+        for (size_t i = 0; i < names.size(); ++i) sig[i].push_back(i < p.values.size() ? p.values[i] : 0.0);
+    }
+    NzWriter w(tol);
+    w.write_file(path, names, t, sig);
+}
+
 static Netlist load_any(const std::string& path, const Args& a) {
     std::ifstream f(path);
     if (!f) throw std::runtime_error("cannot open '" + path + "'");
@@ -156,6 +168,7 @@ static int run_partitioned(const Args& a) {
         ss.total_steps = st.steps; ss.wall_time_secs = st.wall_time_secs; ss.prediction_hits = st.prediction_hits;
         ss.prediction_misses = st.prediction_misses; ss.rollbacks = st.resolves; ss.completed = st.completed;
         if (!a.waveform_json.empty()) write_json(a.waveform_json, "partitioned", runner.names, runner.waveform, ss);
+        if (!a.waveform_nz.empty()) write_nz(a.waveform_nz, runner.names, runner.waveform, a.nz_tol);
         return st.completed ? 0 : 3;
     } catch (const std::exception& e) {
         std::fprintf(stderr, "ERROR: %s\n", e.what());
@@ -187,6 +200,7 @@ static int run_distributed(const Args& a) {
         ss.total_steps = st.steps; ss.wall_time_secs = st.wall_time_secs; ss.prediction_hits = st.prediction_hits;
         ss.prediction_misses = st.prediction_misses; ss.rollbacks = st.resolves; ss.completed = ok;
         if (!a.waveform_json.empty()) write_json(a.waveform_json, name, runner.names, runner.waveform, ss);
+        if (!a.waveform_nz.empty()) write_nz(a.waveform_nz, runner.names, runner.waveform, a.nz_tol);
         // 3: this partition's solve failed; 5: the run stopped because of a peer or the network
         return ok ? 0 : (st.error.find("Newton") != std::string::npos ? 3 : 5);
     } catch (const std::exception& e) {
@@ -272,16 +286,7 @@ int main(int argc, char** argv) {
     for (size_t i = 0; i < names.size() && i < fin.voltages.size() && i < 16; ++i) std::fprintf(stderr, "  V(%s) = %.6f\n", names[i].c_str(), fin.voltages[i]);
     try {
         if (!a.waveform_json.empty()) write_json(a.waveform_json, name, names, solver.waveform, st);
-        if (!a.waveform_nz.empty()) {
-            std::vector<double> t;
-            std::vector<std::vector<double>> sig(names.size());
-            for (auto& p : solver.waveform) {
-                t.push_back(p.time);
-                for (size_t i = 0; i < names.size(); ++i) sig[i].push_back(i < p.values.size() ? p.values[i] : 0.0);
-            }
-            NzWriter w(a.nz_tol);
-            w.write_file(a.waveform_nz, names, t, sig);
-        }
+        if (!a.waveform_nz.empty()) write_nz(a.waveform_nz, names, solver.waveform, a.nz_tol);
     } catch (const std::exception& e) {
         std::fprintf(stderr, "ERROR: %s\n", e.what());
         return 1;
