@@ -190,7 +190,12 @@ struct Element {
         if (!j.is_obj() || j.obj.size() != 1) throw std::runtime_error("element: expected a single-key object");
         const std::string& tag = j.obj[0].first;
         const Json& o = j.obj[0].second;
-        auto I = [&](const char* k) { return int(o.number(k, 0)); };
+        // a node index outside the int range would be undefined behaviour in the cast; Netlist::validate() rejects the
+        // -1 this maps it to (and every other index outside the netlist)
+        auto I = [&](const char* k) {
+            const double v = o.number(k, 0);
+            return (v >= 0.0 && v <= 2147483647.0) ? int(v) : -1;
+        };
         if (tag == "Resistor") return resistor(I("a"), I("b"), o.number("r", 1.0));
         if (tag == "Capacitor") return capacitor(I("a"), I("b"), o.number("c", 0.0));
         if (tag == "Inductor") return inductor(I("a"), I("b"), o.number("l", 0.0));
@@ -250,17 +255,49 @@ struct Netlist {
     static Netlist from_json(const Json& j) {
         Netlist n;
         if (const Json* p = j.find("name")) n.name = p->is_str() ? p->str : "";
-        n.num_nodes = int(j.number("num_nodes", 0));
+        {
+            const double nodes = j.number("num_nodes", 0);
+            if (!(nodes >= 0.0 && nodes <= 100000000.0)) throw std::runtime_error("netlist: num_nodes out of range");
+            n.num_nodes = int(nodes);
+        }
         for (auto& e : j.at("elements").arr) n.elements.push_back(Element::from_json(e));
         if (const Json* gm = j.find("ghost_map"))
             for (auto& t : gm->arr)
-                if (t.arr.size() >= 3) n.ghost_map.push_back({uint64_t(t.arr[0].as_num()), int(t.arr[1].as_num()), uint32_t(t.arr[2].as_num())});
+                if (t.arr.size() >= 3) {
+                    const double id = t.arr[0].as_num(), node = t.arr[1].as_num(), owner = t.arr[2].as_num();
+                    if (!(id >= 0.0 && id < 18446744073709551616.0) || !(node >= 0.0 && node <= 2147483647.0) || !(owner >= 0.0 && owner <= 4294967295.0))
+                        throw std::runtime_error("netlist: ghost link with a number out of range");
+                    n.ghost_map.push_back({uint64_t(id), int(node), uint32_t(owner)});
+                }
         if (const Json* nn = j.find("node_names"))
             for (auto& s : nn->arr) n.node_names.push_back(s.as_str());
         if (const Json* ic = j.find("initial_conditions"))
             for (auto& t : ic->arr)
-                if (t.arr.size() >= 2) n.initial_conditions.emplace_back(int(t.arr[0].as_num()), t.arr[1].as_num());
+                if (t.arr.size() >= 2) {
+                    const double node = t.arr[0].as_num();
+                    n.initial_conditions.emplace_back((node >= 0.0 && node <= 2147483647.0) ? int(node) : -1, t.arr[1].as_num());
+                }
+        n.validate();
         return n;
+    }
+    // Throws when an element, a ghost link or an initial condition names a node outside 0 .. num_nodes, or a part has a
+    // value no solver can use. Files come from the partitioner, but also from users and over the network.
+    void validate() const {
+        auto bad = [&](int node) { return node < 0 || node > num_nodes; };
+        if (num_nodes < 0 || num_nodes > 100000000) throw std::runtime_error("netlist: num_nodes out of range");
+        for (size_t k = 0; k < elements.size(); ++k) {
+            const Element& e = elements[k];
+            const bool mos = e.kind == Element::Mosfet;
+            if (mos ? (bad(e.d) || bad(e.g) || bad(e.s) || bad(e.bulk)) : (bad(e.a) || (e.kind != Element::Ghost && bad(e.b))))
+                throw std::runtime_error("netlist: element " + std::to_string(k) + " names a node outside 0.." + std::to_string(num_nodes));
+            if ((e.kind == Element::Resistor && !(std::fabs(e.value) > 0.0)) || !std::isfinite(e.value))
+                throw std::runtime_error("netlist: element " + std::to_string(k) + " has an unusable value");
+        }
+        for (auto& g : ghost_map)
+            if (g.local_node <= 0 || g.local_node > num_nodes) throw std::runtime_error("netlist: ghost link names a node outside 1.." + std::to_string(num_nodes));
+        for (auto& ic : initial_conditions)
+            if (ic.first <= 0 || ic.first > num_nodes || !std::isfinite(ic.second)) throw std::runtime_error("netlist: initial condition on a node outside 1.." + std::to_string(num_nodes));
+        if (!node_names.empty() && node_names.size() < size_t(num_nodes)) throw std::runtime_error("netlist: fewer node names than nodes");
     }
 };
 

@@ -209,7 +209,18 @@ static int run_distributed(const Args& a) {
     }
 }
 
+static int run(int argc, char** argv);
+
 int main(int argc, char** argv) {
+    try {
+        return run(argc, argv);
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ERROR: %s\n", e.what());
+        return 1;
+    }
+}
+
+static int run(int argc, char** argv) {
     Args a;
     if (!parse_args(argc, argv, a)) { usage(); return 2; }
     if (a.bench) {

@@ -419,3 +419,23 @@ def test_long_line_with_underflowing_far_end_stays_on_the_direct_path():
     assert np.abs(np.asarray(lu["values"]) - np.asarray(dense["values"])).max() < 1e-12
     assert nr["step_cuts"] == 0 and nr["be_fallbacks"] == 0 and nr["lu_fallbacks"] == 0 and nr["lu_repivots"] == 0
     assert nr["lu_analyses"] <= 3 and nr["lu_refactors"] <= 4 and nr["lu_reuses"] >= 90   # DC, first (BE) step, trapezoidal steps
+
+
+def test_partition_files_with_bad_indices_are_rejected():
+    good = {"name": "rc", "num_nodes": 2, "node_names": ["a", "b"], "initial_conditions": [],
+            "elements": [{"VoltageSource": {"pos": 1, "neg": 0, "source": {"Dc": 1.0}}}, {"Resistor": {"a": 1, "b": 2, "r": 1e3}},
+                         {"Capacitor": {"a": 2, "b": 0, "c": 1e-14}}], "ghost_map": []}
+    assert N.simulate(json.dumps(good), 5e-12, 1e-12)["stats"]["completed"]
+    for mutate, what in ((lambda d: d["elements"][1]["Resistor"].update(b=7), "node outside"),
+                         (lambda d: d["elements"][1]["Resistor"].update(a=9e9), "node outside"),
+                         (lambda d: d["elements"][1]["Resistor"].update(a=-3), "node outside"),
+                         (lambda d: d["elements"][1]["Resistor"].update(r=0.0), "unusable value"),
+                         (lambda d: d.update(ghost_map=[[12345, 5, 1]]), "ghost link"),
+                         (lambda d: d.update(ghost_map=[[-1.0, 1, 1]]), "out of range"),
+                         (lambda d: d.update(initial_conditions=[[3, 1.0]]), "initial condition"),
+                         (lambda d: d.update(num_nodes=-4), "num_nodes"),
+                         (lambda d: d.update(node_names=["a"]), "fewer node names")):
+        bad = json.loads(json.dumps(good))
+        mutate(bad)
+        with pytest.raises(Exception, match=what):
+            N.simulate(json.dumps(bad), 5e-12, 1e-12)
