@@ -1,4 +1,4 @@
-.PHONY: all build clean test test-gpu check python-smoke release-check bench
+.PHONY: all build clean test test-gpu sanitize check python-smoke release-check bench
 
 PYTHON ?= python
 
@@ -23,6 +23,10 @@ test:
 # B200 tier: kernel numerics against fp32 PyTorch, multi-GPU workers
 test-gpu:
 	$(PYTHON) -m pytest tests -q -m gpu
+
+# Host code under AddressSanitizer + UndefinedBehaviorSanitizer against hostile input (part of `make test` as well)
+sanitize:
+	$(PYTHON) -m pytest tests/test_sanitizers_cpu.py -q
 
 # Does everything compile (nvcc cross-compiles without a GPU) and import
 check:
