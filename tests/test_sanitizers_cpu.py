@@ -103,3 +103,61 @@ def test_solver_process_under_sanitizers(built):
         r = subprocess.run([node, "--partition", path, "--tstop", "2e-11", "--dt", "1e-12"], capture_output=True, text=True, timeout=300)
         assert r.returncode >= 0 and _clean(r.stderr), (trial, r.returncode, r.stderr[-3000:])
     assert json.load(open(os.path.join(tmp, "w.json")))["stats"]["completed"] is True
+
+
+@pytest.mark.timeout(1200)
+def test_checkpoint_and_mask_tools_under_sanitizers(built, tmp_path):
+    sys.path.insert(0, ROOT)
+    import numpy as np
+
+    import nangila
+
+    tools = {}
+    jobs = []
+    for name in ("dump", "profile"):
+        tools[name] = os.path.join(built["tmp"], f"nangila-{name}-san")
+        jobs.append(subprocess.Popen(["g++", *FLAGS, f"-I{ROOT}/csrc/core", "-o", tools[name], f"{ROOT}/csrc/cli/nangila_{name}.cpp"],
+                                     stderr=subprocess.PIPE, text=True))
+    for j in jobs:
+        err = j.communicate(timeout=900)[1]
+        assert j.returncode == 0, err[-2000:]
+    hook = nangila.NangilaHook.all_drivers(2, nangila.NangilaConfig(warmup_steps=0, shadow_run_steps=0))
+    rng = np.random.default_rng(0)
+    for _ in range(3):
+        for lid in (0, 1):
+            hook.update(lid, hook.decompress_gathered(lid, hook.compress(lid, rng.normal(size=32).astype(np.float32))))
+        hook.step()
+    ckpt = str(tmp_path / "a.ckpt")
+    hook.save_checkpoint(ckpt)
+    grads = tmp_path / "grads.jsonl"
+    with open(grads, "w") as f:
+        base = rng.normal(size=16)
+        for step in range(30):
+            for lid in range(3):
+                f.write(json.dumps({"step": step, "layer_id": lid, "data": [float(v) for v in base * (1 + 0.1 * lid) + 0.01 * rng.normal(size=16)],
+                                    "shape": [16]}) + "\n")
+    mask = str(tmp_path / "mask.bin")
+    r = subprocess.run([tools["profile"], "calibrate", "-g", str(grads), "-s", "20", "-t", "0.9", "-o", mask], capture_output=True, text=True)
+    assert r.returncode == 0 and _clean(r.stderr), r.stderr[-2000:]
+    good = {"ckpt": open(ckpt, "rb").read(), "mask": open(mask, "rb").read()}
+    prng = random.Random(11)
+    for trial in range(60):
+        which = "ckpt" if trial % 2 == 0 else "mask"
+        data = bytearray(good[which])
+        kind = trial % 3
+        if kind == 0:
+            for _ in range(prng.randint(1, 4)):
+                data[prng.randrange(len(data))] = prng.randrange(256)
+        elif kind == 1:
+            data = data[: prng.randrange(len(data))]
+        else:
+            i = prng.randrange(max(1, len(data) - 8))
+            data[i:i + 8] = b"\xff" * 8   # a length field of 2^64 - 1 somewhere
+        path = str(tmp_path / f"fuzzed.{which}")
+        with open(path, "wb") as f:
+            f.write(data)
+        cmds = ([[tools["dump"], c, "-c", path] for c in ("verify", "inspect", "info")] if which == "ckpt"
+                else [[tools["profile"], "info", "-m", path], [tools["profile"], "report", "-m", path, "-o", str(tmp_path / "r.json")]])
+        for cmd in cmds:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=120)
+            assert r.returncode >= 0 and _clean(r.stderr), (trial, cmd, r.stderr[-3000:])
