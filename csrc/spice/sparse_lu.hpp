@@ -29,13 +29,17 @@
 
 namespace nspice {
 
-// Elimination order of the symmetric pattern (row_ptr, col) by minimum degree. Vertices whose degree exceeds
-// `dense_limit` are left out of the graph and come last, highest degree at the very end. Vertices flagged in
-// `removed` are not part of the graph and not part of the result.
+// Elimination order of the symmetric pattern (row_ptr, col) by minimum degree on the quotient graph: an eliminated
+// vertex becomes an element that stands for the clique of its neighbours, a vertex keeps a list of plain neighbours
+// and a list of elements, elements whose boundary is covered by a newer one are absorbed, and degrees are the usual
+// upper bound |plain neighbours| + |boundary of the new element| + sum over the other elements of |boundary outside the
+// new one| (no clique is ever written out, so the cost stays near the size of the factor). Vertices whose degree exceeds
+// `dense_limit` are left out of the graph and come last, highest degree at the very end. Vertices flagged in `removed`
+// are not part of the graph and not part of the result.
 inline std::vector<int> minimum_degree_order(int n, const std::vector<int>& row_ptr, const std::vector<int>& col,
                                              const std::vector<char>& removed = {}) {
     auto out = [&](int v) { return !removed.empty() && removed[size_t(v)] != 0; };
-    std::vector<std::vector<int>> adj(static_cast<size_t>(n));
+    std::vector<std::vector<int>> adj(static_cast<size_t>(n)), elems(static_cast<size_t>(n)), boundary(static_cast<size_t>(n));
     for (int r = 0; r < n; ++r) {
         if (out(r)) continue;
         for (int k = row_ptr[size_t(r)]; k < row_ptr[size_t(r) + 1]; ++k) {
@@ -45,7 +49,7 @@ inline std::vector<int> minimum_degree_order(int n, const std::vector<int>& row_
     }
     for (auto& a : adj) { std::sort(a.begin(), a.end()); a.erase(std::unique(a.begin(), a.end()), a.end()); }
     const size_t dense_limit = std::max<size_t>(16, size_t(10.0 * std::sqrt(double(std::max(n, 1)))));
-    std::vector<char> gone(static_cast<size_t>(n), 0);
+    std::vector<char> gone(static_cast<size_t>(n), 0);   // eliminated, removed or set aside as dense
     for (int v = 0; v < n; ++v) gone[size_t(v)] = out(v) ? 1 : 0;
     std::vector<std::pair<size_t, int>> dense;
     for (int v = 0; v < n; ++v)
@@ -55,41 +59,69 @@ inline std::vector<int> minimum_degree_order(int n, const std::vector<int>& row_
             auto& a = adj[size_t(v)];
             a.erase(std::remove_if(a.begin(), a.end(), [&](int u) { return gone[size_t(u)] != 0; }), a.end());
         }
+    std::vector<size_t> degree(static_cast<size_t>(n), 0);
     std::set<std::pair<size_t, int>> queue;
     for (int v = 0; v < n; ++v)
-        if (!gone[size_t(v)]) queue.emplace(adj[size_t(v)].size(), v);
+        if (!gone[size_t(v)]) { degree[size_t(v)] = adj[size_t(v)].size(); queue.emplace(degree[size_t(v)], v); }
     std::vector<int> order;
     order.reserve(size_t(n));
-    std::vector<int> merged;
+    std::vector<char> element_alive(static_cast<size_t>(n), 0);
+    std::vector<int> in_lp(static_cast<size_t>(n), -1);          // in_lp[v] == p: v belongs to the boundary being built for pivot p
+    std::vector<long> outside(static_cast<size_t>(n), -1);       // per element: |boundary outside the new one|, valid when stamp matches
+    std::vector<int> outside_stamp(static_cast<size_t>(n), -1);
+    std::vector<int> lp;
     while (!queue.empty()) {
         if (queue.begin()->first + 1 >= queue.size()) {
-            // what is left is a clique: any order gives the same fill, and eliminating it vertex by vertex
-            // would cost the cube of its size in list merges
+            // what is left is (bounded by) a clique: any order gives the same fill
             for (auto& dv : queue) order.push_back(dv.second);
             break;
         }
-        const int v = queue.begin()->second;
+        const int p = queue.begin()->second;
         queue.erase(queue.begin());
-        gone[size_t(v)] = 1;
-        order.push_back(v);
-        const std::vector<int> nb = std::move(adj[size_t(v)]);
-        adj[size_t(v)].clear();
-        for (int u : nb) {
-            auto& a = adj[size_t(u)];
-            queue.erase({a.size(), u});
-            // a := (a + nb) without u and v; both lists are sorted
-            merged.clear();
-            size_t i = 0, j = 0;
-            while (i < a.size() || j < nb.size()) {
-                int x;
-                if (j >= nb.size() || (i < a.size() && a[i] < nb[j])) x = a[i++];
-                else if (i >= a.size() || nb[j] < a[i]) x = nb[j++];
-                else { x = a[i]; ++i; ++j; }
-                if (x != u && x != v) merged.push_back(x);
-            }
-            a.swap(merged);
-            queue.emplace(a.size(), u);
+        gone[size_t(p)] = 1;
+        order.push_back(p);
+        // boundary of the new element: plain neighbours of p and the boundaries of p's elements, which it absorbs
+        lp.clear();
+        in_lp[size_t(p)] = p;
+        for (int v : adj[size_t(p)])
+            if (!gone[size_t(v)] && in_lp[size_t(v)] != p) { in_lp[size_t(v)] = p; lp.push_back(v); }
+        for (int e : elems[size_t(p)]) {
+            if (!element_alive[size_t(e)]) continue;
+            for (int v : boundary[size_t(e)])
+                if (!gone[size_t(v)] && in_lp[size_t(v)] != p) { in_lp[size_t(v)] = p; lp.push_back(v); }
+            element_alive[size_t(e)] = 0;
+            std::vector<int>().swap(boundary[size_t(e)]);
         }
+        std::vector<int>().swap(adj[size_t(p)]);
+        std::vector<int>().swap(elems[size_t(p)]);
+        // for every element next to the boundary: how much of it lies outside (counted down from its size)
+        for (int i : lp)
+            for (int e : elems[size_t(i)]) {
+                if (!element_alive[size_t(e)]) continue;
+                if (outside_stamp[size_t(e)] != p) { outside_stamp[size_t(e)] = p; outside[size_t(e)] = long(boundary[size_t(e)].size()); }
+                --outside[size_t(e)];
+            }
+        const size_t remaining = queue.size();
+        for (int i : lp) {
+            queue.erase({degree[size_t(i)], i});
+            auto& a = adj[size_t(i)];
+            a.erase(std::remove_if(a.begin(), a.end(), [&](int v) { return gone[size_t(v)] != 0 || in_lp[size_t(v)] == p; }), a.end());
+            auto& el = elems[size_t(i)];
+            size_t sum_outside = 0, keep = 0;
+            for (int e : el) {
+                if (!element_alive[size_t(e)]) continue;
+                if (outside[size_t(e)] <= 0) { element_alive[size_t(e)] = 0; std::vector<int>().swap(boundary[size_t(e)]); continue; }  // covered by the new element
+                sum_outside += size_t(outside[size_t(e)]);
+                el[keep++] = e;
+            }
+            el.resize(keep);
+            el.push_back(p);
+            const size_t bound = a.size() + (lp.size() - 1) + sum_outside;
+            degree[size_t(i)] = std::min({bound, degree[size_t(i)] + lp.size() - 1, remaining > 0 ? remaining - 1 : size_t(0)});
+            queue.emplace(degree[size_t(i)], i);
+        }
+        boundary[size_t(p)] = lp;
+        element_alive[size_t(p)] = 1;
     }
     std::sort(dense.begin(), dense.end());
     for (auto& d : dense) order.push_back(d.second);
