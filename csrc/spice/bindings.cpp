@@ -117,11 +117,11 @@ PYBIND11_MODULE(_native, m) {
     });
 
     m.def("simulate_partitioned", [](std::vector<std::string> parts_json, double tstop, double dt, double reltol, uint32_t predict_depth, bool compress,
-                                     uint32_t record_every, unsigned threads) {
+                                     uint32_t record_every, unsigned threads, bool speculate) {
         std::vector<Netlist> parts;
         for (auto& js : parts_json) parts.push_back(Netlist::from_json(Json::parse(js)));
         PartitionedConfig cfg;
-        cfg.tstop = tstop; cfg.dt = dt; cfg.reltol = reltol; cfg.predict_depth = predict_depth; cfg.compress = compress; cfg.record_every = std::max(1u, record_every); cfg.threads = threads;
+        cfg.tstop = tstop; cfg.dt = dt; cfg.reltol = reltol; cfg.predict_depth = predict_depth; cfg.compress = compress; cfg.record_every = std::max(1u, record_every); cfg.threads = threads; cfg.speculate = speculate;
         PartitionedRunner r(std::move(parts), cfg);
         {
             py::gil_scoped_release rel;
@@ -135,11 +135,13 @@ PYBIND11_MODULE(_native, m) {
         st["resolves"] = r.stats.resolves; st["messages"] = r.stats.messages; st["bytes_sent"] = r.stats.bytes_sent; st["codec_ratio"] = r.stats.codec_ratio;
         st["completed"] = r.stats.completed; st["wall_time_secs"] = r.stats.wall_time_secs; st["unconverged_steps"] = r.stats.unconverged_steps;
         st["final_depth"] = r.stats.final_depth;
+        st["windows"] = r.stats.windows; st["speculated_steps"] = r.stats.speculated_steps; st["discarded_steps"] = r.stats.discarded_steps;
+        st["rollbacks"] = r.stats.rollbacks;
         py::dict out;
         out["node_names"] = r.names; out["time"] = t; out["values"] = v; out["stats"] = st;
         return out;
     }, py::arg("partitions"), py::arg("tstop"), py::arg("dt"), py::arg("reltol") = 1e-3, py::arg("predict_depth") = 5, py::arg("compress") = true,
-       py::arg("record_every") = 1, py::arg("threads") = 1);
+       py::arg("record_every") = 1, py::arg("threads") = 1, py::arg("speculate") = true);
 
     // ---- linear algebra -----------------------------------------------------------------------
     m.def("solve_csr", [](int n, std::vector<int> row_ptr, std::vector<int> col, std::vector<double> val, std::vector<double> rhs, const std::string& solver) {

@@ -28,6 +28,7 @@ namespace nspice {
 
 struct DistributedConfig {
     double tstop = 1e-9, dt = 1e-12, reltol = 1e-3, abstol = 1e-6;
+    double accept_factor = 0.25;  // a prediction is a hit within accept_factor * reltol (see PartitionedConfig)
     uint32_t predict_depth = 5, record_every = 1;
     int max_sweeps = 50, max_dc_sweeps = 400, io_timeout_ms = 30000;
 };
@@ -208,7 +209,7 @@ private:
             {
                 std::vector<Correction> cs;
                 for (auto& l : latest_) cs.push_back({l.first, l.second, t_next});
-                const bool hit = cs.empty() || ghosts_.apply_corrections(cs, cfg_.reltol);
+                const bool hit = cs.empty() || ghosts_.apply_corrections(cs, cfg_.reltol * cfg_.accept_factor);
                 (hit ? stats.prediction_hits : stats.prediction_misses) += cs.size();
                 mine.ok = hit ? 1 : 0;
             }

@@ -111,7 +111,7 @@ def test_partitioned_run_matches_single_matrix(tmp_path, k):
     path = _write(tmp_path, "ladder.sp", generate_rc_ladder_netlist(40, 1e3, 10e-15))
     res = ns.simulate(path, partitions=k, tstop=300e-12, dt=1e-12, method="bisect")
     assert res.success and res.validation_status == "partitioned_validated", res.summary()
-    assert res.reference_comparison.max_abs_error < 1e-5 and len(res.partition_result.partitions) == k
+    assert res.reference_comparison.max_abs_error < 5e-5 and len(res.partition_result.partitions) == k  # accepted predictions are within 0.25e-3 relative
     assert res.waveform.num_nodes == 41 and res.waveform.num_points == 301
     st = res.solver_stats["stats"]
     assert st["messages"] > 0 and st["codec_ratio"] > 1.0 and st["unconverged_steps"] == 0
@@ -362,3 +362,33 @@ def test_process_mesh_notices_absent_and_dead_peers(tmp_path):
     # what the survivors had computed up to then is on disk
     partial = json.loads((tmp_path / "dead0.json").read_text())
     assert partial["stats"]["completed"] is False and len(partial["waveform"]) > 10
+
+
+def test_speculative_windows_roll_back_on_a_miss_and_keep_the_answer(tmp_path):
+    """Partitions run several steps ahead on predictions; a missed prediction relaxes that step and discards the rest."""
+    from nangila_spice import correctness as cx
+
+    # a smooth line: once the input edge has passed, predictions hit and whole windows are accepted
+    files = _partition_files(tmp_path, generate_rc_ladder_netlist(120, 1e3, 10e-15), 3, "bisect")
+    texts = [open(f).read() for f in files]
+    lock = N.simulate_partitioned(texts, 300e-12, 1e-12, 1e-3, 5, True, 1, 1, False)
+    spec = N.simulate_partitioned(texts, 300e-12, 1e-12, 1e-3, 5, True, 1, 1, True)
+    assert lock["stats"]["windows"] == 0 and lock["stats"]["completed"] and spec["stats"]["completed"]
+    assert spec["stats"]["windows"] > 5 and spec["stats"]["speculated_steps"] >= 100
+    assert np.abs(np.asarray(lock["values"]) - np.asarray(spec["values"])).max() < 1e-4
+    # switching logic: predictions miss at every edge, so windows are cut (rollbacks) and the depth controller backs off,
+    # and the result still agrees with the single matrix
+    case = next(c for c in cx.official_correctness_cases() if c.name == "alu2")
+    path = case.materialize(str(tmp_path))
+    nl = ns.parse_netlist(path)
+    pr = ns.partition_netlist(nl, 4, "spectral")
+    flat = nl.to_native()
+    flat.pop("warnings", None)
+    single = N.simulate(json.dumps(flat), 0.8e-9, 1e-12)
+    part = N.simulate_partitioned(pr.partition_files(), 0.8e-9, 1e-12, 1e-3, 5, True, 1, 2, True)
+    st = part["stats"]
+    assert st["completed"] and st["rollbacks"] > 0 and st["discarded_steps"] > 0 and st["unconverged_steps"] == 0
+    a, names = np.asarray(single["values"]), single["node_names"]
+    b = np.asarray(part["values"])
+    idx = [names.index(n) for n in part["node_names"]]
+    assert np.abs(a[:, idx] - b).max() < 2e-3
