@@ -34,7 +34,7 @@ struct Args {
     int connect_timeout_ms = 30000, io_timeout_ms = 30000;
     uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1, threads = 1;
     double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
-    bool demo = false, bench = false;
+    bool demo = false, bench = false, lockstep = false;
 };
 
 static void usage() {
@@ -43,7 +43,7 @@ static void usage() {
                  "                    [--reltol R] [--tstop T] [--dt DT] [--process P] [--vdd V] [--temp C]\n"
                  "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov|cuda]\n"
                  "                    [--record-every K] [--partitions A.json,B.json,... [--threads T]] [--bench]\n"
-                 "                    [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T]]\n");
+                 "                    [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T] [--lockstep]]\n");
 }
 
 static bool parse_args(int argc, char** argv, Args& a) {
@@ -56,6 +56,7 @@ static bool parse_args(int argc, char** argv, Args& a) {
         const char* v = nullptr;
         if (f == "--demo") a.demo = true;
         else if (f == "--bench") a.bench = true;
+        else if (f == "--lockstep") a.lockstep = true;
         else if (f == "--partitions") { if (!(v = need("--partitions"))) return false; a.partitions = v; }
         else if (f == "-h" || f == "--help") { usage(); std::exit(0); }
         else if (f == "--partition" || f == "-p") { if (!(v = need("--partition"))) return false; a.partition = v; }
@@ -157,6 +158,7 @@ static int run_partitioned(const Args& a) {
         PartitionedConfig cfg;
         cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
         cfg.threads = a.threads;
+        cfg.speculate = !a.lockstep;
         PartitionedRunner runner(std::move(parts), cfg);
         runner.run();
         const PartitionedStats& st = runner.stats;
@@ -186,14 +188,16 @@ static int run_distributed(const Args& a) {
         DistributedConfig cfg;
         cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
         cfg.io_timeout_ms = a.io_timeout_ms;
+        cfg.speculate = !a.lockstep;
         DistributedRunner runner(std::move(nl), mesh, cfg);
         runner.engine().newton.config.reltol = a.reltol;
         if (a.solver == "dense") runner.engine().newton.linear.backend = LinearBackend::Dense;
         else if (a.solver == "krylov") runner.engine().newton.linear.backend = LinearBackend::Krylov;
         const bool ok = runner.run();
         const DistributedStats& st = runner.stats;
-        std::fprintf(stderr, "process %u of %u: %llu steps%s, %.3f s, %llu DC sweeps, hits %llu, misses %llu, extra solves %llu, %llu messages (%llu bytes)%s%s\n",
+        std::fprintf(stderr, "process %u of %u: %llu steps%s, %.3f s, %llu DC sweeps, %llu windows (%llu steps ahead, %llu discarded), hits %llu, misses %llu, extra solves %llu, %llu messages (%llu bytes)%s%s\n",
                      a.node_id, a.total, (unsigned long long)st.steps, ok ? "" : " (stopped early)", st.wall_time_secs, (unsigned long long)st.dc_sweeps,
+                     (unsigned long long)st.windows, (unsigned long long)st.speculated_steps, (unsigned long long)st.discarded_steps,
                      (unsigned long long)st.prediction_hits, (unsigned long long)st.prediction_misses, (unsigned long long)st.resolves,
                      (unsigned long long)mesh.stats.messages_sent, (unsigned long long)mesh.stats.bytes_sent, st.error.empty() ? "" : ": ", st.error.c_str());
         SimStats ss;

@@ -61,6 +61,7 @@ class SimulationConfig:
     prefer_single_node_fallback_for_partitioned: bool = False
     verbose: bool = False
     mode: str = "auto"  # 'auto' | 'in_process' | 'processes' (one nangila-node per partition, boundary values over TCP)
+    speculate: bool = True  # partitions run windows of steps ahead on predictions between exchanges (False: one step per exchange)
     io_timeout_secs: float = 30.0  # processes mode: how long a process waits for a peer before it gives up
     process: str = "TT"
     vdd: float = 1.8
@@ -180,7 +181,7 @@ def _run_processes(config: SimulationConfig, pr: PartitionResult, workdir: str) 
                "--waveform-json", out, "--io-timeout-ms", str(int(config.io_timeout_secs * 1000)),
                "--connect-timeout-ms", str(int(config.io_timeout_secs * 1000))]
         if k > 1:
-            cmd += ["--rendezvous", rendezvous]
+            cmd += ["--rendezvous", rendezvous] + ([] if config.speculate else ["--lockstep"])
         procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     logs, times = [], []
     for proc in procs:
@@ -228,7 +229,7 @@ def run_simulation(config: SimulationConfig) -> SimulationResult:
             if mode == "in_process":
                 threads = config.threads or max(1, min(k, hw.cpu_count))
                 r = _native.simulate_partitioned(pr.partition_files(), config.tstop, config.dt, config.reltol, config.predict_depth, True,
-                                                 config.record_every, threads)
+                                                 config.record_every, threads, config.speculate)
                 result.waveform = Waveform.from_native(r, title=Path(config.netlist_path).name)
                 result.solver_stats = {"stats": r["stats"]}
                 result.success = bool(r["stats"]["completed"])
