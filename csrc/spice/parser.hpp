@@ -357,6 +357,21 @@ private:
                         else if (k == "l") l = value(tok[i].substr(eq + 1));
                     }
                     elements_.push_back(Element::mosfet(d, g, s, b, mos_model(upper(tok[5]), w, l)));
+                    // Constant device capacitances, where the model card gives them (SPICE level-1 names): gate overlap
+                    // cgso / cgdo in F per metre of width, zero-bias junction cbd / cbs in F. Their bias dependence and the
+                    // channel charge are not modelled.
+                    auto mit = models.find(upper(tok[5]));
+                    if (mit != models.end()) {
+                        auto& mp = mit->second.params;
+                        auto cap = [&](const char* key, double scale, int a, int c) {
+                            auto f = mp.find(key);
+                            if (f != mp.end() && f->second * scale > 0.0 && a != c) elements_.push_back(Element::capacitor(a, c, f->second * scale));
+                        };
+                        cap("cgso", w, g, s);
+                        cap("cgdo", w, g, d);
+                        cap("cbd", 1.0, d, b);
+                        cap("cbs", 1.0, s, b);
+                    }
                 }
                 return;
             case 'X': {

@@ -439,3 +439,32 @@ def test_partition_files_with_bad_indices_are_rejected():
         mutate(bad)
         with pytest.raises(Exception, match=what):
             N.simulate(json.dumps(bad), 5e-12, 1e-12)
+
+
+def test_mosfet_overlap_and_junction_capacitances_from_the_model_card():
+    deck = """* inverter behind a source resistance
+VDD vdd 0 DC 1.8
+VIN src 0 PULSE(0 1.8 100p 20p 20p 400p 1n)
+RIN src in 5k
+M1 out in vdd vdd pch w=2u l=180n
+M2 out in 0 0 nch w=1u l=180n
+CL out 0 2f
+.model nch NMOS (vto=0.45 kp=200u lambda=0.05 {caps})
+.model pch PMOS (vto=-0.45 kp=100u lambda=0.05 {caps})
+.end
+"""
+    got = {}
+    for caps in ("", "cgso=3e-10 cgdo=3e-10 cbd=1f cbs=1f"):
+        js, _ = N.parse_spice(deck.format(caps=caps))
+        parts = json.loads(js)["elements"]
+        r = N.simulate(js, 0.4e-9, 0.5e-12)
+        v, names, t = np.asarray(r["values"]), r["node_names"], np.asarray(r["time"])
+        out = v[:, names.index("out")]
+        got[caps] = (sum("Capacitor" in e for e in parts), out.max(), t[np.argmax(out < 0.9)])
+    # cgso, cgdo and cbd per device (cbs would sit between a net and itself here and is left out)
+    assert got[""][0] == 1 and got["cgso=3e-10 cgdo=3e-10 cbd=1f cbs=1f"][0] == 7
+    caps_run = got["cgso=3e-10 cgdo=3e-10 cbd=1f cbs=1f"]
+    widths = [c["Capacitor"]["c"] for c in json.loads(N.parse_spice(deck.format(caps="cgso=3e-10 cgdo=3e-10"))[0])["elements"] if "Capacitor" in c]
+    assert sorted(widths)[:4] == pytest.approx([3e-16, 3e-16, 6e-16, 6e-16])   # F/m times the width of each device
+    # the gate-drain capacitance couples the rising input into the output (above the rail) and slows the edge
+    assert got[""][1] <= 1.8 + 1e-9 and caps_run[1] > 1.82 and caps_run[2] > got[""][2] + 5e-12
