@@ -37,15 +37,17 @@ def built(tmp_path_factory):
     tmp = str(tmp_path_factory.mktemp("san"))
     if not _sanitizers_available(tmp):
         pytest.skip("g++ with -fsanitize=address,undefined is not usable here")
-    fuzz, node = os.path.join(tmp, "ffi_fuzz"), os.path.join(tmp, "nangila-node-san")
+    fuzz, node, tnode = os.path.join(tmp, "ffi_fuzz"), os.path.join(tmp, "nangila-node-san"), os.path.join(tmp, "nangila-node-tsan")
     jobs = [subprocess.Popen(["g++", *FLAGS, f"-I{ROOT}/csrc/core", f"-I{ROOT}/csrc/kernels", "-o", fuzz, f"{ROOT}/tests/native/ffi_fuzz.cpp",
                               f"{ROOT}/csrc/core/c_api.cpp", "-ldl", "-lpthread"], stderr=subprocess.PIPE, text=True),
             subprocess.Popen(["g++", *FLAGS, f"-I{ROOT}/csrc/spice", "-o", node, f"{ROOT}/csrc/spice/node_main.cpp", "-ldl", "-lpthread"],
-                             stderr=subprocess.PIPE, text=True)]
+                             stderr=subprocess.PIPE, text=True),
+            subprocess.Popen(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", f"-I{ROOT}/csrc/spice", "-o", tnode,
+                              f"{ROOT}/csrc/spice/node_main.cpp", "-ldl", "-lpthread"], stderr=subprocess.PIPE, text=True)]
     for j in jobs:
         err = j.communicate(timeout=900)[1]
         assert j.returncode == 0, err[-2000:]
-    return {"fuzz": fuzz, "node": node, "tmp": tmp}
+    return {"fuzz": fuzz, "node": node, "tsan_node": tnode, "tmp": tmp}
 
 
 @pytest.mark.timeout(1200)
@@ -161,3 +163,28 @@ def test_checkpoint_and_mask_tools_under_sanitizers(built, tmp_path):
         for cmd in cmds:
             r = subprocess.run(cmd, capture_output=True, text=True, timeout=120)
             assert r.returncode >= 0 and _clean(r.stderr), (trial, cmd, r.stderr[-3000:])
+
+
+@pytest.mark.timeout(1200)
+def test_threaded_partitioned_run_under_thread_sanitizer(built):
+    """The worker pool of the in-process partitioned run (spin-then-yield generation counter) under ThreadSanitizer."""
+    sys.path.insert(0, ROOT)
+    import nangila_spice as ns
+    from nangila_spice import correctness as cx
+
+    tmp = built["tmp"]
+    probe = subprocess.run([built["tsan_node"], "--demo", "--tstop", "1e-11"], capture_output=True, text=True, timeout=300)
+    if "FATAL: ThreadSanitizer" in probe.stderr:   # e.g. an address-space layout the runtime cannot map
+        pytest.skip("ThreadSanitizer cannot run in this environment: " + probe.stderr.strip().splitlines()[0])
+    case = next(c for c in cx.official_correctness_cases() if c.name == "alu2")
+    deck = case.materialize(os.path.join(tmp, "tsan"))
+    pr = ns.partition_netlist(ns.parse_netlist(deck), 4, "spectral")
+    files = []
+    for i, js in enumerate(pr.partition_files()):
+        files.append(os.path.join(tmp, "tsan", f"p{i}.json"))
+        with open(files[-1], "w") as f:
+            f.write(js)
+    r = subprocess.run([built["tsan_node"], "--partitions", ",".join(files), "--threads", "4", "--tstop", "2e-10", "--dt", "1e-12"],
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "ThreadSanitizer" not in r.stderr and "data race" not in r.stderr, r.stderr[-3000:]
+    assert "partitioned run: 200 steps" in r.stderr
