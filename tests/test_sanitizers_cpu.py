@@ -15,7 +15,7 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-FLAGS = ["-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"]
+FLAGS = ["-std=c++17", "-O0", "-g1", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"]  # -O0: the compile dominates the run
 
 
 def _sanitizers_available(tmp):
@@ -42,7 +42,7 @@ def built(tmp_path_factory):
                               f"{ROOT}/csrc/core/c_api.cpp", "-ldl", "-lpthread"], stderr=subprocess.PIPE, text=True),
             subprocess.Popen(["g++", *FLAGS, f"-I{ROOT}/csrc/spice", "-o", node, f"{ROOT}/csrc/spice/node_main.cpp", "-ldl", "-lpthread"],
                              stderr=subprocess.PIPE, text=True),
-            subprocess.Popen(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", f"-I{ROOT}/csrc/spice", "-o", tnode,
+            subprocess.Popen(["g++", "-std=c++17", "-O0", "-g1", "-fsanitize=thread", f"-I{ROOT}/csrc/spice", "-o", tnode,
                               f"{ROOT}/csrc/spice/node_main.cpp", "-ldl", "-lpthread"], stderr=subprocess.PIPE, text=True)]
     for j in jobs:
         err = j.communicate(timeout=900)[1]
