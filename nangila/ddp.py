@@ -37,7 +37,7 @@ import torch
 import torch.distributed as dist
 from torch.nn.parallel import DistributedDataParallel as DDP
 
-from ._C import CompressorType, MetricsCollector, NangilaConfig, NangilaHook, SyncMode
+from ._C import CompressorType, MetricsCollector, NangilaConfig, NangilaHook, SyncMode  # noqa: F401  (CompressorType is re-exported)
 
 NANGILA_AVAILABLE = True
 

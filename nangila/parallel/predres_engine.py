@@ -19,7 +19,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from .symm import LoopbackArena, Region, SymmArena
+from .symm import LoopbackArena, Region
 
 _DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 

@@ -6,7 +6,7 @@ import statistics
 import subprocess
 import threading
 import time
-from typing import Callable, Optional, Tuple
+from typing import Callable, Tuple
 
 import torch
 import torch.distributed as dist

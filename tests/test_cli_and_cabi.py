@@ -7,7 +7,6 @@ import subprocess
 import sys
 
 import numpy as np
-import pytest
 
 import nangila
 from nangila import _C as C
