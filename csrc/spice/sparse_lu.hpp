@@ -432,25 +432,34 @@ private:
         apply(rhs, x);
         res_.resize(size_t(n));
         for (int round = 0; round < 4; ++round) {
-            // Componentwise backward error |b - A x|_i / (|b| + |A||x|)_i. A row whose terms have all decayed far below
-            // what the largest unknown would contribute to it (the far end of a long RC line holds 1e-300 V) is measured
-            // against that contribution instead: down there the quotient compares rounding noise with underflow.
+            // Two measures per row. Componentwise: |b - A x|_i / (|b| + |A||x|)_i, what refinement normally reaches and the
+            // stronger statement. Normwise: |b - A x|_i / (|b|_i + sum_k |a_ik| * max|x|), what Gaussian elimination
+            // guarantees. A row that mixes coefficients of wildly different size (or whose terms have decayed into the
+            // subnormal range, as at the far end of a long RC line) can be solved to rounding accuracy and still never meet
+            // the first, so the solve is accepted when every row meets the first at 1e-10 or the second at 1e-13.
             double xmax = 0.0;
             for (int i = 0; i < n; ++i) xmax = std::max(xmax, std::fabs(x[size_t(i)]));
-            double worst = 0.0;
+            if (!std::isfinite(xmax)) return false;
+            double worst = 0.0, worst_loose = 0.0;  // over the rows: the measure each row does better on, scaled to its bound
             for (int r = 0; r < n; ++r) {
-                double ax = 0.0, mag = std::fabs(rhs[size_t(r)]) + 1e-16 * xmax / scale_[size_t(r)];
+                double ax = 0.0, mag = std::fabs(rhs[size_t(r)]), rowsum = 0.0;
                 for (int k = a_ptr_[size_t(r)]; k < a_ptr_[size_t(r) + 1]; ++k) {
                     const double t = val[size_t(k)] * x[size_t(a_col_[size_t(k)])];
                     ax += t;
                     mag += std::fabs(t);
+                    rowsum += std::fabs(val[size_t(k)]);
                 }
-                res_[size_t(r)] = rhs[size_t(r)] - ax;
-                if (mag > 0.0) worst = std::max(worst, std::fabs(res_[size_t(r)]) / mag);
+                const double res = rhs[size_t(r)] - ax;
+                res_[size_t(r)] = res;
+                if (!std::isfinite(res) || !std::isfinite(mag)) return false;  // an overflowed answer (std::max would skip a NaN)
+                const double comp = mag > 0.0 ? std::fabs(res) / mag : 0.0;
+                const double normw = std::fabs(rhs[size_t(r)]) + rowsum * (xmax + 1e-280);  // the floor: residuals down in the subnormal range are rounding noise
+                const double norm = normw > 0.0 ? std::fabs(res) / normw : 0.0;
+                worst = std::max(worst, std::min(comp / 1e-10, norm / 1e-13));
+                worst_loose = std::max(worst_loose, std::min(comp / 1e-6, norm / 1e-10));
             }
-            if (!std::isfinite(worst)) return false;
-            if (!(worst > 1e-10)) return true;
-            if (round == 3) return worst < 1e-6;
+            if (!(worst > 1.0)) return true;
+            if (round == 3) return !(worst_loose > 1.0);
             ++stats.refinement_rounds;
             apply(res_, dx_);
             for (int i = 0; i < n; ++i) x[size_t(i)] += dx_[size_t(i)];
