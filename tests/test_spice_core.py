@@ -468,3 +468,17 @@ CL out 0 2f
     assert sorted(widths)[:4] == pytest.approx([3e-16, 3e-16, 6e-16, 6e-16])   # F/m times the width of each device
     # the gate-drain capacitance couples the rising input into the output (above the rail) and slows the edge
     assert got[""][1] <= 1.8 + 1e-9 and caps_run[1] > 1.82 and caps_run[2] > got[""][2] + 5e-12
+
+
+def test_type_stub_lists_every_public_name():
+    import ast
+    import os
+
+    stub = os.path.join(os.path.dirname(N.__file__), "_native.pyi")
+    tree = ast.parse(open(stub).read())
+    declared = {n.name for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef))} | \
+               {n.target.id for n in tree.body if isinstance(n, ast.AnnAssign)}
+    public = {n for n in dir(N) if not n.startswith("_")}
+    assert public <= declared, sorted(public - declared)
+    classes = {n.name: {m.name for m in n.body if isinstance(m, ast.FunctionDef)} for n in tree.body if isinstance(n, ast.ClassDef)}
+    assert {"solve", "stats"} <= classes["FactoredLU"] and {"solve", "stats"} <= classes["PvtDeltaSolver"]
