@@ -6,15 +6,15 @@
 //   set-up    every process tells every owner which of its nets it wants; from then on a values message is just the
 //             time and the voltages in the order they were asked for (8 bytes per net, no identifiers)
 //   window    every process runs several steps ahead on predictions, then one exchange carries the boundary voltages of
-//             the whole window and one all-gathered verdict says up to which step every prediction everywhere hit:
+//             the whole window and one all-gathered tally says up to which step every prediction everywhere hit:
 //             those steps are final, the first missed one is relaxed, the rest is discarded
 //   values    one exchange per relaxation sweep between the pairs of processes that share a boundary
-//   verdict   one all-gather per window and per sweep (first miss, steps ready, sweep converged, failed, largest
+//   tally   one all-gather per window and per sweep (first miss, steps ready, sweep converged, failed, largest
 //             change), so that all processes take the same decision
 //
 // The DC point is relaxed the same way (every process solves its operating point against the neighbours' last
 // values, Jacobi fashion, until nothing moves). A process that fails, or whose peer went away or stays silent past
-// the I/O deadline, stops with an error; the others learn of it through the verdict or through their own deadline.
+// the I/O deadline, stops with an error; the others learn of it through the tally or through their own deadline.
 #pragma once
 #include <map>
 #include <memory>
@@ -78,7 +78,7 @@ public:
     }
 
 private:
-    struct Verdict { uint8_t ok = 1, failed = 0; uint32_t first_miss = 0xFFFFFFFFu, ready = 0xFFFFFFFFu; double change = 0.0; };
+    struct Tally { uint8_t ok = 1, failed = 0; uint32_t first_miss = 0xFFFFFFFFu, ready = 0xFFFFFFFFu; double change = 0.0; };
 
     DistributedConfig cfg_;
     SocketMesh& mesh_;
@@ -162,15 +162,15 @@ private:
         return true;
     }
 
-    // Everybody's verdict on the sweep; the combined one is the same in every process.
-    bool agree(Verdict mine, Verdict& all) {
+    // Everybody's tally on the sweep; the combined one is the same in every process.
+    bool agree(Tally mine, Tally& all) {
         std::vector<std::string> got;
         std::string msg(reinterpret_cast<const char*>(&mine), sizeof mine);
-        if (!mesh_.all_gather(msg, got, cfg_.io_timeout_ms)) return fail("verdict: " + mesh_.error);
-        all = Verdict{};
+        if (!mesh_.all_gather(msg, got, cfg_.io_timeout_ms)) return fail("tally: " + mesh_.error);
+        all = Tally{};
         for (uint32_t p = 0; p < got.size(); ++p) {
-            if (got[p].size() != sizeof(Verdict)) return fail("malformed verdict from process " + std::to_string(p));
-            Verdict v;
+            if (got[p].size() != sizeof(Tally)) return fail("malformed tally from process " + std::to_string(p));
+            Tally v;
             std::memcpy(&v, got[p].data(), sizeof v);
             all.ok = all.ok && v.ok;
             all.failed = all.failed || v.failed;
@@ -187,7 +187,7 @@ private:
         next_ = state_;
         if (!swap_boundaries(next_.voltages, 0.0)) return false;
         for (int sweep = 0; sweep < cfg_.max_dc_sweeps; ++sweep) {
-            Verdict mine, all;
+            Tally mine, all;
             if (!has_ic_) {
                 PartitionState seed = next_, out{0};
                 seed.cap_currents.clear();
@@ -262,7 +262,7 @@ private:
         std::vector<std::vector<std::pair<uint64_t, double>>> ahead_pins;
         while (step < planned) {
             // a window of steps on predicted ghost voltages, nobody spoken to. The depth controller is fed with the outcome
-            // of the whole run (every process sees the same verdicts), so all processes choose the same depth: a process
+            // of the whole run (every process sees the same tallies), so all processes choose the same depth: a process
             // that ran further ahead than the others would only compute steps nobody can verify
             const uint64_t depth = std::min<uint64_t>(cfg_.speculate ? std::max<uint32_t>(1, depth_.depth()) : 1, planned - step);
             ahead.clear();
@@ -275,9 +275,9 @@ private:
                 ahead.push_back(std::move(next));
                 cur = &ahead.back();
             }
-            Verdict mine, all;
+            Tally mine, all;
             mine.failed = ahead.empty() ? 1 : 0;
-            if (ahead.empty()) { ahead.push_back(state_); ahead_pins.push_back(ghosts_.predict_all(double(step + 1) * cfg_.dt)); }  // well-formed; the verdict stops everybody
+            if (ahead.empty()) { ahead.push_back(state_); ahead_pins.push_back(ghosts_.predict_all(double(step + 1) * cfg_.dt)); }  // well-formed; the tally stops everybody
             pins_ = ahead_pins[0];
             uint32_t usable = 0;
             if (!swap_window(ahead, double(step + 1) * cfg_.dt, usable)) return false;
@@ -312,7 +312,7 @@ private:
             while (!all.ok && sweeps < cfg_.max_sweeps) {
                 const std::vector<double> before = next_.voltages;
                 pins_ = latest_;
-                mine = Verdict{};
+                mine = Tally{};
                 mine.failed = engine_->solve_step(state_, pins_, cfg_.dt, next_) ? 0 : 1;
                 if (mine.failed) next_ = state_;
                 ++stats.resolves;

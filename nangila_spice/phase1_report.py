@@ -90,7 +90,7 @@ def _iter_tier_rows(report: dict, tier: str) -> Iterable[str]:
 def render_markdown_report(report: dict) -> str:
     out = ["# Correctness-first benchmark report", "", f"Generated {report['generated']} on {report['platform']}; oracle: {report['oracle_tool']}.", ""]
     for tier, s in report["tiers"].items():
-        out += [f"## {tier}: {s['passed']}/{s['cases']} within contract", "", "| case | oracle | max error | rms error | edge timing | verdict | time |",
+        out += [f"## {tier}: {s['passed']}/{s['cases']} within contract", "", "| case | oracle | max error | rms error | edge timing | result | time |",
                 "|---|---|---|---|---|---|---|", *_iter_tier_rows(report, tier), ""]
     if report.get("blocked"):
         reasons = {}
