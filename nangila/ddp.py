@@ -658,6 +658,31 @@ class NangilaDDPHook:
         return fut
 
     # ------------------------------------------------------------------------------------------
+    # ---- rank liveness (host side; see nangila/utils/liveness.py) ------------------------------------------------
+    def enable_liveness(self, interval: float = 0.5, timeout: float = 5.0):
+        """Starts heartbeats through the process group's store and returns the ``RankMonitor``. From then on ``step()``
+        raises ``RankFailure`` as soon as a peer has said goodbye or has been silent for ``timeout`` seconds, i.e. before
+        this rank launches into another exchange with a rank that is not there; after a failed collective,
+        ``check_peers(wait=...)`` names the rank that went away."""
+        from .utils.liveness import RankMonitor
+
+        if getattr(self, "liveness", None) is None:
+            self.liveness = RankMonitor.for_group(self.process_group, interval=interval, timeout=timeout)
+        return self.liveness
+
+    def check_peers(self, wait: float = 0.0) -> None:
+        """Raises ``nangila.utils.liveness.RankFailure`` if a peer is gone (no-op unless ``enable_liveness`` was called)."""
+        monitor = getattr(self, "liveness", None)
+        if monitor is not None:
+            monitor.check(wait)
+
+    def leave(self) -> None:
+        """Announces that this rank is about to leave the job, so that the others stop at their next ``step()``
+        instead of waiting for it in a collective."""
+        monitor = getattr(self, "liveness", None)
+        if monitor is not None:
+            monitor.leave()
+
     def step(self) -> None:
         """Call after each optimizer step."""
         self._feed_metrics(self._cpp.is_compression_enabled() if self._native else self.compressing)
@@ -692,6 +717,7 @@ class NangilaDDPHook:
             self._cpp.set_paused(self._force_uncompressed or self.hook.is_paused())
         if failure is not None:
             raise failure
+        self.check_peers()   # last: the bookkeeping of the finished step is complete when a missing peer ends the run
 
     def _byte_counters(self) -> tuple:
         """(bytes the buckets held, bytes that would cross the wire per peer) so far, whichever path ran."""
@@ -878,6 +904,7 @@ def register_nangila_hook(
     power_sgd_rank: int = 1,
     mask: Any = None,
     mask_path: Optional[str] = None,
+    liveness_timeout: Optional[float] = None,
     **extra: Any,
 ) -> "NangilaDDPHook":
     """Register the Nangila compression hook on a DDP model and return it (call ``.step()`` after
@@ -886,7 +913,10 @@ def register_nangila_hook(
     ``mask`` (a ``TopologyMask``, or its bytes as ``Sculptor.generate_mask()`` returns them) or ``mask_path`` (a
     file holding those bytes) applies a calibrated topology: Passenger parameters (layer id = position in
     ``ddp_model.parameters()``) are not exchanged; their averaged gradient is ``alpha * g_driver + beta``. The
-    reference accepted no mask here and treated every layer as a Driver (ddp.py:151)."""
+    reference accepted no mask here and treated every layer as a Driver (ddp.py:151).
+
+    ``liveness_timeout`` (seconds) turns on rank heartbeats through the process group's store: ``hook.step()`` then
+    raises ``RankFailure`` naming a peer that left or fell silent (see ``NangilaDDPHook.enable_liveness``)."""
     if not isinstance(ddp_model, DDP):
         raise TypeError(f"Expected DistributedDataParallel, got {type(ddp_model)}")
     _warn_if_advanced_ddp_options(compressor_type, dgc_sparsity, power_sgd_rank)
@@ -914,6 +944,8 @@ def register_nangila_hook(
         hook.install_native(ddp_model)   # C++ hook on the reducer: no Python per bucket
     else:
         ddp_model.register_comm_hook(state=None, hook=hook)
+    if liveness_timeout is not None:
+        hook.enable_liveness(interval=min(0.5, float(liveness_timeout) / 4.0), timeout=float(liveness_timeout))
     return hook
 
 
