@@ -42,10 +42,11 @@ def sparse_systems(draw, tiny=False):
 
 def _backward_error(a, x, b, componentwise, normwise):
     """Largest over the rows of the better of the two usual measures, each divided by its bound."""
-    resid = np.abs(a @ x - b)
-    comp = resid / (np.abs(a) @ np.abs(x) + np.abs(b) + 1e-300)
-    norm = resid / (np.abs(a).sum(axis=1) * np.abs(x).max() + np.abs(b) + 1e-300)
-    return float(np.minimum(comp / componentwise, norm / normwise).max())
+    with np.errstate(over="ignore"):   # an answer of 1e300 is allowed to make these products infinite
+        resid = np.abs(a @ x - b)
+        comp = resid / (np.abs(a) @ np.abs(x) + np.abs(b) + 1e-300)
+        norm = resid / (np.abs(a).sum(axis=1) * np.abs(x).max() + np.abs(b) + 1e-300)
+        return float(np.minimum(comp / componentwise, norm / normwise).max())
 
 
 def _csr(a):
