@@ -38,6 +38,7 @@ import torch.distributed as dist
 from torch.nn.parallel import DistributedDataParallel as DDP
 
 from ._C import CompressorType, MetricsCollector, NangilaConfig, NangilaHook, SyncMode  # noqa: F401  (CompressorType is re-exported)
+from .utils.liveness import LivenessMixin
 
 NANGILA_AVAILABLE = True
 
@@ -149,7 +150,7 @@ def _validate_sync_mode(sync_mode: Any) -> int:
     return m
 
 
-class NangilaDDPHook:
+class NangilaDDPHook(LivenessMixin):
     """DDP communication hook (``ddp_model.register_comm_hook(None, hook)``).
 
     Args mirror the reference (ddp.py:100-112). ``num_layers`` is only the size of the all-Driver
@@ -658,31 +659,6 @@ class NangilaDDPHook:
         return fut
 
     # ------------------------------------------------------------------------------------------
-    # ---- rank liveness (host side; see nangila/utils/liveness.py) ------------------------------------------------
-    def enable_liveness(self, interval: float = 0.5, timeout: float = 5.0):
-        """Starts heartbeats through the process group's store and returns the ``RankMonitor``. From then on ``step()``
-        raises ``RankFailure`` as soon as a peer has said goodbye or has been silent for ``timeout`` seconds, i.e. before
-        this rank launches into another exchange with a rank that is not there; after a failed collective,
-        ``check_peers(wait=...)`` names the rank that went away."""
-        from .utils.liveness import RankMonitor
-
-        if getattr(self, "liveness", None) is None:
-            self.liveness = RankMonitor.for_group(self.process_group, interval=interval, timeout=timeout)
-        return self.liveness
-
-    def check_peers(self, wait: float = 0.0) -> None:
-        """Raises ``nangila.utils.liveness.RankFailure`` if a peer is gone (no-op unless ``enable_liveness`` was called)."""
-        monitor = getattr(self, "liveness", None)
-        if monitor is not None:
-            monitor.check(wait)
-
-    def leave(self) -> None:
-        """Announces that this rank is about to leave the job, so that the others stop at their next ``step()``
-        instead of waiting for it in a collective."""
-        monitor = getattr(self, "liveness", None)
-        if monitor is not None:
-            monitor.leave()
-
     def step(self) -> None:
         """Call after each optimizer step."""
         self._feed_metrics(self._cpp.is_compression_enabled() if self._native else self.compressing)

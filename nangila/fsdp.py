@@ -20,9 +20,10 @@ import torch.distributed as dist
 from ._C import NangilaConfig
 from .ddp import _validate_sync_mode
 from .parallel.fsdp_collectives import NangilaAllGather, NangilaReduceScatter, apply_nangila_fsdp  # noqa: F401
+from .utils.liveness import LivenessMixin
 
 
-class NangilaFSDPState:
+class NangilaFSDPState(LivenessMixin):
     """State object for ``fsdp_model.register_comm_hook(state, nangila_fsdp_hook)``."""
 
     def __init__(self, process_group: Optional[dist.ProcessGroup], config: Optional[NangilaConfig] = None,
@@ -53,6 +54,7 @@ class NangilaFSDPState:
         self._step += 1
         if self._rs is not None:
             self._rs.end_step()
+        self.check_peers()   # rank heartbeats, when enable_liveness() was called (nangila/utils/liveness.py)
 
     def get_history(self, key: int):
         return self.history.get(key)

@@ -153,3 +153,30 @@ class RankMonitor:
             if time.monotonic() >= deadline:
                 return
             time.sleep(min(self.interval, 0.1))
+
+
+class LivenessMixin:
+    """``enable_liveness`` / ``check_peers`` / ``leave`` for an object that has a ``process_group`` and a ``step()`` that
+    ends with ``self.check_peers()`` (the DDP hook and the FSDP state)."""
+
+    liveness: Optional[RankMonitor] = None
+
+    def enable_liveness(self, interval: float = 0.5, timeout: float = 5.0) -> RankMonitor:
+        """Starts heartbeats through the process group's store and returns the ``RankMonitor``. From then on ``step()``
+        raises ``RankFailure`` as soon as a peer has said goodbye or has been silent for ``timeout`` seconds, i.e. before
+        this rank launches into another exchange with a rank that is not there; after a failed collective,
+        ``check_peers(wait=...)`` names the rank that went away."""
+        if self.liveness is None:
+            self.liveness = RankMonitor.for_group(getattr(self, "process_group", None), interval=interval, timeout=timeout)
+        return self.liveness
+
+    def check_peers(self, wait: float = 0.0) -> None:
+        """Raises ``RankFailure`` if a peer is gone (no-op unless ``enable_liveness`` was called)."""
+        if self.liveness is not None:
+            self.liveness.check(wait)
+
+    def leave(self) -> None:
+        """Announces that this rank is about to leave the job, so that the others stop at their next ``step()``
+        instead of waiting for it in a collective."""
+        if self.liveness is not None:
+            self.liveness.leave()
