@@ -20,7 +20,7 @@ from typing import Iterable, Optional
 import numpy as np
 
 from .correctness import (CorrectnessCase, WaveformData, blocked_official_correctness_cases, check_logic_levels, compare_waveforms,
-                          extended_phase1_correctness_cases, find_ngspice_binary, phase1_automated_correctness_cases, run_nangila_waveform,
+                          extended_phase1_correctness_cases, find_ngspice_binary, large_phase1_correctness_cases, phase1_automated_correctness_cases, run_nangila_waveform,
                           run_ngspice_waveform, within_v1_contract)
 
 # Closed-form solutions, by case name.
@@ -40,8 +40,9 @@ def _run_case(case: CorrectnessCase, ngspice_bin: Optional[str]) -> dict:
             tr = _ANALYTIC[case.name](t)
             ref, oracle = WaveformData("analytic", path, list(tr), t.tolist(), {k: v.tolist() for k, v in tr.items()}), "closed form"
         else:
-            ref = run_nangila_waveform(path, tstop=case.tstop, dt=case.dt / 2, in_process=True, solver="dense")
-            oracle = "dense solver, dt / 2"
+            big = case.tier == "large"   # the dense solver is cubic in the circuit size
+            ref = run_nangila_waveform(path, tstop=case.tstop, dt=case.dt / 2, in_process=True, solver="lu" if big else "dense")
+            oracle = "sparse solver, dt / 2" if big else "dense solver, dt / 2"
         lower = {n.lower(): n for n in cand.traces}
         cand_l = WaveformData(cand.tool, cand.netlist, list(lower), cand.times, {k: cand.traces[v] for k, v in lower.items()})
         ref_l = {n.lower(): v for n, v in ref.traces.items()}
@@ -65,11 +66,13 @@ def _tier_summary(cases: list[dict]) -> dict:
             "total_wall_time_secs": sum(c["wall_time_secs"] for c in cases)}
 
 
-def generate_phase1_benchmark_report(include_extended: bool = False) -> dict:
+def generate_phase1_benchmark_report(include_extended: bool = False, include_large: bool = False) -> dict:
     ngspice = find_ngspice_binary()
     cases = phase1_automated_correctness_cases()
     if include_extended:
         cases += extended_phase1_correctness_cases()
+    if include_large:
+        cases += large_phase1_correctness_cases()
     rows = [_run_case(c, ngspice) for c in cases]
     tiers = sorted({r["tier"] for r in rows})
     return {"generated": time.strftime("%Y-%m-%d %H:%M:%S"), "platform": f"{platform.system()} {platform.machine()}",
@@ -103,10 +106,11 @@ def render_markdown_report(report: dict) -> str:
 def main(argv: Optional[list[str]] = None) -> int:
     ap = argparse.ArgumentParser(description="correctness-first benchmark report")
     ap.add_argument("--include-extended", action="store_true")
+    ap.add_argument("--include-large", action="store_true", help="the suite entries of up to 16 000 devices, against the gate-level logic")
     ap.add_argument("--output-json", default="artifacts/phase1_benchmark_report.json")
     ap.add_argument("--output-md", default="artifacts/phase1_benchmark_report.md")
     args = ap.parse_args(argv)
-    report = generate_phase1_benchmark_report(args.include_extended)
+    report = generate_phase1_benchmark_report(args.include_extended, args.include_large)
     for path, text in ((args.output_json, json.dumps(report, indent=2)), (args.output_md, render_markdown_report(report))):
         os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
         Path(path).write_text(text)

@@ -199,6 +199,10 @@ def test_correctness_registry_and_logic_oracle(tmp_path):
     assert len(cx.extended_phase1_correctness_cases()) >= 4
     blocked = cx.blocked_official_correctness_cases()
     assert {"c6288", "s38417", "mult4"} <= {b.name for b in blocked} and all(b.reason for b in blocked)
+    large = cx.large_phase1_correctness_cases()
+    assert len(large) == 16 and {c.tier for c in large} == {"large"} and not {c.name for c in large} & {b.name for b in blocked}
+    assert all(1 <= len(c.expected_levels) <= 16 for c in large)
+    assert [c.deck for c in cx.large_phase1_correctness_cases()] == [c.deck for c in large]   # the random vectors are seeded
     case = next(c for c in official if c.name == "priority4")
     path = case.materialize(str(tmp_path))
     # this deck used to stop at 68 ps (Newton oscillating across the jump of the old model); now it completes without a single retry
@@ -255,3 +259,14 @@ def test_partitions_keep_transistor_channels_whole_and_logic_runs_partitioned(tm
     assert res.success and res.validation_status == "partitioned_validated", res.warnings
     assert res.solver_stats["stats"]["completed"] and res.solver_stats["stats"]["unconverged_steps"] == 0
     assert res.reference_comparison.max_abs_error < 5e-3
+
+
+def test_a_large_suite_entry_settles_to_its_gate_level_outputs():
+    """One of the ``--include-large`` cases end to end (the 27-channel priority encoder, 979 devices)."""
+    from nangila_spice import correctness as cx
+    from nangila_spice.phase1_report import _run_case
+
+    case = next(c for c in cx.large_phase1_correctness_cases() if c.name == "c432")
+    row = _run_case(case, None)
+    assert row["passed"] and row["logic_levels_checked"] == len(case.expected_levels) and row["logic_levels_wrong"] == []
+    assert row["oracle"] == "sparse solver, dt / 2 + gate-level logic" and row["max_abs_error_v"] < 0.036
