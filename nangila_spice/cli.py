@@ -84,6 +84,8 @@ def invoke_phase1_report(args) -> int:
         argv.append("--include-extended")
     if args.include_large:
         argv.append("--include-large")
+    if args.include_partitioned:
+        argv.append("--include-partitioned")
     return report_main(argv)
 
 
@@ -129,7 +131,8 @@ def main(argv=None) -> int:
     w.add_argument("--dt", type=float, default=1e-12)
     p = sub.add_parser("phase1-report", help="correctness-first benchmark report")
     p.add_argument("--include-extended", action="store_true")
-    p.add_argument("--include-large", action="store_true", help="also the suite entries of up to 16 000 devices (about two minutes)")
+    p.add_argument("--include-large", action="store_true", help="also the suite entries of up to 6 000 transistors (about a minute)")
+    p.add_argument("--include-partitioned", action="store_true", help="also five cases run in partitions, as threads and as processes")
     p.add_argument("--output-json", default="artifacts/phase1_benchmark_report.json")
     p.add_argument("--output-md", default="artifacts/phase1_benchmark_report.md")
     v = sub.add_parser("view", help="show a .nz waveform file")

@@ -312,7 +312,7 @@ LARGE_SUITE_ENTRIES = ("c432", "c499", "c880", "c1355", "c1908", "c2670", "c3540
 
 
 def large_phase1_correctness_cases() -> list:
-    """The suite entries of up to some 16 000 devices (``--include-large``): every input and every flip-flop output steps
+    """The suite entries of up to some 6 000 transistors (``--include-large``): every input and every flip-flop output steps
     to a pseudo-random level, and up to 16 outputs (primary outputs first, then next-state nets) have to settle to what
     the gate list computes. The time-step oracle for these is the sparse solver at half the step (the dense one is
     cubic in the circuit size)."""
@@ -344,7 +344,7 @@ def blocked_official_correctness_cases() -> list:
            "(nangila_spice.benchmark), not to a correctness report")
     glitch = ("all eight inputs switch at once and the middle product bits carry runt pulses whose height moves by 50 mV between 0.25 ps "
               "and 0.125 ps steps: a study of glitch sensitivity, not a check of the solver")
-    glitch16 = ("the 16 x 16 multiplier (16 368 devices) runs and all 32 product bits settle to the right levels, but like mult4 its product "
+    glitch16 = ("the 16 x 16 multiplier (11 872 transistors) runs and all 32 product bits settle to the right levels, but like mult4 its product "
                 "bits carry runt pulses that differ by 50-90 mV between 0.5 ps and 0.25 ps steps")
     return [BlockedCorrectnessCase("mult4", glitch), BlockedCorrectnessCase("c6288", glitch16)] + [BlockedCorrectnessCase(name, why) for name in bc.SUITE if name not in ("c17", "s27", "c6288") and name not in LARGE_SUITE_ENTRIES]
 

@@ -60,13 +60,35 @@ def _run_case(case: CorrectnessCase, ngspice_bin: Optional[str]) -> dict:
             "passed": bool(ok) and not wrong and len(keep) == len(case.nodes), "wall_time_secs": wall}
 
 
+def _run_partitioned(case: CorrectnessCase, partitions: int, mode: str) -> dict:
+    """The case split into ``partitions`` (threads of one process or one process each) against its own single-matrix run."""
+    from .correctness import within_v1_contract as contract
+    from .orchestrator import SimulationConfig, run_simulation
+
+    with tempfile.TemporaryDirectory() as tmp:
+        path = case.materialize(tmp)
+        res = run_simulation(SimulationConfig(netlist_path=path, partitions=partitions, tstop=case.tstop, dt=case.dt, mode=mode,
+                                              output_dir=os.path.join(tmp, "run")))
+    cmp_ = res.reference_comparison
+    ok, profile = contract(cmp_, nonlinear=case.nonlinear) if cmp_ is not None else (False, None)
+    stats = res.solver_stats.get("stats", {})
+    return {"name": f"{case.name} / {len(res.partition_result.partitions)} {'processes' if mode == 'processes' else 'threads'}", "tier": "partitioned",
+            "oracle": "single matrix, same step", "nodes": list(cmp_.shared_nodes) if cmp_ else [], "samples": cmp_.sample_count if cmp_ else 0,
+            "max_abs_error_v": cmp_.max_abs_error if cmp_ else float("inf"), "rms_error_v": cmp_.rms_error if cmp_ else float("inf"),
+            "final_abs_error_v": cmp_.final_abs_error if cmp_ else float("inf"), "edge_timing_error_s": cmp_.max_edge_timing_error if cmp_ else None,
+            "max_abs_tol_v": profile.max_abs_tol if profile else 0.0, "logic_levels_checked": 0, "logic_levels_wrong": [],
+            "passed": bool(res.success and ok and res.validation_status == "partitioned_validated"),
+            "wall_time_secs": float(stats.get("wall_time_secs", res.wall_time_secs)),
+            "rollbacks": stats.get("rollbacks"), "relaxation_solves": stats.get("resolves")}
+
+
 def _tier_summary(cases: list[dict]) -> dict:
     return {"cases": len(cases), "passed": sum(1 for c in cases if c["passed"]),
             "worst_max_abs_error_v": max((c["max_abs_error_v"] for c in cases), default=0.0),
             "total_wall_time_secs": sum(c["wall_time_secs"] for c in cases)}
 
 
-def generate_phase1_benchmark_report(include_extended: bool = False, include_large: bool = False) -> dict:
+def generate_phase1_benchmark_report(include_extended: bool = False, include_large: bool = False, include_partitioned: bool = False) -> dict:
     ngspice = find_ngspice_binary()
     cases = phase1_automated_correctness_cases()
     if include_extended:
@@ -74,6 +96,11 @@ def generate_phase1_benchmark_report(include_extended: bool = False, include_lar
     if include_large:
         cases += large_phase1_correctness_cases()
     rows = [_run_case(c, ngspice) for c in cases]
+    if include_partitioned:
+        by_name = {c.name: c for c in phase1_automated_correctness_cases() + extended_phase1_correctness_cases()}
+        for name, k, mode in (("rc_ladder_400", 4, "in_process"), ("alu2", 4, "in_process"), ("adder8", 4, "in_process"),
+                              ("comparator_adder4", 3, "processes"), ("rc_ladder_50", 3, "processes")):
+            rows.append(_run_partitioned(by_name[name], k, mode))
     tiers = sorted({r["tier"] for r in rows})
     return {"generated": time.strftime("%Y-%m-%d %H:%M:%S"), "platform": f"{platform.system()} {platform.machine()}",
             "oracle_tool": "ngspice" if ngspice else "built-in oracles (ngspice not installed)", "cases": rows,
@@ -106,11 +133,12 @@ def render_markdown_report(report: dict) -> str:
 def main(argv: Optional[list[str]] = None) -> int:
     ap = argparse.ArgumentParser(description="correctness-first benchmark report")
     ap.add_argument("--include-extended", action="store_true")
-    ap.add_argument("--include-large", action="store_true", help="the suite entries of up to 16 000 devices, against the gate-level logic")
+    ap.add_argument("--include-large", action="store_true", help="the suite entries of up to 6 000 transistors, against the gate-level logic")
+    ap.add_argument("--include-partitioned", action="store_true", help="five cases split into partitions (threads and processes) against the single matrix")
     ap.add_argument("--output-json", default="artifacts/phase1_benchmark_report.json")
     ap.add_argument("--output-md", default="artifacts/phase1_benchmark_report.md")
     args = ap.parse_args(argv)
-    report = generate_phase1_benchmark_report(args.include_extended, args.include_large)
+    report = generate_phase1_benchmark_report(args.include_extended, args.include_large, args.include_partitioned)
     for path, text in ((args.output_json, json.dumps(report, indent=2)), (args.output_md, render_markdown_report(report))):
         os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
         Path(path).write_text(text)

@@ -37,10 +37,11 @@ def _net(name: str) -> str:
 
 
 class _Deck:
-    def __init__(self, wn: str, wp: str, length: str, cload: str):
+    def __init__(self, wn: str, wp: str, length: str, cload: str, cint: str = "0.1f"):
         self.lines: list[str] = []
-        self.count = 0
-        self.wn, self.wp, self.length, self.cload = wn, wp, length, cload
+        self.count = 0      # transistors
+        self.internal = 0   # nets inside series stacks
+        self.wn, self.wp, self.length, self.cload, self.cint = wn, wp, length, cload, cint
 
     def mos(self, d: str, g: str, s: str, pmos: bool) -> None:
         self.count += 1
@@ -48,8 +49,14 @@ class _Deck:
         self.lines.append(f"M{self.count} {d} {g} {s} {bulk} {model} w={w} l={self.length}")
 
     def tmp(self) -> str:
-        self.count += 1
-        return f"t{self.count}"
+        """A net between two transistors of a series stack. It gets the diffusion capacitance ``cint``: with none at all
+        its voltage is the quotient of two leakage conductances whenever both neighbours are off, which no comparison of
+        two runs can pin down."""
+        self.internal += 1
+        name = f"t{self.internal}"
+        if self.cint not in ("", "0"):
+            self.lines.append(f"CT{self.internal} {name} 0 {self.cint}")
+        return name
 
     def nand(self, out: str, ins: list[str]) -> None:
         for a in ins:
@@ -112,9 +119,10 @@ class _Deck:
 
 
 def bench_to_spice(bench_text: str, title: str = "synthesised", vdd: float = 1.8, period: float = 2e-9, wn: str = "1u", wp: str = "2u",
-                   length: str = "180n", cload: str = "2f", stimulus: Iterable[str] = ()) -> str:
+                   length: str = "180n", cload: str = "2f", stimulus: Iterable[str] = (), cint: str = "0.1f") -> str:
     """Returns the deck. Primary inputs get pulse sources whose periods double from input to input
-    (a binary counter over the input vector) unless listed in ``stimulus`` lines."""
+    (a binary counter over the input vector) unless listed in ``stimulus`` lines. ``cload`` loads every gate output,
+    ``cint`` every net inside a series stack ("0": none)."""
     inputs: list[str] = []
     outputs: list[str] = []
     gates: list[tuple[str, str, list[str]]] = []
@@ -135,10 +143,10 @@ def bench_to_spice(bench_text: str, title: str = "synthesised", vdd: float = 1.8
             outputs.append(args[0])
             continue
         gates.append((kind, out, args))
-    deck = _Deck(wn, wp, length, cload)
+    deck = _Deck(wn, wp, length, cload, cint)
     for kind, out, args in gates:
         deck.gate(kind, out, args)
-    lines = [f"* {title}: {len(gates)} gates, {deck.count} devices", f"VDD vdd 0 DC {vdd}"]
+    lines = [f"* {title}: {len(gates)} gates, {deck.count} transistors", f"VDD vdd 0 DC {vdd}"]
     given = {s.split()[1].lower() for s in stimulus if len(s.split()) > 1}
     for i, name in enumerate(inputs):
         if name.lower() in given:

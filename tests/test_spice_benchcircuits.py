@@ -262,7 +262,7 @@ def test_partitions_keep_transistor_channels_whole_and_logic_runs_partitioned(tm
 
 
 def test_a_large_suite_entry_settles_to_its_gate_level_outputs():
-    """One of the ``--include-large`` cases end to end (the 27-channel priority encoder, 979 devices)."""
+    """One of the ``--include-large`` cases end to end (the 27-channel priority encoder, 740 transistors)."""
     from nangila_spice import correctness as cx
     from nangila_spice.phase1_report import _run_case
 
