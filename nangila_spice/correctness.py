@@ -300,6 +300,8 @@ def extended_phase1_correctness_cases() -> list:
                     [f"s{i}" for i in range(8)] + ["cout"], tstop=3e-9, dt=0.5e-12),
         _logic_case("mult3", bc.multiplier(3), "3 x 3 multiplier", {**_bits("a", 5, 3), **_bits("b", 6, 3)}, [f"p{i}" for i in range(6)],
                     tstop=3e-9, dt=0.5e-12),
+        _logic_case("mult4", bc.multiplier(4), "4 x 4 multiplier", {**_bits("a", 11, 4), **_bits("b", 13, 4)}, [f"p{i}" for i in range(8)],
+                    tstop=3e-9, dt=0.5e-12),
         _logic_case("priority8", bc.priority(8), "8-channel priority encoder", {**_bits("req", 0b01001101, 8), **_bits("en", 0b00101000, 8)},
                     ["idx0", "idx1", "idx2", "any"], tstop=3e-9, dt=0.5e-12),
         _logic_case("comparator_adder4", bc.comparator_adder(4), "4-bit comparator and adder", {**_bits("a", 0b1011, 4), **_bits("b", 0b1100, 4), "cin": 0},
@@ -307,7 +309,7 @@ def extended_phase1_correctness_cases() -> list:
     ]
 
 
-LARGE_SUITE_ENTRIES = ("c432", "c499", "c880", "c1355", "c1908", "c2670", "c3540", "c5315", "c7552",
+LARGE_SUITE_ENTRIES = ("c432", "c499", "c880", "c1355", "c1908", "c2670", "c3540", "c5315", "c6288", "c7552",
                        "s382", "s420", "s641", "s713", "s1238", "s1423", "s1488")
 
 
@@ -342,11 +344,7 @@ def blocked_official_correctness_cases() -> list:
 
     why = ("tens to hundreds of thousands of devices: minutes per run with its half-step oracle; these belong to the scaling study "
            "(nangila_spice.benchmark), not to a correctness report")
-    glitch = ("all eight inputs switch at once and the middle product bits carry runt pulses whose height moves by 50 mV between 0.25 ps "
-              "and 0.125 ps steps: a study of glitch sensitivity, not a check of the solver")
-    glitch16 = ("the 16 x 16 multiplier (11 872 transistors) runs and all 32 product bits settle to the right levels, but like mult4 its product "
-                "bits carry runt pulses that differ by 50-90 mV between 0.5 ps and 0.25 ps steps")
-    return [BlockedCorrectnessCase("mult4", glitch), BlockedCorrectnessCase("c6288", glitch16)] + [BlockedCorrectnessCase(name, why) for name in bc.SUITE if name not in ("c17", "s27", "c6288") and name not in LARGE_SUITE_ENTRIES]
+    return [BlockedCorrectnessCase(name, why) for name in bc.SUITE if name not in ("c17", "s27") and name not in LARGE_SUITE_ENTRIES]
 
 
 def _is_ground(node: str) -> bool:

@@ -198,9 +198,9 @@ def test_correctness_registry_and_logic_oracle(tmp_path):
     assert {c.tier for c in official} == {"passive", "nonlinear", "logic"}
     assert len(cx.extended_phase1_correctness_cases()) >= 4
     blocked = cx.blocked_official_correctness_cases()
-    assert {"c6288", "s38417", "mult4"} <= {b.name for b in blocked} and all(b.reason for b in blocked)
+    assert {"s5378", "s38417"} <= {b.name for b in blocked} and all(b.reason for b in blocked)
     large = cx.large_phase1_correctness_cases()
-    assert len(large) == 16 and {c.tier for c in large} == {"large"} and not {c.name for c in large} & {b.name for b in blocked}
+    assert len(large) == 17 and {c.tier for c in large} == {"large"} and not {c.name for c in large} & {b.name for b in blocked}
     assert all(1 <= len(c.expected_levels) <= 16 for c in large)
     assert [c.deck for c in cx.large_phase1_correctness_cases()] == [c.deck for c in large]   # the random vectors are seeded
     case = next(c for c in official if c.name == "priority4")
