@@ -27,7 +27,7 @@ static py::dict stats_dict(const SimStats& s) {
     py::dict d;
     d["total_steps"] = s.total_steps; d["wall_time_secs"] = s.wall_time_secs; d["prediction_hits"] = s.prediction_hits;
     d["prediction_misses"] = s.prediction_misses; d["rollbacks"] = s.rollbacks; d["completed"] = s.completed;
-    d["hit_rate"] = s.hit_rate();
+    d["hit_rate"] = s.hit_rate(); d["solver_steps"] = s.solver_steps; d["rejected_steps"] = s.rejected_steps;
     return d;
 }
 
@@ -70,13 +70,14 @@ PYBIND11_MODULE(_native, m) {
     // ---- simulation ---------------------------------------------------------------------------
     m.def("simulate", [](const std::string& netlist_json, double tstop, double dt, double reltol, const std::string& solver, uint32_t record_every,
                          uint32_t predict_depth, std::vector<std::tuple<uint32_t, double, std::vector<std::pair<uint64_t, double>>>> inject,
-                         std::vector<double> rollbacks) {
+                         std::vector<double> rollbacks, bool adaptive, double lte_reltol, double max_step_factor) {
         Netlist nl = Netlist::from_json(Json::parse(netlist_json));
         std::vector<std::string> names = nl.names_or_default();
         GhostBuffer ghosts(predict_depth);
         for (auto& g : nl.ghost_map) ghosts.add(GhostNode(g.net_id, g.owner));
         SimConfig cfg;
         cfg.tstop = tstop; cfg.dt = dt; cfg.reltol = reltol; cfg.record_every = std::max(1u, record_every); cfg.predict_depth = predict_depth;
+        cfg.adaptive = adaptive; cfg.lte_reltol = lte_reltol; cfg.max_step_factor = max_step_factor;
         CommLayer comm(0, 1);
         for (auto& msg : inject) { ResidualMessage r; r.from = std::get<0>(msg); r.time = std::get<1>(msg); r.updates = std::get<2>(msg); comm.inject_message(r); }
         for (double t : rollbacks) comm.inject_rollback({1, t});
@@ -107,7 +108,7 @@ PYBIND11_MODULE(_native, m) {
         return out;
     }, py::arg("netlist_json"), py::arg("tstop"), py::arg("dt"), py::arg("reltol") = 1e-3, py::arg("solver") = "lu", py::arg("record_every") = 1,
        py::arg("predict_depth") = 5, py::arg("inject") = std::vector<std::tuple<uint32_t, double, std::vector<std::pair<uint64_t, double>>>>{},
-       py::arg("rollbacks") = std::vector<double>{});
+       py::arg("rollbacks") = std::vector<double>{}, py::arg("adaptive") = false, py::arg("lte_reltol") = 2e-2, py::arg("max_step_factor") = 64.0);
 
     m.def("dc_operating_point", [](const std::string& netlist_json) {
         SolverEngine e(Netlist::from_json(Json::parse(netlist_json)));

@@ -9,6 +9,7 @@
 #pragma once
 #include <algorithm>
 #include <cmath>
+#include <limits>
 #include <cstdint>
 #include <string>
 #include <tuple>
@@ -48,6 +49,19 @@ struct SourceWaveform {
                 if (c > t0 && c <= t1) return true;
             }
         return false;
+    }
+    // The first corner strictly after t (infinity for a DC source).
+    double next_corner_after(double t) const {
+        if (kind != Pulse || per <= 0.0) return std::numeric_limits<double>::infinity();
+        const double offs[4] = {0.0, tr, tr + pw, tr + pw + tf};
+        const double eps = 1e-9 * per;
+        double base = td + std::floor(std::max(0.0, t - td) / per) * per;
+        for (int cyc = 0; cyc < 3; ++cyc)
+            for (double o : offs) {
+                double c = base + cyc * per + o;
+                if (c > t + eps) return c;
+            }
+        return std::numeric_limits<double>::infinity();
     }
     Json to_json() const {
         Json j = Json::object();

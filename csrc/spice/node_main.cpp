@@ -3,7 +3,7 @@
 //   nangila-node --partition deck.sp|part.json [--node-id N] [-k TOTAL] [--predict-depth D]
 //                [--reltol R] [--tstop T] [--dt DT] [--process TT|FF|SS|FS|SF] [--vdd V] [--temp C]
 //                [--waveform-json out.json] [--waveform-nz out.nz] [--solver lu|dense|krylov|cuda]
-//                [--record-every K] [--demo]
+//                [--record-every K] [--adaptive] [--demo]
 //                [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T]]
 //
 // With --rendezvous and -k > 1 the process is one of TOTAL that advance in lockstep and exchange boundary voltages
@@ -34,7 +34,7 @@ struct Args {
     int connect_timeout_ms = 30000, io_timeout_ms = 30000;
     uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1, threads = 1;
     double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
-    bool demo = false, bench = false, lockstep = false;
+    bool demo = false, bench = false, lockstep = false, adaptive = false;
 };
 
 static void usage() {
@@ -42,7 +42,7 @@ static void usage() {
                  "usage: nangila-node [--partition FILE | --demo] [--node-id N] [-k TOTAL] [--predict-depth D]\n"
                  "                    [--reltol R] [--tstop T] [--dt DT] [--process P] [--vdd V] [--temp C]\n"
                  "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov|cuda]\n"
-                 "                    [--record-every K] [--partitions A.json,B.json,... [--threads T]] [--bench]\n"
+                 "                    [--record-every K] [--adaptive] [--partitions A.json,B.json,... [--threads T]] [--bench]\n"
                  "                    [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T] [--lockstep]]\n");
 }
 
@@ -57,6 +57,7 @@ static bool parse_args(int argc, char** argv, Args& a) {
         if (f == "--demo") a.demo = true;
         else if (f == "--bench") a.bench = true;
         else if (f == "--lockstep") a.lockstep = true;
+        else if (f == "--adaptive") a.adaptive = true;
         else if (f == "--partitions") { if (!(v = need("--partitions"))) return false; a.partitions = v; }
         else if (f == "-h" || f == "--help") { usage(); std::exit(0); }
         else if (f == "--partition" || f == "-p") { if (!(v = need("--partition"))) return false; a.partition = v; }
@@ -268,6 +269,7 @@ static int run(int argc, char** argv) {
     for (auto& g : nl.ghost_map) ghosts.add(GhostNode(g.net_id, g.owner));
     SimConfig cfg;
     cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
+    cfg.adaptive = a.adaptive;   // variable internal step, waveform still on the dt grid (single partition only)
     std::vector<std::string> names = nl.names_or_default();
     std::string name = nl.name;
     TransientSolver solver(std::move(nl), std::move(ghosts), CommLayer(a.node_id, a.total), cfg);

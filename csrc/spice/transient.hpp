@@ -5,6 +5,7 @@
 #include <chrono>
 #include <deque>
 #include <functional>
+#include <limits>
 #include <memory>
 
 #include "comm.hpp"
@@ -19,10 +20,18 @@ struct SimConfig {
     size_t max_history = 100;
     // Optional cap on stored waveform points: keep every k-th step (1 = all).
     uint32_t record_every = 1;
+    // Variable internal step (single-partition runs): the waveform is still written on the dt grid, but the solver
+    // takes the steps the signals allow, between dt / 64 and max_step_factor * dt, lands on the corners of the sources,
+    // and bounds how far a solution may depart from the straight line through the two before it (lte_reltol of the
+    // larger of the values involved plus lte_abstol volts). That departure is far larger than the error of the
+    // trapezoidal step itself: at 2 % the observed outputs of the logic cases stay within 3 mV of a run at a quarter of dt.
+    bool adaptive = false;
+    double lte_reltol = 2e-2, lte_abstol = 1e-4, max_step_factor = 64.0;
 };
 
 struct SimStats {
     uint64_t total_steps = 0, prediction_hits = 0, prediction_misses = 0, rollbacks = 0;
+    uint64_t solver_steps = 0, rejected_steps = 0;  // adaptive mode: internal steps accepted / thrown away
     double wall_time_secs = 0.0;
     bool completed = false;
     double hit_rate() const {
@@ -51,6 +60,7 @@ public:
     std::function<void(const PartitionState&)> on_step;
 
     PartitionState run() {
+        if (config.adaptive && ghosts.size() == 0) return run_adaptive();
         auto t0 = std::chrono::steady_clock::now();
         PartitionState state = engine_->initial_state();
         waveform.clear();
@@ -92,6 +102,84 @@ public:
         }
         stats.total_steps = step;
         stats.completed = step == planned;
+        stats.wall_time_secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        return state;
+    }
+
+    // Variable-step form of run(): same waveform grid, the solver chooses its own steps in between.
+    PartitionState run_adaptive() {
+        auto t0 = std::chrono::steady_clock::now();
+        PartitionState state = engine_->initial_state(), older{0};
+        waveform.clear();
+        waveform.push_back({state.time, state.voltages});
+        stats = SimStats{};
+        const double dt = config.dt, tstop = config.tstop;
+        const uint64_t planned = dt > 0 ? uint64_t(std::ceil(tstop / dt - 1e-9)) : 0;
+        const double hmin = dt / 64.0, hmax = dt * config.max_step_factor;
+        const int nodes = engine_->netlist.num_nodes;
+        double t = 0.0, h = dt, h_older = 0.0;
+        uint64_t emitted = 0;   // grid points written so far (beyond t = 0)
+        bool have_older = false, failed = false;
+        auto next_corner = [&](double now) {
+            double c = std::numeric_limits<double>::infinity();
+            for (auto& e : engine_->netlist.elements)
+                if (e.kind == Element::VSource || e.kind == Element::ISource) c = std::min(c, e.source.next_corner_after(now));
+            return c;
+        };
+        const std::vector<std::pair<uint64_t, double>> no_pins;
+        while (emitted < planned && !failed) {
+            const double t_end = double(planned) * dt;
+            double step = std::min(h, t_end - t);
+            const double corner = next_corner(t);
+            bool lands_on_corner = false;
+            if (t + step > corner - 1e-6 * dt) { step = corner - t; lands_on_corner = true; }
+            if (step <= 0.0) step = hmin;
+            PartitionState next{0};
+            if (!engine_->solve_step(state, no_pins, step, next)) {
+                if (step <= hmin * 1.0001) { failed = true; break; }
+                h = std::max(hmin, 0.25 * step);
+                ++stats.rejected_steps;
+                continue;
+            }
+            double err = 0.0;
+            if (have_older && h_older > 0.0) {
+                const double ratio = step / h_older;
+                for (int i = 0; i < nodes; ++i) {
+                    const double now = state.voltages[size_t(i)], was = older.voltages[size_t(i)], got = next.voltages[size_t(i)];
+                    const double line = now + (now - was) * ratio;
+                    const double tol = config.lte_reltol * std::max({std::fabs(got), std::fabs(now), std::fabs(line)}) + config.lte_abstol;
+                    err = std::max(err, std::fabs(got - line) / tol);
+                }
+                if (err > 1.0 && step > hmin * 1.0001) {
+                    h = std::max(hmin, step * std::max(0.25, 0.9 / std::sqrt(err)));
+                    ++stats.rejected_steps;
+                    continue;
+                }
+            }
+            // accepted: write the grid points this step covers (linear between its two ends)
+            const double t_new = t + step;
+            while (emitted < planned && double(emitted + 1) * dt <= t_new + 1e-9 * dt) {
+                const double tg = double(emitted + 1) * dt, w = step > 0.0 ? std::min(1.0, std::max(0.0, (tg - t) / step)) : 1.0;
+                ++emitted;
+                if (emitted % config.record_every == 0 || emitted == planned) {
+                    std::vector<double> v(next.voltages.size());
+                    for (size_t i = 0; i < v.size(); ++i) v[i] = state.voltages[i] + w * (next.voltages[i] - state.voltages[i]);
+                    waveform.push_back({tg, std::move(v)});
+                }
+            }
+            ++stats.solver_steps;
+            older = std::move(state);
+            h_older = step;
+            have_older = !lands_on_corner;   // the slope of a source changes at a corner: the straight line through it says nothing
+            state = std::move(next);
+            state.time = t_new;
+            t = t_new;
+            if (on_step) on_step(state);
+            const double grow = have_older ? std::min(2.0, 0.9 / std::sqrt(std::max(err, 0.05))) : 1.0;
+            h = lands_on_corner ? std::min(dt, step) : std::min(hmax, std::max(hmin, step * std::max(grow, 0.5)));
+        }
+        stats.total_steps = emitted;
+        stats.completed = !failed && emitted == planned;
         stats.wall_time_secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
         return state;
     }

@@ -32,7 +32,7 @@ def invoke_run(args) -> int:
                                              tstop=args.tstop, dt=args.dt, predict_depth=args.predict_depth, output_dir=args.output_dir,
                                              output_format=args.output_format,
                                              validate_partitioned_against_reference=not args.skip_reference_validation,
-                                             reference_vdd=args.vdd, vdd=args.vdd, verbose=args.verbose, mode=args.mode))
+                                             reference_vdd=args.vdd, vdd=args.vdd, verbose=args.verbose, mode=args.mode, adaptive=args.adaptive))
     print(result.summary())
     return 0 if result.success else 1
 
@@ -114,6 +114,7 @@ def main(argv=None) -> int:
     r.add_argument("--output-format", choices=("csv", "json"), default="csv")
     r.add_argument("--vdd", type=float, default=1.8)
     r.add_argument("--mode", choices=("auto", "in_process", "processes"), default="auto")
+    r.add_argument("--adaptive", action="store_true", help="single-partition runs: the solver chooses its own steps between the points of the --dt grid")
     r.add_argument("--verbose", action="store_true")
     r.add_argument("--skip-reference-validation", action="store_true")
     s = sub.add_parser("synth", help="translate an ISCAS .bench gate list into a transistor-level deck")

@@ -122,15 +122,16 @@ def find_ngspice_binary() -> Optional[str]:
 
 def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: float = 1e-3, process: str = "TT", vdd: float = 1.8,
                          temp: float = 27.0, solver: str = "lu", binary: Optional[str] = None, in_process: bool = False,
-                         record_every: int = 1, allow_partial: bool = False) -> WaveformData:
+                         record_every: int = 1, allow_partial: bool = False, adaptive: bool = False) -> WaveformData:
     """Runs this simulator on a deck: through the ``nangila-node`` process (default) or in-process. A run that
-    stops before ``tstop`` (Newton did not converge even after step cutting) raises unless ``allow_partial``."""
+    stops before ``tstop`` (Newton did not converge even after step cutting) raises unless ``allow_partial``.
+    ``adaptive``: the solver chooses its own steps between the points of the ``dt`` grid the waveform is written on."""
     if in_process:
         from . import _native
 
         text = Path(netlist_path).read_text()
         js, _ = _native.parse_spice(text, Path(netlist_path).name, process, vdd, temp)
-        r = _native.simulate(js, tstop, dt, reltol, solver, record_every)
+        r = _native.simulate(js, tstop, dt, reltol, solver, record_every, adaptive=adaptive)
         if not r["stats"]["completed"] and not allow_partial:
             raise RuntimeError(f"{netlist_path}: stopped at t = {r['time'][-1]:.4g} s of {tstop:.4g} s: Newton did not converge")
         vals = np.asarray(r["values"], float)
@@ -143,6 +144,8 @@ def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: 
         out = os.path.join(tmp, "wave.json")
         cmd = [exe, "--partition", netlist_path, "--tstop", repr(tstop), "--dt", repr(dt), "--reltol", repr(reltol), "--process", process,
                "--vdd", repr(vdd), "--temp", repr(temp), "--solver", solver, "--record-every", str(record_every), "--waveform-json", out]
+        if adaptive:
+            cmd.append("--adaptive")
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode == 3 and not allow_partial:
             raise RuntimeError(f"{netlist_path}: stopped before tstop: {proc.stderr[-300:]}")

@@ -60,6 +60,7 @@ class SimulationConfig:
     prefer_single_node_fallback_for_partitioned: bool = False
     verbose: bool = False
     mode: str = "auto"  # 'auto' | 'in_process' | 'processes' (one nangila-node per partition, boundary values over TCP)
+    adaptive: bool = False  # single-matrix runs: variable internal step, waveform still on the dt grid
     speculate: bool = True  # partitions run windows of steps ahead on predictions between exchanges (False: one step per exchange)
     io_timeout_secs: float = 30.0  # processes mode: how long a process waits for a peer before it gives up
     process: str = "TT"
@@ -145,14 +146,15 @@ def _log(config: SimulationConfig, msg: str) -> None:
         print(f"[nangila] {msg}")
 
 
-def _single_run(config: SimulationConfig, flat: dict) -> tuple[Waveform, dict]:
+def _single_run(config: SimulationConfig, flat: dict, adaptive: bool = False) -> tuple[Waveform, dict]:
     from . import _native
 
     if config.solver == "cuda":
         from .gpu import enable_device_solver
 
         enable_device_solver()
-    r = _native.simulate(json.dumps(flat), config.tstop, config.dt, config.reltol, config.solver, config.record_every, config.predict_depth)
+    r = _native.simulate(json.dumps(flat), config.tstop, config.dt, config.reltol, config.solver, config.record_every, config.predict_depth,
+                         adaptive=adaptive)
     return Waveform.from_native(r, title=flat.get("name", "")), {"stats": r["stats"], "newton": r["newton"]}
 
 
@@ -218,7 +220,7 @@ def run_simulation(config: SimulationConfig) -> SimulationResult:
     result.warnings = warnings
     try:
         if k == 1 or config.prefer_single_node_fallback_for_partitioned:
-            result.waveform, result.solver_stats = _single_run(config, flat)
+            result.waveform, result.solver_stats = _single_run(config, flat, adaptive=config.adaptive)
             result.validation_status = "validated_single_node" if k == 1 else "single_node_fallback"
             if k > 1:
                 result.warnings.append("partitioned request served by the single-matrix solver (prefer_single_node_fallback_for_partitioned)")

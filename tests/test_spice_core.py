@@ -482,3 +482,44 @@ def test_type_stub_lists_every_public_name():
     assert public <= declared, sorted(public - declared)
     classes = {n.name: {m.name for m in n.body if isinstance(m, ast.FunctionDef)} for n in tree.body if isinstance(n, ast.ClassDef)}
     assert {"solve", "stats"} <= classes["FactoredLU"] and {"solve", "stats"} <= classes["PvtDeltaSolver"]
+
+
+def test_adaptive_steps_keep_the_grid_and_the_accuracy():
+    # RC step against its closed form: same accuracy as the fixed step, a fraction of the solves
+    rc = "* rc\nV1 vdd 0 DC 1.8\nR1 vdd out 1k\nC1 out 0 10f\n.ic V(out)=0\n.end\n"
+    js, _ = N.parse_spice(rc)
+    fixed = N.simulate(js, 200e-12, 0.25e-12)
+    adapt = N.simulate(js, 200e-12, 0.25e-12, adaptive=True)
+    t = np.asarray(adapt["time"])
+    assert np.array_equal(t, np.asarray(fixed["time"])) and adapt["stats"]["completed"]
+    exact = 1.8 * (1.0 - np.exp(-t / 10e-12))
+    out = adapt["node_names"].index("out")
+    assert np.abs(np.asarray(adapt["values"])[:, out] - exact).max() < 2e-3
+    assert adapt["stats"]["solver_steps"] < fixed["stats"]["total_steps"] / 4
+    # a pulse train: every corner of the source is a step boundary, so no edge is smeared over a long step
+    deck = "* pulse into RC\nV1 in 0 PULSE(0 1.8 1n 20p 20p 2n 6n)\nR1 in out 1k\nC1 out 0 20f\n.end\n"
+    js, _ = N.parse_spice(deck)
+    fixed = N.simulate(js, 20e-9, 5e-12)
+    adapt = N.simulate(js, 20e-9, 5e-12, adaptive=True)
+    vf, va = np.asarray(fixed["values"]), np.asarray(adapt["values"])
+    assert np.abs(vf - va).max() < 5e-3
+    assert adapt["stats"]["solver_steps"] < fixed["stats"]["total_steps"] / 5 and adapt["stats"]["total_steps"] == 4000
+
+
+def test_adaptive_steps_on_logic_with_long_idle_periods():
+    from nangila_spice import benchcircuits as bc
+    from nangila_spice.synth import bench_to_spice
+
+    # a 2-bit adder whose inputs toggle every few nanoseconds: almost all of the run is quiet
+    deck = bench_to_spice(bc.adder(2), "adder2", cload="20f", period=8e-9)
+    js, _ = N.parse_spice(deck)
+    names = json.loads(js)["node_names"]
+    fixed = N.simulate(js, 40e-9, 2e-12)
+    adapt = N.simulate(js, 40e-9, 2e-12, adaptive=True)
+    assert adapt["stats"]["completed"] and adapt["stats"]["solver_steps"] < fixed["stats"]["total_steps"] / 2
+    obs = [names.index(n) for n in ("ns0", "ns1", "ncout")]
+    vf, va = np.asarray(fixed["values"])[:, obs], np.asarray(adapt["values"])[:, obs]
+    # same logic levels at every sample away from the edges, and edges within a couple of grid points of each other
+    settled = np.abs(vf - 0.9) > 0.8
+    assert np.abs(vf - va)[settled].max() < 0.05
+    assert np.mean(np.abs(vf - va) > 0.2) < 0.01
