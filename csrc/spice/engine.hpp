@@ -25,6 +25,7 @@ enum class Integration { BackwardEuler, Trapezoidal };
 struct PartitionState {
     std::vector<double> voltages;      // full solution vector (nodes, then branch currents)
     std::vector<double> cap_currents;  // one per capacitor, in element order; empty before the first step
+    std::vector<double> slopes;        // d/dt of every unknown over the step that led here; empty before the first step
     double time = 0.0;
     bool validated = false;
     explicit PartitionState(size_t n = 0) : voltages(n, 0.0) {}
@@ -361,6 +362,7 @@ public:
     }
 
     uint64_t be_fallbacks = 0, step_cuts = 0, dc_gmin_stepping = 0;
+    bool extrapolate_guess = true;
 
 private:
     Assembler asm_;
@@ -401,6 +403,10 @@ private:
         out = PartitionState{0};
         out.voltages = std::move(r.x);
         out.time = cur.time + dt;
+        if (dt > 0.0 && out.voltages.size() == cur.voltages.size()) {
+            out.slopes.resize(out.voltages.size());
+            for (size_t i = 0; i < out.slopes.size(); ++i) out.slopes[i] = (out.voltages[i] - cur.voltages[i]) / dt;
+        }
         auto V = [](const std::vector<double>& v, int node) { return (node > 0 && size_t(node - 1) < v.size()) ? v[size_t(node - 1)] : 0.0; };
         size_t cap = 0;
         for (auto& e : netlist.elements) {
@@ -418,7 +424,11 @@ private:
                          Integration method) {
         asm_.stamp_linear(cur.voltages, cur.cap_currents, dt, t, method, pins);
         const bool nonlinear = asm_.has_nonlinear();
+        // Newton starts from the straight line through the last step (nonlinear transient steps only: a linear system
+        // needs no guess, and the DC solve has no time)
         std::vector<double> guess = cur.voltages;
+        if (nonlinear && extrapolate_guess && dt > 0.0 && cur.slopes.size() == guess.size())
+            for (int i = 0; i < asm_.num_nodes; ++i) guess[size_t(i)] += cur.slopes[size_t(i)] * dt;
         return newton.solve(std::move(guess), asm_.m, [&](const std::vector<double>& x, CsrMatrix&) {
             if (nonlinear) asm_.stamp_nonlinear(x);
         }, nonlinear ? asm_.num_nodes : 0, !nonlinear);
