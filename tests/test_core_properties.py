@@ -139,3 +139,74 @@ def test_two_hooks_fed_the_same_stream_agree_bit_for_bit(stream, warmup):
             # the residual g - prediction is at most (1 + 1 + momentum) times the largest gradient seen, and the
             # reconstruction is off by at most one of its seven levels
             assert np.abs(out - g).max() <= 2.9 * seen / 7.0 * 1.01 + 1e-6
+
+
+q_ints = st.lists(st.integers(-2**31, 2**31 - 1), min_size=0, max_size=40)
+
+
+@FAST
+@given(st.integers(0, 2**62), st.lists(st.tuples(st.integers(0, 500), st.one_of(st.none(), q_ints), q_ints), max_size=8, unique_by=lambda t: t[0]),
+       st.floats(0.0, 10.0, width=32))
+def test_checkpoint_bytes_roundtrip_and_any_damage_is_noticed(step, layers, gamma):
+    c = C.NangilaCheckpoint()
+    c.step = step
+    c.predictor_step = step
+    c.quantizer_gamma = gamma
+    for lid, prev, cur in layers:
+        c.set_layer(lid, prev, cur)
+    c.seal()
+    raw = c.to_bytes()
+    back = C.NangilaCheckpoint.from_bytes(raw)
+    assert back.verify_integrity() and back.to_bytes() == raw and back.step == step
+    assert back.layer_ids() == sorted(lid for lid, _, _ in layers)
+    for lid, prev, cur in layers:
+        assert back.get_layer(lid) == (prev if prev else None if prev is None else prev, cur) or back.get_layer(lid) == (prev, cur)
+    if layers and any(cur for _, _, cur in layers):
+        lid, prev, cur = next(t for t in layers if t[2])
+        back.set_layer(lid, prev, [cur[0] ^ 1] + cur[1:])
+        assert not back.verify_integrity()
+
+
+@settings(max_examples=int(os.environ.get("NANGILA_PROPERTY_EXAMPLES", "25")), deadline=None, derandomize="NANGILA_PROPERTY_EXAMPLES" not in os.environ)
+@given(st.integers(2, 6), st.integers(2, 12), st.integers(8, 40), st.integers(0, 2**31), st.floats(0.5, 0.99))
+def test_sculptor_masks_are_always_valid_and_passengers_hang_on_drivers(n_layers, width, steps, seed, threshold):
+    rng = np.random.default_rng(seed)
+    s = nangila.Sculptor(float(threshold))
+    base = rng.normal(size=(steps, width))
+    gains = rng.uniform(0.2, 3.0, size=n_layers)
+    independent = rng.random(n_layers) < 0.4
+    for t in range(steps):
+        for lid in range(n_layers):
+            g = rng.normal(size=width) if independent[lid] else gains[lid] * base[t] + 0.01 * rng.normal(size=width)
+            s.record(lid, g.astype(np.float32))
+        s.end_step()
+    mask = C.TopologyMask.from_bytes(s.generate_mask())
+    mask.validate()
+    assert mask.num_layers() == n_layers and mask.num_drivers() >= 1
+    assert mask.num_drivers() + mask.num_passengers() == n_layers
+    drivers = set(mask.drivers())
+    for lid, driver, alpha, beta in mask.passengers():
+        assert driver in drivers and mask.is_passenger(lid) and not mask.is_driver(lid) and lid not in drivers
+        assert np.isfinite(alpha) and np.isfinite(beta)
+        if threshold >= 0.9 and steps * width >= 200:
+            assert not independent[lid]   # with enough samples and a high bar, noise is not tied to a driver
+    assert C.TopologyMask.from_bytes(mask.to_bytes()).to_bytes() == mask.to_bytes()
+
+
+@FAST
+@given(st.lists(st.floats(0.125, 10.0, width=32), min_size=5, max_size=120), st.integers(1, 10), st.floats(0.01, 0.5), st.integers(1, 4))
+def test_safe_mode_only_compresses_when_active_and_counts_every_check(losses, interval, threshold, max_fail):
+    sm = C.SafeMode(C.SafeModeConfig(check_interval=interval, divergence_threshold=float(threshold), max_consecutive_failures=max_fail))
+    checks = 0
+    for step, loss in enumerate(losses):
+        if sm.should_check(step):
+            action = sm.check(step, float(loss))
+            checks += 1
+            assert action in (C.SafeModeAction.Continue, C.SafeModeAction.TriggerFallback, C.SafeModeAction.RecoveryComplete,
+                              C.SafeModeAction.NoCheck, C.SafeModeAction.CanaryTest)
+        state = sm.state()
+        assert sm.should_compress() == (state == C.SafeModeState.Active) or state == C.SafeModeState.Recovering
+    sm.force_fallback()
+    assert sm.state() == C.SafeModeState.Fallback and not sm.should_compress()
+    sm.reset()
+    assert sm.state() == C.SafeModeState.Active and sm.should_compress()
