@@ -81,6 +81,7 @@ private:
 
 struct PartitionedConfig {
     unsigned threads = 1;  // worker threads for the per-partition solves (1 = all on the calling thread)
+    size_t min_unknowns_per_thread = 400;  // smaller partitions are solved on the calling thread whatever `threads` says
     double tstop = 1e-9, dt = 1e-12, reltol = 1e-3, abstol = 1e-6;
     uint32_t predict_depth = 5;
     int max_sweeps = 50;
@@ -108,7 +109,7 @@ public:
     std::vector<WaveformPoint> waveform;       // merged, values in `names` order
 
     PartitionedRunner(std::vector<Netlist> parts, PartitionedConfig cfg)
-        : cfg_(cfg), depth_(cfg.predict_depth, 1, cfg.predict_depth * 3), pool_(std::min<unsigned>(std::max(1u, cfg.threads), unsigned(parts.size()))) {
+        : cfg_(cfg), depth_(cfg.predict_depth, 1, cfg.predict_depth * 3), pool_(worker_count(cfg, parts)) {
         const uint32_t k = uint32_t(parts.size());
         FabricConfig fc;
         fc.compress = cfg.compress;
@@ -232,6 +233,15 @@ public:
     }
 
 private:
+    // Threads pay for themselves only when a sweep is real work: below min_unknowns_per_thread unknowns per partition the
+    // hand-over between threads (and, on a busy machine, waiting to be scheduled) costs more than the solves.
+    static unsigned worker_count(const PartitionedConfig& cfg, const std::vector<Netlist>& parts) {
+        size_t largest = 0;
+        for (auto& p : parts) largest = std::max(largest, size_t(std::max(p.num_nodes, 0)));
+        if (largest < cfg.min_unknowns_per_thread) return 1;
+        return std::min<unsigned>(std::max(1u, cfg.threads), unsigned(parts.size()));
+    }
+
     struct Part {
         std::unique_ptr<SolverEngine> engine;
         GhostBuffer ghosts;
