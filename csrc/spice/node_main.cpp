@@ -159,6 +159,7 @@ static int run_partitioned(const Args& a) {
         PartitionedConfig cfg;
         cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
         cfg.threads = a.threads;
+        if (a.threads > 1) cfg.min_unknowns_per_thread = 0;   // --threads was asked for: take it literally
         cfg.speculate = !a.lockstep;
         PartitionedRunner runner(std::move(parts), cfg);
         runner.run();
