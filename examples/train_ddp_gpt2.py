@@ -35,6 +35,8 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--checkpoint", default="")
     ap.add_argument("--save-every", type=int, default=50)
+    ap.add_argument("--liveness-timeout", type=float, default=0.0,
+                    help="seconds of silence after which a peer counts as gone (0: no heartbeats); the run then stops with its name")
     args = ap.parse_args()
     rank, world, dev = init_distributed()
     seed_everything(0)
@@ -44,7 +46,8 @@ def main() -> int:
         model = model.to(torch.bfloat16)
     ddp = DDP(model, device_ids=[dev.index] if dev.type == "cuda" else None, bucket_cap_mb=25)
     hook = register_nangila_hook(ddp, threshold=0.95, warmup_steps=args.warmup_steps,
-                                 compressor_type=int(COMPRESSORS[args.compressor]), dgc_sparsity=0.999, power_sgd_rank=4)
+                                 compressor_type=int(COMPRESSORS[args.compressor]), dgc_sparsity=0.999, power_sgd_rank=4,
+                                 liveness_timeout=args.liveness_timeout or None)
     hook.enable_safe_mode()  # falls back to exact averaging if the validation loss diverges
     opt = torch.optim.AdamW(ddp.parameters(), lr=3e-4, weight_decay=0.01)
     start = 0
@@ -59,11 +62,15 @@ def main() -> int:
     seq = min(cfg.n_ctx, 1024)
     for step in range(start, args.steps):
         tok = torch.randint(0, cfg.vocab_size, (args.micro_batch, seq + 1), generator=gen).to(dev)
-        loss = ddp(tok[:, :-1], tok[:, 1:])
-        loss.backward()
-        opt.step()
-        opt.zero_grad(set_to_none=True)
-        hook.step()
+        try:
+            loss = ddp(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            hook.step()   # with heartbeats on, raises RankFailure when a peer has left
+        except RuntimeError:
+            hook.check_peers(wait=2.0 * args.liveness_timeout)   # a failed collective: say which rank it was, if one is gone
+            raise
         if step % 10 == 0:
             hook.report_validation_loss(float(loss))
             if rank == 0:
