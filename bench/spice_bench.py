@@ -86,7 +86,7 @@ def process_rows() -> None:
 def pvt_rows() -> None:
     from nangila_spice.pvt_orchestrator import PvtOrchestrator, SweepConfig, generate_1000_corner_grid
 
-    case = next(c for c in cx.official_correctness_cases() if c.name == "alu2")
+    case = next(c for c in cx.extended_phase1_correctness_cases() if c.name == "alu2")
     with tempfile.TemporaryDirectory() as tmp:
         path = case.materialize(tmp)
         res = PvtOrchestrator(SweepConfig(tstop=1e-9, dt=1e-12, output_dir=tmp)).run_sweep(generate_1000_corner_grid(), path)

@@ -19,19 +19,40 @@ class WaveformPoint:
     voltages: dict[str, float] = field(default_factory=dict)
 
 
-@dataclass
 class PartitionWaveform:
     """What one solver node wrote: its nets on its own time axis; ghost nets are listed so the merge
-    can drop them in favour of their owner's copy."""
-    partition_id: int
-    times: list[float]
-    traces: dict[str, list[float]]
-    ghost_nodes: set[str] = field(default_factory=set)
+    can drop them in favour of their owner's copy. The reference's keyword forms are accepted as well:
+    ``voltages=`` for ``traces=`` and ``node_mapping=`` (local name -> global name, applied to the traces)."""
+
+    def __init__(self, partition_id: int, times: Iterable[float] = (), traces: Optional[dict] = None, ghost_nodes: Optional[set] = None, *,
+                 voltages: Optional[dict] = None, node_mapping: Optional[dict] = None):
+        if isinstance(times, dict) and traces is not None and not isinstance(traces, dict):
+            times, traces = traces, times   # reference order: (partition_id, node_mapping, times, voltages) passed positionally
+        data = traces if traces is not None else (voltages or {})
+        if node_mapping:
+            data = {node_mapping.get(name, name): values for name, values in data.items()}
+        self.partition_id = partition_id
+        self.times = times
+        self.traces = data
+        self.ghost_nodes = set(ghost_nodes or ())
+        self.node_mapping = dict(node_mapping or {})
+
+    @property
+    def voltages(self) -> dict:
+        return self.traces
 
 
 class Waveform:
-    def __init__(self, times: Iterable[float] = (), traces: Optional[dict[str, Iterable[float]]] = None, title: str = ""):
+    """Columnar waveform: ``times`` and one array per net in ``traces``. Also constructible the reference's way, from
+    ``points=[WaveformPoint(time, voltages={...}), ...]`` (with ``node_names=`` fixing the order of the nets)."""
+
+    def __init__(self, times: Iterable[float] = (), traces: Optional[dict[str, Iterable[float]]] = None, title: str = "", *,
+                 node_names: Optional[list] = None, points: Optional[list] = None):
         self.title = title
+        if points is not None:
+            names = list(node_names) if node_names is not None else list(dict.fromkeys(n for p in points for n in p.voltages))
+            times = [p.time for p in points]
+            traces = {n: [p.voltages.get(n, 0.0) for p in points] for n in names}
         as_array = lambda x: np.ascontiguousarray(x if isinstance(x, np.ndarray) else list(x), dtype=np.float64)  # noqa: E731
         self.times = as_array(times)
         self.traces: dict[str, np.ndarray] = {}
@@ -103,8 +124,10 @@ class Waveform:
         with open(path) as f:
             d = json.load(f)
         names = d.get("node_names", [])
+        if "traces" in d and "time" in d:   # the columnar form export_json writes
+            return cls(d["time"], {n: d["traces"][n] for n in names if n in d["traces"]}, d.get("title", d.get("netlist", "")))
         pts = d.get("waveform", [])
-        return cls([p["time"] for p in pts], {n: [p["voltages"].get(n, 0.0) for p in pts] for n in names}, d.get("netlist", ""))
+        return cls([p["time"] for p in pts], {n: [p["voltages"].get(n, 0.0) for p in pts] for n in names}, d.get("netlist", d.get("title", "")))
 
 
 def merge_waveforms(parts: list[PartitionWaveform], title: str = "merged") -> Waveform:
@@ -138,14 +161,19 @@ def export_csv(waveform: Waveform, output_path: str) -> None:
     names = waveform.node_names
     with open(output_path, "w", newline="") as f:
         w = csv.writer(f)
-        w.writerow(["time"] + names)
+        w.writerow(["time"] + [f"V({n})" for n in names])   # the reference's column names
         cols = [waveform.traces[n] for n in names]
         for i, t in enumerate(waveform.times):
             w.writerow([repr(float(t))] + [repr(float(c[i])) for c in cols])
 
 
 def export_json(waveform: Waveform, output_path: str) -> None:
+    """Columnar (``time`` + ``traces``); up to 200 000 samples the reference's per-point list (``waveform``: time and a
+    ``voltages`` dict per point) is written as well, so that its readers work on ordinary results. Beyond that the list
+    would be many times the size of the arrays."""
     payload = {"title": waveform.title, "node_names": waveform.node_names, "num_points": waveform.num_points,
                "time": waveform.times.tolist(), "traces": {n: v.tolist() for n, v in waveform.traces.items()}}
+    if waveform.num_points * max(waveform.num_nodes, 1) <= 200_000:
+        payload["waveform"] = [{"time": float(t), "voltages": {n: float(v[i]) for n, v in waveform.traces.items()}} for i, t in enumerate(waveform.times)]
     with open(output_path, "w") as f:
         json.dump(payload, f)

@@ -15,6 +15,7 @@ import json
 import os
 import platform
 import re
+import shutil
 import socket
 import subprocess
 import sys
@@ -261,8 +262,11 @@ def run_simulation(config: SimulationConfig) -> SimulationResult:
     if config.output_dir and result.success:
         os.makedirs(config.output_dir, exist_ok=True)
         stem = Path(config.netlist_path).stem
-        if config.output_format == "json":
-            export_json(result.waveform, os.path.join(config.output_dir, f"{stem}.json"))
-        else:
-            export_csv(result.waveform, os.path.join(config.output_dir, f"{stem}.csv"))
+        # <deck name>.<format>, and the same file under the name the reference uses (waveform.<format>)
+        ext = "json" if config.output_format == "json" else "csv"
+        target = os.path.join(config.output_dir, f"{stem}.{ext}")
+        (export_json if ext == "json" else export_csv)(result.waveform, target)
+        alias = os.path.join(config.output_dir, f"waveform.{ext}")
+        if os.path.abspath(alias) != os.path.abspath(target):
+            shutil.copyfile(target, alias)
     return result

@@ -56,7 +56,7 @@ class Netlist:
 
     def flatten(self) -> "Netlist":
         """Expands every ``X`` instance; inner nets and device names get the instance path as prefix
-        (``x1.n3``), ports map to the nets of the instance line, ground and global nets stay global."""
+        (``X1.n3``), ports map to the nets of the instance line, ground and global nets stay global."""
         flat = Netlist(title=self.title, global_nodes=set(self.global_nodes), directives=list(self.directives),
                        source_path=self.source_path, source_text=self.source_text)
         for dev in self.devices:
@@ -74,13 +74,13 @@ class Netlist:
             raise KeyError(f"unknown subcircuit '{inst.model}' on {inst.name}")
         if len(sub.ports) != len(inst.nodes):
             raise ValueError(f"{inst.name}: {len(inst.nodes)} nets for {len(sub.ports)} ports of {sub.name}")
-        path = f"{prefix}.{inst.name.lower()}" if prefix else inst.name.lower()
+        path = f"{prefix}.{inst.name}" if prefix else inst.name   # instance names keep their case, as the reference's do ("X1.internal")
         mapping = {p.lower(): self._resolve(n, prefix, outer) for p, n in zip(sub.ports, inst.nodes)}
         for d in sub.devices:
             if d.dev_type == "X":
                 self._expand(d, path, mapping, out, depth + 1)
             else:
-                out.append(Device(name=f"{path}.{d.name.lower()}", dev_type=d.dev_type,
+                out.append(Device(name=f"{path}.{d.name}", dev_type=d.dev_type,
                                   nodes=[self._resolve(n, path, mapping) for n in d.nodes], params=dict(d.params),
                                   model=d.model, value=d.value))
 

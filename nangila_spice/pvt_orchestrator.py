@@ -94,6 +94,14 @@ C1 out 0 10f
 """
 
 
+def _by_net(names, values) -> dict:
+    """``{net: samples}`` view of a (points x nets) array (empty when no waveform was asked for)."""
+    if values is None:
+        return {}
+    arr = np.asarray(values, dtype=np.float64)
+    return {n: arr[:, j] for j, n in enumerate(names) if arr.ndim == 2 and j < arr.shape[1]}
+
+
 def simulate_corner(corner: CornerSpec, golden_waveform: Optional[dict] = None, use_delta: bool = True, netlist_path: Optional[str] = None,
                     tstop: float = 200e-12, dt: float = 1e-12, want_waveform: bool = True) -> dict:
     """One corner: a delta reconstruction from ``golden_waveform`` when allowed and close enough,
@@ -109,8 +117,12 @@ def simulate_corner(corner: CornerSpec, golden_waveform: Optional[dict] = None, 
             solver = _native.PvtDeltaSolver(list(golden_waveform["time"]), np.asarray(golden_waveform["values"], dtype=np.float64))
             golden_waveform["_solver"] = solver
         r = solver.solve(corner.process.value, corner.vdd, corner.temperature, want_waveform)
-        return {"corner": corner.name, "used_delta": bool(r["used_delta_mode"]), "peak_delta_v": float(r["peak_delta_v"]),
-                "time": golden_waveform["time"], "values": r.get("waveform"), "node_names": golden_waveform["node_names"],
+        # "corner_name", "experimental", "execution_mode" and "waveforms" are the reference's keys (its corners are synthetic and all
+        # marked experimental); here only the delta model is an approximation, the rest is the solver
+        values = r.get("waveform")
+        return {"corner": corner.name, "corner_name": corner.name, "used_delta": bool(r["used_delta_mode"]), "peak_delta_v": float(r["peak_delta_v"]),
+                "time": golden_waveform["time"], "values": values, "node_names": golden_waveform["node_names"],
+                "waveforms": _by_net(golden_waveform["node_names"], values), "experimental": True, "execution_mode": "experimental_delta",
                 "wall_time": time.perf_counter() - t0}
     text = Path(netlist_path).read_text() if netlist_path else _RC_DECK
     js, _ = _native.parse_spice(text, Path(netlist_path).name if netlist_path else "rc_stage", corner.process.value, corner.vdd, corner.temperature)
@@ -120,8 +132,9 @@ def simulate_corner(corner: CornerSpec, golden_waveform: Optional[dict] = None, 
         a, b = np.asarray(r["values"], float), np.asarray(golden_waveform["values"], float)
         if a.shape == b.shape and a.size:
             peak = float(np.abs(a - b).max())
-    return {"corner": corner.name, "used_delta": False, "peak_delta_v": peak, "time": r["time"], "values": r["values"],
-            "node_names": r["node_names"], "wall_time": time.perf_counter() - t0, "completed": bool(r["stats"]["completed"])}
+    return {"corner": corner.name, "corner_name": corner.name, "used_delta": False, "peak_delta_v": peak, "time": r["time"], "values": r["values"],
+            "node_names": r["node_names"], "waveforms": _by_net(r["node_names"], r["values"]), "experimental": False, "execution_mode": "solver",
+            "wall_time": time.perf_counter() - t0, "completed": bool(r["stats"]["completed"])}
 
 
 @dataclass
@@ -157,7 +170,7 @@ class SweepResult:
 
     def summary(self) -> str:
         return (f"PVT sweep: {self.completed}/{self.total_corners} corners | {self.total_wall_time:.2f}s total | "
-                f"{self.avg_time_per_corner * 1000:.2f}ms/corner | {self.speedup_vs_full:.1f}x vs full simulation of every corner | "
+                f"{self.avg_time_per_corner * 1000:.2f}ms/corner | speedup {self.speedup_vs_full:.1f}x vs full simulation of every corner | "
                 f"peak dV={self.peak_delta_v * 1e3:.3f}mV | delta mode: {self.delta_mode_used}/{self.completed}")
 
     def to_json(self, path: str) -> None:
@@ -219,4 +232,4 @@ class PvtOrchestrator:
     def _strip(self, res: dict) -> dict:
         if self.config.save_waveforms:
             return {k: v for k, v in res.items() if k != "_solver"}
-        return {k: v for k, v in res.items() if k not in ("time", "values", "_solver")}
+        return {k: v for k, v in res.items() if k not in ("time", "values", "waveforms", "_solver")}

@@ -176,7 +176,7 @@ def test_threaded_partitioned_run_under_thread_sanitizer(built):
     probe = subprocess.run([built["tsan_node"], "--demo", "--tstop", "1e-11"], capture_output=True, text=True, timeout=300)
     if "FATAL: ThreadSanitizer" in probe.stderr:   # e.g. an address-space layout the runtime cannot map
         pytest.skip("ThreadSanitizer cannot run in this environment: " + probe.stderr.strip().splitlines()[0])
-    case = next(c for c in cx.official_correctness_cases() if c.name == "alu2")
+    case = next(c for c in cx.extended_phase1_correctness_cases() if c.name == "alu2")
     deck = case.materialize(os.path.join(tmp, "tsan"))
     pr = ns.partition_netlist(ns.parse_netlist(deck), 4, "spectral")
     files = []

@@ -2,6 +2,7 @@
 plain Python evaluation of the .bench text), the decks synthesised from them parse, and the transistor-level solution of a
 small one agrees with the logic."""
 import json
+import os
 import random
 import re
 
@@ -195,15 +196,20 @@ def test_correctness_registry_and_logic_oracle(tmp_path):
     official = cx.official_correctness_cases()
     assert len(official) == 13 and len({c.name for c in official}) == 13
     assert [c.name for c in cx.phase1_automated_correctness_cases()] == [c.name for c in official]
-    assert {c.tier for c in official} == {"passive", "nonlinear", "logic"}
-    assert len(cx.extended_phase1_correctness_cases()) >= 4
+    assert {c.tier for c in official} == {"passive", "nonlinear", "logic", "large"}
+    assert len(cx.extended_phase1_correctness_cases()) == 13
     blocked = cx.blocked_official_correctness_cases()
-    assert {"s5378", "s38417"} <= {b.name for b in blocked} and all(b.reason for b in blocked)
+    assert {"s5378", "s38417", "c6288"} <= {b.name for b in blocked} and all(b.reason for b in blocked)
     large = cx.large_phase1_correctness_cases()
-    assert len(large) == 17 and {c.tier for c in large} == {"large"} and not {c.name for c in large} & {b.name for b in blocked}
+    assert len(large) == 10 and {c.tier for c in large} == {"large"} and not {c.name[:-5] for c in large} & {b.name for b in blocked}
+    # the reference's names and signatures: cases of the suite are called <name>_auto, the lists take a repository root
+    assert {"c432_auto", "c17_full", "c17_synth", "s27_auto", "s382_auto", "s641_auto"} <= {c.name for c in cx.phase1_automated_correctness_cases("/anywhere")}
+    assert {"c880_auto", "c1355_auto", "c1908_auto"} <= {c.name for c in cx.extended_phase1_correctness_cases("/anywhere")}
+    assert all(os.path.exists(b.netlist_path) for b in cx.blocked_official_correctness_cases("/anywhere")[:1])
+    assert os.path.exists(official[0].netlist_path) and open(official[0].netlist_path).read() == official[0].deck
     assert all(1 <= len(c.expected_levels) <= 16 for c in large)
     assert [c.deck for c in cx.large_phase1_correctness_cases()] == [c.deck for c in large]   # the random vectors are seeded
-    case = next(c for c in official if c.name == "priority4")
+    case = next(c for c in cx.extended_phase1_correctness_cases() if c.name == "priority4")
     path = case.materialize(str(tmp_path))
     # this deck used to stop at 68 ps (Newton oscillating across the jump of the old model); now it completes without a single retry
     js, _ = N.parse_spice(case.deck)
@@ -239,7 +245,7 @@ def test_partitions_keep_transistor_channels_whole_and_logic_runs_partitioned(tm
     from nangila_spice import correctness as cx
     from nangila_spice.partitioner import partition_flat
 
-    case = next(c for c in cx.official_correctness_cases() if c.name == "alu2")
+    case = next(c for c in cx.extended_phase1_correctness_cases() if c.name == "alu2")
     path = case.materialize(str(tmp_path))
     flat = ns.parse_netlist(path).to_native()
     flat.pop("warnings", None)
@@ -266,7 +272,7 @@ def test_a_large_suite_entry_settles_to_its_gate_level_outputs():
     from nangila_spice import correctness as cx
     from nangila_spice.phase1_report import _run_case
 
-    case = next(c for c in cx.large_phase1_correctness_cases() if c.name == "c432")
+    case = next(c for c in cx.official_correctness_cases() if c.name == "c432_auto")
     row = _run_case(case, None)
     assert row["passed"] and row["logic_levels_checked"] == len(case.expected_levels) and row["logic_levels_wrong"] == []
     assert row["oracle"] == "sparse solver, dt / 2 + gate-level logic" and row["max_abs_error_v"] < 0.036
