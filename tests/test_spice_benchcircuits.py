@@ -276,3 +276,22 @@ def test_a_large_suite_entry_settles_to_its_gate_level_outputs():
     row = _run_case(case, None)
     assert row["passed"] and row["logic_levels_checked"] == len(case.expected_levels) and row["logic_levels_wrong"] == []
     assert row["oracle"] == "sparse solver, dt / 2 + gate-level logic" and row["max_abs_error_v"] < 0.036
+
+
+def test_committed_decks_match_the_generators(tmp_path):
+    """The decks under ``benchmarks/`` are the generators' output, byte for byte (a sample of the suite, every
+    reference circuit), and the smallest example runs."""
+    import os
+
+    from nangila_spice import benchcircuits as bc
+    from nangila_spice.correctness import run_nangila_waveform
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks")
+    for name, text in bc.reference_circuits().items():
+        assert open(os.path.join(root, "reference_circuits", name + ".sp")).read() == text, name
+    for name in ("c17", "c432", "c1908", "s27", "s382"):
+        assert open(os.path.join(root, "auto_synth", name + ".sp")).read() == bc.deck(name), name
+    carried = {f[:-3] for f in os.listdir(os.path.join(root, "auto_synth"))}
+    assert carried <= set(bc.SUITE) and len(carried) == 19
+    wf = run_nangila_waveform(os.path.join(root, "spice_examples", "simple_rc.sp"), tstop=1e-11, dt=1e-12)
+    assert abs(wf.traces["vdd"][-1] - 1.8) < 1e-9 and wf.traces["n1"][-1] > 1.7
