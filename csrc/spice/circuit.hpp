@@ -20,60 +20,147 @@
 namespace nspice {
 
 struct SourceWaveform {
-    enum Kind { Dc, Pulse } kind = Dc;
+    // Dc and Pulse as in the reference (nangila-spice/nangila-node/src/mna.rs, which holds a SIN source at a constant);
+    // Sin, Exp and Pwl follow the usual SPICE definitions.
+    enum Kind { Dc, Pulse, Sin, Exp, Pwl } kind = Dc;
     double dc = 0.0;
     double v1 = 0, v2 = 0, td = 0, tr = 0, tf = 0, pw = 0, per = 0;
+    // Sin: v1 = offset, v2 = amplitude, per = frequency (Hz), td = delay, tr = damping (1/s), tf = phase (degrees)
+    // Exp: v1, v2, td = rise delay, tr = rise time constant, tf = fall delay, pw = fall time constant
+    std::vector<double> pts;  // Pwl: t0, v0, t1, v1, ... with increasing times
 
     static SourceWaveform make_dc(double v) { SourceWaveform s; s.kind = Dc; s.dc = v; return s; }
     static SourceWaveform make_pulse(double v1, double v2, double td, double tr, double tf, double pw, double per) {
         SourceWaveform s; s.kind = Pulse; s.v1 = v1; s.v2 = v2; s.td = td; s.tr = tr; s.tf = tf; s.pw = pw; s.per = per;
         return s;
     }
+    static SourceWaveform make_sin(double offset, double amplitude, double freq, double delay = 0.0, double damping = 0.0, double phase_deg = 0.0) {
+        SourceWaveform s; s.kind = Sin; s.v1 = offset; s.v2 = amplitude; s.per = freq; s.td = delay; s.tr = damping; s.tf = phase_deg;
+        return s;
+    }
+    static SourceWaveform make_exp(double v1, double v2, double td1, double tau1, double td2, double tau2) {
+        SourceWaveform s; s.kind = Exp; s.v1 = v1; s.v2 = v2; s.td = td1; s.tr = tau1; s.tf = td2; s.pw = tau2;
+        return s;
+    }
+    // Points whose time does not increase are dropped, so that interpolation never divides by zero.
+    static SourceWaveform make_pwl(const std::vector<double>& time_value_pairs) {
+        SourceWaveform s; s.kind = Pwl;
+        for (size_t i = 0; i + 1 < time_value_pairs.size(); i += 2) {
+            double t = time_value_pairs[i], v = time_value_pairs[i + 1];
+            if (!std::isfinite(t) || !std::isfinite(v)) continue;
+            if (!s.pts.empty() && t <= s.pts[s.pts.size() - 2]) continue;
+            s.pts.push_back(t); s.pts.push_back(v);
+        }
+        if (s.pts.empty()) return make_dc(0.0);
+        return s;
+    }
     double value_at(double t) const {
-        if (kind == Dc) return dc;
-        if (per <= 0.0 || t < td) return v1;
-        double local = std::fmod(t - td, per);
-        if (local < tr) return tr <= 0.0 ? v2 : v1 + (v2 - v1) * (local / tr);
-        if (local < tr + pw) return v2;
-        if (local < tr + pw + tf) return tf <= 0.0 ? v1 : v2 + (v1 - v2) * ((local - tr - pw) / tf);
-        return v1;
-    }
-    // Times in (t0, t1] where the waveform has a corner; the transient loop can land steps on them.
-    bool has_corner_in(double t0, double t1) const {
-        if (kind != Pulse || per <= 0.0) return false;
-        const double offs[4] = {0.0, tr, tr + pw, tr + pw + tf};
-        double base = td + std::floor(std::max(0.0, t0 - td) / per) * per;
-        for (int cyc = 0; cyc < 2; ++cyc)
-            for (double o : offs) {
-                double c = base + cyc * per + o;
-                if (c > t0 && c <= t1) return true;
+        switch (kind) {
+            case Dc: return dc;
+            case Pulse: {
+                if (per <= 0.0 || t < td) return v1;
+                double local = std::fmod(t - td, per);
+                if (local < tr) return tr <= 0.0 ? v2 : v1 + (v2 - v1) * (local / tr);
+                if (local < tr + pw) return v2;
+                if (local < tr + pw + tf) return tf <= 0.0 ? v1 : v2 + (v1 - v2) * ((local - tr - pw) / tf);
+                return v1;
             }
-        return false;
+            case Sin: {
+                const double two_pi = 6.283185307179586, ph = tf * (two_pi / 360.0);
+                if (t < td) return v1 + v2 * std::sin(ph);
+                return v1 + v2 * std::sin(two_pi * per * (t - td) + ph) * std::exp(-(t - td) * tr);
+            }
+            case Exp: {
+                double v = v1;
+                if (t > td) v += (v2 - v1) * (1.0 - std::exp(-(t - td) / std::max(tr, 1e-30)));
+                if (t > tf) v += (v1 - v2) * (1.0 - std::exp(-(t - tf) / std::max(pw, 1e-30)));
+                return v;
+            }
+            case Pwl: {
+                size_t n = pts.size() / 2;
+                if (t <= pts[0]) return pts[1];
+                if (t >= pts[2 * (n - 1)]) return pts[2 * (n - 1) + 1];
+                size_t lo = 0, hi = n - 1;  // pts[2 lo] <= t < pts[2 hi]
+                while (hi - lo > 1) {
+                    size_t mid = (lo + hi) / 2;
+                    (pts[2 * mid] <= t ? lo : hi) = mid;
+                }
+                double t0 = pts[2 * lo], t1 = pts[2 * hi];
+                return pts[2 * lo + 1] + (pts[2 * hi + 1] - pts[2 * lo + 1]) * ((t - t0) / (t1 - t0));
+            }
+        }
+        return dc;
     }
-    // The first corner strictly after t (infinity for a DC source).
+    // The first time strictly after t at which the waveform has a corner (infinity when it has none left); the
+    // adaptive transient loop lands a step on it.
     double next_corner_after(double t) const {
-        if (kind != Pulse || per <= 0.0) return std::numeric_limits<double>::infinity();
-        const double offs[4] = {0.0, tr, tr + pw, tr + pw + tf};
-        const double eps = 1e-9 * per;
-        double base = td + std::floor(std::max(0.0, t - td) / per) * per;
-        for (int cyc = 0; cyc < 3; ++cyc)
-            for (double o : offs) {
-                double c = base + cyc * per + o;
-                if (c > t + eps) return c;
+        const double inf = std::numeric_limits<double>::infinity();
+        switch (kind) {
+            case Pulse: {
+                if (per <= 0.0) return inf;
+                const double offs[4] = {0.0, tr, tr + pw, tr + pw + tf};
+                const double eps = 1e-9 * per;
+                double base = td + std::floor(std::max(0.0, t - td) / per) * per;
+                for (int cyc = 0; cyc < 3; ++cyc)
+                    for (double o : offs) {
+                        double c = base + cyc * per + o;
+                        if (c > t + eps) return c;
+                    }
+                return inf;
             }
-        return std::numeric_limits<double>::infinity();
+            case Sin: return t < td ? td : inf;
+            case Exp: return t < td ? td : (t < tf ? tf : inf);
+            case Pwl: {
+                for (size_t i = 0; i < pts.size(); i += 2)
+                    if (pts[i] > t * (1.0 + 1e-12) + 1e-300) return pts[i];
+                return inf;
+            }
+            default: return inf;
+        }
     }
+    // Whether a corner lies in (t0, t1].
+    bool has_corner_in(double t0, double t1) const { return next_corner_after(t0) <= t1; }
     Json to_json() const {
         Json j = Json::object();
-        if (kind == Dc) { j.set("Dc", dc); return j; }
         Json p = Json::object();
-        p.set("v1", v1).set("v2", v2).set("td", td).set("tr", tr).set("tf", tf).set("pw", pw).set("per", per);
-        j.set("Pulse", p);
+        switch (kind) {
+            case Dc: j.set("Dc", dc); return j;
+            case Pulse:
+                p.set("v1", v1).set("v2", v2).set("td", td).set("tr", tr).set("tf", tf).set("pw", pw).set("per", per);
+                j.set("Pulse", p);
+                return j;
+            case Sin:
+                p.set("offset", v1).set("amplitude", v2).set("freq", per).set("delay", td).set("damping", tr).set("phase", tf);
+                j.set("Sin", p);
+                return j;
+            case Exp:
+                p.set("v1", v1).set("v2", v2).set("td1", td).set("tau1", tr).set("td2", tf).set("tau2", pw);
+                j.set("Exp", p);
+                return j;
+            case Pwl: {
+                Json a = Json::array();
+                for (double x : pts) a.push(Json(x));
+                p.set("points", a);
+                j.set("Pwl", p);
+                return j;
+            }
+        }
         return j;
     }
     static SourceWaveform from_json(const Json& j) {
         if (j.is_num()) return make_dc(j.num);
         if (const Json* d = j.find("Dc")) return make_dc(d->as_num());
+        if (const Json* q = j.find("Sin"))
+            return make_sin(q->number("offset", 0), q->number("amplitude", 0), q->number("freq", 0), q->number("delay", 0),
+                            q->number("damping", 0), q->number("phase", 0));
+        if (const Json* q = j.find("Exp"))
+            return make_exp(q->number("v1", 0), q->number("v2", 0), q->number("td1", 0), q->number("tau1", 0), q->number("td2", 0), q->number("tau2", 0));
+        if (const Json* q = j.find("Pwl")) {
+            std::vector<double> flat;
+            if (const Json* a = q->find("points"))
+                for (const Json& x : a->arr) flat.push_back(x.as_num());
+            return make_pwl(flat);
+        }
         const Json& p = j.at("Pulse");
         return make_pulse(p.number("v1", 0), p.number("v2", 0), p.number("td", 0), p.number("tr", 0),
                           p.number("tf", 0), p.number("pw", 0), p.number("per", 0));

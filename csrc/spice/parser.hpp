@@ -1,5 +1,5 @@
 // SPICE-subset reader: R, C, L, V, I, D, M and X lines, `.subckt` flattening (hierarchical names
-// `inst.node`), `.param`, `.model`, `.ic`, PULSE / DC / SIN sources, engineering suffixes, `+`
+// `inst.node`), `.param`, `.model`, `.ic`, DC / PULSE / SIN / EXP / PWL sources, engineering suffixes, `+`
 // continuation lines, and the partition directives `.ghost <net> <local node> <owner>` and
 // `.nodemap <name> <index>`. MOSFET cards are reduced to Level-1 parameters with process corner,
 // supply and temperature scaling applied at parse time.
@@ -84,10 +84,32 @@ public:
         size_t slash = name.find_last_of('/');
         if (slash != std::string::npos) name = name.substr(slash + 1);
         SpiceParser p(c);
+        p.follow_includes_from(directory_of(path));
         return p.parse_text(ss.str(), name);
     }
 
-    Netlist parse_text(const std::string& text, const std::string& name = "netlist") {
+    // Directory part of a path, with its trailing slash ("" for a bare file name).
+    static std::string directory_of(const std::string& path) {
+        size_t slash = path.find_last_of('/');
+        return slash != std::string::npos ? path.substr(0, slash + 1) : std::string();
+    }
+    // From now on `parse_text` follows `.include` / `.lib`, resolving relative paths against `dir`.
+    void follow_includes_from(const std::string& dir) {
+        base_dir_ = dir;
+        if (!base_dir_.empty() && base_dir_.back() != '/') base_dir_ += '/';
+        follow_includes_ = true;
+    }
+    // The deck text with every readable `.include` / `.lib` replaced by what it names.
+    static std::string expand(const std::string& text, const std::string& dir) {
+        SpiceParser p;
+        p.follow_includes_from(dir);
+        return p.expand_includes(text, p.base_dir_, 0);
+    }
+
+    Netlist parse_text(const std::string& raw_text, const std::string& name = "netlist") {
+        // `.include` / `.lib` are followed for decks read from a file (paths relative to the deck); text handed over
+        // directly has no directory to resolve them against and only gets a warning
+        const std::string text = follow_includes_ ? expand_includes(raw_text, base_dir_, 0) : raw_text;
         std::vector<std::string> stmts = statements(text);
         // pass 1: definitions (.subckt bodies, .param, .model), which may follow their first use
         {
@@ -181,8 +203,95 @@ private:
     std::vector<Element> elements_;
     std::map<std::string, Subckt> subckts_;
     std::map<std::string, double> params_;
+    std::string base_dir_;
+    bool follow_includes_ = false;
     std::vector<GhostLink> ghosts_;
     std::vector<std::pair<std::string, double>> ic_raw_;
+
+    // Replaces `.include <file>`, `.lib <file>` (the whole file) and `.lib <file> <section>` (the lines between
+    // `.lib <section>` and `.endl` of that file) by the text they name, up to 16 levels deep. A file that cannot be
+    // read leaves the line in place, which earns the usual warning. The first line (the title) is never a directive.
+    std::string expand_includes(const std::string& text, const std::string& dir, int depth) {
+        std::istringstream in(text);
+        std::string line, out;
+        bool first = depth == 0;
+        while (std::getline(in, line)) {
+            bool title = first;
+            first = false;
+            size_t b = line.find_first_not_of(" \t");
+            if (title || b == std::string::npos || line[b] != '.') { out += line + "\n"; continue; }
+            std::istringstream ls(line.substr(b));
+            std::string kw, file, section;
+            ls >> kw >> file >> section;
+            kw = upper(kw);
+            if (kw == ".ENDL") continue;
+            if ((kw != ".INCLUDE" && kw != ".INC" && kw != ".LIB") || file.empty()) { out += line + "\n"; continue; }
+            auto unquote = [](std::string v) {
+                while (!v.empty() && (v.front() == '"' || v.front() == '\'')) v.erase(v.begin());
+                while (!v.empty() && (v.back() == '"' || v.back() == '\'')) v.pop_back();
+                return v;
+            };
+            file = unquote(file);
+            section = upper(unquote(section));
+            std::string path = (!file.empty() && file[0] == '/') ? file : dir + file;
+            std::ifstream f(path);
+            if (!f || depth >= 16) {
+                if (kw == ".LIB" && section.empty()) continue;  // `.lib <section>` inside a library: a marker, not a request
+                out += line + "\n";
+                continue;
+            }
+            std::stringstream body;
+            body << f.rdbuf();
+            std::string inner = body.str();
+            if (kw == ".LIB" && !section.empty()) {
+                std::istringstream lib(inner);
+                std::string l, picked;
+                bool on = false;
+                while (std::getline(lib, l)) {
+                    std::istringstream t(l);
+                    std::string a, c;
+                    t >> a >> c;
+                    a = upper(a);
+                    if (a == ".LIB" && upper(unquote(c)) == section) { on = true; continue; }
+                    if (a == ".ENDL") { on = false; continue; }
+                    if (on) picked += l + "\n";
+                }
+                inner = picked;
+            }
+            size_t slash = path.find_last_of('/');
+            out += expand_includes(inner, slash != std::string::npos ? path.substr(0, slash + 1) : std::string(), depth + 1);
+            if (out.empty() || out.back() != '\n') out += "\n";
+        }
+        return out;
+    }
+
+    // Decks written by tools often start with an element instead of a title. A first line counts as an element when it
+    // starts with an element letter and has the shape of that card: a two-terminal element or source has nothing but values
+    // (numbers, expressions in quotes or braces, source keywords, `name=value`) after its nodes, a diode four fields, a
+    // MOSFET six, a sub-circuit call three. "inverter with a 10 fF load" is a title, "I1 0 n1 1m" is not.
+    static bool first_line_is_card(char letter, const std::vector<std::string>& tok) {
+        if (tok.size() < 3 || tok[0].size() < 2 || !std::isalnum((unsigned char)tok[0][1])) return false;
+        switch (letter) {
+            case 'D': return tok.size() >= 4;
+            case 'M': return tok.size() >= 6;
+            case 'X': return true;
+            case 'R': case 'C': case 'L': case 'V': case 'I': {
+                // everything after the two nodes is a value, a source keyword or a `name=value` parameter
+                auto value_like = [](const std::string& t) {
+                    size_t d = (t[0] == '+' || t[0] == '-') ? 1 : 0;
+                    if (d < t.size() && (std::isdigit((unsigned char)t[d]) || (t[d] == '.' && d + 1 < t.size() && std::isdigit((unsigned char)t[d + 1])))) return true;
+                    if (t[0] == '{' || t[0] == '\'' || t.find('=') != std::string::npos) return true;
+                    std::string u = upper(t);
+                    return u == "DC" || u == "AC" || u == "PULSE" || u == "SIN" || u == "PWL" || u == "EXP";
+                };
+                if (tok.size() < 4) return false;
+                for (size_t i = 3; i < tok.size(); ++i)
+                    if (!value_like(tok[i])) return false;
+                return true;
+            }
+            default: return false;
+        }
+    }
 
     // Joins `+` continuations, drops comment lines and trailing `;` / `$` comments. The first line of
     // a deck is its title unless it already looks like an element or a directive.
@@ -202,9 +311,7 @@ private:
             if (first_line) {
                 first_line = false;
                 char ch = char(std::toupper((unsigned char)line[0]));
-                bool looks_like_card = ch == '.' || ((std::string("RCLVIDMX").find(ch) != std::string::npos) && split(line).size() >= 3 &&
-                                                     line.find(' ') != std::string::npos && std::isalnum((unsigned char)line[1]));
-                if (!looks_like_card) continue;
+                if (!(ch == '.' || first_line_is_card(ch, split(line)))) continue;
             }
             if (line[0] == '+') {
                 if (!out.empty()) out.back() += " " + line.substr(1);
@@ -232,14 +339,18 @@ private:
         }
         return merged;
     }
-    double value(const std::string& raw) const {
+    // A number with an engineering suffix or the name of a parameter; false for anything else (a keyword, say).
+    bool try_value(const std::string& raw, double& out) const {
         std::string s = lower(raw);
         while (!s.empty() && (s.front() == '\'' || s.front() == '{')) s.erase(s.begin());
         while (!s.empty() && (s.back() == '\'' || s.back() == '}')) s.pop_back();
         auto it = params_.find(s);
-        if (it != params_.end()) return it->second;
+        if (it != params_.end()) { out = it->second; return true; }
+        return parse_scaled(s, out);
+    }
+    double value(const std::string& raw) const {
         double v = 0.0;
-        return parse_scaled(s, v) ? v : 0.0;
+        return try_value(raw, v) ? v : 0.0;
     }
     int node(const std::string& raw, const std::string& prefix, const std::map<std::string, std::string>& alias) {
         std::string n = lower(raw);
@@ -277,9 +388,17 @@ private:
                 if (k >= 2) return SourceWaveform::make_pulse(p[0], p[1], p[2], p[3], p[4], k > 5 ? p[5] : 1e30, 0.0);
                 return w;
             }
-            if (u == "SIN") {  // held at its peak: the element set has no sinusoid
-                double off = i + 1 < tok.size() ? value(tok[i + 1]) : 0.0, amp = i + 2 < tok.size() ? value(tok[i + 2]) : 0.0;
-                return SourceWaveform::make_dc(off + amp);
+            if (u == "SIN" || u == "EXP" || u == "PWL") {
+                std::vector<double> p;
+                double x;
+                for (size_t j = i + 1; j < tok.size() && try_value(tok[j], x); ++j) p.push_back(x);
+                auto arg = [&](size_t k, double dflt) { return k < p.size() ? p[k] : dflt; };
+                if (u == "SIN") return SourceWaveform::make_sin(arg(0, 0), arg(1, 0), arg(2, 0), arg(3, 0), arg(4, 0), arg(5, 0));
+                if (u == "EXP") {
+                    double td1 = arg(2, 0), tau1 = arg(3, 0);
+                    return SourceWaveform::make_exp(arg(0, 0), arg(1, 0), td1, tau1, arg(4, td1 + tau1), arg(5, tau1));
+                }
+                return SourceWaveform::make_pwl(p);
             }
             if (u == "AC") { i += 2; continue; }
             if (!have) { w = SourceWaveform::make_dc(value(tok[i])); have = true; }

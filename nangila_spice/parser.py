@@ -7,6 +7,7 @@ API counterpart: ``nangila-spice/src/nangila_spice/parser.py:15-223`` of the ref
 from __future__ import annotations
 
 import json
+import re
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Optional
@@ -104,6 +105,21 @@ class Netlist:
         return out
 
 
+_VALUE_LIKE = re.compile(r"^([+-]?(\d|\.\d)|[{']|.*=|(DC|AC|PULSE|SIN|PWL|EXP)$)", re.IGNORECASE)
+
+
+def _first_line_is_card(letter: str, line: str) -> bool:
+    """Whether the first line of a deck is an element rather than a title (same rule as the native parser): it starts
+    with an element letter and has the shape of that card, e.g. nothing but values and parameters after the nodes of a two-terminal element."""
+    tok = re.sub(r"[(),]", " ", line).split()
+    if len(tok) < 3 or len(tok[0]) < 2 or not tok[0][1].isalnum():
+        return False
+    if letter in "RCLVI":
+        return len(tok) >= 4 and all(_VALUE_LIKE.match(t) for t in tok[3:])
+    need = {"D": 4, "M": 6, "X": 3}.get(letter, 4 if letter in "QJEG" else None)
+    return need is not None and len(tok) >= need
+
+
 def _statements(text: str) -> list[str]:
     out: list[str] = []
     first = True
@@ -118,7 +134,7 @@ def _statements(text: str) -> list[str]:
         if first:
             first = False
             head = line[0].upper()
-            if not (head == "." or (head in "RCLVIDMXQJEG" and len(line.split()) >= 3)):
+            if not (head == "." or _first_line_is_card(head, line)):
                 out.append("*TITLE* " + line)
                 continue
         if line.startswith("+"):
@@ -196,4 +212,9 @@ def parse_netlist(filepath: str) -> Netlist:
     p = Path(filepath)
     if not p.exists():
         raise FileNotFoundError(filepath)
-    return parse_netlist_text(p.read_text(), str(p))
+    text = p.read_text()
+    if re.search(r"^\s*\.(include|inc|lib)\b", text, re.IGNORECASE | re.MULTILINE):
+        from . import _native
+
+        text = _native.expand_includes(text, str(p.parent))  # model cards and sub-circuits kept in other files
+    return parse_netlist_text(text, str(p))

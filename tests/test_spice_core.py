@@ -523,3 +523,91 @@ def test_adaptive_steps_on_logic_with_long_idle_periods():
     settled = np.abs(vf - 0.9) > 0.8
     assert np.abs(vf - va)[settled].max() < 0.05
     assert np.mean(np.abs(vf - va) > 0.2) < 0.01
+
+
+def test_sin_exp_and_pwl_sources():
+    # value_at of each kind against its definition, and the JSON round trip through a netlist
+    sin = {"Sin": {"offset": 0.9, "amplitude": 0.5, "freq": 1e9, "delay": 1e-10, "damping": 2e9, "phase": 30.0}}
+    for t in (0.0, 5e-11, 1e-10, 3.3e-10, 1.7e-9):
+        want = 0.9 + 0.5 * math.sin(math.radians(30.0)) if t < 1e-10 else \
+            0.9 + 0.5 * math.sin(2 * math.pi * 1e9 * (t - 1e-10) + math.radians(30.0)) * math.exp(-(t - 1e-10) * 2e9)
+        assert math.isclose(N.source_value(json.dumps(sin), t), want, rel_tol=1e-12, abs_tol=1e-15)
+    exp = {"Exp": {"v1": 0.2, "v2": 1.2, "td1": 1e-10, "tau1": 5e-11, "td2": 5e-10, "tau2": 1e-10}}
+    for t in (0.0, 1e-10, 2e-10, 5e-10, 9e-10):
+        want = 0.2 + (1.0 * (1 - math.exp(-(t - 1e-10) / 5e-11)) if t > 1e-10 else 0.0) - (1.0 * (1 - math.exp(-(t - 5e-10) / 1e-10)) if t > 5e-10 else 0.0)
+        assert math.isclose(N.source_value(json.dumps(exp), t), want, rel_tol=1e-12)
+    pwl = {"Pwl": {"points": [1e-10, 0.0, 2e-10, 1.8, 2e-10, 5.0, 6e-10, 1.8, 7e-10, 0.6]}}  # the repeated time is dropped
+    for t, want in ((0.0, 0.0), (1e-10, 0.0), (1.5e-10, 0.9), (2e-10, 1.8), (4e-10, 1.8), (6.5e-10, 1.2), (7e-10, 0.6), (1.0, 0.6)):
+        assert math.isclose(N.source_value(json.dumps(pwl), t), want, abs_tol=1e-12)
+    nl = {"name": "s", "num_nodes": 3, "elements": [{"VoltageSource": {"pos": 1, "neg": 0, "source": sin}},
+                                                     {"VoltageSource": {"pos": 2, "neg": 0, "source": exp}},
+                                                     {"CurrentSource": {"pos": 0, "neg": 3, "source": pwl}},
+                                                     {"Resistor": {"a": 3, "b": 0, "r": 1000.0}}],
+          "ghost_map": [], "node_names": ["a", "b", "c"], "initial_conditions": []}
+    back = json.loads(N.netlist_roundtrip(json.dumps(nl)))
+    assert back["elements"][0]["VoltageSource"]["source"] == sin and back["elements"][1]["VoltageSource"]["source"] == exp
+    assert back["elements"][2]["CurrentSource"]["source"]["Pwl"]["points"] == [1e-10, 0.0, 2e-10, 1.8, 6e-10, 1.8, 7e-10, 0.6]
+    # a transient run follows them: the voltage sources exactly, the current source through its resistor
+    res = N.simulate(json.dumps(nl), 1e-9, 1e-12)
+    t, v = np.asarray(res["time"]), np.asarray(res["values"])
+    assert np.abs(v[:, 0] - [N.source_value(json.dumps(sin), x) for x in t]).max() < 1e-12
+    assert np.allclose(v[:, 2], 1000.0 * np.asarray([N.source_value(json.dumps(pwl), x) for x in t]), rtol=1e-8, atol=1e-9)  # gmin to ground
+    # the adaptive loop lands on the corners of a PWL source: same waveform as the fixed step
+    deck = "* pwl into RC\nV1 in 0 PWL(0 0 1n 0 1.02n 1.8 4n 1.8 4.5n 0.3)\nR1 in out 1k\nC1 out 0 20f\n.end\n"
+    js, _ = N.parse_spice(deck)
+    fixed, adapt = N.simulate(js, 8e-9, 5e-12), N.simulate(js, 8e-9, 5e-12, adaptive=True)
+    assert np.abs(np.asarray(fixed["values"]) - np.asarray(adapt["values"])).max() < 5e-3
+    assert adapt["stats"]["solver_steps"] < fixed["stats"]["total_steps"] / 4
+
+
+def test_parser_reads_sin_exp_pwl_cards():
+    deck = ("* sources\n.param amp=0.5\nVS s 0 SIN(0.9 amp 1g 100p)\nIE 0 e EXP(0 1m 100p 50p)\nVP p 0 PWL(0 0, 100p 0, 150p 1.8)\n"
+            "VD d 0 DC 1.2 AC 1\nRS s 0 1k\nRE e 0 1k\nRP p 0 1k\nRD d 0 1k\n.end\n")
+    js, warnings = N.parse_spice(deck)
+    src = {next(iter(e.values()))["pos"] or -next(iter(e.values()))["neg"]: next(iter(e.values()))["source"]
+           for e in json.loads(js)["elements"] if "Source" in next(iter(e))}
+    names = json.loads(js)["node_names"]
+    by_name = {names[abs(k) - 1]: v for k, v in src.items()}
+    assert by_name["s"] == {"Sin": {"offset": 0.9, "amplitude": 0.5, "freq": 1e9, "delay": 1e-10, "damping": 0, "phase": 0}}
+    assert by_name["e"] == {"Exp": {"v1": 0, "v2": 1e-3, "td1": 1e-10, "tau1": 5e-11, "td2": 1.5e-10, "tau2": 5e-11}}  # SPICE defaults for the fall
+    assert by_name["p"] == {"Pwl": {"points": [0, 0, 1e-10, 0, 1.5e-10, 1.8]}}
+    assert by_name["d"] == {"Dc": 1.2} and not warnings
+
+
+def test_first_line_title_rule_and_includes(tmp_path):
+    from nangila_spice.parser import parse_netlist, parse_netlist_text
+
+    # a first line that reads like prose is the title even when it starts with an element letter
+    for text, title, devices in (("inverter with a 10 fF load\nR1 a 0 1k\nV1 a 0 1\n", "inverter with a 10 fF load", 2),
+                                 ("ring oscillator 3 stages\nR1 a 0 1\nV1 a 0 1\n", "ring oscillator 3 stages", 2),
+                                 ("I1 0 n1 1m\nR1 n1 0 1k\n", "", 2), ("V1 a 0 DC 1\nR1 a 0 1\n", "", 2),
+                                 ("C1 a 0 {cval} ic=0\n.param cval=1p\nV1 a 0 1\n", "", 2), ("VIN in 0 PULSE(0 1.8 100p 20p 20p 400p 1n)\nR1 in 0 1k\n", "", 2)):
+        nl = parse_netlist_text(text)
+        assert (nl.title or "") == title and nl.num_devices == devices and len(nl.to_native()["elements"]) == devices, text
+    # model cards in a library section, a sub-circuit in an included file, both relative to the deck
+    (tmp_path / "models").mkdir()
+    (tmp_path / "models" / "cmos.lib").write_text(
+        "* corners\n.lib tt\n.model nch NMOS (vto=0.45 kp=200u)\n.model pch PMOS (vto=-0.45 kp=100u)\n.endl\n"
+        ".lib ss\n.model nch NMOS (vto=0.60 kp=150u)\n.model pch PMOS (vto=-0.60 kp=75u)\n.endl\n")
+    (tmp_path / "models" / "inv.sub").write_text(".subckt inv a y vdd\nMP y a vdd vdd pch w=2u l=180n\nMN y a 0 0 nch w=1u l=180n\n.ends\n")
+    top = tmp_path / "top.sp"
+    top.write_text("inverter with its models in a library\n.lib 'models/cmos.lib' ss\n.include \"models/inv.sub\"\nVDD vdd 0 DC 1.8\n"
+                   "VIN in 0 PWL(0 0 100p 0 150p 1.8)\nX1 in out vdd inv\nCL out 0 10f\n.include missing.inc\n.end\n")
+    nl = parse_netlist(str(top))
+    assert nl.title.startswith("inverter with") and "INV" in nl.subcircuits and nl.num_devices == 4
+    native = nl.to_native()
+    mos = [e["Mosfet"] for e in native["elements"] if "Mosfet" in e]
+    assert len(mos) == 2 and sorted(round(abs(m["model"]["vth"]), 2) for m in mos) == [0.6, 0.6]  # the ss section, not tt
+    assert any("missing.inc" in w for w in native["warnings"])
+    res = N.simulate(json.dumps({k: v for k, v in native.items() if k != "warnings"}), 6e-10, 1e-12)
+    out = np.asarray(res["values"])[:, res["node_names"].index("out")]
+    assert out[50] > 1.7 and out[-1] < 0.05
+    # the solver process follows the same includes
+    import os
+    import subprocess
+
+    from nangila_spice.correctness import find_nangila_binary
+
+    proc = subprocess.run([find_nangila_binary(), "--partition", str(top), "--tstop", "6e-10", "--dt", "1e-12", "--waveform-json", str(tmp_path / "w.json")],
+                          capture_output=True, text=True, timeout=60)
+    assert proc.returncode == 0 and os.path.exists(tmp_path / "w.json"), proc.stderr[-400:]
