@@ -64,7 +64,7 @@ PYBIND11_MODULE(_native, m) {
         Netlist nl = p.parse_text(text, name);
         return py::make_tuple(nl.to_json().dump(), p.warnings);
     }, py::arg("text"), py::arg("name") = "netlist", py::arg("process") = "TT", py::arg("vdd") = 1.8, py::arg("temp") = 27.0);
-    m.def("expand_includes", &SpiceParser::expand, py::arg("text"), py::arg("directory"),
+    m.def("expand_includes", &SpiceParser::expand, py::arg("text"), py::arg("directory"), py::arg("deck_path") = "",
           "deck text with every readable `.include <file>` / `.lib <file> [section]` replaced by what it names (paths relative to `directory`)");
     m.def("netlist_roundtrip", [](const std::string& js) { return Netlist::from_json(Json::parse(js)).to_json().dump(); });
     m.def("source_value", [](const std::string& js, double t) { return SourceWaveform::from_json(Json::parse(js)).value_at(t); });

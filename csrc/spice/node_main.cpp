@@ -141,7 +141,7 @@ static Netlist load_any(const std::string& path, const Args& a) {
     Corner c;
     c.process = a.process; c.vdd = a.vdd; c.temp_c = a.temp;
     SpiceParser p(c);
-    p.follow_includes_from(SpiceParser::directory_of(path));
+    p.follow_includes_from(SpiceParser::directory_of(path), path);
     return p.parse_text(ss.str(), path.substr(path.find_last_of('/') == std::string::npos ? 0 : path.find_last_of('/') + 1));
 }
 
@@ -258,7 +258,7 @@ static int run(int argc, char** argv) {
             std::stringstream ss;
             ss << f.rdbuf();
             std::string base = a.partition.substr(a.partition.find_last_of('/') == std::string::npos ? 0 : a.partition.find_last_of('/') + 1);
-            p.follow_includes_from(SpiceParser::directory_of(a.partition));
+            p.follow_includes_from(SpiceParser::directory_of(a.partition), a.partition);
             nl = p.parse_text(ss.str(), base);
             for (auto& w : p.warnings) std::fprintf(stderr, "warning: %s\n", w.c_str());
         }

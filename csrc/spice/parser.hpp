@@ -5,6 +5,7 @@
 // supply and temperature scaling applied at parse time.
 // Behavioural reference: nangila-spice/nangila-node/src/parser.rs:13-738.
 #pragma once
+#include <algorithm>
 #include <cctype>
 #include <fstream>
 #include <map>
@@ -84,7 +85,7 @@ public:
         size_t slash = name.find_last_of('/');
         if (slash != std::string::npos) name = name.substr(slash + 1);
         SpiceParser p(c);
-        p.follow_includes_from(directory_of(path));
+        p.follow_includes_from(directory_of(path), path);
         return p.parse_text(ss.str(), name);
     }
 
@@ -94,15 +95,16 @@ public:
         return slash != std::string::npos ? path.substr(0, slash + 1) : std::string();
     }
     // From now on `parse_text` follows `.include` / `.lib`, resolving relative paths against `dir`.
-    void follow_includes_from(const std::string& dir) {
+    void follow_includes_from(const std::string& dir, const std::string& deck_path = std::string()) {
+        if (!deck_path.empty()) include_stack_.assign(1, deck_path);  // so that a deck cannot include itself
         base_dir_ = dir;
         if (!base_dir_.empty() && base_dir_.back() != '/') base_dir_ += '/';
         follow_includes_ = true;
     }
     // The deck text with every readable `.include` / `.lib` replaced by what it names.
-    static std::string expand(const std::string& text, const std::string& dir) {
+    static std::string expand(const std::string& text, const std::string& dir, const std::string& deck_path = std::string()) {
         SpiceParser p;
-        p.follow_includes_from(dir);
+        p.follow_includes_from(dir, deck_path);
         return p.expand_includes(text, p.base_dir_, 0);
     }
 
@@ -205,11 +207,13 @@ private:
     std::map<std::string, double> params_;
     std::string base_dir_;
     bool follow_includes_ = false;
+    size_t included_bytes_ = 0;
+    std::vector<std::string> include_stack_;
     std::vector<GhostLink> ghosts_;
     std::vector<std::pair<std::string, double>> ic_raw_;
 
     // Replaces `.include <file>`, `.lib <file>` (the whole file) and `.lib <file> <section>` (the lines between
-    // `.lib <section>` and `.endl` of that file) by the text they name, up to 16 levels deep. A file that cannot be
+    // `.lib <section>` and `.endl` of that file) by the text they name, up to 16 levels deep and 64 MB in total. A file that cannot be
     // read leaves the line in place, which earns the usual warning. The first line (the title) is never a directive.
     std::string expand_includes(const std::string& text, const std::string& dir, int depth) {
         std::istringstream in(text);
@@ -224,7 +228,7 @@ private:
             std::string kw, file, section;
             ls >> kw >> file >> section;
             kw = upper(kw);
-            if (kw == ".ENDL") continue;
+            if (kw == ".ENDL" || (kw == ".END" && depth > 0)) continue;  // the `.end` of an included file does not end the deck
             if ((kw != ".INCLUDE" && kw != ".INC" && kw != ".LIB") || file.empty()) { out += line + "\n"; continue; }
             auto unquote = [](std::string v) {
                 while (!v.empty() && (v.front() == '"' || v.front() == '\'')) v.erase(v.begin());
@@ -235,7 +239,9 @@ private:
             section = upper(unquote(section));
             std::string path = (!file.empty() && file[0] == '/') ? file : dir + file;
             std::ifstream f(path);
-            if (!f || depth >= 16) {
+            bool cycle = std::find(include_stack_.begin(), include_stack_.end(), path) != include_stack_.end();
+            if (cycle) { warnings.push_back(kw + " of a file that is being included already: " + file); continue; }
+            if (!f || depth >= 16 || included_bytes_ > (size_t(64) << 20)) {
                 if (kw == ".LIB" && section.empty()) continue;  // `.lib <section>` inside a library: a marker, not a request
                 out += line + "\n";
                 continue;
@@ -243,6 +249,7 @@ private:
             std::stringstream body;
             body << f.rdbuf();
             std::string inner = body.str();
+            included_bytes_ += inner.size();
             if (kw == ".LIB" && !section.empty()) {
                 std::istringstream lib(inner);
                 std::string l, picked;
@@ -258,8 +265,9 @@ private:
                 }
                 inner = picked;
             }
-            size_t slash = path.find_last_of('/');
-            out += expand_includes(inner, slash != std::string::npos ? path.substr(0, slash + 1) : std::string(), depth + 1);
+            include_stack_.push_back(path);
+            out += expand_includes(inner, directory_of(path), depth + 1);
+            include_stack_.pop_back();
             if (out.empty() || out.back() != '\n') out += "\n";
         }
         return out;

@@ -216,5 +216,5 @@ def parse_netlist(filepath: str) -> Netlist:
     if re.search(r"^\s*\.(include|inc|lib)\b", text, re.IGNORECASE | re.MULTILINE):
         from . import _native
 
-        text = _native.expand_includes(text, str(p.parent))  # model cards and sub-circuits kept in other files
+        text = _native.expand_includes(text, str(p.parent), str(p))  # model cards and sub-circuits kept in other files
     return parse_netlist_text(text, str(p))

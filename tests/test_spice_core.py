@@ -611,3 +611,13 @@ def test_first_line_title_rule_and_includes(tmp_path):
     proc = subprocess.run([find_nangila_binary(), "--partition", str(top), "--tstop", "6e-10", "--dt", "1e-12", "--waveform-json", str(tmp_path / "w.json")],
                           capture_output=True, text=True, timeout=60)
     assert proc.returncode == 0 and os.path.exists(tmp_path / "w.json"), proc.stderr[-400:]
+
+
+def test_a_deck_that_includes_itself_ends(tmp_path):
+    from nangila_spice.parser import parse_netlist
+
+    deck = tmp_path / "loop.sp"
+    (tmp_path / "part.inc").write_text("* a part with its own end card\nR2 a 0 2k\n.include loop.sp\n.end\n")
+    deck.write_text("* loop\n.include part.inc\n.include loop.sp\nR1 a 0 1k\nV1 a 0 1\n.end\n")
+    nl = parse_netlist(str(deck))  # the cycle is cut, and the `.end` of the included file does not end the deck
+    assert sorted(d.name for d in nl.devices) == ["R1", "R2", "V1"]
