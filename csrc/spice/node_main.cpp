@@ -34,6 +34,7 @@ struct Args {
     int connect_timeout_ms = 30000, io_timeout_ms = 30000;
     uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1, threads = 1;
     double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
+    bool tstop_given = false, dt_given = false;  // a deck's `.tran` card fills in whichever was not given
     bool demo = false, bench = false, lockstep = false, adaptive = false;
 };
 
@@ -67,8 +68,8 @@ static bool parse_args(int argc, char** argv, Args& a) {
         else if (f == "--threads") { if (!(v = need("--threads"))) return false; a.threads = uint32_t(std::max(1, std::atoi(v))); }
         else if (f == "--record-every") { if (!(v = need("--record-every"))) return false; a.record_every = std::max(1, std::atoi(v)); }
         else if (f == "--reltol") { if (!(v = need("--reltol"))) return false; a.reltol = std::atof(v); }
-        else if (f == "--tstop") { if (!(v = need("--tstop"))) return false; a.tstop = std::atof(v); }
-        else if (f == "--dt") { if (!(v = need("--dt"))) return false; a.dt = std::atof(v); }
+        else if (f == "--tstop") { if (!(v = need("--tstop"))) return false; a.tstop = std::atof(v); a.tstop_given = true; }
+        else if (f == "--dt") { if (!(v = need("--dt"))) return false; a.dt = std::atof(v); a.dt_given = true; }
         else if (f == "--vdd") { if (!(v = need("--vdd"))) return false; a.vdd = std::atof(v); }
         else if (f == "--temp") { if (!(v = need("--temp"))) return false; a.temp = std::atof(v); }
         else if (f == "--nz-tol") { if (!(v = need("--nz-tol"))) return false; a.nz_tol = std::atof(v); }
@@ -260,6 +261,8 @@ static int run(int argc, char** argv) {
             std::string base = a.partition.substr(a.partition.find_last_of('/') == std::string::npos ? 0 : a.partition.find_last_of('/') + 1);
             p.follow_includes_from(SpiceParser::directory_of(a.partition), a.partition);
             nl = p.parse_text(ss.str(), base);
+            if (!a.tstop_given && p.tran_stop > 0.0) a.tstop = p.tran_stop;
+            if (!a.dt_given && p.tran_step > 0.0) a.dt = p.tran_step;
             for (auto& w : p.warnings) std::fprintf(stderr, "warning: %s\n", w.c_str());
         }
     } catch (const std::exception& e) {

@@ -69,6 +69,7 @@ class SpiceParser {
 public:
     std::map<std::string, ModelCard> models;
     std::vector<std::string> warnings;
+    double tran_step = 0.0, tran_stop = 0.0;  // `.tran <step> <stop>` of the deck (0 when it has none): defaults for a run
 
     explicit SpiceParser(Corner c = {}) : corner_(std::move(c)) {
         corner_.process = upper(corner_.process);
@@ -532,6 +533,9 @@ private:
                 if (eq == std::string::npos || eq == 0) continue;
                 ic_raw_.emplace_back(resolved_name(t.substr(0, eq), prefix, alias), value(t.substr(eq + 1)));
             }
+        } else if (kw == ".TRAN" && tok.size() >= 3) {
+            tran_step = value(tok[1]);
+            tran_stop = value(tok[2]);
         } else if (kw == ".GHOST" && tok.size() >= 4) {
             ghosts_.push_back({net_name_hash(tok[1]), std::atoi(tok[2].c_str()), uint32_t(std::atoi(tok[3].c_str()))});
         } else if (kw == ".NODEMAP" && tok.size() >= 3) {

@@ -41,6 +41,7 @@ _EXPORT_MAP = {
     "extended_phase1_correctness_cases": (".correctness", "extended_phase1_correctness_cases"),
     "blocked_official_correctness_cases": (".correctness", "blocked_official_correctness_cases"),
     "large_phase1_correctness_cases": (".correctness", "large_phase1_correctness_cases"),
+    "huge_phase1_correctness_cases": (".correctness", "huge_phase1_correctness_cases"),
     "collect_flattened_nodes": (".correctness", "collect_flattened_nodes"), "collect_observable_nodes": (".correctness", "collect_observable_nodes"),
     "check_logic_levels": (".correctness", "check_logic_levels"), "evaluate_bench": (".benchcircuits", "evaluate_bench"),
     "read_nz": (".nz_reader", "read_nz"), "DeviceCsr": (".gpu", "DeviceCsr"),

@@ -28,6 +28,13 @@ def invoke_run(args) -> int:
     if not os.path.exists(args.netlist):
         print(f"Error: netlist not found at {args.netlist}", file=sys.stderr)
         return 1
+    if args.tstop is None or args.dt is None:
+        # the deck's own `.tran <step> <stop>` card, then the reference's defaults (1 us in 1 ps steps)
+        from .parser import parse_netlist
+
+        step, stop = parse_netlist(args.netlist).tran() or (1e-12, 1e-6)
+        args.tstop = stop if args.tstop is None else args.tstop
+        args.dt = step if args.dt is None else args.dt
     result = run_simulation(SimulationConfig(netlist_path=args.netlist, partitions=args.partitions, method=args.method, reltol=args.reltol,
                                              tstop=args.tstop, dt=args.dt, predict_depth=args.predict_depth, output_dir=args.output_dir,
                                              output_format=args.output_format,
@@ -86,6 +93,9 @@ def invoke_phase1_report(args) -> int:
         argv.append("--include-large")
     if args.include_partitioned:
         argv.append("--include-partitioned")
+    if args.include_huge:
+        argv.append("--include-huge")
+    argv += ["--jobs", str(args.jobs)]
     return report_main(argv)
 
 
@@ -107,8 +117,8 @@ def main(argv=None) -> int:
     r.add_argument("--partitions", type=int, default=None)
     r.add_argument("--method", default="auto")
     r.add_argument("--reltol", type=float, default=1e-3)
-    r.add_argument("--tstop", type=float, default=1e-6)
-    r.add_argument("--dt", type=float, default=1e-12)
+    r.add_argument("--tstop", type=float, default=None, help="end time in seconds (default: the deck's .tran card, else 1e-6)")
+    r.add_argument("--dt", type=float, default=None, help="time step in seconds (default: the deck's .tran card, else 1e-12)")
     r.add_argument("--predict-depth", type=int, default=5)
     r.add_argument("--output-dir", default=None)
     r.add_argument("--output-format", choices=("csv", "json"), default="csv")
@@ -134,6 +144,8 @@ def main(argv=None) -> int:
     p.add_argument("--include-extended", action="store_true")
     p.add_argument("--include-large", action="store_true", help="also the suite entries of up to 6 000 transistors (about a minute)")
     p.add_argument("--include-partitioned", action="store_true", help="also five cases run in partitions, as threads and as processes")
+    p.add_argument("--include-huge", action="store_true", help="also the seven largest suite entries (12 000 to 150 000 transistors, up to ten minutes each)")
+    p.add_argument("--jobs", type=int, default=1, help="cases run at a time")
     p.add_argument("--output-json", default="artifacts/phase1_benchmark_report.json")
     p.add_argument("--output-md", default="artifacts/phase1_benchmark_report.md")
     v = sub.add_parser("view", help="show a .nz waveform file")

@@ -379,18 +379,28 @@ def large_phase1_correctness_cases(repo_root: Optional[str] = None) -> list:
     return [_suite_case(name) for name in LARGE_SUITE_ENTRIES]
 
 
+HUGE_SUITE_ENTRIES = ("s5378", "s9234", "s13207", "s15850", "s35932", "s38417", "s38584")
+
+
+def huge_phase1_correctness_cases(repo_root: Optional[str] = None) -> list:
+    """The seven largest suite entries, 12 000 to 150 000 transistors (``--include-huge``): half a minute to ten minutes each
+    with the half-step oracle, so a report runs them on request only (and several at a time with ``--jobs``)."""
+    import dataclasses
+
+    del repo_root
+    return [dataclasses.replace(_suite_case(name), tier="huge") for name in HUGE_SUITE_ENTRIES]
+
+
 def blocked_official_correctness_cases(repo_root: Optional[str] = None) -> list:
     """Suite entries that no report runs, with the reason."""
     from . import benchcircuits as bc
 
     del repo_root
-    why = ("tens to hundreds of thousands of devices: minutes per run with its half-step oracle; these belong to the scaling study "
-           "(nangila_spice.benchmark), not to a correctness report")
     hazards = ("the 16 x 16 multiplier (11 872 transistors) runs and all 32 product bits settle to the right levels for every vector tried, but for "
                "most vectors some output carries a marginal runt pulse (a hazard that fires at one step size and not at half of it), so two runs "
                "differ by up to a rail for a few picoseconds: a property of the circuit, which a pointwise comparison of step sizes cannot pass")
-    covered = set(_OFFICIAL_SUITE + _EXTENDED_SUITE + LARGE_SUITE_ENTRIES) | {"c17", "s27", "c6288"}
-    return [BlockedCorrectnessCase("c6288", hazards)] + [BlockedCorrectnessCase(name, why) for name in bc.SUITE if name not in covered]
+    covered = set(_OFFICIAL_SUITE + _EXTENDED_SUITE + LARGE_SUITE_ENTRIES + HUGE_SUITE_ENTRIES) | {"c17", "s27", "c6288"}
+    return [BlockedCorrectnessCase("c6288", hazards)] + [BlockedCorrectnessCase(name, "no case written yet") for name in bc.SUITE if name not in covered]
 
 
 def _is_ground(node: str) -> bool:

@@ -93,6 +93,18 @@ class Netlist:
             return mapping[n]
         return f"{prefix}.{n}" if prefix else n
 
+    def tran(self) -> Optional[tuple]:
+        """``(step, stop)`` in seconds from the deck's ``.tran`` card, or ``None`` when it has none."""
+        from . import _native
+
+        for d in self.directives:
+            tok = re.sub(r"[(),]", " ", d).split()
+            if tok and tok[0].upper() == ".TRAN" and len(tok) >= 3:
+                step, stop = _native.parse_scaled(tok[1]), _native.parse_scaled(tok[2])
+                if step and stop and step > 0 and stop > 0:
+                    return float(step), float(stop)
+        return None
+
     def to_native(self, process: str = "TT", vdd: float = 1.8, temp: float = 27.0) -> dict:
         """The numeric, flattened netlist (the partition-file form) from the native parser."""
         from . import _native

@@ -20,7 +20,7 @@ from typing import Iterable, Optional
 import numpy as np
 
 from .correctness import (CorrectnessCase, WaveformData, blocked_official_correctness_cases, check_logic_levels, compare_waveforms,
-                          extended_phase1_correctness_cases, find_ngspice_binary, large_phase1_correctness_cases, phase1_automated_correctness_cases, run_nangila_waveform,
+                          extended_phase1_correctness_cases, find_ngspice_binary, huge_phase1_correctness_cases, large_phase1_correctness_cases, phase1_automated_correctness_cases, run_nangila_waveform,
                           run_ngspice_waveform, within_v1_contract)
 
 # Closed-form solutions, by case name.
@@ -40,7 +40,7 @@ def _run_case(case: CorrectnessCase, ngspice_bin: Optional[str]) -> dict:
             tr = _ANALYTIC[case.name](t)
             ref, oracle = WaveformData("analytic", path, list(tr), t.tolist(), {k: v.tolist() for k, v in tr.items()}), "closed form"
         else:
-            big = case.tier == "large"   # the dense solver is cubic in the circuit size
+            big = case.tier in ("large", "huge")   # the dense solver is cubic in the circuit size
             ref = run_nangila_waveform(path, tstop=case.tstop, dt=case.dt / 2, in_process=True, solver="lu" if big else "dense")
             oracle = "sparse solver, dt / 2" if big else "dense solver, dt / 2"
         lower = {n.lower(): n for n in cand.traces}
@@ -88,14 +88,28 @@ def _tier_summary(cases: list[dict]) -> dict:
             "total_wall_time_secs": sum(c["wall_time_secs"] for c in cases)}
 
 
-def generate_phase1_benchmark_report(include_extended: bool = False, include_large: bool = False, include_partitioned: bool = False) -> dict:
+def generate_phase1_benchmark_report(include_extended: bool = False, include_large: bool = False, include_partitioned: bool = False,
+                                     include_huge: bool = False, jobs: int = 1) -> dict:
+    """Runs the chosen tiers. ``jobs`` > 1 runs that many cases at a time in worker processes (the cases are independent;
+    per-case times then include whatever the cases cost one another in memory bandwidth)."""
     ngspice = find_ngspice_binary()
     cases = phase1_automated_correctness_cases()
     if include_extended:
         cases += extended_phase1_correctness_cases()
     if include_large:
         cases += large_phase1_correctness_cases()
-    rows = [_run_case(c, ngspice) for c in cases]
+    if include_huge:
+        cases += huge_phase1_correctness_cases()
+    if jobs > 1:
+        from concurrent.futures import ProcessPoolExecutor
+
+        # the longest cases first, so that the last worker does not start the ten-minute case when the others are done
+        order = sorted(range(len(cases)), key=lambda i: -len(cases[i].deck or ""))
+        with ProcessPoolExecutor(max_workers=jobs) as pool:
+            done = dict(zip(order, pool.map(_run_case, [cases[i] for i in order], [ngspice] * len(order))))
+        rows = [done[i] for i in range(len(cases))]
+    else:
+        rows = [_run_case(c, ngspice) for c in cases]
     if include_partitioned:
         by_name = {c.name: c for c in phase1_automated_correctness_cases() + extended_phase1_correctness_cases()}
         for name, k, mode in (("rc_ladder_400", 4, "in_process"), ("alu2", 4, "in_process"), ("adder8", 4, "in_process"),
@@ -103,7 +117,7 @@ def generate_phase1_benchmark_report(include_extended: bool = False, include_lar
             rows.append(_run_partitioned(by_name[name], k, mode))
     tiers = sorted({r["tier"] for r in rows})
     return {"generated": time.strftime("%Y-%m-%d %H:%M:%S"), "platform": f"{platform.system()} {platform.machine()}",
-            "oracle_tool": "ngspice" if ngspice else "built-in oracles (ngspice not installed)", "cases": rows,
+            "oracle_tool": "ngspice" if ngspice else "built-in oracles (ngspice not installed)", "jobs": jobs, "cases": rows,
             "tiers": {t: _tier_summary([r for r in rows if r["tier"] == t]) for t in tiers},
             "blocked": [{"name": b.name, "reason": b.reason} for b in blocked_official_correctness_cases()],
             "all_passed": all(r["passed"] for r in rows)}
@@ -135,10 +149,12 @@ def main(argv: Optional[list[str]] = None) -> int:
     ap.add_argument("--include-extended", action="store_true")
     ap.add_argument("--include-large", action="store_true", help="the suite entries of up to 6 000 transistors, against the gate-level logic")
     ap.add_argument("--include-partitioned", action="store_true", help="five cases split into partitions (threads and processes) against the single matrix")
+    ap.add_argument("--include-huge", action="store_true", help="the seven largest suite entries (12 000 to 150 000 transistors; up to ten minutes each)")
+    ap.add_argument("--jobs", type=int, default=1, help="cases run at a time (worker processes)")
     ap.add_argument("--output-json", default="artifacts/phase1_benchmark_report.json")
     ap.add_argument("--output-md", default="artifacts/phase1_benchmark_report.md")
     args = ap.parse_args(argv)
-    report = generate_phase1_benchmark_report(args.include_extended, args.include_large, args.include_partitioned)
+    report = generate_phase1_benchmark_report(args.include_extended, args.include_large, args.include_partitioned, args.include_huge, max(1, args.jobs))
     for path, text in ((args.output_json, json.dumps(report, indent=2)), (args.output_md, render_markdown_report(report))):
         os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
         Path(path).write_text(text)

@@ -199,7 +199,10 @@ def test_correctness_registry_and_logic_oracle(tmp_path):
     assert {c.tier for c in official} == {"passive", "nonlinear", "logic", "large"}
     assert len(cx.extended_phase1_correctness_cases()) == 13
     blocked = cx.blocked_official_correctness_cases()
-    assert {"s5378", "s38417", "c6288"} <= {b.name for b in blocked} and all(b.reason for b in blocked)
+    assert {b.name for b in blocked} == {"c6288"} and all(b.reason for b in blocked)
+    huge = cx.huge_phase1_correctness_cases()
+    assert [c.name for c in huge] == [n + "_auto" for n in ("s5378", "s9234", "s13207", "s15850", "s35932", "s38417", "s38584")]
+    assert {c.tier for c in huge} == {"huge"} and all(1 <= len(c.expected_levels) <= 16 for c in huge)
     large = cx.large_phase1_correctness_cases()
     assert len(large) == 10 and {c.tier for c in large} == {"large"} and not {c.name[:-5] for c in large} & {b.name for b in blocked}
     # the reference's names and signatures: cases of the suite are called <name>_auto, the lists take a repository root

@@ -621,3 +621,25 @@ def test_a_deck_that_includes_itself_ends(tmp_path):
     deck.write_text("* loop\n.include part.inc\n.include loop.sp\nR1 a 0 1k\nV1 a 0 1\n.end\n")
     nl = parse_netlist(str(deck))  # the cycle is cut, and the `.end` of the included file does not end the deck
     assert sorted(d.name for d in nl.devices) == ["R1", "R2", "V1"]
+
+
+def test_tran_card_gives_the_default_run_length(tmp_path):
+    import subprocess
+    import sys
+
+    from nangila_spice.correctness import find_nangila_binary
+    from nangila_spice.parser import parse_netlist
+
+    deck = tmp_path / "rc.sp"
+    deck.write_text("* rc\nV1 vdd 0 DC 1.8\nR1 vdd out 1k\nC1 out 0 10f\n.ic v(out)=0\n.tran 2p 40p\n.end\n")
+    assert parse_netlist(str(deck)).tran() == (2e-12, 40e-12)
+    out = tmp_path / "w.json"
+    proc = subprocess.run([find_nangila_binary(), "--partition", str(deck), "--waveform-json", str(out)], capture_output=True, text=True, timeout=60)
+    assert proc.returncode == 0, proc.stderr[-300:]
+    wave = json.loads(out.read_text())["waveform"]
+    assert len(wave) == 21 and math.isclose(wave[-1]["time"], 40e-12)
+    # flags win over the card, each on its own
+    proc = subprocess.run([find_nangila_binary(), "--partition", str(deck), "--dt", "1e-12", "--waveform-json", str(out)], capture_output=True, text=True, timeout=60)
+    assert proc.returncode == 0 and len(json.loads(out.read_text())["waveform"]) == 41
+    run = subprocess.run([sys.executable, "-m", "nangila_spice.cli", "run", str(deck), "--output-dir", str(tmp_path / "o")], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0 and "21 points" in run.stdout, run.stdout + run.stderr
