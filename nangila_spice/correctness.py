@@ -158,8 +158,10 @@ def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: 
     return WaveformData("nangila", netlist_path, names, [p["time"] for p in pts], {n: [p["voltages"].get(n, 0.0) for p in pts] for n in names})
 
 
-def run_ngspice_waveform(netlist_path: str, nodes: list[str], *, tstop: float, dt: float, binary: Optional[str] = None) -> WaveformData:
-    """Runs ``ngspice -b`` with a ``.control`` block that writes the listed nets; needs ngspice on PATH."""
+def run_ngspice_waveform(netlist_path: str, nodes: list[str], *, tstop: float, dt: float, binary: Optional[str] = None,
+                         use_initial_conditions: bool = False) -> WaveformData:
+    """Runs ``ngspice -b`` with a ``.control`` block that writes the listed nets; needs ngspice on PATH (or ``binary``).
+    ``use_initial_conditions`` starts the transient from the deck's ``.ic`` values (``uic``) instead of the DC point."""
     exe = binary or find_ngspice_binary()
     if exe is None:
         raise FileNotFoundError("ngspice is not installed")
@@ -167,7 +169,7 @@ def run_ngspice_waveform(netlist_path: str, nodes: list[str], *, tstop: float, d
     with tempfile.TemporaryDirectory() as tmp:
         data = os.path.join(tmp, "out.data")
         vec = " ".join(f"v({n})" for n in nodes)
-        control = f".control\nset wr_singlescale\ntran {dt!r} {tstop!r}\nwrdata {data} {vec}\nquit\n.endc\n"
+        control = f".control\nset wr_singlescale\ntran {dt!r} {tstop!r}{" uic" if use_initial_conditions else ""}\nwrdata {data} {vec}\nquit\n.endc\n"
         lines = [ln for ln in text.splitlines() if ln.strip().lower() != ".end"]
         deck = os.path.join(tmp, "deck.sp")
         Path(deck).write_text("\n".join(lines) + "\n" + control + ".end\n")

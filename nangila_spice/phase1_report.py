@@ -34,7 +34,8 @@ def _run_case(case: CorrectnessCase, ngspice_bin: Optional[str]) -> dict:
         cand = run_nangila_waveform(path, tstop=case.tstop, dt=case.dt, in_process=True)
         wall = time.perf_counter() - t0
         if ngspice_bin:
-            ref, oracle = run_ngspice_waveform(path, list(case.nodes), tstop=case.tstop, dt=case.dt, binary=ngspice_bin), "ngspice"
+            ref, oracle = run_ngspice_waveform(path, list(case.nodes), tstop=case.tstop, dt=case.dt, binary=ngspice_bin,
+                                                       use_initial_conditions=case.use_initial_conditions), "ngspice"
         elif case.name in _ANALYTIC:
             t = np.asarray(cand.times)
             tr = _ANALYTIC[case.name](t)

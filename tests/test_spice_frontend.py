@@ -392,3 +392,48 @@ def test_speculative_windows_roll_back_on_a_miss_and_keep_the_answer(tmp_path):
     b = np.asarray(part["values"])
     idx = [names.index(n) for n in part["node_names"]]
     assert np.abs(a[:, idx] - b).max() < 2e-3
+
+
+def test_ngspice_oracle_plumbing_with_a_stand_in(tmp_path):
+    """ngspice is not installed where these tests run, so a stand-in executable takes its place: it reads the deck and
+    the ``.control`` block the harness wrote (``tran <dt> <tstop> [uic]``, ``wrdata <file> v(a) v(b)``), solves the deck
+    with this package and writes the columns ``wrdata`` would. What is checked is the harness: the deck it hands over, the
+    control block, the parsing of the data file and the comparison that follows."""
+    import stat
+    import sys
+
+    from nangila_spice.correctness import compare_waveforms, run_nangila_waveform, run_ngspice_waveform, within_v1_contract
+
+    fake = tmp_path / "ngspice"
+    fake.write_text(f"""#!{sys.executable}
+import re, sys
+sys.path.insert(0, {repr(str(__import__('pathlib').Path(__file__).resolve().parents[1]))})
+assert sys.argv[1] == "-b"
+text = open(sys.argv[2]).read()
+ctl = text[text.lower().index(".control"):text.lower().index(".endc")]
+m = re.search(r"tran\\s+(\\S+)\\s+(\\S+)(\\s+uic)?", ctl)
+dt, tstop, uic = float(m.group(1)), float(m.group(2)), bool(m.group(3))
+w = re.search(r"wrdata\\s+(\\S+)\\s+(.*)", ctl)
+nodes = re.findall(r"v\\(([^)]+)\\)", w.group(2))
+deck = text[:text.lower().index(".control")] + ".end\\n"
+if not uic:
+    deck = "\\n".join(l for l in deck.splitlines() if not l.strip().lower().startswith(".ic")) + "\\n"
+open(sys.argv[2] + ".plain.sp", "w").write(deck)
+from nangila_spice.correctness import run_nangila_waveform
+wf = run_nangila_waveform(sys.argv[2] + ".plain.sp", tstop=tstop, dt=dt, in_process=True)
+with open(w.group(1), "w") as out:
+    for i, t in enumerate(wf.times):
+        out.write(" ".join([repr(float(t))] + [repr(float(wf.traces[n][i])) for n in nodes]) + "\\n")
+""")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    deck = tmp_path / "rc.sp"
+    deck.write_text("* rc\nV1 vdd 0 DC 1.8\nR1 vdd out 1k\nC1 out 0 10f\n.ic v(out)=0\n.end\n")
+    with_ic = run_ngspice_waveform(str(deck), ["vdd", "out"], tstop=50e-12, dt=1e-12, binary=str(fake), use_initial_conditions=True)
+    assert with_ic.tool == "ngspice" and len(with_ic.times) == 51 and with_ic.traces["out"][0] == 0.0 and with_ic.traces["out"][-1] > 1.7
+    from_dc = run_ngspice_waveform(str(deck), ["out"], tstop=50e-12, dt=1e-12, binary=str(fake))
+    assert abs(from_dc.traces["out"][0] - 1.8) < 1e-6  # without `uic` the run starts from the operating point
+    cmp_ = compare_waveforms(with_ic, run_nangila_waveform(str(deck), tstop=50e-12, dt=1e-12), vdd=1.8)
+    ok, profile = within_v1_contract(cmp_, nonlinear=False, vdd=1.8)
+    assert ok and cmp_.sample_count == 102 and cmp_.max_abs_error < 1e-9
+    with pytest.raises(RuntimeError, match="ngspice failed"):
+        run_ngspice_waveform(str(deck), ["out"], tstop=1e-11, dt=1e-12, binary=sys.executable)  # "python -b deck" writes no data file
