@@ -2,13 +2,11 @@
 
 Forward results are PyTorch's (cuBLAS GEMM with its bias epilogue; ``F.layer_norm``). What changes is
 the backward of the small reductions over the token dimension: the bias gradient of a linear layer
-and the weight / bias gradients of a LayerNorm, which in eager PyTorch cost 24 us and 72 us per call
-on the GPT-2 benchmark's [8192, 768] activations.
+and the weight / bias gradients of a LayerNorm, each of which is its own small reduction kernel in eager PyTorch.
 
-Off by default, ``NANGILA_FUSED_GRADS=1`` turns both on. Measured on the GPT-2 benchmark step (one B200): the column-sum
-kernel itself replaces 3.9 ms of serialised kernel time per step (launch list under ncu), but the step got slower end to
-end (12.98 ms -> 14.33 ms) because the host is barely ahead of the GPU in this eager step (20 steps take 11.7 ms each to enqueue and 12.6 ms to run)
-and every custom autograd function adds Python work per layer; the kernels pay off only where the step has host slack.
+Off by default, ``NANGILA_FUSED_GRADS=1`` turns both on. The kernels remove device time, but every custom autograd
+function adds Python work per layer, so they pay off only where the host runs well ahead of the GPU; in an eager step
+whose enqueue time is close to its device time the extra host work lands on the critical path.
 """
 from __future__ import annotations
 

@@ -113,8 +113,8 @@ class PredResEngine:
         self.fixed_gain = float(os.environ.get("NANGILA_PRED_GAIN", "1"))
         # with a zero gain the kernel skips the history loads except on every probe_every-th call
         self.probe_every = max(1, int(os.environ.get("NANGILA_PROBE_EVERY", "8")))
-        # two ranks use the kernel's gather mode (one quantization, two phases); from three ranks on the
-        # three-phase form is faster (at four: 13.37 against 13.82 ms per GPT-2 step)
+        # two ranks use the kernel's gather mode (one quantization, two phases); from three ranks on every rank would
+        # dequantize all contributions of every chunk itself, and the three-phase form does less work per rank
         self.gather_max_world = min(4, int(os.environ.get("NANGILA_GATHER_MAX_WORLD", "2")))
         # leave the history unwritten between probes while the gain is 0 (NANGILA_SKIP_HISTORY=0: always write it)
         self.skip_history = os.environ.get("NANGILA_SKIP_HISTORY", "1") != "0"
