@@ -159,3 +159,26 @@ def test_boundary_codec_error_is_one_quantisation_step(entries, bits):
             assert abs(decoded[i] - v) <= 0.5 * step * (1 + 1e-9) + 1e-15
         else:   # deltas below the codec's floor are not sent: the receiver keeps its prediction
             assert abs(v - p) < 1e-15
+
+
+@RUN
+@given(st.lists(st.tuples(st.floats(0.0, 1e-8), st.floats(-5.0, 5.0)), min_size=1, max_size=12), st.floats(-1e-9, 2e-8))
+def test_pwl_source_is_the_interpolant_of_its_increasing_points(points, t):
+    """Whatever the card holds (unsorted, repeated times), the source keeps the points whose time increases, is their
+    piecewise-linear interpolant, holds the end values outside, and its next corner is the next kept time."""
+    import json
+
+    flat = [x for p in points for x in p]
+    kept_t, kept_v = [], []
+    for pt, pv in points:
+        if not kept_t or pt > kept_t[-1]:
+            kept_t.append(pt)
+            kept_v.append(pv)
+    src = json.dumps({"Pwl": {"points": flat}})
+    got = N.source_value(src, t)
+    want = float(np.interp(t, kept_t, kept_v))
+    assert abs(got - want) <= 1e-9 * max(1.0, max(abs(v) for v in kept_v))
+    assert min(kept_v) - 1e-12 <= got <= max(kept_v) + 1e-12
+    back = json.loads(N.netlist_roundtrip(json.dumps({"name": "p", "num_nodes": 1, "elements": [
+        {"VoltageSource": {"pos": 1, "neg": 0, "source": {"Pwl": {"points": flat}}}}], "ghost_map": [], "node_names": ["a"], "initial_conditions": []})))
+    assert back["elements"][0]["VoltageSource"]["source"]["Pwl"]["points"] == [x for p in zip(kept_t, kept_v) for x in p]
