@@ -1,5 +1,8 @@
 // Python module nangila_spice._native: the simulator core for tests, the orchestrator and notebooks.
 // Netlists cross the boundary as JSON text (the partition-file form), numeric data as lists.
+#include <algorithm>
+#include <unordered_map>
+
 #include <pybind11/functional.h>
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
@@ -72,14 +75,27 @@ PYBIND11_MODULE(_native, m) {
     // ---- simulation ---------------------------------------------------------------------------
     m.def("simulate", [](const std::string& netlist_json, double tstop, double dt, double reltol, const std::string& solver, uint32_t record_every,
                          uint32_t predict_depth, std::vector<std::tuple<uint32_t, double, std::vector<std::pair<uint64_t, double>>>> inject,
-                         std::vector<double> rollbacks, bool adaptive, double lte_reltol, double max_step_factor) {
+                         std::vector<double> rollbacks, bool adaptive, double lte_reltol, double max_step_factor, std::vector<std::string> record_nodes) {
         Netlist nl = Netlist::from_json(Json::parse(netlist_json));
         std::vector<std::string> names = nl.names_or_default();
+        std::vector<uint32_t> keep;
+        if (!record_nodes.empty()) {  // names compared without case; unknown names are skipped
+            auto lower = [](std::string v) { for (auto& c : v) c = char(std::tolower((unsigned char)c)); return v; };
+            std::unordered_map<std::string, uint32_t> at;
+            for (uint32_t i = 0; i < names.size(); ++i) at.emplace(lower(names[i]), i);
+            std::vector<std::string> kept;
+            for (auto& want : record_nodes) {
+                auto it = at.find(lower(want));
+                if (it != at.end() && std::find(keep.begin(), keep.end(), it->second) == keep.end()) { keep.push_back(it->second); kept.push_back(names[it->second]); }
+            }
+            names = kept;
+        }
         GhostBuffer ghosts(predict_depth);
         for (auto& g : nl.ghost_map) ghosts.add(GhostNode(g.net_id, g.owner));
         SimConfig cfg;
         cfg.tstop = tstop; cfg.dt = dt; cfg.reltol = reltol; cfg.record_every = std::max(1u, record_every); cfg.predict_depth = predict_depth;
         cfg.adaptive = adaptive; cfg.lte_reltol = lte_reltol; cfg.max_step_factor = max_step_factor;
+        cfg.record_nodes = keep;
         CommLayer comm(0, 1);
         for (auto& msg : inject) { ResidualMessage r; r.from = std::get<0>(msg); r.time = std::get<1>(msg); r.updates = std::get<2>(msg); comm.inject_message(r); }
         for (double t : rollbacks) comm.inject_rollback({1, t});
@@ -110,7 +126,8 @@ PYBIND11_MODULE(_native, m) {
         return out;
     }, py::arg("netlist_json"), py::arg("tstop"), py::arg("dt"), py::arg("reltol") = 1e-3, py::arg("solver") = "lu", py::arg("record_every") = 1,
        py::arg("predict_depth") = 5, py::arg("inject") = std::vector<std::tuple<uint32_t, double, std::vector<std::pair<uint64_t, double>>>>{},
-       py::arg("rollbacks") = std::vector<double>{}, py::arg("adaptive") = false, py::arg("lte_reltol") = 2e-2, py::arg("max_step_factor") = 64.0);
+       py::arg("rollbacks") = std::vector<double>{}, py::arg("adaptive") = false, py::arg("lte_reltol") = 2e-2, py::arg("max_step_factor") = 64.0,
+       py::arg("record_nodes") = std::vector<std::string>{});
 
     m.def("dc_operating_point", [](const std::string& netlist_json) {
         SolverEngine e(Netlist::from_json(Json::parse(netlist_json)));

@@ -27,6 +27,9 @@ struct SimConfig {
     // trapezoidal step itself: at 2 % the observed outputs of the logic cases stay within 3 mV of a run at a quarter of dt.
     bool adaptive = false;
     double lte_reltol = 2e-2, lte_abstol = 1e-4, max_step_factor = 64.0;
+    // Unknowns (0-based) whose values the waveform keeps, in this order; empty = all of them. A deck of 100 000 nets
+    // over thousands of steps is gigabytes of waveform of which a comparison reads a handful of columns.
+    std::vector<uint32_t> record_nodes;
 };
 
 struct SimStats {
@@ -64,7 +67,7 @@ public:
         auto t0 = std::chrono::steady_clock::now();
         PartitionState state = engine_->initial_state();
         waveform.clear();
-        waveform.push_back({state.time, state.voltages});
+        waveform.push_back({state.time, recorded(state.voltages)});
         history_.clear();
         uint64_t step = 0;
         // the loop counts steps instead of comparing accumulated floating-point time with tstop, so
@@ -94,7 +97,7 @@ public:
             if (!engine_->solve_step(state, predictions, config.dt, next)) break;
             ++step;
             next.time = double(step_origin_ + step) * config.dt;
-            if (step % config.record_every == 0 || step == planned) waveform.push_back({next.time, next.voltages});
+            if (step % config.record_every == 0 || step == planned) waveform.push_back({next.time, recorded(next.voltages)});
             if (history_.size() >= config.max_history) history_.pop_front();
             history_.push_back(state);
             state = std::move(next);
@@ -106,12 +109,21 @@ public:
         return state;
     }
 
+    // The columns of a solution the waveform keeps (config.record_nodes; all when that is empty).
+    std::vector<double> recorded(const std::vector<double>& v) const {
+        if (config.record_nodes.empty()) return v;
+        std::vector<double> out(config.record_nodes.size(), 0.0);
+        for (size_t k = 0; k < out.size(); ++k)
+            if (config.record_nodes[k] < v.size()) out[k] = v[config.record_nodes[k]];
+        return out;
+    }
+
     // Variable-step form of run(): same waveform grid, the solver chooses its own steps in between.
     PartitionState run_adaptive() {
         auto t0 = std::chrono::steady_clock::now();
         PartitionState state = engine_->initial_state(), older{0};
         waveform.clear();
-        waveform.push_back({state.time, state.voltages});
+        waveform.push_back({state.time, recorded(state.voltages)});
         stats = SimStats{};
         const double dt = config.dt, tstop = config.tstop;
         const uint64_t planned = dt > 0 ? uint64_t(std::ceil(tstop / dt - 1e-9)) : 0;
@@ -162,9 +174,18 @@ public:
                 const double tg = double(emitted + 1) * dt, w = step > 0.0 ? std::min(1.0, std::max(0.0, (tg - t) / step)) : 1.0;
                 ++emitted;
                 if (emitted % config.record_every == 0 || emitted == planned) {
-                    std::vector<double> v(next.voltages.size());
-                    for (size_t i = 0; i < v.size(); ++i) v[i] = state.voltages[i] + w * (next.voltages[i] - state.voltages[i]);
-                    waveform.push_back({tg, std::move(v)});
+                    if (config.record_nodes.empty()) {
+                        std::vector<double> v(next.voltages.size());
+                        for (size_t i = 0; i < v.size(); ++i) v[i] = state.voltages[i] + w * (next.voltages[i] - state.voltages[i]);
+                        waveform.push_back({tg, std::move(v)});
+                    } else {
+                        std::vector<double> v(config.record_nodes.size(), 0.0);
+                        for (size_t k = 0; k < v.size(); ++k) {
+                            const size_t i = config.record_nodes[k];
+                            if (i < next.voltages.size()) v[k] = state.voltages[i] + w * (next.voltages[i] - state.voltages[i]);
+                        }
+                        waveform.push_back({tg, std::move(v)});
+                    }
                 }
             }
             ++stats.solver_steps;

@@ -122,21 +122,26 @@ def find_ngspice_binary() -> Optional[str]:
 
 def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: float = 1e-3, process: str = "TT", vdd: float = 1.8,
                          temp: float = 27.0, solver: str = "lu", binary: Optional[str] = None, in_process: bool = False,
-                         record_every: int = 1, allow_partial: bool = False, adaptive: bool = False) -> WaveformData:
+                         record_every: int = 1, allow_partial: bool = False, adaptive: bool = False,
+                         nodes: Optional[list] = None) -> WaveformData:
     """Runs this simulator on a deck: through the ``nangila-node`` process (default) or in-process. A run that
     stops before ``tstop`` (Newton did not converge even after step cutting) raises unless ``allow_partial``.
-    ``adaptive``: the solver chooses its own steps between the points of the ``dt`` grid the waveform is written on."""
+    ``adaptive``: the solver chooses its own steps between the points of the ``dt`` grid the waveform is written on.
+    ``nodes``: keep these nets only (names compared without case); a deck of 100 000 nets over thousands of samples
+    is gigabytes as Python lists, and a comparison looks at a handful of them."""
     if in_process:
         from . import _native
 
         text = Path(netlist_path).read_text()
         js, _ = _native.parse_spice(text, Path(netlist_path).name, process, vdd, temp)
-        r = _native.simulate(js, tstop, dt, reltol, solver, record_every, adaptive=adaptive)
+        r = _native.simulate(js, tstop, dt, reltol, solver, record_every, adaptive=adaptive, record_nodes=list(nodes or []))
         if not r["stats"]["completed"] and not allow_partial:
             raise RuntimeError(f"{netlist_path}: stopped at t = {r['time'][-1]:.4g} s of {tstop:.4g} s: Newton did not converge")
         vals = np.asarray(r["values"], float)
-        return WaveformData("nangila", netlist_path, list(r["node_names"]), list(r["time"]),
-                            {n: vals[:, j].tolist() for j, n in enumerate(r["node_names"]) if j < vals.shape[1]})
+        wanted = None if nodes is None else {n.lower() for n in nodes}
+        names = [n for j, n in enumerate(r["node_names"]) if j < vals.shape[1] and (wanted is None or n.lower() in wanted)]
+        col = {n: j for j, n in enumerate(r["node_names"])}
+        return WaveformData("nangila", netlist_path, names, list(r["time"]), {n: vals[:, col[n]].tolist() for n in names})
     exe = binary or find_nangila_binary()
     if exe is None:
         raise FileNotFoundError("nangila-node is not built: run `python -m nangila._build --spice`")
@@ -153,7 +158,8 @@ def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: 
             raise RuntimeError(f"nangila-node failed ({proc.returncode}): {proc.stderr[-500:]}")
         with open(out) as f:
             d = json.load(f)
-    names = d["node_names"]
+    wanted = None if nodes is None else {n.lower() for n in nodes}
+    names = [n for n in d["node_names"] if wanted is None or n.lower() in wanted]
     pts = d["waveform"]
     return WaveformData("nangila", netlist_path, names, [p["time"] for p in pts], {n: [p["voltages"].get(n, 0.0) for p in pts] for n in names})
 

@@ -643,3 +643,16 @@ def test_tran_card_gives_the_default_run_length(tmp_path):
     assert proc.returncode == 0 and len(json.loads(out.read_text())["waveform"]) == 41
     run = subprocess.run([sys.executable, "-m", "nangila_spice.cli", "run", str(deck), "--output-dir", str(tmp_path / "o")], capture_output=True, text=True, timeout=120)
     assert run.returncode == 0 and "21 points" in run.stdout, run.stdout + run.stderr
+
+
+def test_record_nodes_keeps_the_named_columns_only():
+    deck = "* ladder\nV1 a 0 PULSE(0 1.8 10p 5p 5p 40p 100p)\nR1 a b 1k\nC1 b 0 5f\nR2 b c 1k\nC2 c 0 5f\n.end\n"
+    js, _ = N.parse_spice(deck)
+    full = N.simulate(js, 100e-12, 1e-12)
+    for adaptive in (False, True):
+        part = N.simulate(js, 100e-12, 1e-12, adaptive=adaptive, record_nodes=["C", "a", "nosuch", "c"])
+        assert part["node_names"] == ["c", "a"] and np.asarray(part["values"]).shape == (101, 2)
+        ref = N.simulate(js, 100e-12, 1e-12, adaptive=adaptive)
+        cols = [ref["node_names"].index(n) for n in ("c", "a")]
+        assert np.array_equal(np.asarray(part["values"]), np.asarray(ref["values"])[:, cols])
+        assert len(part["final"]) == len(full["final"])  # the final state is whole
