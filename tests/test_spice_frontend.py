@@ -185,6 +185,18 @@ def test_solver_binary_json_and_nz_outputs(tmp_path):
 
     assert compare_waveforms(nz, {"out": direct})["within_bound"]
     assert "out" in plot_nz(str(wz), ["out"], output=str(tmp_path / "p.png")) or os.path.exists(tmp_path / "p.png")
+    # the reference's calling forms: a loaded waveform as the source, its keyword names, one net against its original
+    text = plot_nz(nz, nodes=["out", "nosuch"], title="rc", show_error_bound=True, output_path=str(tmp_path / "p.txt"), time_scale="ps")
+    assert os.path.exists(tmp_path / "p.txt") or os.path.exists(tmp_path / "p.png") or "rc" in text
+    times = [p["time"] for p in d["waveform"]]
+    one = compare_waveforms(times, direct, str(wz), "out", title="t", output_path=str(tmp_path / "c.png"))
+    assert one["within_bound"] and set(one["per_node"]) == {"out"}
+    coarse = compare_waveforms(times[::2], direct[::2], nz, node="out")   # another time axis: interpolated onto the file's
+    assert coarse["max_abs_error"] < 0.05 and not coarse["within_bound"]
+    with pytest.raises(KeyError):
+        compare_waveforms(times, direct, nz, "nosuch")
+    with pytest.raises(TypeError):
+        plot_nz(42)
     assert subprocess.run([exe, "--partition", "/nonexistent.sp"], capture_output=True).returncode == 1
     assert subprocess.run([exe, "--bogus"], capture_output=True).returncode == 2
     demo = subprocess.run([exe, "--demo", "--tstop", "5e-11"], capture_output=True, text=True)
