@@ -102,7 +102,11 @@ def invoke_phase1_report(args) -> int:
 def invoke_view(args) -> int:
     from .nz_viewer import plot_nz
 
-    print(plot_nz(args.file, args.nodes or None, args.output))
+    try:
+        print(plot_nz(args.file, args.nodes or None, args.output))
+    except (OSError, ValueError) as exc:  # unreadable, truncated or not a .nz file
+        print(f"Error: {args.file}: {exc}", file=sys.stderr)
+        return 1
     return 0
 
 
