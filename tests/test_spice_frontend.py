@@ -291,6 +291,13 @@ def test_scaling_study_report_and_cli(tmp_path):
     nl = ns.parse_netlist(deck)
     dot = visualize_partitions(nl, ns.partition_netlist(nl, 2, "bisect"))
     assert dot.startswith("graph partitions {") and "style=dashed" in dot
+    # the reference's form: the circuit graph first, a title, devices only; an image request without matplotlib falls back to DOT
+    pr = ns.partition_netlist(nl, 2, "bisect")
+    cg = ns.build_circuit_graph(nl.flatten())
+    devices_only = visualize_partitions(cg, pr, title="two parts", show_nets=False)
+    assert 'label="two parts"' in devices_only and "shape=ellipse" not in devices_only and "shape=box" in devices_only
+    written = visualize_partitions(cg, pr, output_path=str(tmp_path / "parts.png"), figsize=(6, 4))
+    assert os.path.exists(written) and written.endswith((".png", ".dot"))
     hw = ns.discover_hardware()
     assert hw.cpu_count >= 1 and "cores" in hw.summary()
 
