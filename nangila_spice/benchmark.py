@@ -91,13 +91,27 @@ def generate_rc_ladder_netlist(n_stages: int, r: float = 1e3, c: float = 1e-12) 
     return "\n".join(lines) + "\n"
 
 
-def run_scaling_study(netlist_text: str, name: str, partition_counts: Optional[List[int]] = None, tstop: float = 200e-12, dt: float = 1e-12,
-                      method: str = "auto") -> BenchmarkSuite:
-    """The same deck at several partition counts; errors are against the single-matrix run."""
+def run_scaling_study(netlist_text, name=None, partition_counts: Optional[List[int]] = None, tstop: float = 200e-12, dt: float = 1e-12,
+                      method: str = "auto", *, label: Optional[str] = None) -> BenchmarkSuite:
+    """The same deck at several partition counts; errors are against the single-matrix run.
+
+    Also the reference's form, ``run_scaling_study(circuit_generator, sizes, partition_counts, label="Scaling Study")``
+    (benchmark.py:175-219, where the figures are estimates): every size the generator is called with is simulated at
+    every partition count, and the results of all sizes come back in one suite."""
+    if callable(netlist_text):
+        generator, sizes = netlist_text, list(name or [])
+        title = label or "Scaling Study"
+        suite = BenchmarkSuite(name=title, timestamp=time.strftime("%Y-%m-%d %H:%M:%S"), platform=f"{platform.system()} {platform.machine()}")
+        for size in sizes:
+            one = run_scaling_study(generator(size), f"{title.replace(' ', '_')}_{size}", partition_counts, tstop, dt, method)
+            for r in one.results:
+                suite.add(r)
+        return suite
     import numpy as np
 
     from .orchestrator import SimulationConfig, run_simulation
 
+    name = name or label or "scaling"
     suite = BenchmarkSuite(name=name, timestamp=time.strftime("%Y-%m-%d %H:%M:%S"), platform=f"{platform.system()} {platform.machine()}")
     with tempfile.TemporaryDirectory() as tmp:
         path = os.path.join(tmp, f"{name}.sp")

@@ -272,6 +272,10 @@ def test_scaling_study_report_and_cli(tmp_path):
 
     md = generate_performance_report(suite, str(tmp_path / "perf"))
     assert os.path.exists(md) and "ladder30_k2" in open(md).read() and "Average speedup" in suite.summary()
+    # the reference's form: a generator, sizes, partition counts; here every combination is really simulated
+    study = run_scaling_study(generate_rc_ladder_netlist, [10, 20], [1, 2], label="RC study", tstop=40e-12)
+    assert [(r.element_count, r.partition_count) for r in study.results] == [(21, 1), (22, 2), (41, 1), (42, 2)] and study.name == "RC study"
+    assert all(r.timesteps == 40 and r.wall_time_secs > 0 for r in study.results)
     env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     deck = _write(tmp_path, "rc.sp", generate_rc_ladder_netlist(8, 1e3, 10e-15))
     run = subprocess.run([sys.executable, "-m", "nangila_spice.cli", "run", deck, "--partitions", "2", "--tstop", "5e-11", "--method", "bisect",
