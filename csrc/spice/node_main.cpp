@@ -3,7 +3,7 @@
 //   nangila-node --partition deck.sp|part.json [--node-id N] [-k TOTAL] [--predict-depth D]
 //                [--reltol R] [--tstop T] [--dt DT] [--process TT|FF|SS|FS|SF] [--vdd V] [--temp C]
 //                [--waveform-json out.json] [--waveform-nz out.nz] [--solver lu|dense|krylov|cuda]
-//                [--record-every K] [--adaptive] [--demo]
+//                [--record-every K] [--record-nodes A,B,...] [--adaptive] [--demo]
 //                [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T]]
 //
 // With --rendezvous and -k > 1 the process is one of TOTAL that advance in lockstep and exchange boundary voltages
@@ -12,6 +12,7 @@
 //
 // Flag set and the waveform JSON layout ({netlist, node_names, waveform: [{time, voltages{}}],
 // stats{}}) follow the reference's CLI (nangila-spice/nangila-node/src/main.rs:21-132).
+#include <algorithm>
 #include <unistd.h>
 
 #include <cstdio>
@@ -34,6 +35,7 @@ struct Args {
     int connect_timeout_ms = 30000, io_timeout_ms = 30000;
     uint32_t node_id = 0, total = 1, predict_depth = 5, record_every = 1, threads = 1;
     double reltol = 1e-3, tstop = 1e-6, dt = 1e-12, vdd = 1.8, temp = 27.0, nz_tol = 1e-6;
+    std::string record_nodes;                    // comma-separated net names: the waveform keeps these only (single partition)
     bool tstop_given = false, dt_given = false;  // a deck's `.tran` card fills in whichever was not given
     bool demo = false, bench = false, lockstep = false, adaptive = false;
 };
@@ -43,7 +45,7 @@ static void usage() {
                  "usage: nangila-node [--partition FILE | --demo] [--node-id N] [-k TOTAL] [--predict-depth D]\n"
                  "                    [--reltol R] [--tstop T] [--dt DT] [--process P] [--vdd V] [--temp C]\n"
                  "                    [--waveform-json OUT] [--waveform-nz OUT] [--nz-tol E] [--solver lu|dense|krylov|cuda]\n"
-                 "                    [--record-every K] [--adaptive] [--partitions A.json,B.json,... [--threads T]] [--bench]\n"
+                 "                    [--record-every K] [--record-nodes A,B,...] [--adaptive] [--partitions A.json,B.json,... [--threads T]] [--bench]\n"
                  "                    [--rendezvous DIR [--bind HOST] [--connect-timeout-ms T] [--io-timeout-ms T] [--lockstep]]\n");
 }
 
@@ -59,6 +61,7 @@ static bool parse_args(int argc, char** argv, Args& a) {
         else if (f == "--bench") a.bench = true;
         else if (f == "--lockstep") a.lockstep = true;
         else if (f == "--adaptive") a.adaptive = true;
+        else if (f == "--record-nodes") { if (!(v = need("--record-nodes"))) return false; a.record_nodes = v; }
         else if (f == "--partitions") { if (!(v = need("--partitions"))) return false; a.partitions = v; }
         else if (f == "-h" || f == "--help") { usage(); std::exit(0); }
         else if (f == "--partition" || f == "-p") { if (!(v = need("--partition"))) return false; a.partition = v; }
@@ -277,6 +280,24 @@ static int run(int argc, char** argv) {
     cfg.tstop = a.tstop; cfg.dt = a.dt; cfg.reltol = a.reltol; cfg.predict_depth = a.predict_depth; cfg.record_every = a.record_every;
     cfg.adaptive = a.adaptive;   // variable internal step, waveform still on the dt grid (single partition only)
     std::vector<std::string> names = nl.names_or_default();
+    const std::vector<std::string> all_names = names;
+    if (!a.record_nodes.empty()) {
+        // the waveform keeps the named nets only (compared without case; names the deck does not have are skipped)
+        auto lower = [](std::string v) { for (auto& c : v) c = char(std::tolower((unsigned char)c)); return v; };
+        std::vector<std::string> kept;
+        std::stringstream list(a.record_nodes);
+        std::string want;
+        while (std::getline(list, want, ',')) {
+            for (uint32_t i = 0; i < names.size(); ++i)
+                if (lower(names[i]) == lower(want) && std::find(cfg.record_nodes.begin(), cfg.record_nodes.end(), i) == cfg.record_nodes.end()) {
+                    cfg.record_nodes.push_back(i);
+                    kept.push_back(names[i]);
+                    break;
+                }
+        }
+        if (cfg.record_nodes.empty()) std::fprintf(stderr, "warning: --record-nodes names no net of this deck; the waveform keeps all of them\n");
+        else names = kept;
+    }
     std::string name = nl.name;
     TransientSolver solver(std::move(nl), std::move(ghosts), CommLayer(a.node_id, a.total), cfg);
     solver.engine().newton.config.reltol = a.reltol;
@@ -306,7 +327,7 @@ static int run(int argc, char** argv) {
         std::fprintf(stderr, "device linear solver: %llu solves on the GPU, %llu fell back to the sparse LU%s\n", (unsigned long long)ls.stats.device_solves,
                      (unsigned long long)ls.stats.krylov_fallbacks, ls.cuda_error ? " (kernel library not usable: every solve ran on the host)" : "");
     }
-    for (size_t i = 0; i < names.size() && i < fin.voltages.size() && i < 16; ++i) std::fprintf(stderr, "  V(%s) = %.6f\n", names[i].c_str(), fin.voltages[i]);
+    for (size_t i = 0; i < all_names.size() && i < fin.voltages.size() && i < 16; ++i) std::fprintf(stderr, "  V(%s) = %.6f\n", all_names[i].c_str(), fin.voltages[i]);
     try {
         if (!a.waveform_json.empty()) write_json(a.waveform_json, name, names, solver.waveform, st);
         if (!a.waveform_nz.empty()) write_nz(a.waveform_nz, names, solver.waveform, a.nz_tol);

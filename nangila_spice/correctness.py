@@ -151,6 +151,8 @@ def run_nangila_waveform(netlist_path: str, *, tstop: float, dt: float, reltol: 
                "--vdd", repr(vdd), "--temp", repr(temp), "--solver", solver, "--record-every", str(record_every), "--waveform-json", out]
         if adaptive:
             cmd.append("--adaptive")
+        if nodes:
+            cmd += ["--record-nodes", ",".join(nodes)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode == 3 and not allow_partial:
             raise RuntimeError(f"{netlist_path}: stopped before tstop: {proc.stderr[-300:]}")

@@ -656,3 +656,25 @@ def test_record_nodes_keeps_the_named_columns_only():
         cols = [ref["node_names"].index(n) for n in ("c", "a")]
         assert np.array_equal(np.asarray(part["values"]), np.asarray(ref["values"])[:, cols])
         assert len(part["final"]) == len(full["final"])  # the final state is whole
+
+
+def test_solver_process_records_the_named_nets_only(tmp_path):
+    import subprocess
+
+    from nangila_spice.correctness import find_nangila_binary, run_nangila_waveform
+
+    deck = tmp_path / "ladder.sp"
+    deck.write_text("* ladder\nV1 a 0 PULSE(0 1.8 10p 5p 5p 40p 100p)\nR1 a b 1k\nC1 b 0 5f\nR2 b c 1k\nC2 c 0 5f\n.tran 1p 60p\n.end\n")
+    out = tmp_path / "w.json"
+    proc = subprocess.run([find_nangila_binary(), "--partition", str(deck), "--record-nodes", "C,a,nosuch", "--waveform-json", str(out),
+                           "--waveform-nz", str(tmp_path / "w.nz")], capture_output=True, text=True, timeout=60)
+    assert proc.returncode == 0, proc.stderr[-300:]
+    d = json.loads(out.read_text())
+    assert d["node_names"] == ["c", "a"] and set(d["waveform"][-1]["voltages"]) == {"c", "a"} and len(d["waveform"]) == 61
+    assert "V(b)" in proc.stderr   # the final values printed are still those of every net
+    from nangila_spice.nz_reader import read_nz
+
+    assert read_nz(str(tmp_path / "w.nz")).node_names == ["c", "a"]
+    full = run_nangila_waveform(str(deck), tstop=60e-12, dt=1e-12)
+    part = run_nangila_waveform(str(deck), tstop=60e-12, dt=1e-12, nodes=["c"])
+    assert part.node_names == ["c"] and np.allclose(part.traces["c"], full.traces["c"], atol=1e-12)
