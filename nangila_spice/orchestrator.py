@@ -69,6 +69,7 @@ class SimulationConfig:
     temp: float = 27.0
     solver: str = "lu"
     record_every: int = 1
+    record_nodes: Optional[list] = None  # single-matrix runs: the waveform keeps these nets only (names compared without case)
     threads: Optional[int] = None  # worker threads of the in-process partitioned run (default: one per partition, at most the core count)
 
 
@@ -155,7 +156,7 @@ def _single_run(config: SimulationConfig, flat: dict, adaptive: bool = False) ->
 
         enable_device_solver()
     r = _native.simulate(json.dumps(flat), config.tstop, config.dt, config.reltol, config.solver, config.record_every, config.predict_depth,
-                         adaptive=adaptive)
+                         adaptive=adaptive, record_nodes=list(config.record_nodes or []))
     return Waveform.from_native(r, title=flat.get("name", "")), {"stats": r["stats"], "newton": r["newton"]}
 
 

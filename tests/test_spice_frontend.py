@@ -460,3 +460,11 @@ with open(w.group(1), "w") as out:
     assert ok and cmp_.sample_count == 102 and cmp_.max_abs_error < 1e-9
     with pytest.raises(RuntimeError, match="ngspice failed"):
         run_ngspice_waveform(str(deck), ["out"], tstop=1e-11, dt=1e-12, binary=sys.executable)  # "python -b deck" writes no data file
+
+
+def test_simulate_keeps_the_requested_nets_only():
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "reference_circuits")
+    res = ns.simulate(os.path.join(root, "inverter.sp"), tstop=2e-10, dt=1e-12, record_nodes=["OUT"])
+    assert res.success and res.waveform.node_names == ["out"] and res.waveform.num_points == 201
+    full = ns.simulate(os.path.join(root, "inverter.sp"), tstop=2e-10, dt=1e-12)
+    assert np.array_equal(res.waveform.traces["out"], full.waveform.traces["out"]) and len(full.waveform.node_names) == 4
