@@ -277,13 +277,32 @@ private:
     // Decks written by tools often start with an element instead of a title. A first line counts as an element when it
     // starts with an element letter and has the shape of that card: a two-terminal element or source has nothing but values
     // (numbers, expressions in quotes or braces, source keywords, `name=value`) after its nodes, a diode four fields, a
-    // MOSFET six, a sub-circuit call three. "inverter with a 10 fF load" is a title, "I1 0 n1 1m" is not.
-    static bool first_line_is_card(char letter, const std::vector<std::string>& tok) {
+    // MOSFET six, a sub-circuit call three, and the model / sub-circuit they name is defined in the deck.
+    // "inverter with a 10 fF load" is a title, "I1 0 n1 1m" is not.
+    static bool first_line_is_card(char letter, const std::vector<std::string>& tok, const std::string& deck) {
         if (tok.size() < 3 || tok[0].size() < 2 || !std::isalnum((unsigned char)tok[0][1])) return false;
+        // whether the deck has a `.model <name>` / `.subckt <name>` card
+        auto defines = [&deck](const char* directive, const std::string& name) {
+            std::istringstream in(deck);
+            std::string line, want = upper(name);
+            while (std::getline(in, line)) {
+                std::istringstream ls(line);
+                std::string a, b;
+                ls >> a >> b;
+                if (upper(a) == directive && upper(b) == want) return true;
+            }
+            return false;
+        };
         switch (letter) {
-            case 'D': return tok.size() >= 4;
-            case 'M': return tok.size() >= 6;
-            case 'X': return true;
+            // "Diode bridge rectifier circuit" and "Mixer with two local oscillator inputs" have the field count of a
+            // card, so the model or sub-circuit the line would name has to exist in the deck
+            case 'D': return tok.size() >= 4 && defines(".MODEL", tok[3]);
+            case 'M': return tok.size() >= 6 && defines(".MODEL", tok[5]);
+            case 'X': {
+                size_t last = tok.size() - 1;
+                while (last > 2 && tok[last].find('=') != std::string::npos) --last;
+                return defines(".SUBCKT", tok[last]);
+            }
             case 'R': case 'C': case 'L': case 'V': case 'I': {
                 // everything after the two nodes is a value, a source keyword or a `name=value` parameter
                 auto value_like = [](const std::string& t) {
@@ -320,7 +339,7 @@ private:
             if (first_line) {
                 first_line = false;
                 char ch = char(std::toupper((unsigned char)line[0]));
-                if (!(ch == '.' || first_line_is_card(ch, split(line)))) continue;
+                if (!(ch == '.' || first_line_is_card(ch, split(line), text))) continue;
             }
             if (line[0] == '+') {
                 if (!out.empty()) out.back() += " " + line.substr(1);

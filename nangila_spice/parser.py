@@ -120,16 +120,28 @@ class Netlist:
 _VALUE_LIKE = re.compile(r"^([+-]?(\d|\.\d)|[{']|.*=|(DC|AC|PULSE|SIN|PWL|EXP)$)", re.IGNORECASE)
 
 
-def _first_line_is_card(letter: str, line: str) -> bool:
+def _first_line_is_card(letter: str, line: str, deck: str = "") -> bool:
     """Whether the first line of a deck is an element rather than a title (same rule as the native parser): it starts
-    with an element letter and has the shape of that card, e.g. nothing but values and parameters after the nodes of a two-terminal element."""
+    with an element letter and has the shape of that card: nothing but values and parameters after the nodes of a
+    two-terminal element; for a diode, a MOSFET or a sub-circuit call the model / sub-circuit it names is defined in the
+    deck ("Diode bridge rectifier circuit" has the field count of a diode card)."""
     tok = re.sub(r"[(),]", " ", line).split()
     if len(tok) < 3 or len(tok[0]) < 2 or not tok[0][1].isalnum():
         return False
     if letter in "RCLVI":
         return len(tok) >= 4 and all(_VALUE_LIKE.match(t) for t in tok[3:])
-    need = {"D": 4, "M": 6, "X": 3}.get(letter, 4 if letter in "QJEG" else None)
-    return need is not None and len(tok) >= need
+
+    def defines(directive: str, name: str) -> bool:
+        return re.search(rf"^\s*\{directive}\s+{re.escape(name)}(\s|$)", deck, re.IGNORECASE | re.MULTILINE) is not None
+
+    if letter == "D":
+        return len(tok) >= 4 and defines(".model", tok[3])
+    if letter == "M":
+        return len(tok) >= 6 and defines(".model", tok[5])
+    if letter == "X":
+        plain = [t for t in tok[1:] if "=" not in t]
+        return len(plain) >= 2 and defines(".subckt", plain[-1])
+    return letter in "QJEG" and len(tok) >= 4
 
 
 def _statements(text: str) -> list[str]:
@@ -146,7 +158,7 @@ def _statements(text: str) -> list[str]:
         if first:
             first = False
             head = line[0].upper()
-            if not (head == "." or _first_line_is_card(head, line)):
+            if not (head == "." or _first_line_is_card(head, line, text)):
                 out.append("*TITLE* " + line)
                 continue
         if line.startswith("+"):

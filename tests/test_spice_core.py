@@ -584,6 +584,14 @@ def test_first_line_title_rule_and_includes(tmp_path):
                                  ("C1 a 0 {cval} ic=0\n.param cval=1p\nV1 a 0 1\n", "", 2), ("VIN in 0 PULSE(0 1.8 100p 20p 20p 400p 1n)\nR1 in 0 1k\n", "", 2)):
         nl = parse_netlist_text(text)
         assert (nl.title or "") == title and nl.num_devices == devices and len(nl.to_native()["elements"]) == devices, text
+    # a diode, MOSFET or sub-circuit line has to name something the deck defines; prose with the same field count does not
+    cards = ".model dm D (is=1e-14)\n.model nch NMOS (vto=0.45 kp=200u)\n.subckt inv a y\nR1 a y 1k\n.ends\n"
+    for text, title, devices in (("Diode bridge rectifier circuit\nR1 a 0 1k\nV1 a 0 1\n", "Diode bridge rectifier circuit", 2),
+                                 ("Mixer with two local oscillator inputs\nR1 a 0 1k\nV1 a 0 1\n", "Mixer with two local oscillator inputs", 2),
+                                 ("XOR gate test\nR1 a 0 1k\nV1 a 0 1\n", "XOR gate test", 2), ("D1 a 0 dm\nV1 a 0 1\n" + cards, "", 2),
+                                 ("M1 d g 0 0 nch w=1u l=180n\nV1 d 0 1\nV2 g 0 1\n" + cards, "", 3), ("X1 a b inv\nV1 a 0 1\nR2 b 0 1k\n" + cards, "", 3)):
+        nl = parse_netlist_text(text)
+        assert (nl.title or "") == title and nl.num_devices == devices and len(nl.to_native()["elements"]) == devices, text
     # model cards in a library section, a sub-circuit in an included file, both relative to the deck
     (tmp_path / "models").mkdir()
     (tmp_path / "models" / "cmos.lib").write_text(
