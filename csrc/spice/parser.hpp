@@ -1,5 +1,5 @@
 // SPICE-subset reader: R, C, L, V, I, D, M and X lines, `.subckt` flattening (hierarchical names
-// `inst.node`), `.param`, `.model`, `.ic`, DC / PULSE / SIN / EXP / PWL sources, engineering suffixes, `+`
+// `inst.node`), `.param` (with + - * / expressions in quotes or braces), `.model`, `.ic`, DC / PULSE / SIN / EXP / PWL sources, engineering suffixes, `+`
 // continuation lines, and the partition directives `.ghost <net> <local node> <owner>` and
 // `.nodemap <name> <index>`. MOSFET cards are reduced to Level-1 parameters with process corner,
 // supply and temperature scaling applied at parse time.
@@ -68,7 +68,7 @@ struct Corner {
 class SpiceParser {
 public:
     std::map<std::string, ModelCard> models;
-    std::vector<std::string> warnings;
+    mutable std::vector<std::string> warnings;
     double tran_step = 0.0, tran_stop = 0.0;  // `.tran <step> <stop>` of the deck (0 when it has none): defaults for a run
 
     explicit SpiceParser(Corner c = {}) : corner_(std::move(c)) {
@@ -140,7 +140,7 @@ public:
                     for (size_t i = 1; i < tok.size(); ++i) {
                         size_t eq = tok[i].find('=');
                         double v;
-                        if (eq != std::string::npos && parse_scaled(tok[i].substr(eq + 1), v)) params_[lower(tok[i].substr(0, eq))] = v;
+                        if (eq != std::string::npos && try_value(tok[i].substr(eq + 1), v)) params_[lower(tok[i].substr(0, eq))] = v;  // may use earlier ones
                     }
                 } else if (first == ".MODEL" && tok.size() >= 3) {
                     ModelCard mc;
@@ -153,7 +153,7 @@ public:
                     for (auto& t : rest) {
                         size_t eq = t.find('=');
                         double v;
-                        if (eq != std::string::npos && parse_scaled(t.substr(eq + 1), v)) {
+                        if (eq != std::string::npos && try_value(t.substr(eq + 1), v)) {
                             std::string k = lower(t.substr(0, eq));
                             while (!k.empty() && k.front() == '(') k.erase(k.begin());
                             mc.params[k] = v;
@@ -209,6 +209,7 @@ private:
     std::string base_dir_;
     bool follow_includes_ = false;
     size_t included_bytes_ = 0;
+    mutable std::vector<std::string> unread_;  // fields already reported as unreadable
     std::vector<std::string> include_stack_;
     std::vector<GhostLink> ghosts_;
     std::vector<std::pair<std::string, double>> ic_raw_;
@@ -351,8 +352,18 @@ private:
     }
     static std::vector<std::string> split(const std::string& s) {
         // parentheses and commas become separators except that "PULSE(" keeps its name as a token
+        // ... and an expression in quotes or braces stays one token, blanks removed: '(w + 1u) / 2' -> '(w+1u)/2'
         std::string t;
-        for (char c : s) t += (c == '(' || c == ')' || c == ',') ? ' ' : c;
+        char closing = 0;
+        for (char c : s) {
+            if (closing) {
+                if (c == closing) closing = 0;
+                if (!std::isspace((unsigned char)c)) t += c;
+                continue;
+            }
+            if (c == '\'' || c == '{') { closing = c == '{' ? '}' : '\''; t += c; continue; }
+            t += (c == '(' || c == ')' || c == ',') ? ' ' : c;
+        }
         std::istringstream in(t);
         std::vector<std::string> out;
         std::string w;
@@ -374,11 +385,77 @@ private:
         while (!s.empty() && (s.back() == '\'' || s.back() == '}')) s.pop_back();
         auto it = params_.find(s);
         if (it != params_.end()) { out = it->second; return true; }
+        // arithmetic first where there is an operator: the number reader accepts trailing unit text, and "2*w" would read as 2
+        const bool marked = !raw.empty() && (raw.front() == '\'' || raw.front() == '{');
+        if (s.find_first_of("*/()") != std::string::npos || (marked && s.find_first_of("+-", 1) != std::string::npos)) {
+            size_t pos = 0;
+            double v = 0.0;
+            if (expr_sum(s, pos, v, 0) && pos == s.size() && std::isfinite(v)) { out = v; return true; }
+            if (marked) return false;
+        }
         return parse_scaled(s, out);
     }
+    // The value of a field; what cannot be read counts as 0 and is reported once per text.
     double value(const std::string& raw) const {
         double v = 0.0;
-        return try_value(raw, v) ? v : 0.0;
+        if (try_value(raw, v)) return v;
+        if (!raw.empty() && std::find(unread_.begin(), unread_.end(), raw) == unread_.end()) {
+            unread_.push_back(raw);
+            warnings.push_back("cannot evaluate '" + raw + "': taken as 0");
+        }
+        return 0.0;
+    }
+    // Arithmetic in parameter values: + - * / and parentheses over numbers with engineering suffixes and parameter
+    // names, e.g. '(w + 1u) / 2'. Recursive descent, at most 64 levels of parentheses.
+    bool expr_sum(const std::string& s, size_t& pos, double& out, int depth) const {
+        if (!expr_product(s, pos, out, depth)) return false;
+        while (pos < s.size() && (s[pos] == '+' || s[pos] == '-')) {
+            char op = s[pos++];
+            double rhs;
+            if (!expr_product(s, pos, rhs, depth)) return false;
+            out = op == '+' ? out + rhs : out - rhs;
+        }
+        return true;
+    }
+    bool expr_product(const std::string& s, size_t& pos, double& out, int depth) const {
+        if (!expr_factor(s, pos, out, depth)) return false;
+        while (pos < s.size() && (s[pos] == '*' || s[pos] == '/')) {
+            char op = s[pos++];
+            double rhs;
+            if (!expr_factor(s, pos, rhs, depth)) return false;
+            out = op == '*' ? out * rhs : out / rhs;
+        }
+        return true;
+    }
+    bool expr_factor(const std::string& s, size_t& pos, double& out, int depth) const {
+        if (pos >= s.size() || depth > 64) return false;
+        if (s[pos] == '-' || s[pos] == '+') {
+            bool neg = s[pos++] == '-';
+            if (!expr_factor(s, pos, out, depth + 1)) return false;
+            if (neg) out = -out;
+            return true;
+        }
+        if (s[pos] == '(') {
+            ++pos;
+            if (!expr_sum(s, pos, out, depth + 1) || pos >= s.size() || s[pos] != ')') return false;
+            ++pos;
+            return true;
+        }
+        // a number (its exponent may carry a sign: 1e-9) or a name, up to the next operator
+        size_t start = pos;
+        while (pos < s.size()) {
+            char c = s[pos];
+            if (c == '*' || c == '/' || c == '(' || c == ')') break;
+            if ((c == '+' || c == '-') && !(pos > start && (s[pos - 1] == 'e') && std::isdigit((unsigned char)s[start]) && pos + 1 < s.size() &&
+                                            std::isdigit((unsigned char)s[pos + 1])))
+                break;
+            ++pos;
+        }
+        std::string atom = s.substr(start, pos - start);
+        if (atom.empty()) return false;
+        auto it = params_.find(atom);
+        if (it != params_.end()) { out = it->second; return true; }
+        return parse_scaled(atom, out);
     }
     int node(const std::string& raw, const std::string& prefix, const std::map<std::string, std::string>& alias) {
         std::string n = lower(raw);

@@ -686,3 +686,22 @@ def test_solver_process_records_the_named_nets_only(tmp_path):
     full = run_nangila_waveform(str(deck), tstop=60e-12, dt=1e-12)
     part = run_nangila_waveform(str(deck), tstop=60e-12, dt=1e-12, nodes=["c"])
     assert part.node_names == ["c"] and np.allclose(part.traces["c"], full.traces["c"], atol=1e-12)
+
+
+def test_parameter_expressions():
+    deck = ("expressions in parameter values\n.param w=1u half='w/2' cl={2*(5f + 5f)} vhi=1.8 neg='-w+3u' tiny='1e-9*2'\nVDD vdd 0 vhi\n"
+            "VIN in 0 PULSE(0 vhi 100p 20p 20p 400p 1n)\nM1 out in vdd vdd pch W='2*w' L=180n\nM2 out in 0 0 nch W=half L='0.18u'\n"
+            "C1 out 0 cl\nC2 out 0 tiny\nR1 out 0 {1meg * (1 + 1)}\nR2 out 0 'nosuch*2'\nR3 out 0 neg\n"
+            ".model nch NMOS (VTO=0.45 KP='100u*2' LAMBDA=0.05)\n.model pch PMOS (VTO=-0.45 KP=100u LAMBDA=0.05)\n.end\n")
+    js, warnings = N.parse_spice(deck)
+    el = json.loads(js)["elements"]
+    beta = [e["Mosfet"]["model"]["beta"] for e in el if "Mosfet" in e]
+    assert np.allclose(beta, [100e-6 * 2e-6 / 180e-9, 200e-6 * 0.5e-6 / 0.18e-6])
+    caps = [e["Capacitor"]["c"] for e in el if "Capacitor" in e]
+    res = [e["Resistor"]["r"] for e in el if "Resistor" in e]
+    assert np.allclose(caps, [20e-15, 2e-9]) and np.allclose([res[0], res[2]], [2e6, 2e-6])
+    assert len(warnings) == 1 and "nosuch*2" in warnings[0]   # what cannot be evaluated is said, not silently zero
+    # plain numbers with unit text still read as before, and a keyword is not arithmetic
+    js, warnings = N.parse_spice("* units\nV1 a 0 DC 1.8V\nR1 a b 10kOhm\nC1 b 0 10pF\n.end\n")
+    el = json.loads(js)["elements"]
+    assert el[1]["Resistor"]["r"] == 1e4 and math.isclose(el[2]["Capacitor"]["c"], 1e-11) and not warnings
