@@ -136,6 +136,52 @@ PYBIND11_MODULE(_native, m) {
         return py::make_tuple(ok, ok ? out.voltages : e.seeded_state().voltages);
     });
 
+    // DC transfer curve: the voltage source between `node` and ground takes each of `values` in turn; every point starts
+    // Newton from the previous solution (continuation), which is what carries a bistable or steep circuit along its curve.
+    m.def("dc_sweep", [](const std::string& netlist_json, const std::string& node, std::vector<double> values) {
+        Netlist base = Netlist::from_json(Json::parse(netlist_json));
+        std::vector<std::string> names = base.names_or_default();
+        auto lower = [](std::string v) { for (auto& c : v) c = char(std::tolower((unsigned char)c)); return v; };
+        int idx = -1;
+        for (size_t i = 0; i < names.size(); ++i) if (lower(names[i]) == lower(node)) idx = int(i) + 1;
+        if (idx < 0) throw std::invalid_argument("dc_sweep: no net named '" + node + "'");
+        int which = -1;
+        double sign = 1.0;
+        for (size_t k = 0; k < base.elements.size(); ++k) {
+            const Element& e = base.elements[k];
+            if (e.kind != Element::VSource) continue;
+            if (e.a == idx && e.b == 0) { which = int(k); sign = 1.0; }
+            else if (e.b == idx && e.a == 0) { which = int(k); sign = -1.0; }
+        }
+        if (which < 0) throw std::invalid_argument("dc_sweep: no voltage source between '" + node + "' and ground");
+        const size_t n = size_t(base.num_nodes);
+        py::array_t<double> out({values.size(), n});
+        auto o = out.mutable_unchecked<2>();
+        std::vector<bool> converged;
+        std::vector<double> prev;
+        {
+            for (size_t p = 0; p < values.size(); ++p) {
+                Netlist nl = base;
+                nl.initial_conditions.clear();
+                nl.elements[size_t(which)].source = SourceWaveform::make_dc(sign * values[p]);
+                SolverEngine e(std::move(nl));
+                PartitionState seed = e.seeded_state(), sol(0);
+                if (!prev.empty()) {
+                    for (size_t i = 0; i < prev.size() && i < seed.voltages.size(); ++i) seed.voltages[i] = prev[i];
+                    seed.voltages[size_t(idx - 1)] = values[p];
+                }
+                bool ok = e.solve_dc(seed, sol);
+                converged.push_back(ok);
+                if (ok) prev = sol.voltages;
+                for (size_t i = 0; i < n; ++i) o(p, i) = ok && i < sol.voltages.size() ? sol.voltages[i] : std::nan("");
+            }
+        }
+        py::dict r;
+        r["node_names"] = names; r["sweep"] = values; r["values"] = out; r["converged"] = converged;
+        return r;
+    }, py::arg("netlist_json"), py::arg("node"), py::arg("values"),
+       "operating points over a swept source: {node_names, sweep, values[point, net], converged[point]}");
+
     m.def("simulate_partitioned", [](std::vector<std::string> parts_json, double tstop, double dt, double reltol, uint32_t predict_depth, bool compress,
                                      uint32_t record_every, unsigned threads, bool speculate) {
         std::vector<Netlist> parts;

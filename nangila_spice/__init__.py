@@ -25,7 +25,7 @@ _EXPORT_MAP = {
     "export_csv": (".merger", "export_csv"), "export_json": (".merger", "export_json"),
     "discover_hardware": (".orchestrator", "discover_hardware"), "HardwareTopology": (".orchestrator", "HardwareTopology"),
     "SimulationConfig": (".orchestrator", "SimulationConfig"), "SimulationResult": (".orchestrator", "SimulationResult"),
-    "run_simulation": (".orchestrator", "run_simulation"),
+    "run_simulation": (".orchestrator", "run_simulation"), "dc_sweep": (".orchestrator", "dc_sweep"),
     "PvtOrchestrator": (".pvt_orchestrator", "PvtOrchestrator"), "SweepConfig": (".pvt_orchestrator", "SweepConfig"),
     "SweepResult": (".pvt_orchestrator", "SweepResult"), "generate_corner_grid": (".pvt_orchestrator", "generate_corner_grid"),
     "simulate_corner": (".pvt_orchestrator", "simulate_corner"), "CornerSpec": (".pvt_orchestrator", "CornerSpec"),

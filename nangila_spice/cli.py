@@ -110,6 +110,25 @@ def invoke_view(args) -> int:
     return 0
 
 
+def invoke_dc(args) -> int:
+    from .merger import export_csv
+    from .orchestrator import dc_sweep
+
+    if not os.path.exists(args.netlist):
+        print(f"Error: netlist not found at {args.netlist}", file=sys.stderr)
+        return 1
+    try:
+        curve = dc_sweep(args.netlist, args.source, args.start, args.stop, args.step, process=args.process, vdd=args.vdd, temp=args.temp)
+    except (ValueError, RuntimeError) as exc:
+        print(f"Error: {exc}", file=sys.stderr)
+        return 1
+    if args.output:
+        export_csv(curve, args.output)   # first column: the swept voltage
+        print(f"wrote {args.output}")
+    print(curve.summary())
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="nangila", description="Nangila SPICE command line")
     sub = ap.add_subparsers(dest="command", required=True)
@@ -152,13 +171,23 @@ def main(argv=None) -> int:
     p.add_argument("--jobs", type=int, default=1, help="cases run at a time")
     p.add_argument("--output-json", default="artifacts/phase1_benchmark_report.json")
     p.add_argument("--output-md", default="artifacts/phase1_benchmark_report.md")
+    d = sub.add_parser("dc", help="DC transfer curves: sweep the voltage source on one net")
+    d.add_argument("netlist")
+    d.add_argument("--source", required=True, help="net held by the source to sweep (against ground)")
+    d.add_argument("--start", type=float, default=0.0)
+    d.add_argument("--stop", type=float, default=1.8)
+    d.add_argument("--step", type=float, default=0.05)
+    d.add_argument("--process", default="TT")
+    d.add_argument("--vdd", type=float, default=1.8)
+    d.add_argument("--temp", type=float, default=27.0)
+    d.add_argument("--output", default=None, help="CSV file (first column: the swept voltage)")
     v = sub.add_parser("view", help="show a .nz waveform file")
     v.add_argument("file")
     v.add_argument("--nodes", nargs="*")
     v.add_argument("--output", default=None)
     args = ap.parse_args(argv)
     return {"build": invoke_build, "run": invoke_run, "synth": invoke_synth, "sweep": invoke_sweep, "phase1-report": invoke_phase1_report,
-            "view": invoke_view}[args.command](args)
+            "view": invoke_view, "dc": invoke_dc}[args.command](args)
 
 
 if __name__ == "__main__":

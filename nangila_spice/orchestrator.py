@@ -271,3 +271,26 @@ def run_simulation(config: SimulationConfig) -> SimulationResult:
         if os.path.abspath(alias) != os.path.abspath(target):
             shutil.copyfile(target, alias)
     return result
+
+
+def dc_sweep(netlist_path: str, source_node: str, start: float, stop: float, step: float, process: str = "TT", vdd: float = 1.8,
+             temp: float = 27.0) -> Waveform:
+    """DC transfer curves: the voltage source that holds ``source_node`` (against ground) goes from ``start`` to ``stop``
+    in steps of ``step``; every point is an operating point found from the previous one. The result is a ``Waveform``
+    whose ``times`` are the swept voltages, so ``voltage()``, ``summary()`` and the exporters work on it; points where
+    Newton did not converge hold NaN. The reference has no DC analysis."""
+    import numpy as np
+
+    from . import _native
+    from .parser import parse_netlist
+
+    if step == 0 or (stop - start) * step < 0:
+        raise ValueError("step must be non-zero and point from start to stop")
+    count = int(np.floor((stop - start) / step + 1e-9)) + 1
+    values = [start + i * step for i in range(count)]
+    flat = parse_netlist(netlist_path).to_native(process, vdd, temp)
+    flat.pop("warnings", None)
+    r = _native.dc_sweep(json.dumps(flat), source_node, values)
+    vals = np.asarray(r["values"], dtype=np.float64)
+    traces = {name: vals[:, j] for j, name in enumerate(r["node_names"]) if j < vals.shape[1]}
+    return Waveform(np.asarray(values, dtype=np.float64), traces, f"dc sweep of {source_node}")

@@ -468,3 +468,27 @@ def test_simulate_keeps_the_requested_nets_only():
     assert res.success and res.waveform.node_names == ["out"] and res.waveform.num_points == 201
     full = ns.simulate(os.path.join(root, "inverter.sp"), tstop=2e-10, dt=1e-12)
     assert np.array_equal(res.waveform.traces["out"], full.waveform.traces["out"]) and len(full.waveform.node_names) == 4
+
+
+def test_dc_sweep_transfer_curves(tmp_path):
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "reference_circuits")
+    vtc = ns.dc_sweep(os.path.join(root, "inverter.sp"), "in", 0.0, 1.8, 0.05)
+    vin, out = vtc.times, vtc.traces["out"]
+    assert len(vin) == 37 and out[0] > 1.79 and abs(out[-1]) < 1e-6 and np.all(np.diff(out) <= 1e-9) and not np.isnan(out).any()
+    assert abs(vin[np.argmin(np.abs(out - 0.9))] - 0.9) < 0.051   # the deck's pull-up and pull-down are matched
+    gain = np.abs(np.diff(out) / np.diff(vin)).max()
+    assert gain > 5.0                                             # and the curve is steep at the threshold
+    # a linear divider follows the source exactly; a downward sweep works too
+    deck = tmp_path / "div.sp"
+    deck.write_text("* divider\nV1 a 0 DC 1\nR1 a b 3k\nR2 b 0 1k\n.end\n")
+    lin = ns.dc_sweep(str(deck), "A", 2.0, -2.0, -0.5)
+    assert np.allclose(lin.traces["b"], 0.25 * lin.times, atol=1e-9) and list(lin.times[:2]) == [2.0, 1.5] and len(lin.times) == 9
+    with pytest.raises(ValueError):
+        ns.dc_sweep(str(deck), "b", 0.0, 1.0, 0.1)    # b is not held by a source
+    with pytest.raises(ValueError):
+        ns.dc_sweep(str(deck), "a", 0.0, 1.0, -0.1)   # the step points away from stop
+    run = subprocess.run([sys.executable, "-m", "nangila_spice.cli", "dc", os.path.join(root, "inverter.sp"), "--source", "in", "--step", "0.1",
+                          "--output", str(tmp_path / "vtc.csv")], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0 and "dc sweep of in" in run.stdout, run.stdout + run.stderr
+    rows = (tmp_path / "vtc.csv").read_text().splitlines()
+    assert rows[0].startswith("time,") and "V(out)" in rows[0] and len(rows) == 20
