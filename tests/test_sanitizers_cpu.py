@@ -104,6 +104,25 @@ def test_solver_process_under_sanitizers(built):
             f.write(data)
         r = subprocess.run([node, "--partition", path, "--tstop", "2e-11", "--dt", "1e-12"], capture_output=True, text=True, timeout=300)
         assert r.returncode >= 0 and _clean(r.stderr), (trial, r.returncode, r.stderr[-3000:])
+    # decks written to strain the reader itself: arithmetic, quoting, source cards, includes
+    hostile = [
+        "* deep\n.param a='" + "(" * 5000 + "1" + ")" * 5000 + "'\nR1 x 0 a\nV1 x 0 1\n.end\n",
+        "* unbalanced\n.param a='((1+2)' b={3*(4 c='5\nR1 x 0 'a*\nV1 x 0 {b\n.end\n",
+        "* division\n.param z='1/0' n='0/0' big='1e308*1e308'\nR1 x 0 z\nR2 x 0 n\nC1 x 0 big\nV1 x 0 1\n.end\n",
+        "* operators\nR1 x 0 '*'\nR2 x 0 '1**2'\nR3 x 0 '--++-1'\nR4 x 0 '1e'\nR5 x 0 '1e+'\nV1 x 0 '()'\n.end\n",
+        "* sources\nV1 a 0 PWL(0)\nV2 b 0 PWL(1n 1 0 0 1n 2)\nV3 c 0 SIN()\nV4 d 0 EXP(0 1 0 0 0 0)\nV5 e 0 PWL\nI1 0 f SIN(0 1 1e30 -1 1e30 1e30)\n"
+        "R1 a 0 1\nR2 b 0 1\nR3 c 0 1\nR4 d 0 1\nR5 e 0 1\nR6 f 0 1\n.end\n",
+        "* includes\n.include\n.include ''\n.lib\n.lib fuzzed.sp\n.lib fuzzed.sp nosuch\n.include fuzzed.sp\n.include /\n.include /dev/null\nR1 x 0 1\nV1 x 0 1\n.end\n",
+        "M",
+        "X1 a b c\n",
+        ".tran\n.tran x y\n.tran 0 0\n.tran -1 -1\nR1 x 0 1\nV1 x 0 1\n",
+    ]
+    for k, text in enumerate(hostile):
+        path = os.path.join(tmp, "fuzzed.sp")
+        with open(path, "w") as f:
+            f.write(text)
+        r = subprocess.run([node, "--partition", path, "--tstop", "2e-11", "--dt", "1e-12"], capture_output=True, text=True, timeout=300)
+        assert r.returncode >= 0 and _clean(r.stderr), (k, r.returncode, r.stderr[-3000:])
     assert json.load(open(os.path.join(tmp, "w.json")))["stats"]["completed"] is True
 
 
