@@ -387,7 +387,7 @@ private:
         if (it != params_.end()) { out = it->second; return true; }
         // arithmetic first where there is an operator: the number reader accepts trailing unit text, and "2*w" would read as 2
         const bool marked = !raw.empty() && (raw.front() == '\'' || raw.front() == '{');
-        if (s.find_first_of("*/()") != std::string::npos || (marked && s.find_first_of("+-", 1) != std::string::npos)) {
+        if (s.find_first_of("*/()^") != std::string::npos || (marked && s.find_first_of("+-", 1) != std::string::npos)) {
             size_t pos = 0;
             double v = 0.0;
             if (expr_sum(s, pos, v, 0) && pos == s.size() && std::isfinite(v)) { out = v; return true; }
@@ -405,8 +405,9 @@ private:
         }
         return 0.0;
     }
-    // Arithmetic in parameter values: + - * / and parentheses over numbers with engineering suffixes and parameter
-    // names, e.g. '(w + 1u) / 2'. Recursive descent, at most 64 levels of parentheses.
+    // Arithmetic in parameter values: + - * / ** (or ^), parentheses and sqrt abs exp ln log log10 pow min max over numbers
+    // with engineering suffixes and parameter names, e.g. '(w + 1u) / 2' or 'sqrt(2*kp*i)'. Recursive descent, at most 64
+    // levels of nesting.
     bool expr_sum(const std::string& s, size_t& pos, double& out, int depth) const {
         if (!expr_product(s, pos, out, depth)) return false;
         while (pos < s.size() && (s[pos] == '+' || s[pos] == '-')) {
@@ -419,7 +420,7 @@ private:
     }
     bool expr_product(const std::string& s, size_t& pos, double& out, int depth) const {
         if (!expr_factor(s, pos, out, depth)) return false;
-        while (pos < s.size() && (s[pos] == '*' || s[pos] == '/')) {
+        while (pos < s.size() && (s[pos] == '*' || s[pos] == '/') && !(s[pos] == '*' && pos + 1 < s.size() && s[pos + 1] == '*')) {
             char op = s[pos++];
             double rhs;
             if (!expr_factor(s, pos, rhs, depth)) return false;
@@ -427,11 +428,23 @@ private:
         }
         return true;
     }
+    // A primary with an optional power: a ** b or a ^ b, right to left, binding tighter than a sign in front of it.
     bool expr_factor(const std::string& s, size_t& pos, double& out, int depth) const {
+        if (!expr_primary(s, pos, out, depth)) return false;
+        size_t len = pos + 1 < s.size() && s[pos] == '*' && s[pos + 1] == '*' ? 2 : (pos < s.size() && s[pos] == '^' ? 1 : 0);
+        if (len) {
+            pos += len;
+            double e;
+            if (depth > 64 || !expr_factor(s, pos, e, depth + 1)) return false;
+            out = std::pow(out, e);
+        }
+        return true;
+    }
+    bool expr_primary(const std::string& s, size_t& pos, double& out, int depth) const {
         if (pos >= s.size() || depth > 64) return false;
         if (s[pos] == '-' || s[pos] == '+') {
             bool neg = s[pos++] == '-';
-            if (!expr_factor(s, pos, out, depth + 1)) return false;
+            if (!expr_factor(s, pos, out, depth + 1)) return false;  // -2**2 is -(2**2)
             if (neg) out = -out;
             return true;
         }
@@ -445,7 +458,7 @@ private:
         size_t start = pos;
         while (pos < s.size()) {
             char c = s[pos];
-            if (c == '*' || c == '/' || c == '(' || c == ')') break;
+            if (c == '*' || c == '/' || c == '(' || c == ')' || c == ',' || c == '^') break;
             if ((c == '+' || c == '-') && !(pos > start && (s[pos - 1] == 'e') && std::isdigit((unsigned char)s[start]) && pos + 1 < s.size() &&
                                             std::isdigit((unsigned char)s[pos + 1])))
                 break;
@@ -453,6 +466,29 @@ private:
         }
         std::string atom = s.substr(start, pos - start);
         if (atom.empty()) return false;
+        if (pos < s.size() && s[pos] == '(') {  // a function call: sqrt abs exp ln log log10 pow min max
+            ++pos;
+            std::vector<double> args;
+            for (;;) {
+                double a;
+                if (!expr_sum(s, pos, a, depth + 1) || pos >= s.size()) return false;
+                args.push_back(a);
+                if (s[pos] == ',') { ++pos; continue; }
+                if (s[pos] == ')') { ++pos; break; }
+                return false;
+            }
+            const size_t n = args.size();
+            if (atom == "sqrt" && n == 1) out = std::sqrt(args[0]);
+            else if (atom == "abs" && n == 1) out = std::fabs(args[0]);
+            else if (atom == "exp" && n == 1) out = std::exp(args[0]);
+            else if ((atom == "ln" || atom == "log") && n == 1) out = std::log(args[0]);
+            else if (atom == "log10" && n == 1) out = std::log10(args[0]);
+            else if ((atom == "pow" || atom == "pwr") && n == 2) out = std::pow(args[0], args[1]);
+            else if (atom == "min" && n >= 1) out = *std::min_element(args.begin(), args.end());
+            else if (atom == "max" && n >= 1) out = *std::max_element(args.begin(), args.end());
+            else return false;
+            return true;
+        }
         auto it = params_.find(atom);
         if (it != params_.end()) { out = it->second; return true; }
         return parse_scaled(atom, out);

@@ -701,6 +701,18 @@ def test_parameter_expressions():
     res = [e["Resistor"]["r"] for e in el if "Resistor" in e]
     assert np.allclose(caps, [20e-15, 2e-9]) and np.allclose([res[0], res[2]], [2e6, 2e-6])
     assert len(warnings) == 1 and "nosuch*2" in warnings[0]   # what cannot be evaluated is said, not silently zero
+    # powers (right to left, tighter than a leading sign) and the usual functions; what is undefined is refused
+    def dc(expr):
+        text, notes = N.parse_spice(f"* e\n.param p=3.5 q=0.25\nV1 a 0 DC '{expr}'\nR1 a 0 1k\n.end\n")
+        return json.loads(text)["elements"][0]["VoltageSource"]["source"]["Dc"], notes
+
+    for expr, want in (("2**3", 8), ("2^3^2", 512), ("-2**2", -4), ("2*3**2", 18), ("sqrt(16)+abs(-3)", 7), ("max(1, p, q) * min(4, 8)", 14),
+                       ("pow(p, 2)", 12.25), ("exp(ln(5))", 5), ("log10(1000)", 3), ("sqrt(2*(p+q))", math.sqrt(7.5)), ("10k/4", 2500)):
+        got, notes = dc(expr)
+        assert math.isclose(got, want, rel_tol=1e-12) and not notes, expr
+    for expr in ("nosuch(3)", "sqrt(-1)", "min()", "pow(2)", "2**", "(1,2)"):
+        got, notes = dc(expr)
+        assert got == 0 and notes, expr
     # plain numbers with unit text still read as before, and a keyword is not arithmetic
     js, warnings = N.parse_spice("* units\nV1 a 0 DC 1.8V\nR1 a b 10kOhm\nC1 b 0 10pF\n.end\n")
     el = json.loads(js)["elements"]
