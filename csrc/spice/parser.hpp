@@ -425,6 +425,7 @@ private:
             double rhs;
             if (!expr_factor(s, pos, rhs, depth)) return false;
             out = op == '*' ? out * rhs : out / rhs;
+            if (!std::isfinite(out)) return false;
         }
         return true;
     }
@@ -437,6 +438,7 @@ private:
             double e;
             if (depth > 64 || !expr_factor(s, pos, e, depth + 1)) return false;
             out = std::pow(out, e);
+            if (!std::isfinite(out)) return false;  // 0 ** -1 and the like: refused here, before a later step hides it
         }
         return true;
     }
@@ -487,7 +489,7 @@ private:
             else if (atom == "min" && n >= 1) out = *std::min_element(args.begin(), args.end());
             else if (atom == "max" && n >= 1) out = *std::max_element(args.begin(), args.end());
             else return false;
-            return true;
+            return std::isfinite(out);
         }
         auto it = params_.find(atom);
         if (it != params_.end()) { out = it->second; return true; }

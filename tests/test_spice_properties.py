@@ -190,7 +190,11 @@ def _expressions():
 
     def combine(children):
         binary = st.tuples(children, st.sampled_from(["+", "-", "*", "/"]), children).map(lambda t: f"{t[0]}{t[1]}{t[2]}")
-        return st.one_of(binary, children.map(lambda c: f"({c})"), children.map(lambda c: f"-({c})"))
+        power = st.one_of(st.tuples(children, st.sampled_from(["**2", "**3", "**-1"])).map(lambda t: f"({t[0]}){t[1]}"),
+                          children.map(lambda c: f"(abs({c}))**0.5"))   # Python turns a root of a negative number into a complex one
+        call = st.one_of(children.map(lambda c: f"sqrt(abs({c}))"), st.tuples(children, children).map(lambda t: f"max({t[0]},{t[1]})"),
+                         st.tuples(children, children).map(lambda t: f"min({t[0]},{t[1]})"))
+        return st.one_of(binary, children.map(lambda c: f"({c})"), children.map(lambda c: f"-({c})"), power, call)
 
     return st.recursive(number, combine, max_leaves=12)
 
@@ -198,17 +202,22 @@ def _expressions():
 @RUN
 @given(_expressions(), st.booleans())
 def test_parameter_arithmetic_agrees_with_python(expr, spaced):
-    """An expression over numbers, two parameters, + - * / and parentheses has the value Python gives it (blanks inside
+    """An expression over numbers, two parameters, + - * / **, parentheses, sqrt, abs, min and max has the value Python gives it (blanks inside
     the quotes do not matter); one that divides by zero or overflows is refused with a warning instead of a value."""
     import json
 
     p, q = 3.5, 0.25
     try:
-        want = eval(expr, {"__builtins__": {}}, {"p": p, "q": q})  # noqa: S307 - the grammar above produces arithmetic only
-    except ZeroDivisionError:
+        want = eval(expr, {"__builtins__": {}}, {"p": p, "q": q, "sqrt": np.sqrt, "abs": abs, "min": min, "max": max})  # noqa: S307 - arithmetic only
+    except (ZeroDivisionError, OverflowError):
         want = None
-    if want is not None and not np.isfinite(want):
-        want = None
+    if want is not None and not isinstance(want, complex):
+        try:
+            want = float(want)   # integers are exact and unbounded in Python
+        except OverflowError:
+            want = None
+    if want is not None and (isinstance(want, complex) or not np.isfinite(want)):
+        want = None   # a root of a negative number, an overflow
     shown = expr.replace("+", " + ").replace("*", " * ") if spaced and "e +" not in expr.replace("+", " + ") else expr
     js, warnings = N.parse_spice(f"* arithmetic\n.param p={p} q={q}\nV1 a 0 DC '{shown}'\nR1 a 0 1k\n.end\n")
     got = json.loads(js)["elements"][0]["VoltageSource"]["source"]["Dc"]
