@@ -1,5 +1,5 @@
 // SPICE-subset reader: R, C, L, V, I, D, M and X lines, `.subckt` flattening (hierarchical names
-// `inst.node`), `.param` (with + - * / expressions in quotes or braces), `.model`, `.ic`, DC / PULSE / SIN / EXP / PWL sources, engineering suffixes, `+`
+// `inst.node`), `.param` (with + - * / expressions in quotes or braces), `.global`, `.model`, `.ic`, DC / PULSE / SIN / EXP / PWL sources, engineering suffixes, `+`
 // continuation lines, and the partition directives `.ghost <net> <local node> <owner>` and
 // `.nodemap <name> <index>`. MOSFET cards are reduced to Level-1 parameters with process corner,
 // supply and temperature scaling applied at parse time.
@@ -9,6 +9,7 @@
 #include <cctype>
 #include <fstream>
 #include <map>
+#include <set>
 #include <sstream>
 #include <unordered_map>
 
@@ -136,7 +137,9 @@ public:
                     if (--depth <= 0) { depth = 0; cur = nullptr; continue; }
                 }
                 if (cur) { cur->lines.push_back(st); continue; }
-                if (first == ".PARAM") {
+                if (first == ".GLOBAL") {
+                    for (size_t i = 1; i < tok.size(); ++i) globals_.insert(lower(tok[i]));
+                } else if (first == ".PARAM") {
                     for (size_t i = 1; i < tok.size(); ++i) {
                         size_t eq = tok[i].find('=');
                         double v;
@@ -206,6 +209,7 @@ private:
     std::vector<Element> elements_;
     std::map<std::string, Subckt> subckts_;
     std::map<std::string, double> params_;
+    std::set<std::string> globals_;  // nets named by `.global`
     std::string base_dir_;
     bool follow_includes_ = false;
     size_t included_bytes_ = 0;
@@ -501,7 +505,7 @@ private:
         std::string full;
         auto al = alias.find(n);
         if (al != alias.end()) full = al->second;
-        else if (prefix.empty()) full = n;
+        else if (prefix.empty() || globals_.count(n)) full = n;  // a `.global` net is the same net inside every sub-circuit
         else full = prefix + "." + n;
         if (full == "0" || full == "gnd") return 0;
         auto it = node_map_.find(full);
@@ -514,7 +518,7 @@ private:
         if (n == "0" || n == "gnd") return "0";
         auto al = alias.find(n);
         if (al != alias.end()) return al->second;
-        return prefix.empty() ? n : prefix + "." + n;
+        return prefix.empty() || globals_.count(n) ? n : prefix + "." + n;
     }
     SourceWaveform source(const std::vector<std::string>& tok, size_t from, bool scale_supply) const {
         SourceWaveform w = SourceWaveform::make_dc(0.0);

@@ -717,3 +717,18 @@ def test_parameter_expressions():
     js, warnings = N.parse_spice("* units\nV1 a 0 DC 1.8V\nR1 a b 10kOhm\nC1 b 0 10pF\n.end\n")
     el = json.loads(js)["elements"]
     assert el[1]["Resistor"]["r"] == 1e4 and math.isclose(el[2]["Capacitor"]["c"], 1e-11) and not warnings
+
+
+def test_global_nets_reach_into_nested_subcircuits():
+    deck = ("* globals\n.global vdd\n.subckt inv a y\nMP y a vdd vdd pch w=2u l=180n\nMN y a 0 0 nch w=1u l=180n\n.ends\n"
+            ".subckt buf a y\nX1 a m inv\nX2 m y inv\n.ends\nVDD vdd 0 1.8\nVIN in 0 0\nX1 in out inv\nX2 in out2 buf\n"
+            ".model nch NMOS (vto=0.45 kp=200u)\n.model pch PMOS (vto=-0.45 kp=100u)\n.end\n")
+    js, warnings = N.parse_spice(deck)
+    names = json.loads(js)["node_names"]
+    assert names == ["vdd", "in", "out", "out2", "x2.m"] and not warnings   # no private copy of the supply inside an instance
+    ok, v = N.dc_operating_point(js)
+    assert ok and np.allclose(v[:5], [1.8, 0.0, 1.8, 0.0, 1.8], atol=1e-6)
+    from nangila_spice.parser import parse_netlist_text
+
+    flat = parse_netlist_text(deck).flatten()   # the text-level view agrees
+    assert sorted({n.lower() for d in flat.devices for n in d.nodes}) == ["0", "in", "out", "out2", "vdd", "x2.m"]
