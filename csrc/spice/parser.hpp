@@ -127,9 +127,12 @@ public:
                     if (depth++ == 0 && tok.size() >= 2) {
                         cur = &subckts_[upper(tok[1])];
                         cur->ports.clear();
+                        cur->defaults.clear();
                         for (size_t i = 2; i < tok.size(); ++i) {
-                            if (tok[i].find('=') != std::string::npos) break;
-                            cur->ports.push_back(lower(tok[i]));
+                            size_t eq = tok[i].find('=');
+                            if (eq != std::string::npos) { cur->defaults.emplace_back(lower(tok[i].substr(0, eq)), tok[i].substr(eq + 1)); continue; }
+                            if (upper(tok[i]) == "PARAMS:") continue;
+                            if (cur->defaults.empty()) cur->ports.push_back(lower(tok[i]));
                         }
                         continue;
                     }
@@ -202,7 +205,7 @@ public:
     }
 
 private:
-    struct Subckt { std::vector<std::string> ports, lines; };
+    struct Subckt { std::vector<std::string> ports, lines; std::vector<std::pair<std::string, std::string>> defaults; };  // defaults: name, value text
     Corner corner_;
     std::unordered_map<std::string, int> node_map_;
     int next_node_ = 1;
@@ -210,6 +213,7 @@ private:
     std::map<std::string, Subckt> subckts_;
     std::map<std::string, double> params_;
     std::set<std::string> globals_;  // nets named by `.global`
+    int instance_depth_ = 0;
     std::string base_dir_;
     bool follow_includes_ = false;
     size_t included_bytes_ = 0;
@@ -614,14 +618,16 @@ private:
             case 'M':
                 if (tok.size() >= 6) {
                     int d = N(1), g = N(2), s = N(3), b = N(4);
-                    double w = 1e-6, l = 100e-9;
+                    double w = 1e-6, l = 100e-9, mult = 1.0;
                     for (size_t i = 6; i < tok.size(); ++i) {
                         size_t eq = tok[i].find('=');
                         if (eq == std::string::npos) continue;
                         std::string k = lower(tok[i].substr(0, eq));
                         if (k == "w") w = value(tok[i].substr(eq + 1));
                         else if (k == "l") l = value(tok[i].substr(eq + 1));
+                        else if (k == "m") mult = value(tok[i].substr(eq + 1));
                     }
+                    if (mult > 0.0) w *= mult;  // m devices in parallel are one device of m times the width (current and width-scaled capacitances)
                     elements_.push_back(Element::mosfet(d, g, s, b, mos_model(upper(tok[5]), w, l)));
                     // Constant device capacitances, where the model card gives them (SPICE level-1 names): gate overlap
                     // cgso / cgdo in F per metre of width, zero-bias junction cbd / cbs in F. Their bias dependence and the
@@ -654,9 +660,35 @@ private:
                     inner[def.ports[i]] = resolved_name(tok[i + 1], prefix, alias);
                 }
                 std::string np = prefix.empty() ? lower(tok[0]) : prefix + "." + lower(tok[0]);
-                for (auto& ln : def.lines) {
-                    auto t = split(ln);
-                    if (!t.empty()) element_line(t, np, inner);
+                // parameters of the instance: the sub-circuit's defaults, then what the X line gives, each evaluated in the
+                // caller's scope; they shadow outer parameters of the same name while the body is expanded
+                std::vector<std::pair<std::string, double>> scope;
+                for (auto& d : def.defaults) { double v; if (try_value(d.second, v)) scope.emplace_back(d.first, v); }
+                for (size_t i = last + 1; i < tok.size(); ++i) {
+                    size_t eq = tok[i].find('=');
+                    double v;
+                    if (eq == std::string::npos || !try_value(tok[i].substr(eq + 1), v)) continue;
+                    std::string k = lower(tok[i].substr(0, eq));
+                    bool found = false;
+                    for (auto& kv : scope) if (kv.first == k) { kv.second = v; found = true; }
+                    if (!found) scope.emplace_back(k, v);
+                }
+                std::vector<std::pair<std::string, std::pair<bool, double>>> saved;
+                for (auto& kv : scope) {
+                    auto old = params_.find(kv.first);
+                    saved.push_back({kv.first, {old != params_.end(), old != params_.end() ? old->second : 0.0}});
+                    params_[kv.first] = kv.second;
+                }
+                if (++instance_depth_ <= 64)
+                    for (auto& ln : def.lines) {
+                        auto t = split(ln);
+                        if (!t.empty()) element_line(t, np, inner);
+                    }
+                else warnings.push_back("sub-circuits nested more than 64 deep at '" + tok[0] + "'");
+                --instance_depth_;
+                for (auto& sv : saved) {
+                    if (sv.second.first) params_[sv.first] = sv.second.second;
+                    else params_.erase(sv.first);
                 }
                 return;
             }

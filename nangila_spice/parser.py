@@ -208,7 +208,7 @@ def parse_netlist_text(text: str, path: Optional[str] = None) -> Netlist:
         head = st.split()[0].upper()
         if head == ".SUBCKT":
             tok = st.split()
-            ports = [t for t in tok[2:] if "=" not in t]
+            ports = [t for t in tok[2:] if "=" not in t and t.upper() != "PARAMS:"]
             current = Subcircuit(name=tok[1].upper(), ports=ports)
             continue
         if head == ".ENDS":

@@ -732,3 +732,23 @@ def test_global_nets_reach_into_nested_subcircuits():
 
     flat = parse_netlist_text(deck).flatten()   # the text-level view agrees
     assert sorted({n.lower() for d in flat.devices for n in d.nodes}) == ["0", "in", "out", "out2", "vdd", "x2.m"]
+
+
+def test_subcircuit_parameters_and_device_multiplier():
+    deck = ("* parameters of sub-circuits\n.param r1=10k\n.subckt rdiv top mid r1=1k r2=1k\nR1 top mid r1\nR2 mid 0 'r2*2'\n.ends\n"
+            ".subckt two top mid PARAMS: scale=1\nX1 top mid rdiv r1='1k*scale' r2='500*scale'\n.ends\n"
+            "V1 a 0 4\nX1 a m1 rdiv\nX2 a m2 rdiv r1=3k r2=500\nX3 a m3 two scale=2\nR9 a 0 r1\n"
+            "M1 d g 0 0 nch w=1u l=180n m=4\nVD d 0 1\nVG g 0 1\n.model nch NMOS (vto=0.45 kp=200u)\n.end\n")
+    js, warnings = N.parse_spice(deck)
+    nl = json.loads(js)
+    res = [e["Resistor"]["r"] for e in nl["elements"] if "Resistor" in e]
+    # defaults, overrides on the X line, a parameter handed down two levels, and the outer r1 intact afterwards
+    assert res == [1e3, 2e3, 3e3, 1e3, 2e3, 2e3, 1e4] and not warnings
+    beta = [e["Mosfet"]["model"]["beta"] for e in nl["elements"] if "Mosfet" in e][0]
+    assert math.isclose(beta, 4 * 200e-6 * 1e-6 / 180e-9)   # m = 4: four devices in parallel
+    ok, v = N.dc_operating_point(js)
+    by = dict(zip(nl["node_names"], v))
+    assert ok and np.allclose([by["m1"], by["m2"], by["m3"]], [4 * 2 / 3, 1.0, 2.0], atol=1e-6)
+    # a sub-circuit that calls itself ends with a warning instead of a stack overflow
+    js, warnings = N.parse_spice("* loop\n.subckt a x\nX1 x a\nR1 x 0 1k\n.ends\nV1 n 0 1\nX0 n a\n.end\n")
+    assert any("nested more than" in w for w in warnings)
